@@ -1,0 +1,8 @@
+// Activation codes shared by the GEMM epilogues and the elementwise kernels.
+#pragma once
+#define NB_ACT_NONE 0
+#define NB_ACT_RELU 1
+#define NB_ACT_TANH 2
+#define NB_ACT_GELU 3   // tanh approximation
+#define NB_ACT_SILU 4
+#define NB_ACT_SIGMOID 5

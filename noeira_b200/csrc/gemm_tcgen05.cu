@@ -1,0 +1,410 @@
+// bf16 GEMM on the 5th generation tensor cores: D = epilogue(A · B), fp32 accumulation in TMEM.
+//
+//   * operands are fetched by TMA (128-byte swizzle, no multicast) into a multi-stage shared
+//     memory ring; one elected thread issues tcgen05.mma (M=128, N=BN, K=16) four times per
+//     64-wide k-block; tcgen05.commit releases the stage / publishes the accumulator;
+//   * persistent CTAs (one per SM) walk the tile list; two TMEM accumulators let the epilogue
+//     of tile i overlap the main loop of tile i+1;
+//   * warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+//     warps 2..5 = epilogue (TMEM quarter = warp_id % 4);
+//   * both operands may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major), so
+//     forward (x·W, W stored [IN, OUT]), dgrad (dy·Wᵀ) and wgrad (xᵀ·dy) all run from the
+//     natural layouts without a transpose pass;
+//   * epilogue: +bias[n], activation, or multiplication by the activation derivative taken from
+//     a saved tensor (dgrad of tanh / relu / gelu / silu), optional accumulate into fp32 output
+//     (dW += …), bf16 or fp32 store;
+//   * every mbarrier wait is bounded; on a timeout the CTA records it in `status`, all roles
+//     drain, TMEM is released and the kernel returns.
+//
+// Counterpart in the reference: library GEMMs only (cuBLAS / cuBLASLt epilogues / MAX matmul;
+// noeira/nn/primitives/linear.mojo:1295-1387, noeira/nn/core/cublaslt_gemm.mojo:66-73).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_api.h"
+
+namespace {
+
+using namespace nb;
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;  // operand majors
+  int ldd;         // output row pitch (elements)
+  int ld_aux;      // aux row pitch (elements, bf16)
+  int out_f32, accumulate, act, dact;
+  int tiles_m, tiles_n, num_kb;
+  float alpha;
+  void* D;
+  const float* bias;
+  const __nv_bfloat16* aux;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float act_apply(int act, float v) {
+  switch (act) {
+    case NB_ACT_RELU: return fmaxf(v, 0.f);
+    case NB_ACT_TANH: return tanhf(v);
+    case NB_ACT_GELU: {
+      const float c = 0.7978845608028654f;
+      return 0.5f * v * (1.f + tanhf(c * (v + 0.044715f * v * v * v)));
+    }
+    case NB_ACT_SILU: return v / (1.f + __expf(-v));
+    case NB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
+    default: return v;
+  }
+}
+// derivative factor from the SAVED tensor: tanh/relu/sigmoid save the output y, gelu/silu save the input x
+__device__ __forceinline__ float dact_apply(int dact, float s) {
+  switch (dact) {
+    case NB_ACT_RELU: return s > 0.f ? 1.f : 0.f;
+    case NB_ACT_TANH: return 1.f - s * s;
+    case NB_ACT_SIGMOID: return s * (1.f - s);
+    case NB_ACT_GELU: {
+      const float c = 0.7978845608028654f;
+      const float u = c * (s + 0.044715f * s * s * s);
+      const float t = tanhf(u);
+      return 0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * s * s);
+    }
+    case NB_ACT_SILU: {
+      const float sg = 1.f / (1.f + __expf(-s));
+      return sg * (1.f + s * (1.f - sg));
+    }
+    default: return 1.f;
+  }
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb_) {
+  constexpr int GM = 8;
+  const int per_group = GM * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * GM;
+  const int gsz = min(tiles_m - first_m, GM);
+  const int in_group = tile - group * per_group;
+  mb = first_m + in_group % gsz;
+  nb_ = in_group / gsz;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2;
+  constexpr uint32_t B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb_;
+        tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, 1)) { ok = false; *abort_flag = 1; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, mb * BM);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BM / 64; ++h)
+              tma_load_2d(sa + h * (64 * BK * 2), &tmA, &full_bar[stage], mb * BM + h * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], kb * BK, nb_ * BN);
+          } else {
+#pragma unroll
+            for (int h = 0; h < (BN + 63) / 64; ++h)
+              tma_load_2d(sb + h * (64 * BK * 2), &tmB, &full_bar[stage], nb_ * BN + h * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc(1u, BM, BN, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (*abort_flag || !mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, p.status, 2)) { ok = false; *abort_flag = 1; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (*abort_flag || !mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; *abort_flag = 1; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: advance 32 bytes inside the 128B swizzle row; MN-major: 16 k-rows of 128 B
+            const uint64_t adesc = p.a_mn ? make_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
+                                          : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
+            const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
+                                          : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int mb, nb_;
+      tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
+      if (*abort_flag || !mbar_wait(&tfull_bar[acc], acc_phase, p.status, 4)) { ok = false; *abort_flag = 1; break; }
+      tc_fence_after();
+      const int row = mb * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0);
+        tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
+        const int col0 = nb_ * BN + c0;
+        if (row_ok && col0 < p.N) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          const bool full = (col0 + 16 <= p.N);
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (full || col0 + j < p.N) v[j] += p.bias[col0 + j];
+          }
+          if (p.act) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = act_apply(p.act, v[j]);
+          }
+          if (p.dact) {
+            const __nv_bfloat16* ax = p.aux + (size_t)row * p.ld_aux + col0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (full || col0 + j < p.N) v[j] *= dact_apply(p.dact, __bfloat162float(ax[j]));
+          }
+          if (p.out_f32) {
+            float* o = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
+            if (full && (p.ldd % 4 == 0)) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                float4 x = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (p.accumulate) {
+                  const float4 y = *reinterpret_cast<float4*>(o + j);
+                  x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = x;
+              }
+            } else {
+              for (int j = 0; j < 16 && col0 + j < p.N; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
+            if (full && (p.ldd % 8 == 0)) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]),
+                               h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(o + j) = pk;
+              }
+            } else {
+              for (int j = 0; j < 16 && col0 + j < p.N; ++j) o[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: inner extent `inner` (contiguous), outer extent `outer`, row pitch `ld` elements.
+int make_tmap_bf16(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
+                   int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return NB_ERR_NO_DRIVER_SYMBOL;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return NB_ERR_UNALIGNED;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? NB_OK : NB_ERR_TENSORMAP;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  p.tiles_m = ceil_div(p.M, BM);
+  p.tiles_n = ceil_div(p.N, BN);
+  p.num_kb = ceil_div(p.K, BK);
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_bf16_kernel<BN, STAGES><<<grid, NUM_THREADS, smem, stream>>>(tmA, tmB, p);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// D[M,N] = epi(alpha * A·B).  A: a_mn=0 → [M,K] row-major (lda = pitch of a row of K), a_mn=1 → [K,M]
+// row-major (lda = pitch of a row of M).  B: b_mn=0 → [N,K] row-major, b_mn=1 → [K,N] row-major.
+// Pitches in elements; every pitch*2 bytes and every base must be 16-byte aligned (TMA).
+int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd, int a_mn,
+                 int b_mn, int out_f32, int accumulate, float alpha, const float* bias, int act, const void* aux,
+                 int ld_aux, int dact, unsigned int* status, int bn_hint, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return NB_ERR_BAD_ARG;
+  if (accumulate && !out_f32) return NB_ERR_BAD_ARG;
+  if (dact && !aux) return NB_ERR_BAD_ARG;
+  int BN = bn_hint;
+  if (BN == 0) {
+    // widest tile that still gives every SM work; MN-major B needs whole 64-column boxes
+    BN = 128;
+    const long long t128 = (long long)ceil_div(M, BM) * ceil_div(N, 128);
+    if (N <= 64 || t128 < sm_count()) BN = 64;
+    if (N >= 256 && (long long)ceil_div(M, BM) * ceil_div(N, 256) >= 2LL * sm_count()) BN = 256;
+    if (!b_mn) {
+      if (N <= 16) BN = 16;
+      else if (N <= 32) BN = 32;
+    }
+  }
+  if (b_mn && BN < 64) BN = 64;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = make_tmap_bf16(&tmA, A, K, M, lda, BK, BM);
+  else rc = make_tmap_bf16(&tmA, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_bf16(&tmB, B, K, N, ldb, BK, BN);
+  else rc = make_tmap_bf16(&tmB, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.ldd = ldd; p.ld_aux = ld_aux;
+  p.out_f32 = out_f32; p.accumulate = accumulate; p.act = act; p.dact = dact;
+  p.alpha = alpha;
+  p.D = D; p.bias = bias; p.aux = (const __nv_bfloat16*)aux; p.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (BN) {
+    case 256: return launch<256, 4>(tmA, tmB, p, s);
+    case 128: return launch<128, 6>(tmA, tmB, p, s);
+    case 64: return launch<64, 8>(tmA, tmB, p, s);
+    case 32: return launch<32, 8>(tmA, tmB, p, s);
+    case 16: return launch<16, 8>(tmA, tmB, p, s);
+    default: return NB_ERR_BAD_ARG;
+  }
+}
+
+}  // extern "C"

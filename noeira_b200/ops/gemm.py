@@ -1,0 +1,56 @@
+"""tcgen05 GEMM entry point (csrc/gemm_tcgen05.cu)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .._native import check, cuda_lib, ptr, stream_ptr
+from .status import device_status
+
+ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, "gelu": 3, "silu": 4, "sigmoid": 5}
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor = None,
+         out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor = None,
+         act=None, aux: torch.Tensor = None, dact=None, bn: int = 0, n: int = None) -> torch.Tensor:
+    """``out[M,N] = epi(alpha · A·B)`` in bf16 with fp32 accumulation.
+
+    ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]`` (``b_mn=False``) or
+    ``[K,N]`` (``b_mn=True``).  Rows may be strided (pitch a multiple of 8 elements).  ``bias`` fp32 ``[N]``;
+    ``act`` applied after the bias; ``dact`` multiplies by the derivative of that activation evaluated on the
+    saved bf16 tensor ``aux [M,N]`` (output for tanh/relu/sigmoid, input for gelu/silu); ``accumulate`` adds
+    into an fp32 ``out``.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert Kb == K, (a.shape, b.shape, a_mn, b_mn)
+    if n is not None:
+        N = n
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=out_dtype)
+    assert out.stride(-1) == 1 and out.shape[0] == M
+    out_f32 = out.dtype == torch.float32
+    assert out_f32 or out.dtype == torch.bfloat16
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() >= N
+    if aux is not None:
+        assert aux.dtype == torch.bfloat16 and aux.stride(-1) == 1
+    st = device_status(a.device)
+    rc = cuda_lib().nb_gemm_bf16(
+        ptr(a), ptr(b), ptr(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(out_f32)), ctypes.c_int(int(accumulate)),
+        ctypes.c_float(alpha), ptr(bias), ctypes.c_int(ACT[act]), ptr(aux),
+        ctypes.c_int(aux.stride(0) if aux is not None else 0), ctypes.c_int(ACT[dact]), ptr(st), ctypes.c_int(bn),
+        stream_ptr())
+    check(rc, "nb_gemm_bf16")
+    return out

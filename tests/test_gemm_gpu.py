@@ -1,0 +1,116 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return A @ B
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 512), (300, 200, 136), (4096, 256, 256), (128, 64, 4096)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(0)
+    Mp, Np, Kp = (M + 7) // 8 * 8, (N + 7) // 8 * 8, (K + 7) // 8 * 8
+    a = (torch.randn(Kp if a_mn else Mp, Mp if a_mn else Kp, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(Kp if b_mn else Np, Np if b_mn else Kp, device="cuda") * 0.5).bfloat16()
+    a_v = a[:K, :M] if a_mn else a[:M, :K]
+    b_v = b[:K, :N] if b_mn else b[:N, :K]
+    out = gemm(a_v, b_v, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    check_status()
+    ref = _ref(a_v, b_v, a_mn, b_mn)
+    err = (out - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+def test_gemm_tile_widths(bn):
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(1)
+    M, N, K = 512, 256, 320
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    out = gemm(a, b, bn=bn, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    check_status()
+    ref = a.float() @ b.float().t()
+    assert (out - ref).abs().max().item() < 5e-2
+
+
+@pytest.mark.parametrize("act", ["relu", "tanh", "gelu", "silu", "sigmoid"])
+def test_gemm_epilogues(act):
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(2)
+    M, N, K = 384, 192, 256
+    a = (torch.randn(M, K, device="cuda") * 0.2).bfloat16()
+    w = (torch.randn(K, N, device="cuda") * 0.2).bfloat16()  # [IN, OUT] layout → MN-major B
+    bias = torch.randn(N, device="cuda")
+    y = gemm(a, w, b_mn=True, bias=bias, act=act)
+    pre = a.float() @ w.float() + bias
+    f = dict(relu=torch.relu, tanh=torch.tanh, gelu=lambda x: torch.nn.functional.gelu(x, approximate="tanh"),
+             silu=torch.nn.functional.silu, sigmoid=torch.sigmoid)[act]
+    ref = f(pre)
+    torch.cuda.synchronize()
+    check_status()
+    assert (y.float() - ref).abs().max().item() < 3e-2
+    # dgrad with fused activation derivative: dx = (dy · Wᵀ) ⊙ f'(saved)
+    dy = (torch.randn(M, N, device="cuda") * 0.2).bfloat16()
+    saved = (y if act in ("relu", "tanh", "sigmoid") else pre.bfloat16())
+    # derivative wrt the PRE-activation of a previous layer of width K: use aux of shape [M, K]
+    saved_k = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    if act == "relu":
+        saved_k = saved_k.relu()
+    if act == "tanh":
+        saved_k = saved_k.float().tanh().bfloat16()
+    if act == "sigmoid":
+        saved_k = saved_k.float().sigmoid().bfloat16()
+    dx = gemm(dy, w, b_mn=False, aux=saved_k, dact=act, out_dtype=torch.float32)
+    s = saved_k.float()
+    if act == "relu":
+        d = (s > 0).float()
+    elif act == "tanh":
+        d = 1 - s * s
+    elif act == "sigmoid":
+        d = s * (1 - s)
+    else:
+        x = s.clone().requires_grad_(True)
+        f(x).sum().backward()
+        d = x.grad
+    ref_dx = (dy.float() @ w.float().t()) * d
+    torch.cuda.synchronize()
+    check_status()
+    assert (dx - ref_dx).abs().max().item() < 3e-2
+    assert saved is not None
+
+
+def test_gemm_wgrad_accumulate():
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(3)
+    T, IN, OUT = 2048, 256, 192
+    x = (torch.randn(T, IN, device="cuda") * 0.3).bfloat16()
+    dy = (torch.randn(T, OUT, device="cuda") * 0.3).bfloat16()
+    dW = torch.ones(IN, OUT, device="cuda")
+    gemm(x, dy, a_mn=True, b_mn=True, out=dW, accumulate=True)  # dW[IN,OUT] += xᵀ·dy
+    torch.cuda.synchronize()
+    check_status()
+    ref = 1.0 + x.float().t() @ dy.float()
+    assert (dW - ref).abs().max().item() < 0.15, (dW - ref).abs().max().item()
+
+
+def test_gemm_large_matches_and_times():
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(4)
+    M = N = K = 4096
+    a = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    out = gemm(a, b)
+    ref = (a @ b.t()).float()
+    torch.cuda.synchronize()
+    check_status()
+    assert (out.float() - ref).abs().max().item() < 0.1
