@@ -1,0 +1,214 @@
+"""Headline benchmark: GPU-batched physics + PPO (DDP), env-steps/s.
+
+Configuration (synthetic, seed-generated; random-init weights): 4096 envs per GPU of the 7-capsule
+planar chain (root slide-x, slide-z, hinge-y + 6 hinges, range ±1 rad, gear 120, r = 0.046 m, lengths
+U(0.2, 0.3) m, density 1000, ground friction 0.4, dt 0.01 × 5 substeps, PGS 8 iterations), obs 17,
+reward = forward velocity − 0.1‖a‖², actor-critic MLPs 2×256 tanh in bf16 with fp32 accumulation and
+fp32 master weights, rollout 32, 4 epochs × 8 minibatches, Adam 3e-4 / 1e-3.
+
+One "step" = one full PPO iteration (rollout of 32·4096 env-steps per GPU, GAE, 32 minibatch updates
+with the cross-GPU gradient reduction fused into the Adam update).  Weak scaling: per-GPU work is
+fixed.  Timing: CUDA events on the launching stream, an L2 flush (256 MB write) between timed
+iterations and outside the event pairs, max over ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ppo]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
+        --master-port P bench.py --gpus N --steps K --warmup W
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def _reference_arm(args):
+    # The reference is a Mojo/MAX code base (no setup.py / pyproject.toml, 3.6k .mojo files); the
+    # offline `pip install … /root/reference` fails with "neither setup.py nor pyproject.toml found",
+    # and no Mojo toolchain exists in this image.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is Mojo/MAX source without setup.py/pyproject.toml; pip install fails and no mojo toolchain is in the image"}))
+    return 0
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = f"/tmp/nb_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        for ln in open(self.path):
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            sm.sort()
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="ppo")
+    ap.add_argument("--envs", type=int, default=4096)
+    ap.add_argument("--sync", default="fused", help="fused | nccl  (gradient reduction path for N>1)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return _reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.workload != "ppo":
+        from benchmarks import workloads
+        return workloads.run(args, rank, local_rank, world)
+
+    from noeira_b200 import _native
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs import PlanarChainEnv
+    from noeira_b200.ops import check_status
+
+    env = PlanarChainEnv(args.envs, seed=1000 + rank, model_seed=0)
+    cfg = PPOConfig(n_envs=args.envs, rollout_len=32, n_epochs=4, n_minibatches=8, hidden=256, seed=0)
+    grad_sync = None
+    if world > 1:
+        from noeira_b200.parallel.ddp import make_grad_sync
+        grad_sync = make_grad_sync(args.sync, world, rank, local_rank)
+    tr = PPOTrainer(env, cfg, grad_sync=grad_sync)
+    if grad_sync is not None:
+        grad_sync.attach(tr.actor_opt, tr.critic_opt)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(args.warmup):
+        tr.train_iteration(read_metrics=False)
+    barrier()
+    check_status()
+
+    # ---------------- device-timed region
+    launches0 = _native.launch_count()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for s, e in evs:
+        flush.zero_()
+        s.record()
+        tr.train_iteration(read_metrics=False)
+        e.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else {}
+    launches = _native.launch_count() - launches0
+    ms = sum(s.elapsed_time(e) for s, e in evs)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    metrics = tr.read_metrics()
+    check_status()
+
+    # ---------------- end-to-end through the public API: per iteration a pinned-host control block goes
+    # to the device (learning rates, clip, entropy coefficient) and the iteration's metrics come back.
+    ctrl_host = torch.zeros(16, dtype=torch.float32).pin_memory()
+    ctrl_dev = torch.zeros(16, dtype=torch.float32, device="cuda")
+    res_host = torch.zeros(12, dtype=torch.float32).pin_memory()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        ctrl_host[0], ctrl_host[1] = cfg.actor_lr, cfg.critic_lr
+        ctrl_dev.copy_(ctrl_host, non_blocking=True)
+        tr.actor_opt.hyper[0:1].copy_(ctrl_dev[0:1])
+        tr.critic_opt.hyper[0:1].copy_(ctrl_dev[1:2])
+        tr.train_iteration(read_metrics=False)
+        res_host[:8].copy_(tr.metrics, non_blocking=True)
+        res_host[8:12].copy_(env.ep_stats, non_blocking=True)
+        torch.cuda.synchronize()
+        _ = float(res_host[0])
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+
+    env_steps = tr.env_steps_per_iteration * args.steps * world
+    value = env_steps / (ms_total / 1e3)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ppo_env_steps_per_s", "value": round(value, 1), "unit": "env-steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seed-generated planar chain, random-init weights)",
+            "config": {"model": "planar-chain 9-dof physics + actor-critic MLP 2x256 tanh", "envs_per_gpu": args.envs,
+                       "global_batch": args.envs * world, "seq_len": 32, "rollout": 32, "epochs": 4, "minibatches": 8,
+                       "substeps": 5, "pgs_iters": 8, "parallelism": f"dp{world}",
+                       "grad_sync": (args.sync if world > 1 else "none"),
+                       "l2": "flushed between timed iterations (256 MB write outside the event pairs)"},
+            "clocks": clocks,
+            "e2e": {"value": round(env_steps / e2e_s, 1), "unit": "env-steps/s", "h2d_bytes_per_step": 64,
+                    "d2h_bytes_per_step": 48},
+            "gpu_launches": launches,
+            "train_metrics": {k: (None if v != v else round(v, 5)) for k, v in metrics.items()},
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -166,7 +166,22 @@ _ERRS = {10001: "bad argument", 10002: "unaligned pointer/extent", 10003: "size 
          10004: "driver symbol not found", 10005: "cuTensorMapEncodeTiled failed"}
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of launcher calls made through `check` (graph replays add their captured count)."""
+    return _LAUNCHES
+
+
+def add_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
 def check(rc: int, what: str) -> None:
+    global _LAUNCHES
+    _LAUNCHES += 1
     if rc != 0:
         msg = _ERRS.get(rc)
         if msg is None:

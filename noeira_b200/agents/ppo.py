@@ -1,0 +1,294 @@
+"""PPO (continuous actions) with an on-device rollout.
+
+Pipeline per iteration (the host only enqueues; nothing is copied to the host inside it):
+
+    rollout   T × { actor fwd, critic fwd (tcgen05 GEMMs, fused bias+tanh) → sample kernel →
+                    fused physics env step writing reward/done/next-obs straight into slot t and the
+                    post-reset observation into slot t+1 }
+    gae       critic fwd over all T·N bootstrap states → reverse-scan GAE kernel
+    update    E·K × { gather minibatch by a keyed bijective shuffle → actor fwd → clipped-surrogate
+                      kernel (loss + dμ + d ln σ) → actor vjp → [fused gradient all-reduce +] Adam →
+                      critic fwd → value-loss kernel → critic vjp → Adam }
+
+Each of the three phases is captured once in a CUDA graph and replayed; counters that change between
+replays (minibatch index, rollout index, RNG offset, Adam step / β powers) live on the device.
+
+Reference: PPOTrainer noeira/deep_agents/ppo/trainer.mojo:185 (device rollout :933-940, update
+:837-915), driver noeira/deep_agents/training/driver_onpolicy.mojo:479,1005-1091, preset
+noeira/deep_agents/ppo/config.mojo:51-134 (separate Adam per net, actor lr 3e-4, critic lr 1e-3,
+γ 0.99, λ 0.95, clip 0.2, ln σ init −0.5).  Parameter names: ``actor.{0,1,2}.*`` (+ ``actor.2.log_std``),
+``critic.{0,1,2}.*``.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from .. import nn
+from .. import _native
+from .._native import check, cuda_lib, ptr, stream_ptr
+
+
+@dataclass
+class PPOConfig:
+    n_envs: int = 4096
+    rollout_len: int = 32
+    n_epochs: int = 4
+    n_minibatches: int = 8
+    hidden: int = 256
+    actor_lr: float = 3e-4
+    critic_lr: float = 1e-3
+    gamma: float = 0.99
+    gae_lambda: float = 0.95
+    clip_eps: float = 0.2
+    entropy_coef: float = 0.0
+    action_scale: float = 1.0
+    log_std_init: float = -0.5
+    max_grad_norm: float = 0.0
+    seed: int = 0
+    use_cuda_graphs: bool = True
+
+
+def make_actor(obs_dim, act_dim, hidden, log_std_init=-0.5):
+    return nn.Sequential(nn.LinearTanh(obs_dim, hidden, need_input_grad=False), nn.LinearTanh(hidden, hidden),
+                         nn.GaussianHead(hidden, act_dim, log_std_init=log_std_init))
+
+
+def make_critic(obs_dim, hidden):
+    return nn.Sequential(nn.LinearTanh(obs_dim, hidden, need_input_grad=False), nn.LinearTanh(hidden, hidden),
+                         nn.Linear(hidden, 1, out_fp32=True))
+
+
+class PPOTrainer:
+    def __init__(self, env, cfg: PPOConfig = None, grad_sync=None):
+        """``grad_sync``: optional object with ``reduce_and_step(optimizer)`` that replaces the local
+        optimizer step by a fused cross-GPU reduce + update (``noeira_b200.parallel.DataParallel``)."""
+        self.env = env
+        self.cfg = cfg = cfg or PPOConfig(n_envs=env.n_envs)
+        assert cfg.n_envs == env.n_envs
+        self.device = env.device
+        self.lib = cuda_lib()
+        nn.manual_seed(cfg.seed)
+        self.actor = make_actor(env.obs_dim, env.act_dim, cfg.hidden, cfg.log_std_init).to(self.device)
+        self.critic = make_critic(env.obs_dim, cfg.hidden).to(self.device)
+        self.actor_opt = nn.Adam(self.actor.named_params("actor."), lr=cfg.actor_lr)
+        self.critic_opt = nn.Adam(self.critic.named_params("critic."), lr=cfg.critic_lr)
+        self.actor_opt.max_grad_norm = self.critic_opt.max_grad_norm = cfg.max_grad_norm
+        self.grad_sync = grad_sync
+        T, N, OP = cfg.rollout_len, cfg.n_envs, env.obs_pad
+        self.AP = AP = (env.act_dim + 7) // 8 * 8
+        self.pool = T * N
+        assert self.pool % cfg.n_minibatches == 0
+        self.mb = self.pool // cfg.n_minibatches
+        f = dict(device=self.device, dtype=torch.float32)
+        h = dict(device=self.device, dtype=torch.bfloat16)
+        self.obs_buf = torch.zeros(T + 1, N, OP, **h)
+        self.next_obs_buf = torch.zeros(T, N, OP, **h)
+        self.act_buf = torch.zeros(T, N, AP, **f)
+        self.env_action = torch.zeros(N, AP, **f)
+        self.logp_buf = torch.zeros(T, N, **f)
+        self.val_buf = torch.zeros(T, N, **f)
+        self.rew_buf = torch.zeros(T, N, **f)
+        self.done_buf = torch.zeros(T, N, **f)
+        self.term_buf = torch.zeros(T, N, **f)
+        self.adv_buf = torch.zeros(T, N, **f)
+        self.ret_buf = torch.zeros(T, N, **f)
+        # minibatch staging
+        self.mb_obs = torch.zeros(self.mb, OP, **h)
+        self.mb_act = torch.zeros(self.mb, AP, **f)
+        self.mb_logp = torch.zeros(self.mb, **f)
+        self.mb_adv = torch.zeros(self.mb, **f)
+        self.mb_ret = torch.zeros(self.mb, **f)
+        self.dmu = torch.zeros(self.mb, AP, **h)
+        self.dv = torch.zeros(self.mb, 8, **h)
+        nblk = (self.mb + 255) // 256
+        self.partials = torch.zeros(max(nblk * 2, nblk * env.act_dim, nblk * 4) + 16, **f)
+        self.partials2 = torch.zeros(nblk * 4 + 16, **f)
+        self.adv_stats = torch.zeros(2, **f)
+        # device counters: [0] minibatch index, [1] rollout index, [2] rng offset
+        self.counters = torch.zeros(4, device=self.device, dtype=torch.int64)
+        # metrics: [0] Σ policy loss [1] Σ KL [2] Σ clipfrac [3] Σ entropy [4] samples [5] Σ value loss·MB
+        self.metrics = torch.zeros(8, **f)
+        self._graphs = {}
+        self._graph_launches = {}
+        self.iteration = 0
+        self.env.reset_batch()
+        self.obs_buf[0].copy_(self.env.obs_bf16)
+
+    # ------------------------------------------------------------------ phases
+    def _rollout(self):
+        cfg, env, lib = self.cfg, self.env, self.lib
+        head = self.actor.mods[2]
+        for t in range(cfg.rollout_len):
+            obs = self.obs_buf[t]
+            mu = self.actor.forward(obs)
+            v = self.critic.forward(obs)
+            check(lib.nb_ppo_sample(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(v),
+                                    ctypes.c_int(v.stride(0)), ptr(self.act_buf[t]), ctypes.c_int(self.AP),
+                                    ptr(self.env_action), ctypes.c_int(self.AP), ptr(self.logp_buf[t]),
+                                    ptr(self.val_buf[t]), ctypes.c_int(cfg.n_envs), ctypes.c_int(env.act_dim),
+                                    ctypes.c_float(cfg.action_scale), ctypes.c_ulonglong(cfg.seed * 7919 + 13),
+                                    ptr(self.counters), ctypes.c_int(0), stream_ptr()), "ppo_sample")
+            check(lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(2), ctypes.c_int(0), stream_ptr()), "counter")
+            env.engine.step(self.env_action, self.rew_buf[t], self.done_buf[t], self.term_buf[t],
+                            obs_bf16=self.obs_buf[t + 1], next_obs_bf16=self.next_obs_buf[t], ep_stats=env.ep_stats)
+        self.obs_buf[0].copy_(self.obs_buf[cfg.rollout_len])
+
+    def _gae(self):
+        cfg = self.cfg
+        vnext = self.critic.forward(self.next_obs_buf.view(self.pool, -1))
+        check(self.lib.nb_ppo_gae(ptr(self.rew_buf), ptr(self.done_buf), ptr(self.term_buf), ptr(self.val_buf),
+                                  ptr(vnext), ctypes.c_int(vnext.stride(0)), ptr(self.adv_buf), ptr(self.ret_buf),
+                                  ctypes.c_int(cfg.rollout_len), ctypes.c_int(cfg.n_envs), ctypes.c_float(cfg.gamma),
+                                  ctypes.c_float(cfg.gae_lambda), stream_ptr()), "ppo_gae")
+
+    def _opt_step(self, opt):
+        if self.grad_sync is not None:
+            self.grad_sync.reduce_and_step(opt)
+            return
+        if opt.max_grad_norm > 0:
+            opt.clip()
+        opt.step(zero_grad=True)
+
+    def _minibatch(self):
+        cfg, env, lib = self.cfg, self.env, self.lib
+        head = self.actor.mods[2]
+        check(lib.nb_ppo_gather(ptr(self.obs_buf), ctypes.c_int(env.obs_pad * 2), ptr(self.act_buf), ctypes.c_int(self.AP),
+                                ptr(self.logp_buf), ptr(self.adv_buf), ptr(self.ret_buf), ptr(self.mb_obs),
+                                ptr(self.mb_act), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.mb_ret),
+                                ptr(self.partials), ptr(self.adv_stats), ctypes.c_int(self.pool), ctypes.c_int(self.mb),
+                                ctypes.c_int(cfg.n_minibatches), ctypes.c_ulonglong(cfg.seed * 104729 + 7),
+                                ptr(self.counters), stream_ptr()), "ppo_gather")
+        # ---- actor
+        mu = self.actor.forward(self.mb_obs)
+        check(lib.nb_ppo_objective(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(self.mb_act),
+                                   ctypes.c_int(self.AP), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.adv_stats),
+                                   ptr(self.dmu), ctypes.c_int(self.AP), ptr(self.partials), ptr(self.partials2),
+                                   ptr(head.log_std.grad_storage), ptr(self.metrics), ctypes.c_int(self.mb),
+                                   ctypes.c_int(env.act_dim), ctypes.c_float(cfg.clip_eps),
+                                   ctypes.c_float(cfg.entropy_coef), ctypes.c_float(1.0 / self.mb), stream_ptr()),
+              "ppo_objective")
+        self.actor.vjp(self.dmu[:, : env.act_dim])
+        self._opt_step(self.actor_opt)
+        # ---- critic
+        v = self.critic.forward(self.mb_obs)
+        check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
+                                    ptr(self.partials), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
+                                    ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
+        self.critic.vjp(self.dv[:, :1])
+        self._opt_step(self.critic_opt)
+        check(lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(0), ctypes.c_int(0), stream_ptr()), "counter")
+
+    def _update(self):
+        cfg = self.cfg
+        check(self.lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(0), ctypes.c_int(1), stream_ptr()), "counter")
+        for _ in range(cfg.n_epochs * cfg.n_minibatches):
+            self._run("minibatch", self._minibatch)
+        check(self.lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(1), ctypes.c_int(0), stream_ptr()), "counter")
+
+    # ------------------------------------------------------------------ graphs
+    def _run(self, key, fn):
+        if not self.cfg.use_cuda_graphs:
+            fn()
+            return
+        g = self._graphs.get(key)
+        if g is None:
+            # eager warm-up on a side stream (lazy allocations, kernel attribute set-up), then capture
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                fn()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = _native.launch_count()
+            with torch.cuda.graph(g):
+                fn()
+            self._graph_launches[key] = _native.launch_count() - n0
+            _native.add_launches(-self._graph_launches[key])  # the capture pass launches nothing
+            self._graphs[key] = g
+            return  # the warm-up already did this call's work
+        g.replay()
+        _native.add_launches(self._graph_launches[key])
+
+    # ------------------------------------------------------------------ public
+    def collect(self):
+        self._run("rollout", self._rollout)
+        self._run("gae", self._gae)
+
+    def update(self):
+        self._update()
+
+    def train_iteration(self, read_metrics: bool = True):
+        self.metrics.zero_()
+        self.env.ep_stats.zero_()
+        self.collect()
+        self.update()
+        self.iteration += 1
+        return self.read_metrics() if read_metrics else None
+
+    def read_metrics(self):
+        m = self.metrics.cpu().tolist()
+        e = self.env.ep_stats.cpu().tolist()
+        n = max(m[4], 1.0)
+        nup = self.cfg.n_epochs * self.cfg.n_minibatches
+        return {"policy_loss": m[0] / n, "approx_kl": m[1] / n, "clip_frac": m[2] / n, "entropy": m[3] / n,
+                "value_loss": m[5] / max(nup * self.mb, 1), "mean_step_reward": e[2] / self.pool,
+                "episodes": e[1], "mean_episode_return": e[0] / e[1] if e[1] > 0 else float("nan")}
+
+    @property
+    def env_steps_per_iteration(self) -> int:
+        return self.pool
+
+    # ------------------------------------------------------------------ persistence
+    def named_params(self):
+        yield from self.actor.named_params("actor.")
+        yield from self.critic.named_params("critic.")
+
+    def save(self, path: str):
+        from ..io.checkpoint import save_checkpoint
+        save_checkpoint(path, list(self.named_params()), [], {
+            "iteration": float(self.iteration),
+            **{f"actor_opt.{k}": v for k, v in self.actor_opt.scalars().items()},
+            **{f"critic_opt.{k}": v for k, v in self.critic_opt.scalars().items()}}, with_moments=True)
+
+    def load(self, path: str):
+        from ..io.checkpoint import load_checkpoint
+        sc = load_checkpoint(path, list(self.named_params()), [])
+        self.iteration = int(sc.get("iteration", 0))
+        self.actor_opt.load_scalars({k.split(".", 1)[1]: v for k, v in sc.items() if k.startswith("actor_opt.")})
+        self.critic_opt.load_scalars({k.split(".", 1)[1]: v for k, v in sc.items() if k.startswith("critic_opt.")})
+        for o in (self.actor_opt, self.critic_opt):
+            if o.arena.shadow is not None:
+                o.arena.refresh_shadow()
+
+
+class PPOAgent:
+    """Facade: ``PPOAgent(env, cfg).train(total_env_steps)`` (noeira/deep_agents/ppo/agent.mojo:41)."""
+
+    def __init__(self, env, cfg: PPOConfig = None, logger=None, grad_sync=None):
+        self.trainer = PPOTrainer(env, cfg, grad_sync=grad_sync)
+        self.logger = logger
+
+    def train(self, total_env_steps: int, log_every: int = 1, checkpoint_path: str = None, checkpoint_every: int = 0):
+        tr = self.trainer
+        steps = 0
+        last = {}
+        while steps < total_env_steps:
+            read = (tr.iteration + 1) % log_every == 0
+            m = tr.train_iteration(read_metrics=read)
+            steps += tr.env_steps_per_iteration
+            if m is not None:
+                last = m
+                if self.logger is not None:
+                    self.logger.log_scalars(steps, m)
+            if checkpoint_path and checkpoint_every and tr.iteration % checkpoint_every == 0:
+                tr.save(checkpoint_path)
+        if checkpoint_path:
+            tr.save(checkpoint_path)
+        return last
+
+    def select_greedy_action(self, obs_bf16):
+        return self.trainer.actor.forward(obs_bf16)

@@ -1,0 +1,229 @@
+// Small SIMT kernels around the tensor-core ops: bias gradients (column sums), standalone
+// activation forward/backward, residual adds, casts, gathers.  All vectorised for 16-byte accesses
+// where the pitch allows; bf16 I/O with fp32 math.
+// Reference counterparts: noeira/nn/primitives/elementwise.mojo, bias_add.mojo, ops/*.mojo
+// (1 thread per element, TPB 128 — noeira/nn/constants.mojo:30-31).
+#include "common.cuh"
+#include "gemm_api.h"
+
+namespace {
+using namespace nb;
+
+__device__ __forceinline__ float act_f(int act, float v) {
+  switch (act) {
+    case NB_ACT_RELU: return fmaxf(v, 0.f);
+    case NB_ACT_TANH: return tanhf(v);
+    case NB_ACT_GELU: {
+      const float c = 0.7978845608028654f;
+      return 0.5f * v * (1.f + tanhf(c * (v + 0.044715f * v * v * v)));
+    }
+    case NB_ACT_SILU: return v / (1.f + __expf(-v));
+    case NB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
+    default: return v;
+  }
+}
+__device__ __forceinline__ float dact_f(int act, float s) {
+  switch (act) {
+    case NB_ACT_RELU: return s > 0.f ? 1.f : 0.f;
+    case NB_ACT_TANH: return 1.f - s * s;
+    case NB_ACT_SIGMOID: return s * (1.f - s);
+    case NB_ACT_GELU: {
+      const float c = 0.7978845608028654f;
+      const float u = c * (s + 0.044715f * s * s * s);
+      const float t = tanhf(u);
+      return 0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * s * s);
+    }
+    case NB_ACT_SILU: {
+      const float sg = 1.f / (1.f + __expf(-s));
+      return sg * (1.f + s * (1.f - sg));
+    }
+    default: return 1.f;
+  }
+}
+
+// out[n] (+)= Σ_m x[m, n].  Grid: (ceil(N/64), SPLIT); block 256 = 8 row-groups × 32 column pairs.
+// Each block reduces a row slab and adds its partial with one atomicAdd per column (fp32 atomics on
+// ≤ SPLIT partials per column — order dependent in the last bit, documented non-determinism is
+// avoided by SPLIT = 1 when `deterministic`).
+__global__ void __launch_bounds__(256)
+colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ out,
+                   int rows_per_block) {
+  __shared__ float sh[8][64];
+  const int cp = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int col = blockIdx.x * 64 + cp * 2;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  float a0 = 0.f, a1 = 0.f;
+  if (col < N) {
+    const bool two = (col + 1 < N);
+    for (int r = r0 + rg; r < r1; r += 8) {
+      const __nv_bfloat16* p = x + (size_t)r * ld + col;
+      if (two && ((ld & 1) == 0)) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+        a0 += __low2float(v);
+        a1 += __high2float(v);
+      } else {
+        a0 += __bfloat162float(p[0]);
+        if (two) a1 += __bfloat162float(p[1]);
+      }
+    }
+  }
+  sh[rg][cp * 2] = a0;
+  sh[rg][cp * 2 + 1] = a1;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) s += sh[g][threadIdx.x];
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < N) atomicAdd(out + c, s);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n, int act) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = __float2bfloat16(act_f(act, __bfloat162float(x[i])));
+}
+
+// dx = dy ⊙ f'(saved)
+__global__ void __launch_bounds__(256)
+act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ saved,
+               __nv_bfloat16* __restrict__ dx, long long n, int act) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * dact_f(act, __bfloat162float(saved[i])));
+}
+
+// y = a + b (bf16), 8 elements per thread
+__global__ void __launch_bounds__(256)
+add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                __nv_bfloat16* __restrict__ y, long long n8) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    uint4 va = reinterpret_cast<const uint4*>(a)[i], vb = reinterpret_cast<const uint4*>(b)[i], vo;
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&va);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&vo);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) po[k] = __hadd2(pa[k], pb[k]);
+    reinterpret_cast<uint4*>(y)[i] = vo;
+  }
+}
+
+// SwiGLU: h[m, j] = silu(g[m, j]) * u[m, j] with gu = [gate | up] of width 2H (pitch ld).
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int ld, __nv_bfloat16* __restrict__ h, int ldh, int M,
+                  int H) {
+  const long long total = (long long)M * (H / 2);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int m = (int)(i / (H / 2)), j = (int)(i % (H / 2)) * 2;
+    const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(gu + (size_t)m * ld + j);
+    const __nv_bfloat162 u = *reinterpret_cast<const __nv_bfloat162*>(gu + (size_t)m * ld + H + j);
+    const float g0 = __low2float(g), g1 = __high2float(g);
+    const float r0 = g0 / (1.f + __expf(-g0)) * __low2float(u), r1 = g1 / (1.f + __expf(-g1)) * __high2float(u);
+    *reinterpret_cast<__nv_bfloat162*>(h + (size_t)m * ldh + j) = __floats2bfloat162_rn(r0, r1);
+  }
+}
+// backward: dgu = [dh * u * silu'(g) | dh * silu(g)]
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, int ld, const __nv_bfloat16* __restrict__ dh, int ldh,
+                  __nv_bfloat16* __restrict__ dgu, int M, int H) {
+  const long long total = (long long)M * (H / 2);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int m = (int)(i / (H / 2)), j = (int)(i % (H / 2)) * 2;
+    const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(gu + (size_t)m * ld + j);
+    const __nv_bfloat162 u = *reinterpret_cast<const __nv_bfloat162*>(gu + (size_t)m * ld + H + j);
+    const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(dh + (size_t)m * ldh + j);
+    float gg[2] = {__low2float(g), __high2float(g)}, uu[2] = {__low2float(u), __high2float(u)},
+          dd[2] = {__low2float(d), __high2float(d)}, dg[2], du[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const float sg = 1.f / (1.f + __expf(-gg[k]));
+      const float si = gg[k] * sg;
+      dg[k] = dd[k] * uu[k] * sg * (1.f + gg[k] * (1.f - sg));
+      du[k] = dd[k] * si;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(dgu + (size_t)m * ld + j) = __floats2bfloat162_rn(dg[0], dg[1]);
+    *reinterpret_cast<__nv_bfloat162*>(dgu + (size_t)m * ld + H + j) = __floats2bfloat162_rn(du[0], du[1]);
+  }
+}
+
+// fp32 [M, N] (pitch lds) → bf16 [M, N] (pitch ldd)
+__global__ void __launch_bounds__(256)
+cast_rows_kernel(const float* __restrict__ s, int lds, __nv_bfloat16* __restrict__ d, int ldd, int M, int N) {
+  const long long total = (long long)M * N;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int m = (int)(i / N), n = (int)(i % N);
+    d[(size_t)m * ldd + n] = __float2bfloat16(s[(size_t)m * lds + n]);
+  }
+}
+
+inline int grid1d(long long n) {
+  long long b = (n + 255) / 256;
+  const long long cap = 148LL * 8;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+}  // namespace
+
+extern "C" {
+
+int nb_colsum_bf16(const void* x, int M, int N, int ld, float* out, int accumulate, int deterministic,
+                   void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!accumulate) NB_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * N, s));
+  int split = deterministic ? 1 : min(64, max(1, M / 512));
+  const int rows = ceil_div(M, split);
+  dim3 grid(ceil_div(N, 64), ceil_div(M, rows));
+  colsum_bf16_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, out, rows);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_act_fwd(const void* x, void* y, long long n, int act, void* stream) {
+  act_fwd_kernel<<<grid1d(n), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, act);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_act_bwd(const void* dy, const void* saved, void* dx, long long n, int act, void* stream) {
+  act_bwd_kernel<<<grid1d(n), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)saved,
+                                                             (__nv_bfloat16*)dx, n, act);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_add_bf16(const void* a, const void* b, void* y, long long n, void* stream) {
+  if (n % 8) return NB_ERR_UNALIGNED;
+  add_bf16_kernel<<<grid1d(n / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                                 (__nv_bfloat16*)y, n / 8);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_swiglu_fwd(const void* gu, int ld, void* h, int ldh, int M, int H, void* stream) {
+  if (H % 2 || ld % 2 || ldh % 2) return NB_ERR_UNALIGNED;
+  swiglu_fwd_kernel<<<grid1d((long long)M * H / 2), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ld,
+                                                                                 (__nv_bfloat16*)h, ldh, M, H);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_swiglu_bwd(const void* gu, int ld, const void* dh, int ldh, void* dgu, int M, int H, void* stream) {
+  if (H % 2 || ld % 2 || ldh % 2) return NB_ERR_UNALIGNED;
+  swiglu_bwd_kernel<<<grid1d((long long)M * H / 2), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gu, ld, (const __nv_bfloat16*)dh, ldh, (__nv_bfloat16*)dgu, M, H);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_cast_rows(const float* s, int lds, void* d, int ldd, int M, int N, void* stream) {
+  cast_rows_kernel<<<grid1d((long long)M * N), 256, 0, (cudaStream_t)stream>>>(s, lds, (__nv_bfloat16*)d, ldd, M, N);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+}  // extern "C"

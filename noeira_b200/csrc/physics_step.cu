@@ -599,7 +599,8 @@ phys_env_step_kernel(PhysParams P, const int* __restrict__ imodel, const float* 
                      int obs_bf16_stride, float* __restrict__ next_obs_f32, __nv_bfloat16* __restrict__ next_obs_bf16,
                      float* __restrict__ reward, float* __restrict__ done, float* __restrict__ terminated,
                      float* __restrict__ finished_return, const unsigned long long* __restrict__ rng_counter,
-                     unsigned long long seed, int n_envs, int do_reset, float* __restrict__ dbg) {
+                     unsigned long long seed, int n_envs, int do_reset, float* __restrict__ ep_stats,
+                     float* __restrict__ dbg) {
   extern __shared__ __align__(16) float smem[];
   // stage the model
   int* im_sh = reinterpret_cast<int*>(smem);
@@ -674,6 +675,14 @@ phys_env_step_kernel(PhysParams P, const int* __restrict__ imodel, const float* 
     done[env] = dn ? 1.f : 0.f;
     terminated[env] = term ? 1.f : 0.f;
     if (finished_return) finished_return[env] = dn ? ret : NAN;
+    if (ep_stats) {  // [0] Σ finished returns, [1] finished episodes, [2] Σ reward, [3] Σ episode length
+      if (dn) {
+        atomicAdd(ep_stats + 0, ret);
+        atomicAdd(ep_stats + 1, 1.f);
+        atomicAdd(ep_stats + 3, (float)steps);
+      }
+      atomicAdd(ep_stats + 2, rew);
+    }
   }
   if (dn && do_reset) {
     // selective reset: qpos0 + U(-noise, noise), qvel = U(-noise, noise); counter based RNG
@@ -783,7 +792,7 @@ int nb_phys_env_step(const PhysParams* P, const int* imodel, const float* fmodel
                      float* obs_f32, void* obs_bf16, int obs_bf16_stride, float* next_obs_f32, void* next_obs_bf16,
                      float* reward, float* done, float* terminated, float* finished_return,
                      const unsigned long long* rng_counter, unsigned long long seed, int n_envs, int do_reset,
-                     float* dbg, void* stream) {
+                     float* ep_stats, float* dbg, void* stream) {
   if (P->nv > 32 || P->nbody > 32 || P->nv < 1) return NB_ERR_TOO_LARGE;
   const int smem = nb_phys_smem_bytes(P);
   if (smem > 227 * 1024) return NB_ERR_TOO_LARGE;
@@ -796,7 +805,7 @@ int nb_phys_env_step(const PhysParams* P, const int* imodel, const float* fmodel
   phys_env_step_kernel<<<grid, NB_PHYS_WARPS * 32, smem, (cudaStream_t)stream>>>(
       *P, imodel, fmodel, qpos, qvel, warm, step_count, ep_return, action, action_stride, obs_f32,
       (__nv_bfloat16*)obs_bf16, obs_bf16_stride, next_obs_f32, (__nv_bfloat16*)next_obs_bf16, reward, done,
-      terminated, finished_return, rng_counter, seed, n_envs, do_reset, dbg);
+      terminated, finished_return, rng_counter, seed, n_envs, do_reset, ep_stats, dbg);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

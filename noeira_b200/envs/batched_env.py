@@ -38,6 +38,8 @@ class BatchedEnv:
         self.done = torch.zeros(self.n_envs, **z)
         self.terminated = torch.zeros(self.n_envs, **z)
         self.finished_return = torch.full((self.n_envs,), float("nan"), **z)
+        # device accumulators: Σ finished returns, finished episodes, Σ reward, Σ finished episode lengths
+        self.ep_stats = torch.zeros(4, **z)
 
     def reset_batch(self):
         raise NotImplementedError
@@ -69,7 +71,7 @@ class Physics3dBatchedEnv(BatchedEnv):
     def step_batch(self, action, dbg=None):
         self.engine.step(action, self.reward, self.done, self.terminated, obs_f32=self.obs, obs_bf16=self.obs_bf16,
                          next_obs_f32=self.next_obs, next_obs_bf16=self.next_obs_bf16,
-                         finished_return=self.finished_return, do_reset=True, dbg=dbg)
+                         finished_return=self.finished_return, do_reset=True, ep_stats=self.ep_stats, dbg=dbg)
         return self.obs, self.reward, self.done, self.terminated
 
 

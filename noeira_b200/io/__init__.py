@@ -1,0 +1,4 @@
+from .checkpoint import (CheckpointError, load_checkpoint, load_params_multi, save_checkpoint,  # noqa: F401
+                         save_params_multi)
+from .safetensors import (SafeTensors, SafeTensorsError, SafeTensorsWriter, load_safetensors,  # noqa: F401
+                          save_safetensors)

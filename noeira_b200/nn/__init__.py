@@ -1,0 +1,10 @@
+from .arena import PARAM_ALIGN, ParamArena  # noqa: F401
+from .combinators import (Checkpointed, Parallel, ProjectedResidual, Repeat, RepeatConditional, Residual,  # noqa: F401
+                          Sequential, SkipConcat, StochasticActor, StopGradParams, Tokenwise)
+from .init import (Constant, Deterministic, Kaiming, Normal, Orthogonal, ScaledKaiming, TruncNormalIn, Xavier,  # noqa: F401
+                   Zero)
+from .layers import (BiasAdd, Dropout, Elementwise, GaussianHead, Linear, LinearGELU, LinearReLU, LinearTanh,  # noqa: F401
+                     Scale)
+from .module import Module, as_autograd, manual_seed  # noqa: F401
+from .optim import SGD, Adam, AdamW, LaProp, ScalarAdam, polyak  # noqa: F401
+from .param import Param, State  # noqa: F401

@@ -1,0 +1,304 @@
+"""Leaf modules, part 1: dense layers and activations.
+
+``Linear`` stores its weight ``[IN, OUT]`` row-major — the transpose of torch's ``[out, in]`` —
+exactly like the reference (noeira/nn/primitives/linear.mojo:970-971, torch_names.mojo:11-16), so
+forward, dgrad and wgrad are the NN / NT / TN cases of one tcgen05 GEMM and no transposed copy of the
+weight exists anywhere.  Parameter names: ``weight`` (decay), ``bias`` (no decay).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import ops
+from .._native import check, cuda_lib, ptr, stream_ptr
+from .init import Constant, Initializer, Kaiming, Zero
+from .module import Module
+
+_ACT_CPU = {
+    None: (lambda x: x), "none": (lambda x: x), "relu": torch.relu, "tanh": torch.tanh,
+    "gelu": (lambda x: torch.nn.functional.gelu(x, approximate="tanh")), "silu": torch.nn.functional.silu,
+    "sigmoid": torch.sigmoid,
+}
+# which tensor the derivative is evaluated on: the output (cheap to keep) or the input
+SAVES_OUTPUT = {"relu", "tanh", "sigmoid"}
+
+
+def act_derivative_cpu(act, saved):
+    if act in (None, "none"):
+        return torch.ones_like(saved)
+    if act == "relu":
+        return (saved > 0).to(saved.dtype)
+    if act == "tanh":
+        return 1 - saved * saved
+    if act == "sigmoid":
+        return saved * (1 - saved)
+    x = saved.detach().clone().requires_grad_(True)
+    with torch.enable_grad():
+        _ACT_CPU[act](x).sum().backward()
+    return x.grad
+
+
+def act_backward(dy, saved, act):
+    """dx = dy ⊙ f'(saved) (bf16 kernel on CUDA, torch on CPU)."""
+    if act in (None, "none"):
+        return dy
+    if dy.is_cuda:
+        dy = dy.contiguous()
+        saved = saved.contiguous()
+        dx = torch.empty_like(dy)
+        check(cuda_lib().nb_act_bwd(ptr(dy), ptr(saved), ptr(dx), ctypes.c_longlong(dy.numel()),
+                                    ctypes.c_int(_act_code(act)),
+                                    stream_ptr()), "act_bwd")
+        return dx
+    return dy * act_derivative_cpu(act, saved)
+
+
+def _act_code(act):
+    from ..ops.gemm import ACT
+    return ACT[act]
+
+
+def colsum_into(dy, out_f32, n, accumulate=True, deterministic=True):
+    """out[:n] (+)= Σ_rows dy[:, :n]"""
+    if dy.is_cuda:
+        check(cuda_lib().nb_colsum_bf16(ptr(dy), ctypes.c_int(dy.shape[0]), ctypes.c_int(n), ctypes.c_int(dy.stride(0)),
+                                        ptr(out_f32), ctypes.c_int(int(accumulate)), ctypes.c_int(int(deterministic)),
+                                        stream_ptr()), "colsum")
+    else:
+        s = dy[:, :n].float().sum(0)
+        if accumulate:
+            out_f32[:n] += s
+        else:
+            out_f32[:n] = s
+
+
+class Linear(Module):
+    """y = act(x @ W + b).  ``act`` fused in the GEMM epilogue (``LinearAct`` of the reference,
+    noeira/nn/primitives/linear_act.mojo; cuBLASLt EPI_* there, tcgen05 epilogue functors here)."""
+
+    def __init__(self, in_dim: int, out_dim: int, act: str = None, bias: bool = True, init: Initializer = None,
+                 out_fp32: bool = False, need_input_grad: bool = True):
+        super().__init__()
+        self.in_dim, self.out_dim, self.act = int(in_dim), int(out_dim), (None if act in (None, "none") else act)
+        self.weight = self.add_param("weight", (in_dim, out_dim), decay=True, init=init or Kaiming(), fan_in=in_dim,
+                                     fan_out=out_dim)
+        self.bias = self.add_param("bias", (out_dim,), decay=False, init=Zero()) if bias else None
+        self.out_fp32 = out_fp32
+        self.need_input_grad = need_input_grad
+        self._x = self._saved = None
+
+    def display_label(self):
+        return f"Linear[{self.in_dim},{self.out_dim}]" + (f"+{self.act}" if self.act else "")
+
+    @property
+    def out_pad(self):
+        return self.weight.storage_shape[1]
+
+    # ---- forward
+    def forward(self, x):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        self._lead = lead
+        self._x = x2
+        if not self.on_cuda:
+            pre = x2[:, : self.in_dim].float() @ self.weight.data
+            if self.bias is not None:
+                pre = pre + self.bias.data
+            y = _ACT_CPU[self.act](pre)
+            self._saved = y if self.act in SAVES_OUTPUT else pre
+            return y.reshape(*lead, self.out_dim)
+        W = self.weight.shadow
+        b = self.bias.storage if self.bias is not None else None
+        xa = x2[:, : self.in_dim]
+        if self.act is None or self.act in SAVES_OUTPUT:
+            y = ops.gemm(xa, W, b_mn=True, bias=b, act=self.act,
+                         out_dtype=torch.float32 if self.out_fp32 else torch.bfloat16)
+            self._saved = y
+        else:
+            pre = ops.gemm(xa, W, b_mn=True, bias=b)
+            y = torch.empty_like(pre)
+            check(cuda_lib().nb_act_fwd(ptr(pre), ptr(y), ctypes.c_longlong(pre.numel()), ctypes.c_int(_act_code(self.act)),
+                                        stream_ptr()), "act_fwd")
+            self._saved = pre
+        if self.out_pad != self.out_dim:
+            y = y[:, : self.out_dim]
+        return y.reshape(*lead, self.out_dim) if len(lead) != 1 else y
+
+    # ---- backward
+    def vjp(self, dy, dy_is_pre: bool = False, fuse_dact=None):
+        """``fuse_dact=(act, saved)`` folds the PREVIOUS layer's activation derivative into this layer's
+        dgrad epilogue; the caller then passes ``dy_is_pre=True`` to that layer."""
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not self.on_cuda:
+            dpre = dy2.float()
+            if self.act is not None and not dy_is_pre:
+                dpre = dpre * act_derivative_cpu(self.act, self._saved)
+            x = self._x[:, : self.in_dim].float()
+            if not self.weight.frozen:
+                self.weight.grad.add_(x.t() @ dpre)
+                if self.bias is not None:
+                    self.bias.grad.add_(dpre.sum(0))
+            if not self.need_input_grad:
+                return None
+            dx = dpre @ self.weight.data.t()
+            if fuse_dact is not None:
+                dx = dx * act_derivative_cpu(fuse_dact[0], fuse_dact[1].reshape(dx.shape[0], -1)[:, : self.in_dim].float())
+            return dx.reshape(*self._lead, self.in_dim)
+        if dy2.dtype != torch.bfloat16:
+            dy2 = dy2.to(torch.bfloat16)
+        if dy2.stride(-1) != 1 or (dy2.stride(0) * 2) % 16 != 0 or dy2.data_ptr() % 16 != 0:
+            dy2 = _pad_rows(dy2)
+        if self.act is not None and not dy_is_pre:
+            sv = self._saved if self._saved.dtype == torch.bfloat16 else self._saved.to(torch.bfloat16)
+            dy2 = act_backward(dy2.contiguous(), sv[:, : dy2.shape[1]].contiguous() if sv.shape[1] != dy2.shape[1] else sv, self.act)
+        n = self.out_dim
+        dyv = dy2[:, :n]
+        if not self.weight.frozen:
+            ops.gemm(self._x[:, : self.in_dim], dyv, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=n)
+            if self.bias is not None:
+                colsum_into(dy2, self.bias.grad_storage, n)
+        if not self.need_input_grad:
+            return None
+        W = self.weight.shadow
+        in_pad = (self.in_dim + 7) // 8 * 8
+        alloc = torch.empty if in_pad == self.in_dim else torch.zeros
+        dx = alloc(dy2.shape[0], in_pad, device=dy2.device, dtype=torch.bfloat16)
+        aux, dact = (None, None)
+        if fuse_dact is not None:
+            dact, aux = fuse_dact
+            aux = aux.reshape(dy2.shape[0], -1)
+        ops.gemm(dyv, W[:, :n], out=dx, aux=aux, dact=dact, n=self.in_dim)
+        dx = dx[:, : self.in_dim] if in_pad != self.in_dim else dx
+        return dx.reshape(*self._lead, self.in_dim) if len(self._lead) != 1 else dx
+
+    def _release(self):
+        self._x = self._saved = None
+
+
+def _pad_rows(t):
+    """Copy into a tensor whose row pitch is a multiple of 8 elements (16 bytes in bf16)."""
+    p = (t.shape[1] + 7) // 8 * 8
+    out = torch.zeros(t.shape[0], p, device=t.device, dtype=t.dtype)
+    out[:, : t.shape[1]] = t
+    return out[:, : t.shape[1]]
+
+
+def LinearReLU(i, o, **kw):
+    return Linear(i, o, act="relu", **kw)
+
+
+def LinearTanh(i, o, **kw):
+    return Linear(i, o, act="tanh", **kw)
+
+
+def LinearGELU(i, o, **kw):
+    return Linear(i, o, act="gelu", **kw)
+
+
+class Elementwise(Module):
+    """Standalone activation (noeira/nn/primitives/elementwise.mojo)."""
+
+    def __init__(self, act: str):
+        super().__init__()
+        self.act = act
+
+    def forward(self, x):
+        if not x.is_cuda:
+            y = _ACT_CPU[self.act](x.float())
+            self._saved = y if self.act in SAVES_OUTPUT else x.float()
+            return y
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        check(cuda_lib().nb_act_fwd(ptr(xc), ptr(y), ctypes.c_longlong(xc.numel()), ctypes.c_int(_act_code(self.act)),
+                                    stream_ptr()), "act_fwd")
+        self._saved = y if self.act in SAVES_OUTPUT else xc
+        return y
+
+    def vjp(self, dy):
+        return act_backward(dy if not dy.is_cuda else dy.contiguous(), self._saved, self.act)
+
+
+class GaussianHead(Module):
+    """μ = Linear(H → ACT) plus ONE learnable state-independent ln σ vector
+    (noeira/deep_agents/primitives/gaussian_head.mojo:1-136).  ``forward`` returns μ in fp32
+    (``[M, ACT]``); ``packed()`` gives the reference's ``[μ | ln σ]`` layout."""
+
+    LS_MIN, LS_MAX = -5.0, 2.0
+
+    def __init__(self, hidden: int, act_dim: int, log_std_init: float = -0.5, init: Initializer = None):
+        super().__init__()
+        self.act_dim = act_dim
+        self.lin = Linear(hidden, act_dim, out_fp32=True, init=init)
+        # the reference exposes weight / bias / log_std directly on the head
+        self._params["weight"] = self.lin.weight
+        self._params["bias"] = self.lin.bias
+        self.log_std = self.add_param("log_std", (act_dim,), decay=False, init=Constant(log_std_init))
+
+    def _moved(self, device):
+        self.lin.device = device
+
+    def forward(self, x):
+        self._mu = self.lin.forward(x)
+        return self._mu
+
+    def packed(self):
+        ls = self.log_std.data.clamp(self.LS_MIN, self.LS_MAX)
+        return torch.cat([self._mu.float(), ls.expand(self._mu.shape[0], -1)], dim=1)
+
+    def vjp(self, dmu, fuse_dact=None):
+        return self.lin.vjp(dmu, fuse_dact=fuse_dact)
+
+    def _release(self):
+        self.lin._release()
+
+
+class BiasAdd(Module):
+    def __init__(self, dim):
+        super().__init__()
+        self.bias = self.add_param("bias", (dim,), decay=False, init=Zero())
+
+    def forward(self, x):
+        return x + self.bias.data.to(x.dtype)
+
+    def vjp(self, dy):
+        self.bias.grad.add_(dy.reshape(-1, dy.shape[-1]).float().sum(0))
+        return dy
+
+
+class Scale(Module):
+    def __init__(self, multiplier: float = 1.0):
+        super().__init__()
+        self.multiplier = multiplier
+
+    def _attr_changed(self, name, value):
+        if name == "multiplier":
+            self.multiplier = float(value)
+
+    def forward(self, x):
+        return x * self.multiplier
+
+    def vjp(self, dy):
+        return dy * self.multiplier
+
+
+class Dropout(Module):
+    """Counter-hash dropout: the mask is a pure function of (seed, step counter, element index), so a
+    captured graph replays fresh masks (noeira/nn/random/hash_mask.mojo)."""
+
+    def __init__(self, p: float = 0.1, seed: int = 0):
+        super().__init__()
+        self.p, self.seed, self.counter = p, seed, 0
+
+    def forward(self, x):
+        if not self.training or self.p == 0.0:
+            self._mask = None
+            return x
+        g = torch.Generator(device=x.device).manual_seed(self.seed * 1000003 + self.counter)
+        self.counter += 1
+        self._mask = (torch.rand(x.shape, device=x.device, generator=g) >= self.p).to(x.dtype) / (1.0 - self.p)
+        return x * self._mask
+
+    def vjp(self, dy):
+        return dy if self._mask is None else dy * self._mask

@@ -1,0 +1,276 @@
+"""Optimizers over a ParamArena: Adam / AdamW / SGD / LaProp and the scalar Adam used for the SAC
+temperature.  Hyper-parameters, step count and beta powers live in a small device tensor
+(``hyper``) so that a captured CUDA graph picks up schedule changes on replay
+(noeira/nn/optimizer/adam.mojo:75-160: device resident β^t, lr from device memory).
+Gradient clipping is the reference's three steps — Σg², finalize, scale — with the scale folded into
+the update kernel instead of a separate pass (noeira/nn/optimizer/grad_clip.mojo:255-320); a
+non-finite norm zeroes the step.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Iterable, Tuple
+
+import torch
+
+from .._native import check, cuda_lib, ptr, stream_ptr
+from .arena import ParamArena
+from .param import Param
+
+H_LR, H_BETA1, H_BETA2, H_EPS, H_WD, H_T, H_B1T, H_B2T, H_GSCALE = range(9)
+H_SIZE = 16
+
+
+class Optimizer:
+    def __init__(self, named_params: Iterable[Tuple[str, Param]], lr: float, device=None, tensor_factory=None,
+                 with_moments=True):
+        self.arena = ParamArena(list(named_params), device=device, with_moments=with_moments,
+                                tensor_factory=tensor_factory)
+        self.device = self.arena.device
+        self.cuda = self.device.type == "cuda"
+        self.hyper = torch.zeros(H_SIZE, dtype=torch.float32, device=self.device)
+        self.max_grad_norm = 0.0
+        self.grad_scale = 1.0
+        self._sumsq = torch.zeros(1, device=self.device)
+        self._norm = torch.zeros(1, device=self.device)
+        self._partials = torch.zeros(2048, device=self.device)
+        self._ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._set(H_LR, lr)
+        self._set(H_GSCALE, 1.0)
+
+    def _set(self, idx, v):
+        self.hyper[idx] = float(v)
+
+    def set_lr(self, lr: float):
+        self._set(H_LR, lr)
+
+    def zero_grad(self):
+        self.arena.zero_grad()
+
+    def grad_norm(self) -> torch.Tensor:
+        """Device scalar holding the (scaled) gradient norm measured at the last ``clip`` call."""
+        return self._norm
+
+    def clip(self, max_norm: float = None, base_scale: float = None):
+        """Compute the global gradient norm on the device and fold the clip factor into hyper[GSCALE]."""
+        mx = self.max_grad_norm if max_norm is None else max_norm
+        bs = self.grad_scale if base_scale is None else base_scale
+        a = self.arena
+        if self.cuda:
+            lib = cuda_lib()
+            check(lib.nb_arena_sumsq(ptr(a.grd), ctypes.c_longlong(a.numel), ptr(self._partials), ptr(self._ticket),
+                                     ptr(self._sumsq), stream_ptr()), "sumsq")
+            check(lib.nb_clip_finalize(ptr(self._sumsq), ctypes.c_float(mx), ctypes.c_float(bs), ptr(self.hyper),
+                                       ptr(self._norm), stream_ptr()), "clip_finalize")
+        else:
+            norm = a.grd.double().pow(2).sum().sqrt().item() * bs
+            s = bs
+            if not math.isfinite(norm):
+                s = 0.0
+            elif mx > 0 and norm > mx:
+                s = bs * mx / (norm + 1e-6)
+            self.hyper[H_GSCALE] = s
+            self._norm[0] = norm
+
+    def step(self, zero_grad: bool = False):
+        raise NotImplementedError
+
+    # checkpoint scalars (noeira/nn/optimizer/adam.mojo:353-380: t, β₁ᵗ, β₂ᵗ)
+    def scalars(self):
+        h = self.hyper.cpu()
+        return {"t": float(h[H_T]), "b1t": float(h[H_B1T]), "b2t": float(h[H_B2T])}
+
+    def load_scalars(self, d):
+        self._set(H_T, d.get("t", 0.0))
+        self._set(H_B1T, d.get("b1t", 1.0))
+        self._set(H_B2T, d.get("b2t", 1.0))
+
+
+class AdamW(Optimizer):
+    def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, **kw):
+        super().__init__(named_params, lr, **kw)
+        self._set(H_BETA1, betas[0])
+        self._set(H_BETA2, betas[1])
+        self._set(H_EPS, eps)
+        self._set(H_WD, weight_decay)
+        self._set(H_T, 0.0)
+        self._set(H_B1T, 1.0)
+        self._set(H_B2T, 1.0)
+
+    def step(self, zero_grad: bool = False):
+        a = self.arena
+        if self.cuda:
+            lib = cuda_lib()
+            check(lib.nb_adam_advance(ptr(self.hyper), stream_ptr()), "adam_advance")
+            check(lib.nb_arena_adamw(ptr(a.val), ptr(a.grd), ptr(a.m), ptr(a.v), ptr(a.shadow), ptr(a.row_flags),
+                                     ctypes.c_longlong(a.numel), ptr(self.hyper), ctypes.c_int(int(zero_grad)),
+                                     stream_ptr()), "arena_adamw")
+            a.bump_versions(shadow_fresh=True)
+            return
+        h = self.hyper
+        h[H_T] += 1
+        h[H_B1T] *= h[H_BETA1]
+        h[H_B2T] *= h[H_BETA2]
+        lr, b1, b2, eps, wd, b1t, b2t, gs = (float(h[i]) for i in (H_LR, H_BETA1, H_BETA2, H_EPS, H_WD, H_B1T, H_B2T, H_GSCALE))
+        flags = a.row_flags.repeat_interleave(32)[: a.numel]
+        g = a.grd * gs
+        live = (flags & 2) == 0
+        m = torch.where(live, b1 * a.m + (1 - b1) * g, a.m)
+        v = torch.where(live, b2 * a.v + (1 - b2) * g * g, a.v)
+        upd = (m / (1 - b1t)) / ((v / (1 - b2t)).sqrt() + eps)
+        upd = upd + torch.where((flags & 1) != 0, wd * a.val, torch.zeros_like(a.val))
+        a.val.copy_(torch.where(live, a.val - lr * upd, a.val))
+        a.m.copy_(m)
+        a.v.copy_(v)
+        if zero_grad:
+            a.grd.zero_()
+        a.bump_versions(shadow_fresh=False)
+
+
+class Adam(AdamW):
+    def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, **kw):
+        super().__init__(named_params, lr=lr, betas=betas, eps=eps, weight_decay=0.0, **kw)
+
+
+class SGD(Optimizer):
+    def __init__(self, named_params, lr=1e-2, momentum=0.0, nesterov=False, weight_decay=0.0, **kw):
+        super().__init__(named_params, lr, with_moments=momentum > 0, **kw)
+        self.momentum, self.nesterov = momentum, nesterov
+        self._set(H_WD, weight_decay)
+
+    def step(self, zero_grad: bool = False):
+        a = self.arena
+        if self.cuda:
+            check(cuda_lib().nb_arena_sgd(ptr(a.val), ptr(a.grd), ptr(a.m), ptr(a.shadow), ptr(a.row_flags),
+                                          ctypes.c_longlong(a.numel), ptr(self.hyper), ctypes.c_float(self.momentum),
+                                          ctypes.c_int(int(self.nesterov)), stream_ptr()), "arena_sgd")
+            a.bump_versions(shadow_fresh=True)
+        else:
+            h = self.hyper
+            flags = a.row_flags.repeat_interleave(32)[: a.numel]
+            g = a.grd * float(h[H_GSCALE]) + torch.where((flags & 1) != 0, float(h[H_WD]) * a.val, torch.zeros_like(a.val))
+            if a.m is not None:
+                a.m.mul_(self.momentum).add_(g)
+                g = g + self.momentum * a.m if self.nesterov else a.m
+            a.val.sub_(torch.where((flags & 2) == 0, float(h[H_LR]) * g, torch.zeros_like(g)))
+            a.bump_versions(shadow_fresh=False)
+        if zero_grad:
+            a.grd.zero_()
+
+
+class LaProp(AdamW):
+    """Dreamer-family optimizer: gradient normalised by sqrt(v) before the momentum
+    (noeira/nn/optimizer/dreamer_opt.mojo:179)."""
+
+    def step(self, zero_grad: bool = False):
+        a = self.arena
+        if self.cuda:
+            lib = cuda_lib()
+            check(lib.nb_adam_advance(ptr(self.hyper), stream_ptr()), "adam_advance")
+            check(lib.nb_arena_laprop(ptr(a.val), ptr(a.grd), ptr(a.m), ptr(a.v), ptr(a.shadow), ptr(a.row_flags),
+                                      ctypes.c_longlong(a.numel), ptr(self.hyper), stream_ptr()), "arena_laprop")
+            a.bump_versions(shadow_fresh=True)
+        else:
+            h = self.hyper
+            h[H_T] += 1
+            h[H_B1T] *= h[H_BETA1]
+            h[H_B2T] *= h[H_BETA2]
+            lr, b1, b2, eps, wd, b1t, b2t, gs = (float(h[i]) for i in (H_LR, H_BETA1, H_BETA2, H_EPS, H_WD, H_B1T, H_B2T, H_GSCALE))
+            flags = a.row_flags.repeat_interleave(32)[: a.numel]
+            g = a.grd * gs
+            a.v.mul_(b2).add_((1 - b2) * g * g)
+            a.m.mul_(b1).add_((1 - b1) * g / ((a.v / (1 - b2t)).sqrt() + eps))
+            upd = a.m / (1 - b1t) + torch.where((flags & 1) != 0, wd * a.val, torch.zeros_like(a.val))
+            a.val.sub_(lr * upd)
+            a.bump_versions(shadow_fresh=False)
+        if zero_grad:
+            a.grd.zero_()
+
+
+class ScalarAdam:
+    """Adam on one device-resident scalar (SAC's ln α): state = [ln α, m, v, β₁ᵗ, β₂ᵗ, α]
+    (noeira/nn/optimizer/scalar_adam.mojo:73)."""
+
+    def __init__(self, init_value: float, lr: float, device="cpu", betas=(0.9, 0.999), eps=1e-8):
+        self.state = torch.tensor([math.log(init_value), 0.0, 0.0, 1.0, 1.0, init_value], dtype=torch.float32, device=device)
+        self.lr, self.betas, self.eps = lr, betas, eps
+
+    @property
+    def alpha(self) -> torch.Tensor:
+        return self.state[5]
+
+    def step_alpha(self, mean_logp: torch.Tensor, target_entropy: float):
+        if self.state.is_cuda:
+            check(cuda_lib().nb_scalar_adam_alpha(ptr(self.state), ptr(mean_logp), ctypes.c_float(target_entropy),
+                                                  ctypes.c_float(self.lr), ctypes.c_float(self.betas[0]),
+                                                  ctypes.c_float(self.betas[1]), ctypes.c_float(self.eps), stream_ptr()),
+                  "scalar_adam")
+            return
+        s = self.state
+        g = -(float(mean_logp) + target_entropy)
+        b1, b2 = self.betas
+        s[3] *= b1
+        s[4] *= b2
+        s[1] = b1 * s[1] + (1 - b1) * g
+        s[2] = b2 * s[2] + (1 - b2) * g * g
+        s[0] -= self.lr * (s[1] / (1 - s[3])) / (math.sqrt(float(s[2] / (1 - s[4]))) + self.eps)
+        s[5] = math.exp(float(s[0]))
+
+
+def polyak(target_arena: ParamArena, online_arena: ParamArena, tau: float):
+    """target ← target + τ (online − target) over the whole arena in one kernel
+    (noeira/nn/optimizer/param_arena.mojo:250-288)."""
+    if target_arena.val.is_cuda:
+        check(cuda_lib().nb_polyak(ptr(target_arena.val), ptr(online_arena.val), ctypes.c_longlong(target_arena.numel),
+                                   ctypes.c_float(tau), stream_ptr()), "polyak")
+        if target_arena.shadow is not None:
+            target_arena.refresh_shadow()
+    else:
+        target_arena.val.lerp_(online_arena.val, tau)
+    target_arena.bump_versions(shadow_fresh=target_arena.shadow is not None)
+
+
+# ---- learning-rate schedules (noeira/nn/optimizer/lr_scheduler.mojo:33-121)
+class Constant:
+    def __init__(self, lr):
+        self.lr = lr
+
+    def __call__(self, step):
+        return self.lr
+
+
+class LinearWarmup:
+    def __init__(self, lr, warmup):
+        self.lr, self.warmup = lr, warmup
+
+    def __call__(self, step):
+        return self.lr * min(1.0, (step + 1) / max(1, self.warmup))
+
+
+class Cosine:
+    def __init__(self, lr, total, lr_min=0.0):
+        self.lr, self.total, self.lr_min = lr, total, lr_min
+
+    def __call__(self, step):
+        t = min(step, self.total) / max(1, self.total)
+        return self.lr_min + 0.5 * (self.lr - self.lr_min) * (1 + math.cos(math.pi * t))
+
+
+class WarmupCosine:
+    def __init__(self, lr, warmup, total, lr_min=0.0):
+        self.lr, self.warmup, self.total, self.lr_min = lr, warmup, total, lr_min
+
+    def __call__(self, step):
+        if step < self.warmup:
+            return self.lr * (step + 1) / max(1, self.warmup)
+        t = min(step - self.warmup, self.total - self.warmup) / max(1, self.total - self.warmup)
+        return self.lr_min + 0.5 * (self.lr - self.lr_min) * (1 + math.cos(math.pi * t))
+
+
+class Step:
+    def __init__(self, lr, every, gamma=0.1):
+        self.lr, self.every, self.gamma = lr, every, gamma
+
+    def __call__(self, step):
+        return self.lr * self.gamma ** (step // self.every)

@@ -1,0 +1,123 @@
+"""Data parallelism over the gradient arena.
+
+Because all gradients of an optimizer already live in one contiguous arena, DDP needs no per-module
+hooks: a bucket is a byte range of ``arena.grd`` (noeira/nn/distributed/data_parallel.mojo:190-202).
+``FusedGradSync.reduce_and_step(opt)`` replaces ``all_reduce → scale → clip → Adam → bf16 recast →
+zero_grad`` by ONE kernel that reads every peer's gradient arena over NVLink and applies the update
+(csrc/allreduce_fused.cu).  ``NcclGradSync`` is the library baseline and test oracle.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict
+
+import torch
+import torch.distributed as dist
+
+from .._native import check, cuda_lib, ptr, stream_ptr
+from ..nn.optim import H_GSCALE
+from ..ops.status import device_status
+from .symm import SIGNAL_PAD_WORDS, SymmetricHeap
+
+ONE_SHOT, TWO_SHOT, MULTIMEM = 0, 1, 2
+
+
+def choose_algo(nbytes: int, world: int, have_multicast: bool = False) -> int:
+    """Per-bucket choice.  One-shot moves (N-1)·bytes per GPU but has the fewest flag rounds; two-shot
+    moves 2(N-1)/N·bytes; multimem ≈ 2·bytes/N.  Crossovers follow the measured table in
+    profiles/allreduce_fused.md."""
+    if world <= 2 or nbytes <= (512 << 10):
+        return ONE_SHOT
+    if have_multicast and nbytes >= (4 << 20):
+        return MULTIMEM
+    return TWO_SHOT
+
+
+class NcclGradSync:
+    """Baseline: NCCL all-reduce on the gradient arena, then the local arena optimizer."""
+
+    def __init__(self, world, rank):
+        self.world, self.rank = world, rank
+
+    def attach(self, *opts):
+        for o in opts:
+            o.grad_scale = 1.0 / self.world
+            o.hyper[H_GSCALE] = 1.0 / self.world
+
+    def reduce_and_step(self, opt):
+        dist.all_reduce(opt.arena.grd)
+        if opt.max_grad_norm > 0:
+            opt.clip(base_scale=1.0 / self.world)
+        opt.step(zero_grad=True)
+
+
+class FusedGradSync:
+    """One-shot / two-shot / multimem gradient reduction fused with the optimizer update."""
+
+    def __init__(self, world: int, rank: int, local_rank: int, group=None, algo: int = None, spin_limit: int = 1 << 24):
+        self.world, self.rank, self.local_rank, self.group = world, rank, local_rank, group
+        self.algo = algo
+        self.spin_limit = spin_limit
+        self.state: Dict[int, dict] = {}
+        self.lib = cuda_lib()
+        self.sig_heap = None
+
+    def attach(self, *opts):
+        """Move each optimizer's gradient arena into symmetric memory and build the peer tables."""
+        total = 0
+        for o in opts:
+            total += 2 * (o.arena.numel * 4 + 512)
+        total += 4 * SIGNAL_PAD_WORDS * len(opts) + 4096
+        self.heap = SymmetricHeap(total, self.group)
+        for o in opts:
+            a = o.arena
+            g = self.heap.tensor(a.numel, torch.float32)
+            r = self.heap.tensor(a.numel, torch.float32)
+            s = self.heap.tensor(SIGNAL_PAD_WORDS, torch.int32)
+            g.local.copy_(a.grd)
+            # re-point the arena and every parameter's gradient view
+            a.grd = g.local
+            for _, p, off, n in a.entries:
+                p._grd = a.grd[off:off + n].view(p.storage_shape)
+            o.grad_scale = 1.0 / self.world
+            o.hyper[H_GSCALE] = 1.0 / self.world
+            nbytes = a.numel * 4
+            self.state[id(o)] = dict(grd=g, red=r, sig=s, grd_tab=g.ptr_table(), red_tab=r.ptr_table(),
+                                     sig_tab=s.ptr_table(),
+                                     partials=torch.zeros(256, device=a.grd.device),
+                                     algo=self.algo if self.algo is not None else choose_algo(nbytes, self.world))
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+
+    def reduce_and_step(self, opt):
+        st = self.state[id(opt)]
+        a = opt.arena
+        self._advance(opt)
+        check(self.lib.nb_allreduce_fused(
+            ctypes.c_int(st["algo"]), ctypes.c_int(self.world), ctypes.c_int(self.rank), st["grd_tab"], st["red_tab"],
+            st["sig_tab"], ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_longlong(a.numel), ptr(a.val), ptr(a.m),
+            ptr(a.v), ptr(a.shadow), ptr(a.row_flags), ptr(opt.hyper), ptr(st["partials"]), ptr(opt._norm),
+            ctypes.c_float(opt.max_grad_norm), ctypes.c_int(1), ctypes.c_uint(self.spin_limit),
+            ptr(device_status(a.grd.device)), stream_ptr()), "allreduce_fused")
+        a.bump_versions(shadow_fresh=True)
+
+    def _advance(self, opt):
+        check(self.lib.nb_adam_advance(ptr(opt.hyper), stream_ptr()), "adam_advance")
+
+    def all_reduce(self, opt, scale: float = None) -> torch.Tensor:
+        """Plain fused all-reduce of the gradient arena (no update); returns the reduced arena view."""
+        st = self.state[id(opt)]
+        a = opt.arena
+        check(self.lib.nb_allreduce_fused(
+            ctypes.c_int(st["algo"]), ctypes.c_int(self.world), ctypes.c_int(self.rank), st["grd_tab"], st["red_tab"],
+            st["sig_tab"], ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_longlong(a.numel), None, None, None, None,
+            None, ptr(opt.hyper) if scale is None else None, None, None, ctypes.c_float(0.0), ctypes.c_int(0),
+            ctypes.c_uint(self.spin_limit), ptr(device_status(a.grd.device)), stream_ptr()), "allreduce_fused")
+        return st["red"].local
+
+
+def make_grad_sync(kind: str, world: int, rank: int, local_rank: int):
+    if kind == "nccl":
+        return NcclGradSync(world, rank)
+    return FusedGradSync(world, rank, local_rank)

@@ -114,7 +114,7 @@ class PhysicsEngine:
             stream_ptr()), "phys_env_reset")
 
     def step(self, action, reward, done, terminated, obs_f32=None, obs_bf16=None, next_obs_f32=None,
-             next_obs_bf16=None, finished_return=None, do_reset=True, dbg=None):
+             next_obs_bf16=None, finished_return=None, do_reset=True, ep_stats=None, dbg=None):
         """One control step for every env. `action` is [N, >=nu] fp32 (row stride taken from the tensor)."""
         st = 0
         for t in (obs_bf16, next_obs_bf16):
@@ -125,7 +125,7 @@ class PhysicsEngine:
             ptr(self.step_count), ptr(self.ep_return), ptr(action), ctypes.c_int(action.stride(0)),
             ptr(obs_f32), ptr(obs_bf16), ctypes.c_int(st), ptr(next_obs_f32), ptr(next_obs_bf16),
             ptr(reward), ptr(done), ptr(terminated), ptr(finished_return), ptr(self.rng_counter),
-            ctypes.c_ulonglong(self.seed), ctypes.c_int(self.n), ctypes.c_int(1 if do_reset else 0), ptr(dbg),
+            ctypes.c_ulonglong(self.seed), ctypes.c_int(self.n), ctypes.c_int(1 if do_reset else 0), ptr(ep_stats), ptr(dbg),
             stream_ptr()), "phys_env_step")
         # device resident counter → fresh reset noise on every (captured) replay
         self.rng_counter.add_(1)

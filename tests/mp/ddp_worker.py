@@ -1,0 +1,62 @@
+"""Worker of the multi-GPU DDP test: fused P2P all-reduce + Adam vs NCCL all-reduce + local Adam."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from noeira_b200 import nn
+    from noeira_b200.ops import check_status
+    from noeira_b200.parallel.ddp import FusedGradSync
+    ok = True
+    for algo, hidden, clip in ((0, 64, 0.0), (1, 256, 0.0), (0, 64, 0.5), (1, 512, 0.5)):
+        nn.manual_seed(7)
+        net = nn.Sequential(nn.LinearTanh(32, hidden), nn.LinearTanh(hidden, hidden), nn.Linear(hidden, 8)).to("cuda")
+        ref = nn.Sequential(nn.LinearTanh(32, hidden), nn.LinearTanh(hidden, hidden), nn.Linear(hidden, 8)).to("cuda")
+        ref.copy_from(net)
+        opt = nn.AdamW(net.named_params(), lr=1e-2, weight_decay=0.01)
+        ropt = nn.AdamW(ref.named_params(), lr=1e-2, weight_decay=0.01)
+        opt.max_grad_norm = ropt.max_grad_norm = clip
+        sync = FusedGradSync(world, rank, local, algo=algo)
+        sync.attach(opt)
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        for step in range(4):
+            x = torch.randn(256, 32, device="cuda", generator=g).bfloat16()
+            dy = (torch.randn(256, 8, device="cuda", generator=g) * 0.1).bfloat16()
+            for n_, o in ((net, None), (ref, None)):
+                n_.forward(x)
+                n_.vjp(dy)
+            sync.reduce_and_step(opt)
+            dist.all_reduce(ropt.arena.grd)
+            ropt.hyper[8] = 1.0 / world
+            if clip > 0:
+                ropt.clip(base_scale=1.0 / world)
+            ropt.step(zero_grad=True)
+        torch.cuda.synchronize()
+        check_status()
+        # replicas bit-identical
+        mine = opt.arena.val.clone()
+        lst = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(lst, mine)
+        same = all(torch.equal(lst[0], t) for t in lst)
+        err = (opt.arena.val - ropt.arena.val).abs().max().item()
+        gz = opt.arena.grd.abs().max().item()
+        if rank == 0:
+            print(f"algo={algo} hidden={hidden} clip={clip}: replicas_equal={same} max|fused-nccl|={err:.3e} grd_zeroed={gz == 0.0}")
+        ok = ok and same and err < 2e-5 and gz == 0.0
+    dist.barrier()
+    if rank == 0:
+        print("DDP_WORKER_OK" if ok else "DDP_WORKER_FAIL")
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

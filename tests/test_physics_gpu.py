@@ -66,14 +66,14 @@ def test_free_fall_and_rest():
     env = PlanarChainEnv(256, seed=1)
     env.reset_batch()
     a = torch.zeros(256, 6, device="cuda")
-    for _ in range(60):
+    for _ in range(120):
         env.step_batch(a)
     torch.cuda.synchronize()
     xpos, _ = env.engine.body_poses()
     z = xpos[:, :, 2]
     assert torch.isfinite(z).all()
-    assert (z > 0.02).all() and (z < 0.4).all(), (z.min().item(), z.max().item())
-    assert env.engine.qvel.abs().max().item() < 2.0
+    assert (z > 0.03).all() and (z < 0.06).all(), (z.min().item(), z.max().item())
+    assert env.engine.qvel.abs().max().item() < 0.05
 
 
 def test_env_reset_on_truncation_and_determinism():
