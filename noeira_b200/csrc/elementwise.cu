@@ -41,12 +41,11 @@ __device__ __forceinline__ float dact_f(int act, float s) {
   }
 }
 
-// out[n] (+)= Σ_m x[m, n].  Grid: (ceil(N/64), SPLIT); block 256 = 8 row-groups × 32 column pairs.
-// Each block reduces a row slab and adds its partial with one atomicAdd per column (fp32 atomics on
-// ≤ SPLIT partials per column — order dependent in the last bit, documented non-determinism is
-// avoided by SPLIT = 1 when `deterministic`).
+// Column sums (bias gradients): out[n] (+)= Σ_m x[m, n], deterministic.
+// Stage 1, grid (ceil(N/64), SPLIT): block (bx, by) reduces rows [by·rows, (by+1)·rows) of 64 columns
+// into partials[by][n].  Stage 2 adds the SPLIT partials of a column in index order.
 __global__ void __launch_bounds__(256)
-colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ out,
+colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ partials,
                    int rows_per_block) {
   __shared__ float sh[8][64];
   const int cp = threadIdx.x & 31, rg = threadIdx.x >> 5;
@@ -75,8 +74,17 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, fl
 #pragma unroll
     for (int g = 0; g < 8; ++g) s += sh[g][threadIdx.x];
     const int c = blockIdx.x * 64 + threadIdx.x;
-    if (c < N) atomicAdd(out + c, s);
+    if (c < N) partials[(size_t)blockIdx.y * N + c] = s;
   }
+}
+
+__global__ void colsum_finish_kernel(const float* __restrict__ partials, int N, int split, float* __restrict__ out,
+                                     int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float s = 0.f;
+  for (int k = 0; k < split; ++k) s += partials[(size_t)k * N + c];
+  out[c] = accumulate ? out[c] + s : s;
 }
 
 __global__ void __launch_bounds__(256)
@@ -171,14 +179,23 @@ inline int grid1d(long long n) {
 
 extern "C" {
 
-int nb_colsum_bf16(const void* x, int M, int N, int ld, float* out, int accumulate, int deterministic,
-                   void* stream) {
+// Split factor used for a column sum over M rows (the caller sizes `partials` as split·N floats).
+int nb_colsum_split(int M) {
+  int split = M / 128;
+  if (split < 1) split = 1;
+  if (split > 64) split = 64;
+  return split;
+}
+
+// partials: nb_colsum_split(M)·N floats of scratch.
+int nb_colsum_bf16(const void* x, int M, int N, int ld, float* out, int accumulate, float* partials, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
-  if (!accumulate) NB_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * N, s));
-  int split = deterministic ? 1 : min(64, max(1, M / 512));
+  const int split = nb_colsum_split(M);
   const int rows = ceil_div(M, split);
-  dim3 grid(ceil_div(N, 64), ceil_div(M, rows));
-  colsum_bf16_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, out, rows);
+  dim3 grid(ceil_div(N, 64), split);
+  colsum_bf16_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, partials, rows);
+  NB_LAUNCH_CHECK();
+  colsum_finish_kernel<<<ceil_div(N, 128), 128, 0, s>>>(partials, N, split, out, accumulate);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

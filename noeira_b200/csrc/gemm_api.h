@@ -6,3 +6,7 @@
 #define NB_ACT_GELU 3   // tanh approximation
 #define NB_ACT_SILU 4
 #define NB_ACT_SIGMOID 5
+
+// Split-K workspace: the first NB_GEMM_WS_COUNTERS u32 are per-tile arrival counters (zero at rest),
+// fp32 partial tiles follow.
+#define NB_GEMM_WS_COUNTERS 1024

@@ -39,20 +39,29 @@ struct GemmParams {
   int ld_aux;      // aux row pitch (elements, bf16)
   int out_f32, accumulate, act, dact;
   int tiles_m, tiles_n, num_kb;
+  int splits, kb_per_split;  // split-K: work item = (tile, split); partial tiles meet in `ws`
   float alpha;
+  float* ws;                 // splits>1: fp32 partial tiles, [tile][split][BM*BN]
+  unsigned int* tile_ctr;    // splits>1: one arrival counter per tile (zero between launches)
   void* D;
   const float* bias;
   const __nv_bfloat16* aux;
   unsigned int* status;
 };
 
+// MUFU tanh: one instruction, max relative error 2^-11 — below bf16 resolution of the stored result.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float act_apply(int act, float v) {
   switch (act) {
     case NB_ACT_RELU: return fmaxf(v, 0.f);
-    case NB_ACT_TANH: return tanhf(v);
+    case NB_ACT_TANH: return tanh_fast(v);
     case NB_ACT_GELU: {
       const float c = 0.7978845608028654f;
-      return 0.5f * v * (1.f + tanhf(c * (v + 0.044715f * v * v * v)));
+      return 0.5f * v * (1.f + tanh_fast(c * (v + 0.044715f * v * v * v)));
     }
     case NB_ACT_SILU: return v / (1.f + __expf(-v));
     case NB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
@@ -68,7 +77,7 @@ __device__ __forceinline__ float dact_apply(int dact, float s) {
     case NB_ACT_GELU: {
       const float c = 0.7978845608028654f;
       const float u = c * (s + 0.044715f * s * s * s);
-      const float t = tanhf(u);
+      const float t = tanh_fast(u);
       return 0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * s * s);
     }
     case NB_ACT_SILU: {
@@ -76,6 +85,78 @@ __device__ __forceinline__ float dact_apply(int dact, float s) {
       return sg * (1.f + s * (1.f - sg));
     }
     default: return 1.f;
+  }
+}
+
+// Epilogue for 16 consecutive columns of one output row: alpha, bias, activation / derivative, store.
+__device__ __forceinline__ void epilogue_store16(const GemmParams& p, int row, int col0, float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+  const bool full = (col0 + 16 <= p.N);
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (full || col0 + j < p.N) v[j] += p.bias[col0 + j];
+  }
+  if (p.act) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = act_apply(p.act, v[j]);
+  }
+  if (p.dact) {
+    const __nv_bfloat16* ax = p.aux + (size_t)row * p.ld_aux + col0;
+    if (full && (p.ld_aux % 8 == 0)) {
+      const uint4 a0 = *reinterpret_cast<const uint4*>(ax), a1 = *reinterpret_cast<const uint4*>(ax + 8);
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&a0);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&a1);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] *= dact_apply(p.dact, __low2float(h0[j]));
+        v[2 * j + 1] *= dact_apply(p.dact, __high2float(h0[j]));
+        v[8 + 2 * j] *= dact_apply(p.dact, __low2float(h1[j]));
+        v[8 + 2 * j + 1] *= dact_apply(p.dact, __high2float(h1[j]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (full || col0 + j < p.N) v[j] *= dact_apply(p.dact, __bfloat162float(ax[j]));
+    }
+  }
+  if (p.out_f32) {
+    float* o = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
+    if (full && (p.ldd % 4 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        float4 x = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (p.accumulate) {
+          const float4 y = *reinterpret_cast<float4*>(o + j);
+          x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+        }
+        *reinterpret_cast<float4*>(o + j) = x;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (col0 + j < p.N) o[j] = p.accumulate ? o[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
+    if (full && (p.ldd % 8 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 8) {
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]),
+                       h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2);
+        pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(o + j) = pk;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (col0 + j < p.N) o[j] = __float2bfloat16(v[j]);
+    }
   }
 }
 
@@ -107,10 +188,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* ticket_slot = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_items = p.tiles_m * p.tiles_n * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -141,10 +223,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         int mb, nb_;
+        const int tile = item / p.splits, split = item - tile * p.splits;
         tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, 1)) { ok = false; *abort_flag = 1; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
@@ -176,11 +260,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         if (*abort_flag || !mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, p.status, 2)) { ok = false; *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int split = item % p.splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (*abort_flag || !mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; *abort_flag = 1; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -192,7 +278,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                           : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
             const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
                                           : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -208,78 +294,80 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       int mb, nb_;
+      const int tile = item / p.splits;
       tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
       if (*abort_flag || !mbar_wait(&tfull_bar[acc], acc_phase, p.status, 4)) { ok = false; *abort_flag = 1; break; }
       tc_fence_after();
-      const int row = mb * BM + quarter * 32 + lane;
+      const int row_in_tile = quarter * 32 + lane;
+      const int row = mb * BM + row_in_tile;
       const bool row_ok = row < p.M;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      if (p.splits == 1) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t r[16];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0);
-        tmem_ld_32x32b_x16(taddr, r);
-        tmem_ld_wait();
-        const int col0 = nb_ * BN + c0;
-        if (row_ok && col0 < p.N) {
-          float v[16];
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr0 + (uint32_t)c0, r);
+          tmem_ld_wait();
+          const int col0 = nb_ * BN + c0;
+          if (row_ok && col0 < p.N) {
+            float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-          const bool full = (col0 + 16 <= p.N);
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (full || col0 + j < p.N) v[j] += p.bias[col0 + j];
-          }
-          if (p.act) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = act_apply(p.act, v[j]);
-          }
-          if (p.dact) {
-            const __nv_bfloat16* ax = p.aux + (size_t)row * p.ld_aux + col0;
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (full || col0 + j < p.N) v[j] *= dact_apply(p.dact, __bfloat162float(ax[j]));
-          }
-          if (p.out_f32) {
-            float* o = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
-            if (full && (p.ldd % 4 == 0)) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4) {
-                float4 x = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (p.accumulate) {
-                  const float4 y = *reinterpret_cast<float4*>(o + j);
-                  x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-                }
-                *reinterpret_cast<float4*>(o + j) = x;
-              }
-            } else {
-              for (int j = 0; j < 16 && col0 + j < p.N; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
-            }
-          } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
-            if (full && (p.ldd % 8 == 0)) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 8) {
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]),
-                               h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(o + j) = pk;
-              }
-            } else {
-              for (int j = 0; j < 16 && col0 + j < p.N; ++j) o[j] = __float2bfloat16(v[j]);
-            }
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            epilogue_store16(p, row, col0, v);
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      } else {
+        // split-K: park the fp32 partial tile, the last split to arrive reduces all of them in index order
+        float* wtile = p.ws + (size_t)item * (BM * BN) + (size_t)row_in_tile * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr0 + (uint32_t)c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<uint4*>(wtile + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const unsigned int t = atomicAdd(p.tile_ctr + tile, 1u);
+          *ticket_slot = t;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*ticket_slot == (unsigned int)(p.splits - 1)) {
+          __threadfence();
+          const float* base = p.ws + (size_t)tile * p.splits * (BM * BN) + (size_t)row_in_tile * BN;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            const int col0 = nb_ * BN + c0;
+            if (row_ok && col0 < p.N) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = 0.f;
+              for (int sp = 0; sp < p.splits; ++sp) {
+                const float* src = base + (size_t)sp * (BM * BN) + c0;
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                  const float4 x = __ldcg(reinterpret_cast<const float4*>(src + j));
+                  v[j] += x.x; v[j + 1] += x.y; v[j + 2] += x.z; v[j + 3] += x.w;
+                }
+              }
+              epilogue_store16(p, row, col0, v);
+            }
+          }
+          if (warp == 2 && lane == 0) p.tile_ctr[tile] = 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -338,7 +426,8 @@ int sm_count() {
 }
 
 template <int BN, int STAGES>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long long ws_bytes, int ws_tiles_cap,
+           cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
   static bool configured = false;
   if (!configured) {
@@ -349,7 +438,19 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaSt
   p.tiles_n = ceil_div(p.N, BN);
   p.num_kb = ceil_div(p.K, BK);
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  // split-K when the tile count leaves most SMs idle and K is deep: each split keeps >= 4 k-blocks
+  int splits = 1;
+  if (p.ws && p.tile_ctr && tiles * 2 <= sm_count() && p.num_kb >= 8 && tiles <= ws_tiles_cap) {
+    splits = sm_count() / tiles;
+    if (splits > p.num_kb / 4) splits = p.num_kb / 4;
+    const long long cap = ws_bytes / ((long long)tiles * BM * BN * 4);
+    if (splits > cap) splits = (int)cap;
+    if (splits < 1) splits = 1;
+  }
+  p.kb_per_split = ceil_div(p.num_kb, splits);
+  p.splits = ceil_div(p.num_kb, p.kb_per_split);
+  const int items = tiles * p.splits;
+  const int grid = items < sm_count() ? items : sm_count();
   gemm_bf16_kernel<BN, STAGES><<<grid, NUM_THREADS, smem, stream>>>(tmA, tmB, p);
   NB_LAUNCH_CHECK();
   return NB_OK;
@@ -364,7 +465,8 @@ extern "C" {
 // Pitches in elements; every pitch*2 bytes and every base must be 16-byte aligned (TMA).
 int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd, int a_mn,
                  int b_mn, int out_f32, int accumulate, float alpha, const float* bias, int act, const void* aux,
-                 int ld_aux, int dact, unsigned int* status, int bn_hint, void* stream) {
+                 int ld_aux, int dact, unsigned int* status, int bn_hint, void* workspace, long long workspace_bytes,
+                 void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return NB_ERR_BAD_ARG;
   if (accumulate && !out_f32) return NB_ERR_BAD_ARG;
   if (dact && !aux) return NB_ERR_BAD_ARG;
@@ -396,13 +498,22 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
   p.out_f32 = out_f32; p.accumulate = accumulate; p.act = act; p.dact = dact;
   p.alpha = alpha;
   p.D = D; p.bias = bias; p.aux = (const __nv_bfloat16*)aux; p.status = status;
+  // workspace layout: [NB_GEMM_WS_COUNTERS u32 tile counters (zero at rest)] [fp32 partial tiles]
+  long long ws_bytes = 0;
+  p.ws = nullptr;
+  p.tile_ctr = nullptr;
+  if (workspace && workspace_bytes > NB_GEMM_WS_COUNTERS * 4 + (1 << 20)) {
+    p.tile_ctr = (unsigned int*)workspace;
+    p.ws = (float*)((char*)workspace + NB_GEMM_WS_COUNTERS * 4);
+    ws_bytes = workspace_bytes - NB_GEMM_WS_COUNTERS * 4;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   switch (BN) {
-    case 256: return launch<256, 4>(tmA, tmB, p, s);
-    case 128: return launch<128, 6>(tmA, tmB, p, s);
-    case 64: return launch<64, 8>(tmA, tmB, p, s);
-    case 32: return launch<32, 8>(tmA, tmB, p, s);
-    case 16: return launch<16, 8>(tmA, tmB, p, s);
+    case 256: return launch<256, 4>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
+    case 128: return launch<128, 6>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
+    case 64: return launch<64, 8>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
+    case 32: return launch<32, 8>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
+    case 16: return launch<16, 8>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
     default: return NB_ERR_BAD_ARG;
   }
 }

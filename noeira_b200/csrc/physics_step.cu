@@ -643,7 +643,9 @@ phys_env_step_kernel(PhysParams P, const int* __restrict__ imodel, const float* 
   const float x_after = __shfl_sync(0xffffffffu, qpos, P.forward_dof);
   const float fwd = (x_after - x_before) / (P.dt * P.frame_skip);
   float rew = P.w_forward * fwd - P.w_ctrl * ctrl_cost + P.w_alive;
-  const bool bad = __any_sync(0xffffffffu, !isfinite(qpos) || !isfinite(qvel));
+  // divergence guard: a non-finite state or a velocity pinned at the clamp ends the episode with zero
+  // reward (the reference ends a lane whose obs/reward goes non-finite, docs algorithms/ppo.mdx:231-232)
+  const bool bad = __any_sync(0xffffffffu, !isfinite(qpos) || !isfinite(qvel) || fabsf(qvel) >= P.max_vel);
   bool term = bad;
   if (P.term_dof >= 0) {
     const float a = __shfl_sync(0xffffffffu, qpos, P.term_dof);

@@ -60,12 +60,25 @@ def _act_code(act):
     return ACT[act]
 
 
-def colsum_into(dy, out_f32, n, accumulate=True, deterministic=True):
-    """out[:n] (+)= Σ_rows dy[:, :n]"""
+_COLSUM_WS = {}
+
+
+def _colsum_workspace(device, need: int):
+    ws = _COLSUM_WS.get(device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 64 * 8192), dtype=torch.float32, device=device)
+        _COLSUM_WS[device] = ws
+    return ws
+
+
+def colsum_into(dy, out_f32, n, accumulate=True):
+    """out[:n] (+)= Σ_rows dy[:, :n]  (two-stage, deterministic)."""
     if dy.is_cuda:
-        check(cuda_lib().nb_colsum_bf16(ptr(dy), ctypes.c_int(dy.shape[0]), ctypes.c_int(n), ctypes.c_int(dy.stride(0)),
-                                        ptr(out_f32), ctypes.c_int(int(accumulate)), ctypes.c_int(int(deterministic)),
-                                        stream_ptr()), "colsum")
+        lib = cuda_lib()
+        split = lib.nb_colsum_split(ctypes.c_int(dy.shape[0]))
+        ws = _colsum_workspace(dy.device, split * n)
+        check(lib.nb_colsum_bf16(ptr(dy), ctypes.c_int(dy.shape[0]), ctypes.c_int(n), ctypes.c_int(dy.stride(0)),
+                                 ptr(out_f32), ctypes.c_int(int(accumulate)), ptr(ws), stream_ptr()), "colsum")
     else:
         s = dy[:, :n].float().sum(0)
         if accumulate:

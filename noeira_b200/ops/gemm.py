@@ -10,10 +10,32 @@ from .status import device_status
 
 ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, "gelu": 3, "silu": 4, "sigmoid": 5}
 
+# Split-K workspace: [1024 u32 tile counters | fp32 partial tiles].  One per device, allocated on first use
+# (its address is then stable, so captured CUDA graphs can replay).  GEMMs on ONE stream serialise and may
+# share it; a caller that runs GEMMs concurrently on several streams passes its own via ``workspace=``.
+WORKSPACE_BYTES = 4096 + (32 << 20)
+_WS = {}
+
+
+def new_workspace(device) -> torch.Tensor:
+    return torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+
+
+def default_workspace(device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    w = _WS.get(key)
+    if w is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("run one eager GEMM on this device before capturing a CUDA graph")
+        w = new_workspace(device)
+        _WS[key] = w
+    return w
+
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor = None,
          out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor = None,
-         act=None, aux: torch.Tensor = None, dact=None, bn: int = 0, n: int = None) -> torch.Tensor:
+         act=None, aux: torch.Tensor = None, dact=None, bn: int = 0, n: int = None,
+         workspace: torch.Tensor = None) -> torch.Tensor:
     """``out[M,N] = epi(alpha · A·B)`` in bf16 with fp32 accumulation.
 
     ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]`` (``b_mn=False``) or
@@ -45,12 +67,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if aux is not None:
         assert aux.dtype == torch.bfloat16 and aux.stride(-1) == 1
     st = device_status(a.device)
+    ws = workspace if workspace is not None else default_workspace(a.device)
     rc = cuda_lib().nb_gemm_bf16(
         ptr(a), ptr(b), ptr(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
         ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(out_f32)), ctypes.c_int(int(accumulate)),
         ctypes.c_float(alpha), ptr(bias), ctypes.c_int(ACT[act]), ptr(aux),
         ctypes.c_int(aux.stride(0) if aux is not None else 0), ctypes.c_int(ACT[dact]), ptr(st), ctypes.c_int(bn),
-        stream_ptr())
+        ptr(ws), ctypes.c_longlong(ws.numel()), stream_ptr())
     check(rc, "nb_gemm_bf16")
     return out

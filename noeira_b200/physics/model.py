@@ -132,7 +132,7 @@ class Options:
     friction_reg: float = 1.0
     plane_normal: Sequence[float] = (0.0, 0.0, 1.0)
     plane_offset: float = 0.0
-    max_vel: float = 1000.0
+    max_vel: float = 100.0
     rmax: int = 32
 
 
@@ -301,7 +301,7 @@ class RigidModel:
 
 def planar_chain(seed: int = 0, n_links: int = 7, radius: float = 0.046, length_range=(0.2, 0.3),
                  density: float = 1000.0, gear: float = 120.0, joint_range=(-1.0, 1.0), friction: float = 0.4,
-                 armature: float = 0.1, damping: float = 1.0, z0: float = 0.5, opt: Options = None) -> RigidModel:
+                 armature: float = 0.1, damping: float = 4.0, z0: float = 0.5, opt: Options = None) -> RigidModel:
     """Planar chain: root slide-x, slide-z, hinge-y, then ``n_links-1`` hinge-y joints between capsule
     links laid along +x.  Link lengths are U(length_range) drawn from ``seed``.  nq = nv = n_links + 2."""
     rng = np.random.RandomState(seed)

@@ -76,13 +76,17 @@ def test_ppo_actor_gradient_matches_autograd():
     x = tr.mb_obs[:, :17].double()
     h = torch.tanh(torch.tanh(x @ W0 + b0) @ W1 + b1)
     m = h @ W2 + b2
-    lsc = ls.clamp(-5, 2)
+    MB = m.shape[0]
+    m.register_hook(lambda g: (g * MB).clamp(-10, 10) / MB)   # per-element gradient clip of the objective
+    lsb = ls.expand(MB, -1)
+    lsb.register_hook(lambda g: (g * MB).clamp(-10, 10) / MB)
+    lsc = lsb.clamp(-5, 2)
     sd = lsc.exp() + 1e-6
     act = tr.mb_act[:, : env.act_dim].double()
     lp = (-0.5 * (math.log(2 * math.pi) + 2 * lsc + ((act - m) / sd) ** 2)).sum(1)
     A = (tr.mb_adv.double() - tr.mb_adv.double().mean()) / (tr.mb_adv.double().std(unbiased=False) + 1e-8)
     ratio = (lp - tr.mb_logp.double()).clamp(-20, 20).exp()
-    loss = -torch.min(ratio * A, ratio.clamp(0.8, 1.2) * A) - 0.01 * (0.5 * (math.log(2 * math.pi) + 1) + lsc).sum()
+    loss = -torch.min(ratio * A, ratio.clamp(0.8, 1.2) * A) - 0.01 * (0.5 * (math.log(2 * math.pi) + 1) + lsc).sum(1)
     loss.mean().backward()
     for p, r in zip(tr.actor.params(), ps):
         g, rg = p.grad.double(), r.grad
