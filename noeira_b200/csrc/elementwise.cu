@@ -78,6 +78,40 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, fl
   }
 }
 
+// Vector variant (N % 8 == 0, 16-byte aligned rows): a thread owns 8 columns (one 16-byte load per row),
+// 32 column groups x 8 row lanes per block, grid (ceil(N/256), SPLIT).
+__global__ void __launch_bounds__(256)
+colsum_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, int M, int N, int ld, float* __restrict__ partials,
+                       int rows_per_block) {
+  __shared__ float sh[8][256 + 8];
+  const int cg = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + cg * 8;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  if (col < N) {
+#pragma unroll 4
+    for (int r = r0 + rg; r < r1; r += 8) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * ld + col));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc[2 * k] += __low2float(h[k]);
+        acc[2 * k + 1] += __high2float(h[k]);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) sh[rg][cg * 8 + k] = acc[k];
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) s += sh[g][threadIdx.x];
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) partials[(size_t)blockIdx.y * N + c] = s;
+}
+
 __global__ void colsum_finish_kernel(const float* __restrict__ partials, int N, int split, float* __restrict__ out,
                                      int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -181,9 +215,9 @@ extern "C" {
 
 // Split factor used for a column sum over M rows (the caller sizes `partials` as split·N floats).
 int nb_colsum_split(int M) {
-  int split = M / 128;
+  int split = M / 64;
   if (split < 1) split = 1;
-  if (split > 64) split = 64;
+  if (split > 256) split = 256;
   return split;
 }
 
@@ -192,8 +226,13 @@ int nb_colsum_bf16(const void* x, int M, int N, int ld, float* out, int accumula
   cudaStream_t s = (cudaStream_t)stream;
   const int split = nb_colsum_split(M);
   const int rows = ceil_div(M, split);
-  dim3 grid(ceil_div(N, 64), split);
-  colsum_bf16_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, partials, rows);
+  if (N % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    dim3 grid(ceil_div(N, 256), split);
+    colsum_bf16_vec_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, partials, rows);
+  } else {
+    dim3 grid(ceil_div(N, 64), split);
+    colsum_bf16_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, M, N, ld, partials, rows);
+  }
   NB_LAUNCH_CHECK();
   colsum_finish_kernel<<<ceil_div(N, 128), 128, 0, s>>>(partials, N, split, out, accumulate);
   NB_LAUNCH_CHECK();

@@ -94,7 +94,9 @@ __device__ __forceinline__ float impedance(const PhysParams& P, float pen) {
   float x = pen / P.solimp_width;
   x = fminf(fmaxf(x, 0.f), 1.f);
   float y;
-  if (x <= P.solimp_mid) {
+  if (P.solimp_pow == 2.f) {  // the default exponent: no transcendental
+    y = (x <= P.solimp_mid) ? x * x / P.solimp_mid : 1.f - (1.f - x) * (1.f - x) / (1.f - P.solimp_mid);
+  } else if (x <= P.solimp_mid) {
     y = powf(x, P.solimp_pow) / powf(P.solimp_mid, P.solimp_pow - 1.f);
   } else {
     y = 1.f - powf(1.f - x, P.solimp_pow) / powf(1.f - P.solimp_mid, P.solimp_pow - 1.f);
@@ -109,7 +111,7 @@ __device__ __forceinline__ float impedance(const PhysParams& P, float pen) {
 #define ROW_TANGENT 2
 
 struct WarpScratch {
-  float *xpos, *xmat, *xquat, *S, *I, *Ic, *V, *F, *M, *vec, *J, *B, *row;
+  float *xpos, *xmat, *xquat, *S, *I, *Ic, *V, *F, *M, *vec, *J, *B, *row, *A;
   int* rowi;
 };
 
@@ -130,7 +132,8 @@ __device__ __forceinline__ WarpScratch carve(float* base, const PhysParams& P) {
   w.J = p; p += rmax * nvp;
   w.B = p; p += rmax * nvp;
   w.row = p; p += rmax * 4;
-  w.rowi = reinterpret_cast<int*>(p);  // rmax * 4 ints
+  w.rowi = reinterpret_cast<int*>(p); p += rmax * 4;  // rmax * 4 ints
+  w.A = p;  // 32 x 33 Delassus matrix (dual PGS, rmax <= 32)
   return w;
 }
 
@@ -206,7 +209,11 @@ __device__ __forceinline__ void forward_kinematics(const PhysParams& P, const Mo
         if (m.dof_type[d] == NB_JOINT_HINGE) {
           const V3 anchor = pos + qrot(q, ld3(m.dof_pos + d * 3));
           float s, c;
-          sincosf(0.5f * qd, &s, &c);
+          {
+            float h = 0.5f * qd;
+            h -= 6.283185307179586f * rintf(h * 0.15915494309189535f);
+            __sincosf(h, &s, &c);
+          }
           const V3 al = ld3(m.dof_axis + d * 3);
           q = qmul(q, Q4{c, s * al.x, s * al.y, s * al.z});
           pos = anchor - qrot(q, ld3(m.dof_pos + d * 3));
@@ -377,10 +384,9 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   // ---- in-place Cholesky M̂ = L Lᵀ (lower).  Column k: lane r > k scales, then trailing update.
   for (int k = 0; k < nv; ++k) {
     float dkk = w.M[k * nvp + k];
-    dkk = sqrtf(fmaxf(dkk, 1e-10f));
-    const float inv = 1.f / dkk;
+    const float inv = rsqrtf(fmaxf(dkk, 1e-10f));
     __syncwarp();
-    if (lane == k) w.M[k * nvp + k] = dkk;
+    if (lane == k) w.M[k * nvp + k] = inv;  // the diagonal keeps 1/L_kk
     if (lane > k && lane < nv) w.M[lane * nvp + k] *= inv;
     __syncwarp();
     // trailing: element (r, c) for k < c <= r < nv; lanes stride over the flattened lower triangle rows
@@ -438,9 +444,10 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
       const int r = r0 + lane;
       const bool isn = (r < nuni) && w.rowi[r * 4] == ROW_NORMAL;
       const unsigned bal = __ballot_sync(0xffffffffu, isn);
-      const int my = nrow + 2 * __popc(bal & ((1u << lane) - 1u));
-      if (isn && my + 1 < P.rmax) {  // pairs are written for a prefix of the contacts only
-        for (int t = 0; t < 2; ++t) {
+      const int nd = P.friction_rows;  // 1: planar model (only t1 can move), 2: t1 and t2
+      const int my = nrow + nd * __popc(bal & ((1u << lane) - 1u));
+      if (isn && my + nd - 1 < P.rmax) {  // written for a prefix of the contacts only
+        for (int t = 0; t < nd; ++t) {
           w.rowi[(my + t) * 4 + 0] = ROW_TANGENT + t;
           w.rowi[(my + t) * 4 + 1] = w.rowi[r * 4 + 1];
           w.rowi[(my + t) * 4 + 2] = r;
@@ -448,8 +455,8 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
           w.row[(my + t) * 4 + 1] = 1.f;
         }
       }
-      const int fit = max(0, (P.rmax - nrow) / 2);
-      nrow += 2 * min(fit, __popc(bal));
+      const int fit = max(0, (P.rmax - nrow) / nd);
+      nrow += nd * min(fit, __popc(bal));
     }
   }
   __syncwarp();
@@ -505,12 +512,12 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
       for (int i = 0; i < nv; ++i) {
         float acc = Jr[i];
         for (int j = 0; j < i; ++j) acc -= w.M[i * nvp + j] * Br[j];
-        Br[i] = acc / w.M[i * nvp + i];
+        Br[i] = acc * w.M[i * nvp + i];
       }
       for (int i = nv - 1; i >= 0; --i) {
         float acc = Br[i];
         for (int j = i + 1; j < nv; ++j) acc -= w.M[j * nvp + i] * Br[j];
-        Br[i] = acc / w.M[i * nvp + i];
+        Br[i] = acc * w.M[i * nvp + i];
       }
       if (!smooth) {
         float diag = 0.f, vel = 0.f;
@@ -548,32 +555,90 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
     if (lane == 0) dbg[nv * nv + 3 * nv] = (float)nrow;
   }
 
-  // ---- projected Gauss-Seidel on qacc (lane = dof)
-  float qacc = (lane < nv) ? qacc_sh[lane] : 0.f;
-  // apply warm start
-  for (int r = 0; r < nrow; ++r) {
-    const float lam = w.row[r * 4 + 3];
-    if (lam != 0.f && lane < nv) qacc += w.B[r * nvp + lane] * lam;
-  }
-  for (int it = 0; it < P.pgs_iters; ++it) {
-    for (int r = 0; r < nrow; ++r) {
-      float part = (lane < nv) ? w.J[r * nvp + lane] * qacc : 0.f;
-      part = warp_sum(part);
-      const float lam = w.row[r * 4 + 3];
-      const float res = part - w.row[r * 4 + 0] + w.row[r * 4 + 1] * lam;
-      float ln = lam - res * w.row[r * 4 + 2];
-      const int kind = w.rowi[r * 4];
-      if (kind <= ROW_NORMAL) {
-        ln = fmaxf(ln, 0.f);
-      } else {
-        const int pr = w.rowi[r * 4 + 2];
-        const float bound = m.cs_mu[w.rowi[r * 4 + 1] - P.nlimit] * w.row[pr * 4 + 3];
-        ln = fminf(fmaxf(ln, -bound), bound);
+  // ---- projected Gauss-Seidel.  Dual form, lane = row: each lane keeps c_r = J_r·qacc − aref_r (without
+  // the R_r λ_r term) in a register; when row s moves by Δλ every lane adds A_rs·Δλ with
+  // A = J M̂⁻¹ Jᵀ, so a row update costs two shuffles instead of a cross-lane dot product.  The iterates
+  // are those of the primal sweep (qacc += B_s Δλ) in exact arithmetic.
+  float qacc;
+  if (P.rmax <= 32) {
+    const int r = lane;
+    const bool on = r < nrow;
+    float c = 0.f, lam = 0.f, k1 = 0.f, invd = 0.f, mu = 0.f;
+    int parent = 0;
+    float* a_row = w.A + r * 33;  // A[r][*] in shared memory (odd stride: conflict free)
+    if (on) {
+      float acc = 0.f;
+      for (int j = 0; j < nv; ++j) acc += w.J[r * nvp + j] * qacc_sh[j];
+      c = acc - w.row[r * 4 + 0];
+      invd = w.row[r * 4 + 2];
+      k1 = 1.f - w.row[r * 4 + 1] * invd;  // λ_new = λ·k1 − c·invd
+      lam = w.row[r * 4 + 3];
+      parent = max(w.rowi[r * 4 + 2], 0);
+      if (w.rowi[r * 4] >= ROW_TANGENT) mu = m.cs_mu[w.rowi[r * 4 + 1] - P.nlimit];
+      for (int s2 = 0; s2 < nrow; ++s2) {
+        float a = 0.f;
+        for (int j = 0; j < nv; ++j) a += w.J[r * nvp + j] * w.B[s2 * nvp + j];
+        a_row[s2] = a;
       }
-      const float dl = ln - lam;
-      if (lane == 0) w.row[r * 4 + 3] = ln;
-      if (lane < nv) qacc += w.B[r * nvp + lane] * dl;
-      __syncwarp();
+    }
+    __syncwarp();
+    for (int s2 = 0; s2 < nrow; ++s2) {  // warm start
+      const float ls = __shfl_sync(0xffffffffu, lam, s2);
+      if (on) c += a_row[s2] * ls;
+    }
+    for (int it = 0; it < P.pgs_iters; ++it) {
+      // unilateral rows [0, nuni): limits and contact normals
+      for (int s2 = 0; s2 < nuni; ++s2) {
+        const float a_rs = on ? a_row[s2] : 0.f;
+        const float ln = fmaxf(lam * k1 - c * invd, 0.f);
+        const float dl = __shfl_sync(0xffffffffu, ln - lam, s2);
+        if (lane == s2) lam = ln;
+        c += a_rs * dl;
+      }
+      // friction rows [nuni, nrow): box bounds from the parent normal multiplier
+      for (int s2 = nuni; s2 < nrow; ++s2) {
+        const float a_rs = on ? a_row[s2] : 0.f;
+        const float bound = mu * __shfl_sync(0xffffffffu, lam, parent);
+        const float ln = fminf(fmaxf(lam * k1 - c * invd, -bound), bound);
+        const float dl = __shfl_sync(0xffffffffu, ln - lam, s2);
+        if (lane == s2) lam = ln;
+        c += a_rs * dl;
+      }
+    }
+    if (on) w.row[r * 4 + 3] = lam;
+    qacc = (lane < nv) ? qacc_sh[lane] : 0.f;
+    for (int s2 = 0; s2 < nrow; ++s2) {
+      const float ls = __shfl_sync(0xffffffffu, lam, s2);
+      if (lane < nv) qacc += w.B[s2 * nvp + lane] * ls;
+    }
+    __syncwarp();
+  } else {
+    // primal sweep for models that need more than 32 rows (lane = dof)
+    qacc = (lane < nv) ? qacc_sh[lane] : 0.f;
+    for (int r = 0; r < nrow; ++r) {
+      const float lam = w.row[r * 4 + 3];
+      if (lam != 0.f && lane < nv) qacc += w.B[r * nvp + lane] * lam;
+    }
+    for (int it = 0; it < P.pgs_iters; ++it) {
+      for (int r = 0; r < nrow; ++r) {
+        float part = (lane < nv) ? w.J[r * nvp + lane] * qacc : 0.f;
+        part = warp_sum(part);
+        const float lam = w.row[r * 4 + 3];
+        const float res = part - w.row[r * 4 + 0] + w.row[r * 4 + 1] * lam;
+        float ln = lam - res * w.row[r * 4 + 2];
+        const int kind = w.rowi[r * 4];
+        if (kind <= ROW_NORMAL) {
+          ln = fmaxf(ln, 0.f);
+        } else {
+          const int pr = w.rowi[r * 4 + 2];
+          const float bound = m.cs_mu[w.rowi[r * 4 + 1] - P.nlimit] * w.row[pr * 4 + 3];
+          ln = fminf(fmaxf(ln, -bound), bound);
+        }
+        const float dl = ln - lam;
+        if (lane == 0) w.row[r * 4 + 3] = ln;
+        if (lane < nv) qacc += w.B[r * nvp + lane] * dl;
+        __syncwarp();
+      }
     }
   }
   // store multipliers for the next substep

@@ -66,7 +66,7 @@ _COLSUM_WS = {}
 def _colsum_workspace(device, need: int):
     ws = _COLSUM_WS.get(device)
     if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 64 * 8192), dtype=torch.float32, device=device)
+        ws = torch.empty(max(need, 256 * 8192), dtype=torch.float32, device=device)
         _COLSUM_WS[device] = ws
     return ws
 

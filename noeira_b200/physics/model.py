@@ -281,6 +281,14 @@ class RigidModel:
         self.act_lo = np.array([a.ctrlrange[0] for a in actuators], np.float64)
         self.act_hi = np.array([a.ctrlrange[1] for a in actuators], np.float64)
         self.maxdepth = int(self.body_depth.max())
+        # planar mechanism in the x-z plane: every hinge about ±y, every slide inside the plane, bodies not
+        # rotated out of it → the y tangent of a ground contact can never move and gets no friction row
+        ey = np.array([0.0, 1.0, 0.0])
+        self.planar = bool(
+            all((abs(abs(a @ ey) - 1) < 1e-9) if t == HINGE else (abs(a @ ey) < 1e-9)
+                for a, t in zip(self.dof_axis, self.dof_type))
+            and all(abs(q[1]) < 1e-9 and abs(q[3]) < 1e-9 for q in self.body_quat)
+            and abs(np.asarray(self.opt.plane_normal) @ ey) < 1e-9)
 
     # -------------------------------------------------------------- packing for the kernel
     def pack(self, reset_noise=(0.1, 0.1)):

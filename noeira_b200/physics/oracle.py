@@ -160,10 +160,12 @@ def substep(m: RigidModel, qpos, qvel, tau_act, warm, debug=None):
     rows = rows[: o.rmax]
     nuni = len(rows)
     if o.friction_rows:
+        nd = 1 if m.planar else 2
         for r in range(nuni):
-            if rows[r][0] == ROW_NORMAL and len(rows) + 1 < o.rmax:
+            if rows[r][0] == ROW_NORMAL and len(rows) + nd - 1 < o.rmax:
                 rows.append([ROW_T1, rows[r][1], r, 0.0, 1.0])
-                rows.append([ROW_T2, rows[r][1], r, 0.0, 1.0])
+                if nd == 2:
+                    rows.append([ROW_T2, rows[r][1], r, 0.0, 1.0])
     t1 = np.array([1.0, 0, 0]) - pn[0] * pn
     if np.dot(t1, t1) < 1e-6:
         t1 = np.array([0, 1.0, 0]) - pn[1] * pn
