@@ -3,8 +3,11 @@
 // where the pitch allows; bf16 I/O with fp32 math.
 // Reference counterparts: noeira/nn/primitives/elementwise.mojo, bias_add.mojo, ops/*.mojo
 // (1 thread per element, TPB 128 — noeira/nn/constants.mojo:30-31).
+#include <mutex>
+
 #include "common.cuh"
 #include "gemm_api.h"
+#include "noalloc_api.h"
 
 namespace {
 using namespace nb;
@@ -204,6 +207,30 @@ cast_rows_kernel(const float* __restrict__ s, int lds, __nv_bfloat16* __restrict
   }
 }
 
+// Scratch of the allocation-free column sum (see noalloc_api.h).  In host code this name is only a
+// handle for cudaGetSymbolAddress — it is NOT a device address and must never be passed to a kernel.
+static __device__ __align__(256) float g_colsum_noalloc_scratch[NB_COLSUM_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NB_MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_scratch_ptr[NB_MAX_DEVICES] = {nullptr};
+
+// Device address of the scratch array on the CURRENT device, resolved once per device.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  NB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= NB_MAX_DEVICES) return NB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    NB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_colsum_noalloc_scratch));
+    if (ptr == nullptr) return NB_ERR_BAD_ARG;
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_scratch_ptr[dev];
+  return NB_OK;
+}
+
 inline int grid1d(long long n) {
   long long b = (n + 255) / 256;
   const long long cap = 148LL * 8;
@@ -237,6 +264,17 @@ int nb_colsum_bf16(const void* x, int M, int N, int ld, float* out, int accumula
   colsum_finish_kernel<<<ceil_div(N, 128), 128, 0, s>>>(partials, N, split, out, accumulate);
   NB_LAUNCH_CHECK();
   return NB_OK;
+}
+
+// Column sum whose scratch lives in the library image; full contract in noalloc_api.h.
+int nb_colsum_bf16_noalloc(const void* x, int M, int N, int ld, float* out, int accumulate, void* stream) {
+  if (M <= 0 || N <= 0 || ld < N) return NB_ERR_BAD_ARG;
+  const int split = nb_colsum_split(M);
+  if ((long long)split * N > (long long)NB_COLSUM_NOALLOC_SCRATCH_FLOATS) return NB_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != NB_OK) return rc;
+  return nb_colsum_bf16(x, M, N, ld, out, accumulate, scratch, stream);
 }
 
 int nb_act_fwd(const void* x, void* y, long long n, int act, void* stream) {
