@@ -233,18 +233,38 @@ ar_twoshot_kernel(ARParams p, AdamBufs a, unsigned int* status) {
   const long long per = ((p.n4 + p.world - 1) / p.world + 7) / 8 * 8;
   const long long lo = min(p.n4, per * p.rank), hi = min(p.n4, per * (p.rank + 1));
   if (ok) {
-    for (long long i = lo + i0; i < hi; i += stride) {
-      float4 g;
-      if (MULTIMEM) {
-        g = multimem_ld_reduce4(p.grd_mc + 4 * i);
+    if (MULTIMEM) {
+      for (long long i = lo + i0; i < hi; i += stride) {
+        const float4 g = multimem_ld_reduce4(p.grd_mc + 4 * i);
         multimem_st4(p.red_mc + 4 * i, g);
-      } else {
-        g = ld_peer4(p.grd[0] + 4 * i);
-        for (int r = 1; r < p.world; ++r) {
-          const float4 x = ld_peer4(p.grd[r] + 4 * i);
-          g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+      }
+    } else {
+      // 4 independent float4 per thread and per peer in flight: NVLink round trips are long, so the loop is
+      // unrolled to keep ~1 MB of loads outstanding per GPU
+      constexpr int U = 4;
+      for (long long i = lo + i0; i < hi; i += stride * U) {
+        float4 g[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long k = i + u * stride;
+          g[u] = k < hi ? ld_peer4(p.grd[0] + 4 * k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (int r = 0; r < p.world; ++r) st_peer4(p.red[r] + 4 * i, g);
+        for (int r = 1; r < p.world; ++r) {
+          float4 x[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long k = i + u * stride;
+            x[u] = k < hi ? ld_peer4(p.grd[r] + 4 * k) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) { g[u].x += x[u].x; g[u].y += x[u].y; g[u].z += x[u].z; g[u].w += x[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long k = i + u * stride;
+          if (k < hi)
+            for (int r = 0; r < p.world; ++r) st_peer4(p.red[r] + 4 * k, g[u]);
+        }
       }
     }
   }

@@ -8,3 +8,5 @@ from .layers import (BiasAdd, Dropout, Elementwise, GaussianHead, Linear, Linear
 from .module import Module, as_autograd, manual_seed  # noqa: F401
 from .optim import SGD, Adam, AdamW, LaProp, ScalarAdam, polyak  # noqa: F401
 from .param import Param, State  # noqa: F401
+from .transformer import (AttentionCore, CrossAttention, Embedding, FeedForward, LayerNorm, MSELoss, RMSNorm,  # noqa: F401
+                          SelfAttention, SwiGLU, SwiGLUFFN, TransformerBlock, cross_entropy, rope_, sincos_embed)

@@ -75,7 +75,7 @@ def flash_attention_forward(q, k, v, scale=None, mask=None, frame=0, causal_off=
 
 
 def flash_attention_backward(q, k, v, o, lse, do, scale=None, mask=None, frame=0, causal_off=0, key_valid=None,
-                             bias=None):
+                             bias=None, dq=None, dk=None, dv=None):
     """Gradients of ``flash_attention_forward``: returns (dq, dk, dv) bf16 with the shapes of q, k, v."""
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
@@ -86,9 +86,15 @@ def flash_attention_backward(q, k, v, o, lse, do, scale=None, mask=None, frame=0
         do = do.contiguous()
     assert o.stride(3) == 1 and o.stride(2) == D and o.stride(0) == Sq * o.stride(1)
     assert do.stride(0) == Sq * do.stride(1) or B == 1
-    dq = torch.empty(B, Sq, Hq, D, device=q.device, dtype=torch.bfloat16)
-    dk = torch.empty(B, Sk, Hkv, D, device=q.device, dtype=torch.bfloat16)
-    dv = torch.empty(B, Sk, Hkv, D, device=q.device, dtype=torch.bfloat16)
+    # outputs may be views into a packed dQKV buffer: head stride D, batch stride S * token pitch
+    if dq is None:
+        dq = torch.empty(B, Sq, Hq, D, device=q.device, dtype=torch.bfloat16)
+    if dk is None:
+        dk = torch.empty(B, Sk, Hkv, D, device=q.device, dtype=torch.bfloat16)
+    if dv is None:
+        dv = torch.empty(B, Sk, Hkv, D, device=q.device, dtype=torch.bfloat16)
+    for t, S_ in ((dq, Sq), (dk, Sk), (dv, Sk)):
+        assert t.stride(3) == 1 and t.stride(2) == D and (B == 1 or t.stride(0) == S_ * t.stride(1))
     delta = torch.empty(B, Hq, Sq, device=q.device, dtype=torch.float32)
     kv = key_valid.to(torch.uint8).contiguous() if key_valid is not None else None
     bs = bias.float().contiguous() if bias is not None else None

@@ -47,3 +47,21 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     torch.cuda.synchronize()
     assert int(res.item()) == 1
     check_status()
+
+
+def test_tp_fused_kernels_single_rank():
+    """world = 1: the fused kernels degenerate to GEMM (+ slot round trip) — exercises the tile pipeline."""
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "mp", "tp_worker.py")], capture_output=True, text=True,
+                       timeout=600)
+    assert "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tp_fused_kernels_match_nccl():
+    n = min(_ngpu(), 8)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29621",
+                        os.path.join(ROOT, "tests", "mp", "tp_worker.py")], capture_output=True, text=True, timeout=600,
+                       env=env)
+    assert "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
