@@ -1,0 +1,96 @@
+"""Secondary benchmark workloads behind ``bench.py --workload {wm,gpt}``.
+
+wm   Dreamer-style world-model dynamics transformer (24 × d2048, 16/4 heads GQA, SwiGLU 5632, block-causal over
+     64 frames × (256 latents + 1 action token)), flow-matching loss, AdamW 3e-4, bf16, tensor parallel over all N
+     ranks with sequence-parallel activations (fused all-gather→GEMM and GEMM→reduce-scatter kernels).
+     Global batch = one sequence per rank (8 at N = 8).  Metric: sequences / s.
+"""
+import json
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def run(args, rank, local_rank, world):
+    if args.workload == "wm":
+        return run_wm(args, rank, local_rank, world)
+    raise SystemExit(f"unknown workload {args.workload}")
+
+
+def run_wm(args, rank, local_rank, world):
+    from noeira_b200 import _native
+    from noeira_b200.models.world_model import WorldModel, WorldModelConfig
+    from noeira_b200.ops import check_status
+    from noeira_b200.parallel.ddp import FusedGradSync
+    from noeira_b200.utils.bench_utils import timed_steps
+    cfg = WorldModelConfig()
+    if getattr(args, "small", False):
+        cfg = WorldModelConfig(layers=4, dim=1024, heads=8, kv_heads=4, ff=2816, frames=16)
+    B = world  # one sequence per rank
+    sync = FusedGradSync(world, rank, local_rank) if world > 1 else None
+    model = WorldModel(cfg, batch=B, world=world, rank=rank, grad_sync=sync)
+    ms = model.ms
+    # synthetic data staged in pinned host memory; every step copies this rank's shard to the device
+    z1_h = (torch.randn(ms, cfg.latent_dim)).pin_memory()
+    act_h = (torch.rand(ms, cfg.action_dim) * 2 - 1).pin_memory()
+    z1 = torch.empty(ms, cfg.latent_dim, device="cuda")
+    act = torch.empty(ms, cfg.action_dim, device="cuda")
+    loss_h = torch.zeros(1).pin_memory()
+    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
+    tgen = torch.Generator(device="cuda").manual_seed(7)   # same flow times on every rank
+    rows_seq = torch.arange(ms, device="cuda") // model.S + (rank * ms) // model.S
+
+    def step(e2e=False):
+        if e2e:
+            z1.copy_(z1_h, non_blocking=True)
+            act.copy_(act_h, non_blocking=True)
+        noise = torch.randn(ms, cfg.latent_dim, device="cuda", generator=gen)
+        t = torch.rand(B, device="cuda", generator=tgen)[rows_seq]
+        model.loss_acc.zero_()
+        model.train_step(z1 * model.is_lat[:, None], act, noise * model.is_lat[:, None], t)
+        if e2e:
+            loss_h.copy_(model.loss_acc, non_blocking=True)
+            torch.cuda.synchronize()
+
+    z1.copy_(z1_h)
+    act.copy_(act_h)
+    n0 = _native.launch_count()
+    total_ms, clocks = timed_steps(step, args.steps, args.warmup, world, rank, local_rank)
+    launches = (_native.launch_count() - n0) * args.steps // (args.steps + max(args.warmup, 3))
+    check_status()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(e2e=True)
+    if world > 1:
+        dist.barrier()
+    e2e_s = time.perf_counter() - t0
+    tt = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    e2e_s = float(tt.item())
+    loss = float(model.loss_acc.item())
+    # model FLOPs per sequence: 6 · params · tokens + attention (block-causal ≈ half of S²)
+    S = cfg.seq_len
+    flops = 6.0 * cfg.num_params() * S + 3 * 4.0 * cfg.layers * cfg.heads * cfg.head_dim * S * S * 0.5 * (1 + cfg.frame_len / S)
+    if rank == 0:
+        sps = B * args.steps / (total_ms / 1e3)
+        print(json.dumps({
+            "metric": "world_model_train_sequences_per_s", "value": round(sps, 4), "unit": "sequences/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms / args.steps, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (latents ~N(0,1)^32, actions ~U(-1,1)^6, random-init weights)",
+            "config": {"model": f"dynamics transformer {cfg.layers}x{cfg.dim}, {cfg.heads}/{cfg.kv_heads} heads, ff {cfg.ff}, "
+                                f"{cfg.num_params() / 1e9:.2f}B params", "global_batch": B, "seq_len": S,
+                       "parallelism": f"tp{world}+sp", "l2": "flushed between timed iterations"},
+            "model_tflops_per_gpu": round(flops * sps / world / 1e12, 1),
+            "clocks": clocks,
+            "e2e": {"value": round(B * args.steps / e2e_s, 4), "unit": "sequences/s",
+                    "h2d_bytes_per_step": int(z1_h.numel() * 4 + act_h.numel() * 4), "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "final_loss": round(loss, 5)}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0

@@ -26,7 +26,7 @@ from .symm import SymmetricHeap
 
 class TPLinearContext:
     def __init__(self, world: int, rank: int, ms: int, k: int, n: int, kind: str, group=None, n_fetch: int = 24,
-                 spin_limit: int = 1 << 24):
+                 spin_limit: int = 1 << 24, alloc_stage: bool = True):
         """kind = "ag" (column parallel: K = full input width, N = local output width)
                   "rs" (row parallel:    K = local input width, N = full output width)."""
         assert ms % 128 == 0, "row shards are whole 128-row blocks"
@@ -45,7 +45,7 @@ class TPLinearContext:
         if kind == "ag":
             self.x = self.heap.tensor(ms * k, torch.bfloat16)
             self.x_shard = self.x.local.view(ms, k)
-            self.stage = torch.zeros(world * ms, k, device=dev, dtype=torch.bfloat16)
+            self.stage = torch.zeros(world * ms, k, device=dev, dtype=torch.bfloat16) if alloc_stage else None
         else:
             self.slots = self.heap.tensor(world * ms * n, torch.bfloat16)
         torch.cuda.synchronize()
@@ -54,16 +54,21 @@ class TPLinearContext:
 
     def gathered_input(self):
         """[P·Ms, K] view of the gathered activations after ``ag_gemm`` (own rows copied in lazily)."""
-        self.stage[self.rank * self.ms:(self.rank + 1) * self.ms].copy_(self.x_shard)
-        return self.stage
+        st = getattr(self, "last_stage", self.stage)
+        st[self.rank * self.ms:(self.rank + 1) * self.ms].copy_(self.x_shard)
+        return st
 
-    def ag_gemm(self, w, b_mn: bool, out=None, bias=None, act=None):
-        """Y[P·Ms, N] = act(all_gather(x_shard) · W + bias).  ``w`` is [K, N] (b_mn) or [N, K]."""
+    def ag_gemm(self, w, b_mn: bool, out=None, bias=None, act=None, stage=None):
+        """Y[P·Ms, N] = act(all_gather(x_shard) · W + bias).  ``w`` is [K, N] (b_mn) or [N, K].
+        ``stage`` (optional [P·Ms, K]) receives the remote shards instead of the context's own buffer, so a
+        layer can keep its gathered input for the backward pass."""
         assert self.kind == "ag"
         if out is None:
             out = torch.empty(self.world * self.ms, self.n, device=w.device, dtype=torch.bfloat16)
+        stage = self.stage if stage is None else stage
+        self.last_stage = stage
         check(self.lib.nb_tp_ag_gemm(
-            ctypes.c_int(self.world), ctypes.c_int(self.rank), self.x.ptr_table(), ptr(self.stage), self.ctl.ptr_table(),
+            ctypes.c_int(self.world), ctypes.c_int(self.rank), self.x.ptr_table(), ptr(stage), self.ctl.ptr_table(),
             ptr(w), ptr(out), ctypes.c_int(self.ms), ctypes.c_int(self.n), ctypes.c_int(self.k), ctypes.c_int(self.k),
             ctypes.c_int(w.stride(0)), ctypes.c_int(out.stride(0)), ctypes.c_int(int(b_mn)), ptr(bias),
             ctypes.c_int(ACT[act]), ctypes.c_int(self.n_fetch), ctypes.c_uint(self.spin_limit),
