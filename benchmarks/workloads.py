@@ -26,7 +26,7 @@ def run_wm(args, rank, local_rank, world):
     from noeira_b200.utils.bench_utils import timed_steps
     cfg = WorldModelConfig()
     if getattr(args, "small", False):
-        cfg = WorldModelConfig(layers=4, dim=1024, heads=8, kv_heads=4, ff=2816, frames=16)
+        cfg = WorldModelConfig(layers=4, dim=1024, heads=8, kv_heads=1, ff=2816, frames=16)
     B = world  # one sequence per rank
     sync = FusedGradSync(world, rank, local_rank) if world > 1 else None
     model = WorldModel(cfg, batch=B, world=world, rank=rank, grad_sync=sync)

@@ -1,0 +1,314 @@
+"""SAC and TD3 (continuous control, off-policy) on the explicit-VJP nn layer; run on CPU (fp32) or GPU (bf16).
+
+Pipeline of one update (noeira/deep_agents/sac/trainer.mojo:11-19,604-703):
+    sample → target y = r + γ(1−d)(min Q_targ(s′,a′) − α log π(a′|s′)) → twin-critic MSE step →
+    actor loss mean(α log π − min Q(s, a_π)) with the critics' parameters held fixed → temperature step
+    (ScalarAdam on ln α, gradient −(mean log π + H_target), H_target = −ACT, α₀ = 0.2) → Polyak(τ).
+Networks (noeira/deep_agents/sac/config.mojo:52-74): actor = StochasticActor(trunk 2×LinearReLU, heads μ / ln σ),
+critic = Sequential(LinearReLU(OBS+ACT,H), LinearReLU(H,H), Linear(H,1)), two of them with Polyak targets.
+Squashed Gaussian (noeira/deep_agents/loss/squashed_gaussian.mojo): ln σ clamped to [−5, 2] with zero gradient
+where clamped; u = μ + σ z, a = c·tanh u, log π = Σ(−½z² − ln σ − ½ ln 2π − ln(c(1−tanh²u) + 1e-6)).
+Checkpoint layout: actor, critic 1, critic 2 in pack order in ONE file without prefixes plus K scalars
+``alpha.*`` / ``total_train_steps`` (noeira/deep_agents/sac/trainer.mojo:1083-1103).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import nn
+from ..data.replay import StoreReplay
+
+LOG2PI = math.log(2 * math.pi)
+
+
+@dataclass
+class SACConfig:
+    obs_dim: int = 17
+    act_dim: int = 6
+    hidden: int = 256
+    batch: int = 256
+    actor_lr: float = 3e-4
+    critic_lr: float = 3e-4
+    alpha_lr: float = 3e-4
+    gamma: float = 0.99
+    tau: float = 0.005
+    init_alpha: float = 0.2
+    action_scale: float = 1.0
+    auto_entropy: bool = True
+    seed: int = 0
+
+
+def make_sac_actor(obs, act, hidden):
+    return nn.StochasticActor(nn.Sequential(nn.LinearReLU(obs, hidden, need_input_grad=False), nn.LinearReLU(hidden, hidden)),
+                              hidden, act)
+
+
+def make_critic(obs, act, hidden):
+    return nn.Sequential(nn.LinearReLU(obs + act, hidden), nn.LinearReLU(hidden, hidden), nn.Linear(hidden, 1, out_fp32=True))
+
+
+class SquashedGaussian:
+    """Reparameterised tanh-Gaussian with explicit backward."""
+
+    LS_MIN, LS_MAX = -5.0, 2.0
+
+    def __init__(self, act_dim, scale=1.0):
+        self.A, self.c = act_dim, scale
+
+    def forward(self, packed, z):
+        p = packed.float()
+        mu, ls_raw = p[:, : self.A], p[:, self.A: 2 * self.A]
+        ls = ls_raw.clamp(self.LS_MIN, self.LS_MAX)
+        self._free = ((ls_raw > self.LS_MIN) & (ls_raw < self.LS_MAX)).float()
+        sd = ls.exp()
+        u = mu + sd * z
+        y = torch.tanh(u)
+        self._sd_z, self._y = sd * z, y
+        a = self.c * y
+        logp = (-0.5 * z * z - ls - 0.5 * LOG2PI - torch.log(self.c * (1 - y * y) + 1e-6)).sum(1)
+        return a, logp
+
+    def vjp(self, da, dlogp):
+        """da [B, A] (dL/da), dlogp [B] (dL/dlogπ) → gradient of the packed [μ | ln σ]."""
+        y = self._y
+        one = 1 - y * y
+        gu = 2 * self.c * y * one / (self.c * one + 1e-6)          # d logπ / du
+        du = da * self.c * one + dlogp[:, None] * gu
+        dls = (du * self._sd_z - dlogp[:, None]) * self._free
+        return torch.cat([du, dls], 1)
+
+
+class SACTrainer:
+    def __init__(self, cfg: SACConfig = None, device="cpu"):
+        self.cfg = cfg = cfg or SACConfig()
+        self.device = torch.device(device)
+        nn.manual_seed(cfg.seed)
+        O, A, H = cfg.obs_dim, cfg.act_dim, cfg.hidden
+        self.actor = make_sac_actor(O, A, H).to(self.device)
+        self.q1, self.q2 = make_critic(O, A, H).to(self.device), make_critic(O, A, H).to(self.device)
+        self.q1t, self.q2t = make_critic(O, A, H).to(self.device), make_critic(O, A, H).to(self.device)
+        self.q1t.copy_from(self.q1)
+        self.q2t.copy_from(self.q2)
+        self.actor_opt = nn.Adam(self.actor.named_params(), lr=cfg.actor_lr)
+        self.critic_opt = nn.Adam(list(self.q1.named_params("q1.")) + list(self.q2.named_params("q2.")), lr=cfg.critic_lr)
+        self.target_arena = nn.ParamArena(list(self.q1t.named_params("q1.")) + list(self.q2t.named_params("q2.")),
+                                          with_moments=False)
+        self.alpha_opt = nn.ScalarAdam(cfg.init_alpha, cfg.alpha_lr, device=self.device)
+        self.target_entropy = -float(A)
+        self.dist = SquashedGaussian(A, cfg.action_scale)
+        self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed + 1)
+        self.total_train_steps = 0
+        self.metrics = {}
+        self._pad = (O + A + 7) // 8 * 8 if self.device.type == "cuda" else O + A
+
+    # ------------------------------------------------------------------ helpers
+    def _act_in(self, x):
+        if self.device.type == "cuda":
+            w = (x.shape[1] + 7) // 8 * 8
+            out = torch.zeros(x.shape[0], w, device=self.device, dtype=torch.bfloat16)
+            out[:, : x.shape[1]] = x
+            return out[:, : x.shape[1]]
+        return x
+
+    def _sa(self, s, a):
+        return self._act_in(torch.cat([s.float(), a.float()], 1))
+
+    def _noise(self, n):
+        return torch.randn(n, self.cfg.act_dim, device=self.device, generator=self.gen)
+
+    @property
+    def alpha(self):
+        return self.alpha_opt.alpha
+
+    def select_action(self, obs, deterministic=False):
+        packed = self.actor.forward(self._act_in(obs))
+        if deterministic:
+            return self.cfg.action_scale * torch.tanh(packed.float()[:, : self.cfg.act_dim])
+        a, _ = self.dist.forward(packed, self._noise(obs.shape[0]))
+        return a
+
+    # ------------------------------------------------------------------ update
+    def update(self, s, a, r, sp, d):
+        cfg = self.cfg
+        B = s.shape[0]
+        alpha = float(self.alpha) if self.device.type == "cpu" else self.alpha
+        # ---- target
+        ap, logpp = self.dist.forward(self.actor.forward(self._act_in(sp)), self._noise(B))
+        sap = self._sa(sp, ap)
+        qt = torch.minimum(self.q1t.forward(sap).float()[:, 0], self.q2t.forward(sap).float()[:, 0])
+        y = r + cfg.gamma * (1 - d) * (qt - alpha * logpp)
+        # ---- critics
+        sa = self._sa(s, a)
+        closs = 0.0
+        for q in (self.q1, self.q2):
+            qv = q.forward(sa).float()[:, 0]
+            diff = qv - y
+            closs = closs + (diff * diff).mean()
+            q.vjp((2.0 / B * diff)[:, None])
+        self.critic_opt.step(zero_grad=True)
+        # ---- actor (critic parameters fixed)
+        packed = self.actor.forward(self._act_in(s))
+        api, logpi = self.dist.forward(packed, self._noise(B))
+        sapi = self._sa(s, api)
+        q1v, q2v = self.q1.forward(sapi).float()[:, 0], self.q2.forward(sapi).float()[:, 0]
+        use1 = (q1v <= q2v).float()
+        aloss = (alpha * logpi - torch.minimum(q1v, q2v)).mean()
+        ps = [p for q in (self.q1, self.q2) for p in q.params()]
+        for p in ps:
+            p.frozen = True
+        d1 = self.q1.vjp((-use1 / B)[:, None])
+        d2 = self.q2.vjp((-(1 - use1) / B)[:, None])
+        for p in ps:
+            p.frozen = False
+        da = (d1.float() + d2.float())[:, cfg.obs_dim: cfg.obs_dim + cfg.act_dim]
+        dpacked = self.dist.vjp(da, torch.full((B,), 1.0, device=self.device) * alpha / B)
+        self.actor.vjp(dpacked if self.device.type == "cpu" else dpacked.to(torch.bfloat16))
+        self.actor_opt.step(zero_grad=True)
+        # ---- temperature
+        if cfg.auto_entropy:
+            self.alpha_opt.step_alpha(logpi.mean().reshape(1) if self.device.type == "cuda" else logpi.mean(), self.target_entropy)
+        # ---- Polyak
+        nn.polyak(self.target_arena, self.critic_opt.arena, cfg.tau)
+        self.total_train_steps += 1
+        self.metrics = dict(critic_loss=closs, actor_loss=aloss, mean_q=q1v.mean(), mean_logp=logpi.mean())
+        return self.metrics
+
+    # ------------------------------------------------------------------ persistence (reference layout)
+    def save(self, path):
+        from ..io.checkpoint import save_params_multi
+        st = self.alpha_opt.state.cpu().tolist()
+        save_params_multi(path, [self.actor, self.q1, self.q2], {
+            "alpha.log_alpha": st[0], "alpha.m": st[1], "alpha.v": st[2], "alpha.b1t": st[3], "alpha.b2t": st[4],
+            "alpha.alpha": st[5], "total_train_steps": float(self.total_train_steps)})
+
+    def load(self, path):
+        from ..io.checkpoint import load_params_multi
+        sc = load_params_multi(path, [self.actor, self.q1, self.q2])
+        if "alpha.log_alpha" in sc:
+            self.alpha_opt.state.copy_(torch.tensor([sc[k] for k in ("alpha.log_alpha", "alpha.m", "alpha.v", "alpha.b1t",
+                                                                     "alpha.b2t", "alpha.alpha")]))
+        self.total_train_steps = int(sc.get("total_train_steps", 0))
+        self.q1t.copy_from(self.q1)
+        self.q2t.copy_from(self.q2)
+
+
+class SACAgent:
+    """Facade: drives a BatchedEnv with a replay buffer (noeira/deep_agents/sac/agent.mojo:58,
+    run_offpolicy_train_batched noeira/deep_agents/training/driver_offpolicy.mojo:823)."""
+
+    def __init__(self, env, cfg: SACConfig = None, capacity=1_000_000, learning_starts=1000, utd=1):
+        self.env = env
+        cfg = cfg or SACConfig(obs_dim=env.obs_dim, act_dim=env.act_dim)
+        self.trainer = SACTrainer(cfg, device=env.device)
+        self.replay = StoreReplay(capacity, env.obs_dim, env.act_dim, device=env.device, seed=cfg.seed)
+        self.learning_starts, self.utd = learning_starts, utd
+
+    def train(self, total_env_steps, logger=None, log_every=1000):
+        env, tr = self.env, self.trainer
+        obs = env.reset_batch().clone()
+        steps = 0
+        act_buf = torch.zeros(env.n_envs, (env.act_dim + 7) // 8 * 8, device=env.device)
+        while steps < total_env_steps:
+            if steps < self.learning_starts:
+                a = torch.rand(env.n_envs, env.act_dim, device=env.device) * 2 - 1
+            else:
+                a = tr.select_action(obs).float()
+            act_buf[:, : env.act_dim] = a
+            env.step_batch(act_buf)
+            self.replay.store_batch(obs, a, env.reward, env.next_obs, env.terminated)
+            obs = env.obs.clone()
+            steps += env.n_envs
+            if steps >= self.learning_starts:
+                for _ in range(self.utd):
+                    tr.update(*self.replay.sample(tr.cfg.batch))
+            if logger is not None and steps % log_every < env.n_envs and tr.metrics:
+                logger.log_scalars(steps, {k: float(v) for k, v in tr.metrics.items()})
+        return tr.metrics
+
+
+# ------------------------------------------------------------------------------------------ TD3
+@dataclass
+class TD3Config:
+    obs_dim: int = 17
+    act_dim: int = 6
+    hidden: int = 256
+    batch: int = 256
+    actor_lr: float = 3e-4
+    critic_lr: float = 3e-4
+    gamma: float = 0.99
+    tau: float = 0.005
+    policy_noise: float = 0.2
+    noise_clip: float = 0.5
+    policy_delay: int = 2
+    explore_noise: float = 0.1
+    action_scale: float = 1.0
+    seed: int = 0
+
+
+class TD3Trainer:
+    """Deterministic actor + Gaussian exploration, target-policy smoothing, delayed actor / target updates
+    (noeira/deep_agents/td3/trainer.mojo:84, target_y_block.mojo:79, blocks/delayed_actor_polyak_step.mojo:28)."""
+
+    def __init__(self, cfg: TD3Config = None, device="cpu"):
+        self.cfg = cfg = cfg or TD3Config()
+        self.device = torch.device(device)
+        nn.manual_seed(cfg.seed)
+        O, A, H = cfg.obs_dim, cfg.act_dim, cfg.hidden
+        mk_actor = lambda: nn.Sequential(nn.LinearReLU(O, H, need_input_grad=False), nn.LinearReLU(H, H),
+                                         nn.Linear(H, A, act="tanh", out_fp32=False))
+        self.actor, self.actor_t = mk_actor().to(self.device), mk_actor().to(self.device)
+        self.actor_t.copy_from(self.actor)
+        self.q1, self.q2 = make_critic(O, A, H).to(self.device), make_critic(O, A, H).to(self.device)
+        self.q1t, self.q2t = make_critic(O, A, H).to(self.device), make_critic(O, A, H).to(self.device)
+        self.q1t.copy_from(self.q1)
+        self.q2t.copy_from(self.q2)
+        self.actor_opt = nn.Adam(self.actor.named_params(), lr=cfg.actor_lr)
+        self.critic_opt = nn.Adam(list(self.q1.named_params("q1.")) + list(self.q2.named_params("q2.")), lr=cfg.critic_lr)
+        self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed + 1)
+        self.total_train_steps = 0
+
+    _act_in = SACTrainer._act_in
+    _sa = SACTrainer._sa
+
+    def select_action(self, obs, explore=True):
+        a = self.cfg.action_scale * self.actor.forward(self._act_in(obs)).float()
+        if explore:
+            a = (a + self.cfg.explore_noise * torch.randn(a.shape, device=self.device, generator=self.gen)).clamp(
+                -self.cfg.action_scale, self.cfg.action_scale)
+        return a
+
+    def update(self, s, a, r, sp, d):
+        cfg, B = self.cfg, s.shape[0]
+        noise = (torch.randn(B, cfg.act_dim, device=self.device, generator=self.gen) * cfg.policy_noise).clamp(
+            -cfg.noise_clip, cfg.noise_clip)
+        ap = (cfg.action_scale * self.actor_t.forward(self._act_in(sp)).float() + noise).clamp(-cfg.action_scale, cfg.action_scale)
+        sap = self._sa(sp, ap)
+        y = r + cfg.gamma * (1 - d) * torch.minimum(self.q1t.forward(sap).float()[:, 0], self.q2t.forward(sap).float()[:, 0])
+        sa = self._sa(s, a)
+        closs = 0.0
+        for q in (self.q1, self.q2):
+            diff = q.forward(sa).float()[:, 0] - y
+            closs = closs + (diff * diff).mean()
+            q.vjp((2.0 / B * diff)[:, None])
+        self.critic_opt.step(zero_grad=True)
+        self.total_train_steps += 1
+        out = dict(critic_loss=closs)
+        if self.total_train_steps % cfg.policy_delay == 0:
+            api = self.actor.forward(self._act_in(s))
+            q1v = self.q1.forward(self._sa(s, cfg.action_scale * api.float()))
+            ps = self.q1.params()
+            for p in ps:
+                p.frozen = True
+            dsa = self.q1.vjp(torch.full((B, 1), -1.0 / B, device=self.device))
+            for p in ps:
+                p.frozen = False
+            da = dsa.float()[:, cfg.obs_dim: cfg.obs_dim + cfg.act_dim] * cfg.action_scale
+            self.actor.vjp(da if self.device.type == "cpu" else da.to(torch.bfloat16))
+            self.actor_opt.step(zero_grad=True)
+            for t, o in ((self.actor_t, self.actor), (self.q1t, self.q1), (self.q2t, self.q2)):
+                t.polyak_from(o, cfg.tau)
+            out["actor_loss"] = -q1v.float().mean()
+        return out

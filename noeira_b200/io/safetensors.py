@@ -163,7 +163,7 @@ def load_safetensors(path: str, named_params, named_states=(), strict: bool = Tr
         a = st.get(name)
         if a.size != p.numel:
             raise SafeTensorsError(f"{name}: file has {a.size} values, parameter has {p.numel}")
-        p.set_(torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).reshape(p.shape))
+        p.set_(torch.from_numpy(np.array(a, dtype=np.float32)).reshape(p.shape))
         used += 1
     for name, s in named_states:
         if name not in have:
@@ -172,7 +172,7 @@ def load_safetensors(path: str, named_params, named_states=(), strict: bool = Tr
             continue
         a = st.get(name)
         with torch.no_grad():
-            s.data.copy_(torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).reshape(s.data.shape))
+            s.data.copy_(torch.from_numpy(np.array(a, dtype=np.float32)).reshape(s.data.shape))
         used += 1
     if strict and used != len(have):
         extra = have - {n for n, _ in named_params} - {n for n, _ in named_states}

@@ -70,11 +70,11 @@ class WorldModelConfig:
 
 
 def _mk(name, shape, std, gen, decay=True, fill=None):
-    p = Param(name, shape, decay=decay)
+    p = Param(name, shape, decay=decay, device=gen.device)
     if fill is not None:
         p.set_(torch.full(shape, float(fill)))
     else:
-        p.set_(torch.randn(shape, generator=gen) * std)
+        p.set_(torch.randn(shape, generator=gen, device=gen.device) * std)
     return p
 
 
@@ -94,30 +94,30 @@ class TPBlock:
         pre = f"blocks.{idx}."
         # sharded parameters: every rank draws the FULL matrices from the same stream and keeps its slice, so the
         # model is identical for any P
-        wq = torch.randn(d, cfg.heads * hd, generator=gen) * (1 / math.sqrt(d))
-        wk = torch.randn(d, cfg.kv_heads * hd, generator=gen) * (1 / math.sqrt(d))
-        wv = torch.randn(d, cfg.kv_heads * hd, generator=gen) * (1 / math.sqrt(d))
-        wo = torch.randn(cfg.heads * hd, d, generator=gen) * (1 / math.sqrt(cfg.heads * hd) / math.sqrt(2 * cfg.layers))
-        wg = torch.randn(d, cfg.ff, generator=gen) * (1 / math.sqrt(d))
-        wu = torch.randn(d, cfg.ff, generator=gen) * (1 / math.sqrt(d))
-        wd = torch.randn(cfg.ff, d, generator=gen) * (1 / math.sqrt(cfg.ff) / math.sqrt(2 * cfg.layers))
+        rn = lambda *shape: torch.randn(*shape, generator=gen, device=gen.device)
+        wq = rn(d, cfg.heads * hd) * (1 / math.sqrt(d))
+        wk = rn(d, cfg.kv_heads * hd) * (1 / math.sqrt(d))
+        wv = rn(d, cfg.kv_heads * hd) * (1 / math.sqrt(d))
+        wo = rn(cfg.heads * hd, d) * (1 / math.sqrt(cfg.heads * hd) / math.sqrt(2 * cfg.layers))
+        wg = rn(d, cfg.ff) * (1 / math.sqrt(d))
+        wu = rn(d, cfg.ff) * (1 / math.sqrt(d))
+        wd = rn(cfg.ff, d) * (1 / math.sqrt(cfg.ff) / math.sqrt(2 * cfg.layers))
         q0 = rank * self.hq * hd
         kvh = (rank // self.kv_rep) * self.hkv * hd if world >= cfg.kv_heads else rank * self.hkv * hd
-        self.w_qkv = Param(pre + "attn.qkv.weight", (d, n_qkv))
+        dev = gen.device
+        self.w_qkv = Param(pre + "attn.qkv.weight", (d, n_qkv), device=dev)
         self.w_qkv.set_(torch.cat([wq[:, q0:q0 + self.hq * hd], wk[:, kvh:kvh + self.hkv * hd], wv[:, kvh:kvh + self.hkv * hd]], 1))
-        self.w_out = Param(pre + "attn.out.weight", (self.hq * hd, d))
+        self.w_out = Param(pre + "attn.out.weight", (self.hq * hd, d), device=dev)
         self.w_out.set_(wo[q0:q0 + self.hq * hd])
         f0 = rank * self.ffl
-        self.w_up = Param(pre + "ffn.0.weight", (d, 2 * self.ffl))
+        self.w_up = Param(pre + "ffn.0.weight", (d, 2 * self.ffl), device=dev)
         self.w_up.set_(torch.cat([wg[:, f0:f0 + self.ffl], wu[:, f0:f0 + self.ffl]], 1))
-        self.w_down = Param(pre + "ffn.1.weight", (self.ffl, d))
+        self.w_down = Param(pre + "ffn.1.weight", (self.ffl, d), device=dev)
         self.w_down.set_(wd[f0:f0 + self.ffl])
         self.g1 = _mk(pre + "norm1.gamma", (d,), 0, gen, decay=False, fill=1.0)
         self.g2 = _mk(pre + "norm2.gamma", (d,), 0, gen, decay=False, fill=1.0)
         self.sharded = [self.w_qkv, self.w_out, self.w_up, self.w_down]
         self.replicated = [self.g1, self.g2]
-        for p in self.sharded + self.replicated:
-            p.to(device)
 
 
 class WorldModel:
@@ -134,13 +134,14 @@ class WorldModel:
         self.ms = rows // world
         self.rows = rows
         d, hd = cfg.dim, cfg.head_dim
-        gen = torch.Generator().manual_seed(cfg.seed)
+        # weights are drawn on the device (same seed → same full matrices on every rank, each keeps its slice)
+        gen = torch.Generator(device=self.device).manual_seed(cfg.seed)
         nn.manual_seed(cfg.seed)
         self.in_lat = nn.Linear(cfg.latent_dim, d, bias=False, need_input_grad=False).to(self.device)
         self.in_act = nn.Linear(cfg.action_dim, d, bias=False, need_input_grad=False).to(self.device)
         self.t_lin = nn.Linear(d, d, act="silu", bias=False, need_input_grad=False).to(self.device)
         self.out_lin = nn.Linear(d, cfg.latent_dim, bias=False).to(self.device)
-        self.out_g = _mk("out_norm.gamma", (d,), 0, gen, decay=False, fill=1.0).to(self.device)
+        self.out_g = _mk("out_norm.gamma", (d,), 0, gen, decay=False, fill=1.0)
         self.blocks = [TPBlock(i, cfg, world, rank, gen, self.device) for i in range(cfg.layers)]
         named_rep = (list(self.in_lat.named_params("in_latent.")) + list(self.in_act.named_params("in_action."))
                      + list(self.t_lin.named_params("time.")) + list(self.out_lin.named_params("out."))

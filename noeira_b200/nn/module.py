@@ -25,12 +25,23 @@ import torch
 from .init import Initializer, Kaiming
 from .param import Param, State
 
-_GEN = torch.Generator().manual_seed(0)
+import threading
+
+_TLS = threading.local()
+
+
+def _gen() -> torch.Generator:
+    """Per-thread initialisation stream (rank threads of the simulator must not interleave their draws)."""
+    g = getattr(_TLS, "gen", None)
+    if g is None:
+        g = torch.Generator().manual_seed(0)
+        _TLS.gen = g
+    return g
 
 
 def manual_seed(seed: int):
-    """Seed the (CPU-side, deterministic) parameter initialisation stream."""
-    _GEN.manual_seed(int(seed))
+    """Seed the (CPU-side, deterministic) parameter initialisation stream of the calling thread."""
+    _gen().manual_seed(int(seed))
 
 
 class Module:
@@ -48,7 +59,7 @@ class Module:
     def add_param(self, name: str, shape, decay: bool = True, init: Initializer = None, fan_in: int = 1,
                   fan_out: int = 1, pad_rows: bool = True) -> Param:
         p = Param(name, shape, decay=decay, pad_rows=pad_rows)
-        p.set_((init or Kaiming())(tuple(shape), fan_in, fan_out, _GEN))
+        p.set_((init or Kaiming())(tuple(shape), fan_in, fan_out, _gen()))
         self._params[name] = p
         return p
 

@@ -1,0 +1,144 @@
+"""Distributed gates on the in-process simulator (threads, rank-ordered reductions) and on gloo processes.
+Modelled on the reference's gates (tests/nn/distributed/test_fibers.mojo, test_ddp_mlp.mojo, test_zero1.mojo):
+N=1 identity bit-exact, replica agreement bit-exact, DDP vs ZeRO bit-exact without clip, a failing rank or a
+missing rendezvous ends the run with an error instead of a hang."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _net():
+    from noeira_b200 import nn
+    nn.manual_seed(5)
+    return nn.Sequential(nn.LinearTanh(12, 40), nn.LinearTanh(40, 40), nn.Linear(40, 3))
+
+
+def _train(comm, strategy, steps=4, clip=0.0, world_batch=16):
+    from noeira_b200 import nn
+    from noeira_b200.parallel.strategy import STRATEGIES
+    net = _net()
+    opt = nn.AdamW(net.named_params(), lr=1e-2, weight_decay=0.01)
+    st = STRATEGIES[strategy](opt, comm)
+    st.sync_params()
+    g = torch.Generator().manual_seed(0)
+    per = world_batch // comm.world
+    for _ in range(steps):
+        x = torch.randn(world_batch, 12, generator=g)
+        y = torch.randn(world_batch, 3, generator=g)
+        xs, ys = x[comm.rank * per:(comm.rank + 1) * per], y[comm.rank * per:(comm.rank + 1) * per]
+        if strategy == "zero3" and not st.gathered:
+            st.gather_params()
+        out = net.forward(xs)
+        net.vjp(2.0 * (out - ys) / per)
+        st.reduce_grads()
+        if clip > 0:
+            st.clip_grads(clip)
+        st.step()
+    if strategy == "zero3":
+        st.gather_params()
+    return opt.arena.val.clone(), st.state_bytes_per_rank()
+
+
+def test_n1_identity_and_replica_agreement_and_strategy_equivalence():
+    from noeira_b200.parallel.fibers import run_ranks
+    base = run_ranks(1, lambda c: _train(c, "ddp"))[0][0]
+    single = _train(type("C", (), dict(world=1, rank=0, all_reduce=lambda s, t: None, broadcast=lambda s, t, src=0: None))(), "ddp")[0]
+    assert torch.equal(base, single)                                   # N=1 identity, bit exact
+    res = {}
+    for strat in ("ddp", "zero1", "zero2", "zero3"):
+        out = run_ranks(2, lambda c, s=strat: _train(c, s))
+        assert torch.equal(out[0][0], out[1][0]), strat                # replicas agree bit for bit
+        res[strat] = out[0]
+    for strat in ("zero1", "zero2", "zero3"):
+        assert torch.equal(res["ddp"][0], res[strat][0]), strat        # DDP == ZeRO without clip
+    assert res["ddp"][1] > res["zero1"][1] > res["zero2"][1] > res["zero3"][1]
+    # two ranks with half batches ≈ one rank with the full batch (mean of shard means)
+    assert torch.allclose(res["ddp"][0], base, atol=1e-5)
+
+
+def test_clip_norm_matches_between_ddp_and_zero():
+    from noeira_b200.parallel.fibers import run_ranks
+    a = run_ranks(2, lambda c: _train(c, "ddp", clip=0.05))[0][0]
+    b = run_ranks(2, lambda c: _train(c, "zero1", clip=0.05))[0][0]
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+def test_rank_exception_ends_the_run_without_hanging():
+    from noeira_b200.parallel.fibers import run_ranks
+
+    def body(c):
+        t = torch.ones(4)
+        c.all_reduce(t)
+        if c.rank == 1:
+            raise ValueError("rank 1 broke")
+        c.all_reduce(t)
+        return t
+
+    with pytest.raises(ValueError, match="rank 1 broke"):
+        run_ranks(3, body, timeout=5)
+
+
+def test_missing_rendezvous_is_an_error_not_a_hang():
+    from noeira_b200.parallel.fibers import CollectiveMismatch, RankFailed, run_ranks
+
+    def body(c):
+        t = torch.ones(2)
+        c.all_reduce(t)
+        if c.rank != 0:
+            c.all_reduce(t)       # rank 0 never joins this one
+        return t
+
+    with pytest.raises((RankFailed, CollectiveMismatch)):
+        run_ranks(2, body, timeout=5)
+
+    def body2(c):
+        t = torch.ones(2)
+        if c.rank == 0:
+            c.all_reduce(t)
+        else:
+            c.barrier()
+        return t
+
+    with pytest.raises((RankFailed, CollectiveMismatch)):
+        run_ranks(2, body2, timeout=5)
+
+
+def test_collectives_are_rank_ordered_and_deterministic():
+    from noeira_b200.parallel.fibers import run_ranks
+
+    def body(c):
+        t = torch.full((3,), 0.1 * (c.rank + 1))
+        c.all_reduce(t)
+        out = torch.zeros(2)
+        c.reduce_scatter(out, torch.arange(8.0) + c.rank)
+        gat = torch.zeros(8)
+        c.all_gather(gat, torch.full((2,), float(c.rank)))
+        return t, out, gat
+
+    r = run_ranks(4, body)
+    exp = ((torch.tensor(0.1) + torch.tensor(0.2)) + torch.tensor(0.3)) + torch.tensor(0.4)
+    assert all(torch.equal(x[0], torch.full((3,), float(exp))) for x in r)
+    assert torch.equal(r[1][1], torch.tensor([4 * 2.0 + 6, 4 * 3.0 + 6]))
+    assert torch.equal(r[2][2], torch.tensor([0., 0, 1, 1, 2, 2, 3, 3]))
+
+
+def test_gloo_processes_match_simulator():
+    """Two real processes over gloo reproduce the simulator's DDP result bit for bit."""
+    from noeira_b200.parallel.fibers import run_ranks
+    sim = run_ranks(2, lambda c: _train(c, "ddp"))[0][0]
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        env = dict(os.environ, OUT=os.path.join(d, "v"), OMP_NUM_THREADS="1")
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                            "--master-addr", "127.0.0.1", "--master-port", "29731",
+                            os.path.join(ROOT, "tests", "mp", "gloo_worker.py")], env=env, capture_output=True, text=True,
+                           timeout=240)
+        assert r.returncode == 0, r.stderr[-2000:]
+        v0, v1 = torch.load(os.path.join(d, "v0")), torch.load(os.path.join(d, "v1"))
+    assert torch.equal(v0, v1)
+    assert torch.equal(v0, sim)
