@@ -15,6 +15,8 @@ import torch.distributed as dist
 def run(args, rank, local_rank, world):
     if args.workload == "wm":
         return run_wm(args, rank, local_rank, world)
+    if args.workload in ("act", "vla"):
+        return run_dp(args, rank, local_rank, world)
     raise SystemExit(f"unknown workload {args.workload}")
 
 
@@ -91,6 +93,90 @@ def run_wm(args, rank, local_rank, world):
             "e2e": {"value": round(B * args.steps / e2e_s, 4), "unit": "sequences/s",
                     "h2d_bytes_per_step": int(z1_h.numel() * 4 + act_h.numel() * 4), "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": round(loss, 5)}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_dp(args, rank, local_rank, world):
+    """ACT (batch 8 / GPU, 2 cameras 3x480x640 uint8) and SmolVLA-style VLA (batch 64 / GPU, 3 cameras 3x512x512),
+    data parallel with the fused gradient all-reduce + AdamW kernel.  Metric: training samples / s (whole job)."""
+    from noeira_b200 import _native
+    from noeira_b200.ops import check_status
+    from noeira_b200.parallel.ddp import FusedGradSync
+    from noeira_b200.utils.bench_utils import timed_steps
+    sync = FusedGradSync(world, rank, local_rank) if world > 1 else None
+    g = torch.Generator().manual_seed(100 + rank)
+    if args.workload == "act":
+        from noeira_b200.models.act import ACTConfig, ACTTrainer
+        cfg = ACTConfig()
+        B = 8
+        if args.small:
+            cfg = ACTConfig(height=96, width=128, chunk=20, enc_layers=1, dec_layers=1)
+        tr = ACTTrainer(cfg, grad_sync=sync)
+        host = dict(qpos=torch.randn(B, 6, generator=g).pin_memory(),
+                    img=torch.randint(0, 256, (B, cfg.n_cam, 3, cfg.height, cfg.width), dtype=torch.uint8, generator=g).pin_memory(),
+                    act=torch.randn(B, cfg.chunk, 6, generator=g).pin_memory())
+        dev = {k: v.cuda() for k, v in host.items()}
+        valid = torch.ones(B, cfg.chunk + 2, device="cuda")
+        step_fn = lambda: tr.train_step(dev["qpos"], dev["img"], dev["act"], valid)
+        model_desc = f"ACT ResNet-18 + DETR enc {cfg.enc_layers}/dec {cfg.dec_layers}, d {cfg.dim}, chunk {cfg.chunk}, {cfg.n_cam} cams {cfg.height}x{cfg.width}"
+        loss_of = lambda: float(tr.loss_acc[0])
+    else:
+        from noeira_b200.models.vla import VLAConfig, VLATrainer
+        cfg = VLAConfig()
+        B = 64
+        if args.small:
+            cfg = VLAConfig(image=128, vit_layers=2, lm_layers=2)
+            B = 8
+        tr = VLATrainer(cfg, grad_sync=sync)
+        host = dict(img=torch.rand(B, cfg.n_cam, 3, cfg.image, cfg.image, generator=g).to(torch.bfloat16).pin_memory(),
+                    ids=torch.randint(0, cfg.vocab, (B, cfg.n_lang), generator=g).pin_memory(),
+                    state=torch.randn(B, cfg.action_dim, generator=g).pin_memory(),
+                    act=torch.randn(B, cfg.chunk, cfg.action_dim, generator=g).pin_memory())
+        dev = {k: v.cuda() for k, v in host.items()}
+        step_fn = lambda: tr.train_step(dev["img"], dev["ids"], dev["state"], dev["act"])
+        model_desc = (f"ViT {cfg.vit_layers}x{cfg.vit_dim} + LM {cfg.lm_layers}x{cfg.hidden} ({cfg.heads}/{cfg.kv_heads} heads) + "
+                      f"expert {cfg.lm_layers}x{cfg.expert_width}, {cfg.n_cam} cams {cfg.image}^2, chunk {cfg.chunk}; prefix frozen")
+        loss_of = lambda: float(tr.loss_acc[0])
+
+    def e2e_step():
+        for k in host:
+            dev[k].copy_(host[k], non_blocking=True)
+        step_fn()
+        _ = loss_of()
+
+    n0 = _native.launch_count()
+    total_ms, clocks = timed_steps(step_fn, args.steps, args.warmup, world, rank, local_rank)
+    launches = (_native.launch_count() - n0) * args.steps // (args.steps + max(args.warmup, 3))
+    check_status()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    e2e_s = time.perf_counter() - t0
+    tt = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    e2e_s = float(tt.item())
+    if rank == 0:
+        sps = B * world * args.steps / (total_ms / 1e3)
+        print(json.dumps({
+            "metric": f"{args.workload}_train_samples_per_s", "value": round(sps, 2), "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms / args.steps, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seed-generated inputs, random-init weights)",
+            "config": {"model": model_desc, "global_batch": B * world, "seq_len": cfg.chunk, "parallelism": f"dp{world}",
+                       "l2": "flushed between timed iterations"},
+            "clocks": clocks,
+            "e2e": {"value": round(B * world * args.steps / e2e_s, 2), "unit": "samples/s",
+                    "h2d_bytes_per_step": int(sum(v.numel() * v.element_size() for v in host.values())), "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "params_m": round(sum(p.numel for _, p in tr.model.named_params()) / 1e6, 1),
+            "final_loss": round(loss_of(), 5)}))
     if world > 1:
         dist.destroy_process_group()
     return 0

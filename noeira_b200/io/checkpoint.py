@@ -62,10 +62,10 @@ def save_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], name
             _check_name(name)
             has_m = 1 if (with_moments and p.m is not None) else 0
             f.write(f"P {name} {p.numel} {has_m}\n".encode())
-            _write_chunked(f, _to_host_f32(p.data).tobytes())
+            _write_chunked(f, _to_host_f32(p.file_view()).tobytes())
             if has_m:
-                _write_chunked(f, _to_host_f32(p._logical(p.m)).tobytes())
-                _write_chunked(f, _to_host_f32(p._logical(p.v)).tobytes())
+                _write_chunked(f, _to_host_f32(p.file_view(p._logical(p.m))).tobytes())
+                _write_chunked(f, _to_host_f32(p.file_view(p._logical(p.v))).tobytes())
         for name, s in named_states:
             _check_name(name)
             f.write(f"S {name} {s.data.numel()}\n".encode())
@@ -121,13 +121,14 @@ def load_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], name
         if parts[1] != name or int(parts[2]) != p.numel:
             raise CheckpointError(f"section mismatch: file has {parts[1]}[{parts[2]}], model walk expects {name}[{p.numel}]")
         vals = r.payload(p.numel)
-        p.set_(torch.from_numpy(vals.copy()))
+        p.load_file_(torch.from_numpy(vals.copy()))
         if int(parts[3]):
             m, v = r.payload(p.numel), r.payload(p.numel)
             if load_moments and p.m is not None:
                 with torch.no_grad():
-                    p._logical(p.m).copy_(torch.from_numpy(m.copy()).reshape(p.shape))
-                    p._logical(p.v).copy_(torch.from_numpy(v.copy()).reshape(p.shape))
+                    fm = (lambda t: p.from_file(t)) if p.from_file is not None else (lambda t: t)
+                    p._logical(p.m).copy_(fm(torch.from_numpy(m.copy())).reshape(p.shape))
+                    p._logical(p.v).copy_(fm(torch.from_numpy(v.copy())).reshape(p.shape))
     for name, s in named_states:
         ln = r.line()
         parts = (ln or "").split(" ")

@@ -142,7 +142,7 @@ def save_safetensors(path: str, named_params: Iterable[Tuple[str, "Param"]], nam
     w.add_metadata("producer", producer)
     n = 0
     for name, p in named_params:
-        w.add_f32(name, p.data.detach().float().cpu().contiguous().numpy().reshape(-1))
+        w.add_f32(name, p.file_view().detach().float().cpu().contiguous().numpy().reshape(-1))
         n += 1
     for name, s in named_states:
         w.add_f32(name, s.data.detach().float().cpu().numpy().reshape(-1))
@@ -163,7 +163,7 @@ def load_safetensors(path: str, named_params, named_states=(), strict: bool = Tr
         a = st.get(name)
         if a.size != p.numel:
             raise SafeTensorsError(f"{name}: file has {a.size} values, parameter has {p.numel}")
-        p.set_(torch.from_numpy(np.array(a, dtype=np.float32)).reshape(p.shape))
+        p.load_file_(torch.from_numpy(np.array(a, dtype=np.float32)).reshape(-1))
         used += 1
     for name, s in named_states:
         if name not in have:

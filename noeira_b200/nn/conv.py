@@ -1,0 +1,293 @@
+"""Convolutional leaves on the NHWC bf16 path: Conv2D (patch gather + tcgen05 GEMM with fused bias / ReLU),
+BatchNorm2D (training statistics, fused ReLU and residual add), MaxPool2D, and the torchvision-topology
+ResNet-18 backbone used by ACT (noeira/nn/models/resnet18.mojo:142: stride 32, trainable BatchNorm).
+
+Activations are ``[B, H, W, C]``.  ``Conv2D.weight`` is kept in GEMM layout ``[KH·KW·IC, OC]`` in memory; files
+hold the reference layout ``[OC, IC, KH, KW]`` (the parameter carries export / import hooks that permute).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import ops
+from .._native import check, cuda_lib, ptr, stream_ptr
+from .init import Constant, Kaiming, Zero
+from .layers import colsum_into
+from .module import Module
+
+_WS = {}
+
+
+def _scratch(device, n):
+    t = _WS.get(device)
+    if t is None or t.numel() < n:
+        t = torch.empty(max(n, 1 << 20), dtype=torch.float32, device=device)
+        _WS[device] = t
+    return t
+
+
+class Conv2D(Module):
+    def __init__(self, ic, oc, k, stride=1, pad=0, bias=True, relu=False, need_input_grad=True):
+        super().__init__()
+        self.ic, self.oc, self.k, self.stride, self.pad, self.relu = ic, oc, k, stride, pad, relu
+        self.icp = (ic + 7) // 8 * 8          # channels as stored (stem: 3 → 8, extra channels are zero)
+        self.need_input_grad = need_input_grad
+        self.weight = self.add_param("weight", (k * k * self.icp, oc), decay=True, init=Kaiming(), fan_in=ic * k * k,
+                                     fan_out=oc)
+        if self.icp != ic:
+            w = self.weight.data.view(k * k, self.icp, oc)
+            w[:, ic:, :] = 0
+        self.bias = self.add_param("bias", (oc,), decay=False, init=Zero()) if bias else None
+        icp, KK = self.icp, k
+        self.weight.to_file = lambda t: t.view(KK, KK, icp, oc)[:, :, :ic, :].permute(3, 2, 0, 1).contiguous()
+        self.weight.from_file = lambda t: torch.nn.functional.pad(t.reshape(oc, ic, KK, KK).permute(2, 3, 1, 0),
+                                                                  (0, 0, 0, icp - ic)).reshape(KK * KK * icp, oc)
+
+    def out_hw(self, H, W):
+        return (H + 2 * self.pad - self.k) // self.stride + 1, (W + 2 * self.pad - self.k) // self.stride + 1
+
+    def forward(self, x):
+        B, H, W, C = x.shape
+        assert C == self.icp, (C, self.icp)
+        OH, OW = self.out_hw(H, W)
+        self._in = (B, H, W)
+        if not self.on_cuda:
+            self._x = x.float()
+            w = self.weight.data.view(self.k, self.k, self.icp, self.oc).permute(3, 2, 0, 1)
+            y = torch.nn.functional.conv2d(self._x.permute(0, 3, 1, 2), w, self.bias.data if self.bias is not None else None,
+                                           self.stride, self.pad).permute(0, 2, 3, 1)
+            self._y = torch.relu(y) if self.relu else y
+            return self._y
+        M, K = B * OH * OW, self.k * self.k * C
+        if self.k == 1 and self.stride == 1 and self.pad == 0:
+            col = x.reshape(M, C)
+        else:
+            col = torch.empty(M, K, device=x.device, dtype=torch.bfloat16)
+            xc = x if x.is_contiguous() else x.contiguous()
+            check(cuda_lib().nb_im2col(ptr(xc), ptr(col), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, self.k, self.stride,
+                                                                                   self.pad, OH, OW, K)), stream_ptr()), "im2col")
+        self._col = col
+        y = ops.gemm(col, self.weight.shadow, b_mn=True, bias=self.bias.storage if self.bias is not None else None,
+                     act="relu" if self.relu else None)
+        self._y = y
+        return y[:, : self.oc].reshape(B, OH, OW, self.oc) if y.shape[1] != self.oc else y.view(B, OH, OW, self.oc)
+
+    def vjp(self, dy):
+        B, H, W = self._in
+        OH, OW = self.out_hw(H, W)
+        if not self.on_cuda:
+            g = dy.float()
+            if self.relu:
+                g = g * (self._y > 0)
+            w = self.weight.data.view(self.k, self.k, self.icp, self.oc).permute(3, 2, 0, 1)
+            xn, gn = self._x.permute(0, 3, 1, 2), g.permute(0, 3, 1, 2)
+            if not self.weight.frozen:
+                gw = torch.nn.grad.conv2d_weight(xn, w.shape, gn, self.stride, self.pad)
+                self.weight.grad.add_(gw.permute(2, 3, 1, 0).reshape(self.weight.shape))
+                if self.bias is not None:
+                    self.bias.grad.add_(g.sum((0, 1, 2)))
+            if not self.need_input_grad:
+                return None
+            return torch.nn.grad.conv2d_input(xn.shape, w, gn, self.stride, self.pad).permute(0, 2, 3, 1)
+        M = B * OH * OW
+        d2 = dy.reshape(M, self.oc)
+        d2 = d2 if (d2.stride(-1) == 1 and d2.dtype == torch.bfloat16) else d2.to(torch.bfloat16).contiguous()
+        if self.relu:
+            from .layers import act_backward
+            d2 = act_backward(d2.contiguous(), self._y[:, : self.oc].contiguous() if self._y.shape[1] != self.oc else self._y, "relu")
+        if not self.weight.frozen:
+            ops.gemm(self._col, d2, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=self.oc)
+            if self.bias is not None:
+                colsum_into(d2, self.bias.grad_storage, self.oc)
+        if not self.need_input_grad:
+            return None
+        K = self.k * self.k * self.icp
+        dcol = ops.gemm(d2, self.weight.shadow[:, : self.oc])           # [M, K]
+        if self.k == 1 and self.stride == 1 and self.pad == 0:
+            return dcol.view(B, H, W, self.icp)
+        dx = torch.empty(B, H, W, self.icp, device=dy.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_col2im(ptr(dcol), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, self.icp, self.k, self.k, self.stride,
+                                                                               self.pad, OH, OW, K)), stream_ptr()), "col2im")
+        return dx
+
+    def _release(self):
+        self._col = self._y = None
+
+
+class BatchNorm2D(Module):
+    """Per-channel batch statistics over (B, H, W) in training, running statistics in eval; optional fused ReLU and
+    residual add: y = relu(bn(x) + residual).  Params ``gamma`` / ``beta``, states ``running_mean`` / ``running_var``."""
+
+    def __init__(self, c, eps=1e-5, momentum=0.1, relu=False):
+        super().__init__()
+        self.c, self.eps, self.momentum, self.relu = c, eps, momentum, relu
+        self.gamma = self.add_param("gamma", (c,), decay=False, init=Constant(1.0))
+        self.beta = self.add_param("beta", (c,), decay=False, init=Zero())
+        self.running_mean = self.add_state("running_mean", (c,), 0.0)
+        self.running_var = self.add_state("running_var", (c,), 1.0)
+
+    def forward(self, x, residual=None):
+        shape = x.shape
+        M = x.numel() // self.c
+        self._has_res = residual is not None
+        if not self.on_cuda:
+            xf = x.float().reshape(M, self.c)
+            if self.training:
+                mean, var = xf.mean(0), xf.var(0, unbiased=False)
+                self.running_mean.data.mul_(1 - self.momentum).add_(self.momentum * mean)
+                self.running_var.data.mul_(1 - self.momentum).add_(self.momentum * var * M / max(M - 1, 1))
+            else:
+                mean, var = self.running_mean.data, self.running_var.data
+            self._rstd = torch.rsqrt(var + self.eps)
+            self._xhat = (xf - mean) * self._rstd
+            y = self._xhat * self.gamma.data + self.beta.data
+            if residual is not None:
+                y = y + residual.float().reshape(M, self.c)
+            self._y = torch.relu(y) if self.relu else y
+            return self._y.reshape(shape)
+        xc = x if x.is_contiguous() else x.contiguous()
+        self._x = xc
+        y = torch.empty_like(xc)
+        self._mean = torch.empty(self.c, device=x.device) if self.training else self.running_mean.data
+        self._rstdv = torch.empty(self.c, device=x.device) if self.training else torch.rsqrt(self.running_var.data + self.eps)
+        lib = cuda_lib()
+        split = lib.nb_bn_split(ctypes.c_longlong(M))
+        rc = residual.contiguous() if residual is not None else None
+        check(lib.nb_bn_fwd(ptr(xc), ptr(self.gamma.storage), ptr(self.beta.storage), ptr(rc), ptr(y), ptr(self._mean),
+                            ptr(self._rstdv), ptr(self.running_mean.data), ptr(self.running_var.data),
+                            ptr(_scratch(x.device, 2 * split * self.c)), ctypes.c_longlong(M), ctypes.c_int(self.c),
+                            ctypes.c_float(self.eps), ctypes.c_float(self.momentum), ctypes.c_int(int(self.relu)),
+                            ctypes.c_int(int(self.training)), stream_ptr()), "bn_fwd")
+        self._y = y
+        return y
+
+    def vjp(self, dy):
+        """Returns dx, or (dx, dresidual) when a residual was added in forward."""
+        shape = dy.shape
+        M = dy.numel() // self.c
+        if not self.on_cuda:
+            g = dy.float().reshape(M, self.c)
+            if self.relu:
+                g = g * (self._y > 0)
+            self.gamma.grad.add_((g * self._xhat).sum(0))
+            self.beta.grad.add_(g.sum(0))
+            gg = g * self.gamma.data
+            dx = self._rstd * (gg - gg.mean(0) - self._xhat * (gg * self._xhat).mean(0))
+            dx = dx.reshape(shape)
+            return (dx, g.reshape(shape)) if self._has_res else dx
+        d = dy if (dy.is_contiguous() and dy.dtype == torch.bfloat16) else dy.to(torch.bfloat16).contiguous()
+        dx = torch.empty_like(d)
+        dres = torch.empty_like(d) if self._has_res else None
+        lib = cuda_lib()
+        split = lib.nb_bn_split(ctypes.c_longlong(M))
+        ws = _scratch(dy.device, 2 * split * self.c + 2 * self.c)
+        sums = ws[2 * split * self.c:]
+        check(lib.nb_bn_bwd(ptr(d), ptr(self._x), ptr(self._y if self.relu else None), ptr(self._mean), ptr(self._rstdv),
+                            ptr(self.gamma.storage), ptr(dx), ptr(dres), ptr(self.gamma.grad_storage), ptr(self.beta.grad_storage),
+                            ptr(ws), ptr(sums), ctypes.c_longlong(M), ctypes.c_int(self.c), stream_ptr()), "bn_bwd")
+        return (dx, dres) if self._has_res else dx
+
+
+class MaxPool2D(Module):
+    def __init__(self, k=3, stride=2, pad=1):
+        super().__init__()
+        self.k, self.stride, self.pad = k, stride, pad
+
+    def forward(self, x):
+        B, H, W, C = x.shape
+        OH, OW = (H + 2 * self.pad - self.k) // self.stride + 1, (W + 2 * self.pad - self.k) // self.stride + 1
+        self._dims = (B, H, W, C, OH, OW)
+        if not x.is_cuda:
+            y, idx = torch.nn.functional.max_pool2d(x.float().permute(0, 3, 1, 2), self.k, self.stride, self.pad, return_indices=True)
+            self._idx = idx
+            return y.permute(0, 2, 3, 1)
+        xc = x if x.is_contiguous() else x.contiguous()
+        y = torch.empty(B, OH, OW, C, device=x.device, dtype=torch.bfloat16)
+        self._idx = torch.empty(B, OH, OW, C, device=x.device, dtype=torch.int32)
+        check(cuda_lib().nb_maxpool_fwd(ptr(xc), ptr(y), ptr(self._idx), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, self.stride,
+                                                                                                 self.pad, OH, OW)), stream_ptr()), "maxpool_fwd")
+        return y
+
+    def vjp(self, dy):
+        B, H, W, C, OH, OW = self._dims
+        if not dy.is_cuda:
+            g = torch.nn.functional.max_unpool2d(dy.float().permute(0, 3, 1, 2), self._idx, self.k, self.stride, self.pad, (H, W))
+            return g.permute(0, 2, 3, 1)
+        d = dy if (dy.is_contiguous() and dy.dtype == torch.bfloat16) else dy.to(torch.bfloat16).contiguous()
+        dx = torch.empty(B, H, W, C, device=dy.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_maxpool_bwd(ptr(d), ptr(self._idx), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, self.stride,
+                                                                                                 self.pad, OH, OW)), stream_ptr()), "maxpool_bwd")
+        return dx
+
+
+class BasicBlock(Module):
+    """conv3x3-bn-relu, conv3x3-bn, (+ 1x1 downsample), add, relu — children named as in torchvision."""
+
+    def __init__(self, ic, oc, stride):
+        super().__init__()
+        self.conv1 = self.add_child("conv1", Conv2D(ic, oc, 3, stride, 1, bias=False))
+        self.bn1 = self.add_child("bn1", BatchNorm2D(oc, relu=True))
+        self.conv2 = self.add_child("conv2", Conv2D(oc, oc, 3, 1, 1, bias=False))
+        self.bn2 = self.add_child("bn2", BatchNorm2D(oc, relu=True))
+        self.down = None
+        if stride != 1 or ic != oc:
+            self.down = self.add_child("downsample.0", Conv2D(ic, oc, 1, stride, 0, bias=False))
+            self.down_bn = self.add_child("downsample.1", BatchNorm2D(oc))
+
+    def forward(self, x):
+        idt = self.down_bn.forward(self.down.forward(x)) if self.down is not None else x
+        h = self.bn1.forward(self.conv1.forward(x))
+        return self.bn2.forward(self.conv2.forward(h), residual=idt)
+
+    def vjp(self, dy):
+        dh, dres = self.bn2.vjp(dy)
+        dx = self.conv1.vjp(self.bn1.vjp(self.conv2.vjp(dh)))
+        if self.down is not None:
+            dx = dx + self.down.vjp(self.down_bn.vjp(dres))
+        else:
+            dx = dx + dres
+        return dx
+
+
+class ResNet18Backbone(Module):
+    """Stem (7x7/2, bn, relu, maxpool 3x3/2) + 4 stages of 2 BasicBlocks (64, 128, 256, 512); output stride 32."""
+
+    def __init__(self):
+        super().__init__()
+        self.conv1 = self.add_child("conv1", Conv2D(3, 64, 7, 2, 3, bias=False, need_input_grad=False))
+        self.bn1 = self.add_child("bn1", BatchNorm2D(64, relu=True))
+        self.pool = MaxPool2D(3, 2, 1)
+        self.blocks = []
+        ic = 64
+        for li, (oc, stride) in enumerate(((64, 1), (128, 2), (256, 2), (512, 2)), start=1):
+            for bi in range(2):
+                blk = self.add_child(f"layer{li}.{bi}", BasicBlock(ic, oc, stride if bi == 0 else 1))
+                self.blocks.append(blk)
+                ic = oc
+
+    def forward(self, x):
+        h = self.pool.forward(self.bn1.forward(self.conv1.forward(x)))
+        for b in self.blocks:
+            h = b.forward(h)
+        return h
+
+    def vjp(self, dy):
+        for b in reversed(self.blocks):
+            dy = b.vjp(dy)
+        self.conv1.vjp(self.bn1.vjp(self.pool.vjp(dy)))
+        return None
+
+
+def normalize_images(img_u8, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225)):
+    """uint8 [B, 3, H, W] → NHWC with channels padded to 8 (bf16 on CUDA, fp32 on CPU)."""
+    B, _, H, W = img_u8.shape
+    if img_u8.is_cuda:
+        out = torch.empty(B, H, W, 8, device=img_u8.device, dtype=torch.bfloat16)
+        ic = img_u8 if img_u8.is_contiguous() else img_u8.contiguous()
+        check(cuda_lib().nb_image_normalize(ptr(ic), ptr(out), ctypes.c_int(B), ctypes.c_int(H), ctypes.c_int(W),
+                                            *(ctypes.c_float(v) for v in (*mean, *std)), stream_ptr()), "image_normalize")
+        return out
+    x = (img_u8.float() / 255.0 - torch.tensor(mean).view(1, 3, 1, 1)) / torch.tensor(std).view(1, 3, 1, 1)
+    return torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 5))

@@ -38,6 +38,9 @@ class Param:
         self._shadow: Optional[torch.Tensor] = None
         self.m: Optional[torch.Tensor] = None
         self.v: Optional[torch.Tensor] = None
+        # optional layout hooks: files hold `to_file(data)`; `from_file(tensor)` maps back (e.g. conv weights)
+        self.to_file = None
+        self.from_file = None
 
     # ---- storage (padded) views
     @property
@@ -90,6 +93,13 @@ class Param:
     @property
     def storage_numel(self) -> int:
         return self._val.numel()
+
+    def file_view(self, t: Optional[torch.Tensor] = None) -> torch.Tensor:
+        t = self.data if t is None else t
+        return self.to_file(t) if self.to_file is not None else t
+
+    def load_file_(self, flat: torch.Tensor):
+        self.set_(self.from_file(flat) if self.from_file is not None else flat)
 
     def set_(self, value: torch.Tensor):
         with torch.no_grad():

@@ -204,6 +204,7 @@ class SelfAttention(Module):
         if self.rope_theta:
             rope_(q, self.rope_theta)
             rope_(k, self.rope_theta)
+        self.last_k, self.last_v = k, v      # post-RoPE keys / values (prefix KV cache of a VLA)
         o = self.core.forward(q, k, v, key_valid=key_valid, bias=bias)
         return self.out.forward(o.reshape(B, S, self.h * self.hd))
 
@@ -339,8 +340,8 @@ class TransformerBlock(Module):
         self.n2 = self.add_child("norm2", N(dim, eps))
         self.ffn = self.add_child("ffn", SwiGLUFFN(dim, ff, bias=bias) if ffn == "swiglu" else FeedForward(dim, ff, ffn, bias))
 
-    def forward(self, x, key_valid=None):
-        x = x + self.attn.forward(self.n1.forward(x), key_valid=key_valid)
+    def forward(self, x, key_valid=None, bias=None):
+        x = x + self.attn.forward(self.n1.forward(x), key_valid=key_valid, bias=bias)
         return x + self.ffn.forward(self.n2.forward(x))
 
     def vjp(self, dy):

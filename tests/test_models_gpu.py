@@ -1,0 +1,127 @@
+"""Conv leaves, ACT and VLA on CUDA (our kernels, bf16) against the same modules on CPU (fp32 oracle)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _cmp(a, b, tol, what=""):
+    err = (a.float().cpu() - b.float().cpu()).abs().max().item()
+    ref = b.float().abs().max().item()
+    assert err <= tol * max(1.0, ref), (what, err, ref)
+
+
+def _twin(factory):
+    from noeira_b200 import nn
+    nn.manual_seed(11)
+    a = factory()
+    nn.manual_seed(11)
+    b = factory().to("cuda")
+    return a, b
+
+
+@pytest.mark.parametrize("ic,oc,k,s,p", [(8, 64, 7, 2, 3), (64, 64, 3, 1, 1), (64, 128, 3, 2, 1), (64, 128, 1, 2, 0)])
+def test_conv2d(ic, oc, k, s, p):
+    from noeira_b200 import nn
+    cpu, gpu = _twin(lambda: nn.Conv2D(ic, oc, k, s, p, bias=True, relu=True))
+    x = torch.randn(2, 30, 40, ic) * 0.5
+    yc, yg = cpu.forward(x), gpu.forward(x.cuda().bfloat16())
+    _cmp(yg, yc, 3e-2, "fwd")
+    dy = torch.randn_like(yc) * 0.1
+    dc, dg = cpu.vjp(dy), gpu.vjp(dy.cuda().bfloat16())
+    torch.cuda.synchronize()
+    _cmp(dg, dc, 4e-2, "dx")
+    _cmp(gpu.weight.grad, cpu.weight.grad, 4e-2, "dw")
+    _cmp(gpu.bias.grad, cpu.bias.grad, 4e-2, "db")
+
+
+def test_batchnorm_maxpool_block():
+    from noeira_b200 import nn
+    cpu, gpu = _twin(lambda: nn.BasicBlock(64, 128, 2))
+    x = torch.randn(3, 16, 24, 64)
+    yc, yg = cpu.forward(x), gpu.forward(x.cuda().bfloat16())
+    _cmp(yg, yc, 5e-2, "block fwd")
+    dy = torch.randn_like(yc) * 0.1
+    dc, dg = cpu.vjp(dy), gpu.vjp(dy.cuda().bfloat16())
+    torch.cuda.synchronize()
+    _cmp(dg, dc, 8e-2, "block dx")
+    for (n, pc), (_, pg) in zip(cpu.named_params(), gpu.named_params()):
+        _cmp(pg.grad, pc.grad, 8e-2, n)
+    for (n, sc), (_, sg) in zip(cpu.named_states(), gpu.named_states()):
+        _cmp(sg.data, sc.data, 3e-2, n)
+    pc, pg = nn.MaxPool2D(), nn.MaxPool2D()
+    _cmp(pg.forward(x.cuda().bfloat16()), pc.forward(x.bfloat16().float()), 1e-6, "pool")
+    g = torch.randn(3, 8, 12, 64)
+    _cmp(pg.vjp(g.cuda().bfloat16()), pc.vjp(g.bfloat16().float()), 2e-2, "pool bwd")
+
+
+def test_act_gpu_matches_cpu():
+    from noeira_b200.models.act import ACTConfig, ACTModel
+    from noeira_b200.ops import check_status
+    cfg = ACTConfig(chunk=16, n_cam=2, height=96, width=128, dim=128, heads=2, ff=256, enc_layers=1, dec_layers=2, latent=8,
+                    dropout=0.0)
+    cpu = ACTModel(cfg)
+    gpu = ACTModel(cfg).to("cuda")
+    B = 2
+    g = torch.Generator().manual_seed(0)
+    qpos = torch.randn(B, 6, generator=g)
+    img = torch.randint(0, 255, (B, 2, 3, 96, 128), dtype=torch.uint8, generator=g)
+    act = torch.randn(B, cfg.chunk, 6, generator=g)
+    valid = torch.ones(B, cfg.chunk + 2)
+    valid[1, 10:] = 0
+    eps = torch.randn(B, cfg.latent, generator=g)
+    ac, ic = cpu.forward(qpos, img, act, valid, eps)
+    ag, ig = gpu.forward(qpos.cuda(), img.cuda(), act.cuda(), valid.cuda(), eps.cuda())
+    torch.cuda.synchronize()
+    check_status()
+    _cmp(ag, ac, 8e-2, "ahat")
+    _cmp(ig, ic, 8e-2, "latinfo")
+    dah, dinf = torch.randn_like(ac) * 0.01, torch.randn_like(ic) * 0.01
+    cpu.vjp(dah, dinf)
+    gpu.vjp(dah.cuda(), dinf.cuda())
+    torch.cuda.synchronize()
+    check_status()
+    bad = []
+    for (n, pc), (_, pg) in zip(cpu.named_params(), gpu.named_params()):
+        gc, gg = pc.grad, pg.grad.cpu()
+        cos = torch.nn.functional.cosine_similarity(gc.flatten(), gg.flatten(), dim=0).item()
+        if gc.abs().max() > 1e-6 and cos < 0.95:
+            bad.append((n, round(cos, 3)))
+    assert len(bad) <= 2, bad
+
+
+def test_vla_gpu_matches_cpu():
+    from noeira_b200.models.vla import VLAConfig, VLAModel
+    from noeira_b200.ops import check_status
+    c = VLAConfig(image=64, patch=8, n_cam=2, vit_dim=128, vit_heads=2, vit_ff=256, vit_layers=2, shuffle=2, hidden=256,
+                  heads=4, kv_heads=2, head_dim=64, ff=512, lm_layers=2, vocab=100, n_lang=7, expert_width=192, expert_ff=256,
+                  chunk=10, action_dim=6, action_pad=32)
+    cpu = VLAModel(c)
+    gpu = VLAModel(c).to("cuda")
+    B = 2
+    g = torch.Generator().manual_seed(0)
+    img = torch.rand(B, 2, 3, 64, 64, generator=g)
+    ids = torch.randint(0, 100, (B, 7), generator=g)
+    state = torch.randn(B, 32, generator=g)
+    x_t, t = torch.randn(B, 10, 32, generator=g), torch.rand(B, generator=g)
+    kc = cpu.prefix(img, ids, state)
+    kg = gpu.prefix(img.cuda(), ids.cuda(), state.cuda())
+    _cmp(kg[-1][0], kc[-1][0], 8e-2, "prefix K")
+    vc = cpu.denoise(kc, x_t, t)
+    vg = gpu.denoise(kg, x_t.cuda(), t.cuda())
+    torch.cuda.synchronize()
+    check_status()
+    _cmp(vg, vc, 8e-2, "velocity")
+    dv = torch.randn_like(vc) * 0.01
+    cpu.denoise_vjp(dv)
+    gpu.denoise_vjp(dv.cuda())
+    torch.cuda.synchronize()
+    check_status()
+    bad = []
+    for (n, pc), (_, pg) in zip(cpu.trainable(), gpu.trainable()):
+        gc, gg = pc.grad, pg.grad.cpu()
+        if gc.abs().max() > 1e-7:
+            cos = torch.nn.functional.cosine_similarity(gc.flatten(), gg.flatten(), dim=0).item()
+            if cos < 0.95:
+                bad.append((n, round(cos, 3)))
+    assert len(bad) <= 1, bad
