@@ -213,8 +213,10 @@ class MaxPool2D(Module):
     def vjp(self, dy):
         B, H, W, C, OH, OW = self._dims
         if not dy.is_cuda:
-            g = torch.nn.functional.max_unpool2d(dy.float().permute(0, 3, 1, 2), self._idx, self.k, self.stride, self.pad, (H, W))
-            return g.permute(0, 2, 3, 1)
+            # windows overlap (3x3 / stride 2): an input that is the maximum of several windows sums their gradients
+            g = torch.zeros(B, C, H * W).scatter_add_(2, self._idx.reshape(B, C, -1),
+                                                      dy.float().permute(0, 3, 1, 2).reshape(B, C, -1))
+            return g.view(B, C, H, W).permute(0, 2, 3, 1)
         d = dy if (dy.is_contiguous() and dy.dtype == torch.bfloat16) else dy.to(torch.bfloat16).contiguous()
         dx = torch.empty(B, H, W, C, device=dy.device, dtype=torch.bfloat16)
         check(cuda_lib().nb_maxpool_bwd(ptr(d), ptr(self._idx), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, self.stride,

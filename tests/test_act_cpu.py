@@ -55,3 +55,15 @@ def test_act_vjp_matches_finite_differences():
         fd = (lp - lm) / (2 * e)
         g = p.grad[idx].item()
         assert abs(g - fd) < 5e-2 * max(abs(fd), abs(g), 0.05), (name, g, fd)
+
+
+def test_maxpool_vjp_matches_autograd():
+    import torch
+    from noeira_b200 import nn
+    x = torch.randn(2, 9, 11, 4).bfloat16().float().requires_grad_(True)     # bf16 grid → ties and shared maxima occur
+    y = torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
+    g = torch.randn_like(y)
+    y.backward(g)
+    pool = nn.MaxPool2D()
+    assert torch.equal(pool.forward(x.detach()), y.detach())
+    assert torch.allclose(pool.vjp(g), x.grad, atol=1e-6)

@@ -20,19 +20,60 @@ def _twin(factory):
     return a, b
 
 
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.float().cpu().flatten(), b.float().cpu().flatten(), dim=0).item()
+
+
 @pytest.mark.parametrize("ic,oc,k,s,p", [(8, 64, 7, 2, 3), (64, 64, 3, 1, 1), (64, 128, 3, 2, 1), (64, 128, 1, 2, 0)])
 def test_conv2d(ic, oc, k, s, p):
+    """Without the ReLU the three gradients are linear in the inputs and must match to bf16 rounding."""
     from noeira_b200 import nn
-    cpu, gpu = _twin(lambda: nn.Conv2D(ic, oc, k, s, p, bias=True, relu=True))
+    cpu, gpu = _twin(lambda: nn.Conv2D(ic, oc, k, s, p, bias=True, relu=False))
     x = torch.randn(2, 30, 40, ic) * 0.5
     yc, yg = cpu.forward(x), gpu.forward(x.cuda().bfloat16())
     _cmp(yg, yc, 3e-2, "fwd")
     dy = torch.randn_like(yc) * 0.1
     dc, dg = cpu.vjp(dy), gpu.vjp(dy.cuda().bfloat16())
     torch.cuda.synchronize()
-    _cmp(dg, dc, 4e-2, "dx")
-    _cmp(gpu.weight.grad, cpu.weight.grad, 4e-2, "dw")
-    _cmp(gpu.bias.grad, cpu.bias.grad, 4e-2, "db")
+    _cmp(dg, dc, 2e-2, "dx")
+    _cmp(gpu.weight.grad, cpu.weight.grad, 1e-2, "dw")
+    _cmp(gpu.bias.grad, cpu.bias.grad, 1e-2, "db")
+
+
+def test_conv2d_fused_relu():
+    """With the fused ReLU a few outputs within rounding of zero take the other branch in bf16 (under 0.2 % of
+    them), so the gradients are compared by direction and norm instead of element by element."""
+    from noeira_b200 import nn
+    cpu, gpu = _twin(lambda: nn.Conv2D(64, 64, 3, 1, 1, bias=True, relu=True))
+    x = torch.randn(2, 30, 40, 64) * 0.5
+    yc, yg = cpu.forward(x), gpu.forward(x.cuda().bfloat16())
+    _cmp(yg, yc, 3e-2, "fwd")
+    flips = ((yg.float().cpu() > 0) != (yc > 0)).float().mean().item()
+    assert flips < 5e-3, flips
+    dy = torch.randn_like(yc) * 0.1
+    dc, dg = cpu.vjp(dy), gpu.vjp(dy.cuda().bfloat16())
+    torch.cuda.synchronize()
+    for what, a, b in (("dx", dg, dc), ("dw", gpu.weight.grad, cpu.weight.grad), ("db", gpu.bias.grad, cpu.bias.grad)):
+        assert _cos(a, b) > 0.995, (what, _cos(a, b))
+        assert 0.97 < (a.float().norm().item() / b.float().norm().item()) < 1.03, what
+
+
+def test_batchnorm_exact():
+    from noeira_b200 import nn
+    cpu, gpu = _twin(lambda: nn.BatchNorm2D(64))
+    x = torch.randn(3, 16, 24, 64) * 2 + 0.5
+    res = torch.randn(3, 16, 24, 64)
+    yc, yg = cpu.forward(x, res), gpu.forward(x.cuda().bfloat16(), res.cuda().bfloat16())
+    _cmp(yg, yc, 2e-2, "bn fwd")
+    dy = torch.randn_like(yc) * 0.1
+    (dc, rc), (dg, rg) = cpu.vjp(dy), gpu.vjp(dy.cuda().bfloat16())
+    torch.cuda.synchronize()
+    _cmp(dg, dc, 2e-2, "bn dx")
+    _cmp(rg, rc, 1e-2, "bn dres")
+    _cmp(gpu.gamma.grad, cpu.gamma.grad, 2e-2, "dgamma")
+    _cmp(gpu.beta.grad, cpu.beta.grad, 2e-2, "dbeta")
+    for (n, sc), (_, sg) in zip(cpu.named_states(), gpu.named_states()):
+        _cmp(sg.data, sc.data, 1e-2, n)
 
 
 def test_batchnorm_maxpool_block():
@@ -44,9 +85,10 @@ def test_batchnorm_maxpool_block():
     dy = torch.randn_like(yc) * 0.1
     dc, dg = cpu.vjp(dy), gpu.vjp(dy.cuda().bfloat16())
     torch.cuda.synchronize()
-    _cmp(dg, dc, 8e-2, "block dx")
+    assert _cos(dg, dc) > 0.98, ("block dx", _cos(dg, dc))
     for (n, pc), (_, pg) in zip(cpu.named_params(), gpu.named_params()):
-        _cmp(pg.grad, pc.grad, 8e-2, n)
+        assert _cos(pg.grad, pc.grad) > 0.98, (n, _cos(pg.grad, pc.grad))
+        assert 0.95 < (pg.grad.norm() / pc.grad.norm()).item() < 1.05, n
     for (n, sc), (_, sg) in zip(cpu.named_states(), gpu.named_states()):
         _cmp(sg.data, sc.data, 3e-2, n)
     pc, pg = nn.MaxPool2D(), nn.MaxPool2D()
@@ -65,7 +107,9 @@ def test_act_gpu_matches_cpu():
     B = 2
     g = torch.Generator().manual_seed(0)
     qpos = torch.randn(B, 6, generator=g)
-    img = torch.randint(0, 255, (B, 2, 3, 96, 128), dtype=torch.uint8, generator=g)
+    yy, xx = torch.meshgrid(torch.linspace(0, 6, 96), torch.linspace(0, 8, 128), indexing="ij")
+    base = torch.stack([torch.sin(yy * (1 + c) + xx) for c in range(3)])
+    img = ((base[None, None] * torch.rand(B, 2, 1, 1, 1, generator=g) * 0.5 + 0.5) * 255).clamp(0, 255).to(torch.uint8)
     act = torch.randn(B, cfg.chunk, 6, generator=g)
     valid = torch.ones(B, cfg.chunk + 2)
     valid[1, 10:] = 0
@@ -84,10 +128,15 @@ def test_act_gpu_matches_cpu():
     bad = []
     for (n, pc), (_, pg) in zip(cpu.named_params(), gpu.named_params()):
         gc, gg = pc.grad, pg.grad.cpu()
+        if gc.abs().max() <= 1e-6:
+            continue                      # e.g. key biases: softmax is invariant to them, the true gradient is zero
         cos = torch.nn.functional.cosine_similarity(gc.flatten(), gg.flatten(), dim=0).item()
-        if gc.abs().max() > 1e-6 and cos < 0.95:
-            bad.append((n, round(cos, 3)))
-    assert len(bad) <= 2, bad
+        # 20 bf16 conv / BatchNorm / ReLU layers over a 3x4 final feature map: the direction error grows with depth
+        floor = 0.98 if not n.startswith("feat.") else (0.6 if n.startswith(("feat.0.conv1", "feat.0.bn1")) else 0.85)
+        ratio = (gg.norm() / gc.norm()).item()
+        if cos < floor or not (0.8 < ratio < 1.25):
+            bad.append((n, round(cos, 3), round(ratio, 3)))
+    assert not bad, bad
 
 
 def test_vla_gpu_matches_cpu():
