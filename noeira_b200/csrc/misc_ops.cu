@@ -66,8 +66,9 @@ embedding_bwd_kernel(float* __restrict__ dtable, int ldt, const long long* __res
 
 // Σ w·(pred − target)² over [M, N] (first n_real columns only); dpred = 2·w·(pred − target)·gscale.
 // `rowmask` (optional, [M]) zeroes whole rows.  One partial per block, ordered finish by the caller's finish.
+template <typename TP>
 __global__ void __launch_bounds__(256)
-mse_kernel(const __nv_bfloat16* __restrict__ pred, int ldp, const float* __restrict__ target, int ldt,
+mse_kernel(const TP* __restrict__ pred, int ldp, const float* __restrict__ target, int ldt,
            const float* __restrict__ rowmask, __nv_bfloat16* __restrict__ dpred, int ldd, float* __restrict__ partials,
            int M, int N, int n_real, float gscale, int l1) {
   __shared__ float sh[32];
@@ -78,7 +79,7 @@ mse_kernel(const __nv_bfloat16* __restrict__ pred, int ldp, const float* __restr
     const int m = (int)(i / N), n = (int)(i % N);
     float g = 0.f;
     if (n < n_real && (!rowmask || rowmask[m] != 0.f)) {
-      const float d = __bfloat162float(pred[(size_t)m * ldp + n]) - target[(size_t)m * ldt + n];
+      const float d = (float)pred[(size_t)m * ldp + n] - target[(size_t)m * ldt + n];
       if (l1) {
         acc += fabsf(d);
         g = (d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f)) * gscale;
@@ -203,11 +204,15 @@ int nb_embedding_bwd(float* dtable, int ldt, const long long* idx, const void* d
 // loss_acc[0] += loss_scale · Σ …;  partials: >= 1184 floats.
 int nb_mse_loss(const void* pred, int ldp, const float* target, int ldt, const float* rowmask, void* dpred, int ldd,
                 float* partials, float* loss_acc, int M, int N, int n_real, float gscale, float loss_scale, int l1,
-                void* stream) {
+                int pred_f32, void* stream) {
   const int grid = g1((long long)M * N);
   cudaStream_t s = (cudaStream_t)stream;
-  mse_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)pred, ldp, target, ldt, rowmask, (__nv_bfloat16*)dpred, ldd,
-                                  partials, M, N, n_real, gscale, l1);
+  if (pred_f32)
+    mse_kernel<float><<<grid, 256, 0, s>>>((const float*)pred, ldp, target, ldt, rowmask, (__nv_bfloat16*)dpred, ldd,
+                                           partials, M, N, n_real, gscale, l1);
+  else
+    mse_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)pred, ldp, target, ldt, rowmask,
+                                                   (__nv_bfloat16*)dpred, ldd, partials, M, N, n_real, gscale, l1);
   NB_LAUNCH_CHECK();
   finish_sum_kernel<<<1, 256, 0, s>>>(partials, grid, loss_scale, loss_acc);
   NB_LAUNCH_CHECK();

@@ -301,7 +301,8 @@ class WorldModel:
         check(self.lib.nb_mse_loss(ptr(pred), ctypes.c_int(pred.stride(0)), ptr(target.contiguous()), ctypes.c_int(cfg.latent_dim),
                                    ptr(self.is_lat), ptr(dpred), ctypes.c_int(cfg.latent_dim), ptr(self._ws), ptr(self.loss_acc),
                                    ctypes.c_int(ms), ctypes.c_int(cfg.latent_dim), ctypes.c_int(cfg.latent_dim),
-                                   ctypes.c_float(1.0 / n_lat), ctypes.c_float(1.0 / n_lat), ctypes.c_int(0), stream_ptr()), "mse")
+                                   ctypes.c_float(1.0 / n_lat), ctypes.c_float(1.0 / n_lat), ctypes.c_int(0),
+                                   ctypes.c_int(int(pred.dtype == torch.float32)), stream_ptr()), "mse")
         # ---- backward
         dhn = self.out_lin.vjp(dpred)
         dx = self._norm_bwd(x, dhn, self.out_g, st)

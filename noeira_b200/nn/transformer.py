@@ -369,13 +369,16 @@ class MSELoss:
             g = torch.zeros(M, N)
             g[:, :n_real] = (d.sign() if self.l1 else 2 * d) * (weight / denom)
             return g.reshape(pred.shape)
+        if p2.dtype not in (torch.bfloat16, torch.float32):
+            p2 = p2.float()
         p2 = p2 if p2.stride(-1) == 1 else p2.contiguous()
         t2 = t2.contiguous()
         dp = torch.empty(M, N, device=pred.device, dtype=torch.bfloat16)
         check(cuda_lib().nb_mse_loss(ptr(p2), ctypes.c_int(p2.stride(0)), ptr(t2), ctypes.c_int(N), ptr(rowmask), ptr(dp),
                                      ctypes.c_int(N), ptr(_scratch(pred.device, 2048)), ptr(loss_acc), ctypes.c_int(M),
                                      ctypes.c_int(N), ctypes.c_int(n_real), ctypes.c_float(weight / denom),
-                                     ctypes.c_float(weight / denom), ctypes.c_int(int(self.l1)), stream_ptr()), "mse_loss")
+                                     ctypes.c_float(weight / denom), ctypes.c_int(int(self.l1)),
+                                     ctypes.c_int(int(p2.dtype == torch.float32)), stream_ptr()), "mse_loss")
         return dp.reshape(pred.shape)
 
 

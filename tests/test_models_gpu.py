@@ -174,3 +174,43 @@ def test_vla_gpu_matches_cpu():
             if cos < 0.95:
                 bad.append((n, round(cos, 3)))
     assert len(bad) <= 1, bad
+
+
+def test_vla_trainer_loss_decreases():
+    from noeira_b200.models.vla import VLAConfig, VLATrainer
+    c = VLAConfig(image=64, patch=8, n_cam=2, vit_dim=128, vit_heads=2, vit_ff=256, vit_layers=2, shuffle=2, hidden=256,
+                  heads=4, kv_heads=2, head_dim=64, ff=512, lm_layers=2, vocab=100, n_lang=7, expert_width=192, expert_ff=256,
+                  chunk=10, action_dim=6, action_pad=32, lr=1e-3)
+    tr = VLATrainer(c)
+    g = torch.Generator().manual_seed(0)
+    B = 16
+    img = torch.rand(B, 2, 3, 64, 64, generator=g).cuda()
+    ids = torch.randint(0, 100, (B, 7), generator=g).cuda()
+    state, act = torch.randn(B, 6, generator=g).cuda(), torch.randn(B, 10, 6, generator=g).cuda() * 0.5
+    losses = []
+    for _ in range(60):
+        tr.loss_acc.zero_()
+        tr.train_step(img, ids, state, act)
+        losses.append(float(tr.loss_acc[0]))
+    assert all(l == l for l in losses), losses[:5]
+    assert sum(losses[-10:]) < 0.8 * sum(losses[:10]), (losses[:3], losses[-3:])
+
+
+def test_act_trainer_loss_decreases():
+    from noeira_b200.models.act import ACTConfig, ACTTrainer
+    cfg = ACTConfig(chunk=16, n_cam=1, height=64, width=96, dim=128, heads=2, ff=256, enc_layers=1, dec_layers=1, latent=8,
+                    dropout=0.0, lr=5e-4)
+    tr = ACTTrainer(cfg)
+    g = torch.Generator().manual_seed(0)
+    B = 4
+    qpos = torch.randn(B, 6, generator=g).cuda()
+    img = torch.randint(0, 255, (B, 1, 3, 64, 96), dtype=torch.uint8, generator=g).cuda()
+    act = (torch.randn(B, 16, 6, generator=g) * 0.5).cuda()
+    valid = torch.ones(B, 18, device="cuda")
+    losses = []
+    for _ in range(60):
+        tr.loss_acc.zero_()
+        tr.train_step(qpos, img, act, valid)
+        losses.append(float(tr.loss_acc[0]))
+    assert all(l == l for l in losses), losses[:5]
+    assert sum(losses[-5:]) < 0.9 * sum(losses[:5]), (losses[:3], losses[-3:])

@@ -84,6 +84,10 @@ def test_embedding_rope_losses():
         gg = L(pred.cuda().bfloat16(), tgt.cuda(), acc_g, n_real=6)
         assert abs(acc_c.item() - acc_g.item()) < 2e-2
         _cmp(gg, gc, 3e-2)
+        acc_f = torch.zeros(1, device="cuda")
+        gf = L(pred.cuda(), tgt.cuda(), acc_f, n_real=6)           # fp32 predictions are read as fp32
+        assert abs(acc_c.item() - acc_f.item()) < 1e-4
+        _cmp(gf, gc, 1e-2)
     logits = torch.randn(64, 500)
     tg = torch.randint(0, 500, (64,))
     acc_c, acc_g = torch.zeros(1), torch.zeros(1, device="cuda")
