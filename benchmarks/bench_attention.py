@@ -1,6 +1,6 @@
 """Device-timed flash-attention forward (tcgen05) vs torch SDPA on the same shapes.
 
-    python benchmarks/bench_attention.py [--iters 20]
+    python benchmarks/bench_attention.py [--iters 20] [--only IDX] [--no-sdpa]
 """
 import argparse
 import json
@@ -32,6 +32,8 @@ def timeit(fn, iters, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--only", type=int, default=-1, help="index of the single shape to run (profiling captures)")
+    ap.add_argument("--no-sdpa", action="store_true", help="skip the library comparison")
     args = ap.parse_args()
     from noeira_b200.ops import check_status
     from noeira_b200.ops.attention import flash_attention_backward, flash_attention_forward
@@ -42,6 +44,8 @@ def main():
         (1, 16384, 16, 4, 128, "block_causal", 256),  # world model, 64 frames x 256 tokens
         (8, 602, 8, 8, 64, None, 0),             # ACT encoder memory
     ]
+    if args.only >= 0:
+        shapes = shapes[args.only: args.only + 1]
     for B, S, Hq, Hkv, D, mask, frame in shapes:
         q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
         k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
@@ -62,7 +66,7 @@ def main():
             row.update(bwd_ms=round(tb, 4), bwd_tflops=round(2.5 * fl / tb / 1e9, 1))
         except Exception as e:  # noqa: BLE001
             row["bwd"] = str(e)[:60]
-        if mask in (None, "causal"):
+        if mask in (None, "causal") and not args.no_sdpa:
             qt, kt, vt = (x.permute(0, 2, 1, 3) for x in (q, k, v))
             if Hkv != Hq:
                 kt, vt = kt.repeat_interleave(Hq // Hkv, 1), vt.repeat_interleave(Hq // Hkv, 1)
