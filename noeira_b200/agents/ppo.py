@@ -29,6 +29,7 @@ import torch
 from .. import nn
 from .. import _native
 from .._native import check, cuda_lib, ptr, stream_ptr
+from ..ops.streams import Branch
 
 
 @dataclass
@@ -84,12 +85,14 @@ class PPOTrainer:
         self.mb = self.pool // cfg.n_minibatches
         f = dict(device=self.device, dtype=torch.float32)
         h = dict(device=self.device, dtype=torch.bfloat16)
-        self.obs_buf = torch.zeros(T + 1, N, OP, **h)
-        self.next_obs_buf = torch.zeros(T, N, OP, **h)
+        # [obs_0 .. obs_T | next_obs_0 .. next_obs_{T-1}] in one allocation: the critic evaluates the whole pool
+        # in a single 3-GEMM chain after the rollout instead of 3 small GEMMs per step
+        self.obs_all = torch.zeros(2 * T + 1, N, OP, **h)
+        self.obs_buf = self.obs_all[: T + 1]
+        self.next_obs_buf = self.obs_all[T + 1:]
         self.act_buf = torch.zeros(T, N, AP, **f)
         self.env_action = torch.zeros(N, AP, **f)
         self.logp_buf = torch.zeros(T, N, **f)
-        self.val_buf = torch.zeros(T, N, **f)
         self.rew_buf = torch.zeros(T, N, **f)
         self.done_buf = torch.zeros(T, N, **f)
         self.term_buf = torch.zeros(T, N, **f)
@@ -106,6 +109,9 @@ class PPOTrainer:
         nblk = (self.mb + 255) // 256
         self.partials = torch.zeros(max(nblk * 2, nblk * env.act_dim, nblk * 4) + 16, **f)
         self.partials2 = torch.zeros(nblk * 4 + 16, **f)
+        self.partials_v = torch.zeros(nblk * 4 + 16, **f)
+        self._critic_branch = Branch(torch.cuda.Stream(device=self.device), 1) if self.device.type == "cuda" else None
+        self._cap_stream = torch.cuda.Stream(device=self.device)
         self.adv_stats = torch.zeros(2, **f)
         # device counters: [0] minibatch index, [1] rollout index, [2] rng offset
         self.counters = torch.zeros(4, device=self.device, dtype=torch.int64)
@@ -124,25 +130,27 @@ class PPOTrainer:
         for t in range(cfg.rollout_len):
             obs = self.obs_buf[t]
             mu = self.actor.forward(obs)
-            v = self.critic.forward(obs)
-            check(lib.nb_ppo_sample(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(v),
-                                    ctypes.c_int(v.stride(0)), ptr(self.act_buf[t]), ctypes.c_int(self.AP),
+            check(lib.nb_ppo_sample(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), None,
+                                    ctypes.c_int(0), ptr(self.act_buf[t]), ctypes.c_int(self.AP),
                                     ptr(self.env_action), ctypes.c_int(self.AP), ptr(self.logp_buf[t]),
-                                    ptr(self.val_buf[t]), ctypes.c_int(cfg.n_envs), ctypes.c_int(env.act_dim),
+                                    None, ctypes.c_int(cfg.n_envs), ctypes.c_int(env.act_dim),
                                     ctypes.c_float(cfg.action_scale), ctypes.c_ulonglong(cfg.seed * 7919 + 13),
-                                    ptr(self.counters), ctypes.c_int(0), stream_ptr()), "ppo_sample")
-            check(lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(2), ctypes.c_int(0), stream_ptr()), "counter")
+                                    ptr(self.counters), ctypes.c_int(t), ctypes.c_int(0), stream_ptr()), "ppo_sample")
             env.engine.step(self.env_action, self.rew_buf[t], self.done_buf[t], self.term_buf[t],
                             obs_bf16=self.obs_buf[t + 1], next_obs_bf16=self.next_obs_buf[t], ep_stats=env.ep_stats)
-        self.obs_buf[0].copy_(self.obs_buf[cfg.rollout_len])
+        check(lib.nb_ppo_counter_add(ptr(self.counters), ctypes.c_int(2), ctypes.c_int(cfg.rollout_len), stream_ptr()), "counter")
 
     def _gae(self):
         cfg = self.cfg
-        vnext = self.critic.forward(self.next_obs_buf.view(self.pool, -1))
-        check(self.lib.nb_ppo_gae(ptr(self.rew_buf), ptr(self.done_buf), ptr(self.term_buf), ptr(self.val_buf),
+        T, N = cfg.rollout_len, cfg.n_envs
+        v_all = self.critic.forward(self.obs_all.view((2 * T + 1) * N, -1))      # V(obs_t), V(obs_T), V(next_obs_t)
+        vnext = v_all[(T + 1) * N:]
+        check(self.lib.nb_ppo_gae(ptr(self.rew_buf), ptr(self.done_buf), ptr(self.term_buf), ptr(v_all),
+                                  ctypes.c_int(v_all.stride(0)),
                                   ptr(vnext), ctypes.c_int(vnext.stride(0)), ptr(self.adv_buf), ptr(self.ret_buf),
                                   ctypes.c_int(cfg.rollout_len), ctypes.c_int(cfg.n_envs), ctypes.c_float(cfg.gamma),
                                   ctypes.c_float(cfg.gae_lambda), stream_ptr()), "ppo_gae")
+        self.obs_buf[0].copy_(self.obs_buf[T])
 
     def _opt_step(self, opt):
         if self.grad_sync is not None:
@@ -161,6 +169,14 @@ class PPOTrainer:
                                 ptr(self.partials), ptr(self.adv_stats), ctypes.c_int(self.pool), ctypes.c_int(self.mb),
                                 ctypes.c_int(cfg.n_minibatches), ctypes.c_ulonglong(cfg.seed * 104729 + 7),
                                 ptr(self.counters), stream_ptr()), "ppo_gather")
+        # ---- critic forward / backward on a side stream, overlapping the actor chain
+        br = self._critic_branch
+        with br:
+            v = self.critic.forward(self.mb_obs)
+            check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
+                                        ptr(self.partials_v), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
+                                        ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
+            self.critic.vjp(self.dv[:, :1])
         # ---- actor
         mu = self.actor.forward(self.mb_obs)
         check(lib.nb_ppo_objective(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(self.mb_act),
@@ -171,13 +187,10 @@ class PPOTrainer:
                                    ctypes.c_float(cfg.entropy_coef), ctypes.c_float(1.0 / self.mb), stream_ptr()),
               "ppo_objective")
         self.actor.vjp(self.dmu[:, : env.act_dim])
+        # the optimizer steps (with a gradient sync: two cross-GPU kernels that every rank must run in the same
+        # order) stay on the main stream
         self._opt_step(self.actor_opt)
-        # ---- critic
-        v = self.critic.forward(self.mb_obs)
-        check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
-                                    ptr(self.partials), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
-                                    ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
-        self.critic.vjp(self.dv[:, :1])
+        br.join()
         self._opt_step(self.critic_opt)
         check(lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(0), ctypes.c_int(0), stream_ptr()), "counter")
 
@@ -196,7 +209,7 @@ class PPOTrainer:
         g = self._graphs.get(key)
         if g is None:
             # eager warm-up on a side stream (lazy allocations, kernel attribute set-up), then capture
-            s = torch.cuda.Stream()
+            s = self._cap_stream          # warm-up and capture on ONE stream: workspaces are reused at stable addresses
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
                 fn()
@@ -204,7 +217,7 @@ class PPOTrainer:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = _native.launch_count()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, stream=s):
                 fn()
             self._graph_launches[key] = _native.launch_count() - n0
             _native.add_launches(-self._graph_launches[key])  # the capture pass launches nothing

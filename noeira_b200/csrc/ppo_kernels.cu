@@ -51,10 +51,10 @@ __global__ void ppo_sample_kernel(const float* __restrict__ mu, int ld_mu, const
                                   float* __restrict__ env_action, int ld_a, float* __restrict__ logp,
                                   float* __restrict__ val_out, int n_envs, int act_dim, float action_scale,
                                   unsigned long long seed, const unsigned long long* __restrict__ counters,
-                                  int deterministic) {
+                                  int ctr_offset, int deterministic) {
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= n_envs) return;
-  const unsigned long long ctr = counters[2];
+  const unsigned long long ctr = counters[2] + (unsigned long long)ctr_offset;
   Philox ph(seed);
   float lp = 0.f;
   for (int j0 = 0; j0 < act_dim; j0 += 4) {
@@ -76,18 +76,18 @@ __global__ void ppo_sample_kernel(const float* __restrict__ mu, int ld_mu, const
     }
   }
   logp[e] = lp;
-  val_out[e] = value[(size_t)e * ld_v];
+  if (value) val_out[e] = value[(size_t)e * ld_v];
 }
 
-__global__ void ppo_counters_kernel(unsigned long long* __restrict__ counters, int which, int reset) {
+__global__ void ppo_counters_kernel(unsigned long long* __restrict__ counters, int which, int reset, int inc) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
-    if (reset) counters[which] = 0ull; else counters[which] += 1ull;
+    if (reset) counters[which] = 0ull; else counters[which] += (unsigned long long)inc;
   }
 }
 
 // One thread per env, reverse scan over the T-major rollout.
 __global__ void ppo_gae_kernel(const float* __restrict__ rew, const float* __restrict__ done,
-                               const float* __restrict__ term, const float* __restrict__ val,
+                               const float* __restrict__ term, const float* __restrict__ val, int ld_v,
                                const float* __restrict__ vnext, int ld_vn, float* __restrict__ adv,
                                float* __restrict__ ret, int T, int n_envs, float gamma, float lam) {
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
@@ -98,11 +98,12 @@ __global__ void ppo_gae_kernel(const float* __restrict__ rew, const float* __res
     const float d = done[i];
     float nv;
     if (d != 0.f || t == T - 1) nv = (1.f - term[i]) * vnext[i * ld_vn];
-    else nv = val[i + n_envs];
-    const float delta = rew[i] + gamma * nv - val[i];
+    else nv = val[(i + n_envs) * ld_v];
+    const float v = val[i * ld_v];
+    const float delta = rew[i] + gamma * nv - v;
     gae = delta + gamma * lam * (1.f - d) * gae;
     adv[i] = gae;
-    ret[i] = gae + val[i];
+    ret[i] = gae + v;
   }
 }
 
@@ -279,24 +280,30 @@ extern "C" {
 
 int nb_ppo_sample(const float* mu, int ld_mu, const float* log_std, const float* value, int ld_v, float* sample,
                   int ld_s, float* env_action, int ld_a, float* logp, float* val_out, int n_envs, int act_dim,
-                  float action_scale, unsigned long long seed, const unsigned long long* counters, int deterministic,
-                  void* stream) {
+                  float action_scale, unsigned long long seed, const unsigned long long* counters, int ctr_offset,
+                  int deterministic, void* stream) {
   ppo_sample_kernel<<<ceil_div(n_envs, 128), 128, 0, (cudaStream_t)stream>>>(
       mu, ld_mu, log_std, value, ld_v, sample, ld_s, env_action, ld_a, logp, val_out, n_envs, act_dim, action_scale,
-      seed, counters, deterministic);
+      seed, counters, ctr_offset, deterministic);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_ppo_counter_add(unsigned long long* counters, int which, int inc, void* stream) {
+  ppo_counters_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counters, which, 0, inc);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }
 
 int nb_ppo_counter(unsigned long long* counters, int which, int reset, void* stream) {
-  ppo_counters_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counters, which, reset);
+  ppo_counters_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counters, which, reset, 1);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }
 
-int nb_ppo_gae(const float* rew, const float* done, const float* term, const float* val, const float* vnext,
+int nb_ppo_gae(const float* rew, const float* done, const float* term, const float* val, int ld_v, const float* vnext,
                int ld_vn, float* adv, float* ret, int T, int n_envs, float gamma, float lam, void* stream) {
-  ppo_gae_kernel<<<ceil_div(n_envs, 128), 128, 0, (cudaStream_t)stream>>>(rew, done, term, val, vnext, ld_vn, adv, ret,
+  ppo_gae_kernel<<<ceil_div(n_envs, 128), 128, 0, (cudaStream_t)stream>>>(rew, done, term, val, ld_v, vnext, ld_vn, adv, ret,
                                                                         T, n_envs, gamma, lam);
   NB_LAUNCH_CHECK();
   return NB_OK;

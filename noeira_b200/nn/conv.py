@@ -21,10 +21,12 @@ _WS = {}
 
 
 def _scratch(device, n):
-    t = _WS.get(device)
+    from ..ops.streams import ws_key
+    key = ws_key(device)
+    t = _WS.get(key)
     if t is None or t.numel() < n:
         t = torch.empty(max(n, 1 << 20), dtype=torch.float32, device=device)
-        _WS[device] = t
+        _WS[key] = t
     return t
 
 

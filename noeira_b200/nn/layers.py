@@ -64,10 +64,12 @@ _COLSUM_WS = {}
 
 
 def _colsum_workspace(device, need: int):
-    ws = _COLSUM_WS.get(device)
+    from ..ops.streams import ws_key
+    key = ws_key(device)
+    ws = _COLSUM_WS.get(key)
     if ws is None or ws.numel() < need:
         ws = torch.empty(max(need, 256 * 8192), dtype=torch.float32, device=device)
-        _COLSUM_WS[device] = ws
+        _COLSUM_WS[key] = ws
     return ws
 
 

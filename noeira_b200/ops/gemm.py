@@ -7,12 +7,13 @@ import torch
 
 from .._native import check, cuda_lib, ptr, stream_ptr
 from .status import device_status
+from .streams import ws_key
 
 ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, "gelu": 3, "silu": 4, "sigmoid": 5}
 
 # Split-K workspace: [1024 u32 tile counters | fp32 partial tiles].  One per device, allocated on first use
 # (its address is then stable, so captured CUDA graphs can replay).  GEMMs on ONE stream serialise and may
-# share it; a caller that runs GEMMs concurrently on several streams passes its own via ``workspace=``.
+# share it; code inside an ``ops.streams.Branch`` gets the private workspace of that branch's slot.
 WORKSPACE_BYTES = 4096 + (32 << 20)
 _WS = {}
 
@@ -22,7 +23,7 @@ def new_workspace(device) -> torch.Tensor:
 
 
 def default_workspace(device) -> torch.Tensor:
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    key = ws_key(device)
     w = _WS.get(key)
     if w is None:
         if torch.cuda.is_current_stream_capturing():
