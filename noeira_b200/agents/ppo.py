@@ -112,6 +112,10 @@ class PPOTrainer:
         self.partials_v = torch.zeros(nblk * 4 + 16, **f)
         self._critic_branch = Branch(torch.cuda.Stream(device=self.device), 1) if self.device.type == "cuda" else None
         self._cap_stream = torch.cuda.Stream(device=self.device)
+        self._actor_pg = Branch(torch.cuda.Stream(device=self.device), 2)     # parameter-gradient branches
+        self._critic_pg = Branch(torch.cuda.Stream(device=self.device), 3)
+        self.actor.set_attr("grad_branch", self._actor_pg)
+        self.critic.set_attr("grad_branch", self._critic_pg)
         self.adv_stats = torch.zeros(2, **f)
         # device counters: [0] minibatch index, [1] rollout index, [2] rng offset
         self.counters = torch.zeros(4, device=self.device, dtype=torch.int64)
@@ -177,6 +181,7 @@ class PPOTrainer:
                                         ptr(self.partials_v), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
                                         ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
             self.critic.vjp(self.dv[:, :1])
+            self._critic_pg.join()
         # ---- actor
         mu = self.actor.forward(self.mb_obs)
         check(lib.nb_ppo_objective(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(self.mb_act),
@@ -187,6 +192,7 @@ class PPOTrainer:
                                    ctypes.c_float(cfg.entropy_coef), ctypes.c_float(1.0 / self.mb), stream_ptr()),
               "ppo_objective")
         self.actor.vjp(self.dmu[:, : env.act_dim])
+        self._actor_pg.join()
         # the optimizer steps (with a gradient sync: two cross-GPU kernels that every rank must run in the same
         # order) stay on the main stream
         self._opt_step(self.actor_opt)

@@ -238,6 +238,61 @@ inline int grid1d(long long n) {
 }
 }  // namespace
 
+// Counter-hash dropout: keep(i) = philox(seed; i / 4, step)[i % 4] >= p·2^32.  `step` is read from device memory,
+// so a captured graph draws fresh masks at every replay once the owner advances the counter between steps.
+// Eight elements per thread; the keep bits are stored (one byte per element) for the backward pass.
+__global__ void __launch_bounds__(256)
+dropout_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, unsigned char* __restrict__ keep,
+                   long long n, unsigned long long seed, const unsigned long long* __restrict__ step, float p,
+                   float scale) {
+  const unsigned long long st = step ? step[0] : 0ull;
+  const uint32_t thresh = (uint32_t)fminf(p * 4294967296.0f, 4294967295.0f);
+  Philox ph(seed);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g * 8 < n; g += stride) {
+    uint32_t ra[4], rb[4];
+    ph((uint32_t)(2 * g), (uint32_t)((2 * g) >> 32), (uint32_t)st, (uint32_t)(st >> 32), ra);
+    ph((uint32_t)(2 * g + 1), (uint32_t)((2 * g + 1) >> 32), (uint32_t)st, (uint32_t)(st >> 32), rb);
+    const long long i0 = g * 8;
+    if (i0 + 8 <= n) {
+      const uint4 in = *reinterpret_cast<const uint4*>(x + i0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
+      uint4 out;
+      __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+      unsigned long long kb = 0ull;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t r0 = j < 2 ? ra[2 * j] : rb[2 * j - 4], r1 = j < 2 ? ra[2 * j + 1] : rb[2 * j - 3];
+        const bool k0 = r0 >= thresh, k1 = r1 >= thresh;
+        o[j] = __floats2bfloat162_rn(k0 ? __low2float(h[j]) * scale : 0.f, k1 ? __high2float(h[j]) * scale : 0.f);
+        kb |= (unsigned long long)(k0 ? 1u : 0u) << (16 * j);
+        kb |= (unsigned long long)(k1 ? 1u : 0u) << (16 * j + 8);
+      }
+      *reinterpret_cast<uint4*>(y + i0) = out;
+      *reinterpret_cast<unsigned long long*>(keep + i0) = kb;
+    } else {
+      for (int j = 0; j < 8 && i0 + j < n; ++j) {
+        const uint32_t r = j < 4 ? ra[j] : rb[j - 4];
+        const bool k = r >= thresh;
+        y[i0 + j] = __float2bfloat16(k ? __bfloat162float(x[i0 + j]) * scale : 0.f);
+        keep[i0 + j] = k ? 1 : 0;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+dropout_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const unsigned char* __restrict__ keep,
+                   __nv_bfloat16* __restrict__ dx, long long n, float scale) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    dx[i] = __float2bfloat16(keep[i] ? __bfloat162float(dy[i]) * scale : 0.f);
+}
+
+__global__ void u64_add_kernel(unsigned long long* c, unsigned long long inc) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) c[0] += inc;
+}
+
 extern "C" {
 
 // Split factor used for a column sum over M rows (the caller sizes `partials` as split·N floats).
@@ -320,4 +375,35 @@ int nb_cast_rows(const float* s, int lds, void* d, int ldd, int M, int N, void* 
   return NB_OK;
 }
 
+
+// y = dropout(x) with keep probability 1 − p and scale 1 / (1 − p); x, y 16-byte aligned when n >= 8.
+int nb_dropout_fwd(const void* x, void* y, unsigned char* keep, long long n, unsigned long long seed,
+                   const unsigned long long* step, float p, void* stream) {
+  if (n <= 0) return NB_OK;
+  if (p < 0.f || p >= 1.f) return NB_ERR_BAD_ARG;
+  if ((((uintptr_t)x | (uintptr_t)y) & 15) || ((uintptr_t)keep & 7)) return NB_ERR_UNALIGNED;
+  const long long groups = (n + 7) / 8;
+  long long blocks = (groups + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dropout_fwd_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, keep, n,
+                                                                   seed, step, p, 1.f / (1.f - p));
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_dropout_bwd(const void* dy, const unsigned char* keep, void* dx, long long n, float p, void* stream) {
+  if (n <= 0) return NB_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dropout_bwd_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, keep, (__nv_bfloat16*)dx, n,
+                                                                   1.f / (1.f - p));
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_u64_add(unsigned long long* counter, unsigned long long inc, void* stream) {
+  u64_add_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counter, inc);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
 }  // extern "C"

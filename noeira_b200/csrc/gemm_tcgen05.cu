@@ -55,17 +55,34 @@ __device__ __forceinline__ float tanh_fast(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float act_apply(int act, float v) {
+// The activation code is selected ONCE per 16-column chunk and the taken case is a short straight run: the
+// epilogue executes few instructions per tile, so its speed is set by instruction fetch, i.e. by code size.
+__device__ __forceinline__ void act_apply16(int act, float (&v)[16]) {
   switch (act) {
-    case NB_ACT_RELU: return fmaxf(v, 0.f);
-    case NB_ACT_TANH: return tanh_fast(v);
-    case NB_ACT_GELU: {
-      const float c = 0.7978845608028654f;
-      return 0.5f * v * (1.f + tanh_fast(c * (v + 0.044715f * v * v * v)));
-    }
-    case NB_ACT_SILU: return v / (1.f + __expf(-v));
-    case NB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
-    default: return v;
+    case NB_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+      break;
+    case NB_ACT_TANH:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = tanh_fast(v[j]);
+      break;
+    case NB_ACT_GELU:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float x = v[j];
+        v[j] = 0.5f * x * (1.f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+      }
+      break;
+    case NB_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.f + __expf(-v[j]));
+      break;
+    case NB_ACT_SIGMOID:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = 1.f / (1.f + __expf(-v[j]));
+      break;
+    default: break;
   }
 }
 // derivative factor from the SAVED tensor: tanh/relu/sigmoid save the output y, gelu/silu save the input x
@@ -87,39 +104,91 @@ __device__ __forceinline__ float dact_apply(int dact, float s) {
     default: return 1.f;
   }
 }
+__device__ __forceinline__ void dact_apply16(int dact, float (&v)[16], const float (&sv)[16]) {
+  switch (dact) {
+    case NB_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = sv[j] > 0.f ? v[j] : 0.f;
+      break;
+    case NB_ACT_TANH:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] *= 1.f - sv[j] * sv[j];
+      break;
+    case NB_ACT_SIGMOID:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] *= sv[j] * (1.f - sv[j]);
+      break;
+    case NB_ACT_GELU:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] *= dact_apply(NB_ACT_GELU, sv[j]);
+      break;
+    case NB_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] *= dact_apply(NB_ACT_SILU, sv[j]);
+      break;
+    default: break;
+  }
+}
 
-// Epilogue for 16 consecutive columns of one output row: alpha, bias, activation / derivative, store.
-__device__ __forceinline__ void epilogue_store16(const GemmParams& p, int row, int col0, float (&v)[16]) {
+// Epilogue for 16 consecutive columns of one output row, in two phases so that the global loads it needs (the saved
+// activation for a fused derivative, the old output when accumulating) can be issued one chunk ahead of their use:
+// a chunk costs a DRAM / L2 round trip otherwise, which made narrow-K GEMMs epilogue-bound.
+struct EpiPrefetch {
+  uint4 aux[2];   // 16 bf16 of the saved tensor
+  float4 old[4];  // 16 fp32 of the previous output (accumulate)
+};
+
+__device__ __forceinline__ void epilogue_prefetch16(const GemmParams& p, int row, int col0, bool active, EpiPrefetch& pf) {
+  if (!active || col0 + 16 > p.N) return;
+  if (p.dact && (p.ld_aux % 8 == 0)) {
+    const __nv_bfloat16* ax = p.aux + (size_t)row * p.ld_aux + col0;
+    pf.aux[0] = __ldg(reinterpret_cast<const uint4*>(ax));
+    pf.aux[1] = __ldg(reinterpret_cast<const uint4*>(ax + 8));
+  }
+  if (p.out_f32 && p.accumulate && (p.ldd % 4 == 0)) {
+    const float* o = reinterpret_cast<const float*>(p.D) + (size_t)row * p.ldd + col0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pf.old[j] = *reinterpret_cast<const float4*>(o + 4 * j);
+  }
+}
+
+__device__ __forceinline__ void epilogue_store16(const GemmParams& p, int row, int col0, float (&v)[16],
+                                                 const EpiPrefetch& pf) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
   const bool full = (col0 + 16 <= p.N);
   if (p.bias) {
+    if (full && (col0 % 4 == 0)) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      if (full || col0 + j < p.N) v[j] += p.bias[col0 + j];
-  }
-  if (p.act) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = act_apply(p.act, v[j]);
-  }
-  if (p.dact) {
-    const __nv_bfloat16* ax = p.aux + (size_t)row * p.ld_aux + col0;
-    if (full && (p.ld_aux % 8 == 0)) {
-      const uint4 a0 = *reinterpret_cast<const uint4*>(ax), a1 = *reinterpret_cast<const uint4*>(ax + 8);
-      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&a0);
-      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&a1);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[2 * j] *= dact_apply(p.dact, __low2float(h0[j]));
-        v[2 * j + 1] *= dact_apply(p.dact, __high2float(h0[j]));
-        v[8 + 2 * j] *= dact_apply(p.dact, __low2float(h1[j]));
-        v[8 + 2 * j + 1] *= dact_apply(p.dact, __high2float(h1[j]));
+      for (int j = 0; j < 16; j += 4) {
+        const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + j));
+        v[j] += bv.x; v[j + 1] += bv.y; v[j + 2] += bv.z; v[j + 3] += bv.w;
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (full || col0 + j < p.N) v[j] *= dact_apply(p.dact, __bfloat162float(ax[j]));
+        if (col0 + j < p.N) v[j] += p.bias[col0 + j];
     }
+  }
+  if (p.act) act_apply16(p.act, v);
+  if (p.dact) {
+    float sv[16];
+    if (full && (p.ld_aux % 8 == 0)) {
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&pf.aux[0]);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&pf.aux[1]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sv[2 * j] = __low2float(h0[j]);
+        sv[2 * j + 1] = __high2float(h0[j]);
+        sv[8 + 2 * j] = __low2float(h1[j]);
+        sv[8 + 2 * j + 1] = __high2float(h1[j]);
+      }
+    } else {
+      const __nv_bfloat16* ax = p.aux + (size_t)row * p.ld_aux + col0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) sv[j] = (col0 + j < p.N) ? __bfloat162float(ax[j]) : 0.f;
+    }
+    dact_apply16(p.dact, v, sv);
   }
   if (p.out_f32) {
     float* o = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
@@ -128,7 +197,7 @@ __device__ __forceinline__ void epilogue_store16(const GemmParams& p, int row, i
       for (int j = 0; j < 16; j += 4) {
         float4 x = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         if (p.accumulate) {
-          const float4 y = *reinterpret_cast<float4*>(o + j);
+          const float4 y = pf.old[j >> 2];
           x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
         }
         *reinterpret_cast<float4*>(o + j) = x;
@@ -305,17 +374,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool row_ok = row < p.M;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       if (p.splits == 1) {
+        // rolled on purpose (one copy of the chunk body in the instruction cache); the chunk's global loads
+        // (saved activation, old output) are issued one chunk ahead of their use
+        EpiPrefetch pf;
+        epilogue_prefetch16(p, row, nb_ * BN, row_ok, pf);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16];
           tmem_ld_32x32b_x16(taddr0 + (uint32_t)c0, r);
+          const EpiPrefetch cur = pf;
+          if (c0 + 16 < BN) epilogue_prefetch16(p, row, nb_ * BN + c0 + 16, row_ok, pf);
           tmem_ld_wait();
           const int col0 = nb_ * BN + c0;
           if (row_ok && col0 < p.N) {
             float v[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-            epilogue_store16(p, row, col0, v);
+            epilogue_store16(p, row, col0, v, cur);
           }
         }
         tc_fence_before();
@@ -345,24 +420,57 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*ticket_slot == (unsigned int)(p.splits - 1)) {
           __threadfence();
-          const float* base = p.ws + (size_t)tile * p.splits * (BM * BN) + (size_t)row_in_tile * BN;
+          // pass 1, coalesced: the tile is a flat array of float4; thread t owns elements t, t+128, ... and sums
+          // the splits in index order (16 independent loads in flight per thread per split), leaving the total in
+          // split 0's slot.  pass 2: the usual row-wise epilogue reads that one slot.
+          float* tile_ws = p.ws + (size_t)tile * p.splits * (BM * BN);
+          const int tid = (int)threadIdx.x - 64;
+          constexpr int F4 = BM * BN / 4, PER = F4 / 128, GROUP = PER < 8 ? PER : 8;
+#pragma unroll 1
+          for (int g0 = 0; g0 < PER; g0 += GROUP) {
+            const float4* src0 = reinterpret_cast<const float4*>(tile_ws) + g0 * 128 + tid;
+            float4 accv[GROUP], x[GROUP];
+#pragma unroll
+            for (int k = 0; k < GROUP; ++k) {
+              accv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+              x[k] = __ldcg(src0 + k * 128);
+            }
+            // split sp+1 is in flight while split sp is added (additions stay in index order)
+#pragma unroll 1
+            for (int sp = 1; sp < p.splits; ++sp) {
+              const float4* src = src0 + (size_t)sp * (BM * BN / 4);
+              float4 y[GROUP];
+#pragma unroll
+              for (int k = 0; k < GROUP; ++k) y[k] = __ldcg(src + k * 128);
+#pragma unroll
+              for (int k = 0; k < GROUP; ++k) {
+                accv[k].x += x[k].x; accv[k].y += x[k].y; accv[k].z += x[k].z; accv[k].w += x[k].w;
+                x[k] = y[k];
+              }
+            }
+            float4* dst = reinterpret_cast<float4*>(tile_ws) + g0 * 128 + tid;
+#pragma unroll
+            for (int k = 0; k < GROUP; ++k) {
+              accv[k].x += x[k].x; accv[k].y += x[k].y; accv[k].z += x[k].z; accv[k].w += x[k].w;
+              __stcg(dst + k * 128, accv[k]);
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const float* base = tile_ws + (size_t)row_in_tile * BN;
+          EpiPrefetch pf;
+          epilogue_prefetch16(p, row, nb_ * BN, row_ok, pf);
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) {
             const int col0 = nb_ * BN + c0;
-            if (row_ok && col0 < p.N) {
-              float v[16];
+            float v[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = 0.f;
-              for (int sp = 0; sp < p.splits; ++sp) {
-                const float* src = base + (size_t)sp * (BM * BN) + c0;
-#pragma unroll
-                for (int j = 0; j < 16; j += 4) {
-                  const float4 x = __ldcg(reinterpret_cast<const float4*>(src + j));
-                  v[j] += x.x; v[j + 1] += x.y; v[j + 2] += x.z; v[j + 3] += x.w;
-                }
-              }
-              epilogue_store16(p, row, col0, v);
+            for (int j = 0; j < 16; j += 4) {
+              const float4 x = __ldcg(reinterpret_cast<const float4*>(base + c0 + j));
+              v[j] = x.x; v[j + 1] = x.y; v[j + 2] = x.z; v[j + 3] = x.w;
             }
+            const EpiPrefetch cur = pf;
+            if (c0 + 16 < BN) epilogue_prefetch16(p, row, col0 + 16, row_ok, pf);
+            if (row_ok && col0 < p.N) epilogue_store16(p, row, col0, v, cur);
           }
           if (warp == 2 && lane == 0) p.tile_ctr[tile] = 0u;
         }
@@ -443,6 +551,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long l
   if (p.ws && p.tile_ctr && tiles * 2 <= sm_count() && p.num_kb >= 8 && tiles <= ws_tiles_cap) {
     splits = sm_count() / tiles;
     if (splits > p.num_kb / 4) splits = p.num_kb / 4;
+    if (splits > 24) splits = 24;  // the last CTA of a tile sums the splits one after the other
     const long long cap = ws_bytes / ((long long)tiles * BM * BN * 4);
     if (splits > cap) splits = (int)cap;
     if (splits < 1) splits = 1;

@@ -93,7 +93,7 @@ class _FFN(Module):
     def __init__(self, dim, ff, p):
         super().__init__()
         self.l1 = self.add_child("f1", nn.Linear(dim, ff, act="relu"))
-        self.drop = nn.Dropout(p)
+        self.drop = self.add_child("drop", nn.Dropout(p))
         self.l2 = self.add_child("f2", nn.Linear(ff, dim))
 
     def forward(self, x):
@@ -112,7 +112,7 @@ class DETREncoderLayer(Module):
         self.n1 = self.add_child("n1", nn.LayerNorm(dim))
         self.ffn = self.add_child("ffn", _FFN(dim, ff, p))
         self.n2 = self.add_child("out", nn.LayerNorm(dim))
-        self.d1, self.d2 = nn.Dropout(p), nn.Dropout(p)
+        self.d1, self.d2 = self.add_child("d1", nn.Dropout(p)), self.add_child("d2", nn.Dropout(p))
 
     def forward(self, x, pos, key_valid=None):
         xp = x + pos
@@ -137,7 +137,7 @@ class DETRDecoderLayer(Module):
         self.n2 = self.add_child("n2", nn.LayerNorm(dim))
         self.ffn = self.add_child("ffn", _FFN(dim, ff, p))
         self.n3 = self.add_child("out", nn.LayerNorm(dim))
-        self.d1, self.d2, self.d3 = nn.Dropout(p), nn.Dropout(p), nn.Dropout(p)
+        self.d1, self.d2, self.d3 = (self.add_child(f"d{i}", nn.Dropout(p)) for i in (1, 2, 3))
 
     def forward(self, x, qpos, kmem, mem):
         xq = x + qpos

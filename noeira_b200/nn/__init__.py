@@ -3,7 +3,7 @@ from .combinators import (Checkpointed, Parallel, ProjectedResidual, Repeat, Rep
                           Sequential, SkipConcat, StochasticActor, StopGradParams, Tokenwise)
 from .init import (Constant, Deterministic, Kaiming, Normal, Orthogonal, ScaledKaiming, TruncNormalIn, Xavier,  # noqa: F401
                    Zero)
-from .layers import (BiasAdd, Dropout, Elementwise, GaussianHead, Linear, LinearGELU, LinearReLU, LinearTanh,  # noqa: F401
+from .layers import (BiasAdd, Dropout, advance_rng, rng_step_counter, Elementwise, GaussianHead, Linear, LinearGELU, LinearReLU, LinearTanh,  # noqa: F401
                      Scale)
 from .module import Module, as_autograd, manual_seed  # noqa: F401
 from .optim import SGD, Adam, AdamW, LaProp, ScalarAdam, polyak  # noqa: F401

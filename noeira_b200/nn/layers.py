@@ -171,9 +171,15 @@ class Linear(Module):
         n = self.out_dim
         dyv = dy2[:, :n]
         if not self.weight.frozen:
-            ops.gemm(self._x[:, : self.in_dim], dyv, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=n)
-            if self.bias is not None:
-                colsum_into(dy2, self.bias.grad_storage, n)
+            br = self.attrs.get("grad_branch")
+            if br is not None:
+                # parameter gradients leave the critical path: they run on the branch's stream while the data
+                # gradient continues here; the owner joins the branch before its optimizer step
+                with br:
+                    self._param_grads(dy2, dyv, n)
+                br.keep(dy2, self._x)
+            else:
+                self._param_grads(dy2, dyv, n)
         if not self.need_input_grad:
             return None
         W = self.weight.shadow
@@ -187,6 +193,11 @@ class Linear(Module):
         ops.gemm(dyv, W[:, :n], out=dx, aux=aux, dact=dact, n=self.in_dim)
         dx = dx[:, : self.in_dim] if in_pad != self.in_dim else dx
         return dx.reshape(*self._lead, self.in_dim) if len(self._lead) != 1 else dx
+
+    def _param_grads(self, dy2, dyv, n):
+        ops.gemm(self._x[:, : self.in_dim], dyv, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=n)
+        if self.bias is not None:
+            colsum_into(dy2, self.bias.grad_storage, n)
 
     def _release(self):
         self._x = self._saved = None
@@ -298,22 +309,61 @@ class Scale(Module):
         return dy * self.multiplier
 
 
+_RNG_STEP = {}
+_DROPOUT_IDS = [0]
+
+
+def rng_step_counter(device) -> torch.Tensor:
+    """Device-resident step counter (uint64 in an int64 tensor) that every counter-hash random op reads."""
+    key = torch.device(device).index or 0
+    t = _RNG_STEP.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int64, device=device)
+        _RNG_STEP[key] = t
+    return t
+
+
+def advance_rng(device, inc: int = 1):
+    """counter += inc, as a kernel on the current stream: call once per training step (inside a captured step)."""
+    if torch.device(device).type != "cuda":
+        return
+    check(cuda_lib().nb_u64_add(ptr(rng_step_counter(device)), ctypes.c_ulonglong(inc), stream_ptr()), "u64_add")
+
+
 class Dropout(Module):
-    """Counter-hash dropout: the mask is a pure function of (seed, step counter, element index), so a
-    captured graph replays fresh masks (noeira/nn/random/hash_mask.mojo)."""
+    """Counter-hash dropout: the mask is a pure function of (module seed, step counter, element index), so a
+    captured graph replays fresh masks (noeira/nn/random/hash_mask.mojo).  On CUDA the counter lives on the
+    device (``advance_rng``); on CPU a host counter seeds a generator."""
 
     def __init__(self, p: float = 0.1, seed: int = 0):
         super().__init__()
-        self.p, self.seed, self.counter = p, seed, 0
+        _DROPOUT_IDS[0] += 1
+        self.p, self.seed, self.counter = p, seed * 1000003 + _DROPOUT_IDS[0] * 7919, 0
 
     def forward(self, x):
         if not self.training or self.p == 0.0:
             self._mask = None
             return x
-        g = torch.Generator(device=x.device).manual_seed(self.seed * 1000003 + self.counter)
+        if x.is_cuda:
+            xc = x if (x.is_contiguous() and x.dtype == torch.bfloat16) else x.to(torch.bfloat16).contiguous()
+            y = torch.empty_like(xc)
+            self._mask = torch.empty(xc.numel() + 8, dtype=torch.uint8, device=x.device)
+            check(cuda_lib().nb_dropout_fwd(ptr(xc), ptr(y), ptr(self._mask), ctypes.c_longlong(xc.numel()),
+                                            ctypes.c_ulonglong(self.seed), ptr(rng_step_counter(x.device)),
+                                            ctypes.c_float(self.p), stream_ptr()), "dropout_fwd")
+            return y
+        g = torch.Generator(device=x.device).manual_seed(self.seed + self.counter)
         self.counter += 1
         self._mask = (torch.rand(x.shape, device=x.device, generator=g) >= self.p).to(x.dtype) / (1.0 - self.p)
         return x * self._mask
 
     def vjp(self, dy):
-        return dy if self._mask is None else dy * self._mask
+        if self._mask is None:
+            return dy
+        if dy.is_cuda:
+            d = dy if (dy.is_contiguous() and dy.dtype == torch.bfloat16) else dy.to(torch.bfloat16).contiguous()
+            dx = torch.empty_like(d)
+            check(cuda_lib().nb_dropout_bwd(ptr(d), ptr(self._mask), ptr(dx), ctypes.c_longlong(d.numel()),
+                                            ctypes.c_float(self.p), stream_ptr()), "dropout_bwd")
+            return dx
+        return dy * self._mask

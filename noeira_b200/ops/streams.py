@@ -33,6 +33,7 @@ class Branch:
         assert slot_id > 0
         self.stream, self.slot_id = stream, slot_id
         self._ctx = None
+        self._keep = []
 
     def __enter__(self):
         self.stream.wait_stream(torch.cuda.current_stream())
@@ -47,5 +48,11 @@ class Branch:
         _TLS.slot = self._old
         return False
 
+    def keep(self, *tensors):
+        """Hold references to tensors the branch reads that were allocated on another stream, until the join
+        (the caching allocator would otherwise be free to hand their memory out again while the branch runs)."""
+        self._keep.extend(tensors)
+
     def join(self):
         torch.cuda.current_stream().wait_stream(self.stream)
+        self._keep.clear()
