@@ -397,7 +397,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       } else {
-        // split-K: park the fp32 partial tile, the last split to arrive reduces all of them in index order
+        // split-K: park the fp32 partial tile; splitk_reduce_kernel sums the splits in index order afterwards
         float* wtile = p.ws + (size_t)item * (BM * BN) + (size_t)row_in_tile * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -411,70 +411,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const unsigned int t = atomicAdd(p.tile_ctr + tile, 1u);
-          *ticket_slot = t;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*ticket_slot == (unsigned int)(p.splits - 1)) {
-          __threadfence();
-          // pass 1, coalesced: the tile is a flat array of float4; thread t owns elements t, t+128, ... and sums
-          // the splits in index order (16 independent loads in flight per thread per split), leaving the total in
-          // split 0's slot.  pass 2: the usual row-wise epilogue reads that one slot.
-          float* tile_ws = p.ws + (size_t)tile * p.splits * (BM * BN);
-          const int tid = (int)threadIdx.x - 64;
-          constexpr int F4 = BM * BN / 4, PER = F4 / 128, GROUP = PER < 8 ? PER : 8;
-#pragma unroll 1
-          for (int g0 = 0; g0 < PER; g0 += GROUP) {
-            const float4* src0 = reinterpret_cast<const float4*>(tile_ws) + g0 * 128 + tid;
-            float4 accv[GROUP], x[GROUP];
-#pragma unroll
-            for (int k = 0; k < GROUP; ++k) {
-              accv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-              x[k] = __ldcg(src0 + k * 128);
-            }
-            // split sp+1 is in flight while split sp is added (additions stay in index order)
-#pragma unroll 1
-            for (int sp = 1; sp < p.splits; ++sp) {
-              const float4* src = src0 + (size_t)sp * (BM * BN / 4);
-              float4 y[GROUP];
-#pragma unroll
-              for (int k = 0; k < GROUP; ++k) y[k] = __ldcg(src + k * 128);
-#pragma unroll
-              for (int k = 0; k < GROUP; ++k) {
-                accv[k].x += x[k].x; accv[k].y += x[k].y; accv[k].z += x[k].z; accv[k].w += x[k].w;
-                x[k] = y[k];
-              }
-            }
-            float4* dst = reinterpret_cast<float4*>(tile_ws) + g0 * 128 + tid;
-#pragma unroll
-            for (int k = 0; k < GROUP; ++k) {
-              accv[k].x += x[k].x; accv[k].y += x[k].y; accv[k].z += x[k].z; accv[k].w += x[k].w;
-              __stcg(dst + k * 128, accv[k]);
-            }
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          const float* base = tile_ws + (size_t)row_in_tile * BN;
-          EpiPrefetch pf;
-          epilogue_prefetch16(p, row, nb_ * BN, row_ok, pf);
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            const int col0 = nb_ * BN + c0;
-            float v[16];
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              const float4 x = __ldcg(reinterpret_cast<const float4*>(base + c0 + j));
-              v[j] = x.x; v[j + 1] = x.y; v[j + 2] = x.z; v[j + 3] = x.w;
-            }
-            const EpiPrefetch cur = pf;
-            if (c0 + 16 < BN) epilogue_prefetch16(p, row, col0 + 16, row_ok, pf);
-            if (row_ok && col0 < p.N) epilogue_store16(p, row, col0, v, cur);
-          }
-          if (warp == 2 && lane == 0) p.tile_ctr[tile] = 0u;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
@@ -487,6 +423,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// Second phase of a split-K GEMM: one thread per (row, 16-column chunk) of the output sums that chunk over the
+// splits in index order (deterministic) and runs the epilogue.  A separate launch, not a "last CTA reduces" tail:
+// the serial tail cost 20 us for 18 splits, and a tail that waits for sibling CTAs could deadlock against a
+// second split-K kernel running on another stream.
+__global__ void __launch_bounds__(128)
+splitk_reduce_kernel(const GemmParams p, int BN) {
+  const int chunks = BN / 16;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)p.tiles_m * p.tiles_n * BM * chunks;
+  if (idx >= total) return;
+  const int c = (int)(idx % chunks);
+  const int row_in_tile = (int)((idx / chunks) % BM);
+  const int tile = (int)(idx / ((long long)chunks * BM));
+  int mb, nb_;
+  tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
+  const int row = mb * BM + row_in_tile, col0 = nb_ * BN + c * 16;
+  if (row >= p.M || col0 >= p.N) return;
+  EpiPrefetch pf;
+  epilogue_prefetch16(p, row, col0, true, pf);
+  const size_t tile_elems = (size_t)BM * BN;
+  const float* src = p.ws + (size_t)tile * p.splits * tile_elems + (size_t)row_in_tile * BN + c * 16;
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = 0.f;
+  int sp = 0;
+  for (; sp + 8 <= p.splits; sp += 8) {
+    float4 x[8][4];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + u) * tile_elems) + j);
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+      }
+  }
+  for (; sp < p.splits; ++sp) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * tile_elems) + j);
+      v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+    }
+  }
+  epilogue_store16(p, row, col0, v, pf);
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -551,7 +535,6 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long l
   if (p.ws && p.tile_ctr && tiles * 2 <= sm_count() && p.num_kb >= 8 && tiles <= ws_tiles_cap) {
     splits = sm_count() / tiles;
     if (splits > p.num_kb / 4) splits = p.num_kb / 4;
-    if (splits > 24) splits = 24;  // the last CTA of a tile sums the splits one after the other
     const long long cap = ws_bytes / ((long long)tiles * BM * BN * 4);
     if (splits > cap) splits = (int)cap;
     if (splits < 1) splits = 1;
@@ -562,6 +545,11 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long l
   const int grid = items < sm_count() ? items : sm_count();
   gemm_bf16_kernel<BN, STAGES><<<grid, NUM_THREADS, smem, stream>>>(tmA, tmB, p);
   NB_LAUNCH_CHECK();
+  if (p.splits > 1) {
+    const long long threads = (long long)tiles * BM * (BN / 16);
+    splitk_reduce_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>(p, BN);
+    NB_LAUNCH_CHECK();
+  }
   return NB_OK;
 }
 
