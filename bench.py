@@ -94,6 +94,7 @@ def main():
     ap.add_argument("--workload", default="ppo")
     ap.add_argument("--envs", type=int, default=4096)
     ap.add_argument("--sync", default="fused", help="fused | nccl  (gradient reduction path for N>1)")
+    ap.add_argument("--eager", action="store_true", help="secondary workloads: launch kernels one by one instead of replaying a graph")
     ap.add_argument("--small", action="store_true", help="reduced model for smoke runs of secondary workloads")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -119,7 +119,7 @@ def run_dp(args, rank, local_rank, world):
                     act=torch.randn(B, cfg.chunk, 6, generator=g).pin_memory())
         dev = {k: v.cuda() for k, v in host.items()}
         valid = torch.ones(B, cfg.chunk + 2, device="cuda")
-        step_fn = lambda: tr.train_step(dev["qpos"], dev["img"], dev["act"], valid)
+        step_fn = lambda: (tr.train_step if args.eager else tr.step)(dev["qpos"], dev["img"], dev["act"], valid)
         model_desc = f"ACT ResNet-18 + DETR enc {cfg.enc_layers}/dec {cfg.dec_layers}, d {cfg.dim}, chunk {cfg.chunk}, {cfg.n_cam} cams {cfg.height}x{cfg.width}"
         loss_of = lambda: float(tr.loss_acc[0])
     else:
@@ -135,7 +135,7 @@ def run_dp(args, rank, local_rank, world):
                     state=torch.randn(B, cfg.action_dim, generator=g).pin_memory(),
                     act=torch.randn(B, cfg.chunk, cfg.action_dim, generator=g).pin_memory())
         dev = {k: v.cuda() for k, v in host.items()}
-        step_fn = lambda: tr.train_step(dev["img"], dev["ids"], dev["state"], dev["act"])
+        step_fn = lambda: (tr.train_step if args.eager else tr.step)(dev["img"], dev["ids"], dev["state"], dev["act"])
         model_desc = (f"ViT {cfg.vit_layers}x{cfg.vit_dim} + LM {cfg.lm_layers}x{cfg.hidden} ({cfg.heads}/{cfg.kv_heads} heads) + "
                       f"expert {cfg.lm_layers}x{cfg.expert_width}, {cfg.n_cam} cams {cfg.image}^2, chunk {cfg.chunk}; prefix frozen")
         loss_of = lambda: float(tr.loss_acc[0])

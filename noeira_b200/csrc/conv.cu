@@ -86,15 +86,20 @@ __global__ void __launch_bounds__(256)
 bn_reduce_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b2, const float* __restrict__ mean,
                  const float* __restrict__ rstd, float* __restrict__ p0, float* __restrict__ p1, int M, int C,
                  int rows_per_block, int mode /*0: Σa, Σa² ; 1: Σa, Σa·x̂(b2) */, const __nv_bfloat16* __restrict__ relu_out) {
-  __shared__ float s0[8][256 + 8], s1[8][256 + 8];
-  const int cg = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  // L lanes (of 8 channels each) span a row; the other 256 / L thread groups take different rows, so that narrow
+  // layers (C = 64: L = 8, 32 rows per sweep) keep every lane loading
+  __shared__ float s0[256][9], s1[256][9];
+  int L = 1;
+  while (L < 32 && L * 8 < C) L <<= 1;
+  const int R = 256 / L;
+  const int cg = threadIdx.x % L, rg = threadIdx.x / L;
   const int col = blockIdx.x * 256 + cg * 8;
   const int r0 = blockIdx.y * rows_per_block, r1 = min(M, r0 + rows_per_block);
   float a0[8], a1[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) a0[k] = a1[k] = 0.f;
   if (col < C) {
-    for (int r = r0 + rg; r < r1; r += 8) {
+    for (int r = r0 + rg; r < r1; r += R) {
       const uint4 va = __ldg(reinterpret_cast<const uint4*>(a + (size_t)r * C + col));
       const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&va);
       float fa[8];
@@ -125,13 +130,15 @@ bn_reduce_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __res
     }
   }
 #pragma unroll
-  for (int k = 0; k < 8; ++k) { s0[rg][cg * 8 + k] = a0[k]; s1[rg][cg * 8 + k] = a1[k]; }
+  for (int k = 0; k < 8; ++k) { s0[threadIdx.x][k] = a0[k]; s1[threadIdx.x][k] = a1[k]; }
   __syncthreads();
-  float t0 = 0.f, t1 = 0.f;
-#pragma unroll
-  for (int g = 0; g < 8; ++g) { t0 += s0[g][threadIdx.x]; t1 += s1[g][threadIdx.x]; }
-  const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c < C) { p0[(size_t)blockIdx.y * C + c] = t0; p1[(size_t)blockIdx.y * C + c] = t1; }
+  if ((int)threadIdx.x < L * 8) {
+    float t0 = 0.f, t1 = 0.f;
+    const int lane_of_col = threadIdx.x >> 3, k = threadIdx.x & 7;
+    for (int g = 0; g < R; ++g) { t0 += s0[g * L + lane_of_col][k]; t1 += s1[g * L + lane_of_col][k]; }
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < C) { p0[(size_t)blockIdx.y * C + c] = t0; p1[(size_t)blockIdx.y * C + c] = t1; }
+  }
 }
 
 // forward finish: mean, rstd, running stats
@@ -256,33 +263,55 @@ maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
     idx[i] = bi;
   }
 }
-// dx = gather over the (≤ 4 for 3x3/2) windows that contain the element: deterministic
+// dx = gather over the windows that contain the element (at most ceil(K/stride)^2 = 4 for 3x3 / 2): deterministic.
+// One thread owns 8 consecutive channels of one input pixel when C % 8 == 0 (16-byte dy loads, 32-byte idx loads);
+// the candidate output range is computed directly instead of testing all K*K taps.
+template <int VEC>
 __global__ void __launch_bounds__(256)
 maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const int* __restrict__ idx, __nv_bfloat16* __restrict__ dx, int B,
                    int H, int W, int C, int K, int stride, int pad, int OH, int OW) {
-  const long long total = (long long)B * H * W * C, step = (long long)gridDim.x * blockDim.x;
+  const int CV = C / VEC;
+  const long long total = (long long)B * H * W * CV, step = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
-    const int c = (int)(i % C);
-    long long r = i / C;
+    const int cv = (int)(i % CV);
+    long long r = i / CV;
     const int w = (int)(r % W); r /= W;
     const int h = (int)(r % H);
     const int b = (int)(r / H);
-    float acc = 0.f;
-    for (int kh = 0; kh < K; ++kh) {
-      const int th = h + pad - kh;
-      if (th < 0 || th % stride) continue;
-      const int oh = th / stride;
-      if (oh >= OH) continue;
-      for (int kw = 0; kw < K; ++kw) {
-        const int tw = w + pad - kw;
-        if (tw < 0 || tw % stride) continue;
-        const int ow = tw / stride;
-        if (ow >= OW) continue;
-        const long long o = (((long long)b * OH + oh) * OW + ow) * C + c;
-        if (idx[o] == (int)i) acc += __bfloat162float(dy[o]);
+    const int c0 = cv * VEC;
+    const int my = ((b * H + h) * W + w) * C + c0;
+    // output rows oh with oh*stride - pad <= h <= oh*stride - pad + K - 1
+    const int oh_lo = max(0, (h + pad - K + stride) / stride), oh_hi = min(OH - 1, (h + pad) / stride);
+    const int ow_lo = max(0, (w + pad - K + stride) / stride), ow_hi = min(OW - 1, (w + pad) / stride);
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    for (int oh = oh_lo; oh <= oh_hi; ++oh)
+      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+        const long long o = (((long long)b * OH + oh) * OW + ow) * C + c0;
+        if (VEC == 8) {
+          const int4 i0 = *reinterpret_cast<const int4*>(idx + o), i1 = *reinterpret_cast<const int4*>(idx + o + 4);
+          const uint4 g = *reinterpret_cast<const uint4*>(dy + o);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+          const int id[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float gv = (j & 1) ? __high2float(gh[j >> 1]) : __low2float(gh[j >> 1]);
+            if (id[j] == my + j) acc[j] += gv;
+          }
+        } else {
+          if (idx[o] == my) acc[0] += __bfloat162float(dy[o]);
+        }
       }
+    if (VEC == 8) {
+      uint4 out;
+      __nv_bfloat162* oh2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) oh2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      *reinterpret_cast<uint4*>(dx + my) = out;
+    } else {
+      dx[my] = __float2bfloat16(acc[0]);
     }
-    dx[i] = __float2bfloat16(acc);
   }
 }
 
@@ -331,7 +360,7 @@ int nb_col2im(const void* dcol, void* dx, int B, int H, int W, int C, int KH, in
 
 int nb_bn_split(long long M) {
   long long s = M / 256;
-  return (int)(s < 1 ? 1 : (s > 256 ? 256 : s));
+  return (int)(s < 1 ? 1 : (s > 1024 ? 1024 : s));
 }
 // partials: 2 * nb_bn_split(M) * C floats
 int nb_bn_fwd(const void* x, const float* gamma, const float* beta, const void* residual, void* y, float* mean, float* rstd,
@@ -388,7 +417,11 @@ int nb_maxpool_fwd(const void* x, void* y, int* idx, int B, int H, int W, int C,
 }
 int nb_maxpool_bwd(const void* dy, const int* idx, void* dx, int B, int H, int W, int C, int K, int stride, int pad, int OH,
                    int OW, void* stream) {
-  maxpool_bwd_kernel<<<g1((long long)B * H * W * C), 256, 0, (cudaStream_t)stream>>>(
+  if (C % 8 == 0)
+    maxpool_bwd_kernel<8><<<g1((long long)B * H * W * C / 8), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)dy, idx, (__nv_bfloat16*)dx, B, H, W, C, K, stride, pad, OH, OW);
+  else
+    maxpool_bwd_kernel<1><<<g1((long long)B * H * W * C), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dy, idx, (__nv_bfloat16*)dx, B, H, W, C, K, stride, pad, OH, OW);
   NB_LAUNCH_CHECK();
   return NB_OK;

@@ -6,6 +6,8 @@
 #define NB_ACT_GELU 3   // tanh approximation
 #define NB_ACT_SILU 4
 #define NB_ACT_SIGMOID 5
+// `dact` slot only: the aux tensor is ADDED to the result (residual connection fused into the epilogue)
+#define NB_AUX_ADD 16
 
 // Split-K workspace: the first NB_GEMM_WS_COUNTERS u32 are per-tile arrival counters (zero at rest),
 // fp32 partial tiles follow.

@@ -126,6 +126,10 @@ __device__ __forceinline__ void dact_apply16(int dact, float (&v)[16], const flo
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[j] *= dact_apply(NB_ACT_SILU, sv[j]);
       break;
+    case NB_AUX_ADD:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] += sv[j];
+      break;
     default: break;
   }
 }

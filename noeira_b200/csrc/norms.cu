@@ -30,7 +30,10 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // y = (x - mean) * rstd * gamma + beta   (RMS: mean = 0, no beta).  stats[row] = (mean, rstd).
-template <bool RMS>
+// NV = 16-byte vectors cached per lane (the row is read once when D <= NV * 256).  The cache holds the packed
+// bf16 words, so D = 768 needs 12 registers and five 256-thread blocks fit on an SM: the kernel is bound by
+// bytes in flight per SM, i.e. by occupancy.
+template <bool RMS, int NV>
 __global__ void __launch_bounds__(256)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ gamma,
                 const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, int ldy, float2* __restrict__ stats,
@@ -39,21 +42,27 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __res
   if (row >= M) return;
   const __nv_bfloat16* xr = x + (size_t)row * ldx;
   const int nvec = D / 8;
-  float c[MAXV][8];
+  uint4 c[NV];
   float s = 0.f, ss = 0.f;
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k) {
+  for (int k = 0; k < NV; ++k) {
+    const int v = lane + k * 32;
+    if (v < nvec) c[k] = *reinterpret_cast<const uint4*>(xr + v * 8);
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
     const int v = lane + k * 32;
     if (v < nvec) {
-      unpack8(*reinterpret_cast<const uint4*>(xr + v * 8), c[k]);
+      float t[8];
+      unpack8(c[k], t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        s += c[k][i];
-        ss += c[k][i] * c[k][i];
+        s += t[i];
+        ss += t[i] * t[i];
       }
     }
   }
-  for (int v = lane + MAXV * 32; v < nvec; v += 32) {  // D > 2048: not cached
+  for (int v = lane + NV * 32; v < nvec; v += 32) {  // columns beyond the register cache
     float t[8];
     unpack8(*reinterpret_cast<const uint4*>(xr + v * 8), t);
 #pragma unroll
@@ -69,29 +78,33 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __res
   const float rstd = rsqrtf(var + eps);
   if (lane == 0 && stats) stats[row] = make_float2(mean, rstd);
   __nv_bfloat16* yr = y + (size_t)row * ldy;
+  auto emit = [&](int v, const uint4& packed) {
+    float t[8], o[8], g[8], bt[8];
+    unpack8(packed, t);
+    if (gamma) {
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + v * 8)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + v * 8) + 1);
+      g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+    } else {
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k) {
-    const int v = lane + k * 32;
-    if (v < nvec) {
-      float o[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int col = v * 8 + i;
-        o[i] = (c[k][i] - mean) * rstd * (gamma ? gamma[col] : 1.f) + ((!RMS && beta) ? beta[col] : 0.f);
-      }
-      *reinterpret_cast<uint4*>(yr + v * 8) = pack8(o);
+      for (int i = 0; i < 8; ++i) g[i] = 1.f;
     }
-  }
-  for (int v = lane + MAXV * 32; v < nvec; v += 32) {
-    float t[8], o[8];
-    unpack8(*reinterpret_cast<const uint4*>(xr + v * 8), t);
+    if (!RMS && beta) {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + v * 8)), b1 = __ldg(reinterpret_cast<const float4*>(beta + v * 8) + 1);
+      bt[0] = b0.x; bt[1] = b0.y; bt[2] = b0.z; bt[3] = b0.w; bt[4] = b1.x; bt[5] = b1.y; bt[6] = b1.z; bt[7] = b1.w;
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int col = v * 8 + i;
-      o[i] = (t[i] - mean) * rstd * (gamma ? gamma[col] : 1.f) + ((!RMS && beta) ? beta[col] : 0.f);
+      for (int i = 0; i < 8; ++i) bt[i] = 0.f;
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (t[i] - mean) * rstd * g[i] + bt[i];
     *reinterpret_cast<uint4*>(yr + v * 8) = pack8(o);
+  };
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int v = lane + k * 32;
+    if (v < nvec) emit(v, c[k]);
   }
+  for (int v = lane + NV * 32; v < nvec; v += 32) emit(v, *reinterpret_cast<const uint4*>(xr + v * 8));
 }
 
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * gamma   (RMS: no mean(g) term)
@@ -209,12 +222,23 @@ int nb_norm_fwd(const void* x, int ldx, const float* gamma, const float* beta, v
                 int D, float eps, int rms, void* stream) {
   if (D % 8 || ldx % 8 || ldy % 8) return NB_ERR_UNALIGNED;
   dim3 grid(ceil_div(M, 8));
-  if (rms)
-    norm_fwd_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, gamma, beta,
-                                                                 (__nv_bfloat16*)y, ldy, (float2*)stats, M, D, eps);
-  else
-    norm_fwd_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, gamma, beta,
-                                                                  (__nv_bfloat16*)y, ldy, (float2*)stats, M, D, eps);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int need = ceil_div(D, 256);
+#define NB_NORM_FWD(R, NVV)                                                                                        \
+  norm_fwd_kernel<R, NVV><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, gamma, beta, (__nv_bfloat16*)y, ldy, \
+                                                (float2*)stats, M, D, eps)
+  if (rms) {
+    if (need <= 1) NB_NORM_FWD(true, 1);
+    else if (need <= 2) NB_NORM_FWD(true, 2);
+    else if (need <= 4) NB_NORM_FWD(true, 4);
+    else NB_NORM_FWD(true, 8);
+  } else {
+    if (need <= 1) NB_NORM_FWD(false, 1);
+    else if (need <= 2) NB_NORM_FWD(false, 2);
+    else if (need <= 4) NB_NORM_FWD(false, 4);
+    else NB_NORM_FWD(false, 8);
+  }
+#undef NB_NORM_FWD
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

@@ -306,10 +306,19 @@ class ACTTrainer:
         self.loss_acc = torch.zeros(2, device=self.device)   # [l1, kl]
         self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed + 11)
         self.l1 = nn.MSELoss(l1=True)
+        self._graphed = None
+
+    def step(self, qpos, images_u8, actions, enc_valid):
+        """One optimisation step replayed from a CUDA graph (captured on the third call; shapes must stay fixed)."""
+        if self._graphed is None:
+            from ..utils.graphs import GraphedStep
+            self._graphed = GraphedStep(self.train_step, [qpos, images_u8, actions, enc_valid], generators=[self.gen])
+        return self._graphed(qpos, images_u8, actions, enc_valid)
 
     def train_step(self, qpos, images_u8, actions, enc_valid):
         cfg = self.cfg
         B = qpos.shape[0]
+        nn.advance_rng(self.device)
         eps = torch.randn(B, cfg.latent, device=self.device, generator=self.gen)
         ahat, info = self.model.forward(qpos, images_u8, actions, enc_valid, eps)
         valid = enc_valid[:, 2:].float()

@@ -257,6 +257,14 @@ class VLATrainer:
         self.loss_acc = torch.zeros(1, device=self.device)
         self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed + 3)
         self.mse = nn.MSELoss()
+        self._graphed = None
+
+    def step(self, images, lang_ids, state, actions):
+        """One optimisation step replayed from a CUDA graph (captured on the third call; shapes must stay fixed)."""
+        if self._graphed is None:
+            from ..utils.graphs import GraphedStep
+            self._graphed = GraphedStep(self.train_step, [images, lang_ids, state, actions], generators=[self.gen])
+        return self._graphed(images, lang_ids, state, actions)
 
     def train_step(self, images, lang_ids, state, actions):
         """images [B, n_cam, 3, H, W] in [0,1], lang_ids [B, n_lang] int64, state [B, action_dim], actions [B, chunk, action_dim]."""

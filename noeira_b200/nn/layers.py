@@ -112,7 +112,9 @@ class Linear(Module):
         return self.weight.storage_shape[1]
 
     # ---- forward
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """``residual`` (same shape as the output) is added to the result; on CUDA the addition happens in the GEMM
+        epilogue when the layer has no activation.  Its gradient is the caller's business (identity)."""
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
         self._lead = lead
@@ -123,14 +125,23 @@ class Linear(Module):
                 pre = pre + self.bias.data
             y = _ACT_CPU[self.act](pre)
             self._saved = y if self.act in SAVES_OUTPUT else pre
-            return y.reshape(*lead, self.out_dim)
+            y = y.reshape(*lead, self.out_dim)
+            return y if residual is None else y + residual
         W = self.weight.shadow
         b = self.bias.storage if self.bias is not None else None
         xa = x2[:, : self.in_dim]
-        if self.act is None or self.act in SAVES_OUTPUT:
-            y = ops.gemm(xa, W, b_mn=True, bias=b, act=self.act,
+        res = None
+        if residual is not None and self.act is None and not self.out_fp32 and self.out_pad == self.out_dim:
+            res = residual.reshape(-1, self.out_dim)
+            if res.dtype != torch.bfloat16 or res.stride(-1) != 1 or res.stride(0) % 8:
+                res = None
+        if self.act is None or self.act in SAVES_OUTPUT or not torch.is_grad_enabled():
+            # no backward will follow under no_grad: any activation can then be fused, nothing needs saving
+            y = ops.gemm(xa, W, b_mn=True, bias=b, act=self.act, residual=res,
                          out_dtype=torch.float32 if self.out_fp32 else torch.bfloat16)
-            self._saved = y
+            self._saved = y if res is None else None
+            if res is not None:
+                residual = None
         else:
             pre = ops.gemm(xa, W, b_mn=True, bias=b)
             y = torch.empty_like(pre)
@@ -139,7 +150,8 @@ class Linear(Module):
             self._saved = pre
         if self.out_pad != self.out_dim:
             y = y[:, : self.out_dim]
-        return y.reshape(*lead, self.out_dim) if len(lead) != 1 else y
+        y = y.reshape(*lead, self.out_dim) if len(lead) != 1 else y
+        return y if residual is None else y + residual
 
     # ---- backward
     def vjp(self, dy, dy_is_pre: bool = False, fuse_dact=None):

@@ -199,7 +199,7 @@ class SelfAttention(Module):
         self.out = self.add_child("out", Linear(self.h * self.hd, dim, bias=bias))
         self.core = AttentionCore(mask=mask, frame=frame)
 
-    def forward(self, x, key_valid=None, bias=None):
+    def forward(self, x, key_valid=None, bias=None, residual=None):
         B, S, _ = x.shape
         qkv = self.qkv.forward(x).reshape(B, S, self.h + 2 * self.hkv, self.hd)
         q, k, v = qkv[:, :, : self.h], qkv[:, :, self.h: self.h + self.hkv], qkv[:, :, self.h + self.hkv:]
@@ -208,7 +208,7 @@ class SelfAttention(Module):
             rope_(k, self.rope_theta)
         self.last_k, self.last_v = k, v      # post-RoPE keys / values (prefix KV cache of a VLA)
         o = self.core.forward(q, k, v, key_valid=key_valid, bias=bias)
-        return self.out.forward(o.reshape(B, S, self.h * self.hd))
+        return self.out.forward(o.reshape(B, S, self.h * self.hd), residual=residual)
 
     def vjp(self, dy):
         B, S, _ = dy.shape
@@ -305,8 +305,8 @@ class SwiGLUFFN(Module):
         self.act = SwiGLU(hidden)
         self.down = self.add_child("1", Linear(hidden, dim, bias=bias))
 
-    def forward(self, x):
-        return self.down.forward(self.act.forward(self.up.forward(x)))
+    def forward(self, x, residual=None):
+        return self.down.forward(self.act.forward(self.up.forward(x)), residual=residual)
 
     def vjp(self, dy):
         return self.up.vjp(self.act.vjp(self.down.vjp(dy)))
@@ -320,8 +320,8 @@ class FeedForward(Module):
         self.l0 = self.add_child("0", Linear(dim, hidden, act=act, bias=bias))
         self.l1 = self.add_child("1", Linear(hidden, dim, bias=bias))
 
-    def forward(self, x):
-        return self.l1.forward(self.l0.forward(x))
+    def forward(self, x, residual=None):
+        return self.l1.forward(self.l0.forward(x), residual=residual)
 
     def vjp(self, dy):
         fuse = None
@@ -343,8 +343,8 @@ class TransformerBlock(Module):
         self.ffn = self.add_child("ffn", SwiGLUFFN(dim, ff, bias=bias) if ffn == "swiglu" else FeedForward(dim, ff, ffn, bias))
 
     def forward(self, x, key_valid=None, bias=None):
-        x = x + self.attn.forward(self.n1.forward(x), key_valid=key_valid, bias=bias)
-        return x + self.ffn.forward(self.n2.forward(x))
+        x = self.attn.forward(self.n1.forward(x), key_valid=key_valid, bias=bias, residual=x)
+        return self.ffn.forward(self.n2.forward(x), residual=x)
 
     def vjp(self, dy):
         d = dy + self.n2.vjp(self.ffn.vjp(dy))

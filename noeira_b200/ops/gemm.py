@@ -9,7 +9,7 @@ from .._native import check, cuda_lib, ptr, stream_ptr
 from .status import device_status
 from .streams import ws_key
 
-ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, "gelu": 3, "silu": 4, "sigmoid": 5}
+ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, "gelu": 3, "silu": 4, "sigmoid": 5, "add": 16}
 
 # Split-K workspace: [1024 u32 tile counters | fp32 partial tiles].  One per device, allocated on first use
 # (its address is then stable, so captured CUDA graphs can replay).  GEMMs on ONE stream serialise and may
@@ -36,15 +36,18 @@ def default_workspace(device) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor = None,
          out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor = None,
          act=None, aux: torch.Tensor = None, dact=None, bn: int = 0, n: int = None,
-         workspace: torch.Tensor = None) -> torch.Tensor:
+         workspace: torch.Tensor = None, residual: torch.Tensor = None) -> torch.Tensor:
     """``out[M,N] = epi(alpha · A·B)`` in bf16 with fp32 accumulation.
 
     ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]`` (``b_mn=False``) or
     ``[K,N]`` (``b_mn=True``).  Rows may be strided (pitch a multiple of 8 elements).  ``bias`` fp32 ``[N]``;
     ``act`` applied after the bias; ``dact`` multiplies by the derivative of that activation evaluated on the
     saved bf16 tensor ``aux [M,N]`` (output for tanh/relu/sigmoid, input for gelu/silu); ``accumulate`` adds
-    into an fp32 ``out``.
+    into an fp32 ``out``; ``residual`` (bf16 ``[M,N]``, exclusive with ``dact``) is added after the activation.
     """
+    if residual is not None:
+        assert dact is None and aux is None
+        aux, dact = residual, "add"
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1
     if a_mn:

@@ -214,3 +214,45 @@ def test_act_trainer_loss_decreases():
         losses.append(float(tr.loss_acc[0]))
     assert all(l == l for l in losses), losses[:5]
     assert sum(losses[-5:]) < 0.9 * sum(losses[:5]), (losses[:3], losses[-3:])
+
+
+def test_dropout_kernel_counter_hash():
+    from noeira_b200 import nn
+    d = nn.Dropout(0.25, seed=3).to("cuda")
+    x = torch.ones(1000, 257, device="cuda", dtype=torch.bfloat16)
+    y1 = d.forward(x)
+    keep = (y1 != 0).float().mean().item()
+    assert abs(keep - 0.75) < 0.01, keep
+    assert torch.allclose(y1[y1 != 0].float(), torch.full((1,), 1 / 0.75, device="cuda"), atol=1e-2)
+    g = torch.randn_like(x)
+    dx = d.vjp(g)
+    assert torch.equal(dx != 0, (y1 != 0) & (g != 0))
+    y2 = d.forward(x)                      # same counter: same mask
+    assert torch.equal(y1, y2)
+    nn.advance_rng("cuda")
+    y3 = d.forward(x)                      # advanced counter: a fresh mask
+    assert (y3 != y1).float().mean().item() > 0.2
+    d.eval()
+    assert d.forward(x) is x
+
+
+def test_act_graphed_step_matches_eager():
+    from noeira_b200.models.act import ACTConfig, ACTTrainer
+    cfg = ACTConfig(chunk=16, n_cam=1, height=64, width=96, dim=128, heads=2, ff=256, enc_layers=1, dec_layers=1, latent=8,
+                    dropout=0.0, lr=5e-4)
+    g = torch.Generator().manual_seed(0)
+    B = 4
+    qpos = torch.randn(B, 6, generator=g).cuda()
+    img = torch.randint(0, 255, (B, 1, 3, 64, 96), dtype=torch.uint8, generator=g).cuda()
+    act = (torch.randn(B, 16, 6, generator=g) * 0.5).cuda()
+    valid = torch.ones(B, 18, device="cuda")
+    a, b = ACTTrainer(cfg), ACTTrainer(cfg)
+    for _ in range(6):
+        a.train_step(qpos, img, act, valid)
+        b.step(qpos, img, act, valid)
+    torch.cuda.synchronize()
+    assert b._graphed.graph is not None and b._graphed.launches > 100
+    la, lb = a.loss_acc.cpu(), b.loss_acc.cpu()
+    assert torch.allclose(la, lb, rtol=1e-4, atol=1e-5), (la, lb)
+    for (n, p), (_, q) in zip(a.model.named_params(), b.model.named_params()):
+        assert torch.equal(p.data, q.data), n
