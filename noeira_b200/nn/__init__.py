@@ -11,3 +11,5 @@ from .param import Param, State  # noqa: F401
 from .transformer import (AttentionCore, CrossAttention, Embedding, FeedForward, LayerNorm, MSELoss, RMSNorm,  # noqa: F401
                           SelfAttention, SwiGLU, SwiGLUFFN, TransformerBlock, cross_entropy, rope_, sincos_embed)
 from .conv import BasicBlock, BatchNorm2D, Conv2D, MaxPool2D, ResNet18Backbone, normalize_images  # noqa: F401
+from .graph import ComputeGraph, ExternalNode, InputSlot, Node  # noqa: F401
+from . import schedulers  # noqa: F401
