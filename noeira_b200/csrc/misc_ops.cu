@@ -251,3 +251,41 @@ int nb_sincos_embed(const float* t, void* out, int ld, int B, int D, float min_p
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------ Q4_0 weights
+// Block of 32 values along a ROW of the [IN, OUT] weight: one fp16 scale d and 16 bytes of 4-bit codes q in [0, 15];
+// byte j of a block holds element j (low nibble) and element j + 16 (high nibble); value = (q − 8)·d.
+// (Same block format as noeira/nn/quant/q4_0.mojo.)  Output: bf16 [rows, ld] — the tcgen05 GEMM then reads it.
+namespace {
+__global__ void __launch_bounds__(256)
+q4_0_dequant_kernel(const unsigned char* __restrict__ codes, const __half* __restrict__ scales, __nv_bfloat16* __restrict__ out,
+                    int rows, int cols, int ld) {
+  const int blocks_per_row = cols / 32;
+  const long long total = (long long)rows * blocks_per_row;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(b / blocks_per_row), cb = (int)(b % blocks_per_row);
+    const float d = __half2float(scales[b]);
+    const uint4 q = *reinterpret_cast<const uint4*>(codes + b * 16);
+    const unsigned char* qb = reinterpret_cast<const unsigned char*>(&q);
+    __nv_bfloat16* o = out + (size_t)r * ld + cb * 32;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      o[j] = __float2bfloat16(((int)(qb[j] & 15) - 8) * d);
+      o[j + 16] = __float2bfloat16(((int)(qb[j] >> 4) - 8) * d);
+    }
+  }
+}
+}  // namespace
+
+extern "C" int nb_q4_0_dequant(const unsigned char* codes, const void* scales, void* out, int rows, int cols, int ld,
+                               void* stream) {
+  if (cols % 32 || ((uintptr_t)codes & 15)) return NB_ERR_UNALIGNED;
+  const long long total = (long long)rows * (cols / 32);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  q4_0_dequant_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(codes, (const __half*)scales, (__nv_bfloat16*)out, rows,
+                                                                    cols, ld);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}

@@ -13,3 +13,4 @@ from .transformer import (AttentionCore, CrossAttention, Embedding, FeedForward,
 from .conv import BasicBlock, BatchNorm2D, Conv2D, MaxPool2D, ResNet18Backbone, normalize_images  # noqa: F401
 from .graph import ComputeGraph, ExternalNode, InputSlot, Node  # noqa: F401
 from . import schedulers  # noqa: F401
+from .peft import LoRALinear, QLinear, QLoRALinear, dequantize_q4_0, freeze_params, quantize_q4_0  # noqa: F401
