@@ -1,1 +1,2 @@
 from .batched_env import BatchedEnv, HalfCheetahEnv, HopperEnv, Physics3dBatchedEnv, PlanarChainEnv  # noqa: F401
+from .classic import CartPoleEnv, MountainCarContinuousEnv, PendulumEnv  # noqa: F401

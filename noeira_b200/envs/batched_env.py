@@ -68,10 +68,11 @@ class Physics3dBatchedEnv(BatchedEnv):
         self.engine.reset(self.obs, self.obs_bf16)
         return self.obs
 
-    def step_batch(self, action, dbg=None):
+    def step_batch(self, action, dbg=None, auto_reset: bool = True):
+        """``auto_reset=False`` keeps finished lanes where they are (planning rollouts, evaluation of fixed horizons)."""
         self.engine.step(action, self.reward, self.done, self.terminated, obs_f32=self.obs, obs_bf16=self.obs_bf16,
                          next_obs_f32=self.next_obs, next_obs_bf16=self.next_obs_bf16,
-                         finished_return=self.finished_return, do_reset=True, ep_stats=self.ep_stats, dbg=dbg)
+                         finished_return=self.finished_return, do_reset=auto_reset, ep_stats=self.ep_stats, dbg=dbg)
         return self.obs, self.reward, self.done, self.terminated
 
 

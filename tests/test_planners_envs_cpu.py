@@ -1,0 +1,59 @@
+import math
+
+import torch
+
+
+def _point_mass_rollout(target):
+    """Double integrator in the plane: actions are accelerations, reward = −distance to the target − small effort."""
+    def rollout(acts):
+        K, H, _ = acts.shape
+        p, v = torch.zeros(K, 2), torch.zeros(K, 2)
+        ret = torch.zeros(K)
+        for t in range(H):
+            v = v + 0.1 * acts[:, t]
+            p = p + 0.1 * v
+            ret += -(p - target).norm(dim=1) - 0.01 * acts[:, t].pow(2).sum(1)
+        return ret
+    return rollout
+
+
+def test_planners_improve_over_zero_action():
+    from noeira_b200.planners import CEM, MPPI, RandomShooting
+    target = torch.tensor([1.0, -0.5])
+    ro = _point_mass_rollout(target)
+    base = float(ro(torch.zeros(1, 20, 2)))
+    for P, kw, it in ((MPPI, dict(samples=256, sigma=0.6, lam=0.5), 6), (CEM, dict(samples=256, elites=24), 5),
+                      (RandomShooting, dict(samples=512), 1)):
+        pl = P(ro, 20, 2, seed=0, **kw)
+        a0 = pl.plan(it)
+        assert a0.shape == (2,) and float(ro(pl.mean[None])) > base + 2.0, P.__name__
+        assert a0[0] > 0 and a0[1] < 0, (P.__name__, a0)        # first action points at the target
+        pl.shift()
+        assert pl.mean.shape == (20, 2)
+
+
+def test_classic_envs_dynamics_and_reset():
+    from noeira_b200.envs import CartPoleEnv, MountainCarContinuousEnv, PendulumEnv
+    pen = PendulumEnv(8, seed=0)
+    o = pen.reset_batch()
+    assert o.shape == (8, 3) and torch.allclose(o[:, 0] ** 2 + o[:, 1] ** 2, torch.ones(8), atol=1e-6)
+    th0, thd0 = pen.state[:, 0].clone(), pen.state[:, 1].clone()
+    pen.step_batch(torch.zeros(8, 1))
+    thd1 = (thd0 + 15.0 * torch.sin(th0) * 0.05).clamp(-8, 8)
+    assert torch.allclose(pen.state[:, 1], thd1, atol=1e-6) and (pen.reward <= 0).all()
+    for _ in range(199):
+        pen.step_batch(torch.zeros(8, 1))
+    assert pen.done.all() and not pen.terminated.any() and (pen.steps == 0).all() and pen.ep_stats[1] == 8
+    cp = CartPoleEnv(64, seed=1)
+    cp.reset_batch()
+    n = 0
+    while cp.ep_stats[1] == 0 and n < 400:
+        cp.step_batch(torch.ones(64, 1))                 # constant push topples the pole quickly
+        n += 1
+    assert 5 < n < 120 and cp.terminated.any()
+    mc = MountainCarContinuousEnv(4, seed=2)
+    mc.reset_batch()
+    for t in range(400):                                   # energy pumping: push along the velocity
+        v = mc.state[:, 1]
+        mc.step_batch(torch.where(v >= 0, 1.0, -1.0)[:, None])
+    assert mc.ep_stats[1] >= 4 and mc.ep_stats[0] > 4 * 50
