@@ -675,7 +675,7 @@ phys_env_step_kernel(PhysParams P, const int* __restrict__ imodel, const float* 
   __syncthreads();
   const ModelView m = view(im_sh, fm_sh, P);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int env = blockIdx.x * NB_PHYS_WARPS + warp;
+  const int env = blockIdx.x * (int)(blockDim.x >> 5) + warp;
   if (env >= n_envs) return;
   float* base = smem + P.imodel_words + P.fmodel_words + warp * P.warp_words;
   WarpScratch w = carve(base, P);
@@ -835,7 +835,7 @@ phys_fk_kernel(PhysParams P, const int* __restrict__ imodel, const float* __rest
   __syncthreads();
   const ModelView m = view(im_sh, fm_sh, P);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int env = blockIdx.x * NB_PHYS_WARPS + warp;
+  const int env = blockIdx.x * (int)(blockDim.x >> 5) + warp;
   if (env >= n_envs) return;
   float* base = smem + P.imodel_words + P.fmodel_words + warp * P.warp_words;
   WarpScratch w = carve(base, P);
@@ -850,9 +850,25 @@ phys_fk_kernel(PhysParams P, const int* __restrict__ imodel, const float* __rest
 
 extern "C" {
 
-int nb_phys_smem_bytes(const PhysParams* P) {
-  return (int)sizeof(float) * (P->imodel_words + P->fmodel_words + NB_PHYS_WARPS * P->warp_words);
+static int phys_smem_bytes(const PhysParams* P, int warps) {
+  return (int)sizeof(float) * (P->imodel_words + P->fmodel_words + warps * P->warp_words);
 }
+// Warps (= environments) per block: the kernel is limited by shared memory per SM, so the block size that leaves the
+// least of the 227 KB unused wins (each resident block also costs 1 KB of reserved shared memory).
+static int phys_pick_warps(const PhysParams* P) {
+  int best = NB_PHYS_WARPS, best_total = 0;
+  for (int wpb = NB_PHYS_WARPS; wpb >= 2; --wpb) {
+    const int bytes = phys_smem_bytes(P, wpb) + 1024;
+    if (bytes > 227 * 1024) continue;
+    int blocks = (228 * 1024) / bytes;
+    if (blocks * wpb > 64) blocks = 64 / wpb;       // 64 resident warps per SM
+    const int total = blocks * wpb;
+    if (total > best_total) { best_total = total; best = wpb; }
+  }
+  return best;
+}
+int nb_phys_smem_bytes(const PhysParams* P) { return phys_smem_bytes(P, phys_pick_warps(P)); }
+int nb_phys_warps_per_block(const PhysParams* P) { return phys_pick_warps(P); }
 
 int nb_phys_env_step(const PhysParams* P, const int* imodel, const float* fmodel, float* qpos, float* qvel,
                      float* warm, int* step_count, float* ep_return, const float* action, int action_stride,
@@ -868,8 +884,9 @@ int nb_phys_env_step(const PhysParams* P, const int* imodel, const float* fmodel
     NB_CUDA(cudaFuncSetAttribute(phys_env_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = smem;
   }
-  const int grid = nb::ceil_div(n_envs, NB_PHYS_WARPS);
-  phys_env_step_kernel<<<grid, NB_PHYS_WARPS * 32, smem, (cudaStream_t)stream>>>(
+  const int wpb = phys_pick_warps(P);
+  const int grid = nb::ceil_div(n_envs, wpb);
+  phys_env_step_kernel<<<grid, wpb * 32, smem, (cudaStream_t)stream>>>(
       *P, imodel, fmodel, qpos, qvel, warm, step_count, ep_return, action, action_stride, obs_f32,
       (__nv_bfloat16*)obs_bf16, obs_bf16_stride, next_obs_f32, (__nv_bfloat16*)next_obs_bf16, reward, done,
       terminated, finished_return, rng_counter, seed, n_envs, do_reset, ep_stats, dbg);
@@ -897,7 +914,8 @@ int nb_phys_fk(const PhysParams* P, const int* imodel, const float* fmodel, cons
     NB_CUDA(cudaFuncSetAttribute(phys_fk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = smem;
   }
-  phys_fk_kernel<<<nb::ceil_div(n_envs, NB_PHYS_WARPS), NB_PHYS_WARPS * 32, smem, (cudaStream_t)stream>>>(
+  const int wpb = phys_pick_warps(P);
+  phys_fk_kernel<<<nb::ceil_div(n_envs, wpb), wpb * 32, smem, (cudaStream_t)stream>>>(
       *P, imodel, fmodel, qpos, xpos, xmat, n_envs);
   NB_LAUNCH_CHECK();
   return NB_OK;
