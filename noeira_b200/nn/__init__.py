@@ -14,3 +14,5 @@ from .conv import BasicBlock, BatchNorm2D, Conv2D, MaxPool2D, ResNet18Backbone, 
 from .graph import ComputeGraph, ExternalNode, InputSlot, Node  # noqa: F401
 from . import schedulers  # noqa: F401
 from .peft import LoRALinear, QLinear, QLoRALinear, dequantize_q4_0, freeze_params, quantize_q4_0  # noqa: F401
+from .recurrent import GRUCell, LSTMCell, LSTMSeq  # noqa: F401
+from . import losses  # noqa: F401
