@@ -1,0 +1,56 @@
+import gzip
+import struct
+
+import numpy as np
+
+
+def test_idx_cifar_charcorpus(tmp_path):
+    from noeira_b200.data.datasets import CharCorpus, load_cifar10_bin, load_mnist_idx
+    imgs = np.random.default_rng(0).integers(0, 256, (10, 28, 28), dtype=np.uint8)
+    labels = np.arange(10, dtype=np.uint8)
+    (tmp_path / "im.gz").write_bytes(gzip.compress(struct.pack(">IIII", 2051, 10, 28, 28) + imgs.tobytes()))
+    (tmp_path / "lb").write_bytes(struct.pack(">II", 2049, 10) + labels.tobytes())
+    x, y = load_mnist_idx(str(tmp_path / "im.gz"), str(tmp_path / "lb"))
+    assert np.array_equal(x, imgs) and np.array_equal(y, labels)
+    rec = np.random.default_rng(1).integers(0, 256, (7, 3073), dtype=np.uint8)
+    (tmp_path / "b1.bin").write_bytes(rec.tobytes())
+    cx, cy = load_cifar10_bin([str(tmp_path / "b1.bin")])
+    assert cx.shape == (7, 3, 32, 32) and np.array_equal(cy, rec[:, 0]) and cx[3, 2, 31, 31] == rec[3, -1]
+    c = CharCorpus("hello world")
+    assert c.vocab == 8 and c.decode(c.encode("low")) == "low" and len(c.tokens) == 11
+
+
+def test_trajectory_store_and_loader(tmp_path):
+    from noeira_b200.data.datasets import TrajectoryStore, TrajectoryWriter
+    w = TrajectoryWriter(str(tmp_path / "t.traj"), {"obs": 3, "act": 2, "rew": 1}, {"env": "test"})
+    rng = np.random.default_rng(0)
+    eps = []
+    for T in (5, 17, 40):
+        e = dict(obs=rng.normal(size=(T, 3)), act=rng.normal(size=(T, 2)), rew=rng.normal(size=(T,)))
+        eps.append(e)
+        w.add_episode(**e)
+    w.close()
+    s = TrajectoryStore(str(tmp_path / "t.traj"))
+    assert s.lengths == [5, 17, 40] and s.n_steps == 62 and s.meta == {"env": "test"} and s.width == 6
+    assert np.allclose(s.episode(1)["act"], eps[1]["act"].astype(np.float32))
+    allv = s.all_steps()
+    assert np.allclose(allv["rew"][:5, 0], eps[0]["rew"].astype(np.float32))
+    it = s.loader(batch=16, seed=1)
+    seen = []
+    for batch, idx in it:
+        assert np.allclose(batch["obs"], allv["obs"][idx.astype(np.int64)])
+        seen.extend(idx.tolist())
+    assert len(seen) == 48 and len(set(seen)) == 48          # drop_last: 3 full batches of distinct steps
+    it.close()
+
+
+def test_hyperparam_search(tmp_path):
+    from noeira_b200.core import hyperparam as hp
+    g = hp.grid({"lr": [1e-3, 1e-2], "h": [32, 64, 128]})
+    assert len(g) == 6 and {"lr": 1e-2, "h": 64} in g
+    r = hp.random_configs({"lr": ("loguniform", 1e-5, 1e-1), "layers": ("int", 1, 4), "act": ["relu", "tanh"]}, 20, seed=3)
+    assert len(r) == 20 and all(1e-5 <= c["lr"] <= 1e-1 and 1 <= c["layers"] <= 4 for c in r)
+    assert r == hp.random_configs({"lr": ("loguniform", 1e-5, 1e-1), "layers": ("int", 1, 4), "act": ["relu", "tanh"]}, 20, seed=3)
+    rows = hp.search(g, lambda c: -abs(c["lr"] - 1e-2) - abs(c["h"] - 64) / 1000, csv_path=str(tmp_path / "s.csv"))
+    assert rows[0]["lr"] == 1e-2 and rows[0]["h"] == 64
+    assert open(tmp_path / "s.csv").read().splitlines()[0] == "lr,h,score"
