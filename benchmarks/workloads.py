@@ -17,6 +17,8 @@ def run(args, rank, local_rank, world):
         return run_wm(args, rank, local_rank, world)
     if args.workload in ("act", "vla"):
         return run_dp(args, rank, local_rank, world)
+    if args.workload == "sac_cpu":
+        return run_sac_cpu(args)
     raise SystemExit(f"unknown workload {args.workload}")
 
 
@@ -179,4 +181,34 @@ def run_dp(args, rank, local_rank, world):
             "final_loss": round(loss_of(), 5)}))
     if world > 1:
         dist.destroy_process_group()
+    return 0
+
+
+def run_sac_cpu(args):
+    """SAC update on the CPU in fp32 (actor 17-256-256-(6+6) tanh-Gaussian, twin critics 23-256-256-1 with targets,
+    batch 256 of seed-generated transitions, Adam 3e-4, tau 0.005, gamma 0.99, automatic entropy): updates per second
+    through the explicit-backward ``nn`` path (this is the numerics-oracle path of the framework; no GPU involved)."""
+    from noeira_b200.agents.sac import SACConfig, SACTrainer
+    torch.manual_seed(0)
+    cfg = SACConfig()
+    tr = SACTrainer(cfg, device="cpu")
+    g = torch.Generator().manual_seed(0)
+    B = cfg.batch
+    s, sp = torch.randn(B, 17, generator=g), torch.randn(B, 17, generator=g)
+    a = torch.rand(B, 6, generator=g) * 2 - 1
+    r = torch.randn(B, generator=g)
+    d = (torch.rand(B, generator=g) < 0.01).float()
+    for _ in range(max(args.warmup, 3)):
+        tr.update(s, a, r, sp, d)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        m = tr.update(s, a, r, sp, d)
+    dt = time.perf_counter() - t0
+    print(json.dumps({"metric": "sac_cpu_updates_per_s", "value": round(args.steps / dt, 2), "unit": "updates/s", "n_gpus": 0,
+                      "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(dt / args.steps * 1e3, 3),
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+                      "data": "synthetic (seed-generated transitions, random-init weights)",
+                      "config": {"model": "SAC actor 17-256-256-12, twin critics 23-256-256-1 + targets", "global_batch": B,
+                                 "seq_len": 1, "parallelism": "cpu", "threads": torch.get_num_threads()},
+                      "gpu_launches": 0, "metrics": {k: (round(float(v), 5) if v == v else None) for k, v in (m or {}).items()} if isinstance(m, dict) else None}))
     return 0

@@ -33,6 +33,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   constexpr uint32_t Q_BYTES = BQ * HD * 2;
   constexpr uint32_t KV_BYTES = BKV * HD * 2;
   constexpr uint32_t P_BYTES = BQ * BKV * 2;
+  // P ring: with two buffers the softmax of block j+1 (exponentials, packing) runs while the tensor core still
+  // multiplies P_j V_j; at HD = 128 shared memory only has room for one.
+  constexpr int PS = (HD == 64) ? 2 : 1;
   constexpr uint32_t TMEM_COLS = 256;
   constexpr uint32_t S_COL = 0, O_COL = 128;    // S: 128 columns, O: HD columns
   constexpr float RESCALE_THRESHOLD = 8.f;      // log2 units: exponentials stay below 2^8 between rescales
@@ -43,7 +46,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* sK = sQ + Q_BYTES;             // 2 stages
   uint8_t* sV = sK + 2 * KV_BYTES;        // 2 stages
   uint8_t* sP = sV + 2 * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + PS * P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;    // [2]
   uint64_t* k_empty = bars + 3;   // [2]
@@ -51,10 +54,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;
   uint64_t* s_empty = bars + 10;
-  uint64_t* p_full = bars + 11;   // P_j in smem and O rescaled → the PV GEMM may run
-  uint64_t* pv_done = bars + 12;  // PV_j retired: P buffer free, O holds blocks 0..j
-  uint64_t* x_bar = bars + 13;    // the two threads of a row exchange their partial maxima / sums
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* p_full = bars + 11;   // [2] P_j in smem and O rescaled → the PV GEMM may run        (ring index j % PS)
+  uint64_t* pv_done = bars + 13;  // [2] PV_j retired: P buffer free, O holds blocks 0..j        (ring index j % PS)
+  uint64_t* x_bar = bars + 15;    // the two threads of a row exchange their partial maxima / sums
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* sh_x = reinterpret_cast<float*>(tmem_slot + 4);  // [2 buffers][2 halves][128 rows]
 
@@ -74,8 +77,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
     mbar_init(s_full, 1);
     mbar_init(s_empty, 8);
-    mbar_init(p_full, 8);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&p_full[i], 8);
+      mbar_init(&pv_done[i], 1);
+    }
     mbar_init(x_bar, 256);
     *abort_flag = 0;
     fence_barrier_init();
@@ -123,10 +128,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       auto issue_pv = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (*abort_flag || !mbar_wait(p_full, (uint32_t)j & 1u, p.status, 111)) return false;
+        const int ps = j % PS;
+        if (*abort_flag || !mbar_wait(&p_full[ps], (uint32_t)(j / PS) & 1u, p.status, 111)) return false;
         if (!mbar_wait(&v_full[st], ph, p.status, 112)) return false;
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP), vb = smem_u32(sV + st * KV_BYTES);
+        const uint32_t pa = smem_u32(sP + ps * P_BYTES), vb = smem_u32(sV + st * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           // P: two 64-key sub-tiles of 16 KB; V: 16 key-rows of 128 B per k-step, 64-column chunks 16 KB apart
@@ -134,7 +140,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const uint64_t bdesc = make_smem_desc(vb + k * (16 * 128), BKV * 128, 1024, 2);
           umma_f16(tmem_base + O_COL, adesc, bdesc, idesc_o, (j | k) != 0 ? 1u : 0u);
         }
-        umma_commit(pv_done);
+        umma_commit(&pv_done[ps]);
         umma_commit(&v_empty[st]);
         return true;
       };
@@ -169,7 +175,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     float m_ref = -INFINITY, l = 0.f;  // m_ref: the (possibly stale) maximum the exponentials are taken against
     const unsigned char* kvalid = p.key_valid ? p.key_valid + (size_t)b * p.Sk : nullptr;
     const float* bias_row = (p.bias && q < p.Sq) ? p.bias + (size_t)q * p.Sk : nullptr;
-    uint8_t* prow = sP + half * (BQ * 128) + (row >> 3) * 1024 + (row & 7) * 128;
+    uint8_t* prow0 = sP + half * (BQ * 128) + (row >> 3) * 1024 + (row & 7) * 128;
     bool ok = true;
     for (int j = 0; j < nkb && ok; ++j) {
       const int k0 = j * BKV;
@@ -221,10 +227,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         m_ref = mx;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // P_{j-1} consumed and O holds blocks < j: safe to overwrite P and to rescale O
-      if (!mbar_wait(pv_done, ((uint32_t)j & 1u) ^ 1u, p.status, 121)) { ok = false; break; }
+      // the P buffer of this block is free once PV_{j-PS} has retired
+      uint8_t* prow = prow0 + (j % PS) * P_BYTES;
+      if (!mbar_wait(&pv_done[j % PS], ((uint32_t)(j / PS) & 1u) ^ 1u, p.status, 121)) { ok = false; break; }
       tc_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // O holds blocks < j only after PV_{j-1} has retired (with one buffer that is the wait above)
+        if (PS > 1 && !mbar_wait(&pv_done[(j - 1) % PS], (uint32_t)((j - 1) / PS) & 1u, p.status, 125)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
         for (int c = 0; c < HC; c += 32) {
           uint32_t r[32];
@@ -255,7 +265,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc_fence_before();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[j % PS]);
     }
     // row sum = sum over the two halves
     if (ok) {
@@ -265,7 +275,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ok = mbar_wait(x_bar, (uint32_t)nkb & 1u, p.status, 124);
       if (ok) l += xb[(half ^ 1) * 128 + row];
     }
-    if (ok && nkb > 0) ok = mbar_wait(pv_done, (uint32_t)(nkb - 1) & 1u, p.status, 122);
+    if (ok && nkb > 0) ok = mbar_wait(&pv_done[(nkb - 1) % PS], (uint32_t)((nkb - 1) / PS) & 1u, p.status, 122);
     if (!ok) *abort_flag = 1;
     if (ok) {
       tc_fence_after();
@@ -313,7 +323,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 template <int HD>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p,
                cudaStream_t s) {
-  constexpr size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKV * HD * 2 + (size_t)BQ * BKV * 2 + 1024 + 256 + 2048;
+  constexpr size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKV * HD * 2 + (HD == 64 ? 2 : 1) * (size_t)BQ * BKV * 2 + 1024 + 256 + 2048;
   static bool configured = false;
   if (!configured) {
     NB_CUDA(cudaFuncSetAttribute(fa_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
