@@ -91,6 +91,10 @@ class ParamArena:
     def zero_grad(self):
         self.grd.zero_()
 
+    def layout(self):
+        """(name, element offset, element count) of every parameter, in arena order."""
+        return [(name, o, n) for name, _, o, n in self.entries]
+
     def bump_versions(self, shadow_fresh: bool):
         for _, p, _, _ in self.entries:
             p.version += 1
