@@ -312,3 +312,11 @@ class TD3Trainer:
                 t.polyak_from(o, cfg.tau)
             out["actor_loss"] = -q1v.float().mean()
         return out
+
+
+def DDPGTrainer(cfg: TD3Config = None, device="cpu") -> TD3Trainer:
+    """DDPG = TD3 without target-policy smoothing and without the delayed actor update; the twin critic stays (its
+    minimum only makes the target more conservative).  (noeira/deep_agents/ddpg/)"""
+    import dataclasses
+    cfg = dataclasses.replace(cfg or TD3Config(), policy_noise=0.0, noise_clip=0.0, policy_delay=1)
+    return TD3Trainer(cfg, device)
