@@ -87,6 +87,29 @@ class Optimizer:
         self._set(H_B2T, d.get("b2t", 1.0))
 
 
+def adamw_update_cpu(val, g, m, v, flags, lr, b1, b2, eps, wd, b1t, b2t, masks=None):
+    """In-place AdamW on (views of) fp32 tensors; ``flags`` per element: bit 0 = weight decay, bit 1 = frozen.
+    One arithmetic for every caller (arena optimizer, ZeRO shards): identical inputs give identical bits.
+    ``masks`` = cached ``(all_live, live, decay)`` for the same flags."""
+    if masks is None:
+        live = (flags & 2) == 0
+        masks = (bool(live.all()), live, ((flags & 1) != 0).to(val.dtype))
+    all_live, live, decay = masks
+    if not all_live:
+        g = g * live.to(g.dtype)
+        m_old, v_old, val_old = m.clone(), v.clone(), val.clone()
+    m.mul_(b1).add_(g, alpha=1 - b1)
+    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    denom = (v / (1 - b2t)).sqrt_().add_(eps)
+    if wd != 0.0:
+        val.addcmul_(val, decay, value=-lr * wd)
+    val.addcdiv_(m, denom, value=-lr / (1 - b1t))
+    if not all_live:
+        frozen = ~live
+        m[frozen], v[frozen], val[frozen] = m_old[frozen], v_old[frozen], val_old[frozen]
+    return masks
+
+
 class AdamW(Optimizer):
     def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, **kw):
         super().__init__(named_params, lr, **kw)
@@ -113,16 +136,16 @@ class AdamW(Optimizer):
         h[H_B1T] *= h[H_BETA1]
         h[H_B2T] *= h[H_BETA2]
         lr, b1, b2, eps, wd, b1t, b2t, gs = (float(h[i]) for i in (H_LR, H_BETA1, H_BETA2, H_EPS, H_WD, H_B1T, H_B2T, H_GSCALE))
-        flags = a.row_flags.repeat_interleave(32)[: a.numel]
-        g = a.grd * gs
-        live = (flags & 2) == 0
-        m = torch.where(live, b1 * a.m + (1 - b1) * g, a.m)
-        v = torch.where(live, b2 * a.v + (1 - b2) * g * g, a.v)
-        upd = (m / (1 - b1t)) / ((v / (1 - b2t)).sqrt() + eps)
-        upd = upd + torch.where((flags & 1) != 0, wd * a.val, torch.zeros_like(a.val))
-        a.val.copy_(torch.where(live, a.val - lr * upd, a.val))
-        a.m.copy_(m)
-        a.v.copy_(v)
+        key = a.row_flags._version
+        if getattr(self, "_cpu_masks_key", None) != key:
+            flags = a.row_flags.repeat_interleave(32)[: a.numel]
+            self._cpu_live = (flags & 2) == 0
+            self._cpu_all_live = bool(self._cpu_live.all())
+            self._cpu_decay = ((flags & 1) != 0).to(a.val.dtype)
+            self._cpu_masks_key = key
+        g = a.grd if gs == 1.0 else a.grd * gs
+        adamw_update_cpu(a.val, g, a.m, a.v, None, lr, b1, b2, eps, wd, b1t, b2t,
+                         masks=(self._cpu_all_live, self._cpu_live, self._cpu_decay))
         if zero_grad:
             a.grd.zero_()
         a.bump_versions(shadow_fresh=False)

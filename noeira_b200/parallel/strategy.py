@@ -21,7 +21,7 @@ import math
 import torch
 
 from ..nn.arena import PARAM_ALIGN
-from ..nn.optim import H_B1T, H_B2T, H_BETA1, H_BETA2, H_EPS, H_GSCALE, H_LR, H_T, H_WD, Optimizer
+from ..nn.optim import H_B1T, H_B2T, H_BETA1, H_BETA2, H_EPS, H_GSCALE, H_LR, H_T, H_WD, Optimizer, adamw_update_cpu
 
 
 def shard_range(numel: int, world: int, rank: int):
@@ -106,14 +106,8 @@ class Zero1(DataParallel):
         if n <= 0:
             return
         flags = a.row_flags.repeat_interleave(PARAM_ALIGN)[lo:hi]
-        g = self._gshard[:n] * gs
-        live = (flags & 2) == 0
-        m = torch.where(live, b1 * a.m[lo:hi] + (1 - b1) * g, a.m[lo:hi])
-        v = torch.where(live, b2 * a.v[lo:hi] + (1 - b2) * g * g, a.v[lo:hi])
-        upd = (m / (1 - b1t)) / ((v / (1 - b2t)).sqrt() + eps)
-        upd = upd + torch.where((flags & 1) != 0, wd * a.val[lo:hi], torch.zeros_like(upd))
-        a.val[lo:hi] = torch.where(live, a.val[lo:hi] - lr * upd, a.val[lo:hi])
-        a.m[lo:hi], a.v[lo:hi] = m, v
+        g = self._gshard[:n] if gs == 1.0 else self._gshard[:n] * gs
+        adamw_update_cpu(a.val[lo:hi], g, a.m[lo:hi], a.v[lo:hi], flags, lr, b1, b2, eps, wd, b1t, b2t)
 
     def step(self):
         a = self.opt.arena
