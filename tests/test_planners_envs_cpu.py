@@ -57,3 +57,28 @@ def test_classic_envs_dynamics_and_reset():
         v = mc.state[:, 1]
         mc.step_batch(torch.where(v >= 0, 1.0, -1.0)[:, None])
     assert mc.ep_stats[1] >= 4 and mc.ep_stats[0] > 4 * 50
+
+
+def test_ilqr_swings_pendulum_to_target():
+    from noeira_b200.planners import ILQR
+    dt = 0.05
+
+    def f(x, u):       # damped pendulum, θ = 0 hanging down
+        th, thd = x[0], x[1]
+        thdd = -9.81 * torch.sin(th) - 0.1 * thd + u[0]
+        return torch.stack([th + dt * thd, thd + dt * thdd])
+
+    target = torch.tensor([1.0, 0.0], dtype=torch.float64)
+    cost = lambda x, u: 0.5 * dt * (1e-2 * (u * u).sum() + 0.1 * ((x - target) ** 2).sum())
+    final = lambda x: 50.0 * ((x - target) ** 2).sum()
+    pl = ILQR(f, cost, final, horizon=40, act_dim=1)
+    X0, J0 = pl.rollout(torch.zeros(2, dtype=torch.float64), torch.zeros(40, 1, dtype=torch.float64))
+    U, X, J = pl.plan(torch.zeros(2), iterations=30)
+    assert J < 0.05 * float(J0) and abs(float(X[-1, 0]) - 1.0) < 0.05 and abs(float(X[-1, 1])) < 0.2
+    # linear-quadratic problem: one iteration reaches the optimum (the Riccati solution)
+    A, B = torch.tensor([[1.0, 0.1], [0.0, 1.0]], dtype=torch.float64), torch.tensor([[0.0], [0.1]], dtype=torch.float64)
+    lin = ILQR(lambda x, u: A @ x + B @ u, lambda x, u: (x * x).sum() + 0.1 * (u * u).sum(), lambda x: 10 * (x * x).sum(), 20, 1, reg=1e-9)
+    x0 = torch.tensor([1.0, 0.0])
+    _, _, J1 = lin.plan(x0, iterations=1)
+    _, _, J5 = lin.plan(x0, iterations=5)
+    assert abs(J1 - J5) < 1e-6 * max(1.0, J5)
