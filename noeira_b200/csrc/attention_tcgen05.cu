@@ -81,7 +81,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       mbar_init(&p_full[i], 8);
       mbar_init(&pv_done[i], 1);
     }
-    mbar_init(x_bar, 256);
+    mbar_init(x_bar, 8);        // one arrival per softmax warp (256 per-thread arrivals serialise on the barrier word)
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmQ);
@@ -179,7 +179,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     bool ok = true;
     for (int j = 0; j < nkb && ok; ++j) {
       const int k0 = j * BKV;
-      if (*abort_flag || !mbar_wait(s_full, (uint32_t)j & 1u, p.status, 120)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, !*abort_flag && mbar_wait(s_full, (uint32_t)j & 1u, p.status, 120))) { ok = false; break; }
       tc_fence_after();
       // my 64 scores → registers with ONE wait, then hand the S buffer back to the tensor core
       float s[64];
@@ -216,8 +216,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // row maximum = max over the two halves
       float* xb = sh_x + (j & 1) * 256;
       xb[half * 128 + row] = mx;
-      mbar_arrive(x_bar);
-      if (!mbar_wait(x_bar, (uint32_t)j & 1u, p.status, 123)) { ok = false; break; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_bar);
+      if (!__all_sync(0xffffffffu, mbar_wait(x_bar, (uint32_t)j & 1u, p.status, 123))) { ok = false; break; }
       mx = fmaxf(mx, xb[(half ^ 1) * 128 + row]);
       // lazy rescale: keep the old reference unless the maximum grew by more than the threshold
       float alpha = 1.f;
@@ -229,11 +230,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       // the P buffer of this block is free once PV_{j-PS} has retired
       uint8_t* prow = prow0 + (j % PS) * P_BYTES;
-      if (!mbar_wait(&pv_done[j % PS], ((uint32_t)(j / PS) & 1u) ^ 1u, p.status, 121)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[j % PS], ((uint32_t)(j / PS) & 1u) ^ 1u, p.status, 121))) { ok = false; break; }
       tc_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // O holds blocks < j only after PV_{j-1} has retired (with one buffer that is the wait above)
-        if (PS > 1 && !mbar_wait(&pv_done[(j - 1) % PS], (uint32_t)((j - 1) / PS) & 1u, p.status, 125)) { ok = false; break; }
+        if (PS > 1 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) % PS], (uint32_t)((j - 1) / PS) & 1u, p.status, 125))) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < HC; c += 32) {
@@ -271,11 +272,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (ok) {
       float* xb = sh_x + (nkb & 1) * 256;
       xb[half * 128 + row] = l;
-      mbar_arrive(x_bar);
-      ok = mbar_wait(x_bar, (uint32_t)nkb & 1u, p.status, 124);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_bar);
+      ok = __all_sync(0xffffffffu, mbar_wait(x_bar, (uint32_t)nkb & 1u, p.status, 124));
       if (ok) l += xb[(half ^ 1) * 128 + row];
     }
-    if (ok && nkb > 0) ok = mbar_wait(&pv_done[(nkb - 1) % PS], (uint32_t)((nkb - 1) / PS) & 1u, p.status, 122);
+    if (ok && nkb > 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(nkb - 1) % PS], (uint32_t)((nkb - 1) / PS) & 1u, p.status, 122));
     if (!ok) *abort_flag = 1;
     if (ok) {
       tc_fence_after();

@@ -180,6 +180,8 @@ class Linear(Module):
         if self.act is not None and not dy_is_pre:
             sv = self._saved if self._saved.dtype == torch.bfloat16 else self._saved.to(torch.bfloat16)
             dy2 = act_backward(dy2.contiguous(), sv[:, : dy2.shape[1]].contiguous() if sv.shape[1] != dy2.shape[1] else sv, self.act)
+            if (dy2.stride(0) * 2) % 16 != 0:           # narrow outputs (e.g. 6 actions): back to a 16-byte row pitch
+                dy2 = _pad_rows(dy2)
         n = self.out_dim
         dyv = dy2[:, :n]
         if not self.weight.frozen:
