@@ -3,8 +3,9 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29512 \\
         benchmarks/bench_allreduce.py [--max-mb 256] [--adam]
 
-Roofline: an all-reduce must move (N-1)/N · bytes in each direction per GPU; at the measured 770 GB/s per
-direction that is the target time.  `--adam` times the fused reduce+AdamW kernel against NCCL all-reduce followed
+Roofline: with reduction inside the switch an all-reduce must move (N-1)/N · bytes in each direction per GPU
+(`*_frac_of_roofline`); without it (reduce-scatter then all-gather over peer loads, what these kernels do) the
+bandwidth-optimal bound is 2(N-1)/N · bytes per direction (`*_frac_of_p2p_bound`); both at the measured 770 GB/s.  `--adam` times the fused reduce+AdamW kernel against NCCL all-reduce followed
 by the single-GPU arena AdamW kernel.
 """
 import argparse
@@ -100,9 +101,11 @@ def main():
             t = timed(lambda: fused(algo, n, args.adam))
             row[name + "_us"] = round(t * 1e3, 2)
             row[name + "_frac_of_roofline"] = round(roof_ms / t, 3)
+            row[name + "_frac_of_p2p_bound"] = round(2 * roof_ms / t, 3)
         t = timed(lambda: nccl(n, args.adam))
         row["nccl_us"] = round(t * 1e3, 2)
         row["nccl_frac_of_roofline"] = round(roof_ms / t, 3)
+        row["nccl_frac_of_p2p_bound"] = round(2 * roof_ms / t, 3)
         row["busbw_two_shot_gbs"] = round(2 * (world - 1) / world * size / (row["two_shot_us"] * 1e-6) / 1e9, 1)
         if rank == 0:
             print(json.dumps(row), flush=True)
