@@ -73,3 +73,86 @@ class StoreReplay:
 
     def sample(self, batch):
         return self.gather(self.uniform_indices(batch))
+
+
+class StoreReplayGpu:
+    """Device ring of packed transitions ``[s | a | r | s' | d]`` driven entirely by kernels (``csrc/replay.cu``): the write
+    offset, the size and the sampling counter live in a device ``meta`` block, so ``store`` → ``sample`` → update can be
+    captured in one CUDA graph.  Sampling: ``"uniform"``, ``"ere"`` (pass the fraction ``eta^(k·1000/K)``), ``"per"`` (sum
+    tree; ``update_priorities`` after the TD errors are known).  (noeira/data/replay_gpu.mojo:54-330)"""
+
+    def __init__(self, capacity: int, obs_dim: int, act_dim: int, demo_prefix: int = 0, seed: int = 0, per_alpha: float = 0.6,
+                 per_beta: float = 0.4, device="cuda"):
+        import ctypes
+        from .._native import cuda_lib
+        self._c, self._lib = ctypes, cuda_lib()
+        self.capacity, self.obs_dim, self.act_dim, self.base = capacity, obs_dim, act_dim, demo_prefix
+        self.width = 2 * obs_dim + act_dim + 2
+        self.device = torch.device(device)
+        self.buf = torch.zeros(capacity, self.width, device=self.device)
+        self.meta = torch.tensor([demo_prefix, demo_prefix, 0], dtype=torch.int64, device=self.device)
+        self.seed, self.per_alpha, self.per_beta = seed, per_alpha, per_beta
+        self.leaves = 1
+        while self.leaves < capacity:
+            self.leaves *= 2
+        self.tree = torch.zeros(2 * self.leaves, device=self.device)
+        self._idx, self._out, self._w = {}, {}, {}
+
+    def _ptr(self, t):
+        from .._native import ptr
+        return ptr(t)
+
+    def store_batch(self, s, a, r, sp, d):
+        from .._native import check, stream_ptr
+        rows = torch.cat([s.float(), a.float(), r.float().reshape(-1, 1), sp.float(), d.float().reshape(-1, 1)], 1).contiguous()
+        c = self._c
+        n = rows.shape[0]
+        if self.per_alpha > 0:
+            # new transitions enter with the running maximum priority: here priority 1 before the exponent
+            start = self.meta[0:1].clone()
+        check(self._lib.nb_replay_store(self._ptr(self.buf), c.c_int(self.width), c.c_longlong(self.capacity), self._ptr(self.meta),
+                                        self._ptr(rows), c.c_int(n), c.c_int(self.base), stream_ptr()), "replay_store")
+        if self.per_alpha > 0:
+            ring = self.capacity - self.base
+            idx = (start - self.base + torch.arange(n, device=self.device)) % ring + self.base
+            self.update_priorities(idx, torch.ones(n, device=self.device))
+
+    def indices(self, batch: int, mode: str = "uniform", ere_frac: float = 1.0, c_min: int = 5000):
+        from .._native import check, stream_ptr
+        c = self._c
+        idx = self._idx.setdefault(batch, torch.zeros(batch, dtype=torch.int64, device=self.device))
+        if mode == "per":
+            w = self._w.setdefault(batch, torch.zeros(batch, device=self.device))
+            check(self._lib.nb_per_sample(self._ptr(self.tree), c.c_longlong(self.leaves), self._ptr(idx), self._ptr(w),
+                                          c.c_int(batch), self._ptr(self.meta), c.c_ulonglong(self.seed),
+                                          c.c_float(self.per_beta), stream_ptr()), "per_sample")
+            return idx, w / w.max()
+        check(self._lib.nb_replay_indices(self._ptr(idx), c.c_int(batch), self._ptr(self.meta), c.c_ulonglong(self.seed),
+                                          c.c_int(0 if mode == "uniform" else 1), c.c_float(ere_frac), c.c_longlong(c_min),
+                                          c.c_longlong(self.capacity), c.c_int(self.base), stream_ptr()), "replay_indices")
+        return idx, None
+
+    def update_priorities(self, idx, td_abs):
+        from .._native import check, stream_ptr
+        c = self._c
+        check(self._lib.nb_per_update(self._ptr(self.tree), c.c_longlong(self.leaves), self._ptr(idx.contiguous()),
+                                      self._ptr(td_abs.float().contiguous()), c.c_int(idx.numel()), c.c_float(self.per_alpha),
+                                      c.c_float(1e-6), stream_ptr()), "per_update")
+
+    def gather(self, idx):
+        from .._native import check, stream_ptr
+        c = self._c
+        b = idx.numel()
+        out = self._out.setdefault(b, torch.zeros(b, self.width, device=self.device))
+        check(self._lib.nb_replay_gather(self._ptr(self.buf), c.c_int(self.width), self._ptr(idx), self._ptr(out), c.c_int(b),
+                                         stream_ptr()), "replay_gather")
+        O, A = self.obs_dim, self.act_dim
+        return out[:, :O], out[:, O:O + A], out[:, O + A], out[:, O + A + 1: 2 * O + A + 1], out[:, 2 * O + A + 1]
+
+    def sample(self, batch: int, mode: str = "uniform", **kw):
+        idx, w = self.indices(batch, mode, **kw)
+        return self.gather(idx), idx, w
+
+    @property
+    def size(self) -> int:
+        return int(self.meta[1])
