@@ -32,7 +32,7 @@ def test_ring_store_wraps_and_keeps_demo_prefix():
     assert not torch.equal(a1, i2)                         # the device counter advances the stream
     e, _ = rb.indices(2048, "ere", ere_frac=0.2, c_min=10)
     recent = rb.buf[e, 0]
-    assert recent.min() >= 128 - 18 - 1                    # only the most recent ~18 of 90 online transitions
+    assert recent.min() >= 128 - 20 and recent.max() == 127    # only the most recent 20 = 0.2 x size transitions
 
 
 def test_per_sum_tree_matches_priorities():
