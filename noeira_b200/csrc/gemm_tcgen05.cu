@@ -47,7 +47,17 @@ struct GemmParams {
   const float* bias;
   const __nv_bfloat16* aux;
   unsigned int* status;
+  // implicit-GEMM convolution (conv != 0): A is never materialised; the producer reads activation patches of the NHWC
+  // input through a 4-D tensor map (c, w, h, b), one box of conv_bw output pixels x 64 channels per TMA
+  int conv, conv_c, conv_ow, conv_oh, conv_kw, conv_pad, conv_bw;
 };
+
+__device__ __forceinline__ void tma_load_4d_g(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 
 // MUFU tanh: one instruction, max relative error 2^-11 — below bf16 resolution of the stored result.
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -306,7 +316,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-          if (!p.a_mn) {
+          if (p.conv) {
+            // k-block kb = 64 channels [c0, c0+64) of filter tap (kh, kw); the 128 output pixels of the tile are
+            // 128 / bw runs of bw consecutive pixels of one output row (bw divides OW and 128), stride 1:
+            // input pixel = output pixel + tap − pad; coordinates outside the image read the zero fill
+            const int kpos = kb * BK, tap = kpos / p.conv_c, c0 = kpos - tap * p.conv_c;
+            const int kh = tap / p.conv_kw, kw = tap - kh * p.conv_kw;
+            const int bw = p.conv_bw, per_img = p.conv_oh * p.conv_ow;
+            for (int i = 0; i < BM / bw; ++i) {
+              const int m0 = mb * BM + i * bw;
+              const int bimg = m0 / per_img, rem = m0 - bimg * per_img;
+              const int oh = rem / p.conv_ow, ow0 = rem - oh * p.conv_ow;
+              tma_load_4d_g(sa + i * bw * 128, &tmA, &full_bar[stage], c0, ow0 - p.conv_pad + kw, oh - p.conv_pad + kh, bimg);
+            }
+          } else if (!p.a_mn) {
             tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, mb * BM);
           } else {
 #pragma unroll
@@ -599,6 +622,7 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
   p.out_f32 = out_f32; p.accumulate = accumulate; p.act = act; p.dact = dact;
   p.alpha = alpha;
   p.D = D; p.bias = bias; p.aux = (const __nv_bfloat16*)aux; p.status = status;
+  p.conv = 0;
   // workspace layout: [NB_GEMM_WS_COUNTERS u32 tile counters (zero at rest)] [fp32 partial tiles]
   long long ws_bytes = 0;
   p.ws = nullptr;
@@ -617,6 +641,50 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
     case 16: return launch<16, 8>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
     default: return NB_ERR_BAD_ARG;
   }
+}
+
+// Implicit-GEMM convolution forward, stride 1: y[B·OH·OW, OC] = epi(patches(x) · W), x NHWC bf16 [B, H, W, C] with
+// C % 64 == 0, W in GEMM layout [KH·KW·C, OC] (row pitch ldw).  OW must have a power-of-two factor bw >= 8 (the run
+// length of one TMA box).  Output spatial size: OH = H + 2·pad − KH + 1, OW likewise.
+int nb_conv_implicit_fwd(const void* x, const void* Wt, void* y, int B, int H, int Wd, int C, int OC, int KH, int KW, int pad,
+                         int ldw, int ldy, const float* bias, int act, const void* residual, int ld_res,
+                         unsigned int* status, void* stream) {
+  const int OH = H + 2 * pad - KH + 1, OW = Wd + 2 * pad - KW + 1;
+  if (B <= 0 || OH <= 0 || OW <= 0 || C % 64 || OC <= 0) return NB_ERR_BAD_ARG;
+  int bw = 1;
+  while (bw < 128 && OW % (bw * 2) == 0) bw *= 2;
+  if (bw < 8) return NB_ERR_BAD_ARG;   // every box then starts on a 1024-byte swizzle atom of the A tile
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return NB_ERR_NO_DRIVER_SYMBOL;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return NB_ERR_UNALIGNED;
+  CUtensorMap tmA, tmB;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Wd, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)Wd * C * 2, (cuuint64_t)H * Wd * C * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)bw, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return NB_ERR_TENSORMAP;
+  }
+  const int M = B * OH * OW, K = KH * KW * C;
+  int BN = 128;
+  if (OC <= 64 || (long long)ceil_div(M, BM) * ceil_div(OC, 128) < sm_count()) BN = 64;
+  int rc = make_tmap_bf16(&tmB, Wt, OC, K, ldw, 64, BK);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = OC; p.K = K;
+  p.a_mn = 0; p.b_mn = 1;
+  p.ldd = ldy; p.ld_aux = ld_res;
+  p.out_f32 = 0; p.accumulate = 0; p.act = act; p.dact = residual ? NB_AUX_ADD : 0;
+  p.alpha = 1.f;
+  p.D = y; p.bias = bias; p.aux = (const __nv_bfloat16*)residual; p.status = status;
+  p.ws = nullptr; p.tile_ctr = nullptr;
+  p.conv = 1; p.conv_c = C; p.conv_ow = OW; p.conv_oh = OH; p.conv_kw = KW; p.conv_pad = pad; p.conv_bw = bw;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (BN == 128) return launch<128, 6>(tmA, tmB, p, 0, 0, s);
+  return launch<64, 8>(tmA, tmB, p, 0, 0, s);
 }
 
 }  // extern "C"

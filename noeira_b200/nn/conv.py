@@ -36,6 +36,7 @@ class Conv2D(Module):
         self.ic, self.oc, self.k, self.stride, self.pad, self.relu = ic, oc, k, stride, pad, relu
         self.icp = (ic + 7) // 8 * 8          # channels as stored (stem: 3 → 8, extra channels are zero)
         self.need_input_grad = need_input_grad
+        self.implicit_gemm = True
         self.weight = self.add_param("weight", (k * k * self.icp, oc), decay=True, init=Kaiming(), fan_in=ic * k * k,
                                      fan_out=oc)
         if self.icp != ic:
@@ -46,6 +47,27 @@ class Conv2D(Module):
         self.weight.to_file = lambda t: t.view(KK, KK, icp, oc)[:, :, :ic, :].permute(3, 2, 0, 1).contiguous()
         self.weight.from_file = lambda t: torch.nn.functional.pad(t.reshape(oc, ic, KK, KK).permute(2, 3, 1, 0),
                                                                   (0, 0, 0, icp - ic)).reshape(KK * KK * icp, oc)
+
+    def _implicit_ok(self, C, OW):
+        if self.stride != 1 or C % 64 or not self.implicit_gemm:
+            return False
+        bw = 1
+        while bw < 128 and OW % (bw * 2) == 0:
+            bw *= 2
+        return bw >= 8
+
+    def _patches(self):
+        """Patch matrix [B·OH·OW, KH·KW·C] of the saved input (backward of the implicit-GEMM forward)."""
+        x = self._xin
+        B, H, W, C = x.shape
+        OH, OW = self.out_hw(H, W)
+        K = self.k * self.k * C
+        if self.k == 1 and self.pad == 0:
+            return x.reshape(B * OH * OW, C)
+        col = torch.empty(B * OH * OW, K, device=x.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_im2col(ptr(x), ptr(col), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, self.k, self.stride,
+                                                                               self.pad, OH, OW, K)), stream_ptr()), "im2col")
+        return col
 
     def out_hw(self, H, W):
         return (H + 2 * self.pad - self.k) // self.stride + 1, (W + 2 * self.pad - self.k) // self.stride + 1
@@ -63,6 +85,20 @@ class Conv2D(Module):
             self._y = torch.relu(y) if self.relu else y
             return self._y
         M, K = B * OH * OW, self.k * self.k * C
+        if self._implicit_ok(C, OW):
+            # implicit GEMM: the GEMM's TMA producer reads the patches straight from x (no patch matrix in memory);
+            # the backward pass rebuilds the patch matrix only if a weight gradient is needed
+            xc = x if x.is_contiguous() else x.contiguous()
+            y = torch.empty(M, self.weight.shadow.shape[1], device=x.device, dtype=torch.bfloat16)
+            from ..ops.status import device_status
+            from ..ops.gemm import ACT
+            check(cuda_lib().nb_conv_implicit_fwd(ptr(xc), ptr(self.weight.shadow), ptr(y), *(ctypes.c_int(v) for v in (
+                B, H, W, C, self.oc, self.k, self.k, self.pad, self.weight.shadow.stride(0), y.stride(0))),
+                ptr(self.bias.storage if self.bias is not None else None), ctypes.c_int(ACT["relu" if self.relu else None]),
+                None, ctypes.c_int(0), ptr(device_status(x.device)), stream_ptr()), "conv_implicit_fwd")
+            self._col, self._xin, self._y = None, xc, y
+            return y[:, : self.oc].reshape(B, OH, OW, self.oc) if y.shape[1] != self.oc else y.view(B, OH, OW, self.oc)
+        self._xin = None
         if self.k == 1 and self.stride == 1 and self.pad == 0:
             col = x.reshape(M, C)
         else:
@@ -100,7 +136,8 @@ class Conv2D(Module):
             from .layers import act_backward
             d2 = act_backward(d2.contiguous(), self._y[:, : self.oc].contiguous() if self._y.shape[1] != self.oc else self._y, "relu")
         if not self.weight.frozen:
-            ops.gemm(self._col, d2, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=self.oc)
+            col = self._col if self._col is not None else self._patches()
+            ops.gemm(col, d2, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=self.oc)
             if self.bias is not None:
                 colsum_into(d2, self.bias.grad_storage, self.oc)
         if not self.need_input_grad:
@@ -115,7 +152,7 @@ class Conv2D(Module):
         return dx
 
     def _release(self):
-        self._col = self._y = None
+        self._col = self._y = self._xin = None
 
 
 class BatchNorm2D(Module):
