@@ -62,6 +62,7 @@ def main():
             a = nn.Conv2D(ic, oc, 3, 1, 1, bias=False).to("cuda")
             b = nn.Conv2D(ic, oc, 3, 1, 1, bias=False).to("cuda")
             b.implicit_gemm = False
+            a.force_implicit = True
             x = torch.randn(16, H, W, ic, device="cuda").bfloat16()
             ti = timeit(lambda: a.forward(x), args.iters, flush)
             tp = timeit(lambda: b.forward(x), args.iters, flush)
