@@ -50,6 +50,7 @@ class PPOConfig:
     max_grad_norm: float = 0.0
     seed: int = 0
     use_cuda_graphs: bool = True
+    fused_mlp: bool = True     # actor / critic forward as one fused three-layer kernel when the shapes allow it
 
 
 def make_actor(obs_dim, act_dim, hidden, log_std_init=-0.5):
@@ -122,18 +123,38 @@ class PPOTrainer:
         # metrics: [0] Σ policy loss [1] Σ KL [2] Σ clipfrac [3] Σ entropy [4] samples [5] Σ value loss·MB
         self.metrics = torch.zeros(8, **f)
         self._graphs = {}
+        self._fused = {}
+        if cfg.fused_mlp and self.device.type == "cuda":
+            from ..ops.mlp import fusable
+            for net in (self.actor, self.critic):
+                self._fused[id(net)] = fusable(*self._layers(net))
         self._graph_launches = {}
         self.iteration = 0
         self.env.reset_batch()
         self.obs_buf[0].copy_(self.env.obs_bf16)
 
     # ------------------------------------------------------------------ phases
+    def _layers(self, net):
+        a, b, c = net.mods
+        return a, b, (c.lin if hasattr(c, "lin") else c)
+
+    def _forward(self, net, x, save):
+        """Forward of the actor or the critic: the fused three-layer kernel when it applies, else layer by layer."""
+        if self._fused.get(id(net)):
+            from ..ops.mlp import mlp3_forward
+            l1, l2, l3 = self._layers(net)
+            y = mlp3_forward(x, l1, l2, l3, save=save)
+            if hasattr(net.mods[2], "lin"):
+                net.mods[2]._mu = y
+            return y
+        return net.forward(x)
+
     def _rollout(self):
         cfg, env, lib = self.cfg, self.env, self.lib
         head = self.actor.mods[2]
         for t in range(cfg.rollout_len):
             obs = self.obs_buf[t]
-            mu = self.actor.forward(obs)
+            mu = self._forward(self.actor, obs, save=False)
             check(lib.nb_ppo_sample(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), None,
                                     ctypes.c_int(0), ptr(self.act_buf[t]), ctypes.c_int(self.AP),
                                     ptr(self.env_action), ctypes.c_int(self.AP), ptr(self.logp_buf[t]),
@@ -176,14 +197,14 @@ class PPOTrainer:
         # ---- critic forward / backward on a side stream, overlapping the actor chain
         br = self._critic_branch
         with br:
-            v = self.critic.forward(self.mb_obs)
+            v = self._forward(self.critic, self.mb_obs, save=True)
             check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
                                         ptr(self.partials_v), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
                                         ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
             self.critic.vjp(self.dv[:, :1])
             self._critic_pg.join()
         # ---- actor
-        mu = self.actor.forward(self.mb_obs)
+        mu = self._forward(self.actor, self.mb_obs, save=True)
         check(lib.nb_ppo_objective(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(self.mb_act),
                                    ctypes.c_int(self.AP), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.adv_stats),
                                    ptr(self.dmu), ctypes.c_int(self.AP), ptr(self.partials), ptr(self.partials2),

@@ -1,0 +1,299 @@
+// Fused forward of a three-layer MLP  out = (act(act(X W1 + b1) W2 + b2)) W3 + b3  with hidden width 256:
+// one CTA per 128 rows keeps the hidden activations on chip — TMEM accumulators, bf16 A-operand tile in shared
+// memory — so the actor / critic forward of the RL trainers is ONE launch instead of three GEMM launches whose
+// run time is launch latency and pipeline fill (13 us each for 16384 x 256 x 256).  The hidden activations are
+// optionally written to global memory (bf16) for the backward pass.
+//   warp 0      TMA: X tile and W1, then W2 in four 64-row k-blocks through a 2-stage ring
+//   warp 1      MMA issuer: layer 1 (K <= 64), layer 2 (K = 256, N = 256), layer 3 (K = 256, N = 16)
+//   warps 2..5  epilogue: thread = row; bias + activation, bf16 tile for the next layer in the 128-byte-swizzled
+//               K-major layout, final fp32 output; also stage W3ᵀ into shared memory at start
+// Weights are [IN, OUT] row-major bf16 (the framework's Linear layout): W1, W2 are MN-major B operands, W3 (narrow,
+// OUT <= 16) is transposed into a K-major tile by the epilogue threads.
+// Reference counterpart: none as one kernel (the reference issues cuBLAS GEMMs + bias / activation kernels per layer,
+// noeira/nn/primitives/linear.mojo:1295-1387); the captured actor step it optimises is noeira_max/README.md's
+// "MLP actor inference 17-256-256-6: 21.5 us eager / 12.7 captured".
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_api.h"
+
+namespace {
+using namespace nb;
+
+constexpr int HID = 256;
+constexpr int ROWS = 128;
+constexpr int N3P = 16;
+constexpr int MLP_THREADS = 192;
+
+struct MlpParams {
+  int M, k0, n3;            // rows, input width (<= 64), real output width (<= 16)
+  int ld_w3, ld_out, ld_h;  // pitches in elements
+  int act;                  // NB_ACT_TANH or NB_ACT_RELU
+  const __nv_bfloat16* w3;  // [HID, ld_w3]
+  const float *b1, *b2, *b3;
+  float* out;               // [M, ld_out] fp32
+  __nv_bfloat16 *h1, *h2;   // optional [M, ld_h] saves
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float act1(int act, float v) {
+  if (act == NB_ACT_TANH) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(v));
+    return y;
+  }
+  return fmaxf(v, 0.f);
+}
+
+__global__ void __launch_bounds__(MLP_THREADS, 1)
+mlp3_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW1,
+                const __grid_constant__ CUtensorMap tmW2, const MlpParams p) {
+  constexpr uint32_t X_BYTES = ROWS * 64 * 2;        // 16 KB
+  constexpr uint32_t W1_BYTES = 64 * HID * 2;        // 32 KB (64 k-rows x 256)
+  constexpr uint32_t W2_STAGE = 64 * HID * 2;        // 32 KB per k-block
+  constexpr uint32_t H_BYTES = ROWS * HID * 2;       // 64 KB, four k-blocks of 16 KB
+  constexpr uint32_t W3_BYTES = N3P * HID * 2;       // 8 KB, four k-blocks of 2 KB
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sX = smem;
+  uint8_t* sW1 = sX + X_BYTES;
+  uint8_t* sW2 = sW1 + W1_BYTES;            // 2 stages
+  uint8_t* sH = sW2 + 2 * W2_STAGE;
+  uint8_t* sW3 = sH + H_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sW3 + W3_BYTES);
+  uint64_t* x_full = bars;
+  uint64_t* w2_full = bars + 1;    // [2]
+  uint64_t* w2_empty = bars + 3;   // [2]
+  uint64_t* acc_full = bars + 5;   // [3]
+  uint64_t* h_ready = bars + 8;    // [2]
+  uint64_t* w3_ready = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * ROWS;
+
+  if (threadIdx.x == 0) {
+    mbar_init(x_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&w2_full[i], 1);
+      mbar_init(&w2_empty[i], 1);
+      mbar_init(&h_ready[i], 4);
+    }
+    for (int i = 0; i < 3; ++i) mbar_init(&acc_full[i], 1);
+    mbar_init(w3_ready, 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmX);
+    prefetch_tensormap(&tmW1);
+    prefetch_tensormap(&tmW2);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(x_full, X_BYTES + W1_BYTES);
+      tma_load_2d(sX, &tmX, x_full, 0, row0);                                   // box {64 k, 128 rows}, zero fill past k0 / M
+      for (int h = 0; h < HID / 64; ++h) tma_load_2d(sW1 + h * 8192, &tmW1, x_full, h * 64, 0);   // boxes {64 n, 64 k}
+      for (int kb = 0; kb < HID / 64; ++kb) {
+        const int st = kb & 1;
+        if (*abort_flag || !mbar_wait(&w2_empty[st], ((uint32_t)(kb >> 1) & 1u) ^ 1u, p.status, 301)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&w2_full[st], W2_STAGE);
+        for (int h = 0; h < HID / 64; ++h) tma_load_2d(sW2 + st * W2_STAGE + h * 8192, &tmW2, &w2_full[st], h * 64, kb * 64);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc_h = make_idesc(1u, ROWS, HID, 0u, 1u);   // A K-major, B (weights) MN-major, N = 256
+      const uint32_t idesc_o = make_idesc(1u, ROWS, N3P, 0u, 0u);   // W3ᵀ staged K-major, N = 16
+      bool ok = mbar_wait(x_full, 0u, p.status, 310);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t xa = smem_u32(sX), wb = smem_u32(sW1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_base, make_smem_desc(xa + k * 32, 16, 1024, 2), make_smem_desc(wb + k * (16 * 128), 8192, 1024, 2),
+                   idesc_h, k != 0 ? 1u : 0u);
+        umma_commit(&acc_full[0]);
+      }
+      if (ok) ok = mbar_wait(&h_ready[0], 0u, p.status, 311);
+      for (int kb = 0; kb < HID / 64 && ok; ++kb) {
+        const int st = kb & 1;
+        if (!mbar_wait(&w2_full[st], (uint32_t)(kb >> 1) & 1u, p.status, 312)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ha = smem_u32(sH + kb * 16384), wb = smem_u32(sW2 + st * W2_STAGE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_base + 256, make_smem_desc(ha + k * 32, 16, 1024, 2),
+                   make_smem_desc(wb + k * (16 * 128), 8192, 1024, 2), idesc_h, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(&w2_empty[st]);
+      }
+      if (ok) umma_commit(&acc_full[1]);
+      if (ok) ok = mbar_wait(&h_ready[1], 0u, p.status, 313) && mbar_wait(w3_ready, 0u, p.status, 314);
+      if (ok) {
+        tc_fence_after();
+        for (int kb = 0; kb < HID / 64; ++kb) {
+          const uint32_t ha = smem_u32(sH + kb * 16384), wb = smem_u32(sW3 + kb * 2048);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tmem_base, make_smem_desc(ha + k * 32, 16, 1024, 2), make_smem_desc(wb + k * 32, 16, 1024, 2), idesc_o,
+                     (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&acc_full[2]);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;            // row of the tile = TMEM lane
+    const int row = row0 + r;
+    const int t = (warp - 2) * 32 + lane;         // 0..127 for cooperative loads
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    // ---- stage W3ᵀ: element (n, k) of the K-major [16 x 256] tile
+    for (int e = t; e < N3P * HID; e += 128) {
+      const int k = e / N3P, n = e - k * N3P;
+      const __nv_bfloat16 v = (n < p.n3) ? p.w3[(size_t)k * p.ld_w3 + n] : __float2bfloat16(0.f);
+      const int kb = k >> 6, kk = k & 63;
+      uint8_t* dst = sW3 + kb * 2048 + (n >> 3) * 1024 + (n & 7) * 128 + ((((kk >> 3) ^ (n & 7))) << 4) + (kk & 7) * 2;
+      *reinterpret_cast<__nv_bfloat16*>(dst) = v;
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(w3_ready);
+    bool ok = true;
+    uint8_t* hrow = sH + (r >> 3) * 1024 + (r & 7) * 128;
+    for (int layer = 0; layer < 2 && ok; ++layer) {
+      if (!__all_sync(0xffffffffu, !*abort_flag && mbar_wait(&acc_full[layer], 0u, p.status, 320 + layer))) { ok = false; break; }
+      tc_fence_after();
+      const float* bias = layer == 0 ? p.b1 : p.b2;
+      __nv_bfloat16* hsave = layer == 0 ? p.h1 : p.h2;
+      const uint32_t acc = lane_addr + (uint32_t)(layer * 256);
+#pragma unroll 1
+      for (int c0 = 0; c0 < HID; c0 += 16) {
+        uint32_t rr[16];
+        tmem_ld_32x32b_x16(acc + (uint32_t)c0, rr);
+        tmem_ld_wait();
+        uint32_t pk[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const float4 bv = bias ? __ldg(reinterpret_cast<const float4*>(bias + c0 + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          __nv_bfloat162 a = __floats2bfloat162_rn(act1(p.act, __uint_as_float(rr[j]) + bv.x),
+                                                   act1(p.act, __uint_as_float(rr[j + 1]) + bv.y));
+          __nv_bfloat162 b = __floats2bfloat162_rn(act1(p.act, __uint_as_float(rr[j + 2]) + bv.z),
+                                                   act1(p.act, __uint_as_float(rr[j + 3]) + bv.w));
+          pk[j / 2] = *reinterpret_cast<uint32_t*>(&a);
+          pk[j / 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        // k-block of the next layer's A tile = c0 / 64; 16-byte chunk index inside the 128-byte row is XOR-swizzled
+        const int kb = c0 >> 6, ch = (c0 & 63) >> 3;
+        uint8_t* base = hrow + kb * 16384;
+        *reinterpret_cast<uint4*>(base + (((ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(base + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        if (hsave && row < p.M) {
+          uint4* g = reinterpret_cast<uint4*>(hsave + (size_t)row * p.ld_h + c0);
+          g[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          g[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&h_ready[layer]);
+    }
+    if (ok && !__all_sync(0xffffffffu, !*abort_flag && mbar_wait(&acc_full[2], 0u, p.status, 322))) ok = false;
+    if (ok) {
+      tc_fence_after();
+      uint32_t rr[16];
+      tmem_ld_32x32b_x16(lane_addr, rr);
+      tmem_ld_wait();
+      if (row < p.M) {
+        for (int j = 0; j < p.n3; ++j) p.out[(size_t)row * p.ld_out + j] = __uint_as_float(rr[j]) + (p.b3 ? p.b3[j] : 0.f);
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+int tmap2d(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner, int box_outer) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return NB_ERR_NO_DRIVER_SYMBOL;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return NB_ERR_UNALIGNED;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? NB_OK : NB_ERR_TENSORMAP;
+}
+
+}  // namespace
+
+extern "C" {
+
+// x [M, k0] bf16 (row pitch ldx), W1 [k0, 256], W2 [256, 256], W3 [256, n3] bf16 row-major with the given pitches;
+// biases fp32 (may be null); out fp32 [M, ld_out]; h1 / h2 optional bf16 [M, ld_h] saves.  act: NB_ACT_TANH / NB_ACT_RELU.
+int nb_mlp3_fwd(const void* x, int ldx, const void* w1, int ldw1, const void* w2, int ldw2, const void* w3, int ldw3,
+                const float* b1, const float* b2, const float* b3, float* out, int ld_out, void* h1, void* h2, int ld_h, int M,
+                int k0, int n3, int act, unsigned int* status, void* stream) {
+  if (M <= 0 || k0 <= 0 || k0 > 64 || n3 <= 0 || n3 > N3P) return NB_ERR_BAD_ARG;
+  if (act != NB_ACT_TANH && act != NB_ACT_RELU) return NB_ERR_BAD_ARG;
+  if ((h1 || h2) && (ld_h % 8 || ((uintptr_t)h1 & 15) || ((uintptr_t)h2 & 15))) return NB_ERR_UNALIGNED;
+  CUtensorMap tx, t1, t2;
+  int rc = tmap2d(&tx, x, k0, M, ldx, 64, ROWS);
+  if (rc) return rc;
+  rc = tmap2d(&t1, w1, HID, k0, ldw1, 64, 64);
+  if (rc) return rc;
+  rc = tmap2d(&t2, w2, HID, HID, ldw2, 64, 64);
+  if (rc) return rc;
+  MlpParams p;
+  p.M = M; p.k0 = k0; p.n3 = n3;
+  p.ld_w3 = ldw3; p.ld_out = ld_out; p.ld_h = ld_h;
+  p.act = act;
+  p.w3 = (const __nv_bfloat16*)w3;
+  p.b1 = b1; p.b2 = b2; p.b3 = b3;
+  p.out = out;
+  p.h1 = (__nv_bfloat16*)h1; p.h2 = (__nv_bfloat16*)h2;
+  p.status = status;
+  constexpr size_t smem = 16384 + 32768 + 2 * 32768 + 65536 + 8192 + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(mlp3_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  mlp3_fwd_kernel<<<ceil_div(M, ROWS), MLP_THREADS, smem, (cudaStream_t)stream>>>(tx, t1, t2, p);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+}  // extern "C"
