@@ -225,7 +225,7 @@ class SACAgent:
                 for _ in range(self.utd):
                     tr.update(*self.replay.sample(tr.cfg.batch))
             if logger is not None and steps % log_every < env.n_envs and tr.metrics:
-                logger.log_scalars(steps, {k: float(v) for k, v in tr.metrics.items()})
+                logger.log(steps, {k: float(v) for k, v in tr.metrics.items()})
         return tr.metrics
 
 

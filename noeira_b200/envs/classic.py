@@ -54,7 +54,7 @@ class _TensorEnv(BatchedEnv):
         return self.obs
 
     def step_batch(self, action, auto_reset: bool = True):
-        a = action.to(self.device, torch.float32).reshape(self.n_envs, self.act_dim)
+        a = action.to(self.device, torch.float32).reshape(self.n_envs, -1)[:, : self.act_dim]   # padded action rows are fine
         s2, r, term = self._dynamics(self.state, a)
         self.steps += 1
         trunc = self.steps >= self.max_steps

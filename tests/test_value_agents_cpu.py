@@ -76,3 +76,16 @@ def test_ddpg_is_td3_without_smoothing():
     s, a, r, sp, d = torch.randn(8, 3), torch.rand(8, 1) * 2 - 1, torch.randn(8), torch.randn(8, 3), torch.zeros(8)
     out = tr.update(s, a, r, sp, d)
     assert "actor_loss" in out and torch.isfinite(torch.as_tensor(float(out["critic_loss"])))
+
+
+def test_sac_agent_drives_pendulum_and_logs(tmp_path):
+    from noeira_b200 import core
+    from noeira_b200.agents.sac import SACAgent, SACConfig
+    from noeira_b200.envs import PendulumEnv
+    env = PendulumEnv(4, seed=0)
+    agent = SACAgent(env, SACConfig(obs_dim=3, act_dim=1, hidden=32, batch=32), capacity=5000, learning_starts=200)
+    with core.RunContext(str(tmp_path), "t", "sac") as run:
+        m = agent.train(600, logger=run, log_every=100)
+    assert agent.replay.size == 600 and all(float(v) == float(v) for v in m.values())
+    rows = open(run.path("metrics.csv")).read().splitlines()
+    assert len(rows) >= 3 and "critic_loss" in rows[0]
