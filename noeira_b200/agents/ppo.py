@@ -140,7 +140,7 @@ class PPOTrainer:
 
     def _forward(self, net, x, save):
         """Forward of the actor or the critic: the fused three-layer kernel when it applies, else layer by layer."""
-        if self._fused.get(id(net)):
+        if self._fused.get(id(net)) and x.shape[0] >= 8192:     # below that three GEMM launches are as fast (6.5 us each)
             from ..ops.mlp import mlp3_forward
             l1, l2, l3 = self._layers(net)
             y = mlp3_forward(x, l1, l2, l3, save=save)
