@@ -27,7 +27,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def _reference_arm(args):
     # The reference is a Mojo/MAX code base (no setup.py / pyproject.toml, 3.6k .mojo files); the
-    # offline `pip install … /root/reference` fails with "neither setup.py nor pyproject.toml found",
+    # offline `pip install` of its source tree fails with "neither setup.py nor pyproject.toml found",
     # and no Mojo toolchain exists in this image.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is Mojo/MAX source without setup.py/pyproject.toml; pip install fails and no mojo toolchain is in the image"}))

@@ -44,7 +44,7 @@ class StoreReplay:
         return torch.randint(0, max(self.size, 1), (batch,), device=self.device, generator=self.gen)
 
     def ere_indices(self, batch, k, K, eta=0.996, c_min=5000):
-        """Update k of K in this round samples from the most recent c_k = max(N·eta^(k·1000/K), c_min) items."""
+        """Update k of the K updates that follow one collection phase samples from the most recent c_k = max(N·eta^(k·1000/K), c_min) items."""
         ck = int(max(self.size * eta ** (k * 1000.0 / max(K, 1)), min(c_min, self.size)))
         off = torch.randint(0, max(ck, 1), (batch,), device=self.device, generator=self.gen)
         return (self.pos - 1 - off) % max(self.size, 1)
