@@ -176,6 +176,20 @@ class SACTrainer:
         self.metrics = dict(critic_loss=closs, actor_loss=aloss, mean_q=q1v.mean(), mean_logp=logpi.mean())
         return self.metrics
 
+    def update_captured(self, s, a, r, sp, d):
+        """The same update replayed from one CUDA graph (captured on the third call; batch shape fixed).  The noise
+        generator is registered with the graph, so every replay draws fresh samples
+        (noeira/deep_agents/sac/trainer.mojo:604-703 ``train_device_kernels`` is the reference's capture body)."""
+        if self.device.type != "cuda":
+            return self.update(s, a, r, sp, d)
+        if getattr(self, "_graphed", None) is None:
+            from ..utils.graphs import GraphedStep
+            self._graphed = GraphedStep(self.update, [s, a, r, sp, d], generators=[self.gen])
+        before = self.total_train_steps
+        out = self._graphed(s, a, r, sp, d)
+        self.total_train_steps = before + 1
+        return out
+
     # ------------------------------------------------------------------ persistence (reference layout)
     def save(self, path):
         from ..io.checkpoint import save_params_multi
@@ -223,7 +237,7 @@ class SACAgent:
             steps += env.n_envs
             if steps >= self.learning_starts:
                 for _ in range(self.utd):
-                    tr.update(*self.replay.sample(tr.cfg.batch))
+                    tr.update_captured(*self.replay.sample(tr.cfg.batch))
             if logger is not None and steps % log_every < env.n_envs and tr.metrics:
                 logger.log(steps, {k: float(v) for k, v in tr.metrics.items()})
         return tr.metrics

@@ -38,3 +38,16 @@ def test_td3_update_cuda():
     assert float(m["critic_loss"]) < 0.8 * first
     a = tr.select_action(_batch("cuda")[0])
     assert a.shape == (256, 6) and a.abs().max() <= 1.0 + 1e-6
+
+
+def test_sac_captured_update_tracks_eager():
+    from noeira_b200.agents.sac import SACConfig, SACTrainer
+    a, b = SACTrainer(SACConfig(seed=4), device="cuda"), SACTrainer(SACConfig(seed=4), device="cuda")
+    batch = _batch("cuda")
+    la, lb = [], []
+    for _ in range(12):
+        la.append(float(a.update(*batch)["critic_loss"]))
+        lb.append(float(b.update_captured(*batch)["critic_loss"]))
+    assert b._graphed.graph is not None and b._graphed.launches > 50 and b.total_train_steps == 12
+    assert all(abs(x - y) <= 2e-2 * max(1.0, abs(x)) for x, y in zip(la, lb)), (la, lb)
+    assert lb[-1] < lb[0]
