@@ -54,3 +54,22 @@ def test_hyperparam_search(tmp_path):
     rows = hp.search(g, lambda c: -abs(c["lr"] - 1e-2) - abs(c["h"] - 64) / 1000, csv_path=str(tmp_path / "s.csv"))
     assert rows[0]["lr"] == 1e-2 and rows[0]["h"] == 64
     assert open(tmp_path / "s.csv").read().splitlines()[0] == "lr,h,score"
+
+
+def test_act_dataset_chunks_and_masks():
+    import torch
+    from noeira_b200.data.act_dataset import ACTDataset, synthetic_episodes
+    eps = synthetic_episodes(4, 30, cams=2, height=8, width=10, seed=1)
+    ds = ACTDataset(eps, chunk=12, seed=0)
+    assert ds.n_steps == sum(e["qpos"].shape[0] for e in eps)
+    q, img, act, valid = ds.sample(256)
+    assert q.shape == (256, 6) and img.shape == (256, 2, 3, 8, 10) and img.dtype == torch.uint8
+    assert act.shape == (256, 12, 6) and valid.shape == (256, 14) and (valid[:, :2] == 1).all()
+    # padded steps are exactly zero and masked; real steps reproduce the episode's actions
+    assert (act[valid[:, 2:] == 0] == 0).all() and (valid[:, 2:].sum(1) >= 1).all() and (valid[:, 2:].sum(1) < 12).any()
+    ds.gen.manual_seed(0)
+    t = torch.randint(0, ds.n_steps, (256,), generator=ds.gen)
+    k = int((valid[:, 2:].sum(1) == 12).nonzero()[0])
+    assert torch.allclose(ds.denormalise_action(act[k]), ds.action[t[k]: t[k] + 12], atol=1e-5)
+    m = valid[:, 2:].bool()
+    assert (valid[:, 2:].cumsum(1)[~m] == valid[:, 2:].sum(1, keepdim=True).expand(-1, 12)[~m]).all()   # padding only at the end
