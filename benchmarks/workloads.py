@@ -13,6 +13,15 @@ import torch.distributed as dist
 
 
 def run(args, rank, local_rank, world):
+    try:
+        return _run(args, rank, local_rank, world)
+    except Exception:  # noqa: BLE001 — a launcher keeps only its own traceback; print the worker's cause on stdout
+        import traceback
+        print(json.dumps({"workload": args.workload, "rank": rank, "error": traceback.format_exc()[-1500:]}), flush=True)
+        raise
+
+
+def _run(args, rank, local_rank, world):
     if args.workload == "wm":
         return run_wm(args, rank, local_rank, world)
     if args.workload in ("act", "vla"):
