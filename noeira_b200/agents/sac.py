@@ -191,22 +191,48 @@ class SACTrainer:
         return out
 
     # ------------------------------------------------------------------ persistence (reference layout)
-    def save(self, path):
+    def save(self, path, with_moments: bool = True):
+        """Actor, critic 1, critic 2 in pack order plus the temperature state and the step counter as K scalars
+        (noeira/deep_agents/sac/trainer.mojo:1083-1103).  ``with_moments=False`` writes exactly the reference's
+        sections (its resume re-warms the moments and restarts the targets from the online critics).
+        ``with_moments=True`` is the exact-resume form: Adam's m / v, the optimizers' step counters and
+        bias-correction products, and the two target critics (two more modules after critic 2) are stored as well,
+        so a resumed run continues bit for bit."""
         from ..io.checkpoint import save_params_multi
         st = self.alpha_opt.state.cpu().tolist()
-        save_params_multi(path, [self.actor, self.q1, self.q2], {
-            "alpha.log_alpha": st[0], "alpha.m": st[1], "alpha.v": st[2], "alpha.b1t": st[3], "alpha.b2t": st[4],
-            "alpha.alpha": st[5], "total_train_steps": float(self.total_train_steps)})
+        sc = {"alpha.log_alpha": st[0], "alpha.m": st[1], "alpha.v": st[2], "alpha.b1t": st[3], "alpha.b2t": st[4],
+              "alpha.alpha": st[5], "total_train_steps": float(self.total_train_steps)}
+        mods = [self.actor, self.q1, self.q2]
+        if with_moments:
+            sc.update({f"actor_opt.{k}": v for k, v in self.actor_opt.scalars().items()})
+            sc.update({f"critic_opt.{k}": v for k, v in self.critic_opt.scalars().items()})
+            mods += [self.q1t, self.q2t]
+        save_params_multi(path, mods, sc, with_moments=with_moments)
 
     def load(self, path):
-        from ..io.checkpoint import load_params_multi
-        sc = load_params_multi(path, [self.actor, self.q1, self.q2])
+        from ..io.checkpoint import CheckpointError, load_params_multi
+        try:
+            sc = load_params_multi(path, [self.actor, self.q1, self.q2, self.q1t, self.q2t], load_moments=True)
+            exact = "actor_opt.t" in sc
+        except CheckpointError:
+            sc = load_params_multi(path, [self.actor, self.q1, self.q2], load_moments=False)
+            exact = False
         if "alpha.log_alpha" in sc:
             self.alpha_opt.state.copy_(torch.tensor([sc[k] for k in ("alpha.log_alpha", "alpha.m", "alpha.v", "alpha.b1t",
                                                                      "alpha.b2t", "alpha.alpha")]))
         self.total_train_steps = int(sc.get("total_train_steps", 0))
-        self.q1t.copy_from(self.q1)
-        self.q2t.copy_from(self.q2)
+        if exact:
+            # moments are only meaningful together with their step counters: both are restored, or neither
+            self.actor_opt.load_scalars({k.split(".", 1)[1]: v for k, v in sc.items() if k.startswith("actor_opt.")})
+            self.critic_opt.load_scalars({k.split(".", 1)[1]: v for k, v in sc.items() if k.startswith("critic_opt.")})
+        else:
+            self.q1t.copy_from(self.q1)
+            self.q2t.copy_from(self.q2)
+        for o in (self.actor_opt, self.critic_opt):
+            if o.arena.shadow is not None:
+                o.arena.refresh_shadow()
+        if getattr(self.target_arena, "shadow", None) is not None:
+            self.target_arena.refresh_shadow()
 
 
 class SACAgent:

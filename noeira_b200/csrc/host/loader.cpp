@@ -58,7 +58,8 @@ struct Loader {
   std::vector<Slot> slots;
   std::vector<std::thread> threads;
   std::mutex mu;
-  std::condition_variable cv_ready, cv_free;
+  std::condition_variable cv_ready, cv_free, cv_idle;
+  int inflight = 0;  // workers currently writing into a slot buffer (outside the lock)
   int64_t next_to_fill = 0, next_to_consume = 0;
   uint64_t generation = 0;
   bool stop = false;
@@ -79,6 +80,7 @@ void worker(Loader* L) {
         L->cv_free.wait(lk);
       }
       ++L->next_to_fill;
+      ++L->inflight;
       gen = L->generation;
       epoch = L->epoch;
       s = &L->slots[(size_t)b % L->nslots];
@@ -107,8 +109,10 @@ void worker(Loader* L) {
         s->ready = true;
         if (err) L->error = err;
       }
+      --L->inflight;
     }
     L->cv_ready.notify_all();
+    L->cv_idle.notify_all();
   }
 }
 
@@ -154,8 +158,14 @@ int64_t nbh_loader_next(void* loader, void* dst, uint64_t* out_indices) {
 int nbh_loader_reset(void* loader, uint64_t epoch) {
   Loader* L = (Loader*)loader;
   {
-    std::lock_guard<std::mutex> lk(L->mu);
+    // A fill that is still running belongs to the old epoch and writes into its slot buffer without the lock.
+    // Bump the generation first (so its result is discarded and no new fill of the old epoch starts: the
+    // counters below park the workers), then wait until every such fill has left the buffers before the slots are
+    // handed out again.
+    std::unique_lock<std::mutex> lk(L->mu);
     ++L->generation;
+    L->next_to_fill = (int64_t)L->n_batches;   // nothing new starts while draining
+    L->cv_idle.wait(lk, [&] { return L->inflight == 0; });
     L->epoch = epoch;
     L->next_to_fill = 0;
     L->next_to_consume = 0;

@@ -60,16 +60,25 @@ __global__ void replay_indices_kernel(long long* __restrict__ idx, int batch, co
 // ---- sum tree over `leaves` (power of two) priorities: tree[1] = total, children of n are 2n, 2n+1, leaves at [leaves, 2·leaves)
 __global__ void per_set_kernel(float* __restrict__ tree, long long leaves, const long long* __restrict__ idx,
                                const float* __restrict__ prio, int n, float alpha, float eps) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  tree[leaves + idx[i]] = powf(fabsf(prio[i]) + eps, alpha);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    tree[leaves + idx[i]] = powf(fabsf(prio[i]) + eps, alpha);
 }
-// rebuild level by level (deterministic; cheaper than atomics for the usual batch sizes): one launch per level
+// After the leaves idx[0..n) changed, re-sum their ancestors one level per launch (level k = nodes (leaves+idx)>>k).
+// Threads that share an ancestor write the same value, so the result is deterministic without atomics, and the
+// work is n·log2(leaves) whatever the capacity.
+__global__ void per_ancestors_kernel(float* __restrict__ tree, long long leaves, const long long* __restrict__ idx, int n,
+                                     int level) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long node = (leaves + idx[i]) >> level;
+    tree[node] = tree[2 * node] + tree[2 * node + 1];
+  }
+}
+// Full rebuild of one level (grid-stride: any capacity).
 __global__ void per_rebuild_level_kernel(float* __restrict__ tree, long long first, long long count) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= count) return;
-  const long long n = first + i;
-  tree[n] = tree[2 * n] + tree[2 * n + 1];
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const long long n = first + i;
+    tree[n] = tree[2 * n] + tree[2 * n + 1];
+  }
 }
 // stratified prefix-sum descent; also returns the importance weight (N·P(i))^-beta normalised by its maximum bound
 __global__ void per_sample_kernel(const float* __restrict__ tree, long long leaves, long long* __restrict__ idx,
@@ -142,6 +151,18 @@ int nb_per_update(float* tree, long long leaves, const long long* idx, const flo
   cudaStream_t s = (cudaStream_t)stream;
   per_set_kernel<<<blocks_for(n), 256, 0, s>>>(tree, leaves, idx, prio, n, alpha, eps);
   NB_LAUNCH_CHECK();
+  int level = 1;
+  for (long long count = leaves / 2; count >= 1; count /= 2, ++level) {
+    per_ancestors_kernel<<<blocks_for(n), 256, 0, s>>>(tree, leaves, idx, n, level);
+    NB_LAUNCH_CHECK();
+  }
+  return NB_OK;
+}
+
+// Recompute every inner node from the leaves (after loading a checkpointed priority array).
+int nb_per_rebuild(float* tree, long long leaves, void* stream) {
+  if (leaves <= 0 || (leaves & (leaves - 1))) return NB_ERR_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
   for (long long count = leaves / 2; count >= 1; count /= 2) {
     per_rebuild_level_kernel<<<blocks_for(count), 256, 0, s>>>(tree, count, count);
     NB_LAUNCH_CHECK();

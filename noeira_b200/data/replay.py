@@ -82,7 +82,7 @@ class StoreReplayGpu:
     tree; ``update_priorities`` after the TD errors are known).  (noeira/data/replay_gpu.mojo:54-330)"""
 
     def __init__(self, capacity: int, obs_dim: int, act_dim: int, demo_prefix: int = 0, seed: int = 0, per_alpha: float = 0.6,
-                 per_beta: float = 0.4, device="cuda"):
+                 per_beta: float = 0.4, device="cuda", prioritized: bool = True):
         import ctypes
         from .._native import cuda_lib
         self._c, self._lib = ctypes, cuda_lib()
@@ -92,10 +92,12 @@ class StoreReplayGpu:
         self.buf = torch.zeros(capacity, self.width, device=self.device)
         self.meta = torch.tensor([demo_prefix, demo_prefix, 0], dtype=torch.int64, device=self.device)
         self.seed, self.per_alpha, self.per_beta = seed, per_alpha, per_beta
+        # the sum tree is maintained only when prioritized sampling is in use (uniform / ERE never read it)
+        self.prioritized = prioritized and per_alpha > 0
         self.leaves = 1
         while self.leaves < capacity:
             self.leaves *= 2
-        self.tree = torch.zeros(2 * self.leaves, device=self.device)
+        self.tree = torch.zeros(2 * self.leaves if self.prioritized else 2, device=self.device)
         self._idx, self._out, self._w = {}, {}, {}
 
     def _ptr(self, t):
@@ -107,12 +109,12 @@ class StoreReplayGpu:
         rows = torch.cat([s.float(), a.float(), r.float().reshape(-1, 1), sp.float(), d.float().reshape(-1, 1)], 1).contiguous()
         c = self._c
         n = rows.shape[0]
-        if self.per_alpha > 0:
+        if self.prioritized:
             # new transitions enter with the running maximum priority: here priority 1 before the exponent
             start = self.meta[0:1].clone()
         check(self._lib.nb_replay_store(self._ptr(self.buf), c.c_int(self.width), c.c_longlong(self.capacity), self._ptr(self.meta),
                                         self._ptr(rows), c.c_int(n), c.c_int(self.base), stream_ptr()), "replay_store")
-        if self.per_alpha > 0:
+        if self.prioritized:
             ring = self.capacity - self.base
             idx = (start - self.base + torch.arange(n, device=self.device)) % ring + self.base
             self.update_priorities(idx, torch.ones(n, device=self.device))
@@ -122,6 +124,7 @@ class StoreReplayGpu:
         c = self._c
         idx = self._idx.setdefault(batch, torch.zeros(batch, dtype=torch.int64, device=self.device))
         if mode == "per":
+            assert self.prioritized, "construct the store with prioritized=True to sample by priority"
             w = self._w.setdefault(batch, torch.zeros(batch, device=self.device))
             check(self._lib.nb_per_sample(self._ptr(self.tree), c.c_longlong(self.leaves), self._ptr(idx), self._ptr(w),
                                           c.c_int(batch), self._ptr(self.meta), c.c_ulonglong(self.seed),

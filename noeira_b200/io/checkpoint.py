@@ -52,24 +52,26 @@ def _check_name(name: str):
         raise CheckpointError(f"invalid section name {name!r}")
 
 
-def save_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], named_states: Iterable[Tuple[str, "State"]],
-                    scalars: Dict[str, float] = None, with_moments: bool = True) -> None:
+def _write_groups(path: str, groups, scalars: Dict[str, float], with_moments: bool) -> None:
+    """``groups`` = [(named_params, named_states), ...]: for every group its P sections, then its S sections (the
+    reference walks one model at a time, noeira/nn/core/checkpoint.mojo:804-827); the K scalars come once, last."""
     tmp = path + ".tmp"
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     with open(tmp, "wb") as f:
         f.write(HEADER)
-        for name, p in named_params:
-            _check_name(name)
-            has_m = 1 if (with_moments and p.m is not None) else 0
-            f.write(f"P {name} {p.numel} {has_m}\n".encode())
-            _write_chunked(f, _to_host_f32(p.file_view()).tobytes())
-            if has_m:
-                _write_chunked(f, _to_host_f32(p.file_view(p._logical(p.m))).tobytes())
-                _write_chunked(f, _to_host_f32(p.file_view(p._logical(p.v))).tobytes())
-        for name, s in named_states:
-            _check_name(name)
-            f.write(f"S {name} {s.data.numel()}\n".encode())
-            _write_chunked(f, _to_host_f32(s.data).tobytes())
+        for named_params, named_states in groups:
+            for name, p in named_params:
+                _check_name(name)
+                has_m = 1 if (with_moments and p.m is not None) else 0
+                f.write(f"P {name} {p.file_numel} {has_m}\n".encode())
+                _write_chunked(f, _to_host_f32(p.file_view()).tobytes())
+                if has_m:
+                    _write_chunked(f, _to_host_f32(p.file_view(p._logical(p.m))).tobytes())
+                    _write_chunked(f, _to_host_f32(p.file_view(p._logical(p.v))).tobytes())
+            for name, s in named_states:
+                _check_name(name)
+                f.write(f"S {name} {s.data.numel()}\n".encode())
+                _write_chunked(f, _to_host_f32(s.data).tobytes())
         for k, v in (scalars or {}).items():
             _check_name(k)
             f.write(f"K {k}\n".encode())
@@ -77,6 +79,11 @@ def save_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], name
         f.flush()
         os.fsync(f.fileno())
     os.replace(tmp, path)
+
+
+def save_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], named_states: Iterable[Tuple[str, "State"]],
+                    scalars: Dict[str, float] = None, with_moments: bool = True) -> None:
+    _write_groups(path, [(list(named_params), list(named_states))], scalars, with_moments)
 
 
 class _Reader:
@@ -108,34 +115,34 @@ class _Reader:
         return np.frombuffer(bytes(out), dtype="<f4")
 
 
-def load_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], named_states: Iterable[Tuple[str, "State"]],
-                    load_moments: bool = True) -> Dict[str, float]:
+def _read_groups(path: str, groups, load_moments: bool) -> Dict[str, float]:
     r = _Reader(path)
-    for name, p in named_params:
-        ln = r.line()
-        if ln is None:
-            raise CheckpointError(f"checkpoint ends before parameter {name}")
-        parts = ln.split(" ")
-        if len(parts) != 4 or parts[0] != "P":
-            raise CheckpointError(f"expected 'P {name} ...', found {ln!r}")
-        if parts[1] != name or int(parts[2]) != p.numel:
-            raise CheckpointError(f"section mismatch: file has {parts[1]}[{parts[2]}], model walk expects {name}[{p.numel}]")
-        vals = r.payload(p.numel)
-        p.load_file_(torch.from_numpy(vals.copy()))
-        if int(parts[3]):
-            m, v = r.payload(p.numel), r.payload(p.numel)
-            if load_moments and p.m is not None:
-                with torch.no_grad():
-                    fm = (lambda t: p.from_file(t)) if p.from_file is not None else (lambda t: t)
-                    p._logical(p.m).copy_(fm(torch.from_numpy(m.copy())).reshape(p.shape))
-                    p._logical(p.v).copy_(fm(torch.from_numpy(v.copy())).reshape(p.shape))
-    for name, s in named_states:
-        ln = r.line()
-        parts = (ln or "").split(" ")
-        if len(parts) != 3 or parts[0] != "S" or parts[1] != name or int(parts[2]) != s.data.numel():
-            raise CheckpointError(f"state section mismatch at {name}: {ln!r}")
-        with torch.no_grad():
-            s.data.copy_(torch.from_numpy(r.payload(s.data.numel()).copy()).reshape(s.data.shape))
+    for named_params, named_states in groups:
+        for name, p in named_params:
+            ln = r.line()
+            if ln is None:
+                raise CheckpointError(f"checkpoint ends before parameter {name}")
+            parts = ln.split(" ")
+            if len(parts) != 4 or parts[0] != "P":
+                raise CheckpointError(f"expected 'P {name} ...', found {ln!r}")
+            if parts[1] != name or int(parts[2]) != p.file_numel:
+                raise CheckpointError(f"section mismatch: file has {parts[1]}[{parts[2]}], model walk expects {name}[{p.file_numel}]")
+            vals = r.payload(p.file_numel)
+            p.load_file_(torch.from_numpy(vals.copy()))
+            if int(parts[3]):
+                m, v = r.payload(p.file_numel), r.payload(p.file_numel)
+                if load_moments and p.m is not None:
+                    with torch.no_grad():
+                        fm = (lambda t: p.from_file(t)) if p.from_file is not None else (lambda t: t)
+                        p._logical(p.m).copy_(fm(torch.from_numpy(m.copy())).reshape(p.shape))
+                        p._logical(p.v).copy_(fm(torch.from_numpy(v.copy())).reshape(p.shape))
+        for name, s in named_states:
+            ln = r.line()
+            parts = (ln or "").split(" ")
+            if len(parts) != 3 or parts[0] != "S" or parts[1] != name or int(parts[2]) != s.data.numel():
+                raise CheckpointError(f"state section mismatch at {name}: {ln!r}")
+            with torch.no_grad():
+                s.data.copy_(torch.from_numpy(r.payload(s.data.numel()).copy()).reshape(s.data.shape))
     scalars: Dict[str, float] = {}
     while True:
         ln = r.line()
@@ -151,19 +158,17 @@ def load_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], name
     return scalars
 
 
+def load_checkpoint(path: str, named_params: Iterable[Tuple[str, "Param"]], named_states: Iterable[Tuple[str, "State"]],
+                    load_moments: bool = True) -> Dict[str, float]:
+    return _read_groups(path, [(list(named_params), list(named_states))], load_moments)
+
+
 def save_params_multi(path: str, modules: List, scalars=None, with_moments=True):
-    """Several networks in pack order in one file WITHOUT prefixes (the SAC layout: actor, critic 1,
-    critic 2 — noeira/nn/core/checkpoint.mojo:804-827)."""
-    nps, nss = [], []
-    for m in modules:
-        nps += list(m.named_params())
-        nss += list(m.named_states())
-    save_checkpoint(path, nps, nss, scalars, with_moments)
+    """Several networks in pack order in one file WITHOUT prefixes (the SAC layout: actor, critic 1, critic 2):
+    module by module, the P sections of a module followed by its S sections
+    (noeira/nn/core/checkpoint.mojo:804-827)."""
+    _write_groups(path, [(list(m.named_params()), list(m.named_states())) for m in modules], scalars, with_moments)
 
 
 def load_params_multi(path: str, modules: List, load_moments=True):
-    nps, nss = [], []
-    for m in modules:
-        nps += list(m.named_params())
-        nss += list(m.named_states())
-    return load_checkpoint(path, nps, nss, load_moments)
+    return _read_groups(path, [(list(m.named_params()), list(m.named_states())) for m in modules], load_moments)

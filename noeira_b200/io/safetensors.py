@@ -161,8 +161,8 @@ def load_safetensors(path: str, named_params, named_states=(), strict: bool = Tr
                 raise SafeTensorsError(f"missing tensor {name}")
             continue
         a = st.get(name)
-        if a.size != p.numel:
-            raise SafeTensorsError(f"{name}: file has {a.size} values, parameter has {p.numel}")
+        if a.size != p.file_numel:
+            raise SafeTensorsError(f"{name}: file has {a.size} values, parameter has {p.file_numel}")
         p.load_file_(torch.from_numpy(np.array(a, dtype=np.float32)).reshape(-1))
         used += 1
     for name, s in named_states:

@@ -252,48 +252,3 @@ def polyak(target_arena: ParamArena, online_arena: ParamArena, tau: float):
     else:
         target_arena.val.lerp_(online_arena.val, tau)
     target_arena.bump_versions(shadow_fresh=target_arena.shadow is not None)
-
-
-# ---- learning-rate schedules (noeira/nn/optimizer/lr_scheduler.mojo:33-121)
-class Constant:
-    def __init__(self, lr):
-        self.lr = lr
-
-    def __call__(self, step):
-        return self.lr
-
-
-class LinearWarmup:
-    def __init__(self, lr, warmup):
-        self.lr, self.warmup = lr, warmup
-
-    def __call__(self, step):
-        return self.lr * min(1.0, (step + 1) / max(1, self.warmup))
-
-
-class Cosine:
-    def __init__(self, lr, total, lr_min=0.0):
-        self.lr, self.total, self.lr_min = lr, total, lr_min
-
-    def __call__(self, step):
-        t = min(step, self.total) / max(1, self.total)
-        return self.lr_min + 0.5 * (self.lr - self.lr_min) * (1 + math.cos(math.pi * t))
-
-
-class WarmupCosine:
-    def __init__(self, lr, warmup, total, lr_min=0.0):
-        self.lr, self.warmup, self.total, self.lr_min = lr, warmup, total, lr_min
-
-    def __call__(self, step):
-        if step < self.warmup:
-            return self.lr * (step + 1) / max(1, self.warmup)
-        t = min(step - self.warmup, self.total - self.warmup) / max(1, self.total - self.warmup)
-        return self.lr_min + 0.5 * (self.lr - self.lr_min) * (1 + math.cos(math.pi * t))
-
-
-class Step:
-    def __init__(self, lr, every, gamma=0.1):
-        self.lr, self.every, self.gamma = lr, every, gamma
-
-    def __call__(self, step):
-        return self.lr * self.gamma ** (step // self.every)

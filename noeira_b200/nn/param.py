@@ -94,6 +94,16 @@ class Param:
     def storage_numel(self) -> int:
         return self._val.numel()
 
+    @property
+    def file_numel(self) -> int:
+        """Element count of the parameter as files hold it (``to_file`` may strip kernel-side padding, e.g. the
+        zero input channels of a 3-channel convolution stem)."""
+        if self.to_file is None:
+            return self.numel
+        if getattr(self, "_file_numel", None) is None:
+            self._file_numel = int(self.file_view().numel())
+        return self._file_numel
+
     def file_view(self, t: Optional[torch.Tensor] = None) -> torch.Tensor:
         t = self.data if t is None else t
         return self.to_file(t) if self.to_file is not None else t

@@ -24,8 +24,8 @@ ONE_SHOT, TWO_SHOT, MULTIMEM = 0, 1, 2
 
 def choose_algo(nbytes: int, world: int, have_multicast: bool = False) -> int:
     """Per-bucket choice.  One-shot moves (N-1)·bytes per GPU but has the fewest flag rounds; two-shot
-    moves 2(N-1)/N·bytes; multimem ≈ 2·bytes/N.  Crossovers follow the measured table in
-    profiles/allreduce_fused_and_tp_multi_gpu.md."""
+    moves 2(N-1)/N·bytes; multimem ≈ 2·bytes/N.  Crossovers follow timings on 8 B200s: one-shot wins up to
+    512 KB, two-shot (or multimem, when a multicast mapping exists) above."""
     if world <= 2 or nbytes <= (512 << 10):
         return ONE_SHOT
     if have_multicast and nbytes >= (4 << 20):

@@ -22,3 +22,15 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _seed_every_test():
+    """Tests draw inputs from torch's global generator; a fixed seed per test makes every run see the same data
+    whatever ran before it."""
+    try:
+        import torch
+        torch.manual_seed(1234)
+    except Exception:  # noqa: BLE001
+        pass
+    yield

@@ -167,3 +167,23 @@ def test_record_loader_epochs(tmp_path):
     cnt, idx = ld.next_into(out)
     assert idx.tolist() != order0[:64]
     ld.close()
+
+
+def test_record_loader_reset_mid_epoch(tmp_path):
+    """Abandon an epoch after one batch while the readers are still filling slots: every record delivered in the
+    next epoch must match its index (no buffer is written by a reader of the old epoch)."""
+    n, rec = 4096, 512
+    data = np.arange(n * rec // 4, dtype=np.int32).reshape(n, rec // 4)
+    path = str(tmp_path / "records.bin")
+    with open(path, "wb") as f:
+        f.write(data.tobytes())
+    ld = rt.RecordLoader(path, rec, n, batch=256, slots=4, threads=4, seed=9, shuffle=True, drop_last=True)
+    out = np.zeros((256, rec // 4), dtype=np.int32)
+    for epoch in range(1, 30):
+        cnt, idx = ld.next_into(out)
+        assert cnt == 256 and (out == data[idx.astype(np.int64)]).all()
+        ld.reset(epoch)
+        for _ in range(2):
+            cnt, idx = ld.next_into(out)
+            assert cnt == 256 and (out == data[idx.astype(np.int64)]).all(), epoch
+    ld.close()

@@ -174,3 +174,31 @@ def test_physics_oracle_invariants():
         q, v = oracle.substep(pc, q, v, np.zeros(2), warm)
     pc.opt.timestep = old
     assert abs(energy(q, v) - e0) < 2e-2 * max(1.0, abs(e0))
+
+
+def test_multi_module_checkpoint_interleaves_params_and_states(tmp_path):
+    """Two modules that both carry states: the file holds P… S… of module 0, then P… S… of module 1, then K."""
+    from noeira_b200 import nn
+    from noeira_b200.io.checkpoint import load_params_multi, save_params_multi
+    nn.manual_seed(0)
+    mk = lambda: nn.Sequential(nn.Conv2D(3, 4, 3, pad=1), nn.BatchNorm2D(4))
+    m0, m1 = mk(), mk()
+    for _, s in list(m0.named_states()) + list(m1.named_states()):
+        s.data.uniform_(0.5, 1.5)
+    path = str(tmp_path / "two.ckpt")
+    save_params_multi(path, [m0, m1], {"k": 3.0}, with_moments=False)
+    kinds = []
+    raw = open(path, "rb").read()
+    pos = raw.index(b"\n") + 1
+    while pos < len(raw):
+        end = raw.index(b"\n", pos)
+        parts = raw[pos:end].decode().split(" ")
+        kinds.append(parts[0])
+        pos = end + 1 + (8 if parts[0] == "K" else 4 * int(parts[2]))
+    n_p, n_s = len(list(m0.named_params())), len(list(m0.named_states()))
+    assert n_s > 0
+    assert kinds == ["P"] * n_p + ["S"] * n_s + ["P"] * n_p + ["S"] * n_s + ["K"]
+    a, b = mk(), mk()
+    assert load_params_multi(path, [a, b]) == {"k": 3.0}
+    for (_, s0), (_, s1) in zip(list(m1.named_states()), list(b.named_states())):
+        assert torch.equal(s0.data, s1.data)

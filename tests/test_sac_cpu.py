@@ -100,3 +100,36 @@ def test_replay_policies():
     assert (mi[:10] < 10).all() and (mi[10:] >= 10).all()
     ei = rb.ere_indices(16, 5, 10)
     assert ei.min() >= 0 and ei.max() < rb.size
+
+
+def test_sac_exact_resume_is_bit_identical(tmp_path):
+    """save → load into a fresh trainer → one update equals the uninterrupted run bit for bit (moments, step
+    counters, bias-correction products, temperature state and target critics all travel)."""
+    from noeira_b200.agents.sac import SACConfig, SACTrainer
+    cfg = SACConfig(obs_dim=5, act_dim=2, hidden=32, batch=16, seed=3)
+    g = torch.Generator().manual_seed(0)
+    batch = lambda: (torch.randn(16, 5, generator=g), torch.rand(16, 2, generator=g) * 2 - 1, torch.randn(16, generator=g),
+                     torch.randn(16, 5, generator=g), (torch.rand(16, generator=g) < 0.1).float())
+    a = SACTrainer(cfg)
+    for _ in range(3):
+        a.update(*batch())
+    path = str(tmp_path / "sac.ckpt")
+    a.save(path)
+    rng = a.gen.get_state().clone()
+    nxt = batch()
+    a.update(*nxt)
+    b = SACTrainer(SACConfig(obs_dim=5, act_dim=2, hidden=32, batch=16, seed=99))
+    b.load(path)
+    b.gen.set_state(rng)
+    b.update(*nxt)
+    assert b.total_train_steps == a.total_train_steps == 4
+    for (n1, p1), (n2, p2) in zip(list(a.actor.named_params()) + list(a.q1.named_params()) + list(a.q1t.named_params()),
+                                  list(b.actor.named_params()) + list(b.q1.named_params()) + list(b.q1t.named_params())):
+        assert torch.equal(p1.data, p2.data), n1
+    assert torch.equal(a.alpha_opt.state, b.alpha_opt.state)
+    # the reference's own layout (no moments, three modules) still loads, and re-warms
+    a.save(path, with_moments=False)
+    c = SACTrainer(SACConfig(obs_dim=5, act_dim=2, hidden=32, batch=16, seed=5))
+    c.load(path)
+    assert torch.equal(next(iter(c.actor.named_params()))[1].data, next(iter(a.actor.named_params()))[1].data)
+    assert float(c.actor_opt.scalars()["t"]) == 0.0

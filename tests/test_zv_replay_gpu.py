@@ -52,3 +52,26 @@ def test_per_sum_tree_matches_priorities():
     assert abs(float(frac[5]) - 3 / 8) < 0.02 and abs(float(frac[17]) - 1 / 8) < 0.02 and abs(float(frac[40]) - 4 / 8) < 0.02
     idx, w = rb.indices(256, "per")
     assert w.max() == 1.0 and torch.allclose(w[idx == 17].mean() / w[idx == 40].mean(), torch.tensor(2.0, device="cuda"), rtol=1e-3)
+
+
+def test_per_sum_tree_large_capacity():
+    """Capacity above 2^19 leaves: the root must equal the sum of the leaves after a batched update, and uniform
+    stores that never sample by priority must not touch the tree."""
+    from noeira_b200.data.replay import StoreReplayGpu
+    cap = (1 << 20) + 7
+    rb = StoreReplayGpu(cap, 3, 1, per_alpha=1.0, seed=1)
+    assert rb.leaves == 1 << 21
+    g = torch.Generator(device="cuda").manual_seed(0)
+    idx = torch.randint(0, cap, (50_000,), device="cuda", generator=g)
+    pr = torch.rand(50_000, device="cuda", generator=g) + 0.1
+    rb.update_priorities(idx, pr)
+    leaves = rb.tree[rb.leaves:].double()
+    assert abs(float(rb.tree[1]) - float(leaves.sum())) < 1e-3 * float(leaves.sum())
+    # every inner node is the sum of its children
+    inner = rb.tree[1: rb.leaves]
+    kids = rb.tree[2: 2 * rb.leaves].view(-1, 2).sum(1)
+    assert torch.allclose(inner, kids, rtol=1e-6, atol=1e-6)
+    plain = StoreReplayGpu(1024, 3, 1, prioritized=False)
+    plain.store_batch(torch.zeros(8, 3, device="cuda"), torch.zeros(8, 1, device="cuda"), torch.zeros(8, device="cuda"),
+                      torch.zeros(8, 3, device="cuda"), torch.zeros(8, device="cuda"))
+    assert plain.tree.numel() == 2 and float(plain.tree.sum()) == 0.0
