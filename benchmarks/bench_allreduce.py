@@ -1,4 +1,4 @@
-"""Fused P2P all-reduce (one-shot / two-shot) vs NCCL, per bucket size, device-timed, max over ranks.
+"""Fused P2P all-reduce (push / one-shot / two-shot) vs NCCL, per bucket size, device-timed, max over ranks.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29512 \\
         benchmarks/bench_allreduce.py [--max-mb 256] [--adam]
@@ -46,6 +46,12 @@ def main():
     hyper[:9] = torch.tensor([1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 0.9, 0.999, 1.0 / world])
     partials = torch.zeros(256, device="cuda")
     ref = torch.empty(max_n, device="cuda")
+    # push form: inbox of 2 x world planes + flags; buckets of up to 4 MB (1024 blocks of 16 KB)
+    push_max = min(max_n, 1 << 20)
+    pheap = SymmetricHeap(2 * world * push_max * 4 + 2 * world * 1024 * 4 + 8192)
+    inbox, pflags = pheap.tensor(2 * world * push_max, torch.float32), pheap.tensor(2 * world * 1024, torch.int32)
+    pctl = torch.zeros(4, dtype=torch.int32, device="cuda")
+    pout = torch.empty(push_max, device="cuda")
     torch.cuda.synchronize()
     dist.barrier()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -56,6 +62,14 @@ def main():
             ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_longlong(n), ptr(val) if adam else None, ptr(m) if adam else None,
             ptr(v) if adam else None, ptr(shadow) if adam else None, None, ptr(hyper) if adam else None, ptr(partials), None,
             ctypes.c_float(0.0), ctypes.c_int(0), ctypes.c_uint(1 << 24), ptr(device_status()), stream_ptr()), "ar")
+
+    def push(n, adam):
+        one = lambda t: (ctypes.c_void_p * 1)(t.data_ptr())
+        check(lib.nb_allreduce_push(
+            ctypes.c_int(world), ctypes.c_int(rank), ctypes.c_int(1), inbox.ptr_table(), pflags.ptr_table(), ptr(pctl),
+            one(grd.local), None if adam else one(pout), one(val) if adam else None, one(m) if adam else None,
+            one(v) if adam else None, one(shadow) if adam else None, None, one(hyper), (ctypes.c_longlong * 1)(n),
+            ctypes.c_int(0), ctypes.c_int(0), ctypes.c_uint(1 << 24), ptr(device_status()), stream_ptr()), "push")
 
     def nccl(n, adam):
         ref[:n].copy_(grd.local[:n])
@@ -90,15 +104,18 @@ def main():
     nccl(n, False)
     torch.cuda.synchronize()
     err = (red.local[:n] - ref[:n]).abs().max().item()
+    push(n, False)
+    torch.cuda.synchronize()
+    err = max(err, (pout[:n] * world - ref[:n]).abs().max().item())     # the push form returns the mean (hyper[GSCALE] = 1/N)
     size = 64 << 10
     while size <= args.max_mb << 20:
         n = size // 4
         row = {"bytes": size, "world": world, "adam": args.adam, "check_max_err": err}
         roof_ms = (world - 1) / world * size / (LINK_GBS * 1e9) * 1e3
-        for name, algo in (("one_shot", 0), ("two_shot", 1)):
-            if algo == 0 and size > (16 << 20):
+        for name, algo in (("push", 3), ("one_shot", 0), ("two_shot", 1)):
+            if (algo == 0 and size > (16 << 20)) or (algo == 3 and n > push_max):
                 continue
-            t = timed(lambda: fused(algo, n, args.adam))
+            t = timed((lambda: push(n, args.adam)) if algo == 3 else (lambda: fused(algo, n, args.adam)))
             row[name + "_us"] = round(t * 1e3, 2)
             row[name + "_frac_of_roofline"] = round(roof_ms / t, 3)
             row[name + "_frac_of_p2p_bound"] = round(2 * roof_ms / t, 3)

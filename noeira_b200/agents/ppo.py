@@ -214,11 +214,14 @@ class PPOTrainer:
               "ppo_objective")
         self.actor.vjp(self.dmu[:, : env.act_dim])
         self._actor_pg.join()
-        # the optimizer steps (with a gradient sync: two cross-GPU kernels that every rank must run in the same
-        # order) stay on the main stream
-        self._opt_step(self.actor_opt)
+        # the optimizer steps stay on the main stream; with a gradient sync both arenas are reduced and updated by one
+        # cross-GPU kernel (every rank runs its cross-GPU kernels in the same order)
         br.join()
-        self._opt_step(self.critic_opt)
+        if self.grad_sync is not None and hasattr(self.grad_sync, "reduce_and_step_many"):
+            self.grad_sync.reduce_and_step_many([self.actor_opt, self.critic_opt])
+        else:
+            self._opt_step(self.actor_opt)
+            self._opt_step(self.critic_opt)
         check(lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(0), ctypes.c_int(0), stream_ptr()), "counter")
 
     def _update(self):

@@ -23,6 +23,8 @@
 // Reference path being replaced: MAX comm allreduce → _scale_copy_kernel → 3 clip kernels →
 // _grouped_adam_kernel (noeira/nn/distributed/data_parallel.mojo:190-202,257-298;
 // noeira/nn/optimizer/grad_clip.mojo:255-320; noeira/nn/optimizer/adam.mojo:91-128).
+#include <string.h>
+
 #include "common.cuh"
 #include "optim_math.cuh"
 
@@ -232,38 +234,47 @@ ar_twoshot_kernel(ARParams p, AdamBufs a, unsigned int* status) {
   // slice of this rank (in float4 units, 128-byte granules so stores stay aligned)
   const long long per = ((p.n4 + p.world - 1) / p.world + 7) / 8 * 8;
   const long long lo = min(p.n4, per * p.rank), hi = min(p.n4, per * (p.rank + 1));
+  // plain all-reduce: the scale rides on the slice owner's sum, so no extra pass over the result is needed
+  const float presc = (!a.do_update && a.hyper) ? h.gscale : 1.f;
   if (ok) {
     if (MULTIMEM) {
       for (long long i = lo + i0; i < hi; i += stride) {
-        const float4 g = multimem_ld_reduce4(p.grd_mc + 4 * i);
+        float4 g = multimem_ld_reduce4(p.grd_mc + 4 * i);
+        if (presc != 1.f) { g.x *= presc; g.y *= presc; g.z *= presc; g.w *= presc; }
         multimem_st4(p.red_mc + 4 * i, g);
       }
     } else {
-      // 4 independent float4 per thread and per peer in flight: NVLink round trips are long, so the loop is
-      // unrolled to keep ~1 MB of loads outstanding per GPU
-      constexpr int U = 4;
+      // Loads from ALL peers are issued before the first sum (2 float4 per peer and thread = 16 independent loads in
+      // flight per thread at N = 8): an NVLink round trip is microseconds, so the reduction is latency-bound unless
+      // every link has requests outstanding all the time.  The sum itself stays in rank order (bit-identical replicas).
+      constexpr int U = 2;
       for (long long i = lo + i0; i < hi; i += stride * U) {
-        float4 g[U];
+        float4 x[MAX_RANKS][U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long long k = i + u * stride;
-          g[u] = k < hi ? ld_peer4(p.grd[0] + 4 * k) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        for (int r = 1; r < p.world; ++r) {
-          float4 x[U];
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r < p.world) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const long long k = i + u * stride;
-            x[u] = k < hi ? ld_peer4(p.grd[r] + 4 * k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int u = 0; u < U; ++u) {
+              const long long k = i + u * stride;
+              x[r][u] = k < hi ? ld_peer4(p.grd[r] + 4 * k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
           }
-#pragma unroll
-          for (int u = 0; u < U; ++u) { g[u].x += x[u].x; g[u].y += x[u].y; g[u].z += x[u].z; g[u].w += x[u].w; }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
+          float4 g = x[0][u];
+#pragma unroll
+          for (int r = 1; r < MAX_RANKS; ++r) {
+            if (r < p.world) { g.x += x[r][u].x; g.y += x[r][u].y; g.z += x[r][u].z; g.w += x[r][u].w; }
+          }
           const long long k = i + u * stride;
-          if (k < hi)
-            for (int r = 0; r < p.world; ++r) st_peer4(p.red[r] + 4 * k, g[u]);
+          if (k < hi) {
+            if (presc != 1.f) { g.x *= presc; g.y *= presc; g.z *= presc; g.w *= presc; }
+            for (int d = 0; d < p.world; ++d) {
+              const int r = (p.rank + d) % p.world;   // ring order spreads the stores over the links
+              st_peer4(p.red[r] + 4 * k, g);
+            }
+          }
         }
       }
     }
@@ -286,13 +297,6 @@ ar_twoshot_kernel(ARParams p, AdamBufs a, unsigned int* status) {
       }
       if (ok)
         for (long long i = i0; i < p.n4; i += stride) update4(a, h, i, red[i]);
-    } else if (a.hyper) {
-      float4* r4 = reinterpret_cast<float4*>(p.red[p.rank]);
-      for (long long i = i0; i < p.n4; i += stride) {
-        float4 g = r4[i];
-        g.x *= h.gscale; g.y *= h.gscale; g.z *= h.gscale; g.w *= h.gscale;
-        r4[i] = g;
-      }
     }
     if (a.zero_grad) {
       const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -303,6 +307,132 @@ ar_twoshot_kernel(ARParams p, AdamBufs a, unsigned int* status) {
   ok = cross_barrier(p, SIG_DONE, bases[SIG_DONE], status, 23, &sh_ok) && ok;
   publish_bases(my, bases, p.world,
                 (1u << SIG_ARRIVE) | (1u << SIG_DONE) | (1u << SIG_PHASE) | (clip ? (1u << SIG_GRID) : 0u));
+}
+
+// ------------------------------------------------------------------------------------------ push (small buckets)
+// Latency-optimal form for buckets of up to a few MB: ONE NVLink traversal and no cross-GPU barrier.
+//   1. every block loads its 16 KB chunk of the local gradients and STORES it into a per-source inbox on every peer,
+//      then publishes one flag per (source, block) on that peer (st.release.sys after a block barrier);
+//   2. the block spins on ITS OWN local flags (one per peer) and sums the chunk in rank order 0..N-1 (own
+//      contribution from registers), so every replica computes bit-identical sums;
+//   3. Adam(W) + bf16 recast (or the plain scaled sum), and the local gradients are cleared at once: nobody reads
+//      them remotely in this protocol.
+// The inbox is double-buffered by the parity of a device-resident epoch, so "done" needs no round: a peer can only
+// write parity e again in launch e+2, and its launch e+1 completed only after it saw this rank's flags of e+1,
+// which this rank's launch e+1 sends after its launch e (all reads of parity e) has finished.
+// Blocks never wait before they send, so any schedule of the grid makes progress: no co-residency requirement.
+// Several optimizers' arenas ("segments") travel in one launch; the Adam step counters advance in the same kernel.
+constexpr int PUSH_THREADS = 256, PUSH_U = 4, PUSH_MAX_SEG = 4, PUSH_MAX_BLOCKS = 1024;
+constexpr int PUSH_CHUNK4 = PUSH_THREADS * PUSH_U;  // float4 per block
+
+struct PushSeg {
+  float* grd;            // local gradients of this segment
+  float* out;            // plain all-reduce: where the (scaled) sum goes; null with an update
+  float *val, *m, *v;
+  __nv_bfloat16* shadow;
+  const unsigned char* row_flags;
+  float* hyper;          // device hyper block; its step counter advances here when `advance`
+  long long n4;          // float4 count
+  long long off4;        // offset of the segment inside an inbox plane (float4)
+  int first_block;
+  int advance, zero_grad;
+};
+struct PushParams {
+  float* inbox[MAX_RANKS];         // every rank's inbox  [2][world][plane4] float4
+  unsigned int* flags[MAX_RANKS];  // every rank's flags  [2][world][PUSH_MAX_BLOCKS]
+  unsigned int* ctl;               // local: [0] epoch of the last finished launch, [1] ticket
+  long long plane4;
+  int world, rank, nseg;
+  unsigned long long wait_ns;
+  PushSeg seg[PUSH_MAX_SEG];
+};
+
+__global__ void __launch_bounds__(PUSH_THREADS)
+ar_push_kernel(const __grid_constant__ PushParams p, unsigned int* status) {
+  __shared__ int sh_ok;
+  const unsigned int epoch = ld_acquire_sys(p.ctl) + 1u;
+  const unsigned int par = epoch & 1u;
+  int s = 0;
+  while (s + 1 < p.nseg && (int)blockIdx.x >= p.seg[s + 1].first_block) ++s;
+  const PushSeg& sg = p.seg[s];
+  const long long base = (long long)((int)blockIdx.x - sg.first_block) * PUSH_CHUNK4 + threadIdx.x;
+  float4 g[PUSH_U];
+#pragma unroll
+  for (int u = 0; u < PUSH_U; ++u) {
+    const long long i = base + u * PUSH_THREADS;
+    g[u] = i < sg.n4 ? reinterpret_cast<const float4*>(sg.grd)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  // ---- 1. push to every peer (ring order spreads the traffic over the links), then one flag per peer
+  const long long plane = ((long long)par * p.world + p.rank) * p.plane4 + sg.off4;
+  for (int d = 1; d < p.world; ++d) {
+    float* dst = p.inbox[(p.rank + d) % p.world] + 4 * plane;
+#pragma unroll
+    for (int u = 0; u < PUSH_U; ++u) {
+      const long long i = base + u * PUSH_THREADS;
+      if (i < sg.n4) st_peer4(dst + 4 * i, g[u]);
+    }
+  }
+  if (threadIdx.x == 0) sh_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < p.world - 1) {
+    const int peer = (p.rank + 1 + threadIdx.x) % p.world;
+    __threadfence_system();
+    st_release_sys(p.flags[peer] + ((size_t)par * p.world + p.rank) * PUSH_MAX_BLOCKS + blockIdx.x, epoch);
+  }
+  // ---- 2. wait for this block's chunk from every peer (local polls)
+  if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+    if (!wait_flag_ge_ns(p.flags[p.rank] + ((size_t)par * p.world + threadIdx.x) * PUSH_MAX_BLOCKS + blockIdx.x, epoch, status,
+                         30, threadIdx.x, p.wait_ns))
+      sh_ok = 0;
+  }
+  __syncthreads();
+  const bool ok = sh_ok != 0;
+  // ---- 3. rank-ordered sum, update, clear
+  AdamHyper h;
+  if (sg.hyper) {
+    h = load_hyper(sg.hyper);
+    if (sg.advance) { h.b1t *= h.beta1; h.b2t *= h.beta2; }
+  }
+  if (ok) {
+    const float* mine = p.inbox[p.rank];
+#pragma unroll
+    for (int u = 0; u < PUSH_U; ++u) {
+      const long long i = base + u * PUSH_THREADS;
+      if (i >= sg.n4) continue;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < p.world; ++r) {
+        const float4 x = r == p.rank ? g[u] : ld_peer4(mine + 4 * ((((long long)par * p.world + r) * p.plane4 + sg.off4) + i));
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      }
+      if (sg.val) {
+        AdamBufs a;
+        a.val = sg.val; a.m = sg.m; a.v = sg.v; a.shadow = sg.shadow; a.row_flags = sg.row_flags;
+        update4(a, h, i, acc);
+      } else if (sg.out) {
+        const float sc = sg.hyper ? h.gscale : 1.f;
+        reinterpret_cast<float4*>(sg.out)[i] = make_float4(acc.x * sc, acc.y * sc, acc.z * sc, acc.w * sc);
+      }
+      if (sg.zero_grad) reinterpret_cast<float4*>(sg.grd)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  // ---- 4. last block publishes the epoch and the advanced step counters
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1) {
+      p.ctl[1] = 0u;
+      for (int k = 0; k < p.nseg; ++k) {
+        float* hy = p.seg[k].hyper;
+        if (hy && p.seg[k].advance) {
+          hy[NB_H_T] += 1.f;
+          hy[NB_H_B1T] *= hy[NB_H_BETA1];
+          hy[NB_H_B2T] *= hy[NB_H_BETA2];
+        }
+      }
+      __threadfence();
+      st_release_sys(p.ctl, epoch);
+    }
+  }
 }
 
 // Waits on a flag that the caller controls: exercises the bounded-wait → status path without any
@@ -397,6 +527,56 @@ int nb_allreduce_fused(int algo, int world, int rank, void* const* grd_ptrs, voi
     if (algo == 1) ar_twoshot_kernel<false><<<grid, threads, 0, s>>>(p, a, status);
     else ar_twoshot_kernel<true><<<grid, threads, 0, s>>>(p, a, status);
   }
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+// Push all-reduce of up to PUSH_MAX_SEG arenas in one launch (see ar_push_kernel).  Per segment k: grd[k] (local,
+// n[k] floats, multiple of 4), and either an update (val/m/v/shadow/row_flags/hyper; `advance` also steps the Adam
+// counters t, β₁ᵗ, β₂ᵗ inside the kernel) or a plain sum into out[k] (scaled by hyper[GSCALE] when hyper[k] is given).
+// inbox_ptrs / flag_ptrs: every rank's inbox (2·world·plane floats, plane = Σ n[k] rounded up to 1024-float chunks
+// per segment) and flag block (2·world·1024 u32, zero-initialised); ctl: 4 local u32, zero-initialised.
+int nb_push_blocks(long long n) { return (int)((n / 4 + PUSH_CHUNK4 - 1) / PUSH_CHUNK4); }
+int nb_allreduce_push(int world, int rank, int nseg, void* const* inbox_ptrs, void* const* flag_ptrs, unsigned int* ctl,
+                      float* const* grd, float* const* out, float* const* val, float* const* m, float* const* v,
+                      void* const* shadow, const unsigned char* const* row_flags, float* const* hyper, const long long* n,
+                      int advance, int zero_grad, unsigned int spin_limit, unsigned int* status, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || nseg < 1 || nseg > PUSH_MAX_SEG) return NB_ERR_BAD_ARG;
+  PushParams p;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < world; ++r) {
+    p.inbox[r] = (float*)inbox_ptrs[r];
+    p.flags[r] = (unsigned int*)flag_ptrs[r];
+  }
+  p.ctl = ctl;
+  p.world = world; p.rank = rank; p.nseg = nseg;
+  p.wait_ns = 256ull * (spin_limit ? spin_limit : (1u << 24));
+  int blocks = 0;
+  long long off4 = 0;
+  for (int k = 0; k < nseg; ++k) {
+    if (n[k] <= 0 || n[k] % 4) return NB_ERR_UNALIGNED;
+    PushSeg& sg = p.seg[k];
+    sg.grd = grd[k];
+    sg.out = out ? out[k] : nullptr;
+    sg.val = val ? val[k] : nullptr;
+    sg.m = m ? m[k] : nullptr;
+    sg.v = v ? v[k] : nullptr;
+    sg.shadow = shadow ? (__nv_bfloat16*)shadow[k] : nullptr;
+    sg.row_flags = row_flags ? row_flags[k] : nullptr;
+    sg.hyper = hyper ? hyper[k] : nullptr;
+    sg.n4 = n[k] / 4;
+    sg.off4 = off4;
+    sg.first_block = blocks;
+    sg.advance = advance && sg.val != nullptr;
+    sg.zero_grad = zero_grad;
+    if (sg.val && (!sg.m || !sg.v || !sg.hyper)) return NB_ERR_BAD_ARG;
+    const int nb_ = nb_push_blocks(n[k]);
+    blocks += nb_;
+    off4 += (long long)nb_ * PUSH_CHUNK4;
+  }
+  if (blocks > PUSH_MAX_BLOCKS) return NB_ERR_TOO_LARGE;
+  p.plane4 = off4;
+  ar_push_kernel<<<blocks, PUSH_THREADS, 0, (cudaStream_t)stream>>>(p, status);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

@@ -123,6 +123,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   return false;
 }
 
+// Wall-clock bounded variants for kernels whose waits depend on OTHER GPUs (a peer may be late by a host-side
+// hiccup of seconds; a poll count says little about elapsed time).  `limit_ns` is measured on %globaltimer.
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait_ns(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int where,
+                                             unsigned long long limit_ns) {
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 1024; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (globaltimer_ns() - t0 > limit_ns) break;
+  }
+  report(status, NB_ST_MBAR_TIMEOUT, where, parity);
+  return false;
+}
+
 // ---------------------------------------------------------------- TMA (no multicast anywhere)
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -314,6 +335,40 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* p, unsigned int
   }
   report(status, NB_ST_PEER_TIMEOUT, where, peer);
   return false;
+}
+
+// Same, bounded by elapsed time instead of a poll count.
+__device__ __forceinline__ bool wait_flag_ge_ns(const unsigned int* p, unsigned int target, unsigned int* status,
+                                                unsigned int where, unsigned int peer, unsigned long long limit_ns) {
+  if ((int)(ld_acquire_sys(p) - target) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      if ((int)(ld_acquire_sys(p) - target) >= 0) return true;
+      __nanosleep(20);
+    }
+    if (globaltimer_ns() - t0 > limit_ns) break;
+  }
+  report(status, NB_ST_PEER_TIMEOUT, where, peer);
+  return false;
+}
+
+// ---------------------------------------------------------------- untiled bulk copies (TMA engine, no tensor map)
+// global → shared, completion on an mbarrier; both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// shared → global, tracked by the thread's bulk async-groups.
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all_but_one() {
+  asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- small math helpers

@@ -7,23 +7,27 @@
 // Both are ONE kernel per rank built around the tcgen05 main loop of gemm_tcgen05.cu (TMA → smem ring →
 // tcgen05.mma into TMEM → epilogue warps), with the transfer overlapped tile by tile:
 //
-//   AG→GEMM   a few "fetch" CTAs pull the peers' row shards with plain P2P vector loads into a local staging
-//             buffer, 128-row block by block, in ring order starting at the neighbour, and publish a per-block
-//             ready flag; the GEMM CTAs walk the tiles in the same order (own rows first), their TMA producer
-//             waits on the flag of a row block before loading it.  A remote row crosses NVLink exactly once,
-//             however many N tiles consume it.  No TMA instruction ever addresses peer memory here, and there
-//             is no multicast anywhere.
-//   GEMM→RS   the epilogue writes each bf16 partial tile straight into the OWNER rank's slot buffer
-//             slot[src][row, :] with P2P stores and bumps the owner's per-row-block arrival counter
-//             (red.release.sys); tiles owned by other ranks are computed first.  When a CTA runs out of tiles
-//             it reduces local row blocks whose P·tiles_n arrivals are complete — in rank order, so the sum
-//             is deterministic — optionally adds a residual, and writes the bf16 result.
+//   AG→GEMM   a few "fetch" CTAs pull the peers' row shards into a local staging buffer, 128-row block by block, in
+//             ring order starting at the neighbour, and publish a per-block ready flag; the GEMM CTAs walk the
+//             tiles in the same order (own rows first), their TMA producer waits on the flag of a row block before
+//             loading it.  A remote row crosses NVLink exactly once, however many N tiles consume it.  The fetch
+//             itself is a ring of untiled bulk copies (peer global → shared → local global, 32 KB each, five in
+//             flight per CTA) issued by one thread, so a handful of CTAs keep megabytes of reads outstanding;
+//             shards whose rows are not contiguous fall back to P2P vector loads.  No copy carries a multicast
+//             qualifier, and the tensor-map loads of the GEMM only ever address local memory.
+//   GEMM→RS   the epilogue converts each partial tile to bf16 in shared memory (128-byte swizzle) and ships it to
+//             the OWNER rank's slot buffer slot[src][row, :] with two tensor-map TMA stores over NVLink, then
+//             bumps the owner's per-row-block arrival counter (red.release.sys) once the store has completed;
+//             tiles owned by other ranks are computed first.  When a CTA runs out of tiles it reduces local row
+//             blocks whose P·tiles_n arrivals are complete — in rank order, so the sum is deterministic —
+//             optionally adds a residual, and writes the bf16 result.
 //
-// Flags are monotone epochs in device memory (graph-replay safe); every wait is bounded and reports
-// NB_ST_PEER_TIMEOUT / NB_ST_MBAR_TIMEOUT through `status`.  The reference has no tensor parallelism
+// Flags are monotone epochs in device memory (graph-replay safe); every wait is bounded by elapsed time (a peer may
+// be late by a host-side hiccup) and reports NB_ST_PEER_TIMEOUT / NB_ST_MBAR_TIMEOUT through `status`.  The reference has no tensor parallelism
 // (noeira/nn/distributed/strategy.mojo:1-33 lists DDP and ZeRO only); the baseline these kernels are measured
 // against is NCCL all_gather_into_tensor / reduce_scatter_tensor around the unfused GEMM.
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "gemm_api.h"
@@ -31,10 +35,15 @@
 namespace {
 using namespace nb;
 
-constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16, STAGES = 6;
+constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16, STAGES = 5;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_RANKS = 8;
 constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+// reduce-scatter epilogue staging: two buffers of one bf16 tile = 2 boxes of [128 rows x 64 columns], 128-byte swizzle
+constexpr uint32_t EPI_BOX_BYTES = BM * 64 * 2, EPI_BUF_BYTES = 2 * EPI_BOX_BYTES, EPI_BYTES = 2 * EPI_BUF_BYTES;
+// all-gather fetch ring (fetch CTAs reuse the dynamic shared memory of the GEMM pipeline)
+constexpr int FETCH_SLOTS = 6;
+constexpr uint32_t FETCH_CHUNK = 32768;
 // control block (u32, local device memory, zero-initialised once):
 //   [0] epoch of the last completed launch   [1] ticket   [2] arrive counter (peers add)   [3] done counter
 //   [16 + i] per-row-block flag / arrival counter
@@ -53,7 +62,7 @@ struct TpParams {
   int ld_res;           // RS: residual pitch
   const float* bias;
   int act;
-  unsigned int spin_limit;
+  unsigned long long wait_ns;  // bound of every wait that depends on a peer; mbarrier waits get twice that
   const __nv_bfloat16* x_peer[MAX_RANKS];  // AG: every rank's shard [Ms, K]
   __nv_bfloat16* stage;                    // AG: local staging [P·Ms, K]
   __nv_bfloat16* slot_peer[MAX_RANKS];     // RS: every rank's slot buffer [P][Ms, N]
@@ -61,6 +70,9 @@ struct TpParams {
   __nv_bfloat16* D;                        // AG: [M, N] local output; RS: [Ms, N] reduced output
   const __nv_bfloat16* residual;           // RS: optional [Ms, N]
   unsigned int* status;
+};
+struct SlotMaps {
+  CUtensorMap m[MAX_RANKS];  // RS: every rank's slot buffer [P·Ms, N] as seen from this process (box 64 x 128)
 };
 
 __device__ __forceinline__ float act_apply(int act, float v) {
@@ -84,9 +96,6 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_peer16(void* p, uint4 v) {
-  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -96,10 +105,15 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ bool wait_ge_gpu(const unsigned int* p, unsigned int target, unsigned int* status,
-                                            unsigned int where, unsigned int limit) {
-  for (unsigned int it = 0; it < limit; ++it) {
-    if ((int)(ld_acquire_gpu(p) - target) >= 0) return true;
-    __nanosleep(40);
+                                            unsigned int where, unsigned long long limit_ns) {
+  if ((int)(ld_acquire_gpu(p) - target) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      if ((int)(ld_acquire_gpu(p) - target) >= 0) return true;
+      __nanosleep(40);
+    }
+    if (globaltimer_ns() - t0 > limit_ns) break;
   }
   report(status, NB_ST_PEER_TIMEOUT, where, target);
   return false;
@@ -116,15 +130,19 @@ __device__ __forceinline__ int ordered_block(const TpParams& p, int pos, int blo
 // ------------------------------------------------------------------------------------------ shared main loop
 struct Pipe {
   uint8_t* smem;
+  uint8_t* epi;  // reduce-scatter staging (EPI_BYTES, 1024-byte aligned)
   uint64_t *full_bar, *empty_bar, *tfull_bar, *tempty_bar;
   uint32_t* tmem_slot;
   volatile uint32_t* abort_flag;
+  unsigned long long mbar_ns;
 };
 
-__device__ __forceinline__ Pipe carve_pipe(uint8_t* smem_raw) {
+__device__ __forceinline__ Pipe carve_pipe(uint8_t* smem_raw, unsigned long long wait_ns) {
   Pipe q;
   q.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  q.full_bar = reinterpret_cast<uint64_t*>(q.smem + STAGES * STAGE_BYTES);
+  q.epi = q.smem + STAGES * STAGE_BYTES;
+  q.mbar_ns = 2ull * wait_ns;
+  q.full_bar = reinterpret_cast<uint64_t*>(q.smem + STAGES * STAGE_BYTES + EPI_BYTES);
   q.empty_bar = q.full_bar + STAGES;
   q.tfull_bar = q.empty_bar + STAGES;
   q.tempty_bar = q.tfull_bar + 2;
@@ -136,7 +154,7 @@ __device__ __forceinline__ Pipe carve_pipe(uint8_t* smem_raw) {
 __device__ __forceinline__ void issue_tile_mma(const Pipe& q, uint32_t d_tmem, uint32_t idesc, int b_mn, int num_kb,
                                                int& stage, uint32_t& phase, unsigned int* status, bool& ok) {
   for (int kb = 0; kb < num_kb; ++kb) {
-    if (*q.abort_flag || !mbar_wait(&q.full_bar[stage], phase, status, 403)) { ok = false; *q.abort_flag = 1; return; }
+    if (*q.abort_flag || !mbar_wait_ns(&q.full_bar[stage], phase, status, 403, q.mbar_ns)) { ok = false; *q.abort_flag = 1; return; }
     tc_fence_after();
     const uint32_t sa = smem_u32(q.smem + stage * STAGE_BYTES), sb = sa + A_BYTES;
 #pragma unroll
@@ -216,55 +234,109 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmOwn, const __grid_consta
         __threadfence_system();
         for (int r = 0; r < p.world; ++r) red_release_sys_add(p.ctl_peer[r] + CTL_ARRIVE, 1u);
       }
-      ok = wait_flag_ge(ctl + CTL_ARRIVE, epoch * (unsigned int)p.world, p.status, 410, 0u, p.spin_limit);
+      ok = wait_flag_ge_ns(ctl + CTL_ARRIVE, epoch * (unsigned int)p.world, p.status, 410, 0u, p.wait_ns);
+      asm volatile("fence.proxy.async.global;" ::: "memory");  // the bulk copies below read what the peers' kernels wrote
       sh_ok = ok;
     }
     __syncthreads();
     bool ok = sh_ok;
     const int row_vecs = p.K / 8;  // 16-byte vectors per row
     const int remote_blocks = (p.world - 1) * bpr;
-    for (int pos = blockIdx.x; pos < remote_blocks && ok; pos += p.n_fetch) {
-      const int gb = ordered_block(p, pos, bpr, true);  // remote ranks in ring order
-      const int owner = gb / bpr, lb = gb - owner * bpr;
-      const __nv_bfloat16* src = p.x_peer[owner] + (size_t)lb * BM * p.ldx;
-      __nv_bfloat16* dst = p.stage + (size_t)gb * BM * p.ldx;
-      const int total = BM * row_vecs;
-      for (int i0 = threadIdx.x; i0 < total; i0 += NUM_THREADS * 8) {
-        uint4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int i = i0 + u * NUM_THREADS;
-          if (i < total) {
-            const int rr = i / row_vecs, cv = i - rr * row_vecs;
-            v[u] = ld_peer16(src + (size_t)rr * p.ldx + cv * 8);
+    if (p.ldx == p.K) {
+      // Rows are contiguous: a row block is one byte range.  One thread runs a ring of bulk copies
+      // peer → shared → local; the other threads of the CTA have nothing to do.
+      if (threadIdx.x == 0 && ok) {
+        uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+        uint64_t* fbar = reinterpret_cast<uint64_t*>(ring + (size_t)FETCH_SLOTS * FETCH_CHUNK);
+        for (int i = 0; i < FETCH_SLOTS; ++i) mbar_init(&fbar[i], 1);
+        fence_barrier_init();
+        const uint32_t block_bytes = (uint32_t)BM * (uint32_t)p.K * 2u;
+        const uint32_t cpb = (block_bytes + FETCH_CHUNK - 1) / FETCH_CHUNK;  // chunks per row block
+        int my_blocks = 0;
+        for (int pos = blockIdx.x; pos < remote_blocks; pos += p.n_fetch) ++my_blocks;
+        const uint32_t total = (uint32_t)my_blocks * cpb;
+        uint32_t issued = 0;
+        for (uint32_t done = 0; done < total && ok; ++done) {
+          // keep FETCH_SLOTS - 1 loads in flight ahead of the chunk being stored
+          while (issued < total && issued < done + FETCH_SLOTS - 1 + (done == 0 ? 1 : 0)) {
+            const uint32_t bi = issued / cpb, ci = issued - bi * cpb;
+            const int gb = ordered_block(p, blockIdx.x + (int)bi * p.n_fetch, bpr, true);
+            const int owner = gb / bpr, lb = gb - owner * bpr;
+            const uint32_t off = ci * FETCH_CHUNK;
+            const uint32_t bytes = min(FETCH_CHUNK, block_bytes - off);
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.x_peer[owner]) + (size_t)lb * block_bytes + off;
+            const uint32_t slot = issued % FETCH_SLOTS;
+            mbar_expect_tx(&fbar[slot], bytes);
+            bulk_load(ring + (size_t)slot * FETCH_CHUNK, src, bytes, &fbar[slot]);
+            ++issued;
+          }
+          const uint32_t bi = done / cpb, ci = done - bi * cpb;
+          const int gb = ordered_block(p, blockIdx.x + (int)bi * p.n_fetch, bpr, true);
+          const uint32_t off = ci * FETCH_CHUNK;
+          const uint32_t bytes = min(FETCH_CHUNK, block_bytes - off);
+          const uint32_t slot = done % FETCH_SLOTS;
+          if (!mbar_wait_ns(&fbar[slot], (done / FETCH_SLOTS) & 1u, p.status, 412, 2ull * p.wait_ns)) { ok = false; break; }
+          bulk_store(reinterpret_cast<uint8_t*>(p.stage) + (size_t)gb * block_bytes + off, ring + (size_t)slot * FETCH_CHUNK, bytes);
+          tma_store_commit();
+          if (ci == cpb - 1) {
+            // the whole row block has been written locally: make it visible, then publish its flag
+            tma_store_wait_all();
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence();
+            st_release_gpu(ctl + CTL_BLOCKS + gb, epoch);
+          } else {
+            tma_store_wait_read();  // the slot may be refilled once the store has read it
           }
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int i = i0 + u * NUM_THREADS;
-          if (i < total) {
-            const int rr = i / row_vecs, cv = i - rr * row_vecs;
-            *reinterpret_cast<uint4*>(dst + (size_t)rr * p.ldx + cv * 8) = v[u];
-          }
-        }
+        tma_store_wait_all();
+        sh_ok = ok;
       }
-      __threadfence();
       __syncthreads();
-      if (threadIdx.x == 0) st_release_gpu(ctl + CTL_BLOCKS + gb, epoch);
+      ok = sh_ok;
+    } else {
+      for (int pos = blockIdx.x; pos < remote_blocks && ok; pos += p.n_fetch) {
+        const int gb = ordered_block(p, pos, bpr, true);  // remote ranks in ring order
+        const int owner = gb / bpr, lb = gb - owner * bpr;
+        const __nv_bfloat16* src = p.x_peer[owner] + (size_t)lb * BM * p.ldx;
+        __nv_bfloat16* dst = p.stage + (size_t)gb * BM * p.ldx;
+        const int total = BM * row_vecs;
+        for (int i0 = threadIdx.x; i0 < total; i0 += NUM_THREADS * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * NUM_THREADS;
+            if (i < total) {
+              const int rr = i / row_vecs, cv = i - rr * row_vecs;
+              v[u] = ld_peer16(src + (size_t)rr * p.ldx + cv * 8);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * NUM_THREADS;
+            if (i < total) {
+              const int rr = i / row_vecs, cv = i - rr * row_vecs;
+              *reinterpret_cast<uint4*>(dst + (size_t)rr * p.ldx + cv * 8) = v[u];
+            }
+          }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_gpu(ctl + CTL_BLOCKS + gb, epoch);
+      }
     }
     // nobody may overwrite a shard while a peer still reads it: wait until every rank has fetched everything
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence_system();
       for (int r = 0; r < p.world; ++r) red_release_sys_add(p.ctl_peer[r] + CTL_DONE, 1u);
-      wait_flag_ge(ctl + CTL_DONE, epoch * (unsigned int)(p.world * p.n_fetch), p.status, 411, 0u, p.spin_limit);
+      wait_flag_ge_ns(ctl + CTL_DONE, epoch * (unsigned int)(p.world * p.n_fetch), p.status, 411, 0u, p.wait_ns);
     }
     finish_epoch(ctl, epoch);
     return;
   }
 
   // ------------------------------------------------------------------ GEMM CTAs
-  Pipe q = carve_pipe(smem_raw);
+  Pipe q = carve_pipe(smem_raw, p.wait_ns);
   pipe_setup(q, warp);
   const uint32_t tmem_base = *q.tmem_slot;
   const int ncta = gridDim.x - p.n_fetch, cta = blockIdx.x - p.n_fetch;
@@ -281,12 +353,12 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmOwn, const __grid_consta
         const int owner = gb / bpr;
         const bool own = owner == p.rank;
         if (!own) {
-          if (!wait_ge_gpu(ctl + CTL_BLOCKS + gb, epoch, p.status, 420, p.spin_limit)) { ok = false; *q.abort_flag = 1; break; }
+          if (!wait_ge_gpu(ctl + CTL_BLOCKS + gb, epoch, p.status, 420, p.wait_ns)) { ok = false; *q.abort_flag = 1; break; }
           asm volatile("fence.proxy.async.global;" ::: "memory");  // staged rows were written through the generic proxy
         }
         const int row0 = own ? (gb - owner * bpr) * BM : gb * BM;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (*q.abort_flag || !mbar_wait(&q.empty_bar[stage], phase ^ 1u, p.status, 401)) { ok = false; *q.abort_flag = 1; break; }
+          if (*q.abort_flag || !mbar_wait_ns(&q.empty_bar[stage], phase ^ 1u, p.status, 401, q.mbar_ns)) { ok = false; *q.abort_flag = 1; break; }
           mbar_expect_tx(&q.full_bar[stage], STAGE_BYTES);
           tma_load_2d(q.smem + stage * STAGE_BYTES, own ? &tmOwn : &tmStage, &q.full_bar[stage], kb * BK, row0);
           load_b_tile(q, &tmB, p.b_mn, stage, kb, nb_);
@@ -301,7 +373,7 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmOwn, const __grid_consta
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int t = cta; t < num_tiles && ok; t += ncta) {
-        if (*q.abort_flag || !mbar_wait(&q.tempty_bar[acc], acc_phase ^ 1u, p.status, 402)) { ok = false; *q.abort_flag = 1; break; }
+        if (*q.abort_flag || !mbar_wait_ns(&q.tempty_bar[acc], acc_phase ^ 1u, p.status, 402, q.mbar_ns)) { ok = false; *q.abort_flag = 1; break; }
         tc_fence_after();
         issue_tile_mma(q, tmem_base + acc * BN, idesc, p.b_mn, p.num_kb, stage, phase, p.status, ok);
         if (!ok) break;
@@ -317,7 +389,7 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmOwn, const __grid_consta
     for (int t = cta; t < num_tiles && ok; t += ncta) {
       const int pos = t / p.tiles_n, nb_ = t - pos * p.tiles_n;
       const int gb = ordered_block(p, pos, bpr, false);
-      if (*q.abort_flag || !mbar_wait(&q.tfull_bar[acc], acc_phase, p.status, 404)) { ok = false; *q.abort_flag = 1; break; }
+      if (*q.abort_flag || !mbar_wait_ns(&q.tfull_bar[acc], acc_phase, p.status, 404, q.mbar_ns)) { ok = false; *q.abort_flag = 1; break; }
       tc_fence_after();
       const int row = gb * BM + quarter * 32 + lane;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
@@ -369,13 +441,14 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmOwn, const __grid_consta
 
 // ------------------------------------------------------------------------------------------ GEMM → RS
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TpParams p) {
+tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ SlotMaps slots, const TpParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   unsigned int* ctl = p.ctl_peer[p.rank];
   const unsigned int epoch = ld_acquire_gpu(ctl + CTL_EPOCH) + 1u;
   const int bpr = p.Ms / BM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  Pipe q = carve_pipe(smem_raw);
+  Pipe q = carve_pipe(smem_raw, p.wait_ns);
   pipe_setup(q, warp);
   const uint32_t tmem_base = *q.tmem_slot;
   const int ncta = gridDim.x, cta = blockIdx.x;
@@ -395,7 +468,7 @@ tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int pos = t / p.tiles_n, nb_ = t - pos * p.tiles_n;
         const int gb = ordered_block(p, pos, bpr, true);  // other ranks' rows first
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (*q.abort_flag || !mbar_wait(&q.empty_bar[stage], phase ^ 1u, p.status, 501)) { ok = false; *q.abort_flag = 1; break; }
+          if (*q.abort_flag || !mbar_wait_ns(&q.empty_bar[stage], phase ^ 1u, p.status, 501, q.mbar_ns)) { ok = false; *q.abort_flag = 1; break; }
           mbar_expect_tx(&q.full_bar[stage], STAGE_BYTES);
           tma_load_2d(q.smem + stage * STAGE_BYTES, &tmA, &q.full_bar[stage], kb * BK, gb * BM);
           load_b_tile(q, &tmB, p.b_mn, stage, kb, nb_);
@@ -410,7 +483,7 @@ tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int t = cta; t < num_tiles && ok; t += ncta) {
-        if (*q.abort_flag || !mbar_wait(&q.tempty_bar[acc], acc_phase ^ 1u, p.status, 502)) { ok = false; *q.abort_flag = 1; break; }
+        if (*q.abort_flag || !mbar_wait_ns(&q.tempty_bar[acc], acc_phase ^ 1u, p.status, 502, q.mbar_ns)) { ok = false; *q.abort_flag = 1; break; }
         tc_fence_after();
         issue_tile_mma(q, tmem_base + acc * BN, idesc, p.b_mn, p.num_kb, stage, phase, p.status, ok);
         if (!ok) break;
@@ -425,51 +498,78 @@ tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     bool ok = true;
     // peers must have finished consuming the previous launch before their slots are overwritten
     if (warp == 2 && lane == 0)
-      if (!wait_flag_ge(ctl + CTL_ARRIVE, epoch * (unsigned int)p.world, p.status, 510, 0u, p.spin_limit)) *q.abort_flag = 1;
+      if (!wait_flag_ge_ns(ctl + CTL_ARRIVE, epoch * (unsigned int)p.world, p.status, 510, 0u, p.wait_ns)) *q.abort_flag = 1;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     // Every epilogue thread executes every named barrier below, whatever happened before it (a thread that
     // left early would strand the others), so failures only switch the work off.
-    for (int t = cta; t < num_tiles; t += ncta) {
+    // One thread (`issuer`) owns the TMA stores of this CTA, so their bulk async-groups complete in tile order.
+    const bool issuer = warp == 2 && lane == 0;
+    int prev_owner = -1, prev_lb = 0, it = 0;
+    for (int t = cta; t < num_tiles; t += ncta, ++it) {
       const int pos = t / p.tiles_n, nb_ = t - pos * p.tiles_n;
       const int gb = ordered_block(p, pos, bpr, true);
       const int owner = gb / bpr, lb = gb - owner * bpr;
-      if (ok && (*q.abort_flag || !mbar_wait(&q.tfull_bar[acc], acc_phase, p.status, 504))) { ok = false; *q.abort_flag = 1; }
+      uint8_t* buf = q.epi + (size_t)(it & 1) * EPI_BUF_BYTES;
+      if (ok && (*q.abort_flag || !mbar_wait_ns(&q.tfull_bar[acc], acc_phase, p.status, 504, q.mbar_ns))) { ok = false; *q.abort_flag = 1; }
       if (ok) {
         tc_fence_after();
-        const int lrow = lb * BM + quarter * 32 + lane;  // row inside the owner's shard
-        __nv_bfloat16* slot = p.slot_peer[owner] + ((size_t)p.rank * p.Ms + lrow) * p.ld_slot;
+        const int row = quarter * 32 + lane;  // row inside the tile
         const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr0 + c0, r);
           tmem_ld_wait();
-          const int col0 = nb_ * BN + c0;
-          if (col0 < p.N) {
+          // 32 columns = 4 chunks of 16 bytes inside the 64-column box `c0 / 64`; chunk c of row r sits at c ^ (r & 7)
+          uint8_t* box = buf + (size_t)(c0 >> 6) * EPI_BOX_BYTES + (size_t)row * 128;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j + 8 <= p.N) {
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
-                               h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
-                               h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
-                               h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                st_peer16(slot + col0 + j, pk);
-              }
-            }
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                           h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                           h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                           h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            const int chunk = ((c0 & 63) + j) >> 3;
+            *reinterpret_cast<uint4*>(box + (size_t)((chunk ^ (row & 7)) << 4)) = pk;
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&q.tempty_bar[acc]);
-        __threadfence_system();
+        fence_proxy_async();  // the TMA store reads these shared-memory writes
       }
-      // all 128 rows of the tile have been pushed → one arrival on the owner's row-block counter
+      // the buffer of the NEXT tile is the one the previous tile's store reads: that read must be over before
+      // anyone passes this barrier
+      if (issuer) tma_store_wait_read();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ok && warp == 2 && lane == 0) red_release_sys_add(p.ctl_peer[owner] + CTL_BLOCKS + lb, 1u);
+      if (issuer) {
+        if (ok) {
+          const int y = p.rank * p.Ms + lb * BM;  // row of the tile inside the owner's [P·Ms, N] slot buffer
+          tma_store_2d(&slots.m[owner], buf, nb_ * BN, y);
+          if (nb_ * BN + 64 < p.N) tma_store_2d(&slots.m[owner], buf + EPI_BOX_BYTES, nb_ * BN + 64, y);
+        }
+        tma_store_commit();
+        // the previous tile's store has completed → one arrival on its owner's row-block counter
+        if (prev_owner >= 0) {
+          tma_store_wait_all_but_one();
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence_system();
+          red_release_sys_add(p.ctl_peer[prev_owner] + CTL_BLOCKS + prev_lb, 1u);
+        }
+        prev_owner = ok ? owner : -1;
+        prev_lb = lb;
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (issuer) {
+      tma_store_wait_all();
+      if (prev_owner >= 0) {
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __threadfence_system();
+        red_release_sys_add(p.ctl_peer[prev_owner] + CTL_BLOCKS + prev_lb, 1u);
+      }
     }
     // ---- tail: reduce local row blocks in rank order (deterministic), add the residual, write bf16
     const unsigned int need = epoch * (unsigned int)(p.world * p.tiles_n);
@@ -477,7 +577,7 @@ tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int vecs = p.N / 8;
     for (int lb = cta; lb < bpr; lb += ncta) {
       if (warp == 2 && lane == 0 && !*q.abort_flag)
-        if (!wait_flag_ge(ctl + CTL_BLOCKS + lb, need, p.status, 520, (unsigned)lb, p.spin_limit)) *q.abort_flag = 1;
+        if (!wait_flag_ge_ns(ctl + CTL_BLOCKS + lb, need, p.status, 520, (unsigned)lb, p.wait_ns)) *q.abort_flag = 1;
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*q.abort_flag) continue;
       const __nv_bfloat16* mine = p.slot_peer[p.rank];
@@ -556,7 +656,9 @@ int sm_count() {
   }
   return n;
 }
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+static_assert((size_t)FETCH_SLOTS * FETCH_CHUNK + 64 <= (size_t)STAGES * STAGE_BYTES + EPI_BYTES, "fetch ring fits the GEMM pipeline area");
 
 int fill_common(TpParams& p, int world, int rank, int Ms, int N, int K, int b_mn, unsigned int spin_limit,
                 void* const* ctl_ptrs, unsigned int* status) {
@@ -565,7 +667,8 @@ int fill_common(TpParams& p, int world, int rank, int Ms, int N, int K, int b_mn
   if (CTL_BLOCKS + world * (Ms / BM) > 4096) return NB_ERR_TOO_LARGE;
   p.world = world; p.rank = rank; p.Ms = Ms; p.M = Ms * world; p.N = N; p.K = K; p.b_mn = b_mn;
   p.tiles_m = p.M / BM; p.tiles_n = ceil_div(N, BN); p.num_kb = ceil_div(K, BK);
-  p.spin_limit = spin_limit ? spin_limit : (1u << 24);
+  // `spin_limit` counts units of 256 ns (the default 1 << 24 is about 4.3 s)
+  p.wait_ns = 256ull * (spin_limit ? spin_limit : (1u << 24));
   p.status = status;
   for (int r = 0; r < MAX_RANKS; ++r) {
     p.ctl_peer[r] = r < world ? (unsigned int*)ctl_ptrs[r] : nullptr;
@@ -635,6 +738,12 @@ int nb_tp_gemm_rs(int world, int rank, const void* A, const void* B, void* const
   if (rc) return rc;
   rc = b_mn ? make_tmap(&tmB, B, N, K, ldb, 64, BK) : make_tmap(&tmB, B, K, N, ldb, BK, BN);
   if (rc) return rc;
+  SlotMaps slots;
+  memset(&slots, 0, sizeof(slots));
+  for (int r = 0; r < world; ++r) {
+    rc = make_tmap(&slots.m[r], slot_ptrs[r], N, (long long)Ms * world, ld_slot, 64, BM);
+    if (rc) return rc;
+  }
   static bool configured = false;
   if (!configured) {
     NB_CUDA(cudaFuncSetAttribute(tp_gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
@@ -642,7 +751,7 @@ int nb_tp_gemm_rs(int world, int rank, const void* A, const void* B, void* const
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  tp_gemm_rs_kernel<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
+  tp_gemm_rs_kernel<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, slots, p);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

@@ -84,12 +84,18 @@ class TPBlock:
     def __init__(self, idx, cfg: WorldModelConfig, world, rank, gen, device):
         d, hd = cfg.dim, cfg.head_dim
         self.cfg, self.world, self.rank = cfg, world, rank
+        if cfg.heads % world:
+            raise ValueError(f"{cfg.heads} query heads do not split over {world} ranks")
+        if world > cfg.kv_heads and world % cfg.kv_heads:
+            raise ValueError(f"{world} ranks must be a multiple of the {cfg.kv_heads} KV heads they replicate")
+        if world <= cfg.kv_heads and cfg.kv_heads % world:
+            raise ValueError(f"{cfg.kv_heads} KV heads do not split over {world} ranks")
         self.hq = cfg.heads // world
-        assert cfg.heads % world == 0
         self.hkv = max(cfg.kv_heads // world, 1)
         self.kv_rep = max(world // cfg.kv_heads, 1)       # ranks sharing one KV head
+        if cfg.ff % world or (cfg.ff // world) % 8:
+            raise ValueError(f"ff = {cfg.ff} must split over {world} ranks into multiples of 8 columns")
         self.ffl = cfg.ff // world
-        assert cfg.ff % world == 0 and self.ffl % 8 == 0
         n_qkv = (self.hq + 2 * self.hkv) * hd
         pre = f"blocks.{idx}."
         # sharded parameters: every rank draws the FULL matrices from the same stream and keeps its slice, so the
@@ -130,7 +136,8 @@ class WorldModel:
         self.B = batch
         self.S = cfg.padded_seq_len(128)
         rows = batch * self.S
-        assert rows % (world * 128) == 0, "batch·padded_seq must split into whole 128-row blocks per rank"
+        if rows % (world * 128):
+            raise ValueError(f"batch x padded sequence = {rows} rows must split into whole 128-row blocks on {world} ranks")
         self.ms = rows // world
         self.rows = rows
         d, hd = cfg.dim, cfg.head_dim
@@ -175,13 +182,23 @@ class WorldModel:
         fr, within = pos // cfg.frame_len, pos % cfg.frame_len
         self.is_lat = ((pos < cfg.seq_len) & (within > 0)).float()
         self.is_act = ((pos < cfg.seq_len) & (within == 0)).float()
-        self.kv_group = None
-        if world > cfg.kv_heads and dist.is_initialized():
+        # ranks that replicate one KV head sum that head's weight gradients among themselves: one packed buffer, one
+        # collective per step.  The group's communicator is created AND used once here, so that its set-up cost (which
+        # differs from rank to rank) is not paid between two fused kernels of the first training step.
+        self.kv_group, self._kv_pack = None, None
+        if world > cfg.kv_heads:
+            if not dist.is_initialized():
+                raise RuntimeError("KV-head replica groups need an initialised process group")
             rep_n = world // cfg.kv_heads
             for g0 in range(0, world, rep_n):
                 grp = dist.new_group(list(range(g0, g0 + rep_n)))
                 if g0 <= rank < g0 + rep_n:
                     self.kv_group = grp
+            kvw = 2 * b0.hkv * hd
+            self._kv_pack = torch.zeros(cfg.layers, d, kvw, device=self.device)
+            dist.all_reduce(self._kv_pack[0, :1], group=self.kv_group)
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
 
     # ------------------------------------------------------------------ kernels
     def _norm_fwd(self, x, gamma, out):
@@ -314,12 +331,13 @@ class WorldModel:
         self.t_lin.vjp(dx)
         # ---- optimizer: KV replicas summed in their group, replicated params all-reduced + AdamW fused
         if self.kv_group is not None:
-            hd = cfg.head_dim
-            for blk in self.blocks:
-                g = blk.w_qkv.grad_storage[:, blk.hq * hd:]
-                gc = g.contiguous()
-                dist.all_reduce(gc, group=self.kv_group)
-                g.copy_(gc)
+            q_cols = self.blocks[0].hq * cfg.head_dim
+            kvw = self._kv_pack.shape[2]
+            for i, blk in enumerate(self.blocks):
+                self._kv_pack[i].copy_(blk.w_qkv.grad_storage[:, q_cols: q_cols + kvw])
+            dist.all_reduce(self._kv_pack, group=self.kv_group)
+            for i, blk in enumerate(self.blocks):
+                blk.w_qkv.grad_storage[:, q_cols: q_cols + kvw].copy_(self._kv_pack[i])
         if self.grad_sync is not None:
             self.grad_sync.reduce_and_step(self.opt_rep)
         else:

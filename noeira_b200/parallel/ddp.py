@@ -19,11 +19,14 @@ from ..nn.optim import H_GSCALE
 from ..ops.status import device_status
 from .symm import SIGNAL_PAD_WORDS, SymmetricHeap
 
-ONE_SHOT, TWO_SHOT, MULTIMEM = 0, 1, 2
+ONE_SHOT, TWO_SHOT, MULTIMEM, PUSH = 0, 1, 2, 3
+PUSH_MAX_OUT_BYTES = 16 << 20      # push sends (N-1) x bytes per GPU: beyond this the two-shot form moves fewer bytes
+PUSH_MAX_BLOCKS = 1024
 
 
 def choose_algo(nbytes: int, world: int, have_multicast: bool = False) -> int:
-    """Per-bucket choice.  One-shot moves (N-1)·bytes per GPU but has the fewest flag rounds; two-shot
+    """Per-bucket choice among the barrier-based forms (the push form, one NVLink traversal and no barrier, is chosen
+    by ``FusedGradSync`` for whole groups of small arenas).  One-shot moves (N-1)·bytes per GPU but has the fewest flag rounds; two-shot
     moves 2(N-1)/N·bytes; multimem ≈ 2·bytes/N.  Crossovers follow timings on 8 B200s: one-shot wins up to
     512 KB, two-shot (or multimem, when a multicast mapping exists) above."""
     if world <= 2 or nbytes <= (512 << 10):
@@ -61,6 +64,8 @@ class FusedGradSync:
         self.state: Dict[int, dict] = {}
         self.lib = cuda_lib()
         self.sig_heap = None
+        self.opts = []
+        self.push = None
 
     def attach(self, *opts):
         """Move each optimizer's gradient arena into symmetric memory and build the peer tables."""
@@ -85,12 +90,76 @@ class FusedGradSync:
             self.state[id(o)] = dict(grd=g, red=r, sig=s, grd_tab=g.ptr_table(), red_tab=r.ptr_table(),
                                      sig_tab=s.ptr_table(),
                                      partials=torch.zeros(256, device=a.grd.device),
-                                     algo=self.algo if self.algo is not None else choose_algo(nbytes, self.world))
+                                     algo=self.algo if self.algo in (ONE_SHOT, TWO_SHOT, MULTIMEM)
+                                     else choose_algo(nbytes, self.world))
+        self.opts = list(opts)
+        self._setup_push()
         torch.cuda.synchronize()
         if dist.is_initialized():
             dist.barrier(group=self.group)
 
+    # ------------------------------------------------------------------ push form (small arenas, one launch for all)
+    def _setup_push(self):
+        """Inbox + flags for the latency-optimal push all-reduce over ALL attached optimizers in one launch; used
+        when their arenas together are small enough that sending (N-1) copies beats the two-shot form."""
+        self.push = None
+        if self.algo not in (None, PUSH) or not (1 <= len(self.opts) <= 4):
+            return
+        nblk = [self.lib.nb_push_blocks(ctypes.c_longlong(o.arena.numel)) for o in self.opts]
+        plane = sum(nblk) * 1024 * 4                   # floats per (parity, source) plane
+        if sum(nblk) > PUSH_MAX_BLOCKS or (self.algo is None and plane * 4 * (self.world - 1) > PUSH_MAX_OUT_BYTES):
+            return
+        heap = SymmetricHeap(2 * self.world * plane * 4 + 2 * self.world * PUSH_MAX_BLOCKS * 4 + 8192, self.group)
+        inbox = heap.tensor(2 * self.world * plane, torch.float32)
+        flags = heap.tensor(2 * self.world * PUSH_MAX_BLOCKS, torch.int32)
+        dev = inbox.local.device
+        self.push = dict(heap=heap, inbox=inbox, flags=flags, inbox_tab=inbox.ptr_table(), flag_tab=flags.ptr_table(),
+                         ctl=torch.zeros(4, dtype=torch.int32, device=dev), args={})
+
+    def _push_args(self, opts, update: bool):
+        key = (tuple(id(o) for o in opts), update)
+        a = self.push["args"].get(key)
+        if a is None:
+            k = len(opts)
+            P, F, L = ctypes.c_void_p * k, ctypes.c_void_p * k, ctypes.c_longlong * k
+            arr = lambda ts: P(*[t.data_ptr() if t is not None else 0 for t in ts])
+            ars = [o.arena for o in opts]
+            a = dict(grd=arr([x.grd for x in ars]), n=L(*[x.numel for x in ars]), hyper=arr([o.hyper for o in opts]))
+            if update:
+                a.update(val=arr([x.val for x in ars]), m=arr([x.m for x in ars]), v=arr([x.v for x in ars]),
+                         shadow=arr([x.shadow for x in ars]), flags=arr([x.row_flags for x in ars]), out=None)
+            else:
+                outs = [torch.zeros_like(x.grd) for x in ars]
+                a.update(out=arr(outs), outs=outs, val=None, m=None, v=None, shadow=None, flags=None)
+            self.push["args"][key] = a
+        return a
+
+    def _push_launch(self, opts, update: bool, zero_grad: bool):
+        a, ps = self._push_args(opts, update), self.push
+        check(self.lib.nb_allreduce_push(
+            ctypes.c_int(self.world), ctypes.c_int(self.rank), ctypes.c_int(len(opts)), ps["inbox_tab"], ps["flag_tab"],
+            ptr(ps["ctl"]), a["grd"], a["out"], a["val"], a["m"], a["v"], a["shadow"], a["flags"], a["hyper"], a["n"],
+            ctypes.c_int(1 if update else 0), ctypes.c_int(int(zero_grad)), ctypes.c_uint(self.spin_limit),
+            ptr(device_status(opts[0].arena.grd.device)), stream_ptr()), "allreduce_push")
+        return a
+
+    def reduce_and_step_many(self, opts):
+        """Reduce the gradients of several optimizers across ranks and apply their updates.  When the push form is
+        set up (small arenas, no gradient clipping) this is ONE kernel for all of them, Adam step counters included;
+        otherwise one fused kernel per optimizer, in the given order on every rank."""
+        opts = list(opts)
+        if (self.push is not None and all(id(o) in self.state for o in opts) and set(map(id, opts)) == set(map(id, self.opts))
+                and all(o.max_grad_norm <= 0 for o in opts)):
+            self._push_launch(self.opts, update=True, zero_grad=True)
+            for o in self.opts:
+                o.arena.bump_versions(shadow_fresh=True)
+            return
+        for o in opts:
+            self.reduce_and_step(o)
+
     def reduce_and_step(self, opt):
+        if self.push is not None and len(self.opts) == 1 and opt is self.opts[0] and opt.max_grad_norm <= 0:
+            return self.reduce_and_step_many([opt])
         st = self.state[id(opt)]
         a = opt.arena
         self._advance(opt)
@@ -107,6 +176,9 @@ class FusedGradSync:
 
     def all_reduce(self, opt, scale: float = None) -> torch.Tensor:
         """Plain fused all-reduce of the gradient arena (no update); returns the reduced arena view."""
+        if self.push is not None and len(self.opts) == 1 and opt is self.opts[0] and self.algo in (None, PUSH):
+            a = self._push_launch(self.opts, update=False, zero_grad=False)
+            return a["outs"][0]
         st = self.state[id(opt)]
         a = opt.arena
         check(self.lib.nb_allreduce_fused(

@@ -34,10 +34,11 @@ class SymmetricBuffer:
     """``nbytes`` on every rank; ``local`` is a uint8 torch view, ``peer_ptrs[r]`` the address of rank
     r's part in THIS process (own address at ``[rank]``)."""
 
-    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
+    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None, solo: bool = False):
+        """``solo`` keeps the buffer private to this process (world 1) even when a process group exists."""
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() and not solo else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() and not solo else 0
         self.nbytes = (int(nbytes) + 255) // 256 * 256
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         lib = cuda_lib()
@@ -89,8 +90,8 @@ class SymmetricBuffer:
 class SymmetricHeap:
     """Bump allocator over one SymmetricBuffer: sub-buffers share a single IPC mapping per peer."""
 
-    def __init__(self, nbytes: int, group=None):
-        self.buf = SymmetricBuffer(nbytes, group)
+    def __init__(self, nbytes: int, group=None, solo: bool = False):
+        self.buf = SymmetricBuffer(nbytes, group, solo=solo)
         self.off = 0
         self.world, self.rank = self.buf.world, self.buf.rank
 

@@ -28,7 +28,14 @@ class TPLinearContext:
     def __init__(self, world: int, rank: int, ms: int, k: int, n: int, kind: str, group=None, n_fetch: int = 24,
                  spin_limit: int = 1 << 24, alloc_stage: bool = True):
         """kind = "ag" (column parallel: K = full input width, N = local output width)
-                  "rs" (row parallel:    K = local input width, N = full output width)."""
+                  "rs" (row parallel:    K = local input width, N = full output width).
+        ``spin_limit`` bounds every device-side wait on a peer, in units of 256 ns (default about 4.3 s)."""
+        if not (1 <= world <= 8 and 0 <= rank < world):
+            raise ValueError(f"tensor-parallel world {world} / rank {rank}: the kernels take up to 8 ranks of one node")
+        if k % 8 or n % 8:
+            raise ValueError(f"K = {k} and N = {n} must be multiples of 8 (16-byte rows)")
+        if 16 + world * (ms // 128) > 4096:
+            raise ValueError(f"{world} x {ms // 128} row blocks exceed the control block (4080 flags)")
         assert ms % 128 == 0, "row shards are whole 128-row blocks"
         self.world, self.rank, self.ms, self.k, self.n, self.kind = world, rank, ms, k, n, kind
         self.n_fetch, self.spin_limit = n_fetch, spin_limit
@@ -39,7 +46,7 @@ class TPLinearContext:
             nbytes += ms * k * 2 + 4096
         else:
             nbytes += world * ms * n * 2 + 4096
-        self.heap = SymmetricHeap(nbytes, group)
+        self.heap = SymmetricHeap(nbytes, group, solo=(world == 1))
         self.ctl = self.heap.tensor(words, torch.int32)
         dev = self.ctl.local.device
         if kind == "ag":
@@ -48,6 +55,8 @@ class TPLinearContext:
             self.stage = torch.zeros(world * ms, k, device=dev, dtype=torch.bfloat16) if alloc_stage else None
         else:
             self.slots = self.heap.tensor(world * ms * n, torch.bfloat16)
+        if self.heap.world != world or self.heap.rank != rank:
+            raise ValueError(f"context is rank {rank} of {world} but its process group is rank {self.heap.rank} of {self.heap.world}")
         torch.cuda.synchronize()
         if dist.is_initialized() and world > 1:
             dist.barrier(group=group)

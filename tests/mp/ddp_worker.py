@@ -51,11 +51,70 @@ def main():
         if rank == 0:
             print(f"algo={algo} hidden={hidden} clip={clip}: replicas_equal={same} max|fused-nccl|={err:.3e} grd_zeroed={gz == 0.0}")
         ok = ok and same and err < (2e-4 if clip > 0 else 2e-5) and gz == 0.0
+    ok = push_case(rank, world, local) and ok
     dist.barrier()
     if rank == 0:
         print("DDP_WORKER_OK" if ok else "DDP_WORKER_FAIL")
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
+
+
+def push_case(rank, world, local):
+    """Two optimizers reduced and stepped by ONE push kernel (inbox double-buffered by epoch parity, step counters
+    advanced in the kernel) against NCCL all-reduce + local Adam, over enough steps to reuse both parities."""
+    from noeira_b200 import nn
+    from noeira_b200.ops import check_status
+    from noeira_b200.parallel.ddp import FusedGradSync
+    nn.manual_seed(11)
+    mk = lambda o: nn.Sequential(nn.LinearTanh(24, 256), nn.LinearTanh(256, 256), nn.Linear(256, o)).to("cuda")
+    nets, refs = [mk(8), mk(1)], [mk(8), mk(1)]
+    for n_, r_ in zip(nets, refs):
+        r_.copy_from(n_)
+    opts = [nn.Adam(n_.named_params(), lr=3e-3) for n_ in nets]
+    ropts = [nn.Adam(r_.named_params(), lr=3e-3) for r_ in refs]
+    sync = FusedGradSync(world, rank, local)
+    sync.attach(*opts)
+    assert sync.push is not None
+    g = torch.Generator(device="cuda").manual_seed(200 + rank)
+    for step in range(5):
+        x = torch.randn(512, 24, device="cuda", generator=g).bfloat16()
+        for n_, r_, o in zip(nets, refs, (8, 1)):
+            dy = (torch.randn(512, o, device="cuda", generator=g) * 0.1).bfloat16()
+            for q in (n_, r_):
+                q.forward(x)
+                q.vjp(dy)
+        sync.reduce_and_step_many(opts)
+        for ro in ropts:
+            dist.all_reduce(ro.arena.grd)
+            ro.hyper[8] = 1.0 / world
+            ro.step(zero_grad=True)
+    torch.cuda.synchronize()
+    check_status()
+    ok = True
+    for o, ro in zip(opts, ropts):
+        mine = o.arena.val.clone()
+        lst = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(lst, mine)
+        same = all(torch.equal(lst[0], t) for t in lst)
+        err = (o.arena.val - ro.arena.val).abs().max().item()
+        steps_equal = torch.equal(o.hyper[5:8], ro.hyper[5:8])
+        gz = o.arena.grd.abs().max().item()
+        if rank == 0:
+            print(f"push numel={o.arena.numel}: replicas_equal={same} max|fused-nccl|={err:.3e} step_counters_equal={steps_equal} "
+                  f"grd_zeroed={gz == 0.0}")
+        ok = ok and same and err < 2e-5 and steps_equal and gz == 0.0
+    # plain sum through the same kernel
+    one = nn.Adam(mk(2).named_params(), lr=1e-3)
+    s2 = FusedGradSync(world, rank, local)
+    s2.attach(one)
+    one.arena.grd.copy_(torch.full_like(one.arena.grd, float(rank + 1)))
+    red = s2.all_reduce(one)
+    torch.cuda.synchronize()
+    want = sum(range(1, world + 1)) / world
+    okp = bool((red - want).abs().max().item() < 1e-6)
+    if rank == 0:
+        print(f"push plain all-reduce: ok={okp}")
+    return ok and okp
 
 
 if __name__ == "__main__":

@@ -14,14 +14,28 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_fused_allreduce_adam_matches_nccl():
-    n = min(_ngpu(), 8)
+def _world_sizes():
+    """Every power of two from 2 up to the number of GPUs of the box (2, 4, 8 on a full node)."""
+    n, out = _ngpu(), []
+    w = 2
+    while w <= min(n, 8):
+        out.append(w)
+        w *= 2
+    return out or [2]
+
+
+def _torchrun(script, world, port, timeout=900):
+    # NVLS off: a rank that exits while bound to an NVLink multicast object can fault its peers
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-                        "--master-addr", "127.0.0.1", "--master-port", "29611",
-                        os.path.join(ROOT, "tests", "mp", "ddp_worker.py")], capture_output=True, text=True, timeout=600,
-                       env=env)
+    return subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                           "--master-addr", "127.0.0.1", "--master-port", str(port),
+                           os.path.join(ROOT, "tests", "mp", script)], capture_output=True, text=True, timeout=timeout, env=env)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("world", _world_sizes())
+def test_fused_allreduce_adam_matches_nccl(world):
+    r = _torchrun("ddp_worker.py", world, 29611 + world)
     assert "DDP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -57,11 +71,15 @@ def test_tp_fused_kernels_single_rank():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_tp_fused_kernels_match_nccl():
-    n = min(_ngpu(), 8)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-                        "--master-addr", "127.0.0.1", "--master-port", "29621",
-                        os.path.join(ROOT, "tests", "mp", "tp_worker.py")], capture_output=True, text=True, timeout=600,
-                       env=env)
+@pytest.mark.parametrize("world", _world_sizes())
+def test_tp_fused_kernels_match_nccl(world):
+    r = _torchrun("tp_worker.py", world, 29621 + world)
     assert "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("world", _world_sizes())
+def test_world_model_tp_matches_single_rank(world):
+    """TP + SP world model (KV-head replica groups from 4 ranks up) against the same model on one rank."""
+    r = _torchrun("wm_worker.py", world, 29641 + world)
+    assert "WM_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
