@@ -13,6 +13,7 @@
 // noeira/nn/primitives/linear.mojo:1295-1387); the captured actor step it optimises is noeira_max/README.md's
 // "MLP actor inference 17-256-256-6: 21.5 us eager / 12.7 captured".
 #include <cuda.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "gemm_api.h"
@@ -45,9 +46,22 @@ __device__ __forceinline__ float act1(int act, float v) {
   return fmaxf(v, 0.f);
 }
 
+struct MlpMaps {
+  CUtensorMap x, w1, w2;
+};
+struct MlpGroup {
+  MlpMaps maps[2];
+  MlpParams prm[2];
+};
+
+// blockIdx.y selects the network: the actor and the critic of an RL update run in ONE launch.
 __global__ void __launch_bounds__(MLP_THREADS, 1)
-mlp3_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW1,
-                const __grid_constant__ CUtensorMap tmW2, const MlpParams p) {
+mlp3_fwd_kernel(const __grid_constant__ MlpGroup grp) {
+  const MlpParams& p = grp.prm[blockIdx.y];
+  const CUtensorMap& tmX = grp.maps[blockIdx.y].x;
+  const CUtensorMap& tmW1 = grp.maps[blockIdx.y].w1;
+  const CUtensorMap& tmW2 = grp.maps[blockIdx.y].w2;
+  if ((int)blockIdx.x * ROWS >= p.M) return;
   constexpr uint32_t X_BYTES = ROWS * 64 * 2;        // 16 KB
   constexpr uint32_t W1_BYTES = 64 * HID * 2;        // 32 KB (64 k-rows x 256)
   constexpr uint32_t W2_STAGE = 64 * HID * 2;        // 32 KB per k-block
@@ -257,43 +271,313 @@ int tmap2d(CUtensorMap* tm, const void* base, long long inner, long long outer, 
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? NB_OK : NB_ERR_TENSORMAP;
 }
 
+// ------------------------------------------------------------------------------------------ backward (data gradients)
+// G2 = (dY W3ᵀ) ⊙ f'(h2),  G1 = (G2 W2ᵀ) ⊙ f'(h1)  for one 128-row tile per CTA, both chained on chip: the first
+// product has K = 16 (one tcgen05.mma), its result is multiplied by the activation derivative taken from the saved
+// h2, written out in bf16 (the weight-gradient GEMMs read it) and kept in shared memory as the A operand of the second
+// product.  G1 and G2 are the gradients with respect to the layers' PRE-activations, i.e. exactly the operands of
+// dW1 = Xᵀ G1, dW2 = h1ᵀ G2, dW3 = h2ᵀ dY and of the bias column sums.  The first layer's input gradient is not needed.
+//   warp 0      TMA: W2 as a K-major B operand (box 64 k x 256 n per k-block), 2-stage ring
+//   warp 1      MMA issuer
+//   warps 2..5  stage dY and W3 (zero padded to K = 64) into swizzled tiles; epilogues (thread = row)
+struct MlpBwdParams {
+  int M, n3;
+  int ld_dy, ld_w3, ld_h, ld_g;
+  int act;
+  const __nv_bfloat16 *dy, *w3, *h1, *h2;
+  __nv_bfloat16 *g1, *g2;
+  unsigned int* status;
+};
+struct MlpBwdGroup {
+  CUtensorMap w2[2];
+  MlpBwdParams prm[2];
+};
+
+__device__ __forceinline__ float dact1(int act, float h) { return act == NB_ACT_TANH ? 1.f - h * h : (h > 0.f ? 1.f : 0.f); }
+
+__global__ void __launch_bounds__(MLP_THREADS, 1)
+mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
+  const MlpBwdParams& p = grp.prm[blockIdx.y];
+  const CUtensorMap& tmW2 = grp.w2[blockIdx.y];
+  if ((int)blockIdx.x * ROWS >= p.M) return;
+  constexpr uint32_t DY_BYTES = ROWS * 64 * 2;       // 16 KB: A tile [128 x 64] K-major, columns >= n3 zero
+  constexpr uint32_t W3_BYTES = HID * 64 * 2;        // 32 KB: B tile [256 n x 64 k] K-major, columns >= n3 zero
+  constexpr uint32_t W2_STAGE = HID * 64 * 2;        // 32 KB per k-block: [256 n x 64 k] K-major
+  constexpr uint32_t G_BYTES = ROWS * HID * 2;       // 64 KB: G2 as the next A operand, four k-blocks of 16 KB
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sDY = smem;
+  uint8_t* sW3 = sDY + DY_BYTES;
+  uint8_t* sW2 = sW3 + W3_BYTES;            // 2 stages
+  uint8_t* sG = sW2 + 2 * W2_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sG + G_BYTES);
+  uint64_t* w2_full = bars;        // [2]
+  uint64_t* w2_empty = bars + 2;   // [2]
+  uint64_t* acc_full = bars + 4;   // [2]
+  uint64_t* staged = bars + 6;     // dY and W3 tiles written (4 warps)
+  uint64_t* g_ready = bars + 7;    // G2 tile written (4 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * ROWS;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&w2_full[i], 1);
+      mbar_init(&w2_empty[i], 1);
+      mbar_init(&acc_full[i], 1);
+    }
+    mbar_init(staged, 4);
+    mbar_init(g_ready, 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmW2);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int kb = 0; kb < HID / 64; ++kb) {
+        const int st = kb & 1;
+        if (*abort_flag || !mbar_wait(&w2_empty[st], ((uint32_t)(kb >> 1) & 1u) ^ 1u, p.status, 331)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&w2_full[st], W2_STAGE);
+        // B(n, k) of G2 W2ᵀ is W2[n, k]: row n of the [IN, OUT] matrix, 64 consecutive columns
+        tma_load_2d(sW2 + st * W2_STAGE, &tmW2, &w2_full[st], kb * 64, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc(1u, ROWS, HID, 0u, 0u);   // both operands K-major, N = 256
+      bool ok = mbar_wait(staged, 0u, p.status, 340);
+      if (ok) {
+        tc_fence_after();
+        umma_f16(tmem_base, make_smem_desc(smem_u32(sDY), 16, 1024, 2), make_smem_desc(smem_u32(sW3), 16, 1024, 2), idesc, 0u);
+        umma_commit(&acc_full[0]);
+        ok = mbar_wait(g_ready, 0u, p.status, 341);
+      }
+      for (int kb = 0; kb < HID / 64 && ok; ++kb) {
+        const int st = kb & 1;
+        if (!mbar_wait(&w2_full[st], (uint32_t)(kb >> 1) & 1u, p.status, 342)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ga = smem_u32(sG + kb * 16384), wb = smem_u32(sW2 + st * W2_STAGE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_base + 256, make_smem_desc(ga + k * 32, 16, 1024, 2), make_smem_desc(wb + k * 32, 16, 1024, 2), idesc,
+                   (kb | k) != 0 ? 1u : 0u);
+        umma_commit(&w2_empty[st]);
+      }
+      if (ok) umma_commit(&acc_full[1]);
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;            // row of the tile = TMEM lane
+    const int row = row0 + r;
+    const int t = (warp - 2) * 32 + lane;         // 0..127
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    // ---- stage dY (row r of the tile; threads are TMEM-lane ordered, any order works here) and two rows of W3
+    {
+      uint4 c[2] = {zero4, zero4};
+      if (row < p.M) {
+        const __nv_bfloat16* src = p.dy + (size_t)row * p.ld_dy;
+        __nv_bfloat16 v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = j < p.n3 ? src[j] : __float2bfloat16(0.f);
+        c[0] = *reinterpret_cast<uint4*>(&v[0]);
+        c[1] = *reinterpret_cast<uint4*>(&v[8]);
+      }
+      uint8_t* dst = sDY + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ((ch ^ (r & 7)) << 4)) = ch < 2 ? c[ch] : zero4;
+    }
+    for (int n = t; n < HID; n += 128) {
+      const __nv_bfloat16* src = p.w3 + (size_t)n * p.ld_w3;
+      __nv_bfloat16 v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = j < p.n3 ? src[j] : __float2bfloat16(0.f);
+      uint8_t* dst = sW3 + (n >> 3) * 1024 + (n & 7) * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(dst + ((ch ^ (n & 7)) << 4)) = ch < 2 ? *reinterpret_cast<uint4*>(&v[ch * 8]) : zero4;
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(staged);
+    bool ok = true;
+    uint8_t* grow = sG + (r >> 3) * 1024 + (r & 7) * 128;
+    for (int layer = 0; layer < 2 && ok; ++layer) {
+      if (!__all_sync(0xffffffffu, !*abort_flag && mbar_wait(&acc_full[layer], 0u, p.status, 350 + layer))) { ok = false; break; }
+      tc_fence_after();
+      const __nv_bfloat16* hsrc = (layer == 0 ? p.h2 : p.h1) + (size_t)row * p.ld_h;
+      __nv_bfloat16* gdst = (layer == 0 ? p.g2 : p.g1) + (size_t)row * p.ld_g;
+      const uint32_t acc = lane_addr + (uint32_t)(layer * 256);
+#pragma unroll 1
+      for (int c0 = 0; c0 < HID; c0 += 16) {
+        uint32_t rr[16];
+        tmem_ld_32x32b_x16(acc + (uint32_t)c0, rr);
+        uint4 hv[2] = {zero4, zero4};
+        if (row < p.M) {
+          hv[0] = __ldg(reinterpret_cast<const uint4*>(hsrc + c0));
+          hv[1] = __ldg(reinterpret_cast<const uint4*>(hsrc + c0 + 8));
+        }
+        tmem_ld_wait();
+        const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(hv);
+        uint32_t pk[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float h0 = __low2float(hp[j]), h1 = __high2float(hp[j]);
+          __nv_bfloat162 g = __floats2bfloat162_rn(__uint_as_float(rr[2 * j]) * dact1(p.act, h0),
+                                                   __uint_as_float(rr[2 * j + 1]) * dact1(p.act, h1));
+          pk[j] = *reinterpret_cast<uint32_t*>(&g);
+        }
+        if (layer == 0) {
+          const int kb = c0 >> 6, ch = (c0 & 63) >> 3;
+          uint8_t* base = grow + kb * 16384;
+          *reinterpret_cast<uint4*>(base + (((ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(base + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+        if (row < p.M) {
+          uint4* g = reinterpret_cast<uint4*>(gdst + c0);
+          g[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          g[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+      }
+      if (layer == 0) {
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(g_ready);
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+// One network of a grouped launch (mirrored by a ctypes.Structure in noeira_b200/ops/mlp.py — keep the field order).
+struct NbMlpNet {
+  const void *x, *w1, *w2, *w3;      // x [M, k0] bf16; W1 [k0, 256], W2 [256, 256], W3 [256, n3] bf16 row-major
+  const float *b1, *b2, *b3;         // fp32 biases (b3 may be null)
+  float* out;                        // forward: fp32 [M, ld_out]
+  void *h1, *h2;                     // forward: optional saves / backward: saved activations, bf16 [M, ld_h]
+  const void* dy;                    // backward: bf16 [M, ld_dy], n3 columns used
+  void *g1, *g2;                     // backward: bf16 [M, ld_g] gradients of the pre-activations of layers 1 and 2
+  int ldx, ldw1, ldw2, ldw3, ld_out, ld_h, ld_dy, ld_g;
+  int M, k0, n3, act;
+};
+
+namespace {
+using namespace nb;
+constexpr size_t FWD_SMEM = 16384 + 32768 + 2 * 32768 + 65536 + 8192 + 1024 + 256;
+constexpr size_t BWD_SMEM = 16384 + 32768 + 2 * 32768 + 65536 + 1024 + 256;
+
+int check_net(const NbMlpNet& n) {
+  if (n.M <= 0 || n.k0 <= 0 || n.k0 > 64 || n.n3 <= 0 || n.n3 > N3P) return NB_ERR_BAD_ARG;
+  if (n.act != NB_ACT_TANH && n.act != NB_ACT_RELU) return NB_ERR_BAD_ARG;
+  if ((n.h1 || n.h2) && (n.ld_h % 8 || ((uintptr_t)n.h1 & 15) || ((uintptr_t)n.h2 & 15))) return NB_ERR_UNALIGNED;
+  return NB_OK;
+}
 }  // namespace
 
 extern "C" {
 
-// x [M, k0] bf16 (row pitch ldx), W1 [k0, 256], W2 [256, 256], W3 [256, n3] bf16 row-major with the given pitches;
-// biases fp32 (may be null); out fp32 [M, ld_out]; h1 / h2 optional bf16 [M, ld_h] saves.  act: NB_ACT_TANH / NB_ACT_RELU.
+// Forward of `nets` (1 or 2) three-layer MLPs in one launch; act: NB_ACT_TANH / NB_ACT_RELU.
+int nb_mlp3_fwd_group(const NbMlpNet* net, int nets, unsigned int* status, void* stream) {
+  if (nets < 1 || nets > 2) return NB_ERR_BAD_ARG;
+  MlpGroup g;
+  memset(&g, 0, sizeof(g));
+  int max_m = 0;
+  for (int i = 0; i < nets; ++i) {
+    const NbMlpNet& n = net[i];
+    int rc = check_net(n);
+    if (rc) return rc;
+    rc = tmap2d(&g.maps[i].x, n.x, n.k0, n.M, n.ldx, 64, ROWS);
+    if (rc) return rc;
+    rc = tmap2d(&g.maps[i].w1, n.w1, HID, n.k0, n.ldw1, 64, 64);
+    if (rc) return rc;
+    rc = tmap2d(&g.maps[i].w2, n.w2, HID, HID, n.ldw2, 64, 64);
+    if (rc) return rc;
+    MlpParams& p = g.prm[i];
+    p.M = n.M; p.k0 = n.k0; p.n3 = n.n3;
+    p.ld_w3 = n.ldw3; p.ld_out = n.ld_out; p.ld_h = n.ld_h;
+    p.act = n.act;
+    p.w3 = (const __nv_bfloat16*)n.w3;
+    p.b1 = n.b1; p.b2 = n.b2; p.b3 = n.b3;
+    p.out = n.out;
+    p.h1 = (__nv_bfloat16*)n.h1; p.h2 = (__nv_bfloat16*)n.h2;
+    p.status = status;
+    max_m = n.M > max_m ? n.M : max_m;
+  }
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(mlp3_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SMEM));
+    configured = true;
+  }
+  mlp3_fwd_kernel<<<dim3(ceil_div(max_m, ROWS), nets), MLP_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(g);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+// Data-gradient chain of `nets` (1 or 2) three-layer MLPs in one launch: g2 = (dy W3ᵀ) ⊙ f'(h2), g1 = (g2 W2ᵀ) ⊙ f'(h1).
+int nb_mlp3_bwd_group(const NbMlpNet* net, int nets, unsigned int* status, void* stream) {
+  if (nets < 1 || nets > 2) return NB_ERR_BAD_ARG;
+  MlpBwdGroup g;
+  memset(&g, 0, sizeof(g));
+  int max_m = 0;
+  for (int i = 0; i < nets; ++i) {
+    const NbMlpNet& n = net[i];
+    int rc = check_net(n);
+    if (rc) return rc;
+    if (!n.dy || !n.h1 || !n.h2 || !n.g1 || !n.g2) return NB_ERR_BAD_ARG;
+    if (n.ld_g % 8 || ((uintptr_t)n.g1 & 15) || ((uintptr_t)n.g2 & 15) || n.ldw3 < n.n3 || n.ld_dy < n.n3) return NB_ERR_UNALIGNED;
+    rc = tmap2d(&g.w2[i], n.w2, HID, HID, n.ldw2, 64, HID);
+    if (rc) return rc;
+    MlpBwdParams& p = g.prm[i];
+    p.M = n.M; p.n3 = n.n3;
+    p.ld_dy = n.ld_dy; p.ld_w3 = n.ldw3; p.ld_h = n.ld_h; p.ld_g = n.ld_g;
+    p.act = n.act;
+    p.dy = (const __nv_bfloat16*)n.dy; p.w3 = (const __nv_bfloat16*)n.w3;
+    p.h1 = (const __nv_bfloat16*)n.h1; p.h2 = (const __nv_bfloat16*)n.h2;
+    p.g1 = (__nv_bfloat16*)n.g1; p.g2 = (__nv_bfloat16*)n.g2;
+    p.status = status;
+    max_m = n.M > max_m ? n.M : max_m;
+  }
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(mlp3_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM));
+    configured = true;
+  }
+  mlp3_bwd_kernel<<<dim3(ceil_div(max_m, ROWS), nets), MLP_THREADS, BWD_SMEM, (cudaStream_t)stream>>>(g);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+// Single-network forward (see nb_mlp3_fwd_group).
 int nb_mlp3_fwd(const void* x, int ldx, const void* w1, int ldw1, const void* w2, int ldw2, const void* w3, int ldw3,
                 const float* b1, const float* b2, const float* b3, float* out, int ld_out, void* h1, void* h2, int ld_h, int M,
                 int k0, int n3, int act, unsigned int* status, void* stream) {
-  if (M <= 0 || k0 <= 0 || k0 > 64 || n3 <= 0 || n3 > N3P) return NB_ERR_BAD_ARG;
-  if (act != NB_ACT_TANH && act != NB_ACT_RELU) return NB_ERR_BAD_ARG;
-  if ((h1 || h2) && (ld_h % 8 || ((uintptr_t)h1 & 15) || ((uintptr_t)h2 & 15))) return NB_ERR_UNALIGNED;
-  CUtensorMap tx, t1, t2;
-  int rc = tmap2d(&tx, x, k0, M, ldx, 64, ROWS);
-  if (rc) return rc;
-  rc = tmap2d(&t1, w1, HID, k0, ldw1, 64, 64);
-  if (rc) return rc;
-  rc = tmap2d(&t2, w2, HID, HID, ldw2, 64, 64);
-  if (rc) return rc;
-  MlpParams p;
-  p.M = M; p.k0 = k0; p.n3 = n3;
-  p.ld_w3 = ldw3; p.ld_out = ld_out; p.ld_h = ld_h;
-  p.act = act;
-  p.w3 = (const __nv_bfloat16*)w3;
-  p.b1 = b1; p.b2 = b2; p.b3 = b3;
-  p.out = out;
-  p.h1 = (__nv_bfloat16*)h1; p.h2 = (__nv_bfloat16*)h2;
-  p.status = status;
-  constexpr size_t smem = 16384 + 32768 + 2 * 32768 + 65536 + 8192 + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(mlp3_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
-  mlp3_fwd_kernel<<<ceil_div(M, ROWS), MLP_THREADS, smem, (cudaStream_t)stream>>>(tx, t1, t2, p);
-  NB_LAUNCH_CHECK();
-  return NB_OK;
+  NbMlpNet n;
+  memset(&n, 0, sizeof(n));
+  n.x = x; n.w1 = w1; n.w2 = w2; n.w3 = w3; n.b1 = b1; n.b2 = b2; n.b3 = b3; n.out = out; n.h1 = h1; n.h2 = h2;
+  n.ldx = ldx; n.ldw1 = ldw1; n.ldw2 = ldw2; n.ldw3 = ldw3; n.ld_out = ld_out; n.ld_h = ld_h;
+  n.M = M; n.k0 = k0; n.n3 = n3; n.act = act;
+  return nb_mlp3_fwd_group(&n, 1, status, stream);
 }
 
 }  // extern "C"

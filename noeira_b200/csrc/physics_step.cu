@@ -115,25 +115,28 @@ struct WarpScratch {
   int* rowi;
 };
 
+// Layout of one warp's scratch.  The Delassus matrix A (symmetric, packed lower triangle: 528 words for 32 rows) is
+// built after the inertias, velocities, forces and body quaternions have been consumed, so it overlays them; the
+// scratch of a 9-dof chain is then 7 KB and 28 warps (environments) fit one SM.
 __device__ __forceinline__ WarpScratch carve(float* base, const PhysParams& P) {
   WarpScratch w;
   const int nb_ = P.nbody, nv = P.nv, nvp = P.nvp, rmax = P.rmax;
   float* p = base;
   w.xpos = p; p += nb_ * 3;
-  w.xquat = p; p += nb_ * 4;
   w.xmat = p; p += nb_ * 9;
   w.S = p; p += nv * 6;
-  w.I = p; p += nb_ * 10;
-  w.Ic = p; p += nb_ * 10;
-  w.V = p; p += nb_ * 6;
-  w.F = p; p += nb_ * 6;
   w.M = p; p += nv * nvp;
   w.vec = p; p += 4 * 32;
   w.J = p; p += rmax * nvp;
   w.B = p; p += rmax * nvp;
   w.row = p; p += rmax * 4;
   w.rowi = reinterpret_cast<int*>(p); p += rmax * 4;  // rmax * 4 ints
-  w.A = p;  // 32 x 33 Delassus matrix (dual PGS, rmax <= 32)
+  w.A = p;  // packed 32 x 32 lower triangle (dual PGS, rmax <= 32); shares its space with the five arrays below
+  w.xquat = p; p += nb_ * 4;
+  w.I = p; p += nb_ * 10;
+  w.Ic = p; p += nb_ * 10;
+  w.V = p; p += nb_ * 6;
+  w.F = p; p += nb_ * 6;
   return w;
 }
 
@@ -565,7 +568,10 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
     const bool on = r < nrow;
     float c = 0.f, lam = 0.f, k1 = 0.f, invd = 0.f, mu = 0.f;
     int parent = 0;
-    float* a_row = w.A + r * 33;  // A[r][*] in shared memory (odd stride: conflict free)
+    // A[r][s] = A[s][r] lives at tri(max) + min with tri(k) = k(k+1)/2; the triangular numbers are a permutation
+    // modulo 32, so a sweep column is read without bank conflicts.  Lane r writes its own row's lower part only
+    // (one writer per element: deterministic).
+    const int tri_r = r * (r + 1) / 2;
     if (on) {
       float acc = 0.f;
       for (int j = 0; j < nv; ++j) acc += w.J[r * nvp + j] * qacc_sh[j];
@@ -575,29 +581,34 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
       lam = w.row[r * 4 + 3];
       parent = max(w.rowi[r * 4 + 2], 0);
       if (w.rowi[r * 4] >= ROW_TANGENT) mu = m.cs_mu[w.rowi[r * 4 + 1] - P.nlimit];
-      for (int s2 = 0; s2 < nrow; ++s2) {
+    }
+    __syncwarp();  // every lane has read what it needs from the arrays that A overlays (none are read below)
+    if (on) {
+      for (int s2 = 0; s2 <= r; ++s2) {
         float a = 0.f;
         for (int j = 0; j < nv; ++j) a += w.J[r * nvp + j] * w.B[s2 * nvp + j];
-        a_row[s2] = a;
+        w.A[tri_r + s2] = a;
       }
     }
     __syncwarp();
-    for (int s2 = 0; s2 < nrow; ++s2) {  // warm start
+#define NB_A_AT(s2, tri_s) (on ? w.A[(s2) <= r ? tri_r + (s2) : (tri_s) + r] : 0.f)
+    for (int s2 = 0, ts = 0; s2 < nrow; ts += ++s2) {  // warm start
       const float ls = __shfl_sync(0xffffffffu, lam, s2);
-      if (on) c += a_row[s2] * ls;
+      c += NB_A_AT(s2, ts) * ls;
     }
     for (int it = 0; it < P.pgs_iters; ++it) {
       // unilateral rows [0, nuni): limits and contact normals
-      for (int s2 = 0; s2 < nuni; ++s2) {
-        const float a_rs = on ? a_row[s2] : 0.f;
+      int ts = 0;
+      for (int s2 = 0; s2 < nuni; ts += ++s2) {
+        const float a_rs = NB_A_AT(s2, ts);
         const float ln = fmaxf(lam * k1 - c * invd, 0.f);
         const float dl = __shfl_sync(0xffffffffu, ln - lam, s2);
         if (lane == s2) lam = ln;
         c += a_rs * dl;
       }
       // friction rows [nuni, nrow): box bounds from the parent normal multiplier
-      for (int s2 = nuni; s2 < nrow; ++s2) {
-        const float a_rs = on ? a_row[s2] : 0.f;
+      for (int s2 = nuni; s2 < nrow; ts += ++s2) {
+        const float a_rs = NB_A_AT(s2, ts);
         const float bound = mu * __shfl_sync(0xffffffffu, lam, parent);
         const float ln = fminf(fmaxf(lam * k1 - c * invd, -bound), bound);
         const float dl = __shfl_sync(0xffffffffu, ln - lam, s2);
@@ -605,6 +616,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
         c += a_rs * dl;
       }
     }
+#undef NB_A_AT
     if (on) w.row[r * 4 + 3] = lam;
     qacc = (lane < nv) ? qacc_sh[lane] : 0.f;
     for (int s2 = 0; s2 < nrow; ++s2) {
@@ -656,7 +668,10 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
 }
 
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(NB_PHYS_WARPS * 32)
+// WARPS environments per block, MINB blocks per SM: <7, 4> keeps 28 environments resident per SM (4096 on 148 SMs
+// in one wave) at 72 registers per thread; <8, 2> is the general form for models with a larger scratch.
+template <int WARPS, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 phys_env_step_kernel(PhysParams P, const int* __restrict__ imodel, const float* __restrict__ fmodel,
                      float* __restrict__ qpos_g, float* __restrict__ qvel_g, float* __restrict__ warm_g,
                      int* __restrict__ step_count, float* __restrict__ ep_return, const float* __restrict__ action,
@@ -853,10 +868,12 @@ extern "C" {
 static int phys_smem_bytes(const PhysParams* P, int warps) {
   return (int)sizeof(float) * (P->imodel_words + P->fmodel_words + warps * P->warp_words);
 }
-// Warps (= environments) per block: 8 when that fits.  Blocks of 7 warps raise the resident warps per SM from 16 to 21
-// for the 9-dof chain but measured slower (0.383 ms against 0.361 ms per 4096-environment step): the last wave
-// of blocks then runs at one block per SM.  Smaller blocks are only used for models whose scratch needs them.
+// Warps (= environments) per block.  When four blocks of 7 warps fit one SM (small models: the packed constraint
+// scratch of a 9-dof chain is 7 KB per environment) 28 environments are resident per SM and a 4096-environment batch
+// is a single wave on 148 SMs; otherwise 8 warps per block, or fewer for models whose scratch needs it.
+static bool phys_dense(const PhysParams* P) { return 4 * (phys_smem_bytes(P, 7) + 1024) <= 227 * 1024; }
 static int phys_pick_warps(const PhysParams* P) {
+  if (phys_dense(P)) return 7;
   for (int wpb = NB_PHYS_WARPS; wpb >= 1; --wpb)
     if (phys_smem_bytes(P, wpb) + 1024 <= 227 * 1024) return wpb;
   return 1;
@@ -873,14 +890,28 @@ int nb_phys_env_step(const PhysParams* P, const int* imodel, const float* fmodel
   if (P->nv > 32 || P->nbody > 32 || P->nv < 1) return NB_ERR_TOO_LARGE;
   const int smem = nb_phys_smem_bytes(P);
   if (smem > 227 * 1024) return NB_ERR_TOO_LARGE;
-  static int configured = 0;
-  if (configured < smem) {
-    NB_CUDA(cudaFuncSetAttribute(phys_env_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = smem;
-  }
   const int wpb = phys_pick_warps(P);
   const int grid = nb::ceil_div(n_envs, wpb);
-  phys_env_step_kernel<<<grid, wpb * 32, smem, (cudaStream_t)stream>>>(
+  if (phys_dense(P)) {
+    static int configured = 0;
+    if (configured < smem) {
+      NB_CUDA(cudaFuncSetAttribute(phys_env_step_kernel<7, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      NB_CUDA(cudaFuncSetAttribute(phys_env_step_kernel<7, 4>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+      configured = smem;
+    }
+    phys_env_step_kernel<7, 4><<<grid, wpb * 32, smem, (cudaStream_t)stream>>>(
+        *P, imodel, fmodel, qpos, qvel, warm, step_count, ep_return, action, action_stride, obs_f32,
+        (__nv_bfloat16*)obs_bf16, obs_bf16_stride, next_obs_f32, (__nv_bfloat16*)next_obs_bf16, reward, done,
+        terminated, finished_return, rng_counter, seed, n_envs, do_reset, ep_stats, dbg);
+    NB_LAUNCH_CHECK();
+    return NB_OK;
+  }
+  static int configured = 0;
+  if (configured < smem) {
+    NB_CUDA(cudaFuncSetAttribute(phys_env_step_kernel<NB_PHYS_WARPS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = smem;
+  }
+  phys_env_step_kernel<NB_PHYS_WARPS, 2><<<grid, wpb * 32, smem, (cudaStream_t)stream>>>(
       *P, imodel, fmodel, qpos, qvel, warm, step_count, ep_return, action, action_stride, obs_f32,
       (__nv_bfloat16*)obs_bf16, obs_bf16_stride, next_obs_f32, (__nv_bfloat16*)next_obs_bf16, reward, done,
       terminated, finished_return, rng_counter, seed, n_envs, do_reset, ep_stats, dbg);

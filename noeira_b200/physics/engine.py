@@ -59,7 +59,8 @@ def make_params(m: RigidModel, task: TaskSpec) -> PhysParams:
     P.fmodel_words = (len(f32) + 3) // 4 * 4
     nb, nv, nvp, rmax = m.nbody, m.nv, P.nvp, o.rmax
     P.warm_words = (m.nlimit + 3 * m.ncs + 3) // 4 * 4
-    scratch = nb * 3 + nb * 4 + nb * 9 + nv * 6 + nb * 10 * 2 + nb * 6 * 2 + nv * nvp + 128 + 2 * rmax * nvp + rmax * 8 + 32 * 33
+    # persistent arrays + the larger of (packed Delassus triangle, the per-body arrays it overlays); see `carve`
+    scratch = nb * 3 + nb * 9 + nv * 6 + nv * nvp + 128 + 2 * rmax * nvp + rmax * 8 + max(32 * 33 // 2, nb * (4 + 10 * 2 + 6 * 2))
     P.warp_words = (scratch + 3) // 4 * 4 + P.warm_words
     P.frame_skip, P.pgs_iters, P.max_steps = task.frame_skip, o.pgs_iters, task.max_steps
     P.friction_rows = 0 if not o.friction_rows else (1 if m.planar else 2)
