@@ -98,6 +98,23 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def chained(fn, k=50):
+        """k calls back to back inside one event pair: the per-call time inside a captured training step, where the
+        ranks' launch skew (tens of microseconds after a host barrier) is paid once, not per call."""
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(k):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / k], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     # correctness of the plain all-reduce against NCCL once
     n = 1 << 20
     fused(1, n, False)
@@ -119,7 +136,11 @@ def main():
             row[name + "_us"] = round(t * 1e3, 2)
             row[name + "_frac_of_roofline"] = round(roof_ms / t, 3)
             row[name + "_frac_of_p2p_bound"] = round(2 * roof_ms / t, 3)
+            if size <= (16 << 20):
+                row[name + "_chained_us"] = round(chained((lambda: push(n, args.adam)) if algo == 3 else (lambda: fused(algo, n, args.adam))) * 1e3, 2)
         t = timed(lambda: nccl(n, args.adam))
+        if size <= (16 << 20):
+            row["nccl_chained_us"] = round(chained(lambda: nccl(n, args.adam)) * 1e3, 2)
         row["nccl_us"] = round(t * 1e3, 2)
         row["nccl_frac_of_roofline"] = round(roof_ms / t, 3)
         row["nccl_frac_of_p2p_bound"] = round(2 * roof_ms / t, 3)

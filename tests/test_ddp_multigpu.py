@@ -17,6 +17,9 @@ def _ngpu():
 def _world_sizes():
     """Every power of two from 2 up to the number of GPUs of the box (2, 4, 8 on a full node)."""
     n, out = _ngpu(), []
+    only = os.environ.get("NB_TEST_WORLDS")          # e.g. "4,8": restrict the sweep (each size is one torchrun launch)
+    if only:
+        return [int(x) for x in only.split(",") if int(x) <= n] or [2]
     w = 2
     while w <= min(n, 8):
         out.append(w)
