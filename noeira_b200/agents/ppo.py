@@ -128,6 +128,14 @@ class PPOTrainer:
             from ..ops.mlp import fusable
             for net in (self.actor, self.critic):
                 self._fused[id(net)] = fusable(*self._layers(net))
+        # fused update path: both networks through one grouped forward launch, one grouped data-gradient launch and
+        # six parameter-gradient branches (one per layer) — see ops/mlp.py
+        self._train_pass = None
+        if self._fused.get(id(self.actor)) and self._fused.get(id(self.critic)):
+            from ..ops.mlp import Mlp3Pass
+            self._train_pass = (Mlp3Pass(*self._layers(self.actor), self.mb, self.device),
+                                Mlp3Pass(*self._layers(self.critic), self.mb, self.device))
+            self._layer_pg = [[Branch(torch.cuda.Stream(device=self.device), 4 + 3 * i + j) for j in range(3)] for i in range(2)]
         self._graph_launches = {}
         self.iteration = 0
         self.env.reset_batch()
@@ -188,6 +196,8 @@ class PPOTrainer:
     def _minibatch(self):
         cfg, env, lib = self.cfg, self.env, self.lib
         head = self.actor.mods[2]
+        if self._train_pass is not None:
+            return self._minibatch_fused()
         check(lib.nb_ppo_gather(ptr(self.obs_buf), ctypes.c_int(env.obs_pad * 2), ptr(self.act_buf), ctypes.c_int(self.AP),
                                 ptr(self.logp_buf), ptr(self.adv_buf), ptr(self.ret_buf), ptr(self.mb_obs),
                                 ptr(self.mb_act), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.mb_ret),
@@ -217,6 +227,49 @@ class PPOTrainer:
         # the optimizer steps stay on the main stream; with a gradient sync both arenas are reduced and updated by one
         # cross-GPU kernel (every rank runs its cross-GPU kernels in the same order)
         br.join()
+        if self.grad_sync is not None and hasattr(self.grad_sync, "reduce_and_step_many"):
+            self.grad_sync.reduce_and_step_many([self.actor_opt, self.critic_opt])
+        else:
+            self._opt_step(self.actor_opt)
+            self._opt_step(self.critic_opt)
+        check(lib.nb_ppo_counter(ptr(self.counters), ctypes.c_int(0), ctypes.c_int(0), stream_ptr()), "counter")
+
+    def _gather(self):
+        cfg, env = self.cfg, self.env
+        check(self.lib.nb_ppo_gather(ptr(self.obs_buf), ctypes.c_int(env.obs_pad * 2), ptr(self.act_buf), ctypes.c_int(self.AP),
+                                     ptr(self.logp_buf), ptr(self.adv_buf), ptr(self.ret_buf), ptr(self.mb_obs),
+                                     ptr(self.mb_act), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.mb_ret),
+                                     ptr(self.partials), ptr(self.adv_stats), ctypes.c_int(self.pool), ctypes.c_int(self.mb),
+                                     ctypes.c_int(cfg.n_minibatches), ctypes.c_ulonglong(cfg.seed * 104729 + 7),
+                                     ptr(self.counters), stream_ptr()), "ppo_gather")
+
+    def _minibatch_fused(self):
+        """One minibatch update with the fused kernels: gather → grouped forward (actor + critic, one launch) → the two
+        loss kernels → grouped data-gradient chain (one launch) → six parameter-gradient chains on side streams →
+        optimizer (with a gradient sync: one cross-GPU kernel for both arenas)."""
+        from ..ops.mlp import mlp3_backward_group, mlp3_forward_group, mlp3_param_grads
+        cfg, env, lib = self.cfg, self.env, self.lib
+        head = self.actor.mods[2]
+        pa, pc = self._train_pass
+        self._gather()
+        x = self.mb_obs
+        mu, v = mlp3_forward_group([pa, pc], [x, x])
+        check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
+                                    ptr(self.partials_v), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
+                                    ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
+        check(lib.nb_ppo_objective(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(self.mb_act),
+                                   ctypes.c_int(self.AP), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.adv_stats),
+                                   ptr(self.dmu), ctypes.c_int(self.AP), ptr(self.partials), ptr(self.partials2),
+                                   ptr(head.log_std.grad_storage), ptr(self.metrics), ctypes.c_int(self.mb),
+                                   ctypes.c_int(env.act_dim), ctypes.c_float(cfg.clip_eps),
+                                   ctypes.c_float(cfg.entropy_coef), ctypes.c_float(1.0 / self.mb), stream_ptr()),
+              "ppo_objective")
+        mlp3_backward_group([pa, pc], [x, x], [self.dmu, self.dv])
+        mlp3_param_grads(pa, x, self.dmu, self._layer_pg[0])
+        mlp3_param_grads(pc, x, self.dv, self._layer_pg[1])
+        for brs in self._layer_pg:
+            for b in brs:
+                b.join()
         if self.grad_sync is not None and hasattr(self.grad_sync, "reduce_and_step_many"):
             self.grad_sync.reduce_and_step_many([self.actor_opt, self.critic_opt])
         else:
