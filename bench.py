@@ -34,6 +34,48 @@ def _reference_arm(args):
     return 0
 
 
+def _secondary(world, args):
+    """Run the secondary workloads as ONE child job (its own torchrun for N > 1) and collect the JSON line each of
+    them prints.  The child is given a time limit; whatever it printed before is kept."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 23
+    cmd = [sys.executable]
+    if world > 1:
+        cmd += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                "--master-port", str(port)]
+    cmd += [os.path.join(here, "bench.py"), "--gpus", str(world), "--workload", "secondary", "--steps", "5", "--warmup", "3"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_PORT", "TORCHELASTIC_RUN_ID",
+                                                             "GROUP_RANK", "ROLE_RANK", "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE",
+                                                             "GROUP_WORLD_SIZE", "TORCHELASTIC_RESTART_COUNT",
+                                                             "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_USE_AGENT_STORE",
+                                                             "TORCH_NCCL_ASYNC_ERROR_HANDLING", "TORCHELASTIC_ERROR_FILE")}
+    env["MASTER_ADDR"] = "127.0.0.1"
+    out = {}
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=int(args.secondary_timeout), env=env, cwd=here,
+                           start_new_session=True)
+        text, note = r.stdout, (None if r.returncode == 0 else f"child exit code {r.returncode}")
+    except subprocess.TimeoutExpired as e:          # the child (its own session) has been killed by subprocess.run
+        text = e.stdout.decode() if isinstance(e.stdout, bytes) else (e.stdout or "")
+        note = f"stopped after {args.secondary_timeout} s"
+    for ln in text.splitlines():
+        ln = ln.strip()
+        if not ln.startswith("{"):
+            continue
+        try:
+            d = json.loads(ln)
+        except ValueError:
+            continue
+        key = d.get("metric") or d.get("workload")
+        if key:
+            keep = ("value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "config", "e2e", "model_tflops_per_gpu", "gpu_launches",
+                    "final_loss", "rows", "error", "clocks")
+            out[key] = {k: d[k] for k in keep if k in d}
+    if note:
+        out["note"] = note
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -45,6 +87,9 @@ def main():
     ap.add_argument("--sync", default="fused", help="fused | nccl  (gradient reduction path for N>1)")
     ap.add_argument("--eager", action="store_true", help="secondary workloads: launch kernels one by one instead of replaying a graph")
     ap.add_argument("--small", action="store_true", help="reduced model for smoke runs of secondary workloads")
+    ap.add_argument("--secondary", default="auto", help="auto | none: after the headline, run ACT / VLA / world model / "
+                    "all-reduce in a child job and report them under the `secondary` key")
+    ap.add_argument("--secondary-timeout", type=int, default=420)
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm(args)
@@ -94,26 +139,33 @@ def main():
     barrier()
     check_status()
 
-    # ---------------- device-timed region
+    # ---------------- device-timed region: blocks of exactly `steps` iterations, each bracketed by barrier +
+    # synchronize, repeated until about 3 s have been timed; the reported block is the median one, so a single noisy
+    # block does not set the number and the clock sampler sees seconds of load instead of a fraction of one
     launches0 = _native.launch_count()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    for s, e in evs:
-        flush.zero_()
-        s.record()
-        tr.train_iteration(read_metrics=False)
-        e.record()
-    barrier()
+    blocks = []
+    timed_ms, max_repeats = 0.0, 25
+    while len(blocks) < 3 or (timed_ms < 3000.0 and len(blocks) < max_repeats):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        barrier()
+        for s, e in evs:
+            flush.zero_()
+            s.record()
+            tr.train_iteration(read_metrics=False)
+            e.record()
+        barrier()
+        ms = sum(s.elapsed_time(e) for s, e in evs)
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank sees the same value → the same loop count
+        blocks.append(float(t.item()))
+        timed_ms += blocks[-1]
     clocks = sampler.stop() if rank == 0 else {}
-    launches = _native.launch_count() - launches0
-    ms = sum(s.elapsed_time(e) for s, e in evs)
-    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
+    launches = (_native.launch_count() - launches0) // len(blocks)
+    ms_total = sorted(blocks)[len(blocks) // 2]
     metrics = tr.read_metrics()
     check_status()
 
@@ -143,8 +195,9 @@ def main():
 
     env_steps = tr.env_steps_per_iteration * args.steps * world
     value = env_steps / (ms_total / 1e3)
+    line = None
     if rank == 0:
-        print(json.dumps({
+        line = {
             "metric": "ppo_env_steps_per_s", "value": round(value, 1), "unit": "env-steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -155,13 +208,26 @@ def main():
                        "grad_sync": (args.sync if world > 1 else "none"),
                        "l2": "flushed between timed iterations (256 MB write outside the event pairs)"},
             "clocks": clocks,
+            "timing": {"blocks_of_steps": len(blocks), "block_ms": [round(b, 3) for b in blocks],
+                       "reported": "median block (each block = exactly `steps` iterations, device-timed, max over ranks)"},
             "e2e": {"value": round(env_steps / e2e_s, 1), "unit": "env-steps/s", "h2d_bytes_per_step": 64,
-                    "d2h_bytes_per_step": 48},
+                    "d2h_bytes_per_step": 48,
+                    "note": "wall clock of `steps` iterations incl. the per-iteration H2D control block and D2H metrics; "
+                            "no L2 flush between iterations, which is why it can exceed the device-timed value"},
             "gpu_launches": launches,
             "train_metrics": {k: (None if v != v else round(v, 5)) for k, v in metrics.items()},
-        }))
+        }
+    # ---------------- secondary workloads (ACT, VLA, world model, all-reduce) in a child job of the same size, after
+    # this job has released its GPUs' memory: a failure there cannot take the headline line with it
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    del tr, env, flush
+    torch.cuda.empty_cache()
+    if rank == 0:
+        if args.secondary != "none" and os.environ.get("NOEIRA_BENCH_SECONDARY", "1") != "0":
+            line["secondary"] = _secondary(world, args)
+        print(json.dumps(line), flush=True)
     return 0
 
 

@@ -30,6 +30,15 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    table(rank, world, args.max_mb, args.iters, args.adam, emit=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def table(rank, world, max_mb, iters, adam, emit=True):
+    """Time every form at sizes 64 KB … max_mb (x4 steps) in the current process group; returns the rows."""
+    import types
+    args = types.SimpleNamespace(max_mb=max_mb, iters=iters, adam=adam)
     from noeira_b200._native import check, cuda_lib, ptr, stream_ptr
     from noeira_b200.ops.status import check_status, device_status
     from noeira_b200.parallel.symm import SIGNAL_PAD_WORDS, SymmetricHeap
@@ -125,6 +134,7 @@ def main():
     torch.cuda.synchronize()
     err = max(err, (pout[:n] * world - ref[:n]).abs().max().item())     # the push form returns the mean (hyper[GSCALE] = 1/N)
     size = 64 << 10
+    rows = []
     while size <= args.max_mb << 20:
         n = size // 4
         row = {"bytes": size, "world": world, "adam": args.adam, "check_max_err": err}
@@ -145,12 +155,12 @@ def main():
         row["nccl_frac_of_roofline"] = round(roof_ms / t, 3)
         row["nccl_frac_of_p2p_bound"] = round(2 * roof_ms / t, 3)
         row["busbw_two_shot_gbs"] = round(2 * (world - 1) / world * size / (row["two_shot_us"] * 1e-6) / 1e9, 1)
-        if rank == 0:
+        rows.append(row)
+        if rank == 0 and emit:
             print(json.dumps(row), flush=True)
         size *= 4
     check_status()
-    dist.barrier()
-    dist.destroy_process_group()
+    return rows
 
 
 if __name__ == "__main__":

@@ -1,4 +1,4 @@
-"""Secondary benchmark workloads behind ``bench.py --workload {wm,gpt}``.
+"""Secondary benchmark workloads behind ``bench.py --workload {act,vla,wm,sac_cpu,secondary}``.
 
 wm   Dreamer-style world-model dynamics transformer (24 × d2048, 16/4 heads GQA, SwiGLU 5632, block-causal over
      64 frames × (256 latents + 1 action token)), flow-matching loss, AdamW 3e-4, bf16, tensor parallel over all N
@@ -21,7 +21,47 @@ def run(args, rank, local_rank, world):
         raise
 
 
+def run_secondary(args, rank, local_rank, world):
+    """ACT, VLA, world model (tensor parallel over all ranks) and the all-reduce table, one after the other in this
+    process group; each prints its own JSON line, a failure of one is reported and the next one still runs."""
+    import copy
+    import gc
+    plan = (("act", 5), ("vla", 3), ("wm", 2), ("allreduce", 5))
+    for name, steps in plan:
+        a = copy.copy(args)
+        a.workload, a.steps, a.warmup = name, steps, 3
+        try:
+            if name == "wm":
+                run_wm(a, rank, local_rank, world, finalize=False)
+            elif name == "allreduce":
+                if world > 1:
+                    run_allreduce(a, rank, local_rank, world)
+            else:
+                run_dp(a, rank, local_rank, world, finalize=False)
+        except Exception:  # noqa: BLE001
+            import traceback
+            if rank == 0:
+                print(json.dumps({"workload": name, "error": traceback.format_exc()[-800:]}), flush=True)
+        gc.collect()
+        torch.cuda.empty_cache()
+        if world > 1:
+            dist.barrier()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_allreduce(args, rank, local_rank, world):
+    """Fused all-reduce forms against NCCL at a few bucket sizes (the full table: benchmarks/bench_allreduce.py)."""
+    from benchmarks import bench_allreduce
+    rows = bench_allreduce.table(rank, world, max_mb=64, iters=5, adam=False, emit=False)
+    if rank == 0:
+        print(json.dumps({"metric": "allreduce_us", "n_gpus": world, "unit": "us", "rows": rows}), flush=True)
+
+
 def _run(args, rank, local_rank, world):
+    if args.workload == "secondary":
+        return run_secondary(args, rank, local_rank, world)
     if args.workload == "wm":
         return run_wm(args, rank, local_rank, world)
     if args.workload in ("act", "vla"):
@@ -31,7 +71,7 @@ def _run(args, rank, local_rank, world):
     raise SystemExit(f"unknown workload {args.workload}")
 
 
-def run_wm(args, rank, local_rank, world):
+def run_wm(args, rank, local_rank, world, finalize=True):
     from noeira_b200 import _native
     from noeira_b200.models.world_model import WorldModel, WorldModelConfig
     from noeira_b200.ops import check_status
@@ -104,12 +144,12 @@ def run_wm(args, rank, local_rank, world):
             "e2e": {"value": round(B * args.steps / e2e_s, 4), "unit": "sequences/s",
                     "h2d_bytes_per_step": int(z1_h.numel() * 4 + act_h.numel() * 4), "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": round(loss, 5)}))
-    if world > 1:
+    if world > 1 and finalize:
         dist.destroy_process_group()
     return 0
 
 
-def run_dp(args, rank, local_rank, world):
+def run_dp(args, rank, local_rank, world, finalize=True):
     """ACT (batch 8 / GPU, 2 cameras 3x480x640 uint8) and SmolVLA-style VLA (batch 64 / GPU, 3 cameras 3x512x512),
     data parallel with the fused gradient all-reduce + AdamW kernel.  Metric: training samples / s (whole job)."""
     from noeira_b200 import _native
@@ -188,7 +228,7 @@ def run_dp(args, rank, local_rank, world):
                     "h2d_bytes_per_step": int(sum(v.numel() * v.element_size() for v in host.values())), "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "params_m": round(sum(p.numel for _, p in tr.model.named_params()) / 1e6, 1),
             "final_loss": round(loss_of(), 5)}))
-    if world > 1:
+    if world > 1 and finalize:
         dist.destroy_process_group()
     return 0
 

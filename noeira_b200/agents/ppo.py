@@ -148,7 +148,7 @@ class PPOTrainer:
 
     def _forward(self, net, x, save):
         """Forward of the actor or the critic: the fused three-layer kernel when it applies, else layer by layer."""
-        if self._fused.get(id(net)) and x.shape[0] >= 8192:     # below that three GEMM launches are as fast (6.5 us each)
+        if self._fused.get(id(net)) and x.shape[0] >= 1024:     # one launch instead of three
             from ..ops.mlp import mlp3_forward
             l1, l2, l3 = self._layers(net)
             y = mlp3_forward(x, l1, l2, l3, save=save)
@@ -272,6 +272,9 @@ class PPOTrainer:
                 b.join()
         if self.grad_sync is not None and hasattr(self.grad_sync, "reduce_and_step_many"):
             self.grad_sync.reduce_and_step_many([self.actor_opt, self.critic_opt])
+        elif self.grad_sync is None:
+            from ..nn.optim import step_many
+            step_many([self.actor_opt, self.critic_opt], zero_grad=True)
         else:
             self._opt_step(self.actor_opt)
             self._opt_step(self.critic_opt)

@@ -277,21 +277,40 @@ int tmap2d(CUtensorMap* tm, const void* base, long long inner, long long outer, 
 // h2, written out in bf16 (the weight-gradient GEMMs read it) and kept in shared memory as the A operand of the second
 // product.  G1 and G2 are the gradients with respect to the layers' PRE-activations, i.e. exactly the operands of
 // dW1 = Xᵀ G1, dW2 = h1ᵀ G2, dW3 = h2ᵀ dY and of the bias column sums.  The first layer's input gradient is not needed.
+// The bias gradients ride along: every CTA sums the columns of its dY, G2 and G1 tiles out of shared memory and
+// writes the three partial rows; a small second kernel adds the partials in CTA order (deterministic).
 //   warp 0      TMA: W2 as a K-major B operand (box 64 k x 256 n per k-block), 2-stage ring
 //   warp 1      MMA issuer
-//   warps 2..5  stage dY and W3 (zero padded to K = 64) into swizzled tiles; epilogues (thread = row)
+//   warps 2..5  stage dY and W3 (zero padded to K = 64) into swizzled tiles; epilogues (thread = row); column sums
 struct MlpBwdParams {
   int M, n3;
   int ld_dy, ld_w3, ld_h, ld_g;
   int act;
   const __nv_bfloat16 *dy, *w3, *h1, *h2;
   __nv_bfloat16 *g1, *g2;
+  float* bias_part;   // optional [gridDim.x][3][256]: this CTA's column sums of g1, g2, dy (bias gradients, unreduced)
   unsigned int* status;
 };
 struct MlpBwdGroup {
   CUtensorMap w2[2];
   MlpBwdParams prm[2];
 };
+
+// Sum of columns 2t, 2t+1 over the 128 rows of a [128 x 256] bf16 tile in the swizzled K-major layout (four k-blocks
+// of 16 KB; row r of a k-block at (r>>3)·1024 + (r&7)·128, 16-byte chunk c at position c ^ (r&7)).
+__device__ __forceinline__ float2 tile_colsum2(const uint8_t* tile, int t) {
+  const int col = 2 * t;
+  const uint8_t* kb = tile + (col >> 6) * 16384;
+  const int ch = (col & 63) >> 3, within = (col & 7) * 2;
+  float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 8
+  for (int r = 0; r < ROWS; ++r) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(kb + (r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4) + within);
+    acc.x += __low2float(v);
+    acc.y += __high2float(v);
+  }
+  return acc;
+}
 
 __device__ __forceinline__ float dact1(int act, float h) { return act == NB_ACT_TANH ? 1.f - h * h : (h > 0.f ? 1.f : 0.f); }
 
@@ -411,6 +430,15 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
     fence_proxy_async();
     __syncwarp();
     if (lane == 0) mbar_arrive(staged);
+    float* part = p.bias_part ? p.bias_part + (size_t)blockIdx.x * 3 * HID : nullptr;
+    if (part) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // every row of the dY tile is in shared memory
+      if (t < 8) {                                      // 16 columns: the tile's k-block 0, chunks 0 and 1
+        const float2 sum = tile_colsum2(sDY, t);
+        part[2 * HID + 2 * t] = sum.x;
+        part[2 * HID + 2 * t + 1] = sum.y;
+      }
+    }
     bool ok = true;
     uint8_t* grow = sG + (r >> 3) * 1024 + (r & 7) * 128;
     for (int layer = 0; layer < 2 && ok; ++layer) {
@@ -438,7 +466,9 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
                                                    __uint_as_float(rr[2 * j + 1]) * dact1(p.act, h1));
           pk[j] = *reinterpret_cast<uint32_t*>(&g);
         }
-        if (layer == 0) {
+        if (layer == 0 || part) {
+          // layer 0: G2 is the A operand of the second product.  layer 1: that product has completed (acc_full[1]),
+          // so the same tile holds G1 for the column sums.
           const int kb = c0 >> 6, ch = (c0 & 63) >> 3;
           uint8_t* base = grow + kb * 16384;
           *reinterpret_cast<uint4*>(base + (((ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -456,6 +486,14 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
         __syncwarp();
         if (lane == 0) mbar_arrive(g_ready);
       }
+      if (part) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the whole tile is written
+        const float2 sum = tile_colsum2(sG, t);
+        float* dst = part + (layer == 0 ? HID : 0);       // [0] g1, [1] g2, [2] dy
+        dst[2 * t] = sum.x;
+        dst[2 * t + 1] = sum.y;
+        if (layer == 0) asm volatile("bar.sync 1, 128;" ::: "memory");   // sums read before layer 1 overwrites the tile
+      }
     }
     if (!ok) *abort_flag = 1;
   }
@@ -468,6 +506,27 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
   }
 }
 
+// Bias gradients: db1 += Σ_cta part[cta][0], db2 += Σ part[cta][1], db3 += Σ part[cta][2][:n3], in CTA order.
+struct BiasFinishNet {
+  const float* part;
+  float *db1, *db2, *db3;
+  int ctas, n3;
+};
+struct BiasFinishGroup {
+  BiasFinishNet net[2];
+};
+__global__ void __launch_bounds__(HID)
+mlp3_bias_finish_kernel(const BiasFinishGroup g) {
+  const BiasFinishNet& n = g.net[blockIdx.y];
+  const int layer = blockIdx.x, col = threadIdx.x;
+  if (n.part == nullptr) return;
+  float* dst = layer == 0 ? n.db1 : (layer == 1 ? n.db2 : n.db3);
+  if (dst == nullptr || (layer == 2 && col >= n.n3)) return;
+  float acc = 0.f;
+  for (int c = 0; c < n.ctas; ++c) acc += n.part[((size_t)c * 3 + layer) * HID + col];
+  dst[col] += acc;
+}
+
 }  // namespace
 
 // One network of a grouped launch (mirrored by a ctypes.Structure in noeira_b200/ops/mlp.py — keep the field order).
@@ -478,6 +537,8 @@ struct NbMlpNet {
   void *h1, *h2;                     // forward: optional saves / backward: saved activations, bf16 [M, ld_h]
   const void* dy;                    // backward: bf16 [M, ld_dy], n3 columns used
   void *g1, *g2;                     // backward: bf16 [M, ld_g] gradients of the pre-activations of layers 1 and 2
+  float* bias_part;                  // backward: optional fp32 scratch [ceil(M/128)][3][256] for the bias gradients
+  float *db1, *db2, *db3;            // backward: fp32 bias gradients (accumulated into) when bias_part is given
   int ldx, ldw1, ldw2, ldw3, ld_out, ld_h, ld_dy, ld_g;
   int M, k0, n3, act;
 };
@@ -555,6 +616,7 @@ int nb_mlp3_bwd_group(const NbMlpNet* net, int nets, unsigned int* status, void*
     p.dy = (const __nv_bfloat16*)n.dy; p.w3 = (const __nv_bfloat16*)n.w3;
     p.h1 = (const __nv_bfloat16*)n.h1; p.h2 = (const __nv_bfloat16*)n.h2;
     p.g1 = (__nv_bfloat16*)n.g1; p.g2 = (__nv_bfloat16*)n.g2;
+    p.bias_part = n.bias_part;
     p.status = status;
     max_m = n.M > max_m ? n.M : max_m;
   }
@@ -565,6 +627,20 @@ int nb_mlp3_bwd_group(const NbMlpNet* net, int nets, unsigned int* status, void*
   }
   mlp3_bwd_kernel<<<dim3(ceil_div(max_m, ROWS), nets), MLP_THREADS, BWD_SMEM, (cudaStream_t)stream>>>(g);
   NB_LAUNCH_CHECK();
+  BiasFinishGroup f;
+  memset(&f, 0, sizeof(f));
+  bool any = false;
+  for (int i = 0; i < nets; ++i) {
+    const NbMlpNet& n = net[i];
+    if (!n.bias_part) continue;
+    any = true;
+    f.net[i].part = n.bias_part; f.net[i].db1 = n.db1; f.net[i].db2 = n.db2; f.net[i].db3 = n.db3;
+    f.net[i].ctas = ceil_div(n.M, ROWS); f.net[i].n3 = n.n3;
+  }
+  if (any) {
+    mlp3_bias_finish_kernel<<<dim3(3, nets), HID, 0, (cudaStream_t)stream>>>(f);
+    NB_LAUNCH_CHECK();
+  }
   return NB_OK;
 }
 

@@ -54,6 +54,71 @@ arena_adamw_kernel(float* __restrict__ val, const float* __restrict__ grd, float
   }
 }
 
+// Several arenas (optimizers) in ONE launch, the step counters t, β₁ᵗ, β₂ᵗ advanced in the same kernel: every block
+// derives the advanced powers from the values it reads at entry, the last block (ticket) writes them back.  Four
+// launches (advance + update per optimizer) of an actor-critic update become one.
+constexpr int MULTI_MAX = 4, MULTI_CHUNK4 = 256 * 8;
+struct MultiSeg {
+  float *val, *grd, *m, *v;
+  __nv_bfloat16* shadow;
+  const unsigned char* row_flags;
+  float* hyper;
+  long long n4;
+  int first_block;
+};
+struct MultiArgs {
+  MultiSeg seg[MULTI_MAX];
+  int nseg, zero_grad;
+  unsigned int* ticket;
+};
+__global__ void __launch_bounds__(256)
+arena_adamw_multi_kernel(const __grid_constant__ MultiArgs a) {
+  int s = 0;
+  while (s + 1 < a.nseg && (int)blockIdx.x >= a.seg[s + 1].first_block) ++s;
+  const MultiSeg& sg = a.seg[s];
+  nb::AdamHyper h = nb::load_hyper(sg.hyper);
+  h.b1t *= h.beta1;
+  h.b2t *= h.beta2;
+  const long long base = (long long)((int)blockIdx.x - sg.first_block) * MULTI_CHUNK4;
+#pragma unroll 2
+  for (int u = 0; u < 8; ++u) {
+    const long long i = base + u * 256 + threadIdx.x;
+    if (i >= sg.n4) break;
+    const unsigned char fl = sg.row_flags ? sg.row_flags[i >> 3] : (unsigned char)1;
+    float4 p = reinterpret_cast<float4*>(sg.val)[i];
+    if (!(fl & 2)) {
+      float4 g = reinterpret_cast<const float4*>(sg.grd)[i];
+      float4 mm = reinterpret_cast<float4*>(sg.m)[i];
+      float4 vv = reinterpret_cast<float4*>(sg.v)[i];
+      nb::adamw_update4(p, g, mm, vv, h, (fl & 1) != 0);
+      reinterpret_cast<float4*>(sg.val)[i] = p;
+      reinterpret_cast<float4*>(sg.m)[i] = mm;
+      reinterpret_cast<float4*>(sg.v)[i] = vv;
+    }
+    if (sg.shadow) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(sg.shadow)[i] = pk;
+    }
+    if (a.zero_grad) reinterpret_cast<float4*>(sg.grd)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.ticket, 1u) == gridDim.x - 1) {
+      *a.ticket = 0u;
+      for (int k = 0; k < a.nseg; ++k) {
+        float* hy = a.seg[k].hyper;
+        hy[NB_H_T] += 1.f;
+        hy[NB_H_B1T] *= hy[NB_H_BETA1];
+        hy[NB_H_B2T] *= hy[NB_H_BETA2];
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 arena_sgd_kernel(float* __restrict__ val, const float* __restrict__ grd, float* __restrict__ mom,
                  __nv_bfloat16* __restrict__ shadow, const unsigned char* __restrict__ row_flags, long long n4,
@@ -245,6 +310,31 @@ extern "C" {
 
 int nb_adam_advance(float* hyper, void* stream) {
   adam_advance_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(hyper);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+// Adam(W) step of up to 4 arenas in one launch, step counters included (see arena_adamw_multi_kernel).  `ticket`: one
+// zero-initialised u32 owned by the caller.
+int nb_arena_adamw_multi(int nseg, float* const* val, float* const* grd, float* const* m, float* const* v,
+                         void* const* shadow, const unsigned char* const* row_flags, float* const* hyper,
+                         const long long* n, int zero_grad, unsigned int* ticket, void* stream) {
+  if (nseg < 1 || nseg > MULTI_MAX || !ticket) return NB_ERR_BAD_ARG;
+  MultiArgs a;
+  a.nseg = nseg; a.zero_grad = zero_grad; a.ticket = ticket;
+  int blocks = 0;
+  for (int k = 0; k < nseg; ++k) {
+    if (n[k] <= 0 || n[k] % 4) return NB_ERR_UNALIGNED;
+    MultiSeg& s = a.seg[k];
+    s.val = val[k]; s.grd = grd[k]; s.m = m[k]; s.v = v[k];
+    s.shadow = shadow ? (__nv_bfloat16*)shadow[k] : nullptr;
+    s.row_flags = row_flags ? row_flags[k] : nullptr;
+    s.hyper = hyper[k];
+    s.n4 = n[k] / 4;
+    s.first_block = blocks;
+    blocks += (int)((s.n4 + MULTI_CHUNK4 - 1) / MULTI_CHUNK4);
+  }
+  arena_adamw_multi_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(a);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

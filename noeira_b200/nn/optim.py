@@ -151,6 +151,38 @@ class AdamW(Optimizer):
         a.bump_versions(shadow_fresh=False)
 
 
+_MULTI = {}
+
+
+def step_many(opts, zero_grad: bool = True):
+    """One Adam(W) step of several optimizers.  On CUDA (up to four AdamW-family optimizers without gradient clipping)
+    this is ONE kernel that also advances their step counters; otherwise each optimizer steps on its own."""
+    opts = list(opts)
+    if (len(opts) < 2 or len(opts) > 4 or not all(type(o) in (AdamW, Adam) and o.cuda and o.max_grad_norm <= 0 for o in opts)):
+        for o in opts:
+            if o.max_grad_norm > 0:
+                o.clip()
+            o.step(zero_grad=zero_grad)
+        return
+    key = tuple(id(o) for o in opts)
+    a = _MULTI.get(key)
+    if a is None:
+        k = len(opts)
+        P, L = ctypes.c_void_p * k, ctypes.c_longlong * k
+        arr = lambda ts: P(*[t.data_ptr() if t is not None else 0 for t in ts])
+        ars = [o.arena for o in opts]
+        a = dict(val=arr([x.val for x in ars]), m=arr([x.m for x in ars]), v=arr([x.v for x in ars]),
+                 shadow=arr([x.shadow for x in ars]), flags=arr([x.row_flags for x in ars]), hyper=arr([o.hyper for o in opts]),
+                 n=L(*[x.numel for x in ars]), ticket=torch.zeros(1, dtype=torch.int32, device=opts[0].device), ars=ars)
+        _MULTI[key] = a
+    # gradient arenas may have been re-pointed (e.g. into symmetric memory): read their addresses at call time
+    grd = (ctypes.c_void_p * len(opts))(*[x.grd.data_ptr() for x in a["ars"]])
+    check(cuda_lib().nb_arena_adamw_multi(ctypes.c_int(len(opts)), a["val"], grd, a["m"], a["v"], a["shadow"], a["flags"], a["hyper"],
+                                          a["n"], ctypes.c_int(int(zero_grad)), ptr(a["ticket"]), stream_ptr()), "arena_adamw_multi")
+    for x in a["ars"]:
+        x.bump_versions(shadow_fresh=True)
+
+
 class Adam(AdamW):
     def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, **kw):
         super().__init__(named_params, lr=lr, betas=betas, eps=eps, weight_decay=0.0, **kw)

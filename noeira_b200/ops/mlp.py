@@ -20,7 +20,8 @@ from .status import device_status
 
 class NbMlpNet(ctypes.Structure):
     """Mirror of ``struct NbMlpNet`` (csrc/mlp_fused_tcgen05.cu): same field order."""
-    _fields_ = ([(n, ctypes.c_void_p) for n in ("x", "w1", "w2", "w3", "b1", "b2", "b3", "out", "h1", "h2", "dy", "g1", "g2")]
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("x", "w1", "w2", "w3", "b1", "b2", "b3", "out", "h1", "h2", "dy", "g1", "g2",
+                                                 "bias_part", "db1", "db2", "db3")]
                 + [(n, ctypes.c_int) for n in ("ldx", "ldw1", "ldw2", "ldw3", "ld_out", "ld_h", "ld_dy", "ld_g", "M", "k0", "n3",
                                                "act")])
 
@@ -48,6 +49,8 @@ class Mlp3Pass:
         self.h2 = torch.empty(M, 256, **h) if train else None
         self.g1 = torch.empty(M, 256, **h) if train else None
         self.g2 = torch.empty(M, 256, **h) if train else None
+        # per-CTA column sums of g1, g2, dy: the bias gradients come out of the data-gradient kernel
+        self.bias_part = torch.empty((M + 127) // 128, 3, 256, **f) if train else None
 
     def net(self, x, dy=None) -> NbMlpNet:
         l1, l2, l3 = self.l1, self.l2, self.l3
@@ -57,6 +60,10 @@ class Mlp3Pass:
         n.b1, n.b2, n.b3 = l1.bias.storage.data_ptr(), l2.bias.storage.data_ptr(), _p(l3.bias.storage if l3.bias is not None else None)
         n.out, n.h1, n.h2 = self.out.data_ptr(), _p(self.h1), _p(self.h2)
         n.dy, n.g1, n.g2 = _p(dy), _p(self.g1), _p(self.g2)
+        if dy is not None:
+            n.bias_part = _p(self.bias_part)
+            n.db1, n.db2 = l1.bias.grad_storage.data_ptr(), l2.bias.grad_storage.data_ptr()
+            n.db3 = _p(l3.bias.grad_storage if l3.bias is not None else None)
         n.ldx, n.ldw1, n.ldw2, n.ldw3 = x.stride(0), w1.stride(0), w2.stride(0), w3.stride(0)
         n.ld_out, n.ld_h, n.ld_g = 16, 256, 256
         n.ld_dy = dy.stride(0) if dy is not None else 0
@@ -79,26 +86,25 @@ def mlp3_forward_group(passes, xs):
 
 def mlp3_backward_group(passes, xs, dys):
     """Data-gradient chain of one or two networks in ONE launch; fills ``pass.g1`` / ``pass.g2`` (gradients of the
-    pre-activations of layers 1 and 2).  ``dys``: bf16 ``[M, >= out_dim]`` with a 16-byte row pitch."""
+    pre-activations of layers 1 and 2) and ACCUMULATES the three bias gradients of each network (column sums of g1,
+    g2, dy: per-CTA partials from the same kernel, added in CTA order by a second small launch).
+    ``dys``: bf16 ``[M, >= out_dim]`` with a 16-byte row pitch."""
     arr = (NbMlpNet * len(passes))(*[p.net(x[:, : p.l1.in_dim], dy) for p, x, dy in zip(passes, xs, dys)])
     check(cuda_lib().nb_mlp3_bwd_group(arr, ctypes.c_int(len(passes)), ptr(device_status(xs[0].device)), stream_ptr()),
           "mlp3_bwd_group")
 
 
 def mlp3_param_grads(p: Mlp3Pass, x, dy, branches=None):
-    """dW3 += h2ᵀ dy, dW2 += h1ᵀ g2, dW1 += xᵀ g1 and the three bias column sums, accumulated into the parameters'
-    fp32 gradient storage.  ``branches``: three ``ops.streams.Branch`` objects, one per layer, so the three chains
-    overlap; the caller joins them before the optimizer step."""
+    """dW3 += h2ᵀ dy, dW2 += h1ᵀ g2, dW1 += xᵀ g1, accumulated into the parameters' fp32 gradient storage (the bias
+    gradients were produced by ``mlp3_backward_group``).  ``branches``: three ``ops.streams.Branch`` objects, one per
+    layer, so the three split-K GEMMs overlap; the caller joins them before the optimizer step."""
     from .. import ops
-    from ..nn.layers import colsum_into
     work = ((p.l3, p.h2, dy), (p.l2, p.h1, p.g2), (p.l1, x[:, : p.l1.in_dim], p.g1))
     for i, (lin, a, g) in enumerate(work):
         n = lin.out_dim
 
         def run(lin=lin, a=a, g=g, n=n):
             ops.gemm(a, g[:, :n], a_mn=True, b_mn=True, out=lin.weight.grad_storage, accumulate=True, n=n)
-            if lin.bias is not None:
-                colsum_into(g, lin.bias.grad_storage, n)
         if branches is not None:
             with branches[i]:
                 run()

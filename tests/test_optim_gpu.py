@@ -63,3 +63,31 @@ def test_sumsq_clip_polyak():
     check(lib.nb_polyak(ptr(a), ptr(b), ctypes.c_longlong(n), ctypes.c_float(0.005), stream_ptr()), "polyak")
     torch.cuda.synchronize()
     assert torch.allclose(a, ref, atol=1e-6)
+
+
+def test_step_many_equals_separate_steps():
+    """Two optimizers stepped by the one-launch multi-arena kernel (step counters advanced inside it) end bit-identical
+    to stepping each on its own."""
+    import torch
+    from noeira_b200 import nn
+    from noeira_b200.nn.optim import step_many
+    nn.manual_seed(3)
+    mk = lambda o: nn.Sequential(nn.LinearTanh(17, 256), nn.Linear(256, o)).to("cuda")
+    a, b = [mk(6), mk(1)], [mk(6), mk(1)]
+    for x, y in zip(a, b):
+        y.copy_from(x)
+    oa = [nn.AdamW(n.named_params(), lr=1e-2, weight_decay=0.01) for n in a]
+    ob = [nn.AdamW(n.named_params(), lr=1e-2, weight_decay=0.01) for n in b]
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for _ in range(3):
+        for o1, o2 in zip(oa, ob):
+            gr = torch.randn(o1.arena.numel, device="cuda", generator=g)
+            o1.arena.grd.copy_(gr)
+            o2.arena.grd.copy_(gr)
+        step_many(oa, zero_grad=True)
+        for o in ob:
+            o.step(zero_grad=True)
+    torch.cuda.synchronize()
+    for o1, o2 in zip(oa, ob):
+        assert torch.equal(o1.arena.val, o2.arena.val) and torch.equal(o1.arena.shadow, o2.arena.shadow)
+        assert torch.equal(o1.hyper, o2.hyper) and float(o1.arena.grd.abs().max()) == 0.0
