@@ -90,6 +90,8 @@ def main():
     ap.add_argument("--secondary", default="auto", help="auto | none: after the headline, run ACT / VLA / world model / "
                     "all-reduce in a child job and report them under the `secondary` key")
     ap.add_argument("--secondary-timeout", type=int, default=420)
+    ap.add_argument("--min-time-ms", type=float, default=3000.0, help="repeat the timed block of `steps` iterations until "
+                    "this much device time has been measured (at least 3 blocks; 0 for a profiler run)")
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm(args)
@@ -148,7 +150,7 @@ def main():
         sampler.start()
     blocks = []
     timed_ms, max_repeats = 0.0, 25
-    while len(blocks) < 3 or (timed_ms < 3000.0 and len(blocks) < max_repeats):
+    while len(blocks) < 3 or (timed_ms < args.min_time_ms and len(blocks) < max_repeats):
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
         barrier()
         for s, e in evs:

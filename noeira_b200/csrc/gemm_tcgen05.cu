@@ -500,6 +500,52 @@ splitk_reduce_kernel(const GemmParams p, int BN) {
   epilogue_store16(p, row, col0, v, pf);
 }
 
+// The weight-gradient case (fp32 output, plain or accumulating, no bias / activation): one thread per FOUR output
+// columns, so a 256 x 256 gradient has 16 k threads in flight instead of 4 k and every split's load of a warp is one
+// contiguous 512-byte run.  Splits are still added in index order.
+__global__ void __launch_bounds__(256)
+splitk_reduce_f32_kernel(const GemmParams p, int BN) {
+  const int quads = BN / 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)p.tiles_m * p.tiles_n * BM * quads;
+  if (idx >= total) return;
+  const int c = (int)(idx % quads);
+  const int row_in_tile = (int)((idx / quads) % BM);
+  const int tile = (int)(idx / ((long long)quads * BM));
+  int mb, nb_;
+  tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
+  const int row = mb * BM + row_in_tile, col0 = nb_ * BN + c * 4;
+  if (row >= p.M || col0 >= p.N) return;
+  const size_t tile_elems = (size_t)BM * BN;
+  const float* src = p.ws + (size_t)tile * p.splits * tile_elems + (size_t)row_in_tile * BN + c * 4;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  int sp = 0;
+  for (; sp + 8 <= p.splits; sp += 8) {
+    float4 x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + u) * tile_elems));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { v.x += x[u].x; v.y += x[u].y; v.z += x[u].z; v.w += x[u].w; }
+  }
+  for (; sp < p.splits; ++sp) {
+    const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * tile_elems));
+    v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+  }
+  v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
+  float* o = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
+  if (col0 + 4 <= p.N && (p.ldd % 4 == 0)) {
+    if (p.accumulate) {
+      const float4 y = *reinterpret_cast<const float4*>(o);
+      v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+    }
+    *reinterpret_cast<float4*>(o) = v;
+  } else {
+    const float e[4] = {v.x, v.y, v.z, v.w};
+    for (int j = 0; j < 4; ++j)
+      if (col0 + j < p.N) o[j] = p.accumulate ? o[j] + e[j] : e[j];
+  }
+}
+
 // ------------------------------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -573,8 +619,13 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long l
   gemm_bf16_kernel<BN, STAGES><<<grid, NUM_THREADS, smem, stream>>>(tmA, tmB, p);
   NB_LAUNCH_CHECK();
   if (p.splits > 1) {
-    const long long threads = (long long)tiles * BM * (BN / 16);
-    splitk_reduce_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>(p, BN);
+    if (p.out_f32 && !p.bias && !p.act && !p.dact) {
+      const long long threads = (long long)tiles * BM * (BN / 4);
+      splitk_reduce_f32_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p, BN);
+    } else {
+      const long long threads = (long long)tiles * BM * (BN / 16);
+      splitk_reduce_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>(p, BN);
+    }
     NB_LAUNCH_CHECK();
   }
   return NB_OK;

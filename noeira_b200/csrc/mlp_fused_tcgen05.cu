@@ -5,8 +5,9 @@
 // optionally written to global memory (bf16) for the backward pass.
 //   warp 0      TMA: X tile and W1, then W2 in four 64-row k-blocks through a 2-stage ring
 //   warp 1      MMA issuer: layer 1 (K <= 64), layer 2 (K = 256, N = 256), layer 3 (K = 256, N = 16)
-//   warps 2..5  epilogue: thread = row; bias + activation, bf16 tile for the next layer in the 128-byte-swizzled
-//               K-major layout, final fp32 output; also stage W3ᵀ into shared memory at start
+//   warps 2..9  epilogue: two warps per TMEM lane quarter, each takes half of the 256 columns of its 32 rows; bias +
+//               activation, bf16 tile for the next layer in the 128-byte-swizzled K-major layout, final fp32 output;
+//               also stage W3ᵀ into shared memory at start
 // Weights are [IN, OUT] row-major bf16 (the framework's Linear layout): W1, W2 are MN-major B operands, W3 (narrow,
 // OUT <= 16) is transposed into a K-major tile by the epilogue threads.
 // Reference counterpart: none as one kernel (the reference issues cuBLAS GEMMs + bias / activation kernels per layer,
@@ -24,7 +25,8 @@ using namespace nb;
 constexpr int HID = 256;
 constexpr int ROWS = 128;
 constexpr int N3P = 16;
-constexpr int MLP_THREADS = 192;
+constexpr int MLP_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two warps per TMEM lane quarter)
+constexpr int EPI_THREADS = 256;
 
 struct MlpParams {
   int M, k0, n3;            // rows, input width (<= 64), real output width (<= 16)
@@ -94,10 +96,10 @@ mlp3_fwd_kernel(const __grid_constant__ MlpGroup grp) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&w2_full[i], 1);
       mbar_init(&w2_empty[i], 1);
-      mbar_init(&h_ready[i], 4);
+      mbar_init(&h_ready[i], 8);
     }
     for (int i = 0; i < 3; ++i) mbar_init(&acc_full[i], 1);
-    mbar_init(w3_ready, 4);
+    mbar_init(w3_ready, 8);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmX);
@@ -168,12 +170,13 @@ mlp3_fwd_kernel(const __grid_constant__ MlpGroup grp) {
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;             // which 128 columns of the 256 this warp handles
     const int r = quarter * 32 + lane;            // row of the tile = TMEM lane
     const int row = row0 + r;
-    const int t = (warp - 2) * 32 + lane;         // 0..127 for cooperative loads
+    const int t = (warp - 2) * 32 + lane;         // 0..255 for cooperative loads
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     // ---- stage W3ᵀ: element (n, k) of the K-major [16 x 256] tile
-    for (int e = t; e < N3P * HID; e += 128) {
+    for (int e = t; e < N3P * HID; e += EPI_THREADS) {
       const int k = e / N3P, n = e - k * N3P;
       const __nv_bfloat16 v = (n < p.n3) ? p.w3[(size_t)k * p.ld_w3 + n] : __float2bfloat16(0.f);
       const int kb = k >> 6, kk = k & 63;
@@ -190,41 +193,54 @@ mlp3_fwd_kernel(const __grid_constant__ MlpGroup grp) {
       tc_fence_after();
       const float* bias = layer == 0 ? p.b1 : p.b2;
       __nv_bfloat16* hsave = layer == 0 ? p.h1 : p.h2;
-      const uint32_t acc = lane_addr + (uint32_t)(layer * 256);
-#pragma unroll 1
-      for (int c0 = 0; c0 < HID; c0 += 16) {
-        uint32_t rr[16];
-        tmem_ld_32x32b_x16(acc + (uint32_t)c0, rr);
-        tmem_ld_wait();
-        uint32_t pk[8];
+      const uint32_t acc = lane_addr + (uint32_t)(layer * 256 + half * 128);
+      // 32 columns per step, two register sets in ping-pong: the next step's TMEM load is in flight while this one is
+      // converted and stored.  Written out as four steps (no loop-carried register copy may sit before a wait).
+      auto process = [&](const uint32_t (&cur)[32], int s4) {
+        const int c0 = half * 128 + s4 * 32;
+        uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
+        for (int j = 0; j < 32; j += 4) {
           const float4 bv = bias ? __ldg(reinterpret_cast<const float4*>(bias + c0 + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          __nv_bfloat162 a = __floats2bfloat162_rn(act1(p.act, __uint_as_float(rr[j]) + bv.x),
-                                                   act1(p.act, __uint_as_float(rr[j + 1]) + bv.y));
-          __nv_bfloat162 b = __floats2bfloat162_rn(act1(p.act, __uint_as_float(rr[j + 2]) + bv.z),
-                                                   act1(p.act, __uint_as_float(rr[j + 3]) + bv.w));
+          __nv_bfloat162 a = __floats2bfloat162_rn(act1(p.act, __uint_as_float(cur[j]) + bv.x),
+                                                   act1(p.act, __uint_as_float(cur[j + 1]) + bv.y));
+          __nv_bfloat162 b = __floats2bfloat162_rn(act1(p.act, __uint_as_float(cur[j + 2]) + bv.z),
+                                                   act1(p.act, __uint_as_float(cur[j + 3]) + bv.w));
           pk[j / 2] = *reinterpret_cast<uint32_t*>(&a);
           pk[j / 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
         }
         // k-block of the next layer's A tile = c0 / 64; 16-byte chunk index inside the 128-byte row is XOR-swizzled
         const int kb = c0 >> 6, ch = (c0 & 63) >> 3;
         uint8_t* base = hrow + kb * 16384;
-        *reinterpret_cast<uint4*>(base + (((ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        *reinterpret_cast<uint4*>(base + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(base + (((ch + q) ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         if (hsave && row < p.M) {
           uint4* g = reinterpret_cast<uint4*>(hsave + (size_t)row * p.ld_h + c0);
-          g[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          g[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) g[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
-      }
+      };
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32b_x32_nowait(acc, ra);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x32_nowait(acc + 32u, rb);
+      process(ra, 0);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x32_nowait(acc + 64u, ra);
+      process(rb, 1);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x32_nowait(acc + 96u, rb);
+      process(ra, 2);
+      tmem_ld_wait();
+      process(rb, 3);
       tc_fence_before();
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&h_ready[layer]);
     }
     if (ok && !__all_sync(0xffffffffu, !*abort_flag && mbar_wait(&acc_full[2], 0u, p.status, 322))) ok = false;
-    if (ok) {
+    if (ok && half == 0) {
       tc_fence_after();
       uint32_t rr[16];
       tmem_ld_32x32b_x16(lane_addr, rr);
@@ -281,7 +297,8 @@ int tmap2d(CUtensorMap* tm, const void* base, long long inner, long long outer, 
 // writes the three partial rows; a small second kernel adds the partials in CTA order (deterministic).
 //   warp 0      TMA: W2 as a K-major B operand (box 64 k x 256 n per k-block), 2-stage ring
 //   warp 1      MMA issuer
-//   warps 2..5  stage dY and W3 (zero padded to K = 64) into swizzled tiles; epilogues (thread = row); column sums
+//   warps 2..9  stage dY and W3 (zero padded to K = 64) into swizzled tiles; epilogues (two warps per TMEM lane
+//               quarter, half of the columns each); column sums
 struct MlpBwdParams {
   int M, n3;
   int ld_dy, ld_w3, ld_h, ld_g;
@@ -296,19 +313,15 @@ struct MlpBwdGroup {
   MlpBwdParams prm[2];
 };
 
-// Sum of columns 2t, 2t+1 over the 128 rows of a [128 x 256] bf16 tile in the swizzled K-major layout (four k-blocks
-// of 16 KB; row r of a k-block at (r>>3)·1024 + (r&7)·128, 16-byte chunk c at position c ^ (r&7)).
-__device__ __forceinline__ float2 tile_colsum2(const uint8_t* tile, int t) {
-  const int col = 2 * t;
+// Sum of column `col` over the 128 rows of a [128 x 256] bf16 tile in the swizzled K-major layout (four k-blocks of
+// 16 KB; row r of a k-block at (r>>3)·1024 + (r&7)·128, 16-byte chunk c at position c ^ (r&7)).
+__device__ __forceinline__ float tile_colsum(const uint8_t* tile, int col) {
   const uint8_t* kb = tile + (col >> 6) * 16384;
   const int ch = (col & 63) >> 3, within = (col & 7) * 2;
-  float2 acc = make_float2(0.f, 0.f);
+  float acc = 0.f;
 #pragma unroll 8
-  for (int r = 0; r < ROWS; ++r) {
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(kb + (r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4) + within);
-    acc.x += __low2float(v);
-    acc.y += __high2float(v);
-  }
+  for (int r = 0; r < ROWS; ++r)
+    acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(kb + (r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4) + within));
   return acc;
 }
 
@@ -346,8 +359,8 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
       mbar_init(&w2_empty[i], 1);
       mbar_init(&acc_full[i], 1);
     }
-    mbar_init(staged, 4);
-    mbar_init(g_ready, 4);
+    mbar_init(staged, 8);
+    mbar_init(g_ready, 8);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmW2);
@@ -397,27 +410,30 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;             // which 128 columns of the 256 this warp handles
     const int r = quarter * 32 + lane;            // row of the tile = TMEM lane
     const int row = row0 + r;
-    const int t = (warp - 2) * 32 + lane;         // 0..127
+    const int t = (warp - 2) * 32 + lane;         // 0..255
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    // ---- stage dY (row r of the tile; threads are TMEM-lane ordered, any order works here) and two rows of W3
-    {
+    // ---- stage dY (threads 0..127: one row each) and W3 (one row of the 256 each)
+    if (t < ROWS) {
+      const int rr = t, grow_ = row0 + rr;
       uint4 c[2] = {zero4, zero4};
-      if (row < p.M) {
-        const __nv_bfloat16* src = p.dy + (size_t)row * p.ld_dy;
+      if (grow_ < p.M) {
+        const __nv_bfloat16* src = p.dy + (size_t)grow_ * p.ld_dy;
         __nv_bfloat16 v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = j < p.n3 ? src[j] : __float2bfloat16(0.f);
         c[0] = *reinterpret_cast<uint4*>(&v[0]);
         c[1] = *reinterpret_cast<uint4*>(&v[8]);
       }
-      uint8_t* dst = sDY + (r >> 3) * 1024 + (r & 7) * 128;
+      uint8_t* dst = sDY + (rr >> 3) * 1024 + (rr & 7) * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ((ch ^ (r & 7)) << 4)) = ch < 2 ? c[ch] : zero4;
+      for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(dst + ((ch ^ (rr & 7)) << 4)) = ch < 2 ? c[ch] : zero4;
     }
-    for (int n = t; n < HID; n += 128) {
+    {
+      const int n = t;
       const __nv_bfloat16* src = p.w3 + (size_t)n * p.ld_w3;
       __nv_bfloat16 v[16];
 #pragma unroll
@@ -432,12 +448,8 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
     if (lane == 0) mbar_arrive(staged);
     float* part = p.bias_part ? p.bias_part + (size_t)blockIdx.x * 3 * HID : nullptr;
     if (part) {
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // every row of the dY tile is in shared memory
-      if (t < 8) {                                      // 16 columns: the tile's k-block 0, chunks 0 and 1
-        const float2 sum = tile_colsum2(sDY, t);
-        part[2 * HID + 2 * t] = sum.x;
-        part[2 * HID + 2 * t + 1] = sum.y;
-      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // every row of the dY tile is in shared memory
+      if (t < N3P) part[2 * HID + t] = tile_colsum(sDY, t);
     }
     bool ok = true;
     uint8_t* grow = sG + (r >> 3) * 1024 + (r & 7) * 128;
@@ -446,24 +458,16 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
       tc_fence_after();
       const __nv_bfloat16* hsrc = (layer == 0 ? p.h2 : p.h1) + (size_t)row * p.ld_h;
       __nv_bfloat16* gdst = (layer == 0 ? p.g2 : p.g1) + (size_t)row * p.ld_g;
-      const uint32_t acc = lane_addr + (uint32_t)(layer * 256);
-#pragma unroll 1
-      for (int c0 = 0; c0 < HID; c0 += 16) {
-        uint32_t rr[16];
-        tmem_ld_32x32b_x16(acc + (uint32_t)c0, rr);
-        uint4 hv[2] = {zero4, zero4};
-        if (row < p.M) {
-          hv[0] = __ldg(reinterpret_cast<const uint4*>(hsrc + c0));
-          hv[1] = __ldg(reinterpret_cast<const uint4*>(hsrc + c0 + 8));
-        }
-        tmem_ld_wait();
+      const uint32_t acc = lane_addr + (uint32_t)(layer * 256 + half * 128);
+      auto process = [&](const uint32_t (&cur)[32], const uint4 (&hv)[4], int s4) {
+        const int c0 = half * 128 + s4 * 32;
         const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(hv);
-        uint32_t pk[8];
+        uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 16; ++j) {
           const float h0 = __low2float(hp[j]), h1 = __high2float(hp[j]);
-          __nv_bfloat162 g = __floats2bfloat162_rn(__uint_as_float(rr[2 * j]) * dact1(p.act, h0),
-                                                   __uint_as_float(rr[2 * j + 1]) * dact1(p.act, h1));
+          __nv_bfloat162 g = __floats2bfloat162_rn(__uint_as_float(cur[2 * j]) * dact1(p.act, h0),
+                                                   __uint_as_float(cur[2 * j + 1]) * dact1(p.act, h1));
           pk[j] = *reinterpret_cast<uint32_t*>(&g);
         }
         if (layer == 0 || part) {
@@ -471,15 +475,40 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
           // so the same tile holds G1 for the column sums.
           const int kb = c0 >> 6, ch = (c0 & 63) >> 3;
           uint8_t* base = grow + kb * 16384;
-          *reinterpret_cast<uint4*>(base + (((ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          *reinterpret_cast<uint4*>(base + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(base + (((ch + q) ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
         if (row < p.M) {
           uint4* g = reinterpret_cast<uint4*>(gdst + c0);
-          g[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          g[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) g[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
-      }
+      };
+      auto load_h = [&](uint4 (&hv)[4], int s4) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          hv[q] = row < p.M ? __ldg(reinterpret_cast<const uint4*>(hsrc + half * 128 + s4 * 32 + 8 * q)) : zero4;
+      };
+      // two register sets in ping-pong, written out as four steps (no loop-carried register copy before a wait)
+      uint32_t ra[32], rb[32];
+      uint4 ha[4], hb[4];
+      tmem_ld_32x32b_x32_nowait(acc, ra);
+      load_h(ha, 0);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x32_nowait(acc + 32u, rb);
+      load_h(hb, 1);
+      process(ra, ha, 0);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x32_nowait(acc + 64u, ra);
+      load_h(ha, 2);
+      process(rb, hb, 1);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x32_nowait(acc + 96u, rb);
+      load_h(hb, 3);
+      process(ra, ha, 2);
+      tmem_ld_wait();
+      process(rb, hb, 3);
       if (layer == 0) {
         tc_fence_before();
         fence_proxy_async();
@@ -487,12 +516,9 @@ mlp3_bwd_kernel(const __grid_constant__ MlpBwdGroup grp) {
         if (lane == 0) mbar_arrive(g_ready);
       }
       if (part) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // the whole tile is written
-        const float2 sum = tile_colsum2(sG, t);
-        float* dst = part + (layer == 0 ? HID : 0);       // [0] g1, [1] g2, [2] dy
-        dst[2 * t] = sum.x;
-        dst[2 * t + 1] = sum.y;
-        if (layer == 0) asm volatile("bar.sync 1, 128;" ::: "memory");   // sums read before layer 1 overwrites the tile
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // the whole tile is written
+        part[(layer == 0 ? HID : 0) + t] = tile_colsum(sG, t);       // [0] g1, [1] g2, [2] dy
+        if (layer == 0) asm volatile("bar.sync 1, 256;" ::: "memory");   // sums read before layer 1 overwrites the tile
       }
     }
     if (!ok) *abort_flag = 1;
@@ -515,16 +541,21 @@ struct BiasFinishNet {
 struct BiasFinishGroup {
   BiasFinishNet net[2];
 };
-__global__ void __launch_bounds__(HID)
+__global__ void __launch_bounds__(4 * HID)
 mlp3_bias_finish_kernel(const BiasFinishGroup g) {
+  // 4 x 256 threads: thread (q, col) sums CTAs q, q+4, ...; the four partial sums are added in the order q = 0..3
+  __shared__ float sh[4][HID];
   const BiasFinishNet& n = g.net[blockIdx.y];
-  const int layer = blockIdx.x, col = threadIdx.x;
+  const int layer = blockIdx.x, col = threadIdx.x & (HID - 1), q = threadIdx.x >> 8;
   if (n.part == nullptr) return;
   float* dst = layer == 0 ? n.db1 : (layer == 1 ? n.db2 : n.db3);
-  if (dst == nullptr || (layer == 2 && col >= n.n3)) return;
+  if (dst == nullptr) return;
   float acc = 0.f;
-  for (int c = 0; c < n.ctas; ++c) acc += n.part[((size_t)c * 3 + layer) * HID + col];
-  dst[col] += acc;
+  if (layer != 2 || col < n.n3)
+    for (int c = q; c < n.ctas; c += 4) acc += n.part[((size_t)c * 3 + layer) * HID + col];
+  sh[q][col] = acc;
+  __syncthreads();
+  if (q == 0 && (layer != 2 || col < n.n3)) dst[col] += ((sh[0][col] + sh[1][col]) + sh[2][col]) + sh[3][col];
 }
 
 }  // namespace
@@ -638,7 +669,7 @@ int nb_mlp3_bwd_group(const NbMlpNet* net, int nets, unsigned int* status, void*
     f.net[i].ctas = ceil_div(n.M, ROWS); f.net[i].n3 = n.n3;
   }
   if (any) {
-    mlp3_bias_finish_kernel<<<dim3(3, nets), HID, 0, (cudaStream_t)stream>>>(f);
+    mlp3_bias_finish_kernel<<<dim3(3, nets), 4 * HID, 0, (cudaStream_t)stream>>>(f);
     NB_LAUNCH_CHECK();
   }
   return NB_OK;

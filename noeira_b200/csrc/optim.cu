@@ -57,7 +57,7 @@ arena_adamw_kernel(float* __restrict__ val, const float* __restrict__ grd, float
 // Several arenas (optimizers) in ONE launch, the step counters t, β₁ᵗ, β₂ᵗ advanced in the same kernel: every block
 // derives the advanced powers from the values it reads at entry, the last block (ticket) writes them back.  Four
 // launches (advance + update per optimizer) of an actor-critic update become one.
-constexpr int MULTI_MAX = 4, MULTI_CHUNK4 = 256 * 8;
+constexpr int MULTI_MAX = 4, MULTI_U = 2, MULTI_CHUNK4 = 256 * MULTI_U;   // small chunks: arenas of a few 100 KB still fill the GPU
 struct MultiSeg {
   float *val, *grd, *m, *v;
   __nv_bfloat16* shadow;
@@ -80,8 +80,8 @@ arena_adamw_multi_kernel(const __grid_constant__ MultiArgs a) {
   h.b1t *= h.beta1;
   h.b2t *= h.beta2;
   const long long base = (long long)((int)blockIdx.x - sg.first_block) * MULTI_CHUNK4;
-#pragma unroll 2
-  for (int u = 0; u < 8; ++u) {
+#pragma unroll
+  for (int u = 0; u < MULTI_U; ++u) {
     const long long i = base + u * 256 + threadIdx.x;
     if (i >= sg.n4) break;
     const unsigned char fl = sg.row_flags ? sg.row_flags[i >> 3] : (unsigned char)1;
