@@ -76,8 +76,36 @@ class ParamArena:
         if self.shadow is not None:
             self.refresh_shadow()
 
+    def repad(self, total: int):
+        """Re-allocate ``val`` / ``grd`` (and the shadow) with ``total >= numel`` elements and re-point every parameter's
+        views: sharding strategies need the arena to be a whole number of equal shards so that reduce-scatter and
+        all-gather run in place.  The tail is zero and belongs to no parameter."""
+        if total < self.numel:
+            raise ValueError("an arena cannot shrink")
+        if total == self.val.numel():
+            return
+        with torch.no_grad():
+            for attr in ("val", "grd", "shadow"):
+                old = getattr(self, attr)
+                if old is None:
+                    continue
+                new = torch.zeros(total, dtype=old.dtype, device=old.device)
+                new[: old.numel()].copy_(old)
+                setattr(self, attr, new)
+            for _, p, o, n in self.entries:
+                p._val = self.val[o:o + n].view(p.storage_shape)
+                p._grd = self.grd[o:o + n].view(p.storage_shape)
+                if self.shadow is not None:
+                    p._shadow = self.shadow[o:o + n].view(p.storage_shape)
+
+    def release_moments(self):
+        """Drop the full-size Adam moments (a sharding strategy keeps its own shard-size copies)."""
+        self.m = self.v = None
+        for _, p, _, _ in self.entries:
+            p.m = p.v = None
+
     def refresh_shadow(self):
-        self.shadow.copy_(self.val)
+        self.shadow.copy_(self.val[: self.shadow.numel()])
         for _, p, _, _ in self.entries:
             p.mark_shadow_fresh()
 

@@ -23,25 +23,24 @@ def _train(comm, strategy, steps=4, clip=0.0, world_batch=16):
     from noeira_b200.parallel.strategy import STRATEGIES
     net = _net()
     opt = nn.AdamW(net.named_params(), lr=1e-2, weight_decay=0.01)
-    st = STRATEGIES[strategy](opt, comm)
+    st = STRATEGIES[strategy](opt, comm, model=net)
     st.sync_params()
     g = torch.Generator().manual_seed(0)
     per = world_batch // comm.world
+    peak = 0
     for _ in range(steps):
         x = torch.randn(world_batch, 12, generator=g)
         y = torch.randn(world_batch, 3, generator=g)
         xs, ys = x[comm.rank * per:(comm.rank + 1) * per], y[comm.rank * per:(comm.rank + 1) * per]
-        if strategy == "zero3" and not st.gathered:
-            st.gather_params()
+        st.begin_step()
         out = net.forward(xs)
         net.vjp(2.0 * (out - ys) / per)
         st.reduce_grads()
         if clip > 0:
             st.clip_grads(clip)
         st.step()
-    if strategy == "zero3":
-        st.gather_params()
-    return opt.arena.val.clone(), st.state_bytes_per_rank()
+        peak = max(peak, st.state_bytes_per_rank())
+    return st.full_values(), st.state_bytes_per_rank()
 
 
 def test_n1_identity_and_replica_agreement_and_strategy_equivalence():
@@ -56,7 +55,10 @@ def test_n1_identity_and_replica_agreement_and_strategy_equivalence():
         res[strat] = out[0]
     for strat in ("zero1", "zero2", "zero3"):
         assert torch.equal(res["ddp"][0], res[strat][0]), strat        # DDP == ZeRO without clip
+    # bytes actually allocated between steps: DDP 4Ψ, ZeRO-1 2Ψ + 3Ψ/N, ZeRO-2 Ψ + 3Ψ/N, ZeRO-3 4Ψ/N (N = 2)
+    psi = res["ddp"][1] / 4
     assert res["ddp"][1] > res["zero1"][1] > res["zero2"][1] > res["zero3"][1]
+    assert res["zero1"][1] <= 3.6 * psi and res["zero2"][1] <= 2.6 * psi and res["zero3"][1] <= 2.1 * psi
     # two ranks with half batches ≈ one rank with the full batch (mean of shard means)
     assert torch.allclose(res["ddp"][0], base, atol=1e-5)
 
@@ -142,3 +144,36 @@ def test_gloo_processes_match_simulator():
         v0, v1 = torch.load(os.path.join(d, "v0")), torch.load(os.path.join(d, "v1"))
     assert torch.equal(v0, v1)
     assert torch.equal(v0, sim)
+
+
+def test_zero3_units_are_gathered_only_around_their_own_forward_and_backward():
+    from noeira_b200 import nn
+    from noeira_b200.parallel.fibers import run_ranks
+    from noeira_b200.parallel.strategy import Zero3
+
+    def body(c):
+        net = _net()
+        opt = nn.AdamW(net.named_params(), lr=1e-2)
+        seen, box = [], []
+        for i, child in enumerate(net.mods):         # recorders go in first, so the strategy's hooks wrap them
+            f = child.forward
+            child.forward = (lambda f, i: lambda *a, **k: (seen.append((i, [u["live_v"] for u in box[0].units])), f(*a, **k))[1])(f, i)
+        st = Zero3(opt, c, model=net)
+        box.append(st)
+        assert st.hooked and len(st.units) == 3
+        st.sync_params()
+        x = torch.randn(4, 12)
+        st.begin_step()
+        out = net.forward(x)
+        live_during = [s[1] for s in seen]
+        net.vjp(out)
+        st.reduce_grads()
+        st.step()
+        idle = [(u["live_v"], u["live_g"]) for u in st.units]
+        return live_during, idle, st.state_bytes_per_rank(), opt.arena.numel
+
+    for live_during, idle, nbytes, numel in run_ranks(2, body):
+        # when unit i's own forward runs, exactly unit i is materialised
+        assert live_during == [[True, False, False], [False, True, False], [False, False, True]]
+        assert idle == [(False, False)] * 3
+        assert nbytes <= 4 * 4 * numel / 2 * 1.1          # values, gradients and both moments: a shard of each
