@@ -309,6 +309,75 @@ ar_twoshot_kernel(ARParams p, AdamBufs a, unsigned int* status) {
                 (1u << SIG_ARRIVE) | (1u << SIG_DONE) | (1u << SIG_PHASE) | (clip ? (1u << SIG_GRID) : 0u));
 }
 
+// ------------------------------------------------------------------------------------------ ZeRO step
+// Reduce-scatter fused with the shard's Adam(W) and all-gather fused with the bf16 recast, one kernel:
+// rank r sums slice r of every peer's gradients (peer loads, rank order), updates ITS shard of the fp32 values with
+// moments that exist only at shard size (m_shard / v_shard: Ψ/N floats each), and pushes the new values and their bf16
+// shadow into every peer's arenas (peer stores).  Two flag rounds: all gradients are ready / every push has landed.
+// Reference path: reduce_scatter → shard Adam → all_gather_rows as separate collectives
+// (noeira/nn/distributed/zero.mojo:284-402).
+struct ZeroBufs {
+  float* val[MAX_RANKS];             // every rank's fp32 value arena
+  __nv_bfloat16* shadow[MAX_RANKS];  // every rank's bf16 shadow arena (may be null)
+  float *m_shard, *v_shard;          // this rank's moments: slice_len floats
+  const unsigned char* row_flags;
+  const float* hyper;
+  int zero_grad;
+};
+
+__global__ void __launch_bounds__(512)
+ar_zero_kernel(ARParams p, ZeroBufs z, unsigned int* status) {
+  __shared__ bool sh_ok;
+  unsigned int* my = p.sig[p.rank];
+  unsigned int bases[4];
+  for (int k = 0; k < 4; ++k) bases[k] = ld_acquire_sys(my + SIG_BASE + k);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool ok = cross_barrier(p, SIG_ARRIVE, bases[SIG_ARRIVE], status, 40, &sh_ok);
+  const AdamHyper h = load_hyper(z.hyper);
+  const long long per = ((p.n4 + p.world - 1) / p.world + 7) / 8 * 8;
+  const long long lo = min(p.n4, per * p.rank), hi = min(p.n4, per * (p.rank + 1));
+  if (ok) {
+    for (long long i = lo + i0; i < hi; i += stride) {
+      float4 x[MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < p.world) x[r] = ld_peer4(p.grd[r] + 4 * i);
+      float4 g = x[0];
+#pragma unroll
+      for (int r = 1; r < MAX_RANKS; ++r)
+        if (r < p.world) { g.x += x[r].x; g.y += x[r].y; g.z += x[r].z; g.w += x[r].w; }
+      const unsigned char fl = z.row_flags ? z.row_flags[i >> 3] : (unsigned char)1;
+      float4 pv = reinterpret_cast<const float4*>(z.val[p.rank])[i];
+      if (!(fl & 2)) {
+        const long long j = i - lo;
+        float4 mm = reinterpret_cast<float4*>(z.m_shard)[j];
+        float4 vv = reinterpret_cast<float4*>(z.v_shard)[j];
+        adamw_update4(pv, g, mm, vv, h, (fl & 1) != 0);
+        reinterpret_cast<float4*>(z.m_shard)[j] = mm;
+        reinterpret_cast<float4*>(z.v_shard)[j] = vv;
+      }
+      __nv_bfloat162 b0 = __floats2bfloat162_rn(pv.x, pv.y), b1 = __floats2bfloat162_rn(pv.z, pv.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&b0);
+      pk.y = *reinterpret_cast<uint32_t*>(&b1);
+      for (int d = 0; d < p.world; ++d) {
+        const int r = (p.rank + d) % p.world;
+        st_peer4(z.val[r] + 4 * i, pv);
+        if (z.shadow[r])
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(reinterpret_cast<uint2*>(z.shadow[r]) + i), "r"(pk.x), "r"(pk.y) : "memory");
+      }
+    }
+  }
+  // every shard has landed in my values, and nobody reads my gradients any more
+  ok = cross_barrier(p, SIG_PHASE, bases[SIG_PHASE], status, 41, &sh_ok) && ok;
+  if (ok && z.zero_grad) {
+    const float4 zz = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long i = i0; i < p.n4; i += stride) reinterpret_cast<float4*>(p.grd[p.rank])[i] = zz;
+  }
+  publish_bases(my, bases, p.world, (1u << SIG_ARRIVE) | (1u << SIG_PHASE));
+}
+
 // ------------------------------------------------------------------------------------------ push (small buckets)
 // Latency-optimal form for buckets of up to a few MB: ONE NVLink traversal and no cross-GPU barrier.
 //   1. every block loads its 16 KB chunk of the local gradients and STORES it into a per-source inbox on every peer,
@@ -577,6 +646,32 @@ int nb_allreduce_push(int world, int rank, int nseg, void* const* inbox_ptrs, vo
   if (blocks > PUSH_MAX_BLOCKS) return NB_ERR_TOO_LARGE;
   p.plane4 = off4;
   ar_push_kernel<<<blocks, PUSH_THREADS, 0, (cudaStream_t)stream>>>(p, status);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+// ZeRO-1 step in one kernel (see ar_zero_kernel).  n: arena length in floats (multiple of 4); the slice of rank r is
+// float4 range [per·r, per·(r+1)) with per = nb_zero_slice4(n, world); m_shard / v_shard hold 4·per floats.
+long long nb_zero_slice4(long long n, int world) { return ((n / 4 + world - 1) / world + 7) / 8 * 8; }
+int nb_zero_step_fused(int world, int rank, void* const* grd_ptrs, void* const* val_ptrs, void* const* shadow_ptrs,
+                       void* const* sig_ptrs, long long n, float* m_shard, float* v_shard, const unsigned char* row_flags,
+                       const float* hyper, int zero_grad, unsigned int spin_limit, unsigned int* status, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || !hyper || !m_shard || !v_shard) return NB_ERR_BAD_ARG;
+  if (n % 4) return NB_ERR_UNALIGNED;
+  ARParams p;
+  ZeroBufs z;
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    p.grd[r] = r < world ? (float*)grd_ptrs[r] : nullptr;
+    p.red[r] = nullptr;
+    p.sig[r] = r < world ? (unsigned int*)sig_ptrs[r] : nullptr;
+    z.val[r] = r < world ? (float*)val_ptrs[r] : nullptr;
+    z.shadow[r] = (r < world && shadow_ptrs) ? (__nv_bfloat16*)shadow_ptrs[r] : nullptr;
+  }
+  p.grd_mc = p.red_mc = nullptr;
+  p.world = world; p.rank = rank; p.n4 = n / 4;
+  p.spin_limit = spin_limit ? spin_limit : (1u << 24);
+  z.m_shard = m_shard; z.v_shard = v_shard; z.row_flags = row_flags; z.hyper = hyper; z.zero_grad = zero_grad;
+  ar_zero_kernel<<<grid_for(p.n4 / world > 0 ? p.n4 / world : 1, 512), 512, 0, (cudaStream_t)stream>>>(p, z, status);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

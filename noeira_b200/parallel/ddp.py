@@ -189,7 +189,72 @@ class FusedGradSync:
         return st["red"].local
 
 
+class FusedZeroSync:
+    """ZeRO-1 on GPUs as ONE kernel per step: reduce-scatter fused with the shard's AdamW, all-gather fused with the
+    bf16 recast (``csrc/allreduce_fused.cu::ar_zero_kernel``).  Adam's moments exist only at shard size; gradients,
+    values and the bf16 shadow live in symmetric memory so that peers read / write them directly.
+    Reference: ``Zero1.reduce_scatter_grads`` + shard Adam + ``all_gather_rows`` noeira/nn/distributed/zero.mojo:284-402."""
+
+    def __init__(self, world: int, rank: int, local_rank: int, group=None, spin_limit: int = 1 << 24):
+        self.world, self.rank, self.local_rank, self.group, self.spin_limit = world, rank, local_rank, group, spin_limit
+        self.lib = cuda_lib()
+        self.lib.nb_zero_slice4.restype = ctypes.c_longlong
+        self.state: Dict[int, dict] = {}
+
+    def attach(self, *opts):
+        for o in opts:
+            a = o.arena
+            if a.m is None:
+                raise ValueError("the optimizer has no moments to shard")
+            n = a.numel
+            heap = SymmetricHeap(n * (4 + 4 + 2) + 4 * SIGNAL_PAD_WORDS + 4096, self.group)
+            g, v = heap.tensor(n, torch.float32), heap.tensor(n, torch.float32)
+            sh = heap.tensor(n, torch.bfloat16)
+            sig = heap.tensor(SIGNAL_PAD_WORDS, torch.int32)
+            g.local.copy_(a.grd)
+            v.local.copy_(a.val)
+            sh.local.copy_(a.val)
+            a.grd, a.val, a.shadow = g.local, v.local, sh.local
+            for _, p, off, k in a.entries:
+                p._grd = a.grd[off:off + k].view(p.storage_shape)
+                p._val = a.val[off:off + k].view(p.storage_shape)
+                p._shadow = a.shadow[off:off + k].view(p.storage_shape)
+                p.mark_shadow_fresh()
+            per = 4 * int(self.lib.nb_zero_slice4(ctypes.c_longlong(n), ctypes.c_int(self.world)))
+            lo = min(n, per * self.rank)
+            hi = min(n, lo + per)
+            m = torch.zeros(per, device=a.val.device)
+            vv = torch.zeros(per, device=a.val.device)
+            m[: hi - lo].copy_(a.m[lo:hi])
+            vv[: hi - lo].copy_(a.v[lo:hi])
+            a.release_moments()
+            o.grad_scale = 1.0 / self.world
+            o.hyper[H_GSCALE] = 1.0 / self.world
+            self.state[id(o)] = dict(heap=heap, m=m, v=vv, per=per, grd_tab=g.ptr_table(), val_tab=v.ptr_table(),
+                                     shadow_tab=sh.ptr_table(), sig_tab=sig.ptr_table())
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+
+    def reduce_and_step(self, opt):
+        if opt.max_grad_norm > 0:
+            raise NotImplementedError("gradient clipping is not part of the fused ZeRO step; use parallel.strategy.Zero1")
+        st, a = self.state[id(opt)], opt.arena
+        check(self.lib.nb_adam_advance(ptr(opt.hyper), stream_ptr()), "adam_advance")
+        check(self.lib.nb_zero_step_fused(
+            ctypes.c_int(self.world), ctypes.c_int(self.rank), st["grd_tab"], st["val_tab"], st["shadow_tab"], st["sig_tab"],
+            ctypes.c_longlong(a.numel), ptr(st["m"]), ptr(st["v"]), ptr(a.row_flags), ptr(opt.hyper), ctypes.c_int(1),
+            ctypes.c_uint(self.spin_limit), ptr(device_status(a.grd.device)), stream_ptr()), "zero_step_fused")
+        a.bump_versions(shadow_fresh=True)
+
+    def state_bytes_per_rank(self, opt) -> int:
+        st, a = self.state[id(opt)], opt.arena
+        return a.numel * (4 + 4 + 2) + 2 * st["per"] * 4
+
+
 def make_grad_sync(kind: str, world: int, rank: int, local_rank: int):
     if kind == "nccl":
         return NcclGradSync(world, rank)
+    if kind == "zero":
+        return FusedZeroSync(world, rank, local_rank)
     return FusedGradSync(world, rank, local_rank)

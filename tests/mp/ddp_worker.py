@@ -52,6 +52,7 @@ def main():
             print(f"algo={algo} hidden={hidden} clip={clip}: replicas_equal={same} max|fused-nccl|={err:.3e} grd_zeroed={gz == 0.0}")
         ok = ok and same and err < (2e-4 if clip > 0 else 2e-5) and gz == 0.0
     ok = push_case(rank, world, local) and ok
+    ok = zero_case(rank, world, local) and ok
     dist.barrier()
     if rank == 0:
         print("DDP_WORKER_OK" if ok else "DDP_WORKER_FAIL")
@@ -115,6 +116,48 @@ def push_case(rank, world, local):
     if rank == 0:
         print(f"push plain all-reduce: ok={okp}")
     return ok and okp
+
+
+def zero_case(rank, world, local):
+    """Fused ZeRO-1 step (reduce-scatter + shard AdamW + all-gather with bf16 recast in one kernel) against NCCL
+    all-reduce + the full local AdamW: same values, identical replicas, moments only at shard size."""
+    from noeira_b200 import nn
+    from noeira_b200.ops import check_status
+    from noeira_b200.parallel.ddp import FusedZeroSync
+    nn.manual_seed(21)
+    mk = lambda: nn.Sequential(nn.LinearTanh(32, 384), nn.LinearTanh(384, 384), nn.Linear(384, 8)).to("cuda")
+    net, ref = mk(), mk()
+    ref.copy_from(net)
+    opt = nn.AdamW(net.named_params(), lr=1e-2, weight_decay=0.01)
+    ropt = nn.AdamW(ref.named_params(), lr=1e-2, weight_decay=0.01)
+    full_moment_bytes = opt.arena.m.numel() * 4
+    sync = FusedZeroSync(world, rank, local)
+    sync.attach(opt)
+    g = torch.Generator(device="cuda").manual_seed(300 + rank)
+    for step in range(4):
+        x = torch.randn(256, 32, device="cuda", generator=g).bfloat16()
+        dy = (torch.randn(256, 8, device="cuda", generator=g) * 0.1).bfloat16()
+        for q in (net, ref):
+            q.forward(x)
+            q.vjp(dy)
+        sync.reduce_and_step(opt)
+        dist.all_reduce(ropt.arena.grd)
+        ropt.hyper[8] = 1.0 / world
+        ropt.step(zero_grad=True)
+    torch.cuda.synchronize()
+    check_status()
+    mine = opt.arena.val.clone()
+    lst = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(lst, mine)
+    same = all(torch.equal(lst[0], t) for t in lst)
+    err = (opt.arena.val - ropt.arena.val).abs().max().item()
+    sherr = (opt.arena.shadow.float() - opt.arena.val).abs().max().item()
+    shard_ok = sync.state[id(opt)]["m"].numel() * 4 <= full_moment_bytes / world + 4096
+    gz = opt.arena.grd.abs().max().item()
+    if rank == 0:
+        print(f"zero numel={opt.arena.numel}: replicas_equal={same} max|fused-nccl|={err:.3e} shadow_err={sherr:.2e} "
+              f"moments_sharded={shard_ok} grd_zeroed={gz == 0.0}")
+    return same and err < 2e-5 and sherr < 2e-2 and shard_ok and gz == 0.0
 
 
 if __name__ == "__main__":
