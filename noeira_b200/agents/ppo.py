@@ -372,21 +372,19 @@ class PPOAgent:
         self.logger = logger
 
     def train(self, total_env_steps: int, log_every: int = 1, checkpoint_path: str = None, checkpoint_every: int = 0):
+        """Runs the generic on-policy driver (``training.rl.run_onpolicy_train_batched``) over the device rollout;
+        ``log_every`` / ``checkpoint_every`` count iterations.  Returns the last metrics read."""
+        from ..training.rl import run_onpolicy_train_batched
         tr = self.trainer
-        steps = 0
+        per = tr.env_steps_per_iteration
         last = {}
-        while steps < total_env_steps:
-            read = (tr.iteration + 1) % log_every == 0
-            m = tr.train_iteration(read_metrics=read)
-            steps += tr.env_steps_per_iteration
-            if m is not None:
-                last = m
-                if self.logger is not None:
-                    self.logger.log_scalars(steps, m)
-            if checkpoint_path and checkpoint_every and tr.iteration % checkpoint_every == 0:
-                tr.save(checkpoint_path)
-        if checkpoint_path:
-            tr.save(checkpoint_path)
+
+        def keep(step, m):
+            last.clear()
+            last.update(m)
+        run_onpolicy_train_batched(tr, tr.env, total_env_steps, print_every=per * max(log_every, 1), logger=self.logger,
+                                   checkpoint_every=per * checkpoint_every, checkpoint_path=checkpoint_path or "",
+                                   on_iteration=keep, read_metrics_every=max(log_every, 1))
         return last
 
     def select_greedy_action(self, obs_bf16):

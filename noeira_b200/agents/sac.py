@@ -246,27 +246,21 @@ class SACAgent:
         self.replay = StoreReplay(capacity, env.obs_dim, env.act_dim, device=env.device, seed=cfg.seed)
         self.learning_starts, self.utd = learning_starts, utd
 
-    def train(self, total_env_steps, logger=None, log_every=1000):
-        env, tr = self.env, self.trainer
-        obs = env.reset_batch().clone()
-        steps = 0
-        act_buf = torch.zeros(env.n_envs, (env.act_dim + 7) // 8 * 8, device=env.device)
-        while steps < total_env_steps:
-            if steps < self.learning_starts:
-                a = torch.rand(env.n_envs, env.act_dim, device=env.device) * 2 - 1
-            else:
-                a = tr.select_action(obs).float()
-            act_buf[:, : env.act_dim] = a
-            env.step_batch(act_buf)
-            self.replay.store_batch(obs, a, env.reward, env.next_obs, env.terminated)
-            obs = env.obs.clone()
-            steps += env.n_envs
-            if steps >= self.learning_starts:
-                for _ in range(self.utd):
-                    tr.update_captured(*self.replay.sample(tr.cfg.batch))
-            if logger is not None and steps % log_every < env.n_envs and tr.metrics:
-                logger.log(steps, {k: float(v) for k, v in tr.metrics.items()})
-        return tr.metrics
+    def train(self, total_env_steps, logger=None, log_every=1000, checkpoint_path: str = "", checkpoint_every: int = 0):
+        """Runs the generic off-policy driver (``training.rl.run_offpolicy_train_batched``)."""
+        from ..training.rl import run_offpolicy_train_batched
+
+        class _Scalars:
+            def __init__(self, inner):
+                self.inner = inner
+
+            def log_scalars(self, step, row):
+                (self.inner.log_scalars if hasattr(self.inner, "log_scalars") else self.inner.log)(step, row)
+        self.log = run_offpolicy_train_batched(self.trainer, self.env, self.replay, total_env_steps,
+                                               learning_starts=self.learning_starts, utd=self.utd, batch_size=self.trainer.cfg.batch,
+                                               print_every=log_every, logger=_Scalars(logger) if logger is not None else None,
+                                               checkpoint_every=checkpoint_every, checkpoint_path=checkpoint_path)
+        return self.trainer.metrics
 
 
 # ------------------------------------------------------------------------------------------ TD3
