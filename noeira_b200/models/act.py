@@ -227,6 +227,32 @@ class ACTModel(Module):
         self._eps, self._std = eps, (0.5 * logvar).exp()
         z = mu + self._std * eps
         lat = self.lattok.forward(pad8(z))
+        return self._decode(lat, images_u8, B, dt), info.float()
+
+    def infer(self, qpos, images_u8):
+        """Deployment forward: the latent is the prior mean (z = 0; the reference runs the same graph with the CVAE
+        branch multiplied by zero, noeira/deep_agents/act/loss_graph.mojo:44-53).  Returns the normalised chunk
+        ``[B, K, A]`` fp32."""
+        cfg = self.cfg
+        dev = qpos.device
+        dt = torch.bfloat16 if self.on_cuda else torch.float32
+        self._build_pos(dev, dt)
+        B = qpos.shape[0]
+        q = qpos.float()
+        if self.on_cuda:
+            w = (q.shape[-1] + 7) // 8 * 8
+            o = torch.zeros(B, w, device=dev, dtype=torch.bfloat16)
+            o[:, : q.shape[-1]] = q
+            q = o[:, : q.shape[-1]]
+        self._qpos = q
+        zw = (cfg.latent + 7) // 8 * 8 if self.on_cuda else cfg.latent
+        z = torch.zeros(B, zw, device=dev, dtype=dt)[:, : cfg.latent]
+        lat = self.lattok.forward(z)
+        return self._decode(lat, images_u8, B, dt)
+
+    def _decode(self, lat, images_u8, B, dt):
+        cfg = self.cfg
+        K, D = cfg.chunk, cfg.dim
         # ---- vision
         imgs = nn.normalize_images(images_u8.reshape(B * cfg.n_cam, 3, cfg.height, cfg.width))
         f = self.backbone.forward(imgs)                                  # [B·NC, oh, ow, 512]
@@ -244,7 +270,7 @@ class ACTModel(Module):
         for lyr in self.hs:
             h = lyr.forward(h, qpe, kmem, mem)
         ahat = self.ahat.forward(self.hsn.forward(h))
-        return ahat.float(), info.float()
+        return ahat.float()
 
     def vjp(self, dahat, dinfo_kl):
         """dahat [B,K,A] and the KL gradient wrt latinfo [B, 2L]; accumulates every parameter gradient."""
