@@ -113,7 +113,7 @@ def build(force: bool = False, verbose: bool = False) -> None:
             gx = [shutil.which("g++") or "g++"] + GXX_FLAGS + ["-I", str(CSRC), "-I", str(CSRC / "host")]
             objs, changed = _build_one(cpp, hdr, LIBDIR / "obj" / "host", gx, ".cpp")
             if changed or not HOST_LIB.exists():
-                _run([gx[0], "-shared", "-o", str(HOST_LIB)] + [str(o) for o in objs] + ["-pthread", "-ldl", "-lz"],
+                _run([gx[0], "-shared", "-o", str(HOST_LIB)] + [str(o) for o in objs] + ["-pthread", "-ldl", "-lz", "-lssl", "-lcrypto"],
                      LIBDIR / "obj" / "link_host.log")
         if verbose:
             for log in sorted((LIBDIR / "obj" / "cuda").glob("*.log")):

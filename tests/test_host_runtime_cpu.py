@@ -99,10 +99,56 @@ def test_http_client_local_server():
         assert rt.http_request("GET", base + "/nope")[0] == 404
         assert rt.http_request("POST", base + "/p", {"X-Tag": "t1"}, b"12345") == (201, b"54321t1")
         with pytest.raises(OSError):
-            rt.http_request("GET", "https://127.0.0.1/")
+            rt.http_request("GET", "https://127.0.0.1:9/")          # nothing listens there
     finally:
         srv.shutdown()
     assert rt.gzip_inflate(gzip.compress(b"xyz" * 50)) == b"xyz" * 50
+
+
+def _self_signed(tmp_path, host="localhost"):
+    import datetime
+    import ipaddress
+    from cryptography import x509
+    from cryptography.hazmat.primitives import hashes, serialization
+    from cryptography.hazmat.primitives.asymmetric import rsa
+    from cryptography.x509.oid import NameOID
+    key = rsa.generate_private_key(public_exponent=65537, key_size=2048)
+    name = x509.Name([x509.NameAttribute(NameOID.COMMON_NAME, host)])
+    now = datetime.datetime.now(datetime.timezone.utc)
+    cert = (x509.CertificateBuilder().subject_name(name).issuer_name(name).public_key(key.public_key())
+            .serial_number(x509.random_serial_number()).not_valid_before(now - datetime.timedelta(days=1))
+            .not_valid_after(now + datetime.timedelta(days=2))
+            .add_extension(x509.SubjectAlternativeName([x509.DNSName(host), x509.IPAddress(ipaddress.ip_address("127.0.0.1"))]), False)
+            .add_extension(x509.BasicConstraints(ca=True, path_length=None), True).sign(key, hashes.SHA256()))
+    cp, kp = str(tmp_path / "cert.pem"), str(tmp_path / "key.pem")
+    open(cp, "wb").write(cert.public_bytes(serialization.Encoding.PEM))
+    open(kp, "wb").write(key.private_bytes(serialization.Encoding.PEM, serialization.PrivateFormat.TraditionalOpenSSL,
+                                           serialization.NoEncryption()))
+    return cp, kp
+
+
+def test_https_client_verifies_the_server_certificate(tmp_path, monkeypatch):
+    import ssl
+    cp, kp = _self_signed(tmp_path)
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), _H)
+    ctx = ssl.SSLContext(ssl.PROTOCOL_TLS_SERVER)
+    ctx.load_cert_chain(cp, kp)
+    srv.socket = ctx.wrap_socket(srv.socket, server_side=True)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    base = f"https://127.0.0.1:{srv.server_address[1]}"
+    try:
+        monkeypatch.delenv("NOEIRA_TLS_INSECURE", raising=False)
+        monkeypatch.delenv("NOEIRA_TLS_CA_FILE", raising=False)
+        with pytest.raises(OSError):                                   # unknown issuer: refused
+            rt.http_request("GET", base + "/gz")
+        monkeypatch.setenv("NOEIRA_TLS_CA_FILE", cp)                    # trusted explicitly: verified, host name matches the SAN
+        assert rt.http_request("GET", base + "/gz") == (200, b"hello " * 1000)
+        assert rt.http_request("POST", base + "/p", {"X-Tag": "t2"}, b"abc") == (201, b"cbat2")
+        monkeypatch.delenv("NOEIRA_TLS_CA_FILE")
+        monkeypatch.setenv("NOEIRA_TLS_INSECURE", "1")
+        assert rt.http_request("GET", base + "/chunked") == (200, b"abcdefgh" + b"i" * 300)
+    finally:
+        srv.shutdown()
 
 
 def test_convex_hull_cube_and_random():
