@@ -28,6 +28,9 @@ _PKG = Path(__file__).resolve().parent
 CSRC = _PKG / "csrc"
 LIBDIR = _PKG / "_lib"
 CUDA_LIB = LIBDIR / "libnoeira_b200.so"
+# the same sources compiled with -DNB_BOUNDS=1 (index-driven kernels test their indices; see csrc/common.cuh);
+# selected with NOEIRA_B200_BOUNDS=1
+CUDA_LIB_BOUNDS = LIBDIR / "libnoeira_b200_bounds.so"
 HOST_LIB = LIBDIR / "libnoeira_b200_host.so"
 
 NVCC_FLAGS = [
@@ -102,12 +105,13 @@ def build(force: bool = False, verbose: bool = False) -> None:
         cu = sorted(CSRC.glob("*.cu"))
         hdr = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted((CSRC / "host").glob("*.h"))
         if cu:
-            nv = [_nvcc()] + NVCC_FLAGS + ["-I", str(CSRC)]
-            objs, changed = _build_one(cu, hdr, LIBDIR / "obj" / "cuda", nv, ".cu")
-            if changed or not CUDA_LIB.exists():
-                _run([_nvcc(), "-shared", "-o", str(CUDA_LIB)] + [str(o) for o in objs]
-                     + ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-lpthread", "-ldl"],
-                     LIBDIR / "obj" / "link_cuda.log")
+            for lib, objdir, extra in ((CUDA_LIB, "cuda", []), (CUDA_LIB_BOUNDS, "cuda_bounds", ["-DNB_BOUNDS=1"])):
+                nv = [_nvcc()] + NVCC_FLAGS + extra + ["-I", str(CSRC)]
+                objs, changed = _build_one(cu, hdr, LIBDIR / "obj" / objdir, nv, ".cu")
+                if changed or not lib.exists():
+                    _run([_nvcc(), "-shared", "-o", str(lib)] + [str(o) for o in objs]
+                         + ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-lpthread", "-ldl"],
+                         LIBDIR / "obj" / f"link_{objdir}.log")
         cpp = sorted((CSRC / "host").glob("*.cpp"))
         if cpp:
             gx = [shutil.which("g++") or "g++"] + GXX_FLAGS + ["-I", str(CSRC), "-I", str(CSRC / "host")]
@@ -146,12 +150,34 @@ def cuda_lib() -> ctypes.CDLL:
     """The sm_100a kernel library.  Raises if it cannot be loaded — there is no eager fallback."""
     global _cuda
     if _cuda is None:
-        if not CUDA_LIB.exists() and _autobuild_allowed():
+        bounds = os.environ.get("NOEIRA_B200_BOUNDS", "0") == "1"
+        lib = CUDA_LIB_BOUNDS if bounds else CUDA_LIB
+        if not lib.exists() and _autobuild_allowed():
             build()
-        if not CUDA_LIB.exists():
-            raise RuntimeError(f"{CUDA_LIB} is missing: run `python -m noeira_b200.build`")
-        _cuda = ctypes.CDLL(str(CUDA_LIB))
+        if not lib.exists():
+            raise RuntimeError(f"{lib} is missing: run `python -m noeira_b200.build`")
+        _cuda = ctypes.CDLL(str(lib))
+        _cuda._bounds_registered = set()
     return _cuda
+
+
+def register_bounds_status(status_tensor) -> int:
+    """Bounds-checked build only: point every translation unit's bounds reporter at the device status word of the
+    CURRENT device.  Returns how many units were registered (0 in the normal build)."""
+    lib = cuda_lib()
+    if os.environ.get("NOEIRA_B200_BOUNDS", "0") != "1":
+        return 0
+    key = status_tensor.data_ptr()
+    if key in lib._bounds_registered:
+        return 0
+    n = 0
+    for tu in ("misc_ops", "replay", "ppo_kernels"):
+        fn = getattr(lib, f"nb_bounds_register_{tu}", None)
+        if fn is not None:
+            check(fn(ctypes.c_void_p(key)), f"bounds_register_{tu}")
+            n += 1
+    lib._bounds_registered.add(key)
+    return n
 
 
 def have_cuda_lib() -> bool:

@@ -80,6 +80,24 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---------------------------------------------------------------- bounds-checked build (-DNB_BOUNDS=1)
+// compute-sanitizer is not available everywhere, so the library can be built with its own net: kernels that index
+// memory with values they read from memory (token ids, replay indices, shuffled minibatch rows, class targets) test the
+// value against the extent first.  A failed test records NB_ST_BOUNDS (+ site, block, offending value) in the status
+// word registered for this translation unit and SKIPS the access — no fault, the context stays usable.  In the normal
+// build the test compiles to `true`.
+#ifdef NB_BOUNDS
+static __device__ unsigned int* g_nb_bounds_status = nullptr;
+#define NB_IN_BOUNDS(cond, where, extra) ((cond) ? true : (nb::report(nb::g_nb_bounds_status, NB_ST_BOUNDS, (where), (unsigned int)(extra)), false))
+#define NB_BOUNDS_REGISTER(tu)                                                                                     \
+  extern "C" int nb_bounds_register_##tu(unsigned int* st) {                                                       \
+    return (int)cudaMemcpyToSymbol(nb::g_nb_bounds_status, &st, sizeof(st));                                       \
+  }
+#else
+#define NB_IN_BOUNDS(cond, where, extra) (true)
+#define NB_BOUNDS_REGISTER(tu)
+#endif
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

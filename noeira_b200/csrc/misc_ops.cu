@@ -37,12 +37,13 @@ rope_kernel(__nv_bfloat16* __restrict__ x, int B, int S, int H, int D, long long
 // out[t, :] = table[idx[t], :] * scale
 __global__ void __launch_bounds__(256)
 embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table, int ldt, const long long* __restrict__ idx,
-                     __nv_bfloat16* __restrict__ out, int ldo, int T, int D, float scale) {
+                     __nv_bfloat16* __restrict__ out, int ldo, int T, int D, float scale, int vocab) {
   const int nvec = D / 8;
   const long long total = (long long)T * nvec;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int t = (int)(i / nvec), v = (int)(i % nvec);
+    if (!NB_IN_BOUNDS(idx[t] >= 0 && (vocab <= 0 || idx[t] < vocab), 601, idx[t])) continue;
     uint4 w = *reinterpret_cast<const uint4*>(table + (size_t)idx[t] * ldt + v * 8);
     if (scale != 1.f) {
       __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
@@ -55,11 +56,12 @@ embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table, int ldt, const lon
 // dtable[idx[t], :] += dy[t, :] * scale   (fp32 atomics: order, hence the last bit, is not reproducible)
 __global__ void __launch_bounds__(256)
 embedding_bwd_kernel(float* __restrict__ dtable, int ldt, const long long* __restrict__ idx,
-                     const __nv_bfloat16* __restrict__ dy, int ldy, int T, int D, float scale) {
+                     const __nv_bfloat16* __restrict__ dy, int ldy, int T, int D, float scale, int vocab) {
   const long long total = (long long)T * D;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int t = (int)(i / D), d = (int)(i % D);
+    if (!NB_IN_BOUNDS(idx[t] >= 0 && (vocab <= 0 || idx[t] < vocab), 602, idx[t])) continue;
     atomicAdd(dtable + (size_t)idx[t] * ldt + d, __bfloat162float(dy[(size_t)t * ldy + d]) * scale);
   }
 }
@@ -130,7 +132,8 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, int ld, const long long
   __shared__ float sh[32];
   const int row = blockIdx.x;
   __nv_bfloat16* lr = logits + (size_t)row * ld;
-  const long long tg = target[row];
+  long long tg = target[row];
+  if (!NB_IN_BOUNDS(tg == ignore_index || (tg >= 0 && tg < V), 603, tg)) tg = ignore_index;
   float mx = -INFINITY;
   for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[i]));
   mx = block_max(mx, sh);
@@ -173,6 +176,8 @@ inline int g1(long long n) {
 }
 }  // namespace
 
+NB_BOUNDS_REGISTER(misc_ops)
+
 extern "C" {
 
 int nb_rope(void* x, int B, int S, int H, int D, long long sb, long long ss, long long sh, float theta, int pos0,
@@ -184,19 +189,20 @@ int nb_rope(void* x, int B, int S, int H, int D, long long sb, long long ss, lon
   return NB_OK;
 }
 
+// vocab: number of table rows (<= 0: unknown; only the bounds-checked build reads it)
 int nb_embedding_fwd(const void* table, int ldt, const long long* idx, void* out, int ldo, int T, int D, float scale,
-                     void* stream) {
+                     int vocab, void* stream) {
   if (D % 8 || ldt % 8 || ldo % 8) return NB_ERR_UNALIGNED;
   embedding_fwd_kernel<<<g1((long long)T * D / 8), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)table, ldt, idx, (__nv_bfloat16*)out, ldo, T, D, scale);
+      (const __nv_bfloat16*)table, ldt, idx, (__nv_bfloat16*)out, ldo, T, D, scale, vocab);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }
 
 int nb_embedding_bwd(float* dtable, int ldt, const long long* idx, const void* dy, int ldy, int T, int D, float scale,
-                     void* stream) {
+                     int vocab, void* stream) {
   embedding_bwd_kernel<<<g1((long long)T * D), 256, 0, (cudaStream_t)stream>>>(dtable, ldt, idx,
-                                                                              (const __nv_bfloat16*)dy, ldy, T, D, scale);
+                                                                              (const __nv_bfloat16*)dy, ldy, T, D, scale, vocab);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

@@ -123,7 +123,8 @@ ppo_gather_kernel(const uint4* __restrict__ obs_pool, int obs_words, const float
   const uint32_t key = mix32((uint32_t)seed ^ mix32(epoch + 0x632BE5ABu * (uint32_t)(counters[1] + 1ull)));
   float a = 0.f;
   if (i < mb_size) {
-    const uint32_t src = feistel_perm(k * (uint32_t)mb_size + (uint32_t)i, (uint32_t)pool, hb, key);
+    uint32_t src = feistel_perm(k * (uint32_t)mb_size + (uint32_t)i, (uint32_t)pool, hb, key);
+    if (!NB_IN_BOUNDS(src < (uint32_t)pool, 621, src)) src = 0;
     for (int w = 0; w < obs_words; ++w) obs_mb[(size_t)i * obs_words + w] = obs_pool[(size_t)src * obs_words + w];
     for (int j = 0; j < ld_act; ++j) act_mb[(size_t)i * ld_act + j] = act_pool[(size_t)src * ld_act + j];
     logp_mb[i] = logp_pool[src];
@@ -275,6 +276,8 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
 }
 
 }  // namespace
+
+NB_BOUNDS_REGISTER(ppo_kernels)
 
 extern "C" {
 

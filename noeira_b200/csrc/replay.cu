@@ -60,8 +60,10 @@ __global__ void replay_indices_kernel(long long* __restrict__ idx, int batch, co
 // ---- sum tree over `leaves` (power of two) priorities: tree[1] = total, children of n are 2n, 2n+1, leaves at [leaves, 2·leaves)
 __global__ void per_set_kernel(float* __restrict__ tree, long long leaves, const long long* __restrict__ idx,
                                const float* __restrict__ prio, int n, float alpha, float eps) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    if (!NB_IN_BOUNDS(idx[i] >= 0 && idx[i] < leaves, 612, idx[i])) continue;
     tree[leaves + idx[i]] = powf(fabsf(prio[i]) + eps, alpha);
+  }
 }
 // After the leaves idx[0..n) changed, re-sum their ancestors one level per launch (level k = nodes (leaves+idx)>>k).
 // Threads that share an ancestor write the same value, so the result is deterministic without atomics, and the
@@ -69,6 +71,7 @@ __global__ void per_set_kernel(float* __restrict__ tree, long long leaves, const
 __global__ void per_ancestors_kernel(float* __restrict__ tree, long long leaves, const long long* __restrict__ idx, int n,
                                      int level) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    if (!NB_IN_BOUNDS(idx[i] >= 0 && idx[i] < leaves, 613, idx[i])) continue;
     const long long node = (leaves + idx[i]) >> level;
     tree[node] = tree[2 * node] + tree[2 * node + 1];
   }
@@ -112,15 +115,18 @@ __global__ void replay_bump_counter_kernel(long long* meta) {
 }
 
 __global__ void replay_gather_kernel(const float* __restrict__ buf, int width, const long long* __restrict__ idx,
-                                     float* __restrict__ out, int batch) {
+                                     float* __restrict__ out, int batch, long long capacity) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)batch * width;
        i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / width), c = (int)(i % width);
+    if (!NB_IN_BOUNDS(idx[r] >= 0 && (capacity <= 0 || idx[r] < capacity), 611, idx[r])) continue;
     out[i] = buf[idx[r] * width + c];
   }
 }
 inline int blocks_for(long long n) { long long b = (n + 255) / 256; return (int)(b < 1 ? 1 : (b > 148 * 8 ? 148 * 8 : b)); }
 }  // namespace
+
+NB_BOUNDS_REGISTER(replay)
 
 extern "C" {
 
@@ -180,8 +186,9 @@ int nb_per_sample(const float* tree, long long leaves, long long* idx, float* we
   return NB_OK;
 }
 
-int nb_replay_gather(const float* buf, int width, const long long* idx, float* out, int batch, void* stream) {
-  replay_gather_kernel<<<blocks_for((long long)batch * width), 256, 0, (cudaStream_t)stream>>>(buf, width, idx, out, batch);
+// capacity: number of rows of `buf` (<= 0: unknown; only the bounds-checked build reads it)
+int nb_replay_gather(const float* buf, int width, const long long* idx, float* out, int batch, long long capacity, void* stream) {
+  replay_gather_kernel<<<blocks_for((long long)batch * width), 256, 0, (cudaStream_t)stream>>>(buf, width, idx, out, batch, capacity);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

@@ -148,7 +148,7 @@ class StoreReplayGpu:
         b = idx.numel()
         out = self._out.setdefault(b, torch.zeros(b, self.width, device=self.device))
         check(self._lib.nb_replay_gather(self._ptr(self.buf), c.c_int(self.width), self._ptr(idx), self._ptr(out), c.c_int(b),
-                                         stream_ptr()), "replay_gather")
+                                         c.c_longlong(self.capacity), stream_ptr()), "replay_gather")
         O, A = self.obs_dim, self.act_dim
         return out[:, :O], out[:, O:O + A], out[:, O + A], out[:, O + A + 1: 2 * O + A + 1], out[:, 2 * O + A + 1]
 

@@ -117,7 +117,7 @@ class Embedding(Module):
         out = torch.empty(self._idx.numel(), self.dim, device=idx.device, dtype=torch.bfloat16)
         check(cuda_lib().nb_embedding_fwd(ptr(W), ctypes.c_int(W.stride(0)), ptr(self._idx), ptr(out), ctypes.c_int(self.dim),
                                           ctypes.c_int(self._idx.numel()), ctypes.c_int(self.dim), ctypes.c_float(self.scale),
-                                          stream_ptr()), "embedding_fwd")
+                                          ctypes.c_int(self.weight.shape[0]), stream_ptr()), "embedding_fwd")
         return out.reshape(*idx.shape, self.dim)
 
     def vjp(self, dy):
@@ -131,7 +131,7 @@ class Embedding(Module):
         g = self.weight.grad_storage
         check(cuda_lib().nb_embedding_bwd(ptr(g), ctypes.c_int(g.stride(0)), ptr(self._idx), ptr(d2), ctypes.c_int(d2.stride(0)),
                                           ctypes.c_int(d2.shape[0]), ctypes.c_int(self.dim), ctypes.c_float(self.scale),
-                                          stream_ptr()), "embedding_bwd")
+                                          ctypes.c_int(self.weight.shape[0]), stream_ptr()), "embedding_bwd")
         return None
 
 

@@ -26,6 +26,8 @@ def device_status(device=None) -> torch.Tensor:
     if t is None:
         t = torch.zeros(4, dtype=torch.int32, device=dev)
         _STATUS[key] = t
+        from .._native import register_bounds_status
+        register_bounds_status(t)          # bounds-checked build: failed index tests are reported through this word
     return t
 
 
