@@ -321,10 +321,13 @@ class PPOTrainer:
         self._update()
 
     def train_iteration(self, read_metrics: bool = True):
+        from ..utils.trace import nvtx_range
         self.metrics.zero_()
         self.env.ep_stats.zero_()
-        self.collect()
-        self.update()
+        with nvtx_range("ppo.collect"):
+            self.collect()
+        with nvtx_range("ppo.update"):
+            self.update()
         self.iteration += 1
         return self.read_metrics() if read_metrics else None
 

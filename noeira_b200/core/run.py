@@ -156,6 +156,8 @@ class PerfTimer:
             self.t, self.name = timer, name
 
         def __enter__(self):
+            from ..utils.trace import nvtx_range
+            self._nv = nvtx_range(self.name).__enter__()
             if self.t.cuda:
                 import torch
                 self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -165,6 +167,7 @@ class PerfTimer:
             return self
 
         def __exit__(self, *exc):
+            self._nv.__exit__(*exc)
             if self.t.cuda:
                 self.e1.record()
                 self.t._pending.append((self.name, self.e0, self.e1))

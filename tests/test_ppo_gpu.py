@@ -92,3 +92,21 @@ def test_ppo_actor_gradient_matches_autograd():
         g, rg = p.grad.double(), r.grad
         denom = rg.abs().max().item() + 1e-8
         assert (g - rg).abs().max().item() / denom < 0.06, (p.name, (g - rg).abs().max().item(), denom)
+
+
+def test_steady_state_iteration_allocates_nothing():
+    """After warm-up and capture, a PPO iteration is graph replays only: the caching allocator is not entered."""
+    import torch
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs import PlanarChainEnv
+    from noeira_b200.utils.trace import AllocTracer
+    env = PlanarChainEnv(512, seed=3)
+    tr = PPOTrainer(env, PPOConfig(n_envs=512, rollout_len=4, n_epochs=1, n_minibatches=2))
+    for _ in range(3):
+        tr.train_iteration(read_metrics=False)
+    torch.cuda.synchronize()
+    tracer = AllocTracer(enabled=True)
+    with tracer.scope("iteration"):
+        tr.train_iteration(read_metrics=False)
+        torch.cuda.synchronize()
+    tracer.assert_steady("iteration")
