@@ -34,9 +34,13 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", type=int, default=-1, help="index of the single shape to run (profiling captures)")
     ap.add_argument("--no-sdpa", action="store_true", help="skip the library comparison")
+    ap.add_argument("--fwd-mode", type=int, default=0, help="0 = by size, 1 = one query tile per CTA, 2 = two tiles")
+    ap.add_argument("--no-bwd", action="store_true", help="forward only")
     args = ap.parse_args()
     from noeira_b200.ops import check_status
     from noeira_b200.ops.attention import flash_attention_backward, flash_attention_forward
+    from noeira_b200.ops.attention import set_forward_mode
+    set_forward_mode(args.fwd_mode)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     shapes = [  # B, S, Hq, Hkv, D, mask, frame
         (8, 1024, 12, 12, 64, None, 0),          # ViT tower
@@ -60,6 +64,8 @@ def main():
         fl = 4.0 * B * Hq * S * S * D * frac
         row = {"shape": [B, S, Hq, Hkv, D], "mask": mask, "fwd_ms": round(t, 4), "fwd_tflops": round(fl / t / 1e9, 1)}
         try:
+            if args.no_bwd:
+                raise RuntimeError("skipped")
             o, lse = flash_attention_forward(q, k, v, mask=mask, frame=frame)
             do = torch.randn_like(o)
             tb = timeit(lambda: flash_attention_backward(q, k, v, o, lse, do, mask=mask, frame=frame), args.iters, flush)

@@ -102,5 +102,8 @@ inline int make_tmap_bshd(CUtensorMap* tm, const void* base, int B, int S, int H
   return r == CUDA_SUCCESS ? NB_OK : NB_ERR_TENSORMAP;
 }
 
+// forward with two query tiles per CTA (attention_fwd2_tcgen05.cu)
+int launch_fwd_two_tile(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
+                        cudaStream_t s);
 
 }  // namespace nbattn

@@ -339,7 +339,16 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 
 }  // namespace
 
+static int g_fwd_mode = 0;  // 0 = choose by problem size, 1 = one query tile per CTA, 2 = two query tiles per CTA
+
 extern "C" {
+
+// Selects the forward kernel (tests and benchmarks compare the two forms); returns the previous setting.
+int nb_flash_attn_fwd_mode(int mode) {
+  const int old = g_fwd_mode;
+  if (mode >= 0 && mode <= 2) g_fwd_mode = mode;
+  return old;
+}
 
 // Q [B,Sq,Hq,HD], K/V [B,Sk,Hkv,HD] bf16, element strides given per tensor as (batch, token, head);
 // the innermost (HD) stride is 1.  O is written with the same batch/token/head strides as described by
@@ -368,6 +377,9 @@ int nb_flash_attn_fwd(const void* Q, const void* K, const void* V, void* O, floa
   p.key_valid = key_valid; p.bias = bias;
   p.O = (__nv_bfloat16*)O; p.lse = lse; p.status = status;
   cudaStream_t s = (cudaStream_t)stream;
+  // two tiles per CTA pay once every SM has a CTA of 256 queries; small problems keep the finer grid
+  const bool two = g_fwd_mode == 2 || (g_fwd_mode == 0 && Sq > BQ && (long long)ceil_div(Sq, 2 * BQ) * Hq * B >= 148);
+  if (two) return launch_fwd_two_tile(tq, tk, tv, p, HD, s);
   if (HD == 64) return launch_fwd<64>(tq, tk, tv, p, s);
   return launch_fwd<128>(tq, tk, tv, p, s);
 }

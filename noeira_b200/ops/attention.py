@@ -43,6 +43,15 @@ def attention_reference(q, k, v, scale=None, mask=None, frame=0, causal_off=0, k
     return o.permute(0, 2, 1, 3).contiguous(), lse2
 
 
+FWD_AUTO, FWD_ONE_TILE, FWD_TWO_TILE = 0, 1, 2
+
+
+def set_forward_mode(mode: int) -> int:
+    """Selects the forward kernel: by problem size (default), one 128-query tile per CTA, or two tiles per CTA
+    ping-ponging on the tensor core (csrc/attention_fwd2_tcgen05.cu).  Returns the previous setting."""
+    return int(cuda_lib().nb_flash_attn_fwd_mode(ctypes.c_int(mode)))
+
+
 def flash_attention_forward(q, k, v, scale=None, mask=None, frame=0, causal_off=0, key_valid=None, bias=None,
                             out=None, want_lse=True):
     """q [B,Sq,Hq,D], k/v [B,Sk,Hkv,D] bf16 (any batch/token/head strides, unit stride on D; views into a

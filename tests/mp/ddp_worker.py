@@ -157,7 +157,9 @@ def zero_case(rank, world, local):
     if rank == 0:
         print(f"zero numel={opt.arena.numel}: replicas_equal={same} max|fused-nccl|={err:.3e} shadow_err={sherr:.2e} "
               f"moments_sharded={shard_ok} grd_zeroed={gz == 0.0}")
-    return same and err < 2e-5 and sherr < 2e-2 and shard_ok and gz == 0.0
+    # lr = 1e-2: the library's ring order and this kernel's rank order sum the gradients differently, and Adam turns
+    # a last-bit difference of a near-zero gradient into a difference of a fraction of lr
+    return same and err < 2e-4 and sherr < 2e-2 and shard_ok and gz == 0.0
 
 
 if __name__ == "__main__":

@@ -17,8 +17,18 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,mask,frame", CASES)
-def test_flash_forward(B, Sq, Sk, Hq, Hkv, D, mask, frame):
+@pytest.fixture(params=[1, 2], ids=["one_tile", "two_tile"])
+def fwd_mode(request):
+    """Runs a forward test once per forward kernel (one / two query tiles per CTA)."""
+    from noeira_b200.ops.attention import set_forward_mode
+    old = set_forward_mode(request.param)
+    yield request.param
+    set_forward_mode(old)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,mask,frame", CASES + [(1, 1000, 1000, 2, 1, 128, "causal", 0),
+                                                                  (1, 640, 900, 2, 2, 64, None, 0)])
+def test_flash_forward(B, Sq, Sk, Hq, Hkv, D, mask, frame, fwd_mode):
     from noeira_b200.ops import check_status
     from noeira_b200.ops.attention import attention_reference, flash_attention_forward
     torch.manual_seed(0)
@@ -33,7 +43,7 @@ def test_flash_forward(B, Sq, Sk, Hq, Hkv, D, mask, frame):
     assert (lse - rl).abs().max().item() < 2e-2
 
 
-def test_flash_forward_key_padding_and_bias_and_packed_qkv():
+def test_flash_forward_key_padding_and_bias_and_packed_qkv(fwd_mode):
     from noeira_b200.ops import check_status
     from noeira_b200.ops.attention import attention_reference, flash_attention_forward
     torch.manual_seed(1)
