@@ -27,6 +27,9 @@ using namespace nb;
 using namespace nbattn;
 
 constexpr int FA2_THREADS = 384;  // three warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
+// Register budget: the CTA is launched with 384 x 168 registers and setmaxnreg only moves registers inside that
+// allocation (an increase BLOCKS until the CTA's pool has them), so 128 x 72 + 256 x 216 must not exceed 384 x 168.
+static_assert(128 * 72 + 256 * 216 <= FA2_THREADS * 168, "setmaxnreg budget");
 
 template <int HD>
 __global__ void __launch_bounds__(FA2_THREADS, 1)
@@ -98,7 +101,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (elect_one()) {
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
@@ -125,7 +128,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (elect_one()) {
       const uint32_t idesc_s = make_idesc(1u, BQ, BKV, 0u, 0u);  // S = Q Kᵀ : both K-major
       const uint32_t idesc_o = make_idesc(1u, BQ, HD, 0u, 1u);   // O += P V : P from tensor memory, V MN-major
@@ -180,7 +183,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (!ok) *abort_flag = 1;
     }
   } else if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   } else {
     // ---------------------------------------------------------------- softmax / epilogue: one thread per query row
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");

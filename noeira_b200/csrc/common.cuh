@@ -401,6 +401,11 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
 __device__ __forceinline__ void tma_store_wait_all_but_one() {
   asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
 }
+// waits until at most the N most recent bulk groups of this thread are still pending
+template <int N>
+__device__ __forceinline__ void tma_store_wait_all_but() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // ---------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float warp_sum(float v) {

@@ -439,6 +439,62 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmOwn, const __grid_consta
   finish_epoch(ctl, epoch);
 }
 
+// Sum of the `world` slot copies of one 128 x 128 output tile of this rank (+ residual) → bf16 D.  W = upper bound of the
+// world size, U = vectors per thread and batch: W·U 16-byte loads are in flight per thread.
+template <int W, int U>
+__device__ __forceinline__ void rs_reduce_tile(const TpParams& p, int lb, int nb_, int t128) {
+  const __nv_bfloat16* mine = p.slot_peer[p.rank];
+  const int c0 = nb_ * BN;
+  const int tv = min(BN, p.N - c0) >> 3;   // 16-byte vectors per row of this tile
+  const int total = BM * tv;
+  for (int i0 = t128; i0 < total; i0 += 128 * U) {
+    uint4 sv[U][W];
+    uint4 rv[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int i = i0 + k * 128;
+      if (i < total) {
+        const int rr = i / tv, cv = i - rr * tv;
+        const int lrow = lb * BM + rr;
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < p.world) sv[k][r] = ld_peer16(mine + ((size_t)r * p.Ms + lrow) * p.ld_slot + c0 + cv * 8);
+        if (p.residual) rv[k] = *reinterpret_cast<const uint4*>(p.residual + (size_t)lrow * p.ld_res + c0 + cv * 8);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int i = i0 + k * 128;
+      if (i < total) {
+        const int rr = i / tv, cv = i - rr * tv;
+        const int lrow = lb * BM + rr;
+        float a[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = 0.f;
+        if (p.residual) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rv[k]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { a[2 * e] = __low2float(h[e]); a[2 * e + 1] = __high2float(h[e]); }
+        }
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+          if (r < p.world) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&sv[k][r]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[2 * e] += __low2float(h[e]); a[2 * e + 1] += __high2float(h[e]); }
+          }
+        }
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]),
+                       h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(p.D + (size_t)lrow * p.ldd + c0 + cv * 8) = pk;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ GEMM → RS
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -504,7 +560,13 @@ tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // left early would strand the others), so failures only switch the work off.
     // One thread (`issuer`) owns the TMA stores of this CTA, so their bulk async-groups complete in tile order.
     const bool issuer = warp == 2 && lane == 0;
-    int prev_owner = -1, prev_lb = 0, it = 0;
+    int it = 0;
+    int pend[3] = {-1, -1, -1};  // (owner << 20 | row block) of the tiles whose stores are in flight, oldest first
+    auto signal_block = [&](int packed) {
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence_system();
+      red_release_sys_add(p.ctl_peer[packed >> 20] + CTL_BLOCKS + (packed & 0xFFFFF), 1u);
+    };
     for (int t = cta; t < num_tiles; t += ncta, ++it) {
       const int pos = t / p.tiles_n, nb_ = t - pos * p.tiles_n;
       const int gb = ordered_block(p, pos, bpr, true);
@@ -551,61 +613,34 @@ tp_gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (nb_ * BN + 64 < p.N) tma_store_2d(&slots.m[owner], buf + EPI_BOX_BYTES, nb_ * BN + 64, y);
         }
         tma_store_commit();
-        // the previous tile's store has completed → one arrival on its owner's row-block counter
-        if (prev_owner >= 0) {
-          tma_store_wait_all_but_one();
-          asm volatile("fence.proxy.async.global;" ::: "memory");
-          __threadfence_system();
-          red_release_sys_add(p.ctl_peer[prev_owner] + CTL_BLOCKS + prev_lb, 1u);
-        }
-        prev_owner = ok ? owner : -1;
-        prev_lb = lb;
+        // Exactly one bulk group per tile.  Once at most the three newest are pending, the store of tile it-3 has
+        // completed → one arrival on its owner's row-block counter.  Four stores in flight hide the NVLink round trip.
+        tma_store_wait_all_but<3>();
+        if (pend[0] >= 0) signal_block(pend[0]);
+        pend[0] = pend[1]; pend[1] = pend[2];
+        pend[2] = ok ? ((owner << 20) | lb) : -1;
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
     if (issuer) {
       tma_store_wait_all();
-      if (prev_owner >= 0) {
-        asm volatile("fence.proxy.async.global;" ::: "memory");
-        __threadfence_system();
-        red_release_sys_add(p.ctl_peer[prev_owner] + CTL_BLOCKS + prev_lb, 1u);
-      }
+#pragma unroll
+      for (int i = 0; i < 3; ++i)
+        if (pend[i] >= 0) signal_block(pend[i]);
     }
-    // ---- tail: reduce local row blocks in rank order (deterministic), add the residual, write bf16
+    // ---- tail: reduce the local row blocks in rank order (deterministic), add the residual, write bf16.  Work unit =
+    // one 128 x 128 tile so that every CTA has some; all slot loads of a batch are issued before the first add.
     const unsigned int need = epoch * (unsigned int)(p.world * p.tiles_n);
     const int t128 = (warp - 2) * 32 + lane;  // 0..127
-    const int vecs = p.N / 8;
-    for (int lb = cta; lb < bpr; lb += ncta) {
+    for (int u = cta; u < bpr * p.tiles_n; u += ncta) {
+      const int lb = u / p.tiles_n, nb_ = u - lb * p.tiles_n;
       if (warp == 2 && lane == 0 && !*q.abort_flag)
         if (!wait_flag_ge_ns(ctl + CTL_BLOCKS + lb, need, p.status, 520, (unsigned)lb, p.wait_ns)) *q.abort_flag = 1;
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*q.abort_flag) continue;
-      const __nv_bfloat16* mine = p.slot_peer[p.rank];
-      for (int i = t128; i < BM * vecs; i += 128) {
-        const int rr = i / vecs, cv = i - rr * vecs;
-        const int lrow = lb * BM + rr;
-        float a[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) a[u] = 0.f;
-        if (p.residual) {
-          const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (size_t)lrow * p.ld_res + cv * 8);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) { a[2 * u] = __low2float(h[u]); a[2 * u + 1] = __high2float(h[u]); }
-        }
-        for (int s = 0; s < p.world; ++s) {
-          const uint4 sv = ld_peer16(mine + ((size_t)s * p.Ms + lrow) * p.ld_slot + cv * 8);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&sv);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) { a[2 * u] += __low2float(h[u]); a[2 * u + 1] += __high2float(h[u]); }
-        }
-        uint4 pk;
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]),
-                       h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
-        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(p.D + (size_t)lrow * p.ldd + cv * 8) = pk;
-      }
+      if (p.world <= 2) rs_reduce_tile<2, 4>(p, lb, nb_, t128);
+      else if (p.world <= 4) rs_reduce_tile<4, 2>(p, lb, nb_, t128);
+      else rs_reduce_tile<8, 1>(p, lb, nb_, t128);
     }
   }
   tc_fence_before();
