@@ -26,6 +26,43 @@ namespace {
 using namespace nb;
 using namespace nbattn;
 
+// P = 2^(s * mult - m) of one row (128 scores), written as packed bf16 into tensor-memory columns [s_addr, s_addr + 64);
+// returns the row sum.  Arguments are formed as packed pairs; with EMU pairs 3 and 7 of each group of eight (a quarter
+// of the elements) take the polynomial on the FMA pipe, the rest the special-function unit.
+template <bool EMU>
+__device__ __forceinline__ float exp_store(const float (&s)[128], float mult, float m_use, uint32_t s_addr) {
+  uint64_t lsum2 = pack2(0.f, 0.f);
+  const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(-m_use, -m_use);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint32_t pk[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      uint64_t x2 = fma2(pack2(s[c * 16 + 2 * u], s[c * 16 + 2 * u + 1]), mult2, negm2);
+      float e0, e1;
+      if (EMU && (u & 3) == 3) {
+        x2 = exp2_poly2(x2);
+        unpack2(x2, e0, e1);
+      } else {
+        unpack2(x2, e0, e1);
+        e0 = exp2_fast(e0);
+        e1 = exp2_fast(e1);
+        x2 = pack2(e0, e1);
+      }
+      lsum2 = add2(lsum2, x2);
+      __nv_bfloat162 hv = __floats2bfloat162_rn(e0, e1);
+      pk[u] = *reinterpret_cast<uint32_t*>(&hv);
+    }
+    // 16 keys → 8 packed columns
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(s_addr + c * 8),
+                 "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
+                 : "memory");
+  }
+  float l0, l1;
+  unpack2(lsum2, l0, l1);
+  return l0 + l1;
+}
+
 constexpr int FA2_THREADS = 384;  // three warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 // Register budget: the CTA is launched with 384 x 168 registers and setmaxnreg only moves registers inside that
 // allocation (an increase BLOCKS until the CTA's pool has them), so 128 x 72 + 256 x 216 must not exceed 384 x 168.
@@ -60,7 +97,20 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * (2 * BQ), h = blockIdx.y, b = blockIdx.z;
+  // 1-D grid.  Index masks make the work of a CTA grow with its query position, so those launch the LAST query
+  // super-tiles of every (head, batch) first (longest first: the short ones fill the tail of the last wave);
+  // without a mask consecutive CTAs walk the queries of one (head, batch) and share its K / V in L2.
+  const int nqs = ceil_div(p.Sq, 2 * BQ);
+  int qs, hb;
+  if (p.mask_mode == NB_MASK_NONE) {
+    qs = blockIdx.x % nqs;
+    hb = blockIdx.x / nqs;
+  } else {
+    const int nhb = p.Hq * p.B;
+    qs = nqs - 1 - blockIdx.x / nhb;
+    hb = blockIdx.x % nhb;
+  }
+  const int q0 = qs * (2 * BQ), h = hb % p.Hq, b = hb / p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
   int nkb[2];
 #pragma unroll
@@ -213,12 +263,14 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (fast) {
         float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];
 #pragma unroll
-        for (int i = 4; i < 128; i += 4) {
-          m0 = fmaxf(m0, s[i]);
-          m1 = fmaxf(m1, s[i + 1]);
-          m2 = fmaxf(m2, s[i + 2]);
-          m3 = fmaxf(m3, s[i + 3]);
+        for (int i = 4; i < 124; i += 8) {   // three-input maximum: 64 instructions for 128 scores
+          m0 = max3(m0, s[i], s[i + 1]);
+          m1 = max3(m1, s[i + 2], s[i + 3]);
+          m2 = max3(m2, s[i + 4], s[i + 5]);
+          m3 = max3(m3, s[i + 6], s[i + 7]);
         }
+        m0 = max3(m0, s[124], s[125]);
+        m1 = max3(m1, s[126], s[127]);
         mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * mult;
       } else {
         mult = 1.f;
@@ -257,25 +309,11 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_st_32x32b_x32(o_addr + c, r);
         }
       }
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float e0 = exp2_fast(fmaf(s[c * 16 + 2 * u], mult, -m_use));
-          const float e1 = exp2_fast(fmaf(s[c * 16 + 2 * u + 1], mult, -m_use));
-          l0 += e0;
-          l1 += e1;
-          __nv_bfloat162 hv = __floats2bfloat162_rn(e0, e1);
-          pk[u] = *reinterpret_cast<uint32_t*>(&hv);
-        }
-        // 16 keys → 8 packed columns
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(s_addr + c * 8),
-                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
-                     : "memory");
-      }
-      l = l * alpha + (l0 + l1);
+      // blocks without any masked element (the common case) move a quarter of their exponentials to the FMA pipe; the
+      // polynomial cannot return an exact zero for a masked score, so masked blocks stay on the special-function unit
+      const float lblk = __all_sync(0xffffffffu, fast) ? exp_store<true>(s, mult, m_use, s_addr)
+                                                       : exp_store<false>(s, mult, m_use, s_addr);
+      l = l * alpha + lblk;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -335,7 +373,7 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
     NB_CUDA(cudaFuncSetAttribute(fa_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  dim3 grid(ceil_div(p.Sq, 2 * BQ), p.Hq, p.B);
+  dim3 grid(ceil_div(p.Sq, 2 * BQ) * p.Hq * p.B);
   fa_fwd2_kernel<HD><<<grid, FA2_THREADS, smem, s>>>(tq, tk, tv, p);
   NB_LAUNCH_CHECK();
   return NB_OK;
