@@ -47,6 +47,7 @@ def main():
         (4, 4096, 16, 16, 128, "causal", 0),
         (1, 16384, 16, 4, 128, "block_causal", 256),  # world model, 64 frames x 256 tokens
         (8, 602, 8, 8, 64, None, 0),             # ACT encoder memory
+        (4, 4096, 16, 16, 128, None, 0),
     ]
     if args.only >= 0:
         shapes = shapes[args.only: args.only + 1]

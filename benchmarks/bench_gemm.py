@@ -1,6 +1,6 @@
 """Device-timed GEMM throughput of the tcgen05 kernel vs. cuBLAS (torch.matmul) on the same shapes.
 
-    python benchmarks/bench_gemm.py [--shapes 8192x8192x8192,4096x4096x4096] [--iters 20]
+    python benchmarks/bench_gemm.py [--shapes 8192x8192x8192,4096x4096x4096] [--iters 20] [--two-cta 0|1|2]
 
 Timing: CUDA events on the launching stream, 5 warm-ups, an L2 flush (write of a 256 MB buffer)
 between timed iterations, median of `iters`.
@@ -38,8 +38,12 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--layout", default="nt", help="nt: B [N,K]; nn: B [K,N]; tn: A [K,M], B [K,N]")
+    ap.add_argument("--two-cta", type=int, default=0, help="0 = by size, 1 = one-CTA tiles only, 2 = CTA-pair tiles")
+    ap.add_argument("--no-lib", action="store_true", help="skip the cuBLAS comparison (profiling captures)")
     args = ap.parse_args()
     from noeira_b200.ops import check_status, gemm
+    from noeira_b200.ops.gemm import set_two_cta_mode
+    set_two_cta_mode(args.two_cta)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(os.path.dirname(__file__), "..", "MEASURED_PEAKS.json")))
@@ -58,7 +62,7 @@ def main():
         B = b if b_mn else b.t()
         t_ours = timeit(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, bn=args.bn), args.iters, flush)
         check_status()
-        t_lib = timeit(lambda: torch.matmul(A, B, out=out), args.iters, flush)
+        t_lib = float("nan") if args.no_lib else timeit(lambda: torch.matmul(A, B, out=out), args.iters, flush)
         fl = 2.0 * M * N * K
         print(json.dumps({"shape": sh, "layout": args.layout, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
                           "ours_tflops": round(fl / t_ours / 1e9, 1), "cublas_tflops": round(fl / t_lib / 1e9, 1),

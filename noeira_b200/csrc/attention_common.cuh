@@ -41,6 +41,44 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
       : "memory");
 }
 
+// ---- the same primitives on 32-bit shared-memory addresses.  A role that owns dozens of barriers keeps ONE base
+// address in a register and forms the others by adding constants (rematerialised for free), instead of a hoisted
+// 64-bit pointer + conversion per barrier; that is what lets the TMA and MMA threads run in a small register budget.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P1;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, P1;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_a(uint32_t addr, uint32_t parity, unsigned int* status, unsigned int where) {
+  for (uint32_t it = 0; it < NB_SPIN_LIMIT; ++it)
+    if (mbar_try_wait_a(addr, parity)) return true;
+  report(status, NB_ST_MBAR_TIMEOUT, where, parity);
+  return false;
+}
+__device__ __forceinline__ void mbar_expect_tx_a(uint32_t addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_a(uint32_t addr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void umma_commit_a(uint32_t addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_a(uint32_t dst, const void* tmap, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 __device__ __forceinline__ float exp2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -111,6 +149,13 @@ __device__ __forceinline__ int row_limit(const FaParams& p, int q, int k0) {
   else if (p.mask_mode == NB_MASK_BLOCK_CAUSAL) last = min(last, (q / p.frame + 1) * p.frame - 1);
   return max(0, min(BKV, last - k0 + 1));
 }
+// the same for a window of `width` keys starting at k0
+__device__ __forceinline__ int row_limit_w(const FaParams& p, int q, int k0, int width) {
+  int last = p.Sk - 1;
+  if (p.mask_mode == NB_MASK_CAUSAL) last = min(last, q + p.causal_off);
+  else if (p.mask_mode == NB_MASK_BLOCK_CAUSAL) last = min(last, (q / p.frame + 1) * p.frame - 1);
+  return max(0, min(width, last - k0 + 1));
+}
 __device__ __forceinline__ bool allowed(const FaParams& p, int q, int k) {
   if (k >= p.Sk) return false;
   if (p.mask_mode == NB_MASK_CAUSAL) return k <= q + p.causal_off;
@@ -153,6 +198,10 @@ inline int make_tmap_bshd(CUtensorMap* tm, const void* base, int B, int S, int H
 
 // forward with two query tiles per CTA (attention_fwd2_tcgen05.cu)
 int launch_fwd_two_tile(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
-                        cudaStream_t s);
+                        cudaStream_t s);int launch_fwd_two_tile_v4(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FaParams&, int, cudaStream_t);
+int launch_fwd_two_tile_v5(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FaParams&, int, cudaStream_t);
+int launch_fwd_two_tile_v6(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FaParams&, int, cudaStream_t);
+int launch_fwd_two_tile_base(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
+                             cudaStream_t s);
 
 }  // namespace nbattn

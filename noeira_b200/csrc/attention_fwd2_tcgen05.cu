@@ -10,7 +10,7 @@
 //                                                             [P1_j ready] O1 += P1_j V_j ; S1_{j+1} = Q1 K_{j+1}ᵀ
 //   warps 2,3   idle (they complete the first warpgroup, which gives its registers away with setmaxnreg)
 //   warps 4..7  softmax of tile 0, warps 8..11 softmax of tile 1: thread = query row (TMEM lane), 128 scores in
-//               registers (setmaxnreg raises these two warpgroups to 216 registers), one row maximum / sum without
+//               registers (setmaxnreg raises these two warpgroups to 208 registers), one row maximum / sum without
 //               any cross-thread traffic.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1.  The probabilities P_t are written back as packed bf16 INTO the first
 // 64 columns of S_t with tcgen05.st and consumed from there as the A operand of the second GEMM, so P never passes
@@ -20,27 +20,43 @@
 // (only when a row maximum grows by more than 2^8).
 // Masks, GQA, Q_LEN ≠ KV_LEN, outputs: as in the one-tile kernel (attention_tcgen05.cu).
 // Reference kernels: noeira/nn/primitives/flash_attention_mma.mojo:227-521 (mma.sync, 64-query CTAs).
+#include <type_traits>
+
 #include "attention_common.cuh"
+
+#ifndef FA2_VARIANT
+#define FA2_VARIANT
+#define FA2_SPLIT_P 1
+#define FA2_DEC "88"
+#define FA2_INC "208"
+#define FA2_DEC_N 88
+#define FA2_INC_N 208
+#endif
+#define FA2_CAT_(a, b) a##b
+#define FA2_CAT(a, b) FA2_CAT_(a, b)
+#define FA2_KERNEL FA2_CAT(fa_fwd2_kernel, FA2_VARIANT)
+#define FA2_LAUNCH FA2_CAT(launch_fwd_two_tile, FA2_VARIANT)
 
 namespace {
 using namespace nb;
 using namespace nbattn;
 
-// P = 2^(s * mult - m) of one row (128 scores), written as packed bf16 into tensor-memory columns [s_addr, s_addr + 64);
-// returns the row sum.  Arguments are formed as packed pairs; with EMU pairs 3 and 7 of each group of eight (a quarter
-// of the elements) take the polynomial on the FMA pipe, the rest the special-function unit.
-template <bool EMU>
+// P = 2^(s * mult - m) of half a row (scores [64·HALF, 64·HALF + 64) of 128), written as packed bf16 into tensor-memory
+// columns [s_addr + 32·HALF, +32); returns the sum of that half.  Arguments are formed as packed pairs; pairs 3 and 7 of
+// each group of eight (a quarter of the elements) take the polynomial on the FMA pipe, the rest the special-function
+// unit.
+template <int HALF>
 __device__ __forceinline__ float exp_store(const float (&s)[128], float mult, float m_use, uint32_t s_addr) {
   uint64_t lsum2 = pack2(0.f, 0.f);
   const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(-m_use, -m_use);
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = HALF * 4; c < HALF * 4 + 4; ++c) {
     uint32_t pk[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       uint64_t x2 = fma2(pack2(s[c * 16 + 2 * u], s[c * 16 + 2 * u + 1]), mult2, negm2);
       float e0, e1;
-      if (EMU && (u & 3) == 3) {
+      if ((u & 3) == 3) {
         x2 = exp2_poly2(x2);
         unpack2(x2, e0, e1);
       } else {
@@ -65,12 +81,12 @@ __device__ __forceinline__ float exp_store(const float (&s)[128], float mult, fl
 
 constexpr int FA2_THREADS = 384;  // three warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 // Register budget: the CTA is launched with 384 x 168 registers and setmaxnreg only moves registers inside that
-// allocation (an increase BLOCKS until the CTA's pool has them), so 128 x 72 + 256 x 216 must not exceed 384 x 168.
-static_assert(128 * 72 + 256 * 216 <= FA2_THREADS * 168, "setmaxnreg budget");
+// allocation (an increase BLOCKS until the CTA's pool has them), so 128 x 88 + 256 x 208 must not exceed 384 x 168.
+static_assert(128 * FA2_DEC_N + 256 * FA2_INC_N <= FA2_THREADS * 168, "setmaxnreg budget");
 
 template <int HD>
 __global__ void __launch_bounds__(FA2_THREADS, 1)
-fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const FaParams p) {
   constexpr int NSUB = HD / 64;                 // 64-wide swizzle atoms per row
   constexpr int KS = (HD == 64) ? 4 : 2;        // K ring and V ring depth
@@ -93,7 +109,8 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* s_full = v_empty + KS;         // [2] S_t(j) complete (and every MMA issued before it)
   uint64_t* p_full = s_full + 2;           // [2] P_t(j) stored in tensor memory, O_t rescaled
   uint64_t* o_done = p_full + 2;           // [2] last P V of tile t retired
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  uint64_t* p_lo = o_done + 2;             // [2] first 64 keys of P_t(j) stored
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_lo + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,6 +144,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
       mbar_init(&o_done[i], 1);
+      mbar_init(&p_lo[i], 4);
     }
     for (int i = 0; i < KS; ++i) {
       mbar_init(&k_full[i], 1);
@@ -148,37 +166,48 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // 32-bit shared-memory addresses: one base per array, everything else is base + constant
+  const uint32_t aQ = smem_u32(sQ), aK = aQ + 2 * Q_BYTES, aV = aK + KS * KV_BYTES, aB = aV + KS * KV_BYTES;
+  auto q_full_a = [&](int i) { return aB + 8u * (uint32_t)i; };
+  auto k_full_a = [&](int i) { return aB + 8u * (uint32_t)(2 + i); };
+  auto k_empty_a = [&](int i) { return aB + 8u * (uint32_t)(2 + KS + i); };
+  auto v_full_a = [&](int i) { return aB + 8u * (uint32_t)(2 + 2 * KS + i); };
+  auto v_empty_a = [&](int i) { return aB + 8u * (uint32_t)(2 + 3 * KS + i); };
+  auto s_full_a = [&](int i) { return aB + 8u * (uint32_t)(2 + 4 * KS + i); };
+  auto p_full_a = [&](int i) { return aB + 8u * (uint32_t)(4 + 4 * KS + i); };
+  auto o_done_a = [&](int i) { return aB + 8u * (uint32_t)(6 + 4 * KS + i); };
+  auto p_lo_a = [&](int i) { return aB + 8u * (uint32_t)(8 + 4 * KS + i); };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " FA2_DEC ";");
     if (elect_one()) {
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (nkb[t] == 0) continue;
-        mbar_expect_tx(&q_full[t], Q_BYTES);
+        mbar_expect_tx_a(q_full_a(t), Q_BYTES);
 #pragma unroll
         for (int s = 0; s < NSUB; ++s)
-          tma_load_4d(sQ + t * Q_BYTES + s * (BQ * 128), &tmQ, &q_full[t], s * 64, h, q0 + t * BQ, b);
+          tma_load_4d_a(aQ + t * Q_BYTES + s * (BQ * 128), &tmQ, q_full_a(t), s * 64, h, q0 + t * BQ, b);
       }
       for (int j = 0; j < nmax; ++j) {
         const int st = j % KS;
         const uint32_t ph = (uint32_t)(j / KS) & 1u;
-        if (*abort_flag || !mbar_wait(&k_empty[st], ph ^ 1u, p.status, 201)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&k_full[st], KV_BYTES);
+        if (*abort_flag || !mbar_wait_a(k_empty_a(st), ph ^ 1u, p.status, 201)) { *abort_flag = 1; break; }
+        mbar_expect_tx_a(k_full_a(st), KV_BYTES);
 #pragma unroll
         for (int s = 0; s < NSUB; ++s)
-          tma_load_4d(sK + st * KV_BYTES + s * (BKV * 128), &tmK, &k_full[st], s * 64, hkv, j * BKV, b);
-        if (*abort_flag || !mbar_wait(&v_empty[st], ph ^ 1u, p.status, 202)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&v_full[st], KV_BYTES);
+          tma_load_4d_a(aK + st * KV_BYTES + s * (BKV * 128), &tmK, k_full_a(st), s * 64, hkv, j * BKV, b);
+        if (*abort_flag || !mbar_wait_a(v_empty_a(st), ph ^ 1u, p.status, 202)) { *abort_flag = 1; break; }
+        mbar_expect_tx_a(v_full_a(st), KV_BYTES);
 #pragma unroll
         for (int s = 0; s < NSUB; ++s)
-          tma_load_4d(sV + st * KV_BYTES + s * (BKV * 128), &tmV, &v_full[st], s * 64, hkv, j * BKV, b);
+          tma_load_4d_a(aV + st * KV_BYTES + s * (BKV * 128), &tmV, v_full_a(st), s * 64, hkv, j * BKV, b);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " FA2_DEC ";");
     if (elect_one()) {
       const uint32_t idesc_s = make_idesc(1u, BQ, BKV, 0u, 0u);  // S = Q Kᵀ : both K-major
       const uint32_t idesc_o = make_idesc(1u, BQ, HD, 0u, 1u);   // O += P V : P from tensor memory, V MN-major
@@ -188,37 +217,42 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int st = j % KS;
         const bool first = (t == 0) || !(j < nkb[0]);
         const bool last = (t == 1) || !(j < nkb[1]);
-        if (j == 0 && !mbar_wait(&q_full[t], 0u, p.status, 210)) return false;
-        if (first && !mbar_wait(&k_full[st], (uint32_t)(j / KS) & 1u, p.status, 211)) return false;
+        if (j == 0 && !mbar_wait_a(q_full_a(t), 0u, p.status, 210)) return false;
+        if (first && !mbar_wait_a(k_full_a(st), (uint32_t)(j / KS) & 1u, p.status, 211)) return false;
         tc_fence_after();
         // descriptors of the k-steps differ from the first one only in the start-address field (bytes >> 4)
-        const uint64_t adesc0 = make_smem_desc(smem_u32(sQ + t * Q_BYTES), 16, 1024, 2);
-        const uint64_t bdesc0 = make_smem_desc(smem_u32(sK + st * KV_BYTES), 16, 1024, 2);
+        const uint64_t adesc0 = make_smem_desc(aQ + t * Q_BYTES, 16, 1024, 2);
+        const uint64_t bdesc0 = make_smem_desc(aK + st * KV_BYTES, 16, 1024, 2);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = ((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4;
           umma_f16(tmem_base + t * 128, adesc0 + off, bdesc0 + off, idesc_s, k != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[t]);
-        if (last) umma_commit(&k_empty[st]);
+        umma_commit_a(s_full_a(t));
+        if (last) umma_commit_a(k_empty_a(st));
         return true;
       };
       auto issue_pv = [&](int t, int j) -> bool {
         const int st = j % KS;
         const bool first = (t == 0) || !(j < nkb[0]);
         const bool last = (t == 1) || !(j < nkb[1]);
-        if (*abort_flag || !mbar_wait(&p_full[t], (uint32_t)j & 1u, p.status, 212)) return false;
-        if (first && !mbar_wait(&v_full[st], (uint32_t)(j / KS) & 1u, p.status, 213)) return false;
+        if (*abort_flag || !mbar_wait_a(FA2_SPLIT_P ? p_lo_a(t) : p_full_a(t), (uint32_t)j & 1u, p.status, 214)) return false;
+        if (first && !mbar_wait_a(v_full_a(st), (uint32_t)(j / KS) & 1u, p.status, 213)) return false;
         tc_fence_after();
-        const uint64_t bdesc0 = make_smem_desc(smem_u32(sV + st * KV_BYTES), BKV * 128, 1024, 2);
+        const uint64_t bdesc0 = make_smem_desc(aV + st * KV_BYTES, BKV * 128, 1024, 2);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
+          // the second half of the keys waits for the second half of P
+          if (FA2_SPLIT_P && k == BKV / 32) {
+            if (!mbar_wait_a(p_full_a(t), (uint32_t)j & 1u, p.status, 212)) return false;
+            tc_fence_after();
+          }
           // P: 16 keys = 8 packed columns per k-step; V: 16 key-rows of 128 B per k-step, 64-column chunks 16 KB apart
           umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, bdesc0 + ((k * 16 * 128) >> 4), idesc_o,
                       (j | k) != 0 ? 1u : 0u);
         }
-        if (last) umma_commit(&v_empty[st]);
-        if (j == nkb[t] - 1) umma_commit(&o_done[t]);
+        if (last) umma_commit_a(v_empty_a(st));
+        if (j == nkb[t] - 1) umma_commit_a(o_done_a(t));
         return true;
       };
       for (int t = 0; t < 2 && ok; ++t)
@@ -233,10 +267,10 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (!ok) *abort_flag = 1;
     }
   } else if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " FA2_DEC ";");
   } else {
     // ---------------------------------------------------------------- softmax / epilogue: one thread per query row
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 " FA2_INC ";");
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;          // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;
@@ -248,19 +282,26 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const unsigned char* kvalid = p.key_valid ? p.key_valid + (size_t)b * p.Sk : nullptr;
     const float* bias_row = (p.bias && q < p.Sq) ? p.bias + (size_t)q * p.Sk : nullptr;
     bool ok = true;
-    for (int j = 0; j < n && ok; ++j) {
+    // One key block of this row.  MODE 0: no score of the block is masked for any row of the tile (the hot loop: no
+    // mask arithmetic at all); MODE 1: index masks only, a prefix of the block is allowed (diagonal blocks); MODE 2: key
+    // validity and / or an additive bias (every block of such a call).
+    auto block = [&](int j, auto mode_tag) -> bool {
+      constexpr int MODE = decltype(mode_tag)::value;
       const int k0 = j * BKV;
-      if (!__all_sync(0xffffffffu, !*abort_flag && mbar_wait(&s_full[t], (uint32_t)j & 1u, p.status, 220))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, !*abort_flag && mbar_wait_a(s_full_a(t), (uint32_t)j & 1u, p.status, 220))) return false;
       tc_fence_after();
       float s[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32_nowait(s_addr + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
-      tmem_ld_wait();
-      const int lim = row_limit(p, q, k0);           // allowed leading columns of this block
-      const bool fast = (lim >= BKV) && !kvalid && !bias_row;
-      float mult = p.scale_log2;                     // exp argument = s * mult − m (slow path pre-scales, mult = 1)
+      float mult = p.scale_log2;                     // exp argument = s * mult − m (MODE 2 pre-scales, mult = 1)
       float mx;
-      if (fast) {
+      tmem_ld_wait();
+      if (MODE <= 1) {
+        if (MODE == 1) {
+          const int lim = row_limit(p, q, k0);       // allowed leading columns of this block
+#pragma unroll
+          for (int i = 0; i < 128; ++i) s[i] = i < lim ? s[i] : -INFINITY;
+        }
         float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];
 #pragma unroll
         for (int i = 4; i < 124; i += 8) {   // three-input maximum: 64 instructions for 128 scores
@@ -271,19 +312,18 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         m0 = max3(m0, s[124], s[125]);
         m1 = max3(m1, s[126], s[127]);
-        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * mult;
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * mult;   // -inf stays -inf (the scale is positive)
       } else {
+        const int lim = row_limit(p, q, k0);
         mult = 1.f;
         mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
           float v = s[i] * p.scale_log2;
           bool a = i < lim;
-          if (kvalid || bias_row) {
-            const int k = min(k0 + i, p.Sk - 1);
-            if (kvalid) a = a && (kvalid[k] != 0);
-            if (bias_row) v += bias_row[k] * 1.4426950408889634f;
-          }
+          const int k = min(k0 + i, p.Sk - 1);
+          if (kvalid) a = a && (kvalid[k] != 0);
+          if (bias_row) v += bias_row[k] * 1.4426950408889634f;
           v = a ? v : -INFINITY;
           s[i] = v;
           mx = fmaxf(mx, v);
@@ -309,21 +349,48 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_st_32x32b_x32(o_addr + c, r);
         }
       }
-      // blocks without any masked element (the common case) move a quarter of their exponentials to the FMA pipe; the
-      // polynomial cannot return an exact zero for a masked score, so masked blocks stay on the special-function unit
-      const float lblk = __all_sync(0xffffffffu, fast) ? exp_store<true>(s, mult, m_use, s_addr)
-                                                       : exp_store<false>(s, mult, m_use, s_addr);
+      // The first 64 keys of P are published on their own so that the tensor core starts P V half a softmax earlier.
+      // (A masked score reaches the polynomial as -inf and leaves it as 2^-125 instead of 0: 38 orders of magnitude
+      // below the row maximum; a row without any allowed key is recognised by its maximum, not by its sum.)
+      float lblk = exp_store<0>(s, mult, m_use, s_addr);
+      if (FA2_SPLIT_P) {
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_a(p_lo_a(t));
+      }
+      lblk += exp_store<1>(s, mult, m_use, s_addr);
       l = l * alpha + lblk;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t]);
+      if (lane == 0) mbar_arrive_a(p_full_a(t));
+      return true;
+    };
+    // blocks [0, nfull) are unmasked for every row of the tile: all keys exist and the tile's FIRST query may see them
+    int nfull = 0;
+    if (!kvalid && !p.bias) {
+      const int qf = min(q0 + t * BQ, p.Sq - 1);
+      int last = p.Sk - 1;
+      if (p.mask_mode == NB_MASK_CAUSAL) last = min(last, qf + p.causal_off);
+      else if (p.mask_mode == NB_MASK_BLOCK_CAUSAL) last = min(last, (qf / p.frame + 1) * p.frame - 1);
+      nfull = max(0, min(n, (last + 1) / BKV));
     }
-    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[t], 0u, p.status, 222));
+    int j = 0;
+#pragma unroll 1
+    for (; j < nfull && ok; ++j) ok = block(j, std::integral_constant<int, 0>{});
+    if (!kvalid && !p.bias) {
+#pragma unroll 1
+      for (; j < n && ok; ++j) ok = block(j, std::integral_constant<int, 1>{});
+    } else {
+#pragma unroll 1
+      for (; j < n && ok; ++j) ok = block(j, std::integral_constant<int, 2>{});
+    }
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait_a(o_done_a(t), 0u, p.status, 222));
     if (!ok) *abort_flag = 1;
     if (ok && q0 + t * BQ < p.Sq) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = (m_ref > -INFINITY && l > 0.f) ? 1.f / l : 0.f;   // no allowed key at all → zeros
       __nv_bfloat16* orow = p.O + ((size_t)b * p.Sq + min(q, p.Sq - 1)) * p.ld_o + (size_t)h * HD;
 #pragma unroll
       for (int c = 0; c < HD; c += 32) {
@@ -351,7 +418,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
       }
-      if (p.lse && q < p.Sq) p.lse[((size_t)b * p.Hq + h) * p.Sq + q] = (l > 0.f) ? m_ref + log2f(l) : -INFINITY;
+      if (p.lse && q < p.Sq) p.lse[((size_t)b * p.Hq + h) * p.Sq + q] = (m_ref > -INFINITY && l > 0.f) ? m_ref + log2f(l) : -INFINITY;
     }
   }
 
@@ -370,11 +437,11 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   static_assert(smem <= 232448, "shared memory budget");
   static bool configured = false;
   if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(fa_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(FA2_KERNEL<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   dim3 grid(ceil_div(p.Sq, 2 * BQ) * p.Hq * p.B);
-  fa_fwd2_kernel<HD><<<grid, FA2_THREADS, smem, s>>>(tq, tk, tv, p);
+  FA2_KERNEL<HD><<<grid, FA2_THREADS, smem, s>>>(tq, tk, tv, p);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }
@@ -382,7 +449,7 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
 }  // namespace
 
 namespace nbattn {
-int launch_fwd_two_tile(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
+int FA2_LAUNCH(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
                         cudaStream_t s) {
   if (HD == 64) return launch_fwd2<64>(tq, tk, tv, p, s);
   return launch_fwd2<128>(tq, tk, tv, p, s);

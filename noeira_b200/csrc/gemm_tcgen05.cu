@@ -452,6 +452,223 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------ two-CTA tiles
+// The same GEMM with cta_group::2: a cluster of two CTAs (two SMs) owns one 256 x 256 output tile.  Each CTA stages 128
+// rows of A and 128 of the 256 B columns; ONE thread of the leader CTA issues tcgen05.mma.cta_group::2 (M = 256,
+// N = 256), which reads both CTAs' shared memory and writes rows [0,128) of the tile into the leader's tensor memory
+// and rows [128,256) into the peer's.  Per SM that is half the B bytes of a 128 x 256 one-CTA tile for the same
+// FLOPs, i.e. 64 instead of 96 shared-memory bytes per tensor-core clock.
+//   * both CTAs' TMA loads complete on the LEADER's full barrier (cp.async.bulk.tensor with cta_group::2 may signal a
+//     barrier of the peer; no multicast is used); the leader arms it with the bytes of both;
+//   * tcgen05.commit with a two-CTA mask frees the stage / publishes the accumulator in both CTAs;
+//   * the peer's epilogue warps release the accumulator on the leader's barrier (remote arrive).
+constexpr int BN2 = 256;       // tile columns (both CTAs together)
+constexpr int STAGES2 = 6;     // 6 x (16 KB A + 16 KB B) per CTA
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes go to a barrier given as a shared::cluster address (possibly the peer CTA's)
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far have retired
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"((unsigned short)3)
+               : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2;            // this CTA's 128 rows of A
+  constexpr uint32_t B_BYTES = (BN2 / 2) * BK * 2;     // this CTA's 128 of the 256 B columns
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 512;                  // two accumulators of 256 columns
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE_BYTES);   // used in the leader only
+  uint64_t* empty_bar = full_bar + STAGES2;
+  uint64_t* tfull_bar = empty_bar + STAGES2;
+  uint64_t* tempty_bar = tfull_bar + 2;                                             // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0 = leader
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;       // tiles of 256 x 256
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);   // four epilogue warps in each CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int mb, nb_;
+        tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
+        const int m0 = mb * (2 * BM) + (int)rank * BM;          // this CTA's rows of A
+        const int n0 = nb_ * BN2 + (int)rank * (BN2 / 2);       // this CTA's columns of B
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (*abort_flag || !mbar_wait(&empty_bar[stage], phase ^ 1u, p.status, 21)) { ok = false; *abort_flag = 1; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          const uint32_t fb = mapa_rank(smem_u32(&full_bar[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          if (!p.a_mn) {
+            tma_load_2d_pair(sa, &tmA, fb, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BM / 64; ++h) tma_load_2d_pair(sa + h * (64 * BK * 2), &tmA, fb, m0 + h * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(sb, &tmB, fb, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN2 / 128; ++h) tma_load_2d_pair(sb + h * (64 * BK * 2), &tmB, fb, n0 + h * 64, kb * BK);
+          }
+          if (++stage == STAGES2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = make_idesc(1u, 2 * BM, BN2, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (*abort_flag || !mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, p.status, 22)) { ok = false; *abort_flag = 1; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN2);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (*abort_flag || !mbar_wait(&full_bar[stage], phase, p.status, 23)) { ok = false; *abort_flag = 1; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = p.a_mn ? make_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
+                                          : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
+            const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
+                                          : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
+            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES2) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int mb, nb_;
+      tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb_);
+      if (*abort_flag || !mbar_wait(&tfull_bar[acc], acc_phase, p.status, 24)) { ok = false; *abort_flag = 1; break; }
+      tc_fence_after();
+      const int row = mb * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN2);
+      EpiPrefetch pf;
+      epilogue_prefetch16(p, row, nb_ * BN2, row_ok, pf);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN2; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr0 + (uint32_t)c0, r);
+        const EpiPrefetch cur = pf;
+        if (c0 + 16 < BN2) epilogue_prefetch16(p, row, nb_ * BN2 + c0 + 16, row_ok, pf);
+        tmem_ld_wait();
+        const int col0 = nb_ * BN2 + c0;
+        if (row_ok && col0 < p.N) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+          epilogue_store16(p, row, col0, v, cur);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_rank(smem_u32(&tempty_bar[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still read or signal it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // Second phase of a split-K GEMM: one thread per (row, 16-column chunk) of the output sums that chunk over the
 // splits in index order (deterministic) and runs the epilogue.  A separate launch, not a "last CTA reduces" tail:
 // the serial tail cost 20 us for 18 splits, and a tail that waits for sibling CTAs could deadlock against a
@@ -631,9 +848,38 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long l
   return NB_OK;
 }
 
+int launch_two_cta(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES2 * (BM * BK * 2 + (BN2 / 2) * BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(smem <= 232448, "shared memory budget of one CTA");
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  p.tiles_m = ceil_div(p.M, 2 * BM);
+  p.tiles_n = ceil_div(p.N, BN2);
+  p.num_kb = ceil_div(p.K, BK);
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  gemm2_bf16_kernel<<<2 * clusters, NUM_THREADS, smem, stream>>>(tmA, tmB, p);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int g_two_cta_mode = 0;  // 0 = by problem size, 1 = never, 2 = whenever the shape allows it
+
 }  // namespace
 
 extern "C" {
+
+// Selects between one-CTA tiles and two-CTA (cta_group::2) 256 x 256 tiles; returns the previous setting.
+int nb_gemm_two_cta_mode(int mode) {
+  const int old = g_two_cta_mode;
+  if (mode >= 0 && mode <= 2) g_two_cta_mode = mode;
+  return old;
+}
 
 // D[M,N] = epi(alpha * A·B).  A: a_mn=0 → [M,K] row-major (lda = pitch of a row of K), a_mn=1 → [K,M]
 // row-major (lda = pitch of a row of M).  B: b_mn=0 → [N,K] row-major, b_mn=1 → [K,N] row-major.
@@ -658,6 +904,14 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
     }
   }
   if (b_mn && BN < 64) BN = 64;
+  // two-CTA tiles once the 256 x 256 tiles keep about two thirds of the SM pairs busy (measured: 2048 x 2048 x 16384,
+  // 64 tiles on 74 pairs, runs 1.74x faster this way than as split-K one-CTA tiles)
+  bool two_cta = false;
+  if (bn_hint == 0 && g_two_cta_mode != 1 && M >= 256 && N >= 256 && K >= 128) {
+    const long long t2 = (long long)ceil_div(M, 2 * BM) * ceil_div(N, BN2);
+    two_cta = g_two_cta_mode == 2 || t2 * 3 >= (long long)sm_count();
+  }
+  if (two_cta) BN = BN2 / 2;   // the B box of one CTA
   CUtensorMap tmA, tmB;
   int rc;
   if (!a_mn) rc = make_tmap_bf16(&tmA, A, K, M, lda, BK, BM);
@@ -684,6 +938,7 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
     ws_bytes = workspace_bytes - NB_GEMM_WS_COUNTERS * 4;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  if (two_cta) return launch_two_cta(tmA, tmB, p, s);
   switch (BN) {
     case 256: return launch<256, 4>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
     case 128: return launch<128, 6>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);

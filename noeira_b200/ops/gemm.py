@@ -33,6 +33,15 @@ def default_workspace(device) -> torch.Tensor:
     return w
 
 
+TWO_CTA_AUTO, TWO_CTA_OFF, TWO_CTA_FORCE = 0, 1, 2
+
+
+def set_two_cta_mode(mode: int) -> int:
+    """Tile form of large GEMMs: by problem size (default), one-CTA tiles only, or 256 x 256 tiles computed by a pair
+    of CTAs (``tcgen05.mma.cta_group::2``) whenever M, N >= 256.  Returns the previous setting."""
+    return int(cuda_lib().nb_gemm_two_cta_mode(ctypes.c_int(mode)))
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor = None,
          out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor = None,
          act=None, aux: torch.Tensor = None, dact=None, bn: int = 0, n: int = None,

@@ -139,3 +139,44 @@ def test_gemm_split_k_deterministic(M, N, K, a_mn, b_mn):
     err = (outs[0][:, :N] - ref).abs().max().item()
     assert err < 2e-2 * ref.abs().max().item(), err
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.fixture
+def two_cta():
+    from noeira_b200.ops.gemm import TWO_CTA_FORCE, set_two_cta_mode
+    old = set_two_cta_mode(TWO_CTA_FORCE)
+    yield
+    set_two_cta_mode(old)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 768, 320), (1000, 520, 264), (4096, 1024, 512)])
+def test_gemm_two_cta_tiles(M, N, K, a_mn, b_mn, two_cta):
+    """256 x 256 tiles on CTA pairs (cta_group::2): all four operand layouts, ragged M / N / K edges."""
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(5)
+    a = (torch.randn(K if a_mn else M, M if a_mn else K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(K if b_mn else N, N if b_mn else K, device="cuda") * 0.5).bfloat16()
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    check_status()
+    ref = _ref(a, b, a_mn, b_mn)
+    err = (out - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+
+
+def test_gemm_two_cta_epilogue_and_repeat(two_cta):
+    """Bias + activation + bf16 store through the pair kernel; two runs are bit-identical."""
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(6)
+    M, N, K = 768, 512, 256
+    a = (torch.randn(M, K, device="cuda") * 0.2).bfloat16()
+    w = (torch.randn(K, N, device="cuda") * 0.2).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    y1 = gemm(a, w, b_mn=True, bias=bias, act="gelu")
+    y2 = gemm(a, w, b_mn=True, bias=bias, act="gelu")
+    torch.cuda.synchronize()
+    check_status()
+    ref = torch.nn.functional.gelu(a.float() @ w.float() + bias, approximate="tanh")
+    assert torch.equal(y1, y2)
+    assert (y1.float() - ref).abs().max().item() < 3e-2
