@@ -85,7 +85,7 @@ __device__ __forceinline__ float exp2_fast(float x) {
   return y;
 }
 
-// ---- packed fp32 pairs (two lanes of the FMA pipe per instruction) and a 2^x that runs on the FMA pipe
+// ---- packed fp32 pairs (two lanes of the FMA pipe per instruction)
 __device__ __forceinline__ uint64_t pack2(float a, float b) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
@@ -109,31 +109,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
-// 2^x for a pair, x in [-125, 120], without the special-function unit: x = n + f with n = round(x), f in [-1/2, 1/2];
-// 2^f by a cubic (max relative error 7.5e-5, far below the bf16 rounding of the result), 2^n by adding n to the
-// exponent field.  The softmax spends as long on MUFU exponentials as the tensor core spends on the two GEMMs of a
-// block; moving a quarter of them here takes the special-function unit off the critical path.
-__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
-  float x0, x1;
-  unpack2(x2, x0, x1);
-  x2 = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-  const uint64_t magic = pack2(12582912.f, 12582912.f);      // 1.5 * 2^23: adding it rounds to an integer
-  const uint64_t nmagic = pack2(-12582912.f, -12582912.f);
-  const uint64_t t = add2(x2, magic);
-  const uint64_t n = add2(t, nmagic);
-  const uint64_t f = fma2(n, pack2(-1.f, -1.f), x2);
-  uint64_t p = fma2(pack2(0.055171460f, 0.055171460f), f, pack2(0.24261086f, 0.24261086f));
-  p = fma2(p, f, pack2(0.69326097f, 0.69326097f));
-  p = fma2(p, f, pack2(0.99992812f, 0.99992812f));
-  float t0, t1, p0, p1;
-  unpack2(t, t0, t1);
-  unpack2(p, p0, p1);
-  // the low mantissa bits of t hold n in two's complement; shifted by 23 they land on the exponent field
-  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-  return pack2(p0, p1);
-}
-
 // last key index (inclusive) any query of [q0, q0+BQ) may attend, given the mask mode
 __device__ __forceinline__ int kv_limit(const FaParams& p, int q0) {
   const int qmax = min(q0 + BQ, p.Sq) - 1;
@@ -198,10 +173,5 @@ inline int make_tmap_bshd(CUtensorMap* tm, const void* base, int B, int S, int H
 
 // forward with two query tiles per CTA (attention_fwd2_tcgen05.cu)
 int launch_fwd_two_tile(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
-                        cudaStream_t s);int launch_fwd_two_tile_v4(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FaParams&, int, cudaStream_t);
-int launch_fwd_two_tile_v5(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FaParams&, int, cudaStream_t);
-int launch_fwd_two_tile_v6(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FaParams&, int, cudaStream_t);
-int launch_fwd_two_tile_base(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
-                             cudaStream_t s);
-
+                        cudaStream_t s);
 }  // namespace nbattn

@@ -8,43 +8,37 @@
 //   warp 0      TMA producer: Q0, Q1 once, then a ring of K tiles and a ring of V tiles (128 keys each)
 //   warp 1      MMA issuer.  Steady state per key block j:   [P0_j ready] O0 += P0_j V_j ; S0_{j+1} = Q0 K_{j+1}ᵀ
 //                                                             [P1_j ready] O1 += P1_j V_j ; S1_{j+1} = Q1 K_{j+1}ᵀ
+//               P_t(j) is published in two halves (64 keys each): the first four k-steps of P V start while the
+//               softmax still computes the second half.
 //   warps 2,3   idle (they complete the first warpgroup, which gives its registers away with setmaxnreg)
 //   warps 4..7  softmax of tile 0, warps 8..11 softmax of tile 1: thread = query row (TMEM lane), 128 scores in
 //               registers (setmaxnreg raises these two warpgroups to 208 registers), one row maximum / sum without
-//               any cross-thread traffic.
+//               any cross-thread traffic; packed fp32 arithmetic (fma / add on register pairs) and a three-input
+//               maximum keep the instruction count near 3.5 per score.  Blocks that no row of the tile has masked
+//               run a loop without any mask arithmetic; diagonal blocks (index masks) select -inf first and then
+//               share that code; key-validity / bias calls take a general loop.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1.  The probabilities P_t are written back as packed bf16 INTO the first
 // 64 columns of S_t with tcgen05.st and consumed from there as the A operand of the second GEMM, so P never passes
 // through shared memory and needs no proxy fence.  MMAs of one thread execute in issue order, so S_t(j+1) — issued
 // directly after P_t(j) V_j — cannot overwrite P_t(j) early, and the commit that publishes S_t(j+1) also covers
 // P_t(j) V_j: a softmax thread that sees S_t(j+1) may rescale O_t.  O_t stays in tensor memory and is rescaled lazily
-// (only when a row maximum grows by more than 2^8).
+// (only when a row maximum grows by more than 2^8).  CTAs of masked shapes are launched longest first.
 // Masks, GQA, Q_LEN ≠ KV_LEN, outputs: as in the one-tile kernel (attention_tcgen05.cu).
 // Reference kernels: noeira/nn/primitives/flash_attention_mma.mojo:227-521 (mma.sync, 64-query CTAs).
 #include <type_traits>
 
 #include "attention_common.cuh"
 
-#ifndef FA2_VARIANT
-#define FA2_VARIANT
-#define FA2_SPLIT_P 1
-#define FA2_DEC "88"
-#define FA2_INC "208"
-#define FA2_DEC_N 88
-#define FA2_INC_N 208
-#endif
-#define FA2_CAT_(a, b) a##b
-#define FA2_CAT(a, b) FA2_CAT_(a, b)
-#define FA2_KERNEL FA2_CAT(fa_fwd2_kernel, FA2_VARIANT)
-#define FA2_LAUNCH FA2_CAT(launch_fwd_two_tile, FA2_VARIANT)
 
 namespace {
 using namespace nb;
 using namespace nbattn;
 
 // P = 2^(s * mult - m) of half a row (scores [64·HALF, 64·HALF + 64) of 128), written as packed bf16 into tensor-memory
-// columns [s_addr + 32·HALF, +32); returns the sum of that half.  Arguments are formed as packed pairs; pairs 3 and 7 of
-// each group of eight (a quarter of the elements) take the polynomial on the FMA pipe, the rest the special-function
-// unit.
+// columns [s_addr + 32·HALF, +32); returns the sum of that half.  Arguments and the running sum are formed as packed
+// fp32 pairs (one FMA-pipe instruction per two scores).  All exponentials run on the special-function unit: moving a
+// share of them to a polynomial on the FMA pipe was measured (1/8, 1/4 and 1/2 of the elements, packed and scalar
+// forms) and lost to the extra instructions and registers it costs a thread that already holds 128 scores.
 template <int HALF>
 __device__ __forceinline__ float exp_store(const float (&s)[128], float mult, float m_use, uint32_t s_addr) {
   uint64_t lsum2 = pack2(0.f, 0.f);
@@ -56,15 +50,10 @@ __device__ __forceinline__ float exp_store(const float (&s)[128], float mult, fl
     for (int u = 0; u < 8; ++u) {
       uint64_t x2 = fma2(pack2(s[c * 16 + 2 * u], s[c * 16 + 2 * u + 1]), mult2, negm2);
       float e0, e1;
-      if ((u & 3) == 3) {
-        x2 = exp2_poly2(x2);
-        unpack2(x2, e0, e1);
-      } else {
-        unpack2(x2, e0, e1);
-        e0 = exp2_fast(e0);
-        e1 = exp2_fast(e1);
-        x2 = pack2(e0, e1);
-      }
+      unpack2(x2, e0, e1);
+      e0 = exp2_fast(e0);
+      e1 = exp2_fast(e1);
+      x2 = pack2(e0, e1);
       lsum2 = add2(lsum2, x2);
       __nv_bfloat162 hv = __floats2bfloat162_rn(e0, e1);
       pk[u] = *reinterpret_cast<uint32_t*>(&hv);
@@ -82,11 +71,11 @@ __device__ __forceinline__ float exp_store(const float (&s)[128], float mult, fl
 constexpr int FA2_THREADS = 384;  // three warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 // Register budget: the CTA is launched with 384 x 168 registers and setmaxnreg only moves registers inside that
 // allocation (an increase BLOCKS until the CTA's pool has them), so 128 x 88 + 256 x 208 must not exceed 384 x 168.
-static_assert(128 * FA2_DEC_N + 256 * FA2_INC_N <= FA2_THREADS * 168, "setmaxnreg budget");
+static_assert(128 * 88 + 256 * 208 <= FA2_THREADS * 168, "setmaxnreg budget");
 
 template <int HD>
 __global__ void __launch_bounds__(FA2_THREADS, 1)
-FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const FaParams p) {
   constexpr int NSUB = HD / 64;                 // 64-wide swizzle atoms per row
   constexpr int KS = (HD == 64) ? 4 : 2;        // K ring and V ring depth
@@ -180,7 +169,7 @@ FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " FA2_DEC ";");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     if (elect_one()) {
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
@@ -207,7 +196,7 @@ FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " FA2_DEC ";");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     if (elect_one()) {
       const uint32_t idesc_s = make_idesc(1u, BQ, BKV, 0u, 0u);  // S = Q Kᵀ : both K-major
       const uint32_t idesc_o = make_idesc(1u, BQ, HD, 0u, 1u);   // O += P V : P from tensor memory, V MN-major
@@ -236,14 +225,14 @@ FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const int st = j % KS;
         const bool first = (t == 0) || !(j < nkb[0]);
         const bool last = (t == 1) || !(j < nkb[1]);
-        if (*abort_flag || !mbar_wait_a(FA2_SPLIT_P ? p_lo_a(t) : p_full_a(t), (uint32_t)j & 1u, p.status, 214)) return false;
+        if (*abort_flag || !mbar_wait_a(p_lo_a(t), (uint32_t)j & 1u, p.status, 214)) return false;
         if (first && !mbar_wait_a(v_full_a(st), (uint32_t)(j / KS) & 1u, p.status, 213)) return false;
         tc_fence_after();
         const uint64_t bdesc0 = make_smem_desc(aV + st * KV_BYTES, BKV * 128, 1024, 2);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           // the second half of the keys waits for the second half of P
-          if (FA2_SPLIT_P && k == BKV / 32) {
+          if (k == BKV / 32) {
             if (!mbar_wait_a(p_full_a(t), (uint32_t)j & 1u, p.status, 212)) return false;
             tc_fence_after();
           }
@@ -267,10 +256,10 @@ FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       if (!ok) *abort_flag = 1;
     }
   } else if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 " FA2_DEC ";");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
   } else {
     // ---------------------------------------------------------------- softmax / epilogue: one thread per query row
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 " FA2_INC ";");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;          // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;
@@ -350,10 +339,8 @@ FA2_KERNEL(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
       }
       // The first 64 keys of P are published on their own so that the tensor core starts P V half a softmax earlier.
-      // (A masked score reaches the polynomial as -inf and leaves it as 2^-125 instead of 0: 38 orders of magnitude
-      // below the row maximum; a row without any allowed key is recognised by its maximum, not by its sum.)
       float lblk = exp_store<0>(s, mult, m_use, s_addr);
-      if (FA2_SPLIT_P) {
+      {
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -437,11 +424,11 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   static_assert(smem <= 232448, "shared memory budget");
   static bool configured = false;
   if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(FA2_KERNEL<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(fa_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   dim3 grid(ceil_div(p.Sq, 2 * BQ) * p.Hq * p.B);
-  FA2_KERNEL<HD><<<grid, FA2_THREADS, smem, s>>>(tq, tk, tv, p);
+  fa_fwd2_kernel<HD><<<grid, FA2_THREADS, smem, s>>>(tq, tk, tv, p);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }
@@ -449,7 +436,7 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
 }  // namespace
 
 namespace nbattn {
-int FA2_LAUNCH(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
+int launch_fwd_two_tile(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
                         cudaStream_t s) {
   if (HD == 64) return launch_fwd2<64>(tq, tk, tv, p, s);
   return launch_fwd2<128>(tq, tk, tv, p, s);

@@ -346,7 +346,7 @@ extern "C" {
 // Selects the forward kernel (tests and benchmarks compare the two forms); returns the previous setting.
 int nb_flash_attn_fwd_mode(int mode) {
   const int old = g_fwd_mode;
-  if (mode >= 0 && mode <= 6) g_fwd_mode = mode;
+  if (mode >= 0 && mode <= 2) g_fwd_mode = mode;
   return old;
 }
 
@@ -379,10 +379,6 @@ int nb_flash_attn_fwd(const void* Q, const void* K, const void* V, void* O, floa
   cudaStream_t s = (cudaStream_t)stream;
   // two tiles per CTA pay once every SM has a CTA of 256 queries; small problems keep the finer grid
   const bool two = g_fwd_mode == 2 || (g_fwd_mode == 0 && Sq > BQ && (long long)ceil_div(Sq, 2 * BQ) * Hq * B >= 148);
-  if (g_fwd_mode == 3) return launch_fwd_two_tile_base(tq, tk, tv, p, HD, s);
-  if (g_fwd_mode == 4) return launch_fwd_two_tile_v4(tq, tk, tv, p, HD, s);
-  if (g_fwd_mode == 5) return launch_fwd_two_tile_v5(tq, tk, tv, p, HD, s);
-  if (g_fwd_mode == 6) return launch_fwd_two_tile_v6(tq, tk, tv, p, HD, s);
   if (two) return launch_fwd_two_tile(tq, tk, tv, p, HD, s);
   if (HD == 64) return launch_fwd<64>(tq, tk, tv, p, s);
   return launch_fwd<128>(tq, tk, tv, p, s);

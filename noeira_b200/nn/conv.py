@@ -148,6 +148,8 @@ class Conv2D(Module):
                 colsum_into(d2, self.bias.grad_storage, self.oc)
         if not self.need_input_grad:
             return None
+        if self._implicit_dgrad_ok(W):
+            return self._implicit_dgrad(d2, B, H, W, OH, OW)
         K = self.k * self.k * self.icp
         dcol = ops.gemm(d2, self.weight.shadow[:, : self.oc])           # [M, K]
         if self.k == 1 and self.stride == 1 and self.pad == 0:
@@ -156,6 +158,29 @@ class Conv2D(Module):
         check(cuda_lib().nb_col2im(ptr(dcol), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, self.icp, self.k, self.k, self.stride,
                                                                                self.pad, OH, OW, K)), stream_ptr()), "col2im")
         return dx
+
+    def _implicit_dgrad_ok(self, W):
+        """Stride-1 layers with at least 64 output channels: the input gradient is itself a stride-1 convolution of
+        dy (taps mirrored, channel roles swapped), which the implicit-GEMM kernel computes without the 9x larger
+        patch-gradient matrix and the col2im pass over it."""
+        if self.stride != 1 or self.k == 1 or self.oc % 64 or not self.implicit_gemm or 2 * self.pad > self.k - 1 + self.k - 1:
+            return False
+        bw = 1
+        while bw < 128 and W % (bw * 2) == 0:
+            bw *= 2
+        return bw >= 8
+
+    def _implicit_dgrad(self, d2, B, H, W, OH, OW):
+        k, oc, icp = self.k, self.oc, self.icp
+        # W'[(kh', kw', oc), ic] = W[(k-1-kh', k-1-kw', ic), oc]
+        wt = self.weight.shadow[:, :oc].reshape(k, k, icp, oc).flip(0, 1).permute(0, 1, 3, 2).contiguous().view(k * k * oc, icp)
+        dyc = d2 if d2.is_contiguous() else d2.contiguous()
+        dx = torch.empty(B * H * W, icp, device=d2.device, dtype=torch.bfloat16)
+        from ..ops.status import device_status
+        check(cuda_lib().nb_conv_implicit_fwd(ptr(dyc), ptr(wt), ptr(dx), *(ctypes.c_int(v) for v in (
+            B, OH, OW, oc, icp, k, k, k - 1 - self.pad, wt.stride(0), dx.stride(0))), None, ctypes.c_int(0), None,
+            ctypes.c_int(0), ptr(device_status(d2.device)), stream_ptr()), "conv_implicit_dgrad")
+        return dx.view(B, H, W, icp)
 
     def _release(self):
         self._col = self._y = self._xin = None

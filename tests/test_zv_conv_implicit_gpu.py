@@ -34,3 +34,23 @@ def test_implicit_matches_patch_matrix(ic, oc, k, pad, H, W):
     # the backward of both runs through the patch matrix; only ReLU masks of outputs that differ in sign can differ
     cos = lambda u, v: torch.nn.functional.cosine_similarity(u.float().flatten(), v.float().flatten(), dim=0).item()
     assert cos(da, db) > 0.999 and cos(a.weight.grad, b.weight.grad) > 0.999 and cos(a.bias.grad, b.bias.grad) > 0.999
+
+
+@pytest.mark.parametrize("ic,oc,k,pad,H,W", [(64, 64, 3, 1, 24, 32), (128, 64, 3, 1, 15, 48), (64, 128, 3, 0, 20, 40)])
+def test_implicit_input_gradient_matches_fp32_reference(ic, oc, k, pad, H, W):
+    """dx of a stride-1 layer = a stride-1 convolution of dy with mirrored taps, run by the implicit-GEMM kernel."""
+    from noeira_b200 import nn
+    from noeira_b200.ops import check_status
+    nn.manual_seed(7)
+    c = nn.Conv2D(ic, oc, k, 1, pad, bias=False, relu=False).to("cuda")
+    x = (torch.randn(2, H, W, ic, device="cuda") * 0.5).bfloat16()
+    assert c._implicit_dgrad_ok(W)
+    y = c.forward(x)
+    dy = (torch.randn_like(y.float()) * 0.1).bfloat16()
+    dx = c.vjp(dy)
+    torch.cuda.synchronize()
+    check_status()
+    w = c.weight.shadow.float().view(k, k, ic, oc).permute(3, 2, 0, 1)
+    ref = torch.nn.grad.conv2d_input((2, ic, H, W), w, dy.float().permute(0, 3, 1, 2), 1, pad).permute(0, 2, 3, 1)
+    err = (dx.float() - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
