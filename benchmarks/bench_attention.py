@@ -36,11 +36,14 @@ def main():
     ap.add_argument("--no-sdpa", action="store_true", help="skip the library comparison")
     ap.add_argument("--fwd-mode", type=int, default=0, help="0 = by size, 1 = one query tile per CTA, 2 = two tiles")
     ap.add_argument("--no-bwd", action="store_true", help="forward only")
+    ap.add_argument("--bwd-mode", type=int, default=0, help="0 = second-generation backward kernels, 1 = first generation")
     args = ap.parse_args()
     from noeira_b200.ops import check_status
     from noeira_b200.ops.attention import flash_attention_backward, flash_attention_forward
     from noeira_b200.ops.attention import set_forward_mode
     set_forward_mode(args.fwd_mode)
+    from noeira_b200.ops.attention import set_backward_mode
+    set_backward_mode(args.bwd_mode)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     shapes = [  # B, S, Hq, Hkv, D, mask, frame
         (8, 1024, 12, 12, 64, None, 0),          # ViT tower

@@ -516,9 +516,18 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   return NB_OK;
 }
 
+int g_bwd_mode = 0;  // 0 = second-generation kernels, 1 = first generation (kept for comparison)
+
 }  // namespace
 
 extern "C" {
+
+// Selects the backward kernels; returns the previous setting.
+int nb_flash_attn_bwd_mode(int mode) {
+  const int old = g_bwd_mode;
+  if (mode >= 0 && mode <= 1) g_bwd_mode = mode;
+  return old;
+}
 
 // Strides in elements (batch, token, head); HD stride 1 everywhere.  delta: scratch [B,Hq,Sq] fp32 supplied by the
 // caller.  dQ/dK/dV are written (not accumulated) as [B,S,H,HD] with token pitches dq_ss / dk_ss / dv_ss.
@@ -558,6 +567,7 @@ int nb_flash_attn_bwd(const void* Q, const void* K, const void* V, const void* O
   p.delta = delta;
   p.dQ = (__nv_bfloat16*)dQ; p.dK = (__nv_bfloat16*)dK; p.dV = (__nv_bfloat16*)dV;
   p.ld_dq = (int)dq_ss; p.ld_dk = (int)dk_ss; p.ld_dv = (int)dv_ss;
+  if (g_bwd_mode == 0) return launch_bwd_gen2(tq, tk, tv, tdo, p, HD, s);
   if (HD == 64) return launch_bwd<64>(tq, tk, tv, tdo, p, s);
   return launch_bwd<128>(tq, tk, tv, tdo, p, s);
 }

@@ -173,5 +173,8 @@ inline int make_tmap_bshd(CUtensorMap* tm, const void* base, int B, int S, int H
 
 // forward with two query tiles per CTA (attention_fwd2_tcgen05.cu)
 int launch_fwd_two_tile(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int HD,
-                        cudaStream_t s);
+                        cudaStream_t s);// backward, second generation (attention_bwd2_tcgen05.cu)
+int launch_bwd_gen2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                    const FaParams& p, int HD, cudaStream_t s);
+
 }  // namespace nbattn

@@ -52,6 +52,12 @@ def set_forward_mode(mode: int) -> int:
     return int(cuda_lib().nb_flash_attn_fwd_mode(ctypes.c_int(mode)))
 
 
+def set_backward_mode(mode: int) -> int:
+    """Backward kernels: 0 = second generation (P / dS in tensor memory, transposed tiles for dK / dV), 1 = first
+    generation.  Returns the previous setting."""
+    return int(cuda_lib().nb_flash_attn_bwd_mode(ctypes.c_int(mode)))
+
+
 def flash_attention_forward(q, k, v, scale=None, mask=None, frame=0, causal_off=0, key_valid=None, bias=None,
                             out=None, want_lse=True):
     """q [B,Sq,Hq,D], k/v [B,Sk,Hkv,D] bf16 (any batch/token/head strides, unit stride on D; views into a

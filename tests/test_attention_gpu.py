@@ -72,8 +72,18 @@ BWD_CASES = [
 ]
 
 
-@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,mask,frame", BWD_CASES)
-def test_flash_backward(B, Sq, Sk, Hq, Hkv, D, mask, frame):
+@pytest.fixture(params=[0, 1], ids=["gen2", "gen1"])
+def bwd_mode(request):
+    from noeira_b200.ops.attention import set_backward_mode
+    old = set_backward_mode(request.param)
+    yield request.param
+    set_backward_mode(old)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,mask,frame", BWD_CASES + [(1, 1000, 1000, 2, 1, 128, "causal", 0),
+                                                                      (1, 640, 900, 4, 2, 64, None, 0),
+                                                                      (1, 1024, 1024, 2, 2, 128, "block_causal", 256)])
+def test_flash_backward(B, Sq, Sk, Hq, Hkv, D, mask, frame, bwd_mode):
     from noeira_b200.ops import check_status
     from noeira_b200.ops.attention import attention_reference, flash_attention_backward, flash_attention_forward
     torch.manual_seed(0)
