@@ -252,9 +252,38 @@ class FusedZeroSync:
         return a.numel * (4 + 4 + 2) + 2 * st["per"] * 4
 
 
+class OverlapGradSync:
+    """Gradient reduction overlapped with the backward pass: buckets of the gradient arena are all-reduced (NCCL, on
+    the library's stream) as soon as the backward has finished their units, then the arena optimizer runs.  The
+    trainer hands over its model with ``attach_model`` so that the units' ``vjp`` can be wrapped."""
+
+    def __init__(self, world, rank, bucket_bytes: int = 8 << 20):
+        self.world, self.rank, self.bucket_bytes = world, rank, bucket_bytes
+        self.st = None
+        self.opt = None
+
+    def attach(self, *opts):
+        assert len(opts) == 1, "one optimizer (one arena) per overlapped sync"
+        self.opt = opts[0]
+
+    def attach_model(self, model):
+        from .fibers import DistComm
+        from .strategy import OverlappedDataParallel
+        self.st = OverlappedDataParallel(self.opt, DistComm(), model=model, bucket_bytes=self.bucket_bytes)
+
+    def reduce_and_step(self, opt):
+        assert self.st is not None, "attach_model(model) first"
+        self.st.reduce_grads()
+        if opt.max_grad_norm > 0:
+            opt.clip()
+        opt.step(zero_grad=True)
+
+
 def make_grad_sync(kind: str, world: int, rank: int, local_rank: int):
     if kind == "nccl":
         return NcclGradSync(world, rank)
+    if kind == "overlap":
+        return OverlapGradSync(world, rank)
     if kind == "zero":
         return FusedZeroSync(world, rank, local_rank)
     return FusedGradSync(world, rank, local_rank)

@@ -172,6 +172,11 @@ class DistComm:
     def all_reduce(self, t):
         self.dist.all_reduce(t, group=self.group)
 
+    def all_reduce_async(self, t):
+        """Enqueues the reduction and returns a handle with ``wait()``; on NCCL it runs on the library's own stream,
+        ordered after the work already enqueued on the caller's stream, so later kernels of the caller overlap it."""
+        return self.dist.all_reduce(t, group=self.group, async_op=True)
+
     def reduce_scatter(self, out, inp):
         if self.dist.get_backend(self.group) == "gloo":
             tmp = inp.clone()

@@ -97,6 +97,89 @@ class DataParallel:
         return _nbytes(a.val) + _nbytes(a.grd) + _nbytes(a.m) + _nbytes(a.v)
 
 
+class OverlappedDataParallel(DataParallel):
+    """DDP whose gradient reduction overlaps the backward pass: the arena is cut into buckets of consecutive model
+    units (walking from the end of the arena, the order in which the backward finishes gradients); every unit's
+    ``vjp`` is wrapped, and as soon as the backward has passed the first unit of a bucket that bucket's slice of the
+    gradient arena is reduced — asynchronously where the communicator can (NCCL: on its own stream, behind the
+    kernels already enqueued, while the remaining backward runs).  ``reduce_grads`` only reduces what is left and
+    waits.  Bit-identical to ``DataParallel``: the same elements are summed over the same ranks in the same order.
+    Reference: GradReady / GradMarks + bucketed DDP (noeira/nn/distributed/grad_marks.mojo:75-379,
+    noeira/nn/distributed/buckets.mojo, noeira/nn/distributed/data_parallel.mojo)."""
+    name = "ddp_overlap"
+
+    def __init__(self, opt: Optimizer, comm, model=None, bucket_bytes: int = 8 << 20):
+        super().__init__(opt, comm, model)
+        from .buckets import BucketedReducer, GradMarks, plan_buckets
+        a = opt.arena
+        units, ranges = self._units(a, model)
+        gm = GradMarks()
+        for i, (lo, hi) in enumerate(ranges):
+            gm.add(f"unit{i}", lo, hi)
+        self.buckets = plan_buckets(gm.marks, max(bucket_bytes // 4, 1))
+        self._pending = []
+        self.reducer = BucketedReducer(self.buckets, self._reduce_range)
+        self.launched_during_backward = 0
+        self._in_backward = False
+        self.hooked = bool(units)
+        for i, child in enumerate(units):
+            self._hook(child, f"unit{i}")
+
+    @staticmethod
+    def _units(a, model):
+        """The model's direct children that own parameters, with their arena ranges — when the arena order is the
+        children's registration order (it is for every model built through ``add_child``); otherwise one unit."""
+        kids = []
+        if model is not None:
+            kids = list(getattr(model, "mods", None) or getattr(model, "_children", {}).values())
+            kids = [c for c in kids if list(c.params())]
+        ents, out, i = a.entries, [], 0
+        for child in kids:
+            ids = {id(p) for p in child.params()}
+            lo = ents[i][2] if i < len(ents) else a.numel
+            n0 = i
+            while i < len(ents) and id(ents[i][1]) in ids:
+                i += 1
+            if i == n0:
+                return [], [(0, a.numel)]
+            out.append((lo, ents[i][2] if i < len(ents) else a.numel))
+        if not kids or i != len(ents):
+            return [], [(0, a.numel)]
+        return kids, out
+
+    def _reduce_range(self, begin: int, end: int):
+        view = self.opt.arena.grd[begin:end]
+        if self._in_backward:
+            self.launched_during_backward += 1
+        if hasattr(self.comm, "all_reduce_async"):
+            self._pending.append(self.comm.all_reduce_async(view))
+        else:
+            self.comm.all_reduce(view)
+
+    def _hook(self, child, name):
+        vjp = child.vjp
+
+        def backward(*args, **kw):
+            self._in_backward = True
+            try:
+                out = vjp(*args, **kw)
+            finally:
+                self._in_backward = False
+            self._in_backward = True
+            self.reducer.on_unit_done(name)      # this unit's gradients are complete: its bucket may go
+            self._in_backward = False
+            return out
+
+        child.vjp = backward
+
+    def reduce_grads(self):
+        self.reducer.finish()
+        for w in self._pending:
+            w.wait()
+        self._pending.clear()
+        self.opt.arena.grd.mul_(1.0 / self.world)
+
+
 class _ShardState:
     """Shard-size Adam state of one contiguous arena range ``[lo, lo + per·world)`` split over the ranks."""
 
@@ -377,4 +460,4 @@ class Zero3(DataParallel):
         return sum(_nbytes(u["full_v"]) + _nbytes(u["full_g"]) + _nbytes(u["val_shard"]) + u["state"].nbytes() for u in self.units)
 
 
-STRATEGIES = {"ddp": DataParallel, "zero1": Zero1, "zero2": Zero2, "zero3": Zero3}
+STRATEGIES = {"ddp": DataParallel, "ddp_overlap": OverlappedDataParallel, "zero1": Zero1, "zero2": Zero2, "zero3": Zero3}

@@ -104,6 +104,8 @@ class AutoregressiveTrainer:
         self.grad_sync = grad_sync
         if grad_sync is not None:
             grad_sync.attach(self.opt)
+            if hasattr(grad_sync, "attach_model"):
+                grad_sync.attach_model(model)        # overlapped reduction: the units' vjp launch their buckets
         self.schedule = schedulers.WarmupCosine(lr, warmup, total_steps, lr * min_lr_frac)
         self.loss_acc = torch.zeros(1, device=self.device)
         # every rank draws the GLOBAL batch of window starts from the same stream and keeps its slice, so that N ranks

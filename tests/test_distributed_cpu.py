@@ -129,13 +129,15 @@ def test_collectives_are_rank_ordered_and_deterministic():
     assert torch.equal(r[2][2], torch.tensor([0., 0, 1, 1, 2, 2, 3, 3]))
 
 
-def test_gloo_processes_match_simulator():
-    """Two real processes over gloo reproduce the simulator's DDP result bit for bit."""
+@pytest.mark.parametrize("strategy", ["ddp", "ddp_overlap"])
+def test_gloo_processes_match_simulator(strategy):
+    """Two real processes over gloo reproduce the simulator's DDP result bit for bit (also with the asynchronous,
+    bucketed reduction of the overlapped strategy)."""
     from noeira_b200.parallel.fibers import run_ranks
     sim = run_ranks(2, lambda c: _train(c, "ddp"))[0][0]
     import tempfile
     with tempfile.TemporaryDirectory() as d:
-        env = dict(os.environ, OUT=os.path.join(d, "v"), OMP_NUM_THREADS="1")
+        env = dict(os.environ, OUT=os.path.join(d, "v"), OMP_NUM_THREADS="1", STRATEGY=strategy)
         r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                             "--master-addr", "127.0.0.1", "--master-port", "29731",
                             os.path.join(ROOT, "tests", "mp", "gloo_worker.py")], env=env, capture_output=True, text=True,
@@ -177,3 +179,38 @@ def test_zero3_units_are_gathered_only_around_their_own_forward_and_backward():
         assert live_during == [[True, False, False], [False, True, False], [False, False, True]]
         assert idle == [(False, False)] * 3
         assert nbytes <= 4 * 4 * numel / 2 * 1.1          # values, gradients and both moments: a shard of each
+
+
+def test_overlapped_ddp_reduces_buckets_during_backward_and_matches_ddp():
+    """The bucketed reducer is driven by the model's own backward: with a small bucket size every unit is its own bucket,
+    the buckets of the later units go out while the backward is still running, and the result is bit-identical to the
+    reduce-after-backward strategy."""
+    from noeira_b200 import nn
+    from noeira_b200.parallel.fibers import run_ranks
+    from noeira_b200.parallel.strategy import OverlappedDataParallel
+
+    def body(comm):
+        net = _net()
+        opt = nn.AdamW(net.named_params(), lr=1e-2, weight_decay=0.01)
+        st = OverlappedDataParallel(opt, comm, model=net, bucket_bytes=64)
+        st.sync_params()
+        g = torch.Generator().manual_seed(0)
+        per = 16 // comm.world
+        for _ in range(4):
+            x = torch.randn(16, 12, generator=g)
+            y = torch.randn(16, 3, generator=g)
+            xs, ys = x[comm.rank * per:(comm.rank + 1) * per], y[comm.rank * per:(comm.rank + 1) * per]
+            out = net.forward(xs)
+            net.vjp(2.0 * (out - ys) / per)
+            st.reduce_grads()
+            st.step()
+        return st.full_values(), len(st.buckets), st.launched_during_backward, list(st.reducer.order)
+
+    out = run_ranks(2, body)
+    ref = run_ranks(2, lambda c: _train(c, "ddp"))
+    assert torch.equal(out[0][0], ref[0][0]) and torch.equal(out[0][0], out[1][0])
+    vals, nb, during, order = out[0]
+    assert nb == 3 and during == 4 * 3                       # every bucket of every step left from inside the backward
+    assert order[0][0] > order[1][0] > order[2][0]           # last unit of the arena first
+    default = run_ranks(2, lambda c: _train(c, "ddp_overlap"))
+    assert torch.equal(default[0][0], ref[0][0])             # one 8 MB bucket: reduced by reduce_grads, same values
