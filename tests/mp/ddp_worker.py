@@ -53,6 +53,7 @@ def main():
         ok = ok and same and err < (2e-4 if clip > 0 else 2e-5) and gz == 0.0
     ok = push_case(rank, world, local) and ok
     ok = zero_case(rank, world, local) and ok
+    ok = overlap_case(rank, world, local) and ok
     dist.barrier()
     if rank == 0:
         print("DDP_WORKER_OK" if ok else "DDP_WORKER_FAIL")
@@ -160,6 +161,41 @@ def zero_case(rank, world, local):
     # lr = 1e-2: the library's ring order and this kernel's rank order sum the gradients differently, and Adam turns
     # a last-bit difference of a near-zero gradient into a difference of a fraction of lr
     return same and err < 2e-4 and sherr < 2e-2 and shard_ok and gz == 0.0
+
+
+def overlap_case(rank, world, local):
+    """A small GPT trained by the autoregressive trainer with the gradient reduction overlapped with the backward
+    (bucketed NCCL all-reduces launched from the units' vjp) against the reduce-after-backward NCCL baseline: identical
+    replicas, matching losses, and buckets that really left during the backward."""
+    from noeira_b200.models.gpt import GPT
+    from noeira_b200.ops import check_status
+    from noeira_b200.parallel.ddp import NcclGradSync, OverlapGradSync
+    from noeira_b200.training.trainer import AutoregressiveTrainer
+    torch.manual_seed(3)
+    tokens = torch.randint(0, 96, (20000,), device="cuda")
+    losses, vals, during = [], [], 0
+    for kind in ("overlap", "nccl"):
+        model = GPT(vocab=96, seq=64, dim=128, layers=3, heads=4, seed=5).to("cuda")
+        sync = OverlapGradSync(world, rank, bucket_bytes=256 << 10) if kind == "overlap" else NcclGradSync(world, rank)
+        tr = AutoregressiveTrainer(model, tokens, batch=8, seq=64, lr=1e-3, warmup=2, total_steps=20, seed=9, grad_sync=sync,
+                                   rank=rank, world=world)
+        ls = [float(tr.train_step()) for _ in range(6)]
+        torch.cuda.synchronize()
+        check_status()
+        losses.append(ls)
+        vals.append(tr.opt.arena.val.clone())
+        if kind == "overlap":
+            during, nb = sync.st.launched_during_backward, len(sync.st.buckets)
+    mine = vals[0]
+    lst = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(lst, mine)
+    same = all(torch.equal(lst[0], t) for t in lst)
+    err = (vals[0] - vals[1]).abs().max().item()
+    dl = max(abs(a - b) for a, b in zip(*losses))
+    if rank == 0:
+        print(f"overlap: buckets={nb} launched_during_backward={during} replicas_equal={same} max|overlap-nccl|={err:.3e} "
+              f"max loss diff={dl:.3e}")
+    return same and nb >= 3 and during >= 6 * (nb - 1) and err < 1e-3 and dl < 5e-3
 
 
 if __name__ == "__main__":
