@@ -241,6 +241,24 @@ __device__ __forceinline__ void forward_kinematics(const PhysParams& P, const Mo
   }
 }
 
+// Stage timers of the diagnostic (bounds-checked) build: with a debug buffer, environment 0 adds the clocks each stage
+// of its first substep took to dbg[PHYS_TIMER_BASE + stage].  The normal build compiles them away.
+#define PHYS_TIMER_BASE 240
+#if defined(NB_BOUNDS) && NB_BOUNDS
+#define PHYS_STAGE_BEGIN() long long tstage_ = clock64()
+#define PHYS_STAGE(i)                                             \
+  do {                                                            \
+    if (dbg && lane == 0) {                                       \
+      const long long t_ = clock64();                             \
+      dbg[PHYS_TIMER_BASE + (i)] += (float)(t_ - tstage_);        \
+      tstage_ = t_;                                               \
+    }                                                             \
+  } while (0)
+#else
+#define PHYS_STAGE_BEGIN() do {} while (0)
+#define PHYS_STAGE(i) do {} while (0)
+#endif
+
 // One dynamics substep for the env owned by this warp.  qpos/qvel/ctrl live in registers of
 // lane d (< nv); everything else in the warp's shared scratch.
 __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m, WarpScratch& w, float& qpos,
@@ -253,9 +271,11 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   qpos_sh[lane] = qpos;
   qvel_sh[lane] = qvel;
   __syncwarp();
+  PHYS_STAGE_BEGIN();
 
   forward_kinematics(P, m, w, qpos_sh, lane);
   const V3 c = ld3(w.xpos);  // reference point: origin of body 0
+  PHYS_STAGE(0);
 
   // ---- motion axes about c (lane = dof) and body inertias about c (lane = body)
   if (lane < nv) {
@@ -307,6 +327,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   }
   __syncwarp();
 
+  PHYS_STAGE(1);
   // ---- body velocity, bias acceleration and the resulting spatial force (lane = body)
   if (lane < nbody) {
     V3 vw = v3(0, 0, 0), vv = v3(0, 0, 0);            // cumulative spatial velocity
@@ -334,6 +355,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   }
   __syncwarp();
 
+  PHYS_STAGE(2);
   // ---- composite inertias (lane = body): Ic_b = Σ_{b' : b ∈ anc(b')} I_b'
   if (lane < nbody) {
     float acc[10];
@@ -348,6 +370,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
 #pragma unroll
     for (int k = 0; k < 10; ++k) w.Ic[lane * 10 + k] = acc[k];
   }
+  PHYS_STAGE(3);
   // ---- bias force per dof (lane = dof): S_d · Σ_{b in subtree(body(d))} f_b
   float bias = 0.f;
   if (lane < nv) {
@@ -362,6 +385,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   }
   __syncwarp();
 
+  PHYS_STAGE(4);
   // ---- CRBA (lane = dof i): M[i][j] = S_j · (Ic_body(i) S_i) for ancestor dofs j <= i
   if (lane < nv) {
     const int i = lane, bi = m.dof_body[i];
@@ -384,6 +408,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   }
   __syncwarp();
 
+  PHYS_STAGE(5);
   // ---- in-place Cholesky M̂ = L Lᵀ (lower).  Column k: lane r > k scales, then trailing update.
   for (int k = 0; k < nv; ++k) {
     float dkk = w.M[k * nvp + k];
@@ -400,6 +425,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
     __syncwarp();
   }
 
+  PHYS_STAGE(6);
   // ---- constraint detection.  Slots: [0, nlimit) joint limits, [nlimit, nlimit+ncs) contact spheres.
   // Rows are allocated by ballot compaction: first all unilateral rows (limit / normal), then two
   // tangent rows per contact while space remains.
@@ -473,6 +499,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   }
   const V3 t2 = cross(pn, t1);
 
+  PHYS_STAGE(7);
   // ---- per row (lane = row): Jacobian row, B = M̂⁻¹ Jᵀ, diag, aref, R.  Row `nrow` (virtual)
   // is the smooth solve qacc = M̂⁻¹ tau, handled by the same triangular solves.
   const float k_s = 1.f / (P.solimp_dmax * P.solimp_dmax * P.solref_tc * P.solref_tc * P.solref_dr * P.solref_dr);
@@ -558,6 +585,7 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
     if (lane == 0) dbg[nv * nv + 3 * nv] = (float)nrow;
   }
 
+  PHYS_STAGE(8);
   // ---- projected Gauss-Seidel.  Dual form, lane = row: each lane keeps c_r = J_r·qacc − aref_r (without
   // the R_r λ_r term) in a register; when row s moves by Δλ every lane adds A_rs·Δλ with
   // A = J M̂⁻¹ Jᵀ, so a row update costs two shuffles instead of a cross-lane dot product.  The iterates
@@ -653,10 +681,12 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
       }
     }
   }
+  PHYS_STAGE(9);
   // store multipliers for the next substep
   for (int r = lane; r < nrow; r += 32) warm[w.rowi[r * 4 + 3]] = w.row[r * 4 + 3];
   if (dbg && lane < nv) dbg[nv * nv + 2 * nv + lane] = qacc;
 
+  PHYS_STAGE(10);
   // ---- semi-implicit Euler
   if (lane < nv) {
     if (!isfinite(qacc)) qacc = 0.f;

@@ -1,2 +1,3 @@
 from .batched_env import BatchedEnv, HalfCheetahEnv, HopperEnv, Physics3dBatchedEnv, PlanarChainEnv  # noqa: F401
 from .classic import CartPoleEnv, MountainCarContinuousEnv, PendulumEnv  # noqa: F401
+from .lunar_lander import LunarLanderEnv  # noqa: F401
