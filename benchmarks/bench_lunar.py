@@ -19,7 +19,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
-    from noeira_b200.agents.ppo import PPOAgent, PPOConfig
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
     from noeira_b200.envs.lunar_lander import LunarLanderEnv
     env = LunarLanderEnv(args.envs, device="cuda", seed=0)
     env.reset_batch()
@@ -37,7 +37,7 @@ def main():
     print(json.dumps({"what": "env step only", "envs": args.envs, "ms_per_batched_step": round(ms, 4),
                       "env_steps_per_s": round(args.envs / ms * 1e3)}))
     env = LunarLanderEnv(args.envs, device="cuda", seed=0)
-    agent = PPOAgent(env, PPOConfig(n_envs=args.envs, rollout_len=32, n_epochs=4, n_minibatches=8))
+    agent = PPOTrainer(env, PPOConfig(n_envs=args.envs, rollout_len=32, n_epochs=4, n_minibatches=8))
     for _ in range(3):
         agent.train_iteration(read_metrics=False)
     torch.cuda.synchronize()

@@ -189,56 +189,95 @@ __device__ __forceinline__ ModelView view(const int* im, const float* fm, const 
 }
 
 // ------------------------------------------------------------------------------------------
-// Forward kinematics, level synchronous.  Lane b owns body b.  On exit xpos/xquat/xmat are the
-// body frames and S[d] holds (axis_w, anchor_w) per dof (converted to motion axes later).
+// Forward kinematics by pointer jumping.  Lane b owns body b (at most 32 bodies).
+//   1. every lane composes its body's LOCAL transform (frame offset ∘ joints) relative to the parent frame — no
+//      dependence on other bodies; per dof it records the joint axis and anchor in the parent frame;
+//   2. ⌈log2(depth + 1)⌉ rounds of T[b] ← T[anc[b]] ∘ T[b], anc[b] ← anc[anc[b]] through warp shuffles turn the local
+//      transforms into world transforms (a 7-link chain needs 3 rounds with all lanes busy instead of 7 levels with
+//      one lane busy each);
+//   3. lane d maps dof d's axis and anchor through its body's parent's world transform.
+// On exit xpos / xquat / xmat are the body frames and S[d] holds (axis_w, anchor_w) per dof (converted to motion axes
+// later).
 __device__ __forceinline__ void forward_kinematics(const PhysParams& P, const ModelView& m, WarpScratch& w,
                                                    const float* qpos_sh, int lane) {
-  for (int level = 0; level <= P.maxdepth; ++level) {
-    if (lane < P.nbody && m.body_depth[lane] == level) {
-      const int b = lane, par = m.body_parent[b];
-      V3 ppos = v3(0.f, 0.f, 0.f);
-      Q4 pq = Q4{1.f, 0.f, 0.f, 0.f};
-      if (par >= 0) {
-        ppos = ld3(w.xpos + par * 3);
-        pq = Q4{w.xquat[par * 4], w.xquat[par * 4 + 1], w.xquat[par * 4 + 2], w.xquat[par * 4 + 3]};
-      }
-      V3 pos = ppos + qrot(pq, ld3(m.body_pos + b * 3));
-      Q4 q = qmul(pq, Q4{m.body_quat[b * 4], m.body_quat[b * 4 + 1], m.body_quat[b * 4 + 2], m.body_quat[b * 4 + 3]});
-      const int d0 = m.body_dofadr[b], dn = m.body_dofnum[b];
-      for (int k = 0; k < dn; ++k) {
-        const int d = d0 + k;
-        const V3 axis_w = qrot(q, ld3(m.dof_axis + d * 3));
-        const float qd = qpos_sh[d] - m.qpos0[d];
-        if (m.dof_type[d] == NB_JOINT_HINGE) {
-          const V3 anchor = pos + qrot(q, ld3(m.dof_pos + d * 3));
-          float s, c;
-          {
-            float h = 0.5f * qd;
-            h -= 6.283185307179586f * rintf(h * 0.15915494309189535f);
-            __sincosf(h, &s, &c);
-          }
-          const V3 al = ld3(m.dof_axis + d * 3);
-          q = qmul(q, Q4{c, s * al.x, s * al.y, s * al.z});
-          pos = anchor - qrot(q, ld3(m.dof_pos + d * 3));
-          st3(w.S + d * 6, axis_w);
-          st3(w.S + d * 6 + 3, anchor);
-        } else {
-          pos = pos + qd * axis_w;
-          st3(w.S + d * 6, axis_w);
-          st3(w.S + d * 6 + 3, pos);
+  const bool has_body = lane < P.nbody;
+  const int b = has_body ? lane : 0;
+  V3 pos = v3(0.f, 0.f, 0.f);
+  Q4 q = Q4{1.f, 0.f, 0.f, 0.f};
+  int anc = -1;
+  if (has_body) {
+    anc = m.body_parent[b];
+    pos = ld3(m.body_pos + b * 3);
+    q = Q4{m.body_quat[b * 4], m.body_quat[b * 4 + 1], m.body_quat[b * 4 + 2], m.body_quat[b * 4 + 3]};
+    const int d0 = m.body_dofadr[b], dn = m.body_dofnum[b];
+    for (int k = 0; k < dn; ++k) {
+      const int d = d0 + k;
+      const V3 al = ld3(m.dof_axis + d * 3);
+      const V3 axis_p = qrot(q, al);                 // joint axis in the parent frame
+      const float qd = qpos_sh[d] - m.qpos0[d];
+      if (m.dof_type[d] == NB_JOINT_HINGE) {
+        const V3 dp = ld3(m.dof_pos + d * 3);
+        const V3 anchor = pos + qrot(q, dp);
+        float sn, cs;
+        {
+          float hf = 0.5f * qd;
+          hf -= 6.283185307179586f * rintf(hf * 0.15915494309189535f);
+          __sincosf(hf, &sn, &cs);
         }
+        q = qmul(q, Q4{cs, sn * al.x, sn * al.y, sn * al.z});
+        pos = anchor - qrot(q, dp);
+        st3(w.S + d * 6, axis_p);
+        st3(w.S + d * 6 + 3, anchor);
+      } else {
+        pos = pos + qd * axis_p;
+        st3(w.S + d * 6, axis_p);
+        st3(w.S + d * 6 + 3, pos);
       }
-      const float inv = rsqrtf(q.w * q.w + q.x * q.x + q.y * q.y + q.z * q.z);
-      q = Q4{q.w * inv, q.x * inv, q.y * inv, q.z * inv};
-      st3(w.xpos + b * 3, pos);
-      w.xquat[b * 4] = q.w;
-      w.xquat[b * 4 + 1] = q.x;
-      w.xquat[b * 4 + 2] = q.y;
-      w.xquat[b * 4 + 3] = q.z;
-      qmat(q, w.xmat + b * 9);
     }
-    __syncwarp();
   }
+  // parent's WORLD transform of every body is needed in step 3: remember the parent lane before the jumps change anc
+  const int par = anc;
+  for (int round = 0; round < 5; ++round) {
+    if (__all_sync(0xffffffffu, anc < 0)) break;
+    const int src = anc < 0 ? lane : anc;
+    const float apx = __shfl_sync(0xffffffffu, pos.x, src), apy = __shfl_sync(0xffffffffu, pos.y, src),
+                apz = __shfl_sync(0xffffffffu, pos.z, src);
+    const float aqw = __shfl_sync(0xffffffffu, q.w, src), aqx = __shfl_sync(0xffffffffu, q.x, src),
+                aqy = __shfl_sync(0xffffffffu, q.y, src), aqz = __shfl_sync(0xffffffffu, q.z, src);
+    const int aanc = __shfl_sync(0xffffffffu, anc, src);
+    if (anc >= 0) {
+      const Q4 aq = Q4{aqw, aqx, aqy, aqz};
+      pos = v3(apx, apy, apz) + qrot(aq, pos);
+      q = qmul(aq, q);
+      anc = aanc;
+    }
+  }
+  if (has_body) {
+    const float inv = rsqrtf(q.w * q.w + q.x * q.x + q.y * q.y + q.z * q.z);
+    q = Q4{q.w * inv, q.x * inv, q.y * inv, q.z * inv};
+    st3(w.xpos + b * 3, pos);
+    w.xquat[b * 4] = q.w;
+    w.xquat[b * 4 + 1] = q.x;
+    w.xquat[b * 4 + 2] = q.y;
+    w.xquat[b * 4 + 3] = q.z;
+    qmat(q, w.xmat + b * 9);
+  }
+  __syncwarp();
+  (void)par;
+  // step 3: dof axes / anchors from the parent frame of their body to the world
+  if (lane < P.nv) {
+    const int d = lane;
+    const int pb = m.body_parent[m.dof_body[d]];
+    if (pb >= 0) {
+      const V3 pp = ld3(w.xpos + pb * 3);
+      const Q4 pq = Q4{w.xquat[pb * 4], w.xquat[pb * 4 + 1], w.xquat[pb * 4 + 2], w.xquat[pb * 4 + 3]};
+      const V3 ax = qrot(pq, ld3(w.S + d * 6));
+      const V3 an = pp + qrot(pq, ld3(w.S + d * 6 + 3));
+      st3(w.S + d * 6, ax);
+      st3(w.S + d * 6 + 3, an);
+    }
+  }
+  __syncwarp();
 }
 
 // Stage timers of the diagnostic (bounds-checked) build: with a debug buffer, environment 0 adds the clocks each stage

@@ -253,10 +253,10 @@ def ppo_family_driver(family: FamilySpec, tasks: Sequence[TaskSpec], *, n_envs: 
                       seed: int = 0, **ppo_kw):
     """One task-conditioned PPO policy over every task of the family with the device rollout (CUDA only: the rollout,
     GAE and the minibatch updates are captured graphs).  Returns (agent, env, per-iteration metrics, success rates)."""
-    from ..agents.ppo import PPOAgent, PPOConfig
+    from ..agents.ppo import PPOConfig, PPOTrainer
     env = TabletopFamilyEnv(family, tasks, n_envs, sites=sites, device="cuda", seed=seed)
     env.engine = _EngineAdapter(env)
-    agent = PPOAgent(env, PPOConfig(n_envs=n_envs, **ppo_kw))
+    agent = PPOTrainer(env, PPOConfig(n_envs=n_envs, **ppo_kw))
     hist = [agent.train_iteration() for _ in range(iterations)]
     return agent, env, hist, env.success_rates()
 

@@ -22,9 +22,17 @@ from ..nn import schedulers
 class Trainer:
     def __init__(self, model, x: torch.Tensor, y: torch.Tensor, batch: int, loss: str = "cross_entropy", lr: float = 1e-3,
                  weight_decay: float = 0.0, max_grad_norm: float = 0.0, optimizer: str = "adamw", seed: int = 0,
-                 use_cuda_graph: bool = False, grad_sync=None):
+                 use_cuda_graph: bool = False, grad_sync=None, augmenter=None):
         self.model, self.batch, self.loss_kind = model, batch, loss
         self.device = x.device
+        # with an augmenter the trainer trains from a buffer that is rewritten from the raw set once per epoch (the
+        # buffer keeps its address, so a captured step keeps working)
+        self.augmenter = augmenter if augmenter is not None and not augmenter.is_noop else None
+        self.raw_x = x
+        self.seed = seed
+        if self.augmenter is not None:
+            x = torch.empty_like(x)
+            self.augmenter.augment(x, self.raw_x, 0, seed)
         self.x, self.y = x, y
         self.n = x.shape[0]
         opt_cls = {"adamw": nn.AdamW, "adam": nn.Adam, "sgd": nn.SGD, "laprop": nn.LaProp}[optimizer]
@@ -78,6 +86,8 @@ class Trainer:
         """One pass in a shuffled order (device-side permutation); returns (mean loss, accuracy) read once at the end."""
         self.loss_acc.zero_()
         self.correct.zero_()
+        if self.augmenter is not None:
+            self.augmenter.augment(self.x, self.raw_x, epoch, self.seed)
         g = torch.Generator(device=self.device).manual_seed(1234567 + epoch)
         perm = torch.randperm(self.n, device=self.device, generator=g)
         nb = self.n // self.batch

@@ -38,10 +38,10 @@ def test_long_run_statistics_and_bf16_mirror():
 
 
 def test_ppo_device_rollout_runs_on_lunar_lander():
-    from noeira_b200.agents.ppo import PPOAgent, PPOConfig
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
     from noeira_b200.envs.lunar_lander import LunarLanderEnv
     env = LunarLanderEnv(1024, device="cuda", seed=0)
-    agent = PPOAgent(env, PPOConfig(n_envs=1024, rollout_len=32, n_epochs=4, n_minibatches=8))
+    agent = PPOTrainer(env, PPOConfig(n_envs=1024, rollout_len=32, n_epochs=4, n_minibatches=8))
     m0 = agent.train_iteration()
     for _ in range(5):
         m = agent.train_iteration()
