@@ -28,6 +28,8 @@
 // Joint damping is integrated implicitly by factoring M̂ = M + diag(armature + dt·damping) once
 // and using it for both the smooth solve and the constraint response (the reference re-factors in
 // its finalize stage, euler.mojo:404-552).
+#include <type_traits>
+
 #include "common.cuh"
 #include "physics_params.h"
 
@@ -543,81 +545,180 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
   // is the smooth solve qacc = M̂⁻¹ tau, handled by the same triangular solves.
   const float k_s = 1.f / (P.solimp_dmax * P.solimp_dmax * P.solref_tc * P.solref_tc * P.solref_dr * P.solref_dr);
   const float b_s = 2.f / (P.solimp_dmax * P.solref_tc);
-  for (int r0 = 0; r0 <= nrow; r0 += 32) {
-    const int r = r0 + lane;
-    if (r <= nrow) {
-      const bool smooth = (r == nrow);
-      float* Jr = smooth ? tau_sh : (w.J + r * nvp);
-      float* Br = smooth ? qacc_sh : (w.B + r * nvp);
-      int kind = 0, slot = 0;
-      if (!smooth) {
-        kind = w.rowi[r * 4];
-        slot = w.rowi[r * 4 + 1];
-        if (kind == ROW_LIMIT) {
-          const int d = m.lim_dof[slot];
-          const float sgn = w.row[r * 4 + 1];
-          for (int j = 0; j < nv; ++j) Jr[j] = (j == d) ? sgn : 0.f;
-        } else {
-          const int cs = slot - P.nlimit, b = m.cs_body[cs];
-          const float* R = w.xmat + b * 9;
-          const V3 l = ld3(m.cs_local + cs * 3);
-          const V3 p = ld3(w.xpos + b * 3) + v3(R[0] * l.x + R[1] * l.y + R[2] * l.z, R[3] * l.x + R[4] * l.y + R[5] * l.z,
-                                               R[6] * l.x + R[7] * l.y + R[8] * l.z);
-          const float dist = dot(pn, p) - P.plane_off - m.cs_radius[cs];
-          const V3 pc = p - (m.cs_radius[cs] + 0.5f * dist) * pn - c;  // contact point relative to c
-          const V3 dir = (kind == ROW_NORMAL) ? pn : (kind == ROW_TANGENT ? t1 : t2);
-          const unsigned mask = (unsigned)m.body_dofmask[b];
-          for (int j = 0; j < nv; ++j) {
-            float v = 0.f;
-            if (mask >> j & 1u) {
-              const V3 sw = ld3(w.S + j * 6), sv = ld3(w.S + j * 6 + 3);
-              v = dot(dir, sv + cross(sw, pc));
+  // The solves of a row are a dependency chain; with the dof count known at compile time the loops unroll, the row's
+  // J and B live in registers (instead of going through shared memory and back between dependent steps) and the loads
+  // of the factor are hoisted ahead of the chain.  NV = 0 is the generic path with run-time loops.
+  auto rows_stage = [&](auto nv_tag) {
+    constexpr int NV = decltype(nv_tag)::value;
+    if constexpr (NV > 0) {
+      for (int r0 = 0; r0 <= nrow; r0 += 32) {
+        const int r = r0 + lane;
+        if (r <= nrow) {
+          const bool smooth = (r == nrow);
+          float Jl[NV], Bl[NV];
+          int kind = 0, slot = 0;
+          if (smooth) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) Jl[j] = tau_sh[j];
+          } else {
+            kind = w.rowi[r * 4];
+            slot = w.rowi[r * 4 + 1];
+            if (kind == ROW_LIMIT) {
+              const int d = m.lim_dof[slot];
+              const float sgn = w.row[r * 4 + 1];
+#pragma unroll
+              for (int j = 0; j < NV; ++j) Jl[j] = (j == d) ? sgn : 0.f;
+            } else {
+              const int cs = slot - P.nlimit, b = m.cs_body[cs];
+              const float* R = w.xmat + b * 9;
+              const V3 l = ld3(m.cs_local + cs * 3);
+              const V3 p = ld3(w.xpos + b * 3) + v3(R[0] * l.x + R[1] * l.y + R[2] * l.z, R[3] * l.x + R[4] * l.y + R[5] * l.z,
+                                                   R[6] * l.x + R[7] * l.y + R[8] * l.z);
+              const float dist = dot(pn, p) - P.plane_off - m.cs_radius[cs];
+              const V3 pc = p - (m.cs_radius[cs] + 0.5f * dist) * pn - c;  // contact point relative to c
+              const V3 dir = (kind == ROW_NORMAL) ? pn : (kind == ROW_TANGENT ? t1 : t2);
+              const unsigned mask = (unsigned)m.body_dofmask[b];
+#pragma unroll
+              for (int j = 0; j < NV; ++j) {
+                float v = 0.f;
+                if (mask >> j & 1u) {
+                  const V3 sw = ld3(w.S + j * 6), sv = ld3(w.S + j * 6 + 3);
+                  v = dot(dir, sv + cross(sw, pc));
+                }
+                Jl[j] = v;
+              }
             }
-            Jr[j] = v;
+          }
+          // forward solve L y = J, then back solve Lᵀ x = y
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            float acc = Jl[i];
+#pragma unroll
+            for (int j = 0; j < i; ++j) acc -= w.M[i * nvp + j] * Bl[j];
+            Bl[i] = acc * w.M[i * nvp + i];
+          }
+#pragma unroll
+          for (int i = NV - 1; i >= 0; --i) {
+            float acc = Bl[i];
+#pragma unroll
+            for (int j = i + 1; j < NV; ++j) acc -= w.M[j * nvp + i] * Bl[j];
+            Bl[i] = acc * w.M[i * nvp + i];
+          }
+          float* Br = smooth ? qacc_sh : (w.B + r * nvp);
+#pragma unroll
+          for (int j = 0; j < NV; ++j) Br[j] = Bl[j];
+          if (!smooth) {
+            float* Jr = w.J + r * nvp;
+            float diag = 0.f, vel = 0.f;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+              Jr[j] = Jl[j];
+              diag += Jl[j] * Bl[j];
+              vel += Jl[j] * qvel_sh[j];
+            }
+            diag = fmaxf(diag, 1e-10f);
+            const float dist = w.row[r * 4 + 0];
+            const float imp = impedance(P, fabsf(dist));
+            float aref, Rr;
+            if (kind == ROW_LIMIT || kind == ROW_NORMAL) {
+              aref = -b_s * vel - k_s * imp * dist;
+              Rr = (1.f - imp) / imp * diag;
+            } else {
+              aref = -b_s * vel;
+              const float impf = P.solimp_dmax;
+              Rr = (1.f - impf) / impf * diag * P.friction_reg;
+            }
+            int ws;
+            if (kind == ROW_LIMIT) ws = slot;
+            else ws = P.nlimit + (slot - P.nlimit) * 3 + (kind == ROW_NORMAL ? 0 : (kind == ROW_TANGENT ? 1 : 2));
+            w.row[r * 4 + 0] = aref;
+            w.row[r * 4 + 1] = Rr;
+            w.row[r * 4 + 2] = 1.f / (diag + Rr);
+            w.row[r * 4 + 3] = warm[ws];
+            w.rowi[r * 4 + 3] = ws;
           }
         }
       }
-      // forward solve L y = J, then back solve Lᵀ x = y
-      for (int i = 0; i < nv; ++i) {
-        float acc = Jr[i];
-        for (int j = 0; j < i; ++j) acc -= w.M[i * nvp + j] * Br[j];
-        Br[i] = acc * w.M[i * nvp + i];
-      }
-      for (int i = nv - 1; i >= 0; --i) {
-        float acc = Br[i];
-        for (int j = i + 1; j < nv; ++j) acc -= w.M[j * nvp + i] * Br[j];
-        Br[i] = acc * w.M[i * nvp + i];
-      }
-      if (!smooth) {
-        float diag = 0.f, vel = 0.f;
-        for (int j = 0; j < nv; ++j) {
-          diag += Jr[j] * Br[j];
-          vel += Jr[j] * qvel_sh[j];
+    } else {
+      for (int r0 = 0; r0 <= nrow; r0 += 32) {
+        const int r = r0 + lane;
+        if (r <= nrow) {
+          const bool smooth = (r == nrow);
+          float* Jr = smooth ? tau_sh : (w.J + r * nvp);
+          float* Br = smooth ? qacc_sh : (w.B + r * nvp);
+          int kind = 0, slot = 0;
+          if (!smooth) {
+            kind = w.rowi[r * 4];
+            slot = w.rowi[r * 4 + 1];
+            if (kind == ROW_LIMIT) {
+              const int d = m.lim_dof[slot];
+              const float sgn = w.row[r * 4 + 1];
+              for (int j = 0; j < nv; ++j) Jr[j] = (j == d) ? sgn : 0.f;
+            } else {
+              const int cs = slot - P.nlimit, b = m.cs_body[cs];
+              const float* R = w.xmat + b * 9;
+              const V3 l = ld3(m.cs_local + cs * 3);
+              const V3 p = ld3(w.xpos + b * 3) + v3(R[0] * l.x + R[1] * l.y + R[2] * l.z, R[3] * l.x + R[4] * l.y + R[5] * l.z,
+                                                   R[6] * l.x + R[7] * l.y + R[8] * l.z);
+              const float dist = dot(pn, p) - P.plane_off - m.cs_radius[cs];
+              const V3 pc = p - (m.cs_radius[cs] + 0.5f * dist) * pn - c;  // contact point relative to c
+              const V3 dir = (kind == ROW_NORMAL) ? pn : (kind == ROW_TANGENT ? t1 : t2);
+              const unsigned mask = (unsigned)m.body_dofmask[b];
+              for (int j = 0; j < nv; ++j) {
+                float v = 0.f;
+                if (mask >> j & 1u) {
+                  const V3 sw = ld3(w.S + j * 6), sv = ld3(w.S + j * 6 + 3);
+                  v = dot(dir, sv + cross(sw, pc));
+                }
+                Jr[j] = v;
+              }
+            }
+          }
+          // forward solve L y = J, then back solve Lᵀ x = y
+          for (int i = 0; i < nv; ++i) {
+            float acc = Jr[i];
+            for (int j = 0; j < i; ++j) acc -= w.M[i * nvp + j] * Br[j];
+            Br[i] = acc * w.M[i * nvp + i];
+          }
+          for (int i = nv - 1; i >= 0; --i) {
+            float acc = Br[i];
+            for (int j = i + 1; j < nv; ++j) acc -= w.M[j * nvp + i] * Br[j];
+            Br[i] = acc * w.M[i * nvp + i];
+          }
+          if (!smooth) {
+            float diag = 0.f, vel = 0.f;
+            for (int j = 0; j < nv; ++j) {
+              diag += Jr[j] * Br[j];
+              vel += Jr[j] * qvel_sh[j];
+            }
+            diag = fmaxf(diag, 1e-10f);
+            const float dist = w.row[r * 4 + 0];
+            const float imp = impedance(P, fabsf(dist));
+            float aref, Rr;
+            if (kind == ROW_LIMIT || kind == ROW_NORMAL) {
+              aref = -b_s * vel - k_s * imp * dist;
+              Rr = (1.f - imp) / imp * diag;
+            } else {
+              aref = -b_s * vel;
+              const float impf = P.solimp_dmax;
+              Rr = (1.f - impf) / impf * diag * P.friction_reg;
+            }
+            // warm start slot index
+            int ws;
+            if (kind == ROW_LIMIT) ws = slot;
+            else ws = P.nlimit + (slot - P.nlimit) * 3 + (kind == ROW_NORMAL ? 0 : (kind == ROW_TANGENT ? 1 : 2));
+            w.row[r * 4 + 0] = aref;
+            w.row[r * 4 + 1] = Rr;
+            w.row[r * 4 + 2] = 1.f / (diag + Rr);
+            w.row[r * 4 + 3] = warm[ws];
+            w.rowi[r * 4 + 3] = ws;
+          }
         }
-        diag = fmaxf(diag, 1e-10f);
-        const float dist = w.row[r * 4 + 0];
-        const float imp = impedance(P, fabsf(dist));
-        float aref, Rr;
-        if (kind == ROW_LIMIT || kind == ROW_NORMAL) {
-          aref = -b_s * vel - k_s * imp * dist;
-          Rr = (1.f - imp) / imp * diag;
-        } else {
-          aref = -b_s * vel;
-          const float impf = P.solimp_dmax;
-          Rr = (1.f - impf) / impf * diag * P.friction_reg;
-        }
-        // warm start slot index
-        int ws;
-        if (kind == ROW_LIMIT) ws = slot;
-        else ws = P.nlimit + (slot - P.nlimit) * 3 + (kind == ROW_NORMAL ? 0 : (kind == ROW_TANGENT ? 1 : 2));
-        w.row[r * 4 + 0] = aref;
-        w.row[r * 4 + 1] = Rr;
-        w.row[r * 4 + 2] = 1.f / (diag + Rr);
-        w.row[r * 4 + 3] = warm[ws];
-        w.rowi[r * 4 + 3] = ws;
       }
     }
-  }
+  };
+  if (nv == 9) rows_stage(std::integral_constant<int, 9>{});
+  else rows_stage(std::integral_constant<int, 0>{});
   __syncwarp();
   if (dbg) {
     if (lane < nv) { dbg[nv * nv + nv + lane] = qacc_sh[lane]; }

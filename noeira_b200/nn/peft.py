@@ -94,14 +94,48 @@ def dequantize_q4_0(codes: torch.Tensor, scales: torch.Tensor, out_dtype=torch.f
     return (q * scales.float().unsqueeze(-1)).reshape(rows, cols).to(out_dtype)
 
 
+def gptq_quantize_q4_0(w: torch.Tensor, x: torch.Tensor, damp: float = 0.01):
+    """GPTQ for a Linear weight ``w [IN, OUT]`` (Q4_0 blocks of 32 along OUT) from calibration inputs ``x [n, IN]``:
+    input rows are quantised one after the other and the rounding error of a row is pushed onto the rows not yet
+    quantised through the inverse Hessian of the layer's squared output error (H = 2 XᵀX / n), so that ``x @ w`` is
+    preserved far better than by rounding each weight on its own.  Returns ``(codes, scales)`` in the layout of
+    ``quantize_q4_0``.  (Frantar et al., "GPTQ", 2023; reference: noeira/nn/quant/ GPTQ calibration.)"""
+    IN, OUT = w.shape
+    assert OUT % 32 == 0 and x.shape[1] == IN
+    W = w.detach().double().cpu().clone()
+    X = x.detach().double().cpu()
+    H = 2.0 * (X.t() @ X) / max(X.shape[0], 1)
+    dead = torch.diag(H) == 0
+    H[dead, dead] = 1.0
+    W[dead] = 0.0
+    H += damp * torch.diag(H).mean() * torch.eye(IN, dtype=torch.float64)
+    Hinv = torch.cholesky_inverse(torch.linalg.cholesky(H))
+    U = torch.linalg.cholesky(Hinv, upper=True)          # Hinv = Uᵀ U; row i of U drives the update of rows > i
+    codes = torch.empty(IN, OUT // 2, dtype=torch.uint8)
+    scales = torch.empty(IN, OUT // 32, dtype=torch.float16)
+    for i in range(IN):
+        c, sc = quantize_q4_0(W[i: i + 1].float())
+        codes[i], scales[i] = c[0], sc[0]
+        q = dequantize_q4_0(c, sc, torch.float32)[0].double()
+        err = (W[i] - q) / U[i, i]
+        if i + 1 < IN:
+            W[i + 1:] -= U[i, i + 1:, None] * err[None, :]
+    return codes, scales
+
+
 class QLinear(Module):
     """Frozen Linear with a Q4_0 weight (0.5625 bytes per element).  The bias stays fp32."""
 
-    def __init__(self, linear: Linear):
+    def __init__(self, linear: Linear, calibration: torch.Tensor = None):
+        """``calibration``: optional inputs ``[n, IN]`` of this layer; with them the weight is quantised by GPTQ."""
         super().__init__()
         self.in_dim, self.out_dim, self.act = linear.in_dim, linear.out_dim, linear.act
         assert self.out_dim % 32 == 0, "Q4_0 blocks run along the output dimension of the [IN, OUT] weight"
-        codes, scales = quantize_q4_0(linear.weight.data.float().cpu())
+        wcpu = linear.weight.data.float().cpu()[: self.in_dim, : self.out_dim]
+        if calibration is not None:
+            codes, scales = gptq_quantize_q4_0(wcpu, calibration.float().cpu().reshape(-1, self.in_dim))
+        else:
+            codes, scales = quantize_q4_0(linear.weight.data.float().cpu())
         self.codes = self.add_state("qweight", codes.shape)
         self.codes.data = codes
         self.scales = self.add_state("scales", scales.shape)
