@@ -451,20 +451,53 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
 
   PHYS_STAGE(5);
   // ---- in-place Cholesky M̂ = L Lᵀ (lower).  Column k: lane r > k scales, then trailing update.
-  for (int k = 0; k < nv; ++k) {
-    float dkk = w.M[k * nvp + k];
-    const float inv = rsqrtf(fmaxf(dkk, 1e-10f));
-    __syncwarp();
-    if (lane == k) w.M[k * nvp + k] = inv;  // the diagonal keeps 1/L_kk
-    if (lane > k && lane < nv) w.M[lane * nvp + k] *= inv;
-    __syncwarp();
-    // trailing: element (r, c) for k < c <= r < nv; lanes stride over the flattened lower triangle rows
-    if (lane > k && lane < nv) {
-      const float lrk = w.M[lane * nvp + k];
-      for (int cc = k + 1; cc <= lane; ++cc) w.M[lane * nvp + cc] -= lrk * w.M[cc * nvp + k];
+  auto cholesky_stage = [&](auto nv_tag) {
+    constexpr int NV = decltype(nv_tag)::value;
+    if constexpr (NV > 0) {
+      // lane r keeps row r of the matrix in registers; the column of the current pivot travels by shuffles, so the
+      // factorisation needs neither shared-memory round trips nor warp barriers between its NV dependent columns
+      float Lr[NV];
+      const int rr = lane < NV ? lane : NV - 1;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) Lr[j] = w.M[rr * nvp + j];
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const float dkk = __shfl_sync(0xffffffffu, Lr[k], k);
+        const float inv = rsqrtf(fmaxf(dkk, 1e-10f));
+        const float lrk = Lr[k] * inv;                 // L[r][k] for r > k
+        if (lane == k) Lr[k] = inv;                    // the diagonal keeps 1/L_kk
+        else if (lane > k) Lr[k] = lrk;
+#pragma unroll
+        for (int cc = 0; cc < NV; ++cc) {
+          if (cc > k) {
+            const float lck = __shfl_sync(0xffffffffu, lrk, cc);
+            if (lane >= cc) Lr[cc] -= lrk * lck;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+        if (lane < NV && j <= lane) w.M[lane * nvp + j] = Lr[j];
+      __syncwarp();
+    } else {
+      for (int k = 0; k < nv; ++k) {
+        float dkk = w.M[k * nvp + k];
+        const float inv = rsqrtf(fmaxf(dkk, 1e-10f));
+        __syncwarp();
+        if (lane == k) w.M[k * nvp + k] = inv;  // the diagonal keeps 1/L_kk
+        if (lane > k && lane < nv) w.M[lane * nvp + k] *= inv;
+        __syncwarp();
+        // trailing: element (r, c) for k < c <= r < nv; lanes stride over the flattened lower triangle rows
+        if (lane > k && lane < nv) {
+          const float lrk = w.M[lane * nvp + k];
+          for (int cc = k + 1; cc <= lane; ++cc) w.M[lane * nvp + cc] -= lrk * w.M[cc * nvp + k];
+        }
+        __syncwarp();
+      }
     }
-    __syncwarp();
-  }
+  };
+  if (nv == 9) cholesky_stage(std::integral_constant<int, 9>{});
+  else cholesky_stage(std::integral_constant<int, 0>{});
 
   PHYS_STAGE(6);
   // ---- constraint detection.  Slots: [0, nlimit) joint limits, [nlimit, nlimit+ncs) contact spheres.
@@ -752,10 +785,27 @@ __device__ __forceinline__ void substep(const PhysParams& P, const ModelView& m,
     }
     __syncwarp();  // every lane has read what it needs from the arrays that A overlays (none are read below)
     if (on) {
-      for (int s2 = 0; s2 <= r; ++s2) {
-        float a = 0.f;
-        for (int j = 0; j < nv; ++j) a += w.J[r * nvp + j] * w.B[s2 * nvp + j];
-        w.A[tri_r + s2] = a;
+      if (nv == 9) {   // dof count known: the row of J stays in registers, the dot products unroll
+        float Jl[9];
+#pragma unroll
+        for (int j = 0; j < 9; ++j) Jl[j] = w.J[r * nvp + j];
+        for (int s2 = 0; s2 <= r; ++s2) {
+          const float* Bs = w.B + s2 * nvp;
+          float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+#pragma unroll
+          for (int j = 0; j < 9; j += 3) {
+            a0 += Jl[j] * Bs[j];
+            a1 += Jl[j + 1] * Bs[j + 1];
+            a2 += Jl[j + 2] * Bs[j + 2];
+          }
+          w.A[tri_r + s2] = a0 + a1 + a2;
+        }
+      } else {
+        for (int s2 = 0; s2 <= r; ++s2) {
+          float a = 0.f;
+          for (int j = 0; j < nv; ++j) a += w.J[r * nvp + j] * w.B[s2 * nvp + j];
+          w.A[tri_r + s2] = a;
+        }
       }
     }
     __syncwarp();
