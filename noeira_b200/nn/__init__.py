@@ -16,3 +16,4 @@ from . import schedulers  # noqa: F401
 from .peft import LoRALinear, QLinear, QLoRALinear, dequantize_q4_0, freeze_params, quantize_q4_0  # noqa: F401
 from .recurrent import GRUCell, LSTMCell, LSTMSeq  # noqa: F401
 from . import losses  # noqa: F401
+from .noisy import BlockLinear, NoisyLinear, reset_noise  # noqa: F401
