@@ -175,7 +175,7 @@ def overlap_case(rank, world, local):
     tokens = torch.randint(0, 96, (20000,), device="cuda")
     losses, vals, during = [], [], 0
     for kind in ("overlap", "nccl"):
-        model = GPT(vocab=96, seq=64, dim=128, layers=3, heads=4, seed=5).to("cuda")
+        model = GPT(vocab=96, seq=64, dim=128, layers=3, heads=2, seed=5).to("cuda")
         sync = OverlapGradSync(world, rank, bucket_bytes=256 << 10) if kind == "overlap" else NcclGradSync(world, rank)
         tr = AutoregressiveTrainer(model, tokens, batch=8, seq=64, lr=1e-3, warmup=2, total_steps=20, seed=9, grad_sync=sync,
                                    rank=rank, world=world)
@@ -199,4 +199,9 @@ def overlap_case(rank, world, local):
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except Exception:                      # the launcher keeps only the tail of stderr: put the traceback on stdout too
+        import traceback
+        print(f"rank {os.environ.get('RANK')} raised:\n{traceback.format_exc()}", flush=True)
+        raise
