@@ -40,6 +40,7 @@ def main():
     ap.add_argument("--layout", default="nt", help="nt: B [N,K]; nn: B [K,N]; tn: A [K,M], B [K,N]")
     ap.add_argument("--two-cta", type=int, default=0, help="0 = by size, 1 = one-CTA tiles only, 2 = CTA-pair tiles")
     ap.add_argument("--no-lib", action="store_true", help="skip the cuBLAS comparison (profiling captures)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "tf32"], help="tf32: fp32 operands on the TF32 tensor-core path")
     args = ap.parse_args()
     from noeira_b200.ops import check_status, gemm
     from noeira_b200.ops.gemm import set_two_cta_mode
@@ -49,24 +50,26 @@ def main():
         peaks = json.load(open(os.path.join(os.path.dirname(__file__), "..", "MEASURED_PEAKS.json")))
     except Exception:
         pass
-    peak = peaks.get("bf16_tflops", 1590.0)
+    peak = peaks.get("bf16_tflops", 1590.0)          # TF32 runs at half the bf16 rate: its fraction is taken against peak / 2
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for sh in args.shapes.split(","):
         M, N, K = (int(x) for x in sh.split("x"))
         a_mn = args.layout == "tn"
         b_mn = args.layout in ("nn", "tn")
-        a = (torch.randn((K, M) if a_mn else (M, K), device="cuda") * 0.1).bfloat16()
-        b = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.1).bfloat16()
-        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+        torch.backends.cuda.matmul.allow_tf32 = args.dtype == "tf32"        # the library comparison uses TF32 too
+        a = (torch.randn((K, M) if a_mn else (M, K), device="cuda") * 0.1).to(dt)
+        b = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.1).to(dt)
+        out = torch.empty(M, N, device="cuda", dtype=dt)
         A = a.t() if a_mn else a
         B = b if b_mn else b.t()
         t_ours = timeit(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, bn=args.bn), args.iters, flush)
         check_status()
         t_lib = float("nan") if args.no_lib else timeit(lambda: torch.matmul(A, B, out=out), args.iters, flush)
         fl = 2.0 * M * N * K
-        print(json.dumps({"shape": sh, "layout": args.layout, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
+        print(json.dumps({"shape": sh, "layout": args.layout, "dtype": args.dtype, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
                           "ours_tflops": round(fl / t_ours / 1e9, 1), "cublas_tflops": round(fl / t_lib / 1e9, 1),
-                          "frac_of_measured_peak": round(fl / t_ours / 1e9 / peak, 3)}))
+                          "frac_of_measured_peak": round(fl / t_ours / 1e9 / (peak if args.dtype == "bf16" else peak / 2), 3)}))
 
 
 if __name__ == "__main__":

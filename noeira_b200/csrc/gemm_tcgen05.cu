@@ -35,6 +35,7 @@ constexpr int NUM_THREADS = 192;
 struct GemmParams {
   int M, N, K;
   int a_mn, b_mn;  // operand majors
+  int tf32;        // 1: operands are fp32 read as TF32 (kind::tf32, 8 k per instruction, 32 elements per 128-byte row)
   int ldd;         // output row pitch (elements)
   int ld_aux;      // aux row pitch (elements, bf16)
   int out_f32, accumulate, act, dact;
@@ -306,6 +307,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // a k-block is one 128-byte swizzle row of K: 64 bf16 or 32 fp32 elements; an MN-major operand arrives in chunks of
+      // that many MN elements, each chunk bk rows of 128 bytes
+      const int bk = p.tf32 ? BK / 2 : BK, chunk = bk;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         int mb, nb_;
         const int tile = item / p.splits, split = item - tile * p.splits;
@@ -330,18 +334,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_4d_g(sa + i * bw * 128, &tmA, &full_bar[stage], c0, ow0 - p.conv_pad + kw, oh - p.conv_pad + kh, bimg);
             }
           } else if (!p.a_mn) {
-            tma_load_2d(sa, &tmA, &full_bar[stage], kb * BK, mb * BM);
+            tma_load_2d(sa, &tmA, &full_bar[stage], kb * bk, mb * BM);
           } else {
-#pragma unroll
-            for (int h = 0; h < BM / 64; ++h)
-              tma_load_2d(sa + h * (64 * BK * 2), &tmA, &full_bar[stage], mb * BM + h * 64, kb * BK);
+            for (int h = 0; h < BM / chunk; ++h)
+              tma_load_2d(sa + h * (bk * 128), &tmA, &full_bar[stage], mb * BM + h * chunk, kb * bk);
           }
           if (!p.b_mn) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], kb * BK, nb_ * BN);
+            tma_load_2d(sb, &tmB, &full_bar[stage], kb * bk, nb_ * BN);
           } else {
-#pragma unroll
-            for (int h = 0; h < (BN + 63) / 64; ++h)
-              tma_load_2d(sb + h * (64 * BK * 2), &tmB, &full_bar[stage], nb_ * BN + h * 64, kb * BK);
+            for (int h = 0; h < (BN + chunk - 1) / chunk; ++h)
+              tma_load_2d(sb + h * (bk * 128), &tmB, &full_bar[stage], nb_ * BN + h * chunk, kb * bk);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -350,7 +352,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = make_idesc(1u, BM, BN, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+      const uint32_t idesc = make_idesc(p.tf32 ? 2u : 1u, BM, BN, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+      // one instruction consumes 32 bytes of K: 16 bf16 or 8 tf32.  K-major: 32 bytes further inside the swizzle row;
+      // MN-major: that many k-rows of 128 bytes further, chunks of MN one k-block of rows apart
+      const uint32_t kadv_mn = p.tf32 ? 8u * 128u : 16u * 128u, lbo_mn = p.tf32 ? 32u * 128u : 64u * 128u;
+      const bool tf32 = p.tf32 != 0;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -370,11 +376,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // K-major: advance 32 bytes inside the 128B swizzle row; MN-major: 16 k-rows of 128 B
-            const uint64_t adesc = p.a_mn ? make_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
+            const uint64_t adesc = p.a_mn ? make_smem_desc(sa + k * kadv_mn, lbo_mn, 1024, 2)
                                           : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
-            const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024, 2)
+            const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * kadv_mn, lbo_mn, 1024, 2)
                                           : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
-            umma_f16(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            if (tf32) umma_tf32(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            else umma_f16(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -781,19 +788,25 @@ EncodeTiledFn get_encode() {
 }
 
 // 2-D bf16 tensor map: inner extent `inner` (contiguous), outer extent `outer`, row pitch `ld` elements.
-int make_tmap_bf16(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
-                   int box_outer) {
+int make_tmap_elt(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
+                  int box_outer, int elt_bytes) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return NB_ERR_NO_DRIVER_SYMBOL;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return NB_ERR_UNALIGNED;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * elt_bytes) & 15)) return NB_ERR_UNALIGNED;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elt_bytes};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  // fp32 operands are loaded as TFLOAT32: the copy rounds them to the 10-bit mantissa the tensor core reads
+  CUresult r = enc(tm, elt_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? NB_OK : NB_ERR_TENSORMAP;
+}
+int make_tmap_bf16(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
+                   int box_outer) {
+  return make_tmap_elt(tm, base, inner, outer, ld, box_inner, box_outer, 2);
 }
 
 int sm_count() {
@@ -818,7 +831,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, long l
   }
   p.tiles_m = ceil_div(p.M, BM);
   p.tiles_n = ceil_div(p.N, BN);
-  p.num_kb = ceil_div(p.K, BK);
+  p.num_kb = ceil_div(p.K, p.tf32 ? BK / 2 : BK);
   const int tiles = p.tiles_m * p.tiles_n;
   // split-K when the tile count leaves most SMs idle and K is deep: each split keeps >= 4 k-blocks
   int splits = 1;
@@ -884,11 +897,12 @@ int nb_gemm_two_cta_mode(int mode) {
 // D[M,N] = epi(alpha * A·B).  A: a_mn=0 → [M,K] row-major (lda = pitch of a row of K), a_mn=1 → [K,M]
 // row-major (lda = pitch of a row of M).  B: b_mn=0 → [N,K] row-major, b_mn=1 → [K,N] row-major.
 // Pitches in elements; every pitch*2 bytes and every base must be 16-byte aligned (TMA).
-int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd, int a_mn,
-                 int b_mn, int out_f32, int accumulate, float alpha, const float* bias, int act, const void* aux,
-                 int ld_aux, int dact, unsigned int* status, int bn_hint, void* workspace, long long workspace_bytes,
-                 void* stream) {
+static int gemm_any(int tf32, const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd, int a_mn,
+                    int b_mn, int out_f32, int accumulate, float alpha, const float* bias, int act, const void* aux,
+                    int ld_aux, int dact, unsigned int* status, int bn_hint, void* workspace, long long workspace_bytes,
+                    void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return NB_ERR_BAD_ARG;
+  const int elt = tf32 ? 4 : 2, bk = 128 / elt;   // elements per 128-byte row = k-block depth = MN-major chunk width
   if (accumulate && !out_f32) return NB_ERR_BAD_ARG;
   if (dact && !aux) return NB_ERR_BAD_ARG;
   int BN = bn_hint;
@@ -903,26 +917,26 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
       else if (N <= 32) BN = 32;
     }
   }
-  if (b_mn && BN < 64) BN = 64;
+  if (b_mn && BN < bk) BN = bk;
   // two-CTA tiles once the 256 x 256 tiles keep about two thirds of the SM pairs busy (measured: 2048 x 2048 x 16384,
   // 64 tiles on 74 pairs, runs 1.74x faster this way than as split-K one-CTA tiles)
   bool two_cta = false;
-  if (bn_hint == 0 && g_two_cta_mode != 1 && M >= 256 && N >= 256 && K >= 128) {
+  if (!tf32 && bn_hint == 0 && g_two_cta_mode != 1 && M >= 256 && N >= 256 && K >= 128) {
     const long long t2 = (long long)ceil_div(M, 2 * BM) * ceil_div(N, BN2);
     two_cta = g_two_cta_mode == 2 || t2 * 3 >= (long long)sm_count();
   }
   if (two_cta) BN = BN2 / 2;   // the B box of one CTA
   CUtensorMap tmA, tmB;
   int rc;
-  if (!a_mn) rc = make_tmap_bf16(&tmA, A, K, M, lda, BK, BM);
-  else rc = make_tmap_bf16(&tmA, A, M, K, lda, 64, BK);
+  if (!a_mn) rc = make_tmap_elt(&tmA, A, K, M, lda, bk, BM, elt);
+  else rc = make_tmap_elt(&tmA, A, M, K, lda, bk, bk, elt);
   if (rc) return rc;
-  if (!b_mn) rc = make_tmap_bf16(&tmB, B, K, N, ldb, BK, BN);
-  else rc = make_tmap_bf16(&tmB, B, N, K, ldb, 64, BK);
+  if (!b_mn) rc = make_tmap_elt(&tmB, B, K, N, ldb, bk, BN, elt);
+  else rc = make_tmap_elt(&tmB, B, N, K, ldb, bk, bk, elt);
   if (rc) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.a_mn = a_mn; p.b_mn = b_mn; p.tf32 = tf32;
   p.ldd = ldd; p.ld_aux = ld_aux;
   p.out_f32 = out_f32; p.accumulate = accumulate; p.act = act; p.dact = dact;
   p.alpha = alpha;
@@ -947,6 +961,23 @@ int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int
     case 16: return launch<16, 8>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
     default: return NB_ERR_BAD_ARG;
   }
+}
+
+int nb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd, int a_mn,
+                 int b_mn, int out_f32, int accumulate, float alpha, const float* bias, int act, const void* aux,
+                 int ld_aux, int dact, unsigned int* status, int bn_hint, void* workspace, long long workspace_bytes,
+                 void* stream) {
+  return gemm_any(0, A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, accumulate, alpha, bias, act, aux, ld_aux, dact,
+                  status, bn_hint, workspace, workspace_bytes, stream);
+}
+// The same contraction on fp32 operands read as TF32 (10-bit mantissa, fp32 accumulation): `kind::tf32`, one-CTA tiles.
+// Pitches in fp32 elements (multiples of 4); `aux` stays a bf16 tensor.
+int nb_gemm_tf32(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd, int a_mn,
+                 int b_mn, int out_f32, int accumulate, float alpha, const float* bias, int act, const void* aux,
+                 int ld_aux, int dact, unsigned int* status, int bn_hint, void* workspace, long long workspace_bytes,
+                 void* stream) {
+  return gemm_any(1, A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, accumulate, alpha, bias, act, aux, ld_aux, dact,
+                  status, bn_hint, workspace, workspace_bytes, stream);
 }
 
 // Implicit-GEMM convolution forward, stride 1: y[B·OH·OW, OC] = epi(patches(x) · W), x NHWC bf16 [B, H, W, C] with
@@ -981,7 +1012,7 @@ int nb_conv_implicit_fwd(const void* x, const void* Wt, void* y, int B, int H, i
   if (rc) return rc;
   GemmParams p;
   p.M = M; p.N = OC; p.K = K;
-  p.a_mn = 0; p.b_mn = 1;
+  p.a_mn = 0; p.b_mn = 1; p.tf32 = 0;
   p.ldd = ldy; p.ld_aux = ld_res;
   p.out_f32 = 0; p.accumulate = 0; p.act = act; p.dact = residual ? NB_AUX_ADD : 0;
   p.alpha = 1.f;

@@ -46,7 +46,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0, bias: torch.Tensor = None,
          act=None, aux: torch.Tensor = None, dact=None, bn: int = 0, n: int = None,
          workspace: torch.Tensor = None, residual: torch.Tensor = None) -> torch.Tensor:
-    """``out[M,N] = epi(alpha · A·B)`` in bf16 with fp32 accumulation.
+    """``out[M,N] = epi(alpha · A·B)`` in bf16 with fp32 accumulation; fp32 operands run as TF32 (``kind::tf32``: the
+    copy into shared memory rounds them to a 10-bit mantissa, accumulation and the default output stay fp32).
 
     ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]`` (``b_mn=False``) or
     ``[K,N]`` (``b_mn=True``).  Rows may be strided (pitch a multiple of 8 elements).  ``bias`` fp32 ``[N]``;
@@ -57,8 +58,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if residual is not None:
         assert dact is None and aux is None
         aux, dact = residual, "add"
-    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    tf32 = a.dtype == torch.float32
+    assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float32)
     assert a.stride(-1) == 1 and b.stride(-1) == 1
+    if tf32 and out is None and out_dtype == torch.bfloat16:
+        out_dtype = torch.float32
     if a_mn:
         K, M = a.shape
     else:
@@ -81,12 +85,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         assert aux.dtype == torch.bfloat16 and aux.stride(-1) == 1
     st = device_status(a.device)
     ws = workspace if workspace is not None else default_workspace(a.device)
-    rc = cuda_lib().nb_gemm_bf16(
+    rc = (cuda_lib().nb_gemm_tf32 if tf32 else cuda_lib().nb_gemm_bf16)(
         ptr(a), ptr(b), ptr(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
         ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(out_f32)), ctypes.c_int(int(accumulate)),
         ctypes.c_float(alpha), ptr(bias), ctypes.c_int(ACT[act]), ptr(aux),
         ctypes.c_int(aux.stride(0) if aux is not None else 0), ctypes.c_int(ACT[dact]), ptr(st), ctypes.c_int(bn),
         ptr(ws), ctypes.c_longlong(ws.numel()), stream_ptr())
-    check(rc, "nb_gemm_bf16")
+    check(rc, "nb_gemm_tf32" if tf32 else "nb_gemm_bf16")
     return out

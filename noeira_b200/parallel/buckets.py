@@ -71,26 +71,33 @@ def plan_buckets(marks: Sequence[Mark], bucket_elems: int) -> List[Bucket]:
 
 
 class BucketedReducer:
-    """``on_unit_done(name)`` is called by the model's backward after a unit finished; buckets whose last missing unit
-    that was are reduced immediately by ``reduce_fn(begin, end)`` (which enqueues on its own stream); ``finish()``
-    reduces what is left and resets for the next step."""
+    """``on_unit_done(name)`` is called by the model's backward after a unit finished; a bucket is reduced by
+    ``reduce_fn(begin, end)`` (which enqueues on its own stream) once EVERY unit of it has reported, and only after all
+    buckets before it went — the launch order is the planned order on every rank, whatever order the model's backward
+    visits the units of one bucket in (a language model finishes its token table before its position table although the
+    arena holds them the other way round).  A unit must report once per backward: a module that is applied twice in
+    one forward has to be marked as one unit around both applications.  ``finish()`` reduces what is left and resets for
+    the next step."""
 
     def __init__(self, buckets: Sequence[Bucket], reduce_fn: Callable[[int, int], None]):
         self.buckets, self.reduce_fn = list(buckets), reduce_fn
         self._next = 0
+        self._done = set()
         self.order: List[Tuple[int, int]] = []
 
+    def _launch(self):
+        b = self.buckets[self._next]
+        self.reduce_fn(b.begin, b.end)
+        self.order.append((b.begin, b.end))
+        self._next += 1
+
     def on_unit_done(self, name: str):
-        while self._next < len(self.buckets) and self.buckets[self._next].ready_after == name:
-            b = self.buckets[self._next]
-            self.reduce_fn(b.begin, b.end)
-            self.order.append((b.begin, b.end))
-            self._next += 1
+        self._done.add(name)
+        while self._next < len(self.buckets) and self._done.issuperset(self.buckets[self._next].units):
+            self._launch()
 
     def finish(self):
         while self._next < len(self.buckets):
-            b = self.buckets[self._next]
-            self.reduce_fn(b.begin, b.end)
-            self.order.append((b.begin, b.end))
-            self._next += 1
+            self._launch()
         self._next = 0
+        self._done.clear()

@@ -32,3 +32,30 @@ def test_marks_from_arena_and_bucket_plan():
     assert covered[0][0] == 0 and covered[-1][1] == marks.marks[-1].end and covered[0][1] <= covered[1][0]   # alignment padding between units is not reduced
     one = plan_buckets(marks.marks, bucket_elems=1)
     assert [b.units for b in one] == [("4",), ("3",), ("2",), ("1",), ("0",)]
+
+
+def test_bucket_waits_for_all_of_its_units_in_any_order():
+    """Units of one bucket may finish in any order (token table before position table); the bucket leaves only after the
+    last of them, and buckets leave in the planned order."""
+    from noeira_b200.parallel.buckets import BucketedReducer, GradMarks, plan_buckets
+    gm = GradMarks()
+    for i in range(5):
+        gm.add(f"u{i}", i * 100, (i + 1) * 100)
+    buckets = plan_buckets(gm.marks, 200)            # {u3,u4}, {u1,u2}, {u0}
+    assert [b.units for b in buckets] == [("u3", "u4"), ("u1", "u2"), ("u0",)]
+    sent = []
+    red = BucketedReducer(buckets, lambda b, e: sent.append((b, e)))
+    red.on_unit_done("u4")
+    assert sent == []
+    red.on_unit_done("u1")                            # out of order: bucket 1 is not complete, bucket 0 neither
+    assert sent == []
+    red.on_unit_done("u3")
+    assert sent == [(300, 500)]
+    red.on_unit_done("u0")                            # complete, but bucket 1 has to go first
+    assert sent == [(300, 500)]
+    red.on_unit_done("u2")
+    assert sent == [(300, 500), (100, 300), (0, 100)]
+    red.finish()
+    assert len(sent) == 3
+    red.on_unit_done("u3")                            # next step starts clean
+    assert len(sent) == 3

@@ -180,3 +180,64 @@ def test_gemm_two_cta_epilogue_and_repeat(two_cta):
     ref = torch.nn.functional.gelu(a.float() @ w.float() + bias, approximate="tanh")
     assert torch.equal(y1, y2)
     assert (y1.float() - ref).abs().max().item() < 3e-2
+
+
+def _tf32_round(x):
+    """fp32 → TF32 by round-to-nearest-even on the 13 dropped mantissa bits (what the copy into shared memory does)."""
+    i = x.contiguous().view(torch.int32)
+    r = i + 0xFFF + ((i >> 13) & 1)
+    return (r & ~0x1FFF).view(torch.float32)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 256, 512), (300, 200, 132), (4096, 256, 256), (128, 64, 4096), (64, 16, 96)])
+def test_gemm_tf32_layouts(M, N, K, a_mn, b_mn):
+    """fp32 operands through the TF32 tensor-core path, all four operand layouts, against an fp32 reference on operands
+    rounded to TF32 (tight) and on the raw operands (the 10-bit-mantissa error bound)."""
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(0)
+    Mp, Np, Kp = (M + 3) // 4 * 4, (N + 3) // 4 * 4, (K + 3) // 4 * 4
+    a = torch.randn(Kp if a_mn else Mp, Mp if a_mn else Kp, device="cuda") * 0.5
+    b = torch.randn(Kp if b_mn else Np, Np if b_mn else Kp, device="cuda") * 0.5
+    a_v = a[:K, :M] if a_mn else a[:M, :K]
+    b_v = b[:K, :N] if b_mn else b[:N, :K]
+    out = gemm(a_v, b_v, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    check_status()
+    assert out.dtype == torch.float32
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        raw = _ref(a_v, b_v, a_mn, b_mn)
+        rounded = _ref(_tf32_round(a_v), _tf32_round(b_v), a_mn, b_mn)
+        trunc = _ref((a_v.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32),
+                     (b_v.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32), a_mn, b_mn)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    scale = max(1.0, raw.abs().max().item())
+    e_exact = min((out - rounded).abs().max().item(), (out - trunc).abs().max().item())
+    assert e_exact < 2e-5 * scale * max(1.0, K / 512), (e_exact, (out - raw).abs().max().item())
+    assert (out - raw).abs().max().item() < 2e-3 * scale * max(1.0, (K / 256) ** 0.5)
+
+
+def test_gemm_tf32_epilogue_accumulate_and_split_k():
+    from noeira_b200.ops import check_status, gemm
+    torch.manual_seed(3)
+    M, N, K = 384, 96, 160
+    a, b = torch.randn(M, K, device="cuda") * 0.3, torch.randn(K, N, device="cuda") * 0.3
+    bias = torch.randn(N, device="cuda")
+    y = gemm(a, b, b_mn=True, bias=bias, act="tanh")
+    ref = torch.tanh(_tf32_round(a) @ _tf32_round(b) + bias)
+    assert (y - ref).abs().max().item() < 2e-3
+    yb = gemm(a, b, b_mn=True, bias=bias, act="relu", out_dtype=torch.bfloat16, out=torch.empty(M, N, device="cuda", dtype=torch.bfloat16))
+    assert (yb.float() - torch.relu(a @ b + bias)).abs().max().item() < 3e-2
+    # weight-gradient form: accumulate x^T dy into fp32, deep K through the split-K path, bit-repeatable
+    x, dy = torch.randn(16384, 64, device="cuda") * 0.1, torch.randn(16384, 128, device="cuda") * 0.1
+    acc = torch.ones(64, 128, device="cuda")
+    gemm(x, dy, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    acc2 = torch.ones(64, 128, device="cuda")
+    gemm(x, dy, a_mn=True, b_mn=True, out=acc2, accumulate=True)
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(acc, acc2)
+    assert (acc - (1 + x.double().t() @ dy.double()).float()).abs().max().item() < 2e-2
