@@ -84,6 +84,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="ppo")
     ap.add_argument("--envs", type=int, default=4096)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "tf32"], help="precision of the policy / value networks: bf16 "
+                    "(fused three-layer kernels) or tf32 (fp32 activations and master weights on the TF32 tensor-core path)")
     ap.add_argument("--sync", default="fused", help="fused | nccl  (gradient reduction path for N>1)")
     ap.add_argument("--eager", action="store_true", help="secondary workloads: launch kernels one by one instead of replaying a graph")
     ap.add_argument("--small", action="store_true", help="reduced model for smoke runs of secondary workloads")
@@ -121,7 +123,7 @@ def main():
     from noeira_b200.ops import check_status
 
     env = PlanarChainEnv(args.envs, seed=1000 + rank, model_seed=0)
-    cfg = PPOConfig(n_envs=args.envs, rollout_len=32, n_epochs=4, n_minibatches=8, hidden=256, seed=0)
+    cfg = PPOConfig(n_envs=args.envs, rollout_len=32, n_epochs=4, n_minibatches=8, hidden=256, seed=0, precision=args.dtype)
     grad_sync = None
     if world > 1:
         from noeira_b200.parallel.ddp import make_grad_sync
@@ -202,7 +204,7 @@ def main():
         line = {
             "metric": "ppo_env_steps_per_s", "value": round(value, 1), "unit": "env-steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype,
             "data": "synthetic (seed-generated planar chain, random-init weights)",
             "config": {"model": "planar-chain 9-dof physics + actor-critic MLP 2x256 tanh", "envs_per_gpu": args.envs,
                        "global_batch": args.envs * world, "seq_len": 32, "rollout": 32, "epochs": 4, "minibatches": 8,

@@ -51,6 +51,7 @@ class PPOConfig:
     seed: int = 0
     use_cuda_graphs: bool = True
     fused_mlp: bool = True     # actor / critic forward as one fused three-layer kernel when the shapes allow it
+    precision: str = "bf16"    # "tf32": fp32 activations and master weights on the TF32 tensor-core path, layer by layer
 
 
 def make_actor(obs_dim, act_dim, hidden, log_std_init=-0.5):
@@ -124,14 +125,18 @@ class PPOTrainer:
         self.metrics = torch.zeros(8, **f)
         self._graphs = {}
         self._fused = {}
-        if cfg.fused_mlp and self.device.type == "cuda":
+        self._tf32 = cfg.precision == "tf32" and self.device.type == "cuda"
+        if self._tf32:
+            self.actor.set_attr("precision", "tf32")
+            self.critic.set_attr("precision", "tf32")
+        if cfg.fused_mlp and self.device.type == "cuda" and not self._tf32:
             from ..ops.mlp import fusable
             for net in (self.actor, self.critic):
                 self._fused[id(net)] = fusable(*self._layers(net))
         # fused update path: both networks through one grouped forward launch, one grouped data-gradient launch and
         # six parameter-gradient branches (one per layer) — see ops/mlp.py
         self._train_pass = None
-        if self._fused.get(id(self.actor)) and self._fused.get(id(self.critic)):
+        if self._fused.get(id(self.actor)) and self._fused.get(id(self.critic)) and not self._tf32:
             from ..ops.mlp import Mlp3Pass
             self._train_pass = (Mlp3Pass(*self._layers(self.actor), self.mb, self.device),
                                 Mlp3Pass(*self._layers(self.critic), self.mb, self.device))
@@ -155,7 +160,15 @@ class PPOTrainer:
             if hasattr(net.mods[2], "lin"):
                 net.mods[2]._mu = y
             return y
-        return net.forward(x)
+        return self._kernel_rows(net.forward(x))
+
+    def _kernel_rows(self, y):
+        """The loss / sampling / GAE kernels read network outputs as bf16 rows; the TF32 path produces fp32."""
+        if y.dtype == torch.bfloat16:
+            return y
+        out = torch.zeros(y.shape[0], (y.shape[1] + 7) // 8 * 8, device=y.device, dtype=torch.bfloat16)
+        out[:, : y.shape[1]] = y
+        return out[:, : y.shape[1]]
 
     def _rollout(self):
         cfg, env, lib = self.cfg, self.env, self.lib
@@ -176,7 +189,7 @@ class PPOTrainer:
     def _gae(self):
         cfg = self.cfg
         T, N = cfg.rollout_len, cfg.n_envs
-        v_all = self.critic.forward(self.obs_all.view((2 * T + 1) * N, -1))      # V(obs_t), V(obs_T), V(next_obs_t)
+        v_all = self._kernel_rows(self.critic.forward(self.obs_all.view((2 * T + 1) * N, -1)))      # V(obs_t), V(obs_T), V(next_obs_t)
         vnext = v_all[(T + 1) * N:]
         check(self.lib.nb_ppo_gae(ptr(self.rew_buf), ptr(self.done_buf), ptr(self.term_buf), ptr(v_all),
                                   ctypes.c_int(v_all.stride(0)),

@@ -127,6 +127,8 @@ class Linear(Module):
             self._saved = y if self.act in SAVES_OUTPUT else pre
             y = y.reshape(*lead, self.out_dim)
             return y if residual is None else y + residual
+        if self.attrs.get("precision") == "tf32":
+            return self._forward_tf32(x2, lead, residual)
         W = self.weight.shadow
         b = self.bias.storage if self.bias is not None else None
         xa = x2[:, : self.in_dim]
@@ -173,6 +175,8 @@ class Linear(Module):
             if fuse_dact is not None:
                 dx = dx * act_derivative_cpu(fuse_dact[0], fuse_dact[1].reshape(dx.shape[0], -1)[:, : self.in_dim].float())
             return dx.reshape(*self._lead, self.in_dim)
+        if self.attrs.get("precision") == "tf32":
+            return self._vjp_tf32(dy2, dy_is_pre, fuse_dact)
         if dy2.dtype != torch.bfloat16:
             dy2 = dy2.to(torch.bfloat16)
         if dy2.stride(-1) != 1 or (dy2.stride(0) * 2) % 16 != 0 or dy2.data_ptr() % 16 != 0:
@@ -206,6 +210,53 @@ class Linear(Module):
             aux = aux.reshape(dy2.shape[0], -1)
         ops.gemm(dyv, W[:, :n], out=dx, aux=aux, dact=dact, n=self.in_dim)
         dx = dx[:, : self.in_dim] if in_pad != self.in_dim else dx
+        return dx.reshape(*self._lead, self.in_dim) if len(self._lead) != 1 else dx
+
+    # ---- fp32 activations on the TF32 tensor-core path (``set_attr("precision", "tf32")``): the fp32 master weights are
+    # the operands, no bf16 shadow is read; activations, saved tensors and gradients stay fp32
+    @staticmethod
+    def _rows4(t):
+        """fp32 [M, n] with a 16-byte aligned base and row pitch (TMA): a padded copy only when needed."""
+        if t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(0) % 4 == 0 and t.data_ptr() % 16 == 0:
+            return t
+        out = torch.zeros(t.shape[0], (t.shape[1] + 3) // 4 * 4, device=t.device, dtype=torch.float32)
+        out[:, : t.shape[1]] = t
+        return out[:, : t.shape[1]]
+
+    def _forward_tf32(self, x2, lead, residual):
+        xa = self._rows4(x2[:, : self.in_dim])
+        self._x = xa
+        b = self.bias.storage if self.bias is not None else None
+        fuse = self.act is None or self.act in SAVES_OUTPUT or not torch.is_grad_enabled()
+        y = ops.gemm(xa, self.weight.storage, b_mn=True, bias=b, act=self.act if fuse else None)
+        if fuse:
+            self._saved = y
+        else:
+            self._saved = y
+            y = _ACT_CPU[self.act](y)
+        if self.out_pad != self.out_dim:
+            y = y[:, : self.out_dim]
+        y = y.reshape(*lead, self.out_dim) if len(lead) != 1 else y
+        return y if residual is None else y + residual
+
+    def _vjp_tf32(self, dy2, dy_is_pre, fuse_dact):
+        n = self.out_dim
+        d = dy2[:, :n].float()
+        if self.act is not None and not dy_is_pre:
+            d = d * act_derivative_cpu(self.act, self._saved[:, :n])
+        d = self._rows4(d)
+        if not self.weight.frozen:
+            ops.gemm(self._x, d, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=n)
+            if self.bias is not None:
+                self.bias.grad_storage[:n].add_(d.sum(0))
+        if not self.need_input_grad:
+            return None
+        in4 = (self.in_dim + 3) // 4 * 4
+        dx = (torch.empty if in4 == self.in_dim else torch.zeros)(d.shape[0], in4, device=d.device, dtype=torch.float32)
+        ops.gemm(d, self.weight.storage[:, :n], out=dx, n=self.in_dim)
+        dx = dx[:, : self.in_dim]
+        if fuse_dact is not None:
+            dx = dx * act_derivative_cpu(fuse_dact[0], fuse_dact[1].reshape(dx.shape[0], -1)[:, : self.in_dim].float())
         return dx.reshape(*self._lead, self.in_dim) if len(self._lead) != 1 else dx
 
     def _param_grads(self, dy2, dyv, n):

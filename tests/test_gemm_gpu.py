@@ -241,3 +241,41 @@ def test_gemm_tf32_epilogue_accumulate_and_split_k():
     check_status()
     assert torch.equal(acc, acc2)
     assert (acc - (1 + x.double().t() @ dy.double()).float()).abs().max().item() < 2e-2
+
+
+def test_linear_tf32_precision_mode_matches_fp32_reference():
+    """``set_attr("precision", "tf32")``: an MLP with fp32 activations on the TF32 path; forward, input gradient and
+    parameter gradients against plain fp32 PyTorch on the same weights."""
+    from noeira_b200 import nn
+    from noeira_b200.ops import check_status
+    nn.manual_seed(0)
+    net = nn.Sequential(nn.LinearTanh(22, 96), nn.LinearGELU(96, 64), nn.Linear(64, 6)).to("cuda")
+    net.set_attr("precision", "tf32")
+    torch.manual_seed(1)
+    x = torch.randn(300, 22, device="cuda")
+    dy = torch.randn(300, 6, device="cuda")
+    y = net.forward(x)
+    dx = net.vjp(dy)
+    torch.cuda.synchronize()
+    check_status()
+    assert y.dtype == torch.float32 and dx.dtype == torch.float32
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        xr = x.clone().requires_grad_(True)
+        Ws = [(m.weight.data.clone().requires_grad_(True), m.bias.data.clone().requires_grad_(True)) for m in net.mods]
+        h = torch.tanh(xr @ Ws[0][0] + Ws[0][1])
+        h = torch.nn.functional.gelu(h @ Ws[1][0] + Ws[1][1], approximate="tanh")
+        ref = h @ Ws[2][0] + Ws[2][1]
+        ref.backward(dy)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert (y - ref).abs().max().item() < 5e-3
+    assert (dx - xr.grad).abs().max().item() < 2e-2
+    for m, (W, b) in zip(net.mods, Ws):
+        assert (m.weight.grad - W.grad).abs().max().item() < 5e-2 * max(1.0, W.grad.abs().max().item())
+        assert (m.bias.grad - b.grad).abs().max().item() < 1e-3 * max(1.0, b.grad.abs().max().item())
+    # far closer to fp32 than the bf16 path of the same layers
+    net.set_attr("precision", None)
+    yb = net.forward(x.bfloat16()).float()
+    assert (y - ref).abs().max().item() < 0.5 * (yb - ref).abs().max().item()

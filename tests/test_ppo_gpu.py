@@ -110,3 +110,26 @@ def test_steady_state_iteration_allocates_nothing():
         tr.train_iteration(read_metrics=False)
         torch.cuda.synchronize()
     tracer.assert_steady("iteration")
+
+
+def test_ppo_tf32_precision_arm_tracks_the_bf16_arm():
+    """The same iterations with the policy / value networks on the TF32 path (fp32 activations and weights, layer by
+    layer) and on the fused bf16 path: both finite, same entropy, first-iteration losses close."""
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs import PlanarChainEnv
+    from noeira_b200.ops import check_status
+    out = {}
+    for prec in ("bf16", "tf32"):
+        env = PlanarChainEnv(1024, seed=3)
+        tr = PPOTrainer(env, PPOConfig(n_envs=1024, rollout_len=8, n_epochs=2, n_minibatches=2, hidden=256, seed=1,
+                                       precision=prec))
+        first = tr.train_iteration()
+        for _ in range(2):
+            last = tr.train_iteration()
+        torch.cuda.synchronize()
+        check_status()
+        assert torch.isfinite(tr.actor_opt.arena.val).all() and torch.isfinite(tr.critic_opt.arena.val).all()
+        out[prec] = (first, last)
+    a, b = out["bf16"][0], out["tf32"][0]
+    assert abs(a["entropy"] - b["entropy"]) < 1e-3
+    assert abs(a["value_loss"] - b["value_loss"]) < 0.1 * max(1.0, abs(a["value_loss"])), (a, b)
