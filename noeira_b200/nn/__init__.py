@@ -11,7 +11,8 @@ from .param import Param, State  # noqa: F401
 from .transformer import (AttentionCore, CrossAttention, Embedding, FeedForward, LayerNorm, MSELoss, RMSNorm,  # noqa: F401
                           SelfAttention, SwiGLU, SwiGLUFFN, TransformerBlock, cross_entropy, rope_, sincos_embed)
 from .conv import BasicBlock, BatchNorm2D, Conv2D, MaxPool2D, ResNet18Backbone, normalize_images  # noqa: F401
-from .graph import ComputeGraph, ExternalNode, InputSlot, Node  # noqa: F401
+from .graph import (ComputeGraph, ExternalNode, FusionReport, GraphExporter, InputSlot, MermaidExporter, Node,  # noqa: F401
+                    TextExporter)
 from . import schedulers  # noqa: F401
 from .peft import LoRALinear, QLinear, QLoRALinear, dequantize_q4_0, freeze_params, quantize_q4_0  # noqa: F401
 from .recurrent import GRUCell, LSTMCell, LSTMSeq  # noqa: F401

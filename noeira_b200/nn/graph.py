@@ -104,3 +104,97 @@ class ComputeGraph(Module):
 
     def display_label(self):
         return f"ComputeGraph[{len(self.slots)} inputs, {len(self.nodes)} nodes]"
+
+    # ------------------------------------------------------------------ exporters
+    def describe(self, exporter: "GraphExporter", name: str = "graph") -> str:
+        """Walk the declarations in order and let ``exporter`` render them
+        (noeira/nn/combinators/graph_export.mojo:95,171,266: text, Mermaid and fusion-report visitors)."""
+        exporter.begin(name, self)
+        for s in self.slots:
+            exporter.slot(s)
+        consumers: Dict[str, List[str]] = {}
+        for nd in self.nodes:
+            for i in nd.inputs:
+                consumers.setdefault(i, []).append(nd.name)
+        for nd in self.nodes:
+            label = nd.module.display_label() if nd.module is not None else f"external:{getattr(nd.fn, '__name__', 'fn')}"
+            n_params = sum(p.numel for p in nd.module.params()) if nd.module is not None else 0
+            exporter.node(nd.name, label, list(nd.inputs), n_params, consumers.get(nd.name, []))
+        return exporter.end()
+
+
+class GraphExporter:
+    def begin(self, name, graph): ...
+    def slot(self, name): ...
+    def node(self, name, label, inputs, n_params, consumers): ...
+    def end(self) -> str: return ""
+
+
+class TextExporter(GraphExporter):
+    """One line per declaration: ``name = Label(inputs)  [parameters]  -> consumers``."""
+
+    def begin(self, name, graph):
+        self.lines = [f"{name}: {graph.display_label()}"]
+
+    def slot(self, name):
+        self.lines.append(f"  input {name}")
+
+    def node(self, name, label, inputs, n_params, consumers):
+        tail = f"  [{n_params} params]" if n_params else ""
+        fan = f"  -> {', '.join(consumers)}" if consumers else "  -> (output)"
+        self.lines.append(f"  {name} = {label}({', '.join(inputs)}){tail}{fan}")
+
+    def end(self):
+        return "\n".join(self.lines)
+
+
+class MermaidExporter(GraphExporter):
+    """A ``flowchart TD`` document: rounded boxes for inputs, rectangles for nodes, one edge per use."""
+
+    @staticmethod
+    def _id(name):
+        return "n_" + "".join(c if c.isalnum() else "_" for c in name)
+
+    def begin(self, name, graph):
+        self.lines = ["flowchart TD"]
+
+    def slot(self, name):
+        self.lines.append(f'  {self._id(name)}(["{name}"])')
+
+    def node(self, name, label, inputs, n_params, consumers):
+        self.lines.append(f'  {self._id(name)}["{name}<br/>{label}"]')
+        for i in inputs:
+            self.lines.append(f"  {self._id(i)} --> {self._id(name)}")
+
+    def end(self):
+        return "\n".join(self.lines)
+
+
+class FusionReport(GraphExporter):
+    """Lists what an epilogue-fusing backend can merge: a node with a single consumer whose consumer is an elementwise
+    module (activation, bias add, scale, residual add) is a producer → epilogue pair; a value consumed more than once
+    needs gradient accumulation in the backward (fan-out)."""
+
+    ELEMENTWISE = ("Elementwise", "BiasAdd", "Scale", "Dropout", "external:add", "external:residual")
+
+    def begin(self, name, graph):
+        self.name, self.labels, self.inputs, self.consumers, self.order = name, {}, {}, {}, []
+
+    def node(self, name, label, inputs, n_params, consumers):
+        self.labels[name], self.inputs[name], self.consumers[name] = label, inputs, consumers
+        self.order.append(name)
+
+    def end(self):
+        pairs, fanout = [], []
+        for n in self.order:
+            cons = self.consumers[n]
+            if len(cons) == 1 and self.labels[cons[0]].startswith(self.ELEMENTWISE) and not self.labels[n].startswith(self.ELEMENTWISE):
+                pairs.append((n, cons[0]))
+            if len(cons) > 1:
+                fanout.append((n, len(cons)))
+        lines = [f"fusion report for {self.name}: {len(self.order)} nodes, {len(pairs)} producer/epilogue pairs, "
+                 f"{len(fanout)} fan-out values"]
+        lines += [f"  fuse {a} ({self.labels[a]}) + {b} ({self.labels[b]})" for a, b in pairs]
+        lines += [f"  fan-out {n} x{k}: gradient accumulation in backward" for n, k in fanout]
+        self.pairs, self.fanout = pairs, fanout
+        return "\n".join(lines)

@@ -48,6 +48,21 @@ def test_compute_graph_fanout_and_names():
     assert torch.allclose(G.node_output("b"), (h @ b.weight.data + b.bias.data).detach(), atol=1e-6)
 
 
+def test_compute_graph_exporters():
+    nn.manual_seed(0)
+    G = nn.ComputeGraph([nn.InputSlot("x"), nn.Node("lin", nn.Linear(5, 7), ["x"]), nn.Node("act", nn.Elementwise("tanh"), ["lin"]),
+                         nn.Node("b", nn.Linear(7, 3), ["act"]), nn.Node("c", nn.Linear(7, 3), ["act"]),
+                         nn.ExternalNode("sum", lambda u, v: u + v, lambda g, u, v: (g, g), ["b", "c"])])
+    text = G.describe(nn.TextExporter(), "toy")
+    assert "toy: ComputeGraph[1 inputs, 5 nodes]" in text and "lin = Linear[5,7](x)  [42 params]  -> act" in text
+    assert "sum = external:<lambda>(b, c)  -> (output)" in text
+    mm = G.describe(nn.MermaidExporter())
+    assert mm.startswith("flowchart TD") and "n_x --> n_lin" in mm and mm.count("-->") == 6
+    rep = nn.FusionReport()
+    out = G.describe(rep, "toy")
+    assert rep.pairs == [("lin", "act")] and rep.fanout == [("act", 2)] and "fuse lin" in out
+
+
 def test_schedulers():
     s = nn.schedulers.WarmupCosine(1.0, 10, 110, 0.1)
     assert abs(s(0) - 0.1) < 1e-9 and abs(s(9) - 1.0) < 1e-9
