@@ -5,7 +5,7 @@ from .init import (Constant, Deterministic, Kaiming, Normal, Orthogonal, ScaledK
                    Zero)
 from .layers import (BiasAdd, Dropout, advance_rng, rng_step_counter, Elementwise, GaussianHead, Linear, LinearGELU, LinearReLU, LinearTanh,  # noqa: F401
                      Scale)
-from .module import Module, as_autograd, manual_seed  # noqa: F401
+from .module import Module, apply, as_autograd, manual_seed  # noqa: F401
 from .optim import SGD, Adam, AdamW, LaProp, ScalarAdam, polyak  # noqa: F401
 from .param import Param, State  # noqa: F401
 from .transformer import (AttentionCore, CrossAttention, Embedding, FeedForward, LayerNorm, MSELoss, RMSNorm,  # noqa: F401

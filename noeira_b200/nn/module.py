@@ -216,3 +216,41 @@ class AutogradBridge(torch.autograd.Function):
 
 def as_autograd(module: Module, *xs):
     return AutogradBridge.apply(module, *xs)
+
+
+class RecomputeBridge(torch.autograd.Function):
+    """Re-entrant form of ``AutogradBridge`` for modules that are applied SEVERAL times inside one autograd graph (an
+    unrolled latent model, a shared head): a module caches one set of activations, so each application keeps only its
+    inputs and runs the module's forward again right before its ``vjp`` (activation checkpointing per application).
+    Parameter gradients of all applications add up in ``Param.grad``."""
+
+    @staticmethod
+    def forward(ctx, module, anchor, *xs):
+        ctx.module = module
+        ctx.xs = tuple(x.detach() if torch.is_tensor(x) else x for x in xs)
+        return module.forward(*ctx.xs)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        with torch.enable_grad():                 # layers skip saving activations when no backward can follow
+            ctx.module.forward(*ctx.xs)
+        with torch.no_grad():
+            g = ctx.module.vjp(*gs)
+        if not isinstance(g, (tuple, list)):
+            g = (g,)
+        g = tuple(g) + (None,) * (len(ctx.xs) - len(g))
+        return (None, None) + tuple(gi if torch.is_tensor(x) and x.is_floating_point() else None for gi, x in zip(g, ctx.xs))
+
+
+_ANCHOR = {}
+
+
+def apply(module: Module, *xs):
+    """``module(*xs)`` as a differentiable torch operation that may be repeated within one graph (see ``RecomputeBridge``).
+    The parameters are not torch leaves, so an application on inputs that carry no gradient (an encoder on observations)
+    would be cut out of the graph; a constant anchor that requires grad keeps it in."""
+    dev = next((x.device for x in xs if torch.is_tensor(x)), torch.device("cpu"))
+    a = _ANCHOR.get(dev)
+    if a is None:
+        a = _ANCHOR[dev] = torch.zeros((), device=dev, requires_grad=True)
+    return RecomputeBridge.apply(module, a, *xs)
