@@ -160,15 +160,7 @@ class PPOTrainer:
             if hasattr(net.mods[2], "lin"):
                 net.mods[2]._mu = y
             return y
-        return self._kernel_rows(net.forward(x))
-
-    def _kernel_rows(self, y):
-        """The loss / sampling / GAE kernels read network outputs as bf16 rows; the TF32 path produces fp32."""
-        if y.dtype == torch.bfloat16:
-            return y
-        out = torch.zeros(y.shape[0], (y.shape[1] + 7) // 8 * 8, device=y.device, dtype=torch.bfloat16)
-        out[:, : y.shape[1]] = y
-        return out[:, : y.shape[1]]
+        return net.forward(x)          # both heads write fp32 rows (what the sampling / loss / GAE kernels read) on either path
 
     def _rollout(self):
         cfg, env, lib = self.cfg, self.env, self.lib
@@ -189,7 +181,7 @@ class PPOTrainer:
     def _gae(self):
         cfg = self.cfg
         T, N = cfg.rollout_len, cfg.n_envs
-        v_all = self._kernel_rows(self.critic.forward(self.obs_all.view((2 * T + 1) * N, -1)))      # V(obs_t), V(obs_T), V(next_obs_t)
+        v_all = self.critic.forward(self.obs_all.view((2 * T + 1) * N, -1))      # V(obs_t), V(obs_T), V(next_obs_t)
         vnext = v_all[(T + 1) * N:]
         check(self.lib.nb_ppo_gae(ptr(self.rew_buf), ptr(self.done_buf), ptr(self.term_buf), ptr(v_all),
                                   ctypes.c_int(v_all.stride(0)),

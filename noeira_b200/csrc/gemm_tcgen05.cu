@@ -355,7 +355,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t idesc = make_idesc(p.tf32 ? 2u : 1u, BM, BN, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
       // one instruction consumes 32 bytes of K: 16 bf16 or 8 tf32.  K-major: 32 bytes further inside the swizzle row;
       // MN-major: that many k-rows of 128 bytes further, chunks of MN one k-block of rows apart
+      // an MN-major TF32 operand is in the 32-byte-atom form of the 128-byte swizzle (descriptor layout 1): its pattern
+      // repeats every 4 k-rows, so the stride between row groups is 512 bytes instead of 1024
       const uint32_t kadv_mn = p.tf32 ? 8u * 128u : 16u * 128u, lbo_mn = p.tf32 ? 32u * 128u : 64u * 128u;
+      const uint32_t sbo_mn = p.tf32 ? 512u : 1024u, lay_mn = p.tf32 ? 1u : 2u;
       const bool tf32 = p.tf32 != 0;
       int stage = 0;
       uint32_t phase = 0;
@@ -376,9 +379,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // K-major: advance 32 bytes inside the 128B swizzle row; MN-major: 16 k-rows of 128 B
-            const uint64_t adesc = p.a_mn ? make_smem_desc(sa + k * kadv_mn, lbo_mn, 1024, 2)
+            const uint64_t adesc = p.a_mn ? make_smem_desc(sa + k * kadv_mn, lbo_mn, sbo_mn, lay_mn)
                                           : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
-            const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * kadv_mn, lbo_mn, 1024, 2)
+            const uint64_t bdesc = p.b_mn ? make_smem_desc(sb + k * kadv_mn, lbo_mn, sbo_mn, lay_mn)
                                           : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
             if (tf32) umma_tf32(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
             else umma_f16(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
@@ -788,8 +791,10 @@ EncodeTiledFn get_encode() {
 }
 
 // 2-D bf16 tensor map: inner extent `inner` (contiguous), outer extent `outer`, row pitch `ld` elements.
+// `mn_major` matters for 32-bit elements only: an MN-major TF32 operand has to use the 128-byte swizzle with 32-byte
+// atoms (two-bit XOR of the 32-byte chunk index with the row index modulo 4); every other operand uses the 16-byte-atom form
 int make_tmap_elt(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
-                  int box_outer, int elt_bytes) {
+                  int box_outer, int elt_bytes, int mn_major = 0) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return NB_ERR_NO_DRIVER_SYMBOL;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * elt_bytes) & 15)) return NB_ERR_UNALIGNED;
@@ -799,8 +804,9 @@ int make_tmap_elt(CUtensorMap* tm, const void* base, long long inner, long long 
   cuuint32_t estr[2] = {1, 1};
   // fp32 operands are loaded as TFLOAT32: the copy rounds them to the 10-bit mantissa the tensor core reads
   CUresult r = enc(tm, elt_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                   const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   (elt_bytes == 4 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? NB_OK : NB_ERR_TENSORMAP;
 }
@@ -929,10 +935,10 @@ static int gemm_any(int tf32, const void* A, const void* B, void* D, int M, int 
   CUtensorMap tmA, tmB;
   int rc;
   if (!a_mn) rc = make_tmap_elt(&tmA, A, K, M, lda, bk, BM, elt);
-  else rc = make_tmap_elt(&tmA, A, M, K, lda, bk, bk, elt);
+  else rc = make_tmap_elt(&tmA, A, M, K, lda, bk, bk, elt, 1);
   if (rc) return rc;
   if (!b_mn) rc = make_tmap_elt(&tmB, B, K, N, ldb, bk, BN, elt);
-  else rc = make_tmap_elt(&tmB, B, N, K, ldb, bk, bk, elt);
+  else rc = make_tmap_elt(&tmB, B, N, K, ldb, bk, bk, elt, 1);
   if (rc) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;

@@ -330,6 +330,11 @@ class GaussianHead(Module):
     def _moved(self, device):
         self.lin.device = device
 
+    def _attr_changed(self, name, value):
+        self.lin.attrs[name] = value            # the inner layer is not a registered child (its parameters are exposed here)
+        if name == "training":
+            self.lin.training = bool(value)
+
     def forward(self, x):
         self._mu = self.lin.forward(x)
         return self._mu

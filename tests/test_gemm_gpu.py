@@ -249,10 +249,10 @@ def test_linear_tf32_precision_mode_matches_fp32_reference():
     from noeira_b200 import nn
     from noeira_b200.ops import check_status
     nn.manual_seed(0)
-    net = nn.Sequential(nn.LinearTanh(22, 96), nn.LinearGELU(96, 64), nn.Linear(64, 6)).to("cuda")
+    net = nn.Sequential(nn.LinearTanh(24, 96), nn.LinearGELU(96, 64), nn.Linear(64, 6)).to("cuda")
     net.set_attr("precision", "tf32")
     torch.manual_seed(1)
-    x = torch.randn(300, 22, device="cuda")
+    x = torch.randn(300, 24, device="cuda")
     dy = torch.randn(300, 6, device="cuda")
     y = net.forward(x)
     dx = net.vjp(dy)
