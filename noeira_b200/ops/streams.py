@@ -34,9 +34,11 @@ class Branch:
         self.stream, self.slot_id = stream, slot_id
         self._ctx = None
         self._keep = []
+        self._forked = False
 
     def __enter__(self):
         self.stream.wait_stream(torch.cuda.current_stream())
+        self._forked = True
         self._old = slot()
         _TLS.slot = self.slot_id
         self._ctx = torch.cuda.stream(self.stream)
@@ -54,5 +56,9 @@ class Branch:
         self._keep.extend(tensors)
 
     def join(self):
-        torch.cuda.current_stream().wait_stream(self.stream)
+        """A join without a fork since the last join is a no-op: waiting on a stream that took no part in the current
+        capture would make the capture depend on uncaptured work."""
+        if self._forked:
+            torch.cuda.current_stream().wait_stream(self.stream)
+            self._forked = False
         self._keep.clear()

@@ -1,0 +1,221 @@
+"""General rigid-body engine: agreement with the hinge / slide oracle, conservation laws for free and ball joints,
+collision geometry, resting / sliding / colliding contacts with both solvers, joint limits, integrators, sensors."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from noeira_b200.physics import general as G
+from noeira_b200.physics.model import Body, Geom, Joint, Options
+
+
+def _free_box(opt=None, half=(0.2, 0.1, 0.05), z=1.0, plane=False, friction=1.0):
+    b = Body(parent=-1, pos=(0, 0, z), joints=[Joint(G.FREE, (0, 0, 1), name="root")],
+             geoms=[Geom("box", half, friction=friction)])
+    return G.GeneralModel([b], opt=opt or Options(timestep=0.002), plane=plane)
+
+
+def test_mass_matrix_and_bias_match_the_hinge_slide_oracle():
+    from noeira_b200.physics import oracle
+    from noeira_b200.physics.model import planar_chain
+    rm = planar_chain(seed=2)
+    gm = G.GeneralModel(rm.bodies, opt=rm.opt, plane=False)
+    assert gm.nv == rm.nv
+    rng = np.random.default_rng(0)
+    q = rm.qpos0 + rng.normal(0, 0.4, rm.nv)
+    v = rng.normal(0, 1.0, rm.nv)
+    k = G.kinematics(gm, torch.tensor(q)[None], torch.tensor(v)[None])
+    M = G.mass_matrix(gm, k)[0].numpy()
+    c = G.bias_force(gm, k, torch.tensor(v)[None])[0].numpy()
+    Mo = oracle.mass_matrix(rm, q)
+    co = oracle.bias_force(rm, q, v)
+    Mo = Mo + np.diag(rm.dof_armature) if np.abs(np.diag(M) - np.diag(Mo)).max() > 1e-9 else Mo
+    assert np.abs(M - Mo).max() < 1e-8 * max(1.0, np.abs(Mo).max())
+    assert np.abs(c - co).max() < 2e-5 * max(1.0, np.abs(co).max())          # the oracle differentiates numerically
+
+
+def test_kinetic_energy_from_body_velocities_equals_quadratic_form():
+    """½ vᵀ M v (Jacobians) against Σ ½ m |v_com|² + ½ ωᵀ I ω (the recursive velocity pass): two code paths."""
+    bodies = [Body(-1, (0, 0, 1), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("box", (0.2, 0.1, 0.05))]),
+              Body(0, (0.3, 0, 0), joints=[Joint(G.BALL, (0, 0, 1), pos=(-0.1, 0, 0))], geoms=[Geom("capsule", (0.04, 0.15), pos=(0.1, 0, 0))]),
+              Body(1, (0.3, 0, 0), quat=(0.9238795, 0, 0.3826834, 0), joints=[Joint(G.HINGE, (0, 1, 0), pos=(0, 0.02, 0)), Joint(G.SLIDE, (1, 0, 0))],
+                   geoms=[Geom("sphere", (0.07,), pos=(0.05, 0, 0.02))])]
+    m = G.GeneralModel(bodies, plane=False)
+    assert (m.nq, m.nv) == (7 + 4 + 2, 6 + 3 + 2)
+    g = torch.Generator().manual_seed(0)
+    q, v = m.init_state(3)
+    q[:, 3:7] = torch.nn.functional.normalize(torch.randn(3, 4, generator=g, dtype=torch.float64), dim=-1)
+    q[:, 7:11] = torch.nn.functional.normalize(torch.randn(3, 4, generator=g, dtype=torch.float64), dim=-1)
+    q[:, 11:] = torch.randn(3, 2, generator=g, dtype=torch.float64) * 0.3
+    v = torch.randn(3, m.nv, generator=g, dtype=torch.float64)
+    k = G.kinematics(m, q, v)
+    M = G.mass_matrix(m, k)
+    T1 = 0.5 * (v[:, None] @ M @ v[:, :, None])[:, 0, 0]
+    Iw = G.world_inertia(m, k)
+    T2 = (0.5 * m.mass[None] * (k.v_com ** 2).sum(-1)).sum(1) + 0.5 * (k.w_body[:, :, None] @ Iw @ k.w_body[..., None])[..., 0, 0].sum(1)
+    assert torch.allclose(T1, T2, rtol=1e-10)
+    # velocities from the Jacobians equal the recursive ones
+    Jv, Jw = G.body_jacobians(m, k)
+    assert torch.allclose((Jv @ v[:, None, :, None])[..., 0], k.v_com, atol=1e-10)
+    assert torch.allclose((Jw @ v[:, None, :, None])[..., 0], k.w_body, atol=1e-10)
+
+
+@pytest.mark.parametrize("integrator,tol,etol", [("rk4", 5e-4, 1e-5), ("euler", 0.1, 0.05)])
+def test_conservation_laws_of_a_free_chain(integrator, tol, etol):
+    """No gravity: linear and angular momentum and the energy of a tumbling free body with a ball-jointed and a hinged link.
+    (The errors shrink with the step: second order for Runge-Kutta with averaged body-frame rates, first order for Euler.)"""
+    opt = Options(timestep=0.002, gravity=(0, 0, 0))
+    bodies = [Body(-1, (0, 0, 0), joints=[Joint(G.FREE, (0, 0, 1))], mass=2.0, inertia=(0.02, 0.05, 0.04)),
+              Body(0, (0.3, 0, 0), joints=[Joint(G.BALL, (0, 0, 1))], mass=1.0, inertia=(0.01, 0.02, 0.015), ipos=(0.1, 0.05, 0)),
+              Body(1, (0.2, 0.1, 0), joints=[Joint(G.HINGE, (0, 0.6, 0.8))], mass=0.5, inertia=(0.004, 0.006, 0.005), ipos=(0, 0.1, 0.05))]
+    m = G.GeneralModel(bodies, opt=opt, plane=False)
+    sim = G.GeneralSim(m, 2, integrator=integrator)
+    g = torch.Generator().manual_seed(1)
+    sim.qvel = torch.randn(2, m.nv, generator=g, dtype=torch.float64) * torch.tensor([0.3] * 3 + [2.0] * 7)
+
+    def momenta():
+        k = G.kinematics(m, sim.qpos, sim.qvel)
+        P = (m.mass[None, :, None] * k.v_com).sum(1)
+        Iw = G.world_inertia(m, k)
+        L = (torch.linalg.cross(k.com, m.mass[None, :, None] * k.v_com) + (Iw @ k.w_body[..., None])[..., 0]).sum(1)
+        T, U = G.energy(m, sim.qpos, sim.qvel)
+        return P, L, T + U
+
+    P0, L0, E0 = momenta()
+    for _ in range(300):
+        sim.step()
+    P1, L1, E1 = momenta()
+    assert torch.allclose(P0, P1, atol=tol) and torch.allclose(L0, L1, atol=tol)
+    assert ((E1 - E0).abs() / E0 < etol).all()
+
+
+def test_spherical_pendulum_energy_and_hinge_period():
+    opt = Options(timestep=0.002)
+    ball = G.GeneralModel([Body(-1, (0, 0, 2), joints=[Joint(G.BALL, (0, 0, 1))], mass=1.0, inertia=(0.01, 0.01, 0.01), ipos=(0, 0, -0.5))],
+                          opt=opt, plane=False)
+    sim = G.GeneralSim(ball, 1, integrator="rk4")
+    sim.qvel = torch.tensor([[1.5, -0.7, 0.9]], dtype=torch.float64)
+    E0 = sum(G.energy(ball, sim.qpos, sim.qvel))
+    for _ in range(500):
+        sim.step()
+    E1 = sum(G.energy(ball, sim.qpos, sim.qvel))
+    assert abs(float(E1 - E0)) < 1e-6 * abs(float(E0))
+    # point-mass hinge pendulum, small angle: period 2π sqrt(l / g)
+    L = 0.8
+    hinge = G.GeneralModel([Body(-1, (0, 0, 2), joints=[Joint(G.HINGE, (0, 1, 0))], mass=1.0, inertia=(1e-9, 1e-9, 1e-9), ipos=(0, 0, -L))],
+                           opt=opt, plane=False)
+    sim = G.GeneralSim(hinge, 1, integrator="rk4")
+    sim.qpos[:, 0] = 0.02
+    prev, crossings = float(sim.qpos[0, 0]), []
+    for i in range(2200):
+        sim.step()
+        cur = float(sim.qpos[0, 0])
+        if prev > 0 >= cur:
+            crossings.append(i * opt.timestep + opt.timestep * prev / (prev - cur))
+        prev = cur
+    period = crossings[1] - crossings[0]
+    assert abs(period - 2 * math.pi * math.sqrt(L / 9.81)) < 2e-3
+
+
+def test_segment_distance_against_dense_sampling():
+    g = torch.Generator().manual_seed(0)
+    p1, d1, p2, d2 = (torch.randn(64, 3, generator=g, dtype=torch.float64) for _ in range(4))
+    d2[:8] = d1[:8] * 0.7                                           # parallel segments
+    d1[8:12] = 0                                                    # a point against a segment
+    c1, c2 = G.closest_segment_points(p1, d1, p2, d2)
+    s = torch.linspace(0, 1, 201, dtype=torch.float64)
+    a = p1[:, None, None] + s[None, :, None, None] * d1[:, None, None]
+    b = p2[:, None, None] + s[None, None, :, None] * d2[:, None, None]
+    brute = (a - b).norm(dim=-1).reshape(64, -1).min(1).values
+    got = (c1 - c2).norm(dim=-1)
+    assert (got <= brute + 1e-9).all() and (brute - got < 2e-2).all()
+
+
+@pytest.mark.parametrize("solver", ["pgs", "newton"])
+def test_resting_box_sliding_friction_and_touch(solver):
+    opt = Options(timestep=0.002, solref=(0.01, 1.0))
+    m = _free_box(opt, z=0.05, plane=True, friction=0.5)
+    sim = G.GeneralSim(m, 2, integrator="euler", solver=solver, solver_iters=60 if solver == "pgs" else 20)
+    sim.qvel[1, 0] = 2.0                                            # env 1 slides along x
+    xs = []
+    for i in range(400):
+        sim.step()
+        xs.append(float(sim.qvel[1, 0]))
+    mass = float(m.mass[0])
+    s = sim.sensors(0)
+    assert abs(float(sim.qpos[0, 2]) - 0.05) < 2e-3 and float(sim.qvel[0].abs().max()) < 1e-3      # at rest on its face
+    assert abs(float(s["touch"][0]) - mass * 9.81) < 0.02 * mass * 9.81                             # the plane carries the weight
+    assert abs(float(s["accelerometer"][0, 2]) - 9.81) < 0.2                                        # proper acceleration at rest
+    # Coulomb friction: deceleration μ g until it stops (box friction on two axes bounds it by μ g √2)
+    t_stop = next(i for i, v in enumerate(xs) if v < 1e-3) * opt.timestep
+    assert 2.0 / (0.5 * 9.81 * 1.45) < t_stop < 2.0 / (0.5 * 9.81) * 1.1, t_stop
+    assert abs(float(sim.qvel[1, 0])) < 1e-3 and float(sim.qpos[1, 0]) > 0.25
+
+
+def test_solvers_agree_on_the_contact_forces():
+    opt = Options(timestep=0.002)
+    bodies = [Body(-1, (0, 0, 0.1), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("capsule", (0.1, 0.3), quat=(0.70710678, 0, 0.70710678, 0))]),
+              Body(-1, (0.05, 0.02, 0.28), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("sphere", (0.1,))])]
+    m = G.GeneralModel(bodies, opt=opt, plane=True)
+    assert len(m.pairs) == 1
+    q, v = m.init_state(1)
+    v[0, 8] = -0.3
+    out = {}
+    for solver, it in (("pgs", 400), ("newton", 30)):
+        sim = G.GeneralSim(m, 1, solver=solver, solver_iters=it)
+        sim.forward(q, v)
+        out[solver] = (sim.last["force"].clone(), sim.last["qacc"].clone())
+    assert out["newton"][0].max() > 1.0
+    assert torch.allclose(out["pgs"][0], out["newton"][0], atol=2e-3 * float(out["newton"][0].abs().max()))
+    assert torch.allclose(out["pgs"][1], out["newton"][1], atol=1e-2)
+
+
+def test_sphere_sphere_collision_conserves_momentum_and_separates():
+    opt = Options(timestep=0.001, gravity=(0, 0, 0), solref=(0.005, 0.3))
+    mk = lambda x: Body(-1, (x, 0, 0), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("sphere", (0.1,), friction=0.0)])
+    m = G.GeneralModel([mk(-0.3), mk(0.3)], opt=opt, plane=False)
+    sim = G.GeneralSim(m, 1)
+    sim.qvel[0, 0], sim.qvel[0, 6] = 1.0, -0.5
+    p0 = float(sim.qvel[0, 0] + sim.qvel[0, 6])
+    for _ in range(800):
+        sim.step()
+    assert abs(float(sim.qvel[0, 0] + sim.qvel[0, 6]) - p0) < 1e-9          # equal masses: Σ v conserved
+    assert float(sim.qvel[0, 0]) < float(sim.qvel[0, 6])                       # they separated
+    assert float(sim.qpos[0, 7] - sim.qpos[0, 0]) > 0.2 - 1e-3
+
+
+def test_joint_limit_and_implicit_damping():
+    opt = Options(timestep=0.002)
+    j = Joint(G.HINGE, (0, 1, 0), range=(-0.5, 0.5), damping=0.0, name="h")
+    m = G.GeneralModel([Body(-1, (0, 0, 1), joints=[j], mass=1.0, inertia=(0.01, 0.01, 0.01), ipos=(0.3, 0, 0))], opt=opt, plane=False)
+    sim = G.GeneralSim(m, 1)
+    lo = 0.0
+    for _ in range(1500):
+        sim.step()
+        lo = max(lo, float(sim.qpos[0, 0]))
+    assert 0.5 < lo < 0.56 and abs(float(sim.qpos[0, 0]) - 0.5) < 0.03       # gravity pushes it into the upper stop and it stays there
+    # stiff damping: explicit Euler diverges at this step size, the implicit form decays
+    jd = Joint(G.HINGE, (0, 1, 0), damping=40.0, name="h")
+    md = G.GeneralModel([Body(-1, (0, 0, 1), joints=[jd], mass=1.0, inertia=(0.01, 0.01, 0.01))], opt=Options(timestep=0.002, gravity=(0, 0, 0)), plane=False)
+    res = {}
+    for integ in ("euler", "implicit"):
+        s2 = G.GeneralSim(md, 1, integrator=integ)
+        s2.qvel[0, 0] = 1.0
+        for _ in range(50):
+            s2.step()
+        res[integ] = abs(float(s2.qvel[0, 0]))
+    assert res["implicit"] < 1e-3 and res["euler"] > 1e3
+
+
+def test_motor_and_sensors_on_a_spinning_body():
+    opt = Options(timestep=0.002, gravity=(0, 0, 0))
+    j = Joint(G.HINGE, (0, 0, 1), name="spin")
+    m = G.GeneralModel([Body(-1, (0, 0, 0), joints=[j], mass=1.0, inertia=(0.1, 0.1, 0.2))], motors=[G.Motor("spin", gear=2.0)], opt=opt, plane=False)
+    sim = G.GeneralSim(m, 1, integrator="rk4")
+    for _ in range(100):
+        sim.step(torch.tensor([[0.5]]))
+    w = 2.0 * 0.5 / 0.2 * 0.2                                                 # τ / I · t
+    s = sim.sensors(0)
+    assert abs(float(sim.qvel[0, 0]) - w) < 1e-9 and abs(float(s["gyro"][0, 2]) - w) < 0.02
+    assert float(s["actuatorfrc"][0, 0]) == 1.0 and s["jointpos"].shape == (1, 1)
