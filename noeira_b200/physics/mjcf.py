@@ -89,8 +89,10 @@ def _quat_of(attrs, degrees):
     return np.array([1.0, 0, 0, 0])
 
 
-def from_mjcf(source: str, opt: Optional[Options] = None) -> RigidModel:
-    """``source``: a file path or an XML string."""
+def from_mjcf(source: str, opt: Optional[Options] = None, general: bool = False):
+    """``source``: a file path or an XML string.  By default the result is a ``RigidModel`` for the fused step (hinge / slide
+    trees, capsule / sphere geoms); ``general=True`` also accepts free and ball joints (``<freejoint/>``, ``type="free"`` /
+    ``"ball"``) and box geoms and returns a ``physics.general.GeneralModel``."""
     if source.lstrip().startswith("<"):
         root, base_dir = ET.fromstring(source), "."
     else:
@@ -139,7 +141,10 @@ def from_mjcf(source: str, opt: Optional[Options] = None) -> RigidModel:
                         fr, dens, rgba, contact)
         if typ == "sphere":
             return Geom("sphere", (size[0],), tuple(_floats(a.get("pos", "0 0 0"), 3)), (1.0, 0, 0, 0), fr, dens, rgba, contact)
-        raise MjcfError(f"geom type {typ!r} is not supported (capsule, sphere; plane at world level)")
+        if typ == "box" and general:
+            return Geom("box", tuple(size[:3]), tuple(_floats(a.get("pos", "0 0 0"), 3)), tuple(_quat_of(a, degrees)), fr, dens, rgba,
+                        contact)
+        raise MjcfError(f"geom type {typ!r} is not supported (capsule, sphere; box in the general engine; plane at world level)")
 
     def parse_body(elem, parent, childclass):
         cc = elem.get("childclass", childclass)
@@ -149,8 +154,13 @@ def from_mjcf(source: str, opt: Optional[Options] = None) -> RigidModel:
             if ch.tag == "joint":
                 a = defaults.resolve("joint", ch, cc)
                 jt = a.get("type", "hinge")
+                if jt in ("free", "ball") and general:
+                    from .general import BALL, FREE
+                    joints.append(Joint(FREE if jt == "free" else BALL, (0.0, 0.0, 1.0), tuple(_floats(a.get("pos", "0 0 0"), 3)),
+                                        name=a.get("name", f"joint{len(bodies)}_{len(joints)}")))
+                    continue
                 if jt not in ("hinge", "slide"):
-                    raise MjcfError(f"joint type {jt!r} is not supported (hinge, slide)")
+                    raise MjcfError(f"joint type {jt!r} is not supported (hinge, slide; free / ball in the general engine)")
                 rng = None
                 if "range" in a and a.get("limited", "auto") != "false":
                     r = _floats(a["range"], 2)
@@ -168,8 +178,11 @@ def from_mjcf(source: str, opt: Optional[Options] = None) -> RigidModel:
                 ipos = tuple(_floats(ch.get("pos", "0 0 0"), 3))
                 if "diaginertia" in ch.attrib:
                     inertia = tuple(_floats(ch.get("diaginertia"), 3))
-            elif ch.tag == "freejoint" or (ch.tag == "joint" and ch.get("type") in ("free", "ball")):
-                raise MjcfError("free / ball joints are not supported (nq == nv trees only)")
+            elif ch.tag == "freejoint":
+                if not general:
+                    raise MjcfError("free / ball joints are not supported by the fused step (nq == nv trees only): general=True")
+                from .general import FREE
+                joints.append(Joint(FREE, (0.0, 0.0, 1.0), name=ch.get("name", f"joint{len(bodies)}_{len(joints)}")))
             elif ch.tag not in ("body", "site", "camera", "light"):
                 raise MjcfError(f"<{ch.tag}> inside <body> is not supported")
         idx = len(bodies)
@@ -199,4 +212,7 @@ def from_mjcf(source: str, opt: Optional[Options] = None) -> RigidModel:
                 raise MjcfError(f"actuator <{m.tag}> is not supported (motor)")
             a = defaults.resolve("motor", m, None)
             acts.append(Actuator(a["joint"], _floats(a.get("gear", "1"))[0], tuple(_floats(a.get("ctrlrange", "-1 1"), 2))))
+    if general:
+        from .general import GeneralModel, Motor
+        return GeneralModel(bodies, [Motor(a.joint, a.gear, tuple(a.ctrlrange)) for a in acts], o)
     return RigidModel(bodies, acts, o)

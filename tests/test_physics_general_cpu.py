@@ -219,3 +219,23 @@ def test_motor_and_sensors_on_a_spinning_body():
     s = sim.sensors(0)
     assert abs(float(sim.qvel[0, 0]) - w) < 1e-9 and abs(float(s["gyro"][0, 2]) - w) < 0.02
     assert float(s["actuatorfrc"][0, 0]) == 1.0 and s["jointpos"].shape == (1, 1)
+
+
+def test_mjcf_with_free_and_ball_joints_and_boxes():
+    from noeira_b200.physics.mjcf import MjcfError, from_mjcf
+    xml = """<mujoco><compiler angle="radian"/><option timestep="0.002"/>
+      <worldbody><geom type="plane" pos="0 0 0" size="5 5 0.1"/>
+        <body name="base" pos="0 0 0.3"><freejoint name="root"/><geom type="box" size="0.2 0.1 0.05"/>
+          <body name="arm" pos="0.2 0 0.05"><joint type="ball" name="shoulder"/><geom type="capsule" fromto="0 0 0 0.3 0 0" size="0.03"/>
+            <body name="hand" pos="0.3 0 0"><joint type="hinge" axis="0 1 0" range="-1 1" name="wrist"/><geom type="sphere" size="0.04"/></body>
+          </body></body></worldbody>
+      <actuator><motor joint="wrist" gear="3"/></actuator></mujoco>"""
+    m = from_mjcf(xml, general=True)
+    assert (m.nb, m.nq, m.nv) == (3, 12, 10) and len(m.motors) == 1 and m.limits[0][0] == 9
+    with pytest.raises(MjcfError):
+        from_mjcf(xml)
+    sim = G.GeneralSim(m, 2, solver="newton")
+    for _ in range(300):
+        sim.step(torch.tensor([[0.3], [-0.3]]))
+    assert torch.isfinite(sim.qpos).all() and float(sim.qpos[:, 2].min()) > 0.03           # the box landed on the plane and stayed
+    assert abs(float(sim.qpos[0, 3:7].norm()) - 1) < 1e-9
