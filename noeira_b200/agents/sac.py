@@ -131,8 +131,94 @@ class SACTrainer:
         return a
 
     # ------------------------------------------------------------------ update
+    # ------------------------------------------------------------------ update on the device: GEMMs + glue kernels only
+    def _glue(self, B):
+        """Buffers of the kernel path for batch size ``B`` (allocated once: a captured update keeps their addresses)."""
+        g = getattr(self, "_glue_buf", None)
+        if g is None or g["B"] != B:
+            c, dev = self.cfg, self.device
+            f = dict(device=dev, dtype=torch.float32)
+            h = dict(device=dev, dtype=torch.bfloat16)
+            nblk = (B + 255) // 256
+            g = self._glue_buf = dict(
+                B=B, sa=torch.zeros(B, self._pad, **h), sa2=torch.zeros(B, self._pad, **h), act=torch.zeros(B, c.act_dim, **f),
+                logp=torch.zeros(B, **f), logp2=torch.zeros(B, **f), y=torch.zeros(B, **f),
+                ysq=torch.zeros(B, c.act_dim, **f), sdz=torch.zeros(B, c.act_dim, **f),
+                free=torch.zeros(B, c.act_dim, device=dev, dtype=torch.uint8), dq1=torch.zeros(B, 8, **h), dq2=torch.zeros(B, 8, **h),
+                dpacked=torch.zeros(B, (2 * c.act_dim + 7) // 8 * 8, **h), partials=torch.zeros(3 * nblk + 8, **f),
+                closs=torch.zeros(1, **f), stats=torch.zeros(3, **f))
+        return g
+
+    def _update_kernels(self, s, a, r, sp, d):
+        """The same update as ``update`` with every elementwise stage in ``csrc/sac_kernels.cu``: sample + log-probability +
+        critic input rows in one launch, target, critic gradients, critic choice for the actor loss, and the squashed
+        Gaussian's backward; reductions are two-pass and deterministic."""
+        import ctypes
+        from .._native import check, cuda_lib, ptr, stream_ptr
+        cfg, lib, B = self.cfg, cuda_lib(), s.shape[0]
+        O, A, ci = cfg.obs_dim, cfg.act_dim, ctypes.c_int
+        g = self._glue(B)
+        s, a, sp = s.float().contiguous(), a.float().contiguous(), sp.float().contiguous()
+        r, d = r.float().contiguous(), d.float().contiguous()
+        alpha = self.alpha_opt.alpha
+        st = stream_ptr()
+        scale = ctypes.c_float(cfg.action_scale)
+
+        def sample(obs, noise, sa, logp, save):
+            packed = self.actor.forward(self._act_in(obs))
+            packed = packed if packed.dtype == torch.float32 else packed.float()
+            check(lib.nb_sac_sample(ptr(packed), ci(packed.stride(0)), ptr(noise), ptr(obs), ci(obs.stride(0)), ptr(g["act"]), ptr(logp),
+                                    ptr(g["ysq"]) if save else None, ptr(g["sdz"]) if save else None, ptr(g["free"]) if save else None,
+                                    ptr(sa), ci(sa.stride(0)), ci(B), ci(O), ci(A), scale, st), "sac_sample")
+
+        def qpair(q1, q2, sa):
+            x = sa[:, : O + A]
+            return q1.forward(x), q2.forward(x)
+
+        # ---- target
+        sample(sp, self._noise(B), g["sa"], g["logp"], False)
+        q1t, q2t = qpair(self.q1t, self.q2t, g["sa"])
+        check(lib.nb_sac_target(ptr(q1t), ci(q1t.stride(0)), ptr(q2t), ci(q2t.stride(0)), ptr(g["logp"]), ptr(r), ptr(d), ptr(alpha),
+                                ctypes.c_float(cfg.gamma), ptr(g["y"]), ci(B), st), "sac_target")
+        # ---- critics
+        check(lib.nb_sac_pack_sa(ptr(s), ci(s.stride(0)), ptr(a), ci(a.stride(0)), ptr(g["sa2"]), ci(g["sa2"].stride(0)), ci(B), ci(O),
+                                 ci(A), st), "sac_pack_sa")
+        q1v, q2v = qpair(self.q1, self.q2, g["sa2"])
+        check(lib.nb_sac_critic_grad(ptr(q1v), ci(q1v.stride(0)), ptr(q2v), ci(q2v.stride(0)), ptr(g["y"]), ptr(g["dq1"]), ptr(g["dq2"]),
+                                     ci(8), ptr(g["partials"]), ptr(g["closs"]), ci(B), st), "sac_critic_grad")
+        self.q1.vjp(g["dq1"][:, :1])
+        self.q2.vjp(g["dq2"][:, :1])
+        self.critic_opt.step(zero_grad=True)
+        # ---- actor (critic parameters fixed)
+        sample(s, self._noise(B), g["sa"], g["logp2"], True)
+        q1v, q2v = qpair(self.q1, self.q2, g["sa"])
+        check(lib.nb_sac_actor_qgrad(ptr(q1v), ci(q1v.stride(0)), ptr(q2v), ci(q2v.stride(0)), ptr(g["logp2"]), ptr(alpha), ptr(g["dq1"]),
+                                     ptr(g["dq2"]), ci(8), ptr(g["partials"]), ptr(g["stats"]), ci(B), st), "sac_actor_qgrad")
+        ps = [p for q in (self.q1, self.q2) for p in q.params()]
+        for p in ps:
+            p.frozen = True
+        d1 = self.q1.vjp(g["dq1"][:, :1])
+        d2 = self.q2.vjp(g["dq2"][:, :1])
+        for p in ps:
+            p.frozen = False
+        d1 = d1 if d1.dtype == torch.bfloat16 else d1.to(torch.bfloat16)
+        d2 = d2 if d2.dtype == torch.bfloat16 else d2.to(torch.bfloat16)
+        check(lib.nb_sac_dist_bwd(ptr(d1), ci(d1.stride(0)), ptr(d2), ci(d2.stride(0)), ptr(g["ysq"]), ptr(g["sdz"]), ptr(g["free"]),
+                                  ptr(alpha), ptr(g["dpacked"]), ci(g["dpacked"].stride(0)), ci(B), ci(O), ci(A), scale, st),
+              "sac_dist_bwd")
+        self.actor.vjp(g["dpacked"][:, : 2 * A])
+        self.actor_opt.step(zero_grad=True)
+        if cfg.auto_entropy:
+            self.alpha_opt.step_alpha(g["stats"][1:2], self.target_entropy)
+        nn.polyak(self.target_arena, self.critic_opt.arena, cfg.tau)
+        self.total_train_steps += 1
+        self.metrics = dict(critic_loss=g["closs"][0], actor_loss=g["stats"][0], mean_q=g["stats"][2], mean_logp=g["stats"][1])
+        return self.metrics
+
     def update(self, s, a, r, sp, d):
         cfg = self.cfg
+        if self.device.type == "cuda" and getattr(self, "use_kernels", True):
+            return self._update_kernels(s, a, r, sp, d)
         B = s.shape[0]
         alpha = float(self.alpha) if self.device.type == "cpu" else self.alpha
         # ---- target
