@@ -133,3 +133,18 @@ def test_ppo_tf32_precision_arm_tracks_the_bf16_arm():
     a, b = out["bf16"][0], out["tf32"][0]
     assert abs(a["entropy"] - b["entropy"]) < 1e-3
     assert abs(a["value_loss"] - b["value_loss"]) < 0.1 * max(1.0, abs(a["value_loss"])), (a, b)
+
+
+def test_ppo_learns_the_planar_chain_task():
+    """Convergence gate: the mean reward per step of the planar-chain locomotion task starts negative and must be clearly
+    positive after 50 iterations of 1024 envs x 32 steps (measured: about -0.3 at the start, 1.4 to 1.7 at iteration 50,
+    above 4 at iteration 80, for two seeds)."""
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs import PlanarChainEnv
+    env = PlanarChainEnv(1024, seed=1)
+    tr = PPOTrainer(env, PPOConfig(n_envs=1024, rollout_len=32, n_epochs=4, n_minibatches=8, hidden=256, seed=1))
+    first = tr.train_iteration()["mean_step_reward"]
+    for _ in range(49):
+        last = tr.train_iteration()
+    assert first < 0.0 and last["mean_step_reward"] > 0.5, (first, last)
+    assert last["mean_step_reward"] > first + 0.8
