@@ -235,6 +235,61 @@ bn_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
   }
 }
 
+// Average pooling with window K, stride = K (non-overlapping) on NHWC: forward averages, backward spreads dy / K².
+// `back != 0`: `src` is dy [B, OH, OW, C] and `dst` is dx [B, H, W, C] (pixels outside the pooled area get zero).
+__global__ void __launch_bounds__(256)
+avgpool_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int B, int H, int W, int C, int K, int OH,
+               int OW, int back) {
+  const long long total = back ? (long long)B * H * W * C : (long long)B * OH * OW * C, step = (long long)gridDim.x * blockDim.x;
+  const float inv = 1.f / (float)(K * K);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int c = (int)(i % C);
+    long long r = i / C;
+    if (back) {
+      const int w = (int)(r % W); r /= W;
+      const int h = (int)(r % H);
+      const int b = (int)(r / H);
+      const int oh = h / K, ow = w / K;
+      dst[i] = (oh < OH && ow < OW) ? __float2bfloat16(__bfloat162float(src[(((long long)b * OH + oh) * OW + ow) * C + c]) * inv)
+                                    : __float2bfloat16(0.f);
+    } else {
+      const int ow = (int)(r % OW); r /= OW;
+      const int oh = (int)(r % OH);
+      const int b = (int)(r / OH);
+      float acc = 0.f;
+      for (int kh = 0; kh < K; ++kh)
+        for (int kw = 0; kw < K; ++kw)
+          acc += __bfloat162float(src[(((long long)b * H + oh * K + kh) * W + ow * K + kw) * C + c]);
+      dst[i] = __float2bfloat16(acc * inv);
+    }
+  }
+}
+// Nearest-neighbour upsampling by an integer factor S on NHWC: forward replicates, backward sums the S x S block.
+__global__ void __launch_bounds__(256)
+upsample_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int B, int H, int W, int C, int S, int back) {
+  const int OH = H * S, OW = W * S;
+  const long long total = back ? (long long)B * H * W * C : (long long)B * OH * OW * C, step = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int c = (int)(i % C);
+    long long r = i / C;
+    if (back) {
+      const int w = (int)(r % W); r /= W;
+      const int h = (int)(r % H);
+      const int b = (int)(r / H);
+      float acc = 0.f;
+      for (int kh = 0; kh < S; ++kh)
+        for (int kw = 0; kw < S; ++kw)
+          acc += __bfloat162float(src[(((long long)b * OH + h * S + kh) * OW + w * S + kw) * C + c]);
+      dst[i] = __float2bfloat16(acc);
+    } else {
+      const int ow = (int)(r % OW); r /= OW;
+      const int oh = (int)(r % OH);
+      const int b = (int)(r / OH);
+      dst[i] = src[(((long long)b * H + oh / S) * W + ow / S) * C + c];
+    }
+  }
+}
+
 // 3x3 / stride 2 / pad 1 style max pooling on NHWC; idx stores the flat input offset of the maximum
 __global__ void __launch_bounds__(256)
 maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int* __restrict__ idx, int B, int H,
@@ -423,6 +478,21 @@ int nb_maxpool_bwd(const void* dy, const int* idx, void* dx, int B, int H, int W
   else
     maxpool_bwd_kernel<1><<<g1((long long)B * H * W * C), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dy, idx, (__nv_bfloat16*)dx, B, H, W, C, K, stride, pad, OH, OW);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+int nb_avgpool(const void* src, void* dst, int B, int H, int W, int C, int K, int OH, int OW, int back, void* stream) {
+  if (K <= 0 || OH * K > H || OW * K > W) return NB_ERR_BAD_ARG;
+  const long long total = back ? (long long)B * H * W * C : (long long)B * OH * OW * C;
+  avgpool_kernel<<<g1(total), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, B, H, W, C, K, OH, OW, back);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+// H, W are the LOW-resolution sizes in both directions
+int nb_upsample_nearest(const void* src, void* dst, int B, int H, int W, int C, int S, int back, void* stream) {
+  if (S <= 0) return NB_ERR_BAD_ARG;
+  const long long total = back ? (long long)B * H * W * C : (long long)B * H * S * W * S * C;
+  upsample_kernel<<<g1(total), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, B, H, W, C, S, back);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

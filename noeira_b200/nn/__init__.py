@@ -10,7 +10,8 @@ from .optim import SGD, Adam, AdamW, LaProp, ScalarAdam, polyak  # noqa: F401
 from .param import Param, State  # noqa: F401
 from .transformer import (AttentionCore, CrossAttention, Embedding, FeedForward, LayerNorm, MSELoss, RMSNorm,  # noqa: F401
                           SelfAttention, SwiGLU, SwiGLUFFN, TransformerBlock, cross_entropy, rope_, sincos_embed)
-from .conv import BasicBlock, BatchNorm2D, Conv2D, MaxPool2D, ResNet18Backbone, normalize_images  # noqa: F401
+from .conv import (AvgPool2D, BasicBlock, BatchNorm2D, Conv2D, Conv2DTranspose, MaxPool2D, ResNet18Backbone, Upsample2D,  # noqa: F401
+                   normalize_images)
 from .graph import (ComputeGraph, ExternalNode, FusionReport, GraphExporter, InputSlot, MermaidExporter, Node,  # noqa: F401
                     TextExporter)
 from . import schedulers  # noqa: F401

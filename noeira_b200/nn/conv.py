@@ -294,6 +294,163 @@ class MaxPool2D(Module):
         return dx
 
 
+class AvgPool2D(Module):
+    """Non-overlapping K x K average pooling on NHWC (a trailing partial window is dropped)."""
+
+    def __init__(self, k=2):
+        super().__init__()
+        self.k = k
+
+    def forward(self, x):
+        B, H, W, C = x.shape
+        OH, OW = H // self.k, W // self.k
+        self._in = (B, H, W, C)
+        if not x.is_cuda:
+            return x[:, : OH * self.k, : OW * self.k].reshape(B, OH, self.k, OW, self.k, C).float().mean((2, 4))
+        xc = x if x.is_contiguous() else x.contiguous()
+        y = torch.empty(B, OH, OW, C, device=x.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_avgpool(ptr(xc), ptr(y), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, OH, OW, 0)), stream_ptr()), "avgpool")
+        return y
+
+    def vjp(self, dy):
+        B, H, W, C = self._in
+        OH, OW = H // self.k, W // self.k
+        if not dy.is_cuda:
+            dx = torch.zeros(B, H, W, C)
+            dx[:, : OH * self.k, : OW * self.k] = (dy.float() / (self.k * self.k)).repeat_interleave(self.k, 1).repeat_interleave(self.k, 2)
+            return dx
+        d = dy if (dy.is_contiguous() and dy.dtype == torch.bfloat16) else dy.to(torch.bfloat16).contiguous()
+        dx = torch.empty(B, H, W, C, device=dy.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_avgpool(ptr(d), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, C, self.k, OH, OW, 1)), stream_ptr()), "avgpool_bwd")
+        return dx
+
+
+class Upsample2D(Module):
+    """Nearest-neighbour upsampling by an integer factor on NHWC."""
+
+    def __init__(self, scale=2):
+        super().__init__()
+        self.s = scale
+
+    def forward(self, x):
+        B, H, W, C = x.shape
+        self._in = (B, H, W, C)
+        if not x.is_cuda:
+            return x.repeat_interleave(self.s, 1).repeat_interleave(self.s, 2)
+        xc = x if x.is_contiguous() else x.contiguous()
+        y = torch.empty(B, H * self.s, W * self.s, C, device=x.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_upsample_nearest(ptr(xc), ptr(y), *(ctypes.c_int(v) for v in (B, H, W, C, self.s, 0)), stream_ptr()), "upsample")
+        return y
+
+    def vjp(self, dy):
+        B, H, W, C = self._in
+        if not dy.is_cuda:
+            return dy.float().reshape(B, H, self.s, W, self.s, C).sum((2, 4))
+        d = dy if (dy.is_contiguous() and dy.dtype == torch.bfloat16) else dy.to(torch.bfloat16).contiguous()
+        dx = torch.empty(B, H, W, C, device=dy.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_upsample_nearest(ptr(d), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, C, self.s, 1)), stream_ptr()), "upsample_bwd")
+        return dx
+
+
+class Conv2DTranspose(Module):
+    """Transposed convolution on NHWC: the adjoint of ``Conv2D(oc → ic, k, stride, pad)``.  Output size
+    ``(H − 1)·stride − 2·pad + k``.  On CUDA the forward is the data-gradient path of the convolution (GEMM with the weight,
+    then the deterministic gather-style col2im), the input gradient is the convolution's forward (patch gather + GEMM),
+    the weight gradient one GEMM on the patches of dy.  Weight in the GEMM layout of the adjoint convolution
+    ``[k·k·oc_pad, ic]``; files hold the torch layout ``[ic, oc, k, k]``.
+    (noeira/nn/primitives/conv2d_transpose.mojo)"""
+
+    def __init__(self, ic, oc, k, stride=1, pad=0, bias=True, relu=False, need_input_grad=True):
+        super().__init__()
+        self.ic, self.oc, self.k, self.stride, self.pad, self.relu = ic, oc, k, stride, pad, relu
+        self.ocp = (oc + 7) // 8 * 8
+        self.need_input_grad = need_input_grad
+        self.weight = self.add_param("weight", (k * k * self.ocp, ic), decay=True, init=Kaiming(), fan_in=ic * k * k, fan_out=oc)
+        if self.ocp != oc:
+            self.weight.data.view(k * k, self.ocp, ic)[:, oc:, :] = 0
+        self.bias = self.add_param("bias", (oc,), decay=False, init=Zero()) if bias else None
+        ocp, KK = self.ocp, k
+        self.weight.to_file = lambda t: t.view(KK, KK, ocp, ic)[:, :, :oc, :].permute(3, 2, 0, 1).contiguous()
+        self.weight.from_file = lambda t: torch.nn.functional.pad(t.reshape(ic, oc, KK, KK).permute(2, 3, 1, 0),
+                                                                  (0, 0, 0, ocp - oc)).reshape(KK * KK * ocp, ic)
+
+    def out_hw(self, H, W):
+        return (H - 1) * self.stride - 2 * self.pad + self.k, (W - 1) * self.stride - 2 * self.pad + self.k
+
+    def _w_torch(self):
+        return self.weight.data.view(self.k, self.k, self.ocp, self.ic)[:, :, : self.oc].permute(3, 2, 0, 1)      # [ic, oc, k, k]
+
+    def forward(self, x):
+        B, H, W, C = x.shape
+        assert C == self.ic
+        OH, OW = self.out_hw(H, W)
+        self._in = (B, H, W)
+        if not self.on_cuda:
+            self._x = x.float()
+            y = torch.nn.functional.conv_transpose2d(self._x.permute(0, 3, 1, 2), self._w_torch(),
+                                                     self.bias.data if self.bias is not None else None, self.stride, self.pad).permute(0, 2, 3, 1)
+            self._y = torch.relu(y) if self.relu else y
+            return self._y
+        M, K = B * H * W, self.k * self.k * self.ocp
+        x2 = x.reshape(M, C)
+        x2 = x2 if (x2.stride(-1) == 1 and x2.dtype == torch.bfloat16 and (x2.stride(0) * 2) % 16 == 0) else _rows16(x2)
+        self._x2 = x2
+        dcol = ops.gemm(x2, self.weight.shadow[:, : self.ic])                    # [M, K] = x · Wᵀ
+        y = torch.empty(B, OH, OW, self.ocp, device=x.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_col2im(ptr(dcol), ptr(y), *(ctypes.c_int(v) for v in (B, OH, OW, self.ocp, self.k, self.k, self.stride,
+                                                                              self.pad, H, W, K)), stream_ptr()), "col2im")
+        y = y[..., : self.oc]
+        if self.bias is not None:
+            y = y + self.bias.data.to(torch.bfloat16)
+        if self.relu:
+            y = torch.relu(y)
+        self._y = y
+        return y
+
+    def vjp(self, dy):
+        B, H, W = self._in
+        OH, OW = self.out_hw(H, W)
+        if not self.on_cuda:
+            g = dy.float()
+            if self.relu:
+                g = g * (self._y > 0)
+            gn, xn, w = g.permute(0, 3, 1, 2), self._x.permute(0, 3, 1, 2), self._w_torch()
+            if not self.weight.frozen:
+                gw = torch.nn.grad.conv2d_weight(gn, w.shape, xn, self.stride, self.pad)          # adjoint conv: input dy, output x
+                self.weight.grad.view(self.k, self.k, self.ocp, self.ic)[:, :, : self.oc].add_(gw.permute(2, 3, 1, 0))
+                if self.bias is not None:
+                    self.bias.grad.add_(g.sum((0, 1, 2)))
+            if not self.need_input_grad:
+                return None
+            return torch.nn.functional.conv2d(gn, w, None, self.stride, self.pad).permute(0, 2, 3, 1)
+        g = dy
+        if self.relu:
+            g = g * (self._y > 0)
+        M, K = B * H * W, self.k * self.k * self.ocp
+        gp = torch.zeros(B, OH, OW, self.ocp, device=dy.device, dtype=torch.bfloat16)
+        gp[..., : self.oc] = g
+        col = torch.empty(M, K, device=dy.device, dtype=torch.bfloat16)
+        check(cuda_lib().nb_im2col(ptr(gp), ptr(col), *(ctypes.c_int(v) for v in (B, OH, OW, self.ocp, self.k, self.k, self.stride,
+                                                                              self.pad, H, W, K)), stream_ptr()), "im2col")
+        if not self.weight.frozen:
+            ops.gemm(col, self._x2, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=self.ic)
+            if self.bias is not None:
+                self.bias.grad_storage[: self.oc].add_(g.float().sum((0, 1, 2)))
+        if not self.need_input_grad:
+            return None
+        dx = ops.gemm(col, self.weight.shadow, b_mn=True)
+        return dx[:, : self.ic].reshape(B, H, W, self.ic)
+
+    def _release(self):
+        self._x = self._x2 = self._y = None
+
+
+def _rows16(t):
+    out = torch.zeros(t.shape[0], (t.shape[1] + 7) // 8 * 8, device=t.device, dtype=torch.bfloat16)
+    out[:, : t.shape[1]] = t
+    return out[:, : t.shape[1]]
+
+
 class BasicBlock(Module):
     """conv3x3-bn-relu, conv3x3-bn, (+ 1x1 downsample), add, relu — children named as in torchvision."""
 
