@@ -19,14 +19,30 @@
 #define NB2D_HD inline
 #endif
 
-namespace nb2d {
+// The capacities are compile-time constants of the including translation unit: an environment with more bodies defines
+// NB2D_MAX_BODIES / NB2D_MAX_JOINTS / NB2D_MAX_TERRAIN and its own namespace name NB2D_NS before the include, so that two
+// environments with different capacities can live in one library.
+#ifndef NB2D_NS
+#define NB2D_NS nb2d
+#endif
+#ifndef NB2D_MAX_BODIES
+#define NB2D_MAX_BODIES 4
+#endif
+#ifndef NB2D_MAX_JOINTS
+#define NB2D_MAX_JOINTS 3
+#endif
+#ifndef NB2D_MAX_TERRAIN
+#define NB2D_MAX_TERRAIN 16
+#endif
 
-constexpr int MAX_BODIES = 4;
-constexpr int MAX_JOINTS = 3;
+namespace NB2D_NS {
+
+constexpr int MAX_BODIES = NB2D_MAX_BODIES;
+constexpr int MAX_JOINTS = NB2D_MAX_JOINTS;
 constexpr int MAX_VERTS = 6;
 constexpr int CONTACTS_PER_BODY = 2;
 constexpr int MAX_CONTACTS = MAX_BODIES * CONTACTS_PER_BODY;
-constexpr int MAX_TERRAIN = 16;
+constexpr int MAX_TERRAIN = NB2D_MAX_TERRAIN;
 
 struct Body {
   float x, y, a;          // pose (centre of mass, angle)
@@ -379,4 +395,4 @@ NB2D_HD void step(World& w) {
   w.sleep_time = slow ? w.sleep_time + dt : 0.f;
 }
 
-}  // namespace nb2d
+}  // namespace NB2D_NS

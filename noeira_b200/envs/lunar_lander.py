@@ -18,6 +18,7 @@ from .batched_env import BatchedEnv
 
 class LunarLanderEnv(BatchedEnv):
     obs_dim, act_dim = 8, 2
+    _name = "lunar"                # entry points nb_<name>_* (CUDA library) and nbh_<name>_* (host library)
 
     def __init__(self, n_envs: int, device="cuda", seed: int = 0):
         self.n_envs, self.device, self.seed = int(n_envs), torch.device(device), int(seed)
@@ -25,22 +26,25 @@ class LunarLanderEnv(BatchedEnv):
         if self.on_cuda:
             from .._native import cuda_lib
             self.lib = cuda_lib()
-            nbytes = int(self.lib.nb_lunar_state_bytes())
+            nbytes = int(self._fn("state_bytes")())
         else:
             from .._native import host_lib
             self.lib = host_lib()
-            nbytes = int(self.lib.nbh_lunar_state_bytes())
+            nbytes = int(self._fn("state_bytes")())
         self.state = torch.zeros(self.n_envs, nbytes, dtype=torch.uint8, device=self.device)
         self._alloc_io(self.device)
         self.engine = self            # the PPO device rollout drives an environment through ``env.engine.step``
 
+    def _fn(self, what):
+        return getattr(self.lib, f"{'nb' if self.on_cuda else 'nbh'}_{self._name}_{what}")
+
     def reset_batch(self):
         from .._native import check, ptr, stream_ptr
         if self.on_cuda:
-            check(self.lib.nb_lunar_reset(ptr(self.state), ctypes.c_int(self.n_envs), ctypes.c_uint(self.seed), ptr(self.obs),
-                                          ptr(self.obs_bf16), ctypes.c_int(self.obs_pad), stream_ptr()), "lunar_reset")
+            check(self._fn("reset")(ptr(self.state), ctypes.c_int(self.n_envs), ctypes.c_uint(self.seed), ptr(self.obs),
+                                          ptr(self.obs_bf16), ctypes.c_int(self.obs_pad), stream_ptr()), f"{self._name}_reset")
         else:
-            self.lib.nbh_lunar_reset(ptr(self.state), ctypes.c_int(self.n_envs), ctypes.c_uint(self.seed), ptr(self.obs))
+            self._fn("reset")(ptr(self.state), ctypes.c_int(self.n_envs), ctypes.c_uint(self.seed), ptr(self.obs))
             self.obs_bf16[:, : self.obs_dim].copy_(self.obs)
         return self.obs
 
@@ -51,17 +55,17 @@ class LunarLanderEnv(BatchedEnv):
         assert action.dtype == torch.float32 and action.stride(-1) == 1
         c = ctypes
         if self.on_cuda:
-            check(self.lib.nb_lunar_step(ptr(self.state), c.c_int(self.n_envs), c.c_uint(self.seed), ptr(action),
+            check(self._fn("step")(ptr(self.state), c.c_int(self.n_envs), c.c_uint(self.seed), ptr(action),
                                          c.c_int(action.stride(0)), ptr(reward), ptr(done), ptr(terminated), ptr(obs_f32),
                                          ptr(obs_bf16), ptr(next_obs_f32), ptr(next_obs_bf16),
                                          c.c_int((obs_bf16 if obs_bf16 is not None else self.obs_bf16).stride(0)),
                                          ptr(finished_return), ptr(ep_stats), c.c_int(1 if do_reset else 0), stream_ptr()),
-                  "lunar_step")
+                  f"{self._name}_step")
             return
         obs = obs_f32 if obs_f32 is not None else torch.empty_like(self.obs)
         nxt = next_obs_f32 if next_obs_f32 is not None else torch.empty_like(self.obs)
         fr = finished_return if finished_return is not None else torch.empty_like(self.reward)
-        self.lib.nbh_lunar_step(ptr(self.state), c.c_int(self.n_envs), c.c_uint(self.seed), ptr(action), c.c_int(action.stride(0)),
+        self._fn("step")(ptr(self.state), c.c_int(self.n_envs), c.c_uint(self.seed), ptr(action), c.c_int(action.stride(0)),
                                 ptr(reward), ptr(done), ptr(terminated), ptr(obs), ptr(nxt), ptr(fr), c.c_int(1 if do_reset else 0))
         if obs_bf16 is not None:
             obs_bf16[:, : self.obs_dim].copy_(obs)
@@ -84,3 +88,18 @@ class LunarLanderEnv(BatchedEnv):
     def lander_pose(self) -> torch.Tensor:
         """[N, 6] x, y, angle, vx, vy, omega of the hull (state inspection in tests)."""
         return self.state.view(torch.float32)[:, :6].clone() if self.state.shape[1] % 4 == 0 else None
+
+
+class BipedalWalkerEnv(LunarLanderEnv):
+    """BipedalWalker: hull + two two-segment legs on motorised revolute joints, rolling random terrain, 10 lidar rays;
+    observation (24), actions = four motor commands (sign = direction, magnitude = torque fraction), reward 130·Δx/30 minus
+    posture and torque costs, −100 when the hull touches the ground.  Same structure as the lander: one CUDA thread per
+    environment (``csrc/bipedal_walker.cu``), the same source on the host (``csrc/host/bipedal_host.cpp``).
+    Reference: noeira/envs/bipedal_walker/."""
+    obs_dim, act_dim = 24, 4
+    _name = "bipedal"
+
+    def hull_pose(self) -> torch.Tensor:
+        return self.state.view(torch.float32)[:, :6].clone()
+
+    lander_pose = hull_pose
