@@ -15,7 +15,8 @@ from .conv import (AvgPool2D, BasicBlock, BatchNorm2D, Conv2D, Conv2DTranspose, 
 from .graph import (ComputeGraph, ExternalNode, FusionReport, GraphExporter, InputSlot, MermaidExporter, Node,  # noqa: F401
                     TextExporter)
 from . import schedulers  # noqa: F401
-from .peft import LoRALinear, QLinear, QLoRALinear, dequantize_q4_0, freeze_params, quantize_q4_0  # noqa: F401
+from .peft import (LoRALinear, QLinear, QLoRALinear, add_lora, dequantize_q4_0, freeze_params, quantize_linears,  # noqa: F401
+                   quantize_q4_0, replace_linears)
 from .recurrent import GRUCell, LSTMCell, LSTMSeq  # noqa: F401
 from . import losses  # noqa: F401
 from .noisy import BlockLinear, NoisyLinear, reset_noise  # noqa: F401

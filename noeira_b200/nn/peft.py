@@ -188,3 +188,57 @@ class QLinear(Module):
 
 def QLoRALinear(linear: Linear, rank: int = 16, alpha: float = 32.0) -> LoRALinear:
     return LoRALinear(QLinear(linear), rank, alpha)
+
+
+# ------------------------------------------------------------------------------------------ adapter / quantisation slots
+def replace_linears(module: Module, factory, predicate=lambda path, lin: True, prefix: str = "") -> int:
+    """Replaces every plain ``Linear`` below ``module`` whose dotted path passes ``predicate`` by ``factory(linear)``: in
+    the child registry and in every attribute (or list attribute) of the parent that holds the same object, so that model
+    code written against ``self.q_proj`` / ``self.mods[i]`` picks the wrapper up.  Returns the number of replacements.
+    (The reference gives each decoder linear an adapter slot and a quantised slot at compile time,
+    noeira/deep_agents/smolvla/layer_weights.mojo:30-105; here the slot is filled at run time.)"""
+    n = 0
+    for key, child in list(module._children.items()):
+        path = prefix + key
+        if type(child) is Linear:
+            if not predicate(path, child):
+                continue
+            new = factory(child)
+            new.device = child.device
+            module._children[key] = new
+            for attr, val in list(vars(module).items()):
+                if val is child:
+                    setattr(module, attr, new)
+                elif isinstance(val, list):
+                    for i, v in enumerate(val):
+                        if v is child:
+                            val[i] = new
+            n += 1
+        else:
+            n += replace_linears(child, factory, predicate, path + ".")
+    return n
+
+
+def add_lora(module: Module, rank: int = 16, alpha: float = 32.0, predicate=lambda path, lin: True) -> int:
+    """LoRA adapters on the selected linears (their base weights are frozen); the adapters are the only trainable
+    parameters they add: ``<path>.lora_A.weight``, ``<path>.lora_B.weight``."""
+    return replace_linears(module, lambda lin: LoRALinear(lin, rank=rank, alpha=alpha), predicate)
+
+
+def quantize_linears(module: Module, predicate=lambda path, lin: lin.out_dim % 32 == 0, calibration=None, lora_rank: int = 0,
+                     alpha: float = 32.0) -> int:
+    """Q4_0 weights on the selected linears (``calibration``: ``{path: inputs}`` quantises those layers by GPTQ); with
+    ``lora_rank`` every quantised layer also carries a trainable adapter (QLoRA)."""
+    cal, paths = calibration or {}, {}
+
+    def pred(path, lin):
+        ok = predicate(path, lin)
+        if ok:
+            paths[id(lin)] = path
+        return ok
+
+    def factory(lin):
+        q = QLinear(lin, calibration=cal.get(paths.get(id(lin))))
+        return LoRALinear(q, lora_rank, alpha) if lora_rank else q
+
+    return replace_linears(module, factory, pred)
