@@ -38,6 +38,10 @@ class MuZeroConfig:
     temperature: float = 1.0
     max_grad_norm: float = 5.0
     seed: int = 0
+    # EfficientZero-style options: Gumbel root search with sequential halving (acting and policy targets), and a
+    # self-supervised consistency loss −cos(ĥ_{t+k}, sg(h(o_{t+k}))) that ties the unrolled latents to the encoder
+    gumbel: bool = False
+    consistency_coef: float = 0.0
 
 
 def _mlp(i, h, o):
@@ -109,8 +113,11 @@ class MuZeroAgent:
     # ---- step-wise interface of the generic on-policy driver
     @torch.no_grad()
     def select_action_batched(self, obs, greedy: bool = False):
-        policy, value, action = self.mcts.search(obs.to(self.device), temperature=0.0 if greedy else self.cfg.temperature,
-                                                 generator=self.gen)
+        if self.cfg.gumbel:
+            policy, value, action = self.mcts.search_gumbel(obs.to(self.device), generator=self.gen, greedy=greedy)
+        else:
+            policy, value, action = self.mcts.search(obs.to(self.device), temperature=0.0 if greedy else self.cfg.temperature,
+                                                     generator=self.gen)
         self._pending = (policy, value)
         return action
 
@@ -157,7 +164,8 @@ class MuZeroAgent:
         hs, raws, acts, alive_k = [h], [raw0], [], []
         alive = torch.ones(B, device=self.device)
         dpred, dhead = [], []
-        loss_p = loss_v = loss_r = 0.0
+        dcons = [None] * (K + 1)
+        loss_p = loss_v = loss_r = loss_c = 0.0
         for k in range(K + 1):
             tt = t0 + k
             out = self.pred.forward(self._inp(hs[k])).float()
@@ -182,6 +190,16 @@ class MuZeroAgent:
             dhead.append(c.reward_coef * 2.0 * w * (r_pred - r_true))
             raws.append(y[:, : c.latent])
             hs.append(_scale01(y[:, : c.latent]))
+            if c.consistency_coef > 0:
+                with torch.no_grad():
+                    tgt = _scale01(self.repr.forward(self._inp(self.obs_buf[(tt + 1) % W, e])).float())
+                hk = hs[-1].detach().requires_grad_(True)
+                wn = alive * (1 - self.done_buf[tt % W, e]) / (B * K)
+                with torch.enable_grad():
+                    lc = -(wn * torch.nn.functional.cosine_similarity(hk, tgt, dim=-1)).sum()
+                    lc.backward()
+                dcons[k + 1] = c.consistency_coef * hk.grad
+                loss_c = loss_c + float(lc.detach())
             acts.append(x)
             alive_k.append(alive)
             alive = alive * (1 - self.done_buf[tt % W, e])      # no targets past an episode end
@@ -190,6 +208,8 @@ class MuZeroAgent:
         for k in range(K, -1, -1):
             self.pred.forward(self._inp(hs[k]))
             dh = dh + self.pred.vjp(dpred[k]).float()
+            if dcons[k] is not None:
+                dh = dh + dcons[k]
             if k == 0:
                 break
             # hs[k] = scale01(raws[k]), raws[k] = dyn(x_{k-1})[:, :latent]; the gradient is halved at every step so that
@@ -203,7 +223,7 @@ class MuZeroAgent:
         if c.max_grad_norm > 0:
             self.opt.clip()
         self.opt.step(zero_grad=True)
-        self.last = dict(policy_loss=float(loss_p), value_loss=float(loss_v), reward_loss=float(loss_r))
+        self.last = dict(policy_loss=float(loss_p), value_loss=float(loss_v), reward_loss=float(loss_r), consistency=float(loss_c))
         return self.last
 
     def save(self, path):

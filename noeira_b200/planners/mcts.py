@@ -29,6 +29,10 @@ class MCTSConfig:
     dirichlet_alpha: float = 0.3
     root_noise_frac: float = 0.0        # 0.25 for self-play exploration
     max_depth: int = 32
+    # Gumbel root search (``search_gumbel``): actions considered at the root, and the σ transform of completed Q values
+    gumbel_considered: int = 16
+    gumbel_c_visit: float = 50.0
+    gumbel_c_scale: float = 1.0
 
 
 class MCTSTree:
@@ -201,3 +205,93 @@ class BatchedMCTS:
             p = counts.pow(1.0 / temperature)
             action = torch.multinomial(p / p.sum(-1, keepdim=True), 1, generator=generator).squeeze(-1)
         return policy, root_value, action
+
+
+    # ------------------------------------------------------------------ Gumbel root search with sequential halving
+    def _simulate(self, t, kern, ar):
+        (_cuda_select if kern else select_torch)(t)
+        lat = t.latent[ar, t.leaf_parent.long()]
+        nl, r, lg, v = self.recurrent(lat, t.leaf_action.long())
+        if kern:
+            _cuda_expand_backup(t, nl, r, lg, v, None)
+        else:
+            backup_torch(t, expand_torch(t, nl, r, lg, v, None), v)
+
+    @torch.no_grad()
+    def search_gumbel(self, obs, legal=None, generator=None, greedy: bool = False):
+        """Policy improvement by planning with Gumbel (Danihelka et al.): sample Gumbel noise g, consider the top-m actions
+        by g + logits, split the simulation budget over ⌈log₂ m⌉ halving phases (every surviving action gets the same
+        number of visits in a phase; the root action of a simulation is forced by a one-hot root prior, below the root the
+        usual PUCT descent runs), drop the worse half by g + logits + σ(q̂) after each phase.  Returns the improved policy
+        softmax(logits + σ(completed Q)) — the training target —, the root value, and the surviving action.
+        ``greedy``: no noise (evaluation)."""
+        cfg = self.cfg
+        latent, logits, value = self.initial(obs)
+        n, dev, A = latent.shape[0], latent.device, cfg.n_actions
+        kern = self.use_kernels if self.use_kernels is not None else dev.type == "cuda"
+        if self.tree is None or self.tree.n != n or self.tree.L != latent.shape[1] or self.tree.visit.device != dev:
+            self.tree = MCTSTree(n, cfg, latent.shape[1], dev)
+        t = self.tree
+        t.reset()
+        logits = logits.float()
+        if legal is not None:
+            logits = logits.masked_fill(~legal, -1e9)
+        pri = torch.softmax(logits, -1)
+        t.latent[:, 0] = latent.float()
+        t.visit[:, 0] = 1.0
+        t.value_sum[:, 0] = value.float()
+        ar = torch.arange(n, device=dev)
+        if greedy:
+            g = torch.zeros(n, A, device=dev)
+        else:
+            u = torch.rand(n, A, device=dev, generator=generator).clamp(1e-9, 1 - 1e-9)
+            g = -torch.log(-torch.log(u))
+        m = min(cfg.gumbel_considered, A)
+        cand = (g + logits).topk(m, dim=1).indices                                  # [n, m], best first
+        budget, used = cfg.n_simulations, 0
+        phases = max(1, int(torch.ceil(torch.log2(torch.tensor(float(m)))).item()))
+        eye = torch.eye(A, device=dev)
+
+        def q_and_counts():
+            ch = t.children[:, 0].long()
+            nc = torch.where(ch >= 0, t.visit[ar[:, None], ch.clamp(min=0)], torch.zeros(n, A, device=dev))
+            q = t.reward[ar[:, None], ch.clamp(min=0)] + cfg.discount * t.value_sum[ar[:, None], ch.clamp(min=0)] / nc.clamp(min=1)
+            return torch.where(nc > 0, q, torch.zeros_like(q)), nc
+
+        def sigma(q, nc):
+            lo = torch.where(nc > 0, q, torch.full_like(q, float("inf"))).min(1, keepdim=True).values
+            hi = torch.where(nc > 0, q, torch.full_like(q, float("-inf"))).max(1, keepdim=True).values
+            lo, hi = torch.minimum(lo, value.float()[:, None]), torch.maximum(hi, value.float()[:, None])
+            qn = (q - lo) / (hi - lo).clamp(min=1e-6)
+            return (cfg.gumbel_c_visit + nc.max(1, keepdim=True).values) * cfg.gumbel_c_scale * qn
+
+        cur = m
+        for ph in range(phases):
+            per = max(1, budget // (phases * cur))
+            for rep in range(per):
+                for k in range(cur):
+                    if used >= budget:
+                        break
+                    t.prior[:, 0] = eye[cand[:, k]]
+                    self._simulate(t, kern, ar)
+                    used += 1
+            if cur == 1:
+                break
+            q, nc = q_and_counts()
+            score = (g + logits + sigma(q, nc)).gather(1, cand[:, :cur])
+            order = score.argsort(dim=1, descending=True)
+            cand = torch.cat([cand[:, :cur].gather(1, order), cand[:, cur:]], 1)
+            cur = max(1, cur // 2)
+        while used < budget:                                                        # leftover budget goes to the survivor
+            t.prior[:, 0] = eye[cand[:, 0]]
+            self._simulate(t, kern, ar)
+            used += 1
+        q, nc = q_and_counts()
+        score = (g + logits + sigma(q, nc)).gather(1, cand[:, :cur])
+        action = cand[:, :cur].gather(1, score.argmax(1, keepdim=True))[:, 0]
+        # completed Q: visited actions keep their estimate, the others take the root value
+        completed = torch.where(nc > 0, q, value.float()[:, None].expand(n, A))
+        improved = torch.softmax(logits + sigma(completed, torch.where(nc > 0, nc, torch.ones_like(nc)) * (nc.max(1, keepdim=True).values > 0)), -1)
+        t.prior[:, 0] = pri
+        root_value = t.value_sum[:, 0] / t.visit[:, 0]
+        return improved, root_value, action

@@ -68,3 +68,36 @@ def test_temperature_sampling_follows_visit_counts():
     g = torch.Generator().manual_seed(0)
     _, _, a = m.search(torch.zeros(256, 1), temperature=1.0, generator=g)
     assert (a == 2).float().mean() > 0.5 and (a != 2).any()
+
+
+def test_gumbel_search_improves_the_policy_with_few_simulations():
+    """A bandit behind a one-step model: arm rewards are known to the model, the prior is uniform.  With 16 simulations over
+    8 arms the Gumbel search must return the best arm (greedy) and an improved policy that ranks the arms by reward."""
+    from noeira_b200.planners.mcts import BatchedMCTS, MCTSConfig
+    n, A = 32, 8
+    g = torch.Generator().manual_seed(0)
+    arm = torch.rand(n, A, generator=g)
+
+    def initial(obs):
+        return obs, torch.zeros(n, A), torch.zeros(n)
+
+    def recurrent(latent, action):
+        r = latent[torch.arange(latent.shape[0]), action.long()] * (latent[:, -1] == 0).float()    # reward on the first move only
+        nxt = latent.clone()
+        nxt[:, -1] = 1.0
+        return nxt, r, torch.zeros(latent.shape[0], A), torch.zeros(latent.shape[0])
+
+    obs = torch.cat([arm, torch.zeros(n, 1)], 1)
+    mcts = BatchedMCTS(MCTSConfig(n_actions=A, n_simulations=16, discount=1.0, gumbel_considered=8, max_depth=17), initial, recurrent,
+                       use_kernels=False)
+    pol, val, act = mcts.search_gumbel(obs, greedy=True)
+    assert (act == arm.argmax(1)).all()
+    assert torch.allclose(pol.sum(1), torch.ones(n), atol=1e-5)
+    assert (pol.argmax(1) == arm.argmax(1)).float().mean() > 0.9
+    # with noise the chosen arm is still a good one on average, and different trees explore differently
+    pol2, _, act2 = mcts.search_gumbel(obs, generator=g)
+    assert float(arm[torch.arange(n), act2].mean()) > float(arm.mean()) + 0.2
+    legal = torch.ones(n, A, dtype=torch.bool)
+    legal[:, 0] = False
+    pol3, _, act3 = mcts.search_gumbel(obs, legal=legal, greedy=True)
+    assert (act3 != 0).all() and float(pol3[:, 0].max()) < 1e-6

@@ -84,3 +84,27 @@ def test_muzero_learns_the_corridor():
         reached |= env2.terminated > 0
         obs = env2.obs.clone()
     assert reached.float().mean().item() >= 0.8
+
+
+def test_gumbel_search_and_consistency_loss_options():
+    """EfficientZero-style options: Gumbel root search for acting / targets and the latent consistency loss; the
+    consistency term falls as the dynamics learn to predict the encoder's next latent."""
+    from noeira_b200.agents.muzero import MuZeroAgent, MuZeroConfig
+    from test_discrete_agents_cpu import _DiscreteCartPole
+    env = _DiscreteCartPole(8, seed=0)
+    ag = MuZeroAgent(MuZeroConfig(obs_dim=4, n_actions=2, latent=16, hidden=32, n_simulations=8, unroll=3, td_steps=5, batch=64,
+                                  gumbel=True, consistency_coef=2.0, window=256, seed=0), n_envs=8)
+    obs = env.reset_batch().clone()
+    cons = []
+    for t in range(160):
+        a = ag.select_action_batched(obs)
+        assert abs(float(ag._pending[0].sum(1)[0]) - 1) < 1e-5                 # the improved policy is the stored target
+        nxt, r, done, term = env.step_batch(a)
+        ag.record_batch(obs, a, r, env.next_obs, done, term)
+        obs = nxt.clone()
+        out = ag.train_step()
+        if out is not None:
+            cons.append(out["consistency"])
+    assert len(cons) > 20 and all(c == c for c in cons)
+    assert sum(cons[-5:]) / 5 < sum(cons[:5]) / 5                              # −cos decreases: latents line up
+    assert cons[-1] < -0.5
