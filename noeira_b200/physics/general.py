@@ -12,8 +12,8 @@ integrators, sensors), batched over environments as plain tensor operations (any
                 (Coriolis / centrifugal / gyroscopic) and gravity, passive forces, motors
   collision     plane vs sphere / capsule / box, sphere–sphere, sphere–capsule, capsule–capsule (closest points of segments)
   constraints   soft constraints with reference acceleration −b·v − k·r and impedance-regularised diagonal; contact normal +
-                two friction rows (box friction |f_t| ≤ μ f_n), joint limits; solvers: projected Gauss-Seidel and an
-                active-set Newton method on the dual (batched linear solves on the free set)
+                two friction rows (box friction |f_t| ≤ μ f_n), joint limits; solvers: projected Gauss-Seidel, projected conjugate
+                gradients, and an active-set Newton method on the dual (batched linear solves on the free set)
   integrators   semi-implicit Euler, Euler with implicit joint damping, 4th-order Runge-Kutta on the manifold
   sensors       joint position / velocity, frame position / orientation / linear / angular velocity, accelerometer, gyro,
                 touch (contact normal force per body), actuator force, subtree centre of mass, energies
@@ -577,6 +577,39 @@ def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters
                 f = new
                 break
             f = new
+    elif solver == "cg":
+        # projected conjugate gradients on the dual.  Outer rounds fix the friction bounds at μ times the current normal
+        # forces, which leaves a plain box-constrained quadratic; inside, Polak-Ribière directions on the free set, steps
+        # clipped to the box, and a restart of the direction whenever a step was clipped
+        outer = 6
+        inner = max(iters // outer, 4)
+        for _ in range(outer):
+            lo, hi = project(f)
+            f = torch.maximum(torch.minimum(f, hi), lo)
+            p = torch.zeros_like(f)
+            r_prev = torch.zeros_like(f)
+            restart = torch.ones(B, dtype=torch.bool, device=A.device)
+            for _ in range(inner):
+                g = (A @ f[:, :, None])[..., 0] + b
+                free = ~(((f <= lo) & (g > 0)) | ((f >= hi) & (g < 0)))
+                r = -g * free
+                rr_prev = (r_prev * r_prev).sum(1)
+                beta = ((r * (r - r_prev)).sum(1) / rr_prev.clamp(min=1e-30)).clamp(min=0)
+                beta = torch.where(restart | (rr_prev <= 0), torch.zeros_like(beta), beta)
+                p = (r + beta[:, None] * p) * free
+                Ap = (A @ p[:, :, None])[..., 0]
+                denom = (p * Ap).sum(1)
+                alpha = torch.where(denom > 1e-30, (r * p).sum(1) / denom.clamp(min=1e-30), torch.zeros_like(denom))
+                step = f + alpha[:, None] * p
+                new = torch.maximum(torch.minimum(step, hi), lo)
+                restart = (new != step).any(1)
+                r_prev = r
+                done = float((new - f).abs().max()) < 1e-13
+                f = new
+                if done:
+                    break
+        lo, hi = project(f)
+        f = torch.maximum(torch.minimum(f, hi), lo)
     else:
         raise ValueError(solver)
     f = f * act

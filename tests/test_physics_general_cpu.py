@@ -132,11 +132,11 @@ def test_segment_distance_against_dense_sampling():
     assert (got <= brute + 1e-9).all() and (brute - got < 2e-2).all()
 
 
-@pytest.mark.parametrize("solver", ["pgs", "newton"])
+@pytest.mark.parametrize("solver", ["pgs", "newton", "cg"])
 def test_resting_box_sliding_friction_and_touch(solver):
     opt = Options(timestep=0.002, solref=(0.01, 1.0))
     m = _free_box(opt, z=0.05, plane=True, friction=0.5)
-    sim = G.GeneralSim(m, 2, integrator="euler", solver=solver, solver_iters=60 if solver == "pgs" else 20)
+    sim = G.GeneralSim(m, 2, integrator="euler", solver=solver, solver_iters={"pgs": 60, "newton": 20, "cg": 60}[solver])
     sim.qvel[1, 0] = 2.0                                            # env 1 slides along x
     xs = []
     for i in range(400):
@@ -162,13 +162,14 @@ def test_solvers_agree_on_the_contact_forces():
     q, v = m.init_state(1)
     v[0, 8] = -0.3
     out = {}
-    for solver, it in (("pgs", 400), ("newton", 30)):
+    for solver, it in (("pgs", 400), ("newton", 30), ("cg", 200)):
         sim = G.GeneralSim(m, 1, solver=solver, solver_iters=it)
         sim.forward(q, v)
         out[solver] = (sim.last["force"].clone(), sim.last["qacc"].clone())
     assert out["newton"][0].max() > 1.0
     assert torch.allclose(out["pgs"][0], out["newton"][0], atol=2e-3 * float(out["newton"][0].abs().max()))
     assert torch.allclose(out["pgs"][1], out["newton"][1], atol=1e-2)
+    assert torch.allclose(out["cg"][0], out["newton"][0], atol=2e-3 * float(out["newton"][0].abs().max()))
 
 
 def test_sphere_sphere_collision_conserves_momentum_and_separates():
