@@ -259,9 +259,12 @@ class PPOTrainer:
         self._gather()
         x = self.mb_obs
         mu, v = mlp3_forward_group([pa, pc], [x, x])
-        check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
-                                    ptr(self.partials_v), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
-                                    ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
+        # the two loss chains are independent (value loss + its reduction, objective + its finalisation): the value side
+        # runs on a branch next to the objective instead of in front of it
+        with self._critic_branch:
+            check(lib.nb_ppo_value_loss(ptr(v), ctypes.c_int(v.stride(0)), ptr(self.mb_ret), ptr(self.dv), ctypes.c_int(8),
+                                        ptr(self.partials_v), ptr(self.metrics[5:]), ctypes.c_int(self.mb),
+                                        ctypes.c_float(1.0 / self.mb), stream_ptr()), "ppo_value_loss")
         check(lib.nb_ppo_objective(ptr(mu), ctypes.c_int(mu.stride(0)), ptr(head.log_std.storage), ptr(self.mb_act),
                                    ctypes.c_int(self.AP), ptr(self.mb_logp), ptr(self.mb_adv), ptr(self.adv_stats),
                                    ptr(self.dmu), ctypes.c_int(self.AP), ptr(self.partials), ptr(self.partials2),
@@ -269,6 +272,7 @@ class PPOTrainer:
                                    ctypes.c_int(env.act_dim), ctypes.c_float(cfg.clip_eps),
                                    ctypes.c_float(cfg.entropy_coef), ctypes.c_float(1.0 / self.mb), stream_ptr()),
               "ppo_objective")
+        self._critic_branch.join()
         mlp3_backward_group([pa, pc], [x, x], [self.dmu, self.dv])
         mlp3_param_grads(pa, x, self.dmu, self._layer_pg[0])
         mlp3_param_grads(pc, x, self.dv, self._layer_pg[1])

@@ -10,7 +10,8 @@ integrators, sensors), batched over environments as plain tensor operations (any
   kinematics    body frames, per-dof world motion axes and anchors, body / point Jacobians, frame velocities
   dynamics      mass matrix M = Σ m JvᵀJv + Jwᵀ I Jw (+ armature), bias force from the time derivative of the Jacobians
                 (Coriolis / centrifugal / gyroscopic) and gravity, passive forces, motors
-  collision     plane vs sphere / capsule / box, sphere–sphere, sphere–capsule, capsule–capsule (closest points of segments)
+  collision     plane vs sphere / capsule / box, sphere–sphere, sphere–capsule, capsule–capsule (closest points of segments),
+                sphere–box (closest point of the box), box–box (corner-in-box contacts both ways)
   constraints   soft constraints with reference acceleration −b·v − k·r and impedance-regularised diagonal; contact normal +
                 two friction rows (box friction |f_t| ≤ μ f_n), joint limits; solvers: projected Gauss-Seidel, projected conjugate
                 gradients, and an active-set Newton method on the dual (batched linear solves on the free set)
@@ -187,7 +188,7 @@ class GeneralModel:
             collide_pairs = [(i, j) for i in range(len(self.geoms)) for j in range(i + 1, len(self.geoms))
                              if self.geoms[i][0] != self.geoms[j][0] and self.parent[self.geoms[i][0]] != self.geoms[j][0]
                              and self.parent[self.geoms[j][0]] != self.geoms[i][0]
-                             and self.geoms[i][1].type != "box" and self.geoms[j][1].type != "box"]
+                             and not ({self.geoms[i][1].type, self.geoms[j][1].type} == {"box", "capsule"})]
         self.pairs = list(collide_pairs)
 
     def t(self, x):
@@ -431,6 +432,37 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
                 d = g.size[0] - ((e * n_pl).sum(-1) - m.opt.plane_offset)
                 add(e - n_pl * (g.size[0] - 0.5 * d)[:, None], n_pl.expand_as(e), d, -1, b, g.friction)
     for gi, gj in m.pairs:
+        ta, tb = m.geoms[gi][1].type, m.geoms[gj][1].type
+        fr = math.sqrt(m.geoms[gi][1].friction * m.geoms[gj][1].friction)
+        if ta == "box" or tb == "box":
+            if ta == "box" and tb == "box":
+                # vertex-face contacts both ways (8 + 8 slots): a corner of one box inside the other is pushed out through
+                # the nearest face of the box that contains it.  Edge-edge crossings without a contained corner are not found.
+                for g_in, g_box in ((gi, gj), (gj, gi)):
+                    b_in, gin, c_in, R_in = _geom_frame(m, k, g_in)
+                    b_bx, gbx, c_bx, R_bx = _geom_frame(m, k, g_box)
+                    h_in, h_bx = m.t(gin.size), m.t(gbx.size)
+                    for sx in (-1, 1):
+                        for sy in (-1, 1):
+                            for sz in (-1, 1):
+                                p = c_in + R_in @ (h_in * m.t([sx, sy, sz]))
+                                n, d = _point_in_box(p, c_bx, R_bx, h_bx)
+                                add(p + n * (0.5 * d)[:, None], n, d, b_bx, b_in, fr)
+            else:
+                g_s, g_b = (gi, gj) if tb == "box" else (gj, gi)
+                b_s, gs, c_s, _ = _geom_frame(m, k, g_s)
+                b_b, gb, c_b, R_b = _geom_frame(m, k, g_b)
+                loc = (R_b.transpose(1, 2) @ (c_s - c_b)[:, :, None])[..., 0]
+                h = m.t(gb.size)
+                near = c_b + (R_b @ torch.maximum(torch.minimum(loc, h), -h)[:, :, None])[..., 0]      # closest point of the box
+                diff = c_s - near
+                dist = diff.norm(dim=-1)
+                inside = dist < 1e-9
+                n_in, d_in = _point_in_box(c_s, c_b, R_b, h)                                       # centre inside the box
+                n = torch.where(inside[:, None], n_in, diff / dist.clamp(min=1e-12)[:, None])
+                d = torch.where(inside, d_in + gs.size[0], gs.size[0] - dist)
+                add(c_s - n * (gs.size[0] - 0.5 * d)[:, None], n, d, b_b, b_s, fr)
+            continue
         ba, pa, da, ra = _spheres_of(m, k, gi)
         bb, pb, db, rb = _spheres_of(m, k, gj)
         ca, cb = closest_segment_points(pa, da, pb, db)
@@ -444,6 +476,19 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
         z = torch.zeros(B, 0, 3, dtype=k.xpos.dtype, device=k.xpos.device)
         return Contacts(z, z, z[..., 0], [], [], m.t([]))
     return Contacts(torch.stack(pts, 1), torch.stack(nrm, 1), torch.stack(dep, 1), b1, b2, m.t(mu))
+
+
+def _point_in_box(p, c, R, h):
+    """(outward normal of the nearest face, depth below it) of a point relative to a box; depth <= 0 outside."""
+    loc = (R.transpose(1, 2) @ (p - c)[:, :, None])[..., 0]
+    room = h - loc.abs()                                        # distance to the face pair of every axis
+    inside = (room > 0).all(-1)
+    ax = room.argmin(-1)
+    sgn = torch.sign(loc.gather(1, ax[:, None]))[:, 0]
+    sgn = torch.where(sgn == 0, torch.ones_like(sgn), sgn)
+    n = R.gather(2, ax[:, None, None].expand(-1, 3, 1))[..., 0] * sgn[:, None]
+    depth = torch.where(inside, room.min(-1).values, -torch.ones_like(sgn))
+    return n, depth
 
 
 def _tangents(n):

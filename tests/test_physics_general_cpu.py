@@ -240,3 +240,32 @@ def test_mjcf_with_free_and_ball_joints_and_boxes():
         sim.step(torch.tensor([[0.3], [-0.3]]))
     assert torch.isfinite(sim.qpos).all() and float(sim.qpos[:, 2].min()) > 0.03           # the box landed on the plane and stayed
     assert abs(float(sim.qpos[0, 3:7].norm()) - 1) < 1e-9
+
+
+def test_box_on_box_and_sphere_on_box_rest():
+    opt = Options(timestep=0.002, solref=(0.01, 1.0))
+    base = Body(-1, (0, 0, 0.1), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("box", (0.3, 0.3, 0.1), density=2000.0)])
+    top = Body(-1, (0.05, -0.03, 0.27), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("box", (0.1, 0.1, 0.07))])
+    ball = Body(-1, (-0.15, 0.1, 0.285), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("sphere", (0.08,))])
+    m = G.GeneralModel([base, top, ball], opt=opt, plane=True)
+    assert len(m.pairs) == 3
+    sim = G.GeneralSim(m, 1, solver="newton", solver_iters=30)
+    for _ in range(500):
+        sim.step()
+    q = sim.qpos[0]
+    assert float(sim.qvel.abs().max()) < 5e-3                                       # everything came to rest
+    assert abs(float(q[2]) - 0.1) < 3e-3                                            # the base on the plane
+    assert abs(float(q[7 + 2]) - 0.27) < 4e-3                                       # the small box on the base (0.2 + 0.07)
+    assert abs(float(q[14 + 2]) - 0.28) < 4e-3                                      # the ball on the base (0.2 + 0.08)
+    assert abs(float(q[7]) - 0.05) < 2e-3 and abs(float(q[14]) + 0.15) < 2e-3       # friction keeps them in place
+    # the base feels its own weight plus the two riders from the plane
+    s = sim.sensors(0)
+    assert abs(float(s["touch"][0]) - float(m.mass.sum()) * 9.81) < 0.03 * float(m.mass.sum()) * 9.81
+    # geometry helper: a point inside / outside a rotated box
+    R = G.quat_to_mat(torch.tensor([[0.9238795, 0.0, 0.0, 0.3826834]], dtype=torch.float64))
+    n, d = G._point_in_box(torch.tensor([[0.0, 0.0, 0.09]], dtype=torch.float64), torch.zeros(1, 3, dtype=torch.float64), R,
+                           torch.tensor([0.3, 0.2, 0.1], dtype=torch.float64))
+    assert torch.allclose(n, torch.tensor([[0.0, 0.0, 1.0]], dtype=torch.float64)) and abs(float(d) - 0.01) < 1e-9
+    _, d2 = G._point_in_box(torch.tensor([[0.0, 0.0, 0.2]], dtype=torch.float64), torch.zeros(1, 3, dtype=torch.float64), R,
+                            torch.tensor([0.3, 0.2, 0.1], dtype=torch.float64))
+    assert float(d2) < 0
