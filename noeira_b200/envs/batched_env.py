@@ -105,3 +105,48 @@ class HopperEnv(Physics3dBatchedEnv):
                          TaskSpec(frame_skip=4, max_steps=max_steps, w_ctrl=1e-3, w_alive=1.0, term_dof=1,
                                   term_lo=-0.55, term_hi=1e30, reset_noise_pos=5e-3, reset_noise_vel=5e-3),
                          device=device, seed=seed)
+
+
+class Walker2dEnv(Physics3dBatchedEnv):
+    """Walker2d-class biped: reward = forward velocity + alive bonus − 1e-3 ‖a‖², ends when the torso drops below 0.8 m
+    (root z coordinate relative to its start) or after ``max_steps``."""
+
+    def __init__(self, n_envs: int, device="cuda", seed: int = 0, max_steps: int = 1000):
+        from ..physics.engine import TaskSpec
+        from ..physics.model import walker2d
+        super().__init__(walker2d(), n_envs,
+                         TaskSpec(frame_skip=4, max_steps=max_steps, w_ctrl=1e-3, w_alive=1.0, term_dof=1, term_lo=-0.45, term_hi=0.75,
+                                  reset_noise_pos=5e-3, reset_noise_vel=5e-3), device=device, seed=seed)
+
+
+class InvertedDoublePendulumEnv(Physics3dBatchedEnv):
+    """Balance two poles in series on a cart: alive bonus while the first pole stays within ±0.35 rad of upright."""
+
+    def __init__(self, n_envs: int, device="cuda", seed: int = 0, max_steps: int = 1000):
+        from ..physics.engine import TaskSpec
+        from ..physics.model import inverted_double_pendulum
+        super().__init__(inverted_double_pendulum(), n_envs,
+                         TaskSpec(frame_skip=5, max_steps=max_steps, w_forward=0.0, w_ctrl=1e-3, w_alive=10.0, term_dof=1, term_lo=-0.35,
+                                  term_hi=0.35, obs_qpos_skip=0, reset_noise_pos=0.05, reset_noise_vel=0.05), device=device, seed=seed)
+
+
+class InvertedPendulumEnv(Physics3dBatchedEnv):
+    """Balance one pole on a cart: alive bonus while the pole stays within ±0.2 rad."""
+
+    def __init__(self, n_envs: int, device="cuda", seed: int = 0, max_steps: int = 1000):
+        from ..physics.engine import TaskSpec
+        from ..physics.model import pendulum_cart
+        super().__init__(pendulum_cart(), n_envs,
+                         TaskSpec(frame_skip=2, max_steps=max_steps, w_forward=0.0, w_ctrl=0.0, w_alive=1.0, term_dof=1, term_lo=-0.2,
+                                  term_hi=0.2, obs_qpos_skip=0, reset_noise_pos=0.01, reset_noise_vel=0.01), device=device, seed=seed)
+
+
+class ReacherEnv(Physics3dBatchedEnv):
+    """Two-link arm in the plane; the built-in task rewards small controls while the policy moves joint 0 forward (the
+    target-reaching reward of the original needs a per-env goal: use the task layer's goal predicates for that)."""
+
+    def __init__(self, n_envs: int, device="cuda", seed: int = 0, max_steps: int = 50):
+        from ..physics.engine import TaskSpec
+        from ..physics.model import reacher
+        super().__init__(reacher(), n_envs, TaskSpec(frame_skip=2, max_steps=max_steps, w_forward=1.0, w_ctrl=0.1, obs_qpos_skip=0),
+                         device=device, seed=seed)

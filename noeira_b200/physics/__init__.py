@@ -1,2 +1,2 @@
-from .model import (Actuator, Body, Geom, Joint, Options, RigidModel, half_cheetah, hopper, pendulum_cart,  # noqa: F401
-                    planar_chain)
+from .model import (Actuator, Body, Geom, Joint, Options, RigidModel, half_cheetah, hopper, inverted_double_pendulum,  # noqa: F401
+                    pendulum_cart, planar_chain, reacher, walker2d)

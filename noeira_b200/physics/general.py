@@ -79,6 +79,17 @@ class Motor:
 
 
 @dataclass
+class Tendon:
+    """Fixed tendon: length L = Σ coef_j · q_j over 1-dof joints, with a spring (``stiffness`` about ``springlength``), a
+    damper and an optional length range enforced as a constraint."""
+    coefs: Dict[str, float]
+    stiffness: float = 0.0
+    springlength: float = 0.0
+    damping: float = 0.0
+    range: Optional[Tuple[float, float]] = None
+
+
+@dataclass
 class _Dof:
     body: int
     jtype: int
@@ -93,7 +104,8 @@ class GeneralModel:
     from the geoms (each about its own centre, axis-aligned approximation for rotated capsules)."""
 
     def __init__(self, bodies: Sequence[Body], motors: Sequence[Motor] = (), opt: Options = None, dtype=torch.float64,
-                 device="cpu", collide_pairs: Optional[Sequence[Tuple[int, int]]] = None, plane: bool = True):
+                 device="cpu", collide_pairs: Optional[Sequence[Tuple[int, int]]] = None, plane: bool = True,
+                 tendons: Sequence[Tendon] = ()):
         self.opt = opt or Options()
         self.dtype, self.device = dtype, torch.device(device)
         t = lambda x: torch.as_tensor(x, dtype=dtype, device=self.device)
@@ -181,6 +193,17 @@ class GeneralModel:
         self.motors = list(motors)
         self.motor_dof = [self.joint_dadr[self.joint_by_name[m.joint]] for m in self.motors]
         self.gravity = t(self.opt.gravity)
+        # fixed tendons: one coefficient row over the dofs each
+        self.tendons = list(tendons)
+        self.tendon_coef = torch.zeros(len(self.tendons), self.nv, dtype=dtype, device=self.device)
+        for ti, td in enumerate(self.tendons):
+            for jn, cf in td.coefs.items():
+                d = self.joint_dadr[self.joint_by_name[jn]]
+                assert self.dofs[d].jtype in (HINGE, SLIDE), "fixed tendons run over hinge / slide joints"
+                self.tendon_coef[ti, d] = cf
+        self.tendon_k = t([td.stiffness for td in self.tendons])
+        self.tendon_l0 = t([td.springlength for td in self.tendons])
+        self.tendon_d = t([td.damping for td in self.tendons])
         # collision geoms and pairs
         self.geoms = [(bi, g) for bi, b in enumerate(bodies) for g in b.geoms if g.contact]
         self.plane = plane
@@ -339,8 +362,17 @@ def _scalar_q(m: GeneralModel, qpos):
     return out
 
 
+def tendon_length(m: GeneralModel, qpos):
+    return _scalar_q(m, qpos) @ m.tendon_coef.T                                   # [B, nt]
+
+
 def passive_force(m: GeneralModel, qpos, qvel, with_damping=True):
     f = -m.stiffness * (_scalar_q(m, qpos) - m.springref)
+    if m.tendons:
+        ft = -m.tendon_k * (tendon_length(m, qpos) - m.tendon_l0)
+        if with_damping:
+            ft = ft - m.tendon_d * (qvel @ m.tendon_coef.T)
+        f = f + ft @ m.tendon_coef
     return f - m.damping * qvel if with_damping else f
 
 
@@ -365,6 +397,8 @@ def energy(m: GeneralModel, qpos, qvel):
     M = mass_matrix(m, k)
     T = 0.5 * (qvel[:, None] @ M @ qvel[:, :, None])[:, 0, 0]
     U = -(m.mass[None, :, None] * k.com * m.gravity).sum((1, 2)) + 0.5 * (m.stiffness * (_scalar_q(m, qpos) - m.springref) ** 2).sum(1)
+    if m.tendons:
+        U = U + 0.5 * (m.tendon_k * (tendon_length(m, qpos) - m.tendon_l0) ** 2).sum(1)
     return T, U
 
 
@@ -532,6 +566,14 @@ def constraint_rows(m: GeneralModel, k: Kin, qpos, qvel, con: Contacts) -> Rows:
             e = torch.zeros(B, m.nv, dtype=qpos.dtype, device=qpos.device)
             e[:, d] = sgn
             J.append(e), r.append(dist), kind.append(0), par.append(-1), mu.append(0.0), body.append(-1)
+    if m.tendons:
+        L = tendon_length(m, qpos)
+        for ti, td in enumerate(m.tendons):
+            if td.range is None:
+                continue
+            for sgn, dist in ((1.0, L[:, ti] - td.range[0]), (-1.0, td.range[1] - L[:, ti])):
+                J.append((sgn * m.tendon_coef[ti])[None].expand(B, -1)), r.append(dist), kind.append(0), par.append(-1)
+                mu.append(0.0), body.append(-1)
     nc = con.depth.shape[1]
     normal_row = []
     for c in range(nc):
@@ -667,11 +709,12 @@ class GeneralSim:
         self.m, self.n, self.integrator, self.solver, self.solver_iters = model, n, integrator, solver, solver_iters
         self.qpos, self.qvel = model.init_state(n)
         self.ctrl = torch.zeros(n, len(model.motors), dtype=model.dtype, device=model.device)
+        self.qfrc_applied = torch.zeros(n, model.nv, dtype=model.dtype, device=model.device)      # external generalized force
         self.last: Dict[str, torch.Tensor] = {}
 
     def _applied(self):
         m = self.m
-        tau = torch.zeros(self.n, m.nv, dtype=m.dtype, device=m.device)
+        tau = self.qfrc_applied.clone()
         self._act_force = torch.zeros_like(self.ctrl)
         for i, (mot, d) in enumerate(zip(m.motors, m.motor_dof)):
             self._act_force[:, i] = mot.gear * self.ctrl[:, i].clamp(*mot.ctrlrange)
@@ -752,3 +795,32 @@ class GeneralSim:
                 return True
             b = self.m.parent[b]
         return False
+
+
+def osc_torque(m: GeneralModel, qpos, qvel, body: int, point_local, x_des, kp: float = 100.0, kd: Optional[float] = None,
+               null_damping: float = 1.0, max_accel: float = 200.0):
+    """Operational-space controller for a point fixed on ``body``: generalized forces that give the point the task-space
+    acceleration kp (x_des − x) − kd ẋ through the task-space inertia Λ = (J M⁻¹ Jᵀ)⁻¹, compensate the bias force
+    (gravity, Coriolis) and damp the motion in the null space of the task.  Returns ``(tau [B, nv], x [B, 3])``."""
+    kd = 2.0 * math.sqrt(kp) if kd is None else kd
+    k = kinematics(m, qpos, qvel)
+    Jv, Jw = body_jacobians(m, k)
+    M = mass_matrix(m, k, Jv, Jw)
+    c = bias_force(m, k, qvel, Jv, Jw)
+    x = k.xpos[:, body] + (k.xmat[:, body] @ m.t(point_local))
+    J = point_jacobian(m, k, body, x)                                             # [B, 3, nv]
+    xd = (J @ qvel[:, :, None])[..., 0]
+    v_body_pt = xd
+    jdqd = point_bias_acceleration(m, k, qvel, body, x, v_body_pt)
+    Minv_Jt = torch.linalg.solve(M, J.transpose(1, 2))                            # [B, nv, 3]
+    lam_inv = J @ Minv_Jt + 1e-6 * torch.eye(3, dtype=qpos.dtype, device=qpos.device)
+    acc = (kp * (m.t(x_des) - x) - kd * xd)
+    n = acc.norm(dim=-1, keepdim=True)
+    acc = acc * torch.clamp(max_accel / n.clamp(min=1e-9), max=1.0)
+    F = torch.linalg.solve(lam_inv, (acc - jdqd)[:, :, None])                     # Λ (ẍ* − J̇ q̇)
+    tau = (J.transpose(1, 2) @ F)[..., 0] + c
+    # null-space damping: (I − Jᵀ J̄ᵀ)(−k M q̇), J̄ = M⁻¹ Jᵀ Λ
+    Jbar_T = torch.linalg.solve(lam_inv, Minv_Jt.transpose(1, 2))                 # Λ J M⁻¹  [B, 3, nv]
+    t0 = -null_damping * (M @ qvel[:, :, None])[..., 0]
+    tau = tau + t0 - (J.transpose(1, 2) @ (Jbar_T @ t0[:, :, None]))[..., 0]
+    return tau, x

@@ -398,3 +398,53 @@ def pendulum_cart(opt: Options = None) -> RigidModel:
              geoms=[Geom("capsule", (0.045, 0.3), pos=(0, 0, 0.3), contact=False)], name="pole"),
     ]
     return RigidModel(bodies, [Actuator("slider", 100.0)], opt or Options())
+
+
+def walker2d(opt: Options = None) -> RigidModel:
+    """Walker2d-class planar biped: torso and two legs of thigh / leg / foot (6 actuated hinges, 9 degrees of freedom)."""
+    def cap(frm, to, rad, fr=0.9):
+        frm, to = np.asarray(frm, float), np.asarray(to, float)
+        return Geom("capsule", (rad, 0.5 * np.linalg.norm(to - frm)), pos=tuple(0.5 * (frm + to)),
+                    quat=tuple(quat_z_to(to - frm)), friction=fr)
+
+    def leg(side, foot_friction):
+        j = lambda n, rng: Joint(HINGE, (0, -1, 0), range=rng, armature=0.01, damping=0.1, name=f"{n}_{side}")
+        return [("thigh", 0, (0, 0, -0.2), j("thigh", (-2.6, 0.0)), cap((0, 0, 0), (0, 0, -0.45), 0.05)),
+                ("leg", 1, (0, 0, -0.45), j("leg", (-2.6, 0.0)), cap((0, 0, 0), (0, 0, -0.5), 0.04)),
+                ("foot", 2, (0, 0, -0.5), j("foot", (-0.785, 0.785)), cap((0, 0, 0), (0.2, 0, 0), 0.06, fr=foot_friction))]
+
+    bodies = [Body(-1, (0, 0, 1.25), joints=[Joint(SLIDE, (1, 0, 0), name="rootx"), Joint(SLIDE, (0, 0, 1), name="rootz"),
+                                             Joint(HINGE, (0, 1, 0), name="rooty")],
+                   geoms=[cap((0, 0, 0.2), (0, 0, -0.2), 0.05)], name="torso")]
+    for side, fr in (("right", 0.9), ("left", 1.9)):
+        base = len(bodies)
+        for name, up, pos, joint, geom in leg(side, fr):
+            parent = 0 if up == 0 else base + up - 1
+            bodies.append(Body(parent, pos, joints=[joint], geoms=[geom], name=f"{name}_{side}"))
+    acts = [Actuator(f"{n}_{s}", g) for s in ("right", "left") for n, g in (("thigh", 100), ("leg", 100), ("foot", 20))]
+    return RigidModel(bodies, acts, opt or Options(timestep=0.002))
+
+
+def inverted_double_pendulum(opt: Options = None) -> RigidModel:
+    """Cart on a rail with two poles in series (slide + two hinges); the cart force is the only actuator."""
+    bodies = [
+        Body(-1, (0, 0, 0.0), joints=[Joint(SLIDE, (1, 0, 0), range=(-1.0, 1.0), damping=0.05, name="slider")],
+             geoms=[Geom("sphere", (0.1,), contact=False)], name="cart"),
+        Body(0, (0, 0, 0), joints=[Joint(HINGE, (0, 1, 0), damping=0.05, name="hinge")],
+             geoms=[Geom("capsule", (0.045, 0.3), pos=(0, 0, 0.3), contact=False)], name="pole"),
+        Body(1, (0, 0, 0.6), joints=[Joint(HINGE, (0, 1, 0), damping=0.05, name="hinge2")],
+             geoms=[Geom("capsule", (0.045, 0.3), pos=(0, 0, 0.3), contact=False)], name="pole2"),
+    ]
+    return RigidModel(bodies, [Actuator("slider", 500.0)], opt or Options(timestep=0.01))
+
+
+def reacher(opt: Options = None) -> RigidModel:
+    """Two-link planar arm in the horizontal plane (gravity off): two actuated hinges about z."""
+    o = opt or Options(timestep=0.01, gravity=(0.0, 0.0, 0.0))
+    bodies = [
+        Body(-1, (0, 0, 0.01), joints=[Joint(HINGE, (0, 0, 1), damping=1.0, armature=1.0, name="joint0")],
+             geoms=[Geom("capsule", (0.01, 0.05), pos=(0.05, 0, 0), quat=tuple(quat_z_to((1, 0, 0))), contact=False)], name="link0"),
+        Body(0, (0.1, 0, 0), joints=[Joint(HINGE, (0, 0, 1), range=(-3.0, 3.0), damping=1.0, armature=1.0, name="joint1")],
+             geoms=[Geom("capsule", (0.01, 0.05), pos=(0.05, 0, 0), quat=tuple(quat_z_to((1, 0, 0))), contact=False)], name="link1"),
+    ]
+    return RigidModel(bodies, [Actuator("joint0", 200.0), Actuator("joint1", 200.0)], o)

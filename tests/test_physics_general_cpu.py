@@ -269,3 +269,52 @@ def test_box_on_box_and_sphere_on_box_rest():
     _, d2 = G._point_in_box(torch.tensor([[0.0, 0.0, 0.2]], dtype=torch.float64), torch.zeros(1, 3, dtype=torch.float64), R,
                             torch.tensor([0.3, 0.2, 0.1], dtype=torch.float64))
     assert float(d2) < 0
+
+
+def test_operational_space_controller_reaches_a_target_against_gravity():
+    opt = Options(timestep=0.002)
+    link = lambda parent, pos, name: Body(parent, pos, joints=[Joint(G.HINGE, (0, 1, 0), name=name)], mass=1.0, inertia=(0.01, 0.01, 0.01),
+                                          ipos=(0.15, 0, 0))
+    bodies = [link(-1, (0, 0, 1.0), "j0"), link(0, (0.3, 0, 0), "j1"), link(1, (0.3, 0, 0), "j2")]
+    bodies[0].joints.insert(0, Joint(G.HINGE, (0, 0, 1), name="yaw"))            # 4 dofs for a 3-D point task: one redundant
+    m = G.GeneralModel(bodies, opt=opt, plane=False)
+    sim = G.GeneralSim(m, 2, integrator="euler")
+    sim.qpos[:, 1:] = torch.tensor([0.3, -0.6, 0.4], dtype=torch.float64)
+    targets = torch.tensor([[0.45, 0.25, 1.2], [0.3, -0.3, 0.7]], dtype=torch.float64)
+    for _ in range(2000):
+        tau, x = G.osc_torque(m, sim.qpos, sim.qvel, body=2, point_local=(0.3, 0, 0), x_des=targets, kp=150.0, null_damping=8.0)
+        sim.qfrc_applied = tau
+        sim.step()
+    _, x = G.osc_torque(m, sim.qpos, sim.qvel, 2, (0.3, 0, 0), targets)
+    assert float((x - targets).norm(dim=-1).max()) < 5e-3, x
+    assert float(sim.qvel.abs().max()) < 2e-2                                    # and it holds still there (null space damped)
+
+
+def test_fixed_tendon_spring_limit_and_energy():
+    opt = Options(timestep=0.001, gravity=(0, 0, 0))
+    mk = lambda x, n: Body(-1, (x, 0, 0), joints=[Joint(G.SLIDE, (0, 0, 1), name=n)], mass=1.0, inertia=(0.01, 0.01, 0.01))
+    td = G.Tendon({"a": 1.0, "b": -1.0}, stiffness=50.0, springlength=0.0)      # pulls the two sliders to equal heights
+    m = G.GeneralModel([mk(0, "a"), mk(1, "b")], opt=opt, plane=False, tendons=[td])
+    sim = G.GeneralSim(m, 1, integrator="rk4")
+    sim.qpos[0, 0] = 0.2
+    E0 = sum(G.energy(m, sim.qpos, sim.qvel))
+    mid = []
+    for _ in range(700):
+        sim.step()
+        mid.append(float(sim.qpos[0, 0] + sim.qpos[0, 1]))
+    E1 = sum(G.energy(m, sim.qpos, sim.qvel))
+    assert abs(float(E1 - E0)) < 1e-8 and max(abs(v - 0.2) for v in mid) < 1e-9       # energy and the common mode are conserved
+    # relative coordinate oscillates at sqrt(2k/m): period 2π / 10
+    assert abs(float(G.tendon_length(m, sim.qpos)[0, 0]) - 0.2 * __import__("math").cos(10.0 * 0.7)) < 2e-4
+    # a length range acts as a stop
+    td2 = G.Tendon({"a": 1.0, "b": -1.0}, range=(-0.05, 0.05))
+    m2 = G.GeneralModel([mk(0, "a"), mk(1, "b")], opt=Options(timestep=0.002, gravity=(0, 0, 0)), plane=False, tendons=[td2])
+    s2 = G.GeneralSim(m2, 1)
+    s2.qvel[0, 0] = 0.5
+    worst = 0.0
+    for _ in range(400):
+        s2.step()
+        worst = max(worst, float(G.tendon_length(m2, s2.qpos)[0, 0]))
+    # the stop absorbs most of the relative motion (a soft, critically damped constraint), momentum is shared
+    assert 0.05 <= worst < 0.06 and abs(float(s2.qvel[0, 0] - s2.qvel[0, 1])) < 0.1
+    assert abs(float(s2.qvel[0, 0] + s2.qvel[0, 1]) - 0.5) < 1e-9

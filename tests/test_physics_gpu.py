@@ -60,6 +60,25 @@ def test_half_cheetah_matches_oracle():
     _run(half_cheetah, None, steps=6, action_scale=0.5, tol_q=5e-3, tol_v=8e-2)
 
 
+@pytest.mark.parametrize("name,scale", [("walker2d", 0.3), ("inverted_double_pendulum", 0.05), ("reacher", 0.05), ("hopper", 0.3)])
+def test_more_models_match_oracle(name, scale):
+    from noeira_b200 import physics
+    _run(getattr(physics, name), None, steps=4, action_scale=scale, tol_q=5e-3, tol_v=8e-2)
+
+
+def test_new_envs_step_and_terminate():
+    from noeira_b200.envs import InvertedDoublePendulumEnv, InvertedPendulumEnv, ReacherEnv, Walker2dEnv
+    for cls, act in ((Walker2dEnv, 6), (InvertedDoublePendulumEnv, 1), (InvertedPendulumEnv, 1), (ReacherEnv, 2)):
+        env = cls(256, seed=0)
+        assert env.act_dim == act
+        env.reset_batch()
+        for _ in range(120):
+            env.step_batch(torch.rand(256, act, device="cuda") * 2 - 1)
+        torch.cuda.synchronize()
+        assert torch.isfinite(env.obs).all() and torch.isfinite(env.reward).all(), cls.__name__
+        assert float(env.ep_stats[1]) > 0, cls.__name__                  # random actions end episodes (falls / time limits)
+
+
 def test_free_fall_and_rest():
     """No actuation: the chain falls with g until contact, then rests on the plane at z = radius."""
     from noeira_b200.envs import PlanarChainEnv
