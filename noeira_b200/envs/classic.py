@@ -139,3 +139,66 @@ class MountainCarContinuousEnv(_TensorEnv):
         v2 = torch.where((p2 <= -1.2) & (v2 < 0), torch.zeros_like(v2), v2)
         term = p2 >= self.goal
         return torch.stack([p2, v2], 1), term.float() * 100.0 - 0.1 * f ** 2, term
+
+
+class AcrobotEnv(_TensorEnv):
+    """Two-link underactuated pendulum (torque on the second joint only), the book dynamics integrated with one RK4 step of
+    0.2 s; reward −1 per step until the tip is above the bar by one link length.  Action in [−1, 1] scales the torque."""
+    obs_dim, act_dim, max_steps = 6, 1, 500
+    m1 = m2 = 1.0
+    l1 = 1.0
+    lc1 = lc2 = 0.5
+    i1 = i2 = 1.0
+    g, dt = 9.8, 0.2
+
+    def _sample_state(self, n):
+        return (self._rand(n, 4) - 0.5) * 0.2
+
+    def _observe(self, s):
+        return torch.stack([torch.cos(s[:, 0]), torch.sin(s[:, 0]), torch.cos(s[:, 1]), torch.sin(s[:, 1]), s[:, 2], s[:, 3]], 1)
+
+    def _deriv(self, s, u):
+        t1, t2, d1, d2 = s.unbind(1)
+        m1, m2, l1, lc1, lc2, i1, i2, g = self.m1, self.m2, self.l1, self.lc1, self.lc2, self.i1, self.i2, self.g
+        dd1 = m1 * lc1 ** 2 + m2 * (l1 ** 2 + lc2 ** 2 + 2 * l1 * lc2 * torch.cos(t2)) + i1 + i2
+        dd2 = m2 * (lc2 ** 2 + l1 * lc2 * torch.cos(t2)) + i2
+        phi2 = m2 * lc2 * g * torch.cos(t1 + t2 - math.pi / 2)
+        phi1 = -m2 * l1 * lc2 * d2 ** 2 * torch.sin(t2) - 2 * m2 * l1 * lc2 * d2 * d1 * torch.sin(t2) + \
+            (m1 * lc1 + m2 * l1) * g * torch.cos(t1 - math.pi / 2) + phi2
+        a2 = (u + dd2 / dd1 * phi1 - m2 * l1 * lc2 * d1 ** 2 * torch.sin(t2) - phi2) / (m2 * lc2 ** 2 + i2 - dd2 ** 2 / dd1)
+        a1 = -(dd2 * a2 + phi1) / dd1
+        return torch.stack([d1, d2, a1, a2], 1)
+
+    def _dynamics(self, s, a):
+        u = a[:, 0].clamp(-1, 1)
+        k1 = self._deriv(s, u)
+        k2 = self._deriv(s + 0.5 * self.dt * k1, u)
+        k3 = self._deriv(s + 0.5 * self.dt * k2, u)
+        k4 = self._deriv(s + self.dt * k3, u)
+        s2 = s + self.dt / 6 * (k1 + 2 * k2 + 2 * k3 + k4)
+        wrap = lambda x: ((x + math.pi) % (2 * math.pi)) - math.pi
+        s2 = torch.stack([wrap(s2[:, 0]), wrap(s2[:, 1]), s2[:, 2].clamp(-4 * math.pi, 4 * math.pi), s2[:, 3].clamp(-9 * math.pi, 9 * math.pi)], 1)
+        term = (-torch.cos(s2[:, 0]) - torch.cos(s2[:, 0] + s2[:, 1])) > 1.0
+        return s2, torch.where(term, torch.zeros_like(u), -torch.ones_like(u)), term
+
+
+class DiscreteActions:
+    """A batched env with continuous actions driven by a table of discrete ones: action index i → ``table[i]``
+    (two pushes for CartPole, three torques for Acrobot or MountainCar)."""
+
+    def __init__(self, env, table):
+        self.env = env
+        self.table = torch.as_tensor(table, dtype=torch.float32, device=env.device).reshape(len(table), -1)
+        self.n_actions = self.table.shape[0]
+
+    def __getattr__(self, k):
+        return getattr(self.env, k)
+
+    def reset_batch(self):
+        return self.env.reset_batch()
+
+    def step_batch(self, a, auto_reset: bool = True):
+        return self.env.step_batch(self.table[a.long().reshape(-1)], auto_reset=auto_reset)
+
+    def selective_reset_batch(self):
+        pass
