@@ -62,3 +62,25 @@ def synthetic_episodes(n: int, length: int, cams: int, height: int, width: int, 
         out.append(dict(images=torch.randint(0, 256, (T, cams, 3, height, width), dtype=torch.uint8, generator=g),
                         qpos=q, action=q + torch.randn(T, joints, generator=g) * 0.01))
     return out
+
+
+def load_aloha_episode(path: str, cameras: Sequence[str] = None) -> dict:
+    """One ALOHA / ACT episode file (HDF5: ``/action [T, A]``, ``/observations/qpos [T, J]``,
+    ``/observations/images/<camera> [T, H, W, 3] uint8``) as the dict ``ACTDataset`` takes (images channel-first, cameras in
+    the given or the file's sorted order)."""
+    from ..io.hdf5 import H5File
+    with H5File(path) as f:
+        cams = list(cameras) if cameras is not None else f["observations/images"].keys()
+        frames = [torch.from_numpy(f[f"observations/images/{c}"].read()).permute(0, 3, 1, 2) for c in cams]
+        return dict(images=torch.stack(frames, 1).contiguous(), qpos=torch.from_numpy(f["observations/qpos"].read()).float(),
+                    action=torch.from_numpy(f["action"].read()).float(), cameras=cams, attrs=dict(f.attrs))
+
+
+def save_aloha_episode(path: str, episode: dict, cameras: Sequence[str], compression: str = "gzip"):
+    """The inverse of ``load_aloha_episode`` (episodes recorded here can be read by the usual ACT tooling)."""
+    from ..io.hdf5 import write_hdf5
+    img = torch.as_tensor(episode["images"])
+    tree = {"action": torch.as_tensor(episode["action"]).float().numpy(),
+            "observations": {"qpos": torch.as_tensor(episode["qpos"]).float().numpy(),
+                             "images": {c: img[:, i].permute(0, 2, 3, 1).contiguous().numpy() for i, c in enumerate(cameras)}}}
+    write_hdf5(path, tree, compression=compression, chunk_rows=max(1, min(64, img.shape[0] // 4 or 1)), attrs={"": {"sim": False}})
