@@ -56,6 +56,25 @@ def test_hyperparam_search(tmp_path):
     assert open(tmp_path / "s.csv").read().splitlines()[0] == "lr,h,score"
 
 
+def test_successive_halving_and_tabular_search(tmp_path):
+    from noeira_b200.agents.tabular import GridWorld, TabularAgent
+    from noeira_b200.core import hyperparam as hp
+    calls = []
+
+    def objective(cfg, budget):                       # better configurations improve faster with budget
+        calls.append((cfg["q"], budget))
+        return cfg["q"] * (1 - 0.5 ** budget)
+
+    rows = hp.successive_halving([{"q": q} for q in range(9)], objective, min_budget=1, eta=3, max_budget=9,
+                                 csv_path=str(tmp_path / "sh.csv"))
+    assert rows[0]["q"] == 8 and rows[0]["budget"] == 9 and rows[0]["rung"] == 2
+    assert sorted(b for _, b in calls) == [1] * 9 + [3] * 3 + [9]           # 9 → 3 → 1 survivors
+    assert open(tmp_path / "sh.csv").read().splitlines()[0] == "q,budget,score,rung"
+    res = hp.search_tabular(lambda c: TabularAgent(25, 4, kind=c["kind"], alpha=c["alpha"], eps=0.1, seed=0), lambda: GridWorld(),
+                            {"kind": ["q_learning", "sarsa"], "alpha": [0.02, 0.3]}, episodes=150)
+    assert len(res) == 4 and res[0]["score"] >= res[-1]["score"] and res[0]["score"] > 0.5 and {r["kind"] for r in res} == {"q_learning", "sarsa"}
+
+
 def test_act_dataset_chunks_and_masks():
     import torch
     from noeira_b200.data.act_dataset import ACTDataset, synthetic_episodes
