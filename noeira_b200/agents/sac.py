@@ -400,8 +400,72 @@ class TD3Trainer:
                 -self.cfg.action_scale, self.cfg.action_scale)
         return a
 
+    def _update_kernels(self, s, a, r, sp, d):
+        """The same update with the elementwise stages in ``csrc/sac_kernels.cu`` (smoothed target action + critic input rows,
+        target, critic gradients, actor gradient, deterministic loss reductions)."""
+        import ctypes
+        from .._native import check, cuda_lib, ptr, stream_ptr
+        cfg, lib, B = self.cfg, cuda_lib(), s.shape[0]
+        O, A, ci, cf = cfg.obs_dim, cfg.act_dim, ctypes.c_int, ctypes.c_float
+        g = getattr(self, "_glue_buf", None)
+        if g is None or g["B"] != B:
+            f = dict(device=self.device, dtype=torch.float32)
+            h = dict(device=self.device, dtype=torch.bfloat16)
+            pad = (O + A + 7) // 8 * 8
+            g = self._glue_buf = dict(B=B, sa=torch.zeros(B, pad, **h), sa2=torch.zeros(B, pad, **h), y=torch.zeros(B, **f),
+                                      dq1=torch.zeros(B, 8, **h), dq2=torch.zeros(B, 8, **h), dqa=torch.zeros(B, 8, **h),
+                                      da=torch.zeros(B, (A + 7) // 8 * 8, **h), partials=torch.zeros((B + 255) // 256 + 8, **f),
+                                      closs=torch.zeros(1, **f), aloss=torch.zeros(1, **f))
+            g["dqa"][:, 0] = -1.0 / B
+        s, a, sp = s.float().contiguous(), a.float().contiguous(), sp.float().contiguous()
+        r, d = r.float().contiguous(), d.float().contiguous()
+        st = stream_ptr()
+        z = torch.randn(B, A, device=self.device, generator=self.gen)
+        at = self.actor_t.forward(self._act_in(sp))
+        check(lib.nb_td3_pack(ptr(sp), ci(sp.stride(0)), ptr(at), ci(at.stride(0)), ptr(z) if cfg.policy_noise > 0 else None,
+                              cf(cfg.policy_noise), cf(cfg.noise_clip), cf(cfg.action_scale), ptr(g["sa"]), ci(g["sa"].stride(0)), ci(B),
+                              ci(O), ci(A), st), "td3_pack")
+        x = g["sa"][:, : O + A]
+        q1t, q2t = self.q1t.forward(x), self.q2t.forward(x)
+        check(lib.nb_sac_target(ptr(q1t), ci(q1t.stride(0)), ptr(q2t), ci(q2t.stride(0)), None, ptr(r), ptr(d), None, cf(cfg.gamma),
+                                ptr(g["y"]), ci(B), st), "td3_target")
+        check(lib.nb_sac_pack_sa(ptr(s), ci(s.stride(0)), ptr(a), ci(a.stride(0)), ptr(g["sa2"]), ci(g["sa2"].stride(0)), ci(B), ci(O),
+                                 ci(A), st), "sac_pack_sa")
+        x2 = g["sa2"][:, : O + A]
+        q1v, q2v = self.q1.forward(x2), self.q2.forward(x2)
+        check(lib.nb_sac_critic_grad(ptr(q1v), ci(q1v.stride(0)), ptr(q2v), ci(q2v.stride(0)), ptr(g["y"]), ptr(g["dq1"]), ptr(g["dq2"]),
+                                     ci(8), ptr(g["partials"]), ptr(g["closs"]), ci(B), st), "sac_critic_grad")
+        self.q1.vjp(g["dq1"][:, :1])
+        self.q2.vjp(g["dq2"][:, :1])
+        self.critic_opt.step(zero_grad=True)
+        self.total_train_steps += 1
+        out = dict(critic_loss=g["closs"][0])
+        if self.total_train_steps % cfg.policy_delay == 0:
+            api = self.actor.forward(self._act_in(s))
+            check(lib.nb_td3_pack(ptr(s), ci(s.stride(0)), ptr(api), ci(api.stride(0)), None, cf(0.0), cf(0.0), cf(cfg.action_scale),
+                                  ptr(g["sa"]), ci(g["sa"].stride(0)), ci(B), ci(O), ci(A), st), "td3_pack")
+            q1pi = self.q1.forward(g["sa"][:, : O + A])
+            check(lib.nb_column_sum(ptr(q1pi), ci(q1pi.stride(0)), ptr(g["partials"]), ptr(g["aloss"]), cf(-1.0 / B), ci(B), st), "column_sum")
+            ps = self.q1.params()
+            for p in ps:
+                p.frozen = True
+            dsa = self.q1.vjp(g["dqa"][:, :1])
+            for p in ps:
+                p.frozen = False
+            dsa = dsa if dsa.dtype == torch.bfloat16 else dsa.to(torch.bfloat16)
+            check(lib.nb_td3_actor_grad(ptr(dsa), ci(dsa.stride(0)), ptr(g["da"]), ci(g["da"].stride(0)), ci(B), ci(O), ci(A),
+                                        cf(cfg.action_scale), st), "td3_actor_grad")
+            self.actor.vjp(g["da"][:, :A])
+            self.actor_opt.step(zero_grad=True)
+            for t, o in ((self.actor_t, self.actor), (self.q1t, self.q1), (self.q2t, self.q2)):
+                t.polyak_from(o, cfg.tau)
+            out["actor_loss"] = g["aloss"][0]
+        return out
+
     def update(self, s, a, r, sp, d):
         cfg, B = self.cfg, s.shape[0]
+        if self.device.type == "cuda" and getattr(self, "use_kernels", True):
+            return self._update_kernels(s, a, r, sp, d)
         noise = (torch.randn(B, cfg.act_dim, device=self.device, generator=self.gen) * cfg.policy_noise).clamp(
             -cfg.noise_clip, cfg.noise_clip)
         ap = (cfg.action_scale * self.actor_t.forward(self._act_in(sp)).float() + noise).clamp(-cfg.action_scale, cfg.action_scale)

@@ -141,6 +141,39 @@ __global__ void sac_dist_bwd_kernel(const __nv_bfloat16* __restrict__ d1, int ld
   for (int j = 2 * A; j < ld_dp; ++j) dpacked[(size_t)i * ld_dp + j] = __float2bfloat16(0.f);
 }
 
+// TD3 / DDPG: critic input row [s | clamp(c·a + clamp(σ z, ±nc), ±c) | 0] from the actor's bf16 output (tanh applied);
+// z == nullptr: no smoothing noise (the actor pass)
+__global__ void td3_pack_kernel(const float* __restrict__ s, int ld_s, const __nv_bfloat16* __restrict__ a, int ld_a,
+                                const float* __restrict__ z, float sigma, float noise_clip, float c,
+                                __nv_bfloat16* __restrict__ out, int ld_o, int B, int O, int A) {
+  const int i = blockIdx.x;
+  for (int j = threadIdx.x; j < ld_o; j += blockDim.x) {
+    float v = 0.f;
+    if (j < O) v = s[(size_t)i * ld_s + j];
+    else if (j < O + A) {
+      const int k = j - O;
+      v = c * __bfloat162float(a[(size_t)i * ld_a + k]);
+      if (z) v = fminf(fmaxf(v + fminf(fmaxf(sigma * z[(size_t)i * A + k], -noise_clip), noise_clip), -c), c);
+    }
+    out[(size_t)i * ld_o + j] = __float2bfloat16(v);
+  }
+}
+// dL/d(actor output) = c · dQ/da from the critic's input gradient (columns [O, O + A)), as bf16 rows
+__global__ void td3_actor_grad_kernel(const __nv_bfloat16* __restrict__ dsa, int ld, __nv_bfloat16* __restrict__ out, int ld_o,
+                                      int B, int O, int A, float c) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B) return;
+  for (int j = 0; j < ld_o; ++j)
+    out[(size_t)i * ld_o + j] = __float2bfloat16(j < A ? c * __bfloat162float(dsa[(size_t)i * ld + O + j]) : 0.f);
+}
+__global__ void __launch_bounds__(256)
+column_partials_kernel(const float* __restrict__ x, int ld, float* __restrict__ partials, int B) {
+  __shared__ float sh[32];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const float s = block_sum(i < B ? x[(size_t)i * ld] : 0.f, sh);
+  if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
 // out[k] = scale · Σ partials[k][0..n)
 __global__ void sac_sum_partials_kernel(const float* __restrict__ partials, int n, int groups, float scale,
                                         float* __restrict__ out) {
@@ -215,6 +248,33 @@ int nb_sac_dist_bwd(const void* d1, int ld1, const void* d2, int ld2, const floa
   sac_dist_bwd_kernel<<<ceil_div(B, 128), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)d1, ld1, (const __nv_bfloat16*)d2,
                                                                          ld2, y, sdz, free_, alpha, (__nv_bfloat16*)dpacked,
                                                                          ld_dp, B, O, A, c);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_td3_pack(const float* s, int ld_s, const void* a, int ld_a, const float* z, float sigma, float noise_clip, float c,
+                void* out, int ld_o, int B, int O, int A, void* stream) {
+  if (B <= 0 || O + A > ld_o) return NB_ERR_BAD_ARG;
+  td3_pack_kernel<<<B, 64, 0, (cudaStream_t)stream>>>(s, ld_s, (const __nv_bfloat16*)a, ld_a, z, sigma, noise_clip, c,
+                                                     (__nv_bfloat16*)out, ld_o, B, O, A);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_td3_actor_grad(const void* dsa, int ld, void* out, int ld_o, int B, int O, int A, float c, void* stream) {
+  td3_actor_grad_kernel<<<ceil_div(B, 128), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dsa, ld, (__nv_bfloat16*)out, ld_o,
+                                                                           B, O, A, c);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+// out[0] = scale · Σ_i x[i · ld]   (mean of a column with scale = ±1 / B); partials needs ceil(B / 256) floats
+int nb_column_sum(const float* x, int ld, float* partials, float* out, float scale, int B, void* stream) {
+  const int nb_ = ceil_div(B, 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  column_partials_kernel<<<nb_, 256, 0, st>>>(x, ld, partials, B);
+  NB_LAUNCH_CHECK();
+  sac_sum_partials_kernel<<<1, 256, 0, st>>>(partials, nb_, 1, scale, out);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

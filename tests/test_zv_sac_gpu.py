@@ -75,3 +75,20 @@ def test_sac_kernel_path_matches_the_eager_tensor_path():
     for _ in range(5):
         k2.update(*batch)
     assert torch.equal(k2.actor_opt.arena.val, k.actor_opt.arena.val) and torch.equal(k2.critic_opt.arena.val, k.critic_opt.arena.val)
+
+
+def test_td3_kernel_path_matches_the_eager_tensor_path():
+    from noeira_b200.agents.sac import TD3Config, TD3Trainer
+    from noeira_b200.ops import check_status
+    k, e = TD3Trainer(TD3Config(seed=2), device="cuda"), TD3Trainer(TD3Config(seed=2), device="cuda")
+    e.use_kernels = False
+    batch = _batch("cuda")
+    for step in range(6):
+        mk, me = k.update(*batch), e.update(*batch)
+        torch.cuda.synchronize()
+        check_status()
+        assert set(mk) == set(me)
+        for key in mk:
+            assert abs(float(mk[key]) - float(me[key])) < 2e-2 * max(1.0, abs(float(me[key]))), (step, key, float(mk[key]), float(me[key]))
+    for a, b in ((k.actor_opt, e.actor_opt), (k.critic_opt, e.critic_opt)):
+        assert (a.arena.val - b.arena.val).abs().max().item() < 3e-3
