@@ -138,3 +138,100 @@ def write_jsonl(path: str, rows):
 
 def read_jsonl(path: str):
     return [json.loads(l) for l in open(path, encoding="utf-8") if l.strip()]
+
+
+# ------------------------------------------------------------------------------------------ zstd (system libzstd through ctypes)
+_ZSTD = None
+
+
+def _zstd():
+    global _ZSTD
+    if _ZSTD is None:
+        import ctypes
+        import ctypes.util
+        name = ctypes.util.find_library("zstd") or "libzstd.so.1"
+        lib = ctypes.CDLL(name)
+        lib.ZSTD_compressBound.restype = ctypes.c_size_t
+        lib.ZSTD_compressBound.argtypes = [ctypes.c_size_t]
+        lib.ZSTD_compress.restype = ctypes.c_size_t
+        lib.ZSTD_compress.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int]
+        lib.ZSTD_isError.restype = ctypes.c_uint
+        lib.ZSTD_isError.argtypes = [ctypes.c_size_t]
+        lib.ZSTD_getErrorName.restype = ctypes.c_char_p
+        lib.ZSTD_getErrorName.argtypes = [ctypes.c_size_t]
+        lib.ZSTD_createDStream.restype = ctypes.c_void_p
+        lib.ZSTD_freeDStream.argtypes = [ctypes.c_void_p]
+        lib.ZSTD_initDStream.restype = ctypes.c_size_t
+        lib.ZSTD_initDStream.argtypes = [ctypes.c_void_p]
+        lib.ZSTD_decompressStream.restype = ctypes.c_size_t
+        lib.ZSTD_decompressStream.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        _ZSTD = lib
+    return _ZSTD
+
+
+def zstd_compress(data: bytes, level: int = 3) -> bytes:
+    import ctypes
+    lib = _zstd()
+    cap = lib.ZSTD_compressBound(len(data))
+    buf = ctypes.create_string_buffer(cap)
+    n = lib.ZSTD_compress(buf, cap, data, len(data), level)
+    if lib.ZSTD_isError(n):
+        raise ValueError(f"zstd: {lib.ZSTD_getErrorName(n).decode()}")
+    return buf.raw[:n]
+
+
+def zstd_decompress(data: bytes, chunk: int = 1 << 17) -> bytes:
+    """Streaming decode: works for frames without a stored content size and for several concatenated frames (what a
+    chunked HTTP body of a ``.zst`` shard delivers)."""
+    import ctypes
+
+    class _Buf(ctypes.Structure):
+        _fields_ = [("ptr", ctypes.c_void_p), ("size", ctypes.c_size_t), ("pos", ctypes.c_size_t)]
+
+    lib = _zstd()
+    ds = lib.ZSTD_createDStream()
+    try:
+        lib.ZSTD_initDStream(ds)
+        src = ctypes.create_string_buffer(data, len(data))
+        inb = _Buf(ctypes.cast(src, ctypes.c_void_p), len(data), 0)
+        dst = ctypes.create_string_buffer(chunk)
+        out = bytearray()
+        while True:
+            outb = _Buf(ctypes.cast(dst, ctypes.c_void_p), chunk, 0)
+            rc = lib.ZSTD_decompressStream(ds, ctypes.byref(outb), ctypes.byref(inb))
+            if lib.ZSTD_isError(rc):
+                raise ValueError(f"zstd: {lib.ZSTD_getErrorName(rc).decode()}")
+            out += dst.raw[: outb.pos]
+            if inb.pos >= inb.size and outb.pos < chunk:
+                if rc != 0:
+                    raise ValueError("zstd: truncated frame")
+                return bytes(out)
+    finally:
+        lib.ZSTD_freeDStream(ds)
+
+
+# ------------------------------------------------------------------------------------------ tar archives
+def write_tar(path: str, members: dict, compression: str = ""):
+    """``members``: ``{name: bytes}``; ``compression``: "", "gz", "bz2" or "xz"."""
+    import io
+    import tarfile
+    with tarfile.open(path, f"w:{compression}" if compression else "w") as tf:
+        for name, data in members.items():
+            info = tarfile.TarInfo(name)
+            info.size = len(data)
+            tf.addfile(info, io.BytesIO(data))
+
+
+def read_tar(path: str, prefix: str = "") -> dict:
+    """Regular files of an archive (any compression tarfile recognises) as ``{name: bytes}``.  Members whose names would
+    leave the archive root (absolute paths, ``..``) are refused."""
+    import tarfile
+    out = {}
+    with tarfile.open(path, "r:*") as tf:
+        for m in tf:
+            if not m.isfile() or not m.name.startswith(prefix):
+                continue
+            if m.name.startswith("/") or ".." in m.name.split("/"):
+                raise ValueError(f"unsafe member name {m.name!r}")
+            out[m.name] = tf.extractfile(m).read()
+    return out

@@ -92,3 +92,20 @@ def test_act_dataset_chunks_and_masks():
     assert torch.allclose(ds.denormalise_action(act[k]), ds.action[t[k]: t[k] + 12], atol=1e-5)
     m = valid[:, 2:].bool()
     assert (valid[:, 2:].cumsum(1)[~m] == valid[:, 2:].sum(1, keepdim=True).expand(-1, 12)[~m]).all()   # padding only at the end
+
+
+def test_zstd_stream_and_tar(tmp_path):
+    import os
+    from noeira_b200.io import formats as F
+    data = (b"trajectory " * 5000) + os.urandom(3000)
+    z = F.zstd_compress(data, 5)
+    assert len(z) < len(data) // 4 and F.zstd_decompress(z) == data
+    two = z + F.zstd_compress(b"second frame")
+    assert F.zstd_decompress(two, chunk=1024) == data + b"second frame"        # concatenated frames, small output window
+    import pytest
+    with pytest.raises(ValueError):
+        F.zstd_decompress(z[:-5])
+    p = str(tmp_path / "shard.tar.gz")
+    F.write_tar(p, {"a/x.npy": b"123", "a/y.json": b"{}", "b/z.bin": bytes(range(10))}, compression="gz")
+    assert F.read_tar(p) == {"a/x.npy": b"123", "a/y.json": b"{}", "b/z.bin": bytes(range(10))}
+    assert list(F.read_tar(p, prefix="b/")) == ["b/z.bin"]
