@@ -28,7 +28,7 @@ from typing import Callable, Optional
 import torch
 
 from .. import nn
-from ..nn.losses import symlog, two_hot
+from ..nn.losses import symexp, symlog, two_hot
 from ..nn.module import Module
 from ..nn.transformer import RMSNorm, SelfAttention, SwiGLUFFN
 
@@ -426,3 +426,157 @@ def mae_mask(n: int, n_patches: int, p_min: float, p_max: float, gen: Optional[t
     """Per-sample masking ratio U(p_min, p_max); returns [n, n_patches] with 1 = masked."""
     ratio = p_min + (p_max - p_min) * torch.rand(n, 1, generator=gen, device=device)
     return (torch.rand(n, n_patches, generator=gen, device=device) < ratio).float()
+
+
+# ------------------------------------------------------------------------------------------ agent facade
+class Dreamer4Agent:
+    """The three training phases over one dynamics model and its heads
+    (noeira/deep_agents/dreamer4/agent.mojo:79-169, 716-1099):
+
+      ``bc_train_step``    video prediction (shortcut forcing on the latents) + behaviour cloning of the policy head on the
+                           agent-token outputs, one backward through the dynamics carrying both gradients
+      ``acwm_train_step``  action-conditioned world model + reward / continue heads
+      ``imag_train_step``  imagination RL with the dynamics frozen: roll the model forward from context frames with actions
+                           of the policy head (one shortcut sample of ``K`` Euler steps per frame), λ-returns, two-hot value
+                           TD loss, PMPO policy loss with a KL pull to the frozen behavioural prior
+
+    Latents ``z [B, T, NSP·DSP]`` come from the tokenizer; actions are discrete (one-hot conditioning, ``cfg.adim`` =
+    number of actions)."""
+
+    def __init__(self, cfg: Dreamer4Config, T: int, n_actions: int, n_bins: int = 41, head_hidden: int = 64, lr: float = 1e-3,
+                 gamma: float = 0.97, lam: float = 0.95, device="cpu"):
+        assert cfg.adim == n_actions, "discrete actions condition the dynamics as one-hot vectors: cfg.adim = n_actions"
+        self.cfg, self.T, self.nact, self.gamma, self.lam = cfg, T, n_actions, gamma, lam
+        self.device = torch.device(device)
+        self.dyn = Dreamer4Dynamics(cfg, T).to(self.device)
+        D = cfg.dim
+        nn.manual_seed(cfg.seed + 7)
+        self.ph, self.ph_prior = policy_head(D, head_hidden, n_actions).to(self.device), policy_head(D, head_hidden, n_actions).to(self.device)
+        self.rh, self.vh, self.ch = reward_head(D, head_hidden, n_bins).to(self.device), value_head(D, head_hidden, n_bins).to(self.device), \
+            continue_head(D, head_hidden).to(self.device)
+        self.ph_prior.copy_from(self.ph)
+        self.bins = torch.linspace(-10.0, 10.0, n_bins, device=self.device)
+        # one optimizer per group that a phase may freeze: a zero gradient alone would still move parameters through
+        # Adam's running moments
+        self.wm_opt = nn.Adam(list(self.dyn.named_params("dyn.")) + list(self.rh.named_params("rh.")) + list(self.ch.named_params("ch.")), lr=lr)
+        self.ph_opt = nn.Adam(self.ph.named_params("ph."), lr=lr)
+        self.vh_opt = nn.Adam(self.vh.named_params("vh."), lr=lr)
+        for o in (self.wm_opt, self.ph_opt, self.vh_opt):
+            o.max_grad_norm = 10.0
+        self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed + 11)
+
+    def named_params(self):
+        yield from self.dyn.named_params("dyn.")
+        for k, m in (("ph", self.ph), ("rh", self.rh), ("vh", self.vh), ("ch", self.ch)):
+            yield from m.named_params(k + ".")
+
+    # ---- shared: noise levels of a shortcut-forcing batch
+    def _levels(self, B, b_self):
+        """Signal level and step index per frame row: the first ``B − b_self`` sequences train at the finest step against
+        the data (flow-matching rows), the last ``b_self`` at a coarser step d = 1 / 2^e, e < emax, against two half steps."""
+        c, T = self.cfg, self.T
+        n, ns = B * T, b_self * T
+        step = torch.full((n,), c.emax, device=self.device, dtype=torch.long)
+        if ns:
+            step[n - ns:] = torch.randint(0, max(c.emax, 1), (ns,), device=self.device, generator=self.gen)
+        grid = 2 ** step
+        k = (torch.rand(n, device=self.device, generator=self.gen) * grid).long().clamp(max=c.kmax - 1)
+        k = torch.minimum(k, grid - 1)
+        sigma_idx = k * (c.kmax // grid)
+        return sigma_idx.float() / c.kmax, sigma_idx, step
+
+    def _one_hot(self, a):
+        return torch.nn.functional.one_hot(a.long().reshape(-1), self.nact).float()
+
+    def _wm_pass(self, z, actions):
+        B, T, ND = z.shape
+        z1 = z.reshape(B * T, ND)
+        z0 = torch.randn(z1.shape, device=self.device, generator=self.gen)
+        b_self = B // 4 if self.cfg.emax > 0 else 0
+        sigma, sidx, stp = self._levels(B, b_self)
+        return shortcut_forcing_loss(self.dyn, z1, z0, sigma, sidx, stp, T, b_self, self.cfg.kmax, do_boot=b_self > 0,
+                                     actions=None if actions is None else self._one_hot(actions))
+
+    @staticmethod
+    def _finish(*opts):
+        for o in opts:
+            if o.max_grad_norm > 0:
+                o.clip()
+            o.step(zero_grad=True)
+
+    def bc_train_step(self, z, actions):
+        """z [B, T, ND], actions [B, T] (the action taken at frame t): video prediction + BC."""
+        B, T, _ = z.shape
+        loss, grad, _ = self._wm_pass(z, None)
+        h = self.dyn.agent_out().reshape(B * T, -1)
+        logits = self.ph.forward(h).float()
+        logp = torch.log_softmax(logits, -1)
+        onehot = self._one_hot(actions)
+        bc = -(onehot * logp).sum(-1).mean()
+        dh = self.ph.vjp((logp.exp() - onehot) / (B * T))
+        self.dyn.vjp(grad, dh.reshape(B, T, -1))
+        self._finish(self.wm_opt, self.ph_opt)
+        return dict(wm_loss=float(loss), bc_loss=float(bc))
+
+    def acwm_train_step(self, z, actions, rewards, cont):
+        """Action-conditioned world model + reward and continue heads (rewards / cont [B, T] arriving at frame t)."""
+        B, T, _ = z.shape
+        loss, grad, _ = self._wm_pass(z, actions)
+        h = self.dyn.agent_out().reshape(B * T, -1)
+        rl, drl = two_hot_ce(self.rh.forward(h).float(), rewards.reshape(-1), self.bins)
+        cl, dcl = continue_bce(self.ch.forward(h).float(), cont.reshape(-1, 1))
+        dh = self.rh.vjp(drl) + self.ch.vjp(dcl)
+        self.dyn.vjp(grad, dh.reshape(B, T, -1))
+        self._finish(self.wm_opt)
+        return dict(wm_loss=float(loss), reward_loss=float(rl), cont_loss=float(cl))
+
+    @torch.no_grad()
+    def _features(self, window, acts):
+        """Agent-token outputs of a window of clean frames ``[B, T, ND]`` (finest signal level, one-step index)."""
+        c, (B, T, ND) = self.cfg, window.shape
+        self.dyn.set_actions(acts.reshape(B * T, -1))
+        self.dyn.set_indices(torch.full((B * T,), c.kmax - 1, device=self.device), torch.full((B * T,), c.emax, device=self.device))
+        self.dyn.forward(window.reshape(B * T, ND))
+        return self.dyn.agent_out()[:, -1]
+
+    def imag_train_step(self, context, context_actions, horizon: int = 6, K: int = 2, alpha: float = 0.5, beta: float = 0.3):
+        """context [B, T, ND] real latents, context_actions [B, T]: imagine ``horizon`` frames, train value and policy heads."""
+        c, (B, T, ND) = self.cfg, context.shape
+        win, acts = context.clone(), self._one_hot(context_actions).reshape(B, T, -1)
+        feats, actions = [], []
+        for _ in range(horizon):
+            h = self._features(win, acts)                                         # state of the newest frame
+            with torch.no_grad():
+                a = torch.multinomial(_unimix_probs(self.ph.forward(h).float())[0], 1, generator=self.gen)[:, 0]
+            feats.append(h), actions.append(a)
+            a_win = torch.cat([acts[:, 1:], self._one_hot(a)[:, None]], 1)        # the new action conditions the next frame
+            z_next = sample_one_timestep(self.dyn, win[:, 1:].reshape(B * (T - 1), ND), torch.randn(B, ND, device=self.device, generator=self.gen),
+                                         T, c.kmax, K, actions=a_win.reshape(B * T, -1))
+            win, acts = torch.cat([win[:, 1:], z_next[:, None]], 1), a_win
+        feats.append(self._features(win, acts))
+        F_ = torch.stack(feats, 1).detach()                                       # [B, H+1, D]
+        A_ = torch.stack(actions + [actions[-1]], 1)
+        H1 = horizon + 1
+        flat = F_.reshape(B * H1, -1)
+        with torch.no_grad():
+            rew = symexp((torch.softmax(self.rh.forward(flat).float(), -1) * self.bins).sum(-1)).reshape(B, H1)
+            con = self.gamma * torch.sigmoid(self.ch.forward(flat).float()).reshape(B, H1)
+        vlogits = self.vh.forward(flat).float().reshape(B, H1, -1)
+        val = symexp((torch.softmax(vlogits, -1) * self.bins).sum(-1)).detach()
+        ret = lambda_returns(rew, val, con, self.lam)
+        vloss, dv = value_td_loss(vlogits, ret, self.bins)
+        self.vh.vjp(dv.reshape(B * H1, -1))
+        plogits = self.ph.forward(flat).float().reshape(B, H1, -1)
+        with torch.no_grad():
+            prior = self.ph_prior.forward(flat).float().reshape(B, H1, -1)
+        ploss, dp = pmpo_policy_loss(plogits, prior, A_, ret - val[:, :-1], alpha, beta)
+        self.ph.vjp(dp.reshape(B * H1, -1))
+        self._finish(self.ph_opt, self.vh_opt)                                    # the world model's optimizer does not step
+        return dict(value_loss=float(vloss), policy_loss=float(ploss), imag_return=float(ret.mean()), imag_reward=float(rew[:, 1:].mean()))
+
+
+def two_hot_ce(logits, target, bins):
+    """Cross entropy against the two-hot encoding of symlog(target); returns (loss, dL/dlogits)."""
+    tgt = two_hot(symlog(target.float()), bins)
+    logp = torch.log_softmax(logits.float(), -1)
+    return -(tgt * logp).sum(-1).mean(), (logp.exp() - tgt) / logits.shape[0]

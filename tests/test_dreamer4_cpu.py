@@ -163,3 +163,42 @@ def test_tokenizer_gradients_and_patchify_roundtrip():
     _fd(loss, list(tok.named_params()), n=3, eps=2e-2, tol=8e-2)   # sigmoid outputs summed over 1.7 k pixels: wide steps keep fp32 rounding out of the quotient
     z = tok.encode(p)
     assert z.shape == (6, 6) and float(z.abs().max()) <= 1.0
+
+
+def test_agent_facade_three_phases():
+    """Video prediction + BC, action-conditioned world model + reward / continue heads, imagination RL with the dynamics
+    frozen: losses fall on a synthetic latent process whose next frame depends on the action."""
+    from noeira_b200.agents.dreamer4 import Dreamer4Agent, Dreamer4Config
+    cfg = Dreamer4Config(nsp=4, dsp=4, dim=32, heads=2, ff=64, depth=1, nreg=1, kmax=4, adim=3, seed=0)
+    T, B, ND = 4, 8, 16
+    ag = Dreamer4Agent(cfg, T, n_actions=3, n_bins=21, head_hidden=32, lr=2e-3)
+    g = torch.Generator().manual_seed(0)
+    base = torch.randn(3, ND, generator=g)
+
+    def batch():
+        a = torch.randint(0, 3, (B, T), generator=g)
+        z = torch.zeros(B, T, ND)
+        z[:, 0] = torch.randn(B, ND, generator=g) * 0.3
+        for t in range(1, T):
+            z[:, t] = 0.5 * z[:, t - 1] + base[a[:, t - 1]] + 0.05 * torch.randn(B, ND, generator=g)
+        rew = (a == 2).float().roll(1, 1)                                  # reward for having chosen action 2
+        rew[:, 0] = 0
+        return z, a, rew, torch.ones(B, T)
+
+    first = ag.acwm_train_step(*batch())
+    for _ in range(60):
+        last = ag.acwm_train_step(*batch())
+    assert all(v == v for v in last.values())
+    assert last["wm_loss"] < first["wm_loss"] and last["reward_loss"] < first["reward_loss"] and last["cont_loss"] < first["cont_loss"]
+    z, a, _, _ = batch()
+    b0 = ag.bc_train_step(z, torch.full_like(a, 1))
+    for _ in range(30):
+        b1 = ag.bc_train_step(batch()[0], torch.full((B, T), 1))
+    assert b1["bc_loss"] < 0.5 * b0["bc_loss"]                             # the policy head clones the constant demonstrator
+    dyn_before = [p.data.clone() for _, p in ag.dyn.named_params()]
+    ph_before = ag.ph.params()[0].data.clone()
+    out = ag.imag_train_step(z, a, horizon=3, K=2)
+    assert all(v == v for v in out.values()) and 0.0 <= out["imag_reward"]
+    assert all(torch.equal(p.data, q) for (_, p), q in zip(ag.dyn.named_params(), dyn_before))      # dynamics frozen
+    assert not torch.equal(ag.ph.params()[0].data, ph_before)
+    assert [n.split(".")[0] for n, _ in ag.named_params()][0] == "dyn"
