@@ -50,7 +50,9 @@ struct GemmParams {
   unsigned int* status;
   // implicit-GEMM convolution (conv != 0): A is never materialised; the producer reads activation patches of the NHWC
   // input through a 4-D tensor map (c, w, h, b), one box of conv_bw output pixels x 64 channels per TMA
-  int conv, conv_c, conv_ow, conv_oh, conv_kw, conv_pad, conv_bw;
+  // conv == 2: weight gradient.  A = patches^T is MN-major: the SAME shared-memory image as the forward's A tile (rows =
+  // pixels, 128 bytes of channels), now read with the pixels as the reduction dimension; B = dy, MN-major
+  int conv, conv_c, conv_ow, conv_oh, conv_kw, conv_pad, conv_bw, conv_taps, conv_b;
 };
 
 __device__ __forceinline__ void tma_load_4d_g(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z, int w) {
@@ -320,7 +322,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-          if (p.conv) {
+          if (p.conv == 2) {
+            // rows of the tile = 2 chunks of 64 channels of one filter tap each; k-block kb = 64 output pixels as runs of
+            // bw consecutive pixels of one output row.  A chunk past the last tap and pixels past the last image read the
+            // zero fill (image index out of range), so the byte count of the stage stays the same.
+            const int bw = p.conv_bw, per_img = p.conv_oh * p.conv_ow;
+            for (int h = 0; h < BM / 64; ++h) {
+              const int kpos = mb * BM + h * 64, tap = kpos / p.conv_c, c0 = kpos - tap * p.conv_c;
+              const int kh = tap / p.conv_kw, kw = tap - kh * p.conv_kw;
+              for (int i = 0; i < BK / bw; ++i) {
+                const int m0 = kb * BK + i * bw;
+                int bimg = m0 / per_img;
+                const int rem = m0 - bimg * per_img;
+                const int oh = rem / p.conv_ow, ow0 = rem - oh * p.conv_ow;
+                if (tap >= p.conv_taps) bimg = p.conv_b;
+                tma_load_4d_g(sa + h * (64 * BK * 2) + i * bw * 128, &tmA, &full_bar[stage], c0, ow0 - p.conv_pad + kw,
+                              oh - p.conv_pad + kh, bimg);
+              }
+            }
+          } else if (p.conv) {
             // k-block kb = 64 channels [c0, c0+64) of filter tap (kh, kw); the 128 output pixels of the tile are
             // 128 / bw runs of bw consecutive pixels of one output row (bw divides OW and 128), stride 1:
             // input pixel = output pixel + tap − pad; coordinates outside the image read the zero fill
@@ -1025,9 +1045,61 @@ int nb_conv_implicit_fwd(const void* x, const void* Wt, void* y, int B, int H, i
   p.D = y; p.bias = bias; p.aux = (const __nv_bfloat16*)residual; p.status = status;
   p.ws = nullptr; p.tile_ctr = nullptr;
   p.conv = 1; p.conv_c = C; p.conv_ow = OW; p.conv_oh = OH; p.conv_kw = KW; p.conv_pad = pad; p.conv_bw = bw;
+  p.conv_taps = KH * KW; p.conv_b = B;
   cudaStream_t s = (cudaStream_t)stream;
   if (BN == 128) return launch<128, 6>(tmA, tmB, p, 0, 0, s);
   return launch<64, 8>(tmA, tmB, p, 0, 0, s);
+}
+
+
+// Implicit-GEMM weight gradient of a stride-1 convolution: dW[KH·KW·C, OC] (+)= patches(x)^T · dy without the patch
+// matrix.  x NHWC bf16 [B, H, W, C], C % 64 == 0; dy bf16 [B·OH·OW, OC] (row pitch ld_dy); dW fp32 (row pitch ld_dw), the
+// result is ADDED to it.  OW needs a power-of-two factor bw in [8, 64].  Split-K over the pixels through `workspace`.
+int nb_conv_implicit_wgrad(const void* x, const void* dy, float* dW, int B, int H, int Wd, int C, int OC, int KH, int KW, int pad,
+                           int ld_dy, int ld_dw, unsigned int* status, void* workspace, long long workspace_bytes, void* stream) {
+  const int OH = H + 2 * pad - KH + 1, OW = Wd + 2 * pad - KW + 1;
+  if (B <= 0 || OH <= 0 || OW <= 0 || C % 64 || OC <= 0) return NB_ERR_BAD_ARG;
+  int bw = 1;
+  while (bw < 64 && OW % (bw * 2) == 0) bw *= 2;
+  if (bw < 8) return NB_ERR_BAD_ARG;
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return NB_ERR_NO_DRIVER_SYMBOL;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return NB_ERR_UNALIGNED;
+  CUtensorMap tmA, tmB;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Wd, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)Wd * C * 2, (cuuint64_t)H * Wd * C * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)bw, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return NB_ERR_TENSORMAP;
+  }
+  const int Mpix = B * OH * OW, Kc = KH * KW * C;
+  int BN = 128;
+  if (OC <= 64 || (long long)ceil_div(Kc, BM) * ceil_div(OC, 128) * 2 < sm_count()) BN = 64;
+  int rc = make_tmap_bf16(&tmB, dy, OC, Mpix, ld_dy, 64, BK);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = Kc; p.N = OC; p.K = Mpix;
+  p.a_mn = 1; p.b_mn = 1; p.tf32 = 0;
+  p.ldd = ld_dw; p.ld_aux = 0;
+  p.out_f32 = 1; p.accumulate = 1; p.act = 0; p.dact = 0;
+  p.alpha = 1.f;
+  p.D = dW; p.bias = nullptr; p.aux = nullptr; p.status = status;
+  p.ws = nullptr; p.tile_ctr = nullptr;
+  long long ws_bytes = 0;
+  if (workspace && workspace_bytes > NB_GEMM_WS_COUNTERS * 4 + (1 << 20)) {
+    p.tile_ctr = (unsigned int*)workspace;
+    p.ws = (float*)((char*)workspace + NB_GEMM_WS_COUNTERS * 4);
+    ws_bytes = workspace_bytes - NB_GEMM_WS_COUNTERS * 4;
+  }
+  p.conv = 2; p.conv_c = C; p.conv_ow = OW; p.conv_oh = OH; p.conv_kw = KW; p.conv_pad = pad; p.conv_bw = bw;
+  p.conv_taps = KH * KW; p.conv_b = B;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (BN == 128) return launch<128, 6>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
+  return launch<64, 8>(tmA, tmB, p, ws_bytes, NB_GEMM_WS_COUNTERS, s);
 }
 
 }  // extern "C"

@@ -39,6 +39,8 @@ class Conv2D(Module):
         self.need_input_grad = need_input_grad
         self.force_implicit = False
         self.implicit_gemm = os.environ.get("NOEIRA_B200_IMPLICIT_CONV", "1") != "0"
+        # weight gradient straight from the NHWC input (no patch matrix in the backward either)
+        self.implicit_wgrad = os.environ.get("NOEIRA_B200_IMPLICIT_WGRAD", "0") == "1"
         self.weight = self.add_param("weight", (k * k * self.icp, oc), decay=True, init=Kaiming(), fan_in=ic * k * k,
                                      fan_out=oc)
         if self.icp != ic:
@@ -55,7 +57,8 @@ class Conv2D(Module):
             return False
         # a trainable layer needs the patch matrix for its weight gradient anyway; building it in the forward and
         # reusing it measured 0.3 ms faster per ACT step than implicit forward + rebuild in the backward
-        if self.training and torch.is_grad_enabled() and not self.weight.frozen and not self.force_implicit:
+        if self.training and torch.is_grad_enabled() and not self.weight.frozen and not self.force_implicit \
+                and not (self.implicit_wgrad and self._implicit_wgrad_ok(OW)):
             return False
         bw = 1
         while bw < 128 and OW % (bw * 2) == 0:
@@ -142,8 +145,11 @@ class Conv2D(Module):
             from .layers import act_backward
             d2 = act_backward(d2.contiguous(), self._y[:, : self.oc].contiguous() if self._y.shape[1] != self.oc else self._y, "relu")
         if not self.weight.frozen:
-            col = self._col if self._col is not None else self._patches()
-            ops.gemm(col, d2, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=self.oc)
+            if self._col is None and self._xin is not None and self.implicit_wgrad and self._implicit_wgrad_ok(OW):
+                self._implicit_wgrad(d2, B, H, W)
+            else:
+                col = self._col if self._col is not None else self._patches()
+                ops.gemm(col, d2, a_mn=True, b_mn=True, out=self.weight.grad_storage, accumulate=True, n=self.oc)
             if self.bias is not None:
                 colsum_into(d2, self.bias.grad_storage, self.oc)
         if not self.need_input_grad:
@@ -158,6 +164,23 @@ class Conv2D(Module):
         check(cuda_lib().nb_col2im(ptr(dcol), ptr(dx), *(ctypes.c_int(v) for v in (B, H, W, self.icp, self.k, self.k, self.stride,
                                                                                self.pad, OH, OW, K)), stream_ptr()), "col2im")
         return dx
+
+    def _implicit_wgrad_ok(self, OW):
+        bw = 1
+        while bw < 64 and OW % (bw * 2) == 0:
+            bw *= 2
+        return self.stride == 1 and self.icp % 64 == 0 and bw >= 8
+
+    def _implicit_wgrad(self, d2, B, H, W):
+        """dW += patches(x)ᵀ · dy with the patches read by the GEMM's TMA producer from the saved NHWC input."""
+        from ..ops.gemm import default_workspace
+        from ..ops.status import device_status
+        x, g = self._xin, self.weight.grad_storage
+        d2 = d2 if (d2.stride(0) * 2) % 16 == 0 and d2.data_ptr() % 16 == 0 else d2.contiguous()
+        ws = default_workspace(x.device)
+        check(cuda_lib().nb_conv_implicit_wgrad(ptr(x), ptr(d2), ptr(g), *(ctypes.c_int(v) for v in (
+            B, H, W, self.icp, self.oc, self.k, self.k, self.pad, d2.stride(0), g.stride(0))), ptr(device_status(x.device)),
+            ptr(ws), ctypes.c_longlong(ws.numel()), stream_ptr()), "conv_implicit_wgrad")
 
     def _implicit_dgrad_ok(self, W):
         """Stride-1 layers with at least 64 output channels: the input gradient is itself a stride-1 convolution of
