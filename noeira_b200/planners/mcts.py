@@ -295,3 +295,47 @@ class BatchedMCTS:
         t.prior[:, 0] = pri
         root_value = t.value_sum[:, 0] / t.visit[:, 0]
         return improved, root_value, action
+
+
+class SampledMCTS:
+    """Tree search over continuous (or very large) action spaces: every node carries ``K`` actions SAMPLED from the policy at
+    that node, and the tree branches over those K slots (Sampled MuZero).  The priors of the slots are uniform — the
+    samples already follow the policy, so the visit counts of the slots estimate the improved policy relative to it.
+
+    ``initial(obs) → (latent, policy_params, value)``, ``recurrent(latent, action [n, act_dim]) → (latent', reward, policy_params',
+    value')``, ``sample(policy_params, K, generator) → actions [n, K, act_dim]``.  ``search`` returns the root's sampled actions,
+    their visit-count weights, the root value and the chosen action vector."""
+
+    def __init__(self, cfg: MCTSConfig, initial: Callable, recurrent: Callable, sample: Callable, act_dim: int,
+                 use_kernels: Optional[bool] = None):
+        self.K, self.act_dim, self.sample = cfg.n_actions, act_dim, sample
+        self._initial, self._recurrent = initial, recurrent
+        self.node_actions = None
+        self._gen = None
+        self.inner = BatchedMCTS(cfg, self._init_cb, self._rec_cb, use_kernels)
+
+    def _init_cb(self, obs):
+        latent, params, value = self._initial(obs)
+        n, dev = latent.shape[0], latent.device
+        N = self.inner.cfg.n_simulations + 1
+        if self.node_actions is None or self.node_actions.shape[0] != n or self.node_actions.device != dev:
+            self.node_actions = torch.zeros(n, N, self.K, self.act_dim, device=dev)
+        self.node_actions[:, 0] = self.sample(params, self.K, self._gen)
+        return latent, torch.zeros(n, self.K, device=dev), value
+
+    def _rec_cb(self, latent, slot):
+        t = self.inner.tree
+        ar = torch.arange(latent.shape[0], device=latent.device)
+        action = self.node_actions[ar, t.leaf_parent.long(), slot]
+        nl, r, params, v = self._recurrent(latent, action)
+        new = t.n_nodes.long().clamp(max=t.N - 1)                       # the index the expansion is about to use
+        self.node_actions[ar, new] = self.sample(params, self.K, self._gen)
+        return nl, r, torch.zeros(latent.shape[0], self.K, device=latent.device), v
+
+    @torch.no_grad()
+    def search(self, obs, temperature: float = 0.0, generator=None):
+        self._gen = generator
+        weights, value, slot = self.inner.search(obs, temperature=temperature, generator=generator)
+        actions = self.node_actions[:, 0].clone()
+        chosen = actions[torch.arange(actions.shape[0], device=actions.device), slot]
+        return actions, weights, value, chosen

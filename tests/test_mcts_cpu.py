@@ -101,3 +101,36 @@ def test_gumbel_search_improves_the_policy_with_few_simulations():
     legal[:, 0] = False
     pol3, _, act3 = mcts.search_gumbel(obs, legal=legal, greedy=True)
     assert (act3 != 0).all() and float(pol3[:, 0].max()) < 1e-6
+
+
+def test_sampled_search_over_continuous_actions():
+    """One-step continuous bandit: reward −(a − target)² per tree, policy N(0, 1).  Among the K sampled root actions the
+    search must concentrate its visits on those nearest the target and return one of the best."""
+    from noeira_b200.planners.mcts import MCTSConfig, SampledMCTS
+    n, K = 16, 12
+    g = torch.Generator().manual_seed(0)
+    target = torch.rand(n, generator=g) * 2 - 1
+
+    def initial(obs):
+        return obs, torch.zeros(n, 2), torch.zeros(n)                       # latent = [target, moved flag]
+
+    def recurrent(latent, action):
+        first = latent[:, 1] == 0
+        r = torch.where(first, -(action[:, 0] - latent[:, 0]) ** 2, torch.zeros(latent.shape[0]))
+        nxt = latent.clone()
+        nxt[:, 1] = 1.0
+        return nxt, r, torch.zeros(latent.shape[0], 2), torch.zeros(latent.shape[0])
+
+    def sample(params, k, gen):
+        return torch.randn(params.shape[0], k, 1, generator=gen)
+
+    obs = torch.stack([target, torch.zeros(n)], 1)
+    mcts = SampledMCTS(MCTSConfig(n_actions=K, n_simulations=48, discount=1.0, max_depth=49), initial, recurrent, sample, act_dim=1,
+                       use_kernels=False)
+    actions, w, value, chosen = mcts.search(obs, generator=g)
+    assert actions.shape == (n, K, 1) and chosen.shape == (n, 1) and torch.allclose(w.sum(1), torch.ones(n), atol=1e-5)
+    err = (actions[..., 0] - target[:, None]).abs()
+    # unvisited slots count as the worst value (as in MuZero), so not every sample is tried with 48 simulations: the chosen
+    # action is among the better half of the samples, and the visits concentrate near the target
+    assert ((chosen[:, 0] - target).abs() <= err.median(1).values + 1e-6).float().mean() > 0.85
+    assert float((w * err).sum(1).mean()) < float(err.mean()) * 0.6
