@@ -1,0 +1,189 @@
+// Top-down car racing: one fused step kernel (tile test + tire model + rigid hull, one warp per lane of the batch) and the
+// ego-centric grey-scale camera (one CTA per lane: cull the track to the view, then one thread per pixel).
+// The tire model is the slip model of Gymnasium's car_dynamics.py on a single rigid hull, as the reference's
+// noeira/physics2d/car/ does (wheel_friction.mojo, car_dynamics.mojo); the image palette (grass 0.3, road 0.7, car 1.0)
+// follows noeira/envs/car_racing/car_racing_pixel.mojo.
+#include "common.cuh"
+
+namespace {
+
+struct CarParams {
+  float dt, engine_power, brake_force, wheel_moment, wheel_radius, friction_limit, friction_coef, grass_friction;
+  float steer_limit, steer_speed, steer_gain, hull_mass, hull_inertia, half_width, playfield, tile_reward, lap_fraction;
+  float wheel_x[4], wheel_y[4];
+};
+
+constexpr int CAR_HDR = 16;   // x y angle vx vy omega | joint_fl joint_fr | wheel omega x4 | track id | visited | gas | spare
+
+__device__ __forceinline__ float seg_dist2(float qx, float qy, float ax, float ay, float bx, float by) {
+  const float ex = bx - ax, ey = by - ay, px = qx - ax, py = qy - ay;
+  const float l2 = ex * ex + ey * ey;
+  float t = l2 > 0.f ? (px * ex + py * ey) / l2 : 0.f;
+  t = fminf(fmaxf(t, 0.f), 1.f);
+  const float dx = px - t * ex, dy = py - t * ey;
+  return dx * dx + dy * dy;
+}
+
+// state [N, CAR_HDR + T] -> next [N, CAR_HDR + T]; action [N, lda] (steer, gas, brake); track [K, T, 2]
+__global__ void car_step_kernel(const float* __restrict__ state, const float* __restrict__ action, int lda,
+                                const float* __restrict__ track, int T, float* __restrict__ next, float* __restrict__ reward,
+                                float* __restrict__ term, int N, CarParams P) {
+  const int env = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (env >= N) return;
+  const int S = CAR_HDR + T;
+  const float* s = state + (size_t)env * S;
+  float* o = next + (size_t)env * S;
+  const float x = s[0], y = s[1], ang = s[2], vx = s[3], vy = s[4], om = s[5];
+  float joint[4] = {s[6], s[7], 0.f, 0.f}, womega[4] = {s[8], s[9], s[10], s[11]};
+  const int trk = (int)s[12];
+  float gas_state = s[14];
+  const float* tr = track + (size_t)trk * T * 2;
+  const float ca = cosf(ang), sa = sinf(ang);
+  float wx[4], wy[4], rx[4], ry[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    rx[w] = ca * P.wheel_x[w] - sa * P.wheel_y[w];
+    ry[w] = sa * P.wheel_x[w] + ca * P.wheel_y[w];
+    wx[w] = x + rx[w];
+    wy[w] = y + ry[w];
+  }
+  // tiles under the wheels: friction surface, visit flags, reward
+  const float w2 = P.half_width * P.half_width;
+  float dmin[4] = {3.4e38f, 3.4e38f, 3.4e38f, 3.4e38f};
+  int fresh = 0;
+  for (int j = lane; j < T; j += 32) {
+    const int j1 = j + 1 == T ? 0 : j + 1;
+    const float ax = tr[2 * j], ay = tr[2 * j + 1], bx = tr[2 * j1], by = tr[2 * j1 + 1];
+    bool hit = false;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float d = seg_dist2(wx[w], wy[w], ax, ay, bx, by);
+      dmin[w] = fminf(dmin[w], d);
+      hit |= d <= w2;
+    }
+    const float was = s[CAR_HDR + j];
+    if (hit && was == 0.f) ++fresh;
+    o[CAR_HDR + j] = (hit || was != 0.f) ? 1.f : 0.f;
+  }
+#pragma unroll
+  for (int sft = 16; sft; sft >>= 1) {
+    fresh += __shfl_xor_sync(0xffffffffu, fresh, sft);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) dmin[w] = fminf(dmin[w], __shfl_xor_sync(0xffffffffu, dmin[w], sft));
+  }
+  if (lane) return;
+  const float* a = action + (size_t)env * lda;
+  const float steer = fminf(fmaxf(a[0], -1.f), 1.f), gas = fminf(fmaxf(a[1], 0.f), 1.f), brake = fminf(fmaxf(a[2], 0.f), 1.f);
+  gas_state += fminf(gas - gas_state, 0.1f);
+  float fx = 0.f, fy = 0.f, tq = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    if (w < 2) {   // steering servo
+      const float diff = -steer * P.steer_limit - joint[w];
+      const float rate = copysignf(fminf(P.steer_gain * fabsf(diff), P.steer_speed), diff);
+      const float stepv = rate * P.dt;
+      joint[w] += fabsf(stepv) > fabsf(diff) ? diff : stepv;
+    } else {       // engine on the rear axle
+      womega[w] += P.dt * P.engine_power * gas_state / P.wheel_moment / (fabsf(womega[w]) + 5.f);
+    }
+    if (brake >= 0.9f) womega[w] = 0.f;
+    else if (brake > 0.f) {
+      const float val = fminf(P.brake_force * brake, fabsf(womega[w]));
+      womega[w] -= copysignf(val, womega[w]);
+    }
+    const float wa = ang + joint[w], cw = cosf(wa), sw = sinf(wa);
+    const float fdx = -sw, fdy = cw, sdx = cw, sdy = sw;
+    const float pvx = vx - om * ry[w], pvy = vy + om * rx[w];
+    const float vf = fdx * pvx + fdy * pvy, vs = sdx * pvx + sdy * pvy;
+    float ff = (-vf + womega[w] * P.wheel_radius) * P.friction_coef, pf = -vs * P.friction_coef;
+    const float lim = P.friction_limit * (dmin[w] <= w2 ? 1.f : P.grass_friction);
+    const float mag = sqrtf(ff * ff + pf * pf);
+    if (mag > lim) { ff *= lim / mag; pf *= lim / mag; }
+    womega[w] -= P.dt * ff * P.wheel_radius / P.wheel_moment;
+    const float gx = pf * sdx + ff * fdx, gy = pf * sdy + ff * fdy;
+    fx += gx; fy += gy; tq += rx[w] * gy - ry[w] * gx;
+  }
+  const float vx2 = vx + P.dt * fx / P.hull_mass, vy2 = vy + P.dt * fy / P.hull_mass, om2 = om + P.dt * tq / P.hull_inertia;
+  const float x2 = x + P.dt * vx2, y2 = y + P.dt * vy2;
+  const float visited = s[13] + (float)fresh;
+  const bool out = fabsf(x2) > P.playfield || fabsf(y2) > P.playfield;
+  const bool lap = visited >= P.lap_fraction * (float)T;
+  o[0] = x2; o[1] = y2; o[2] = ang + P.dt * om2; o[3] = vx2; o[4] = vy2; o[5] = om2;
+  o[6] = joint[0]; o[7] = joint[1];
+  o[8] = womega[0]; o[9] = womega[1]; o[10] = womega[2]; o[11] = womega[3];
+  o[12] = s[12]; o[13] = visited; o[14] = gas_state; o[15] = s[15];
+  reward[env] = out ? -100.f : -0.1f + P.tile_reward * (float)fresh;
+  term[env] = (out || lap) ? 1.f : 0.f;
+}
+
+// pose = the state rows (x, y, angle first, track id at 12); image [N, res, res], the car at (res/2, cy) heading up
+__global__ void car_render_kernel(const float* __restrict__ state, int S, const float* __restrict__ track, int T,
+                                  float* __restrict__ img, int res, float px_per_unit, float cy, float half_width,
+                                  float car_hw, float car_hl) {
+  extern __shared__ float seg[];   // culled segments: ax ay bx by
+  __shared__ int nseg;
+  const int env = blockIdx.x;
+  const float* s = state + (size_t)env * S;
+  const float x = s[0], y = s[1], ang = s[2];
+  const float* tr = track + (size_t)((int)s[12]) * T * 2;
+  if (threadIdx.x == 0) nseg = 0;
+  __syncthreads();
+  const float ca = cosf(ang), sa = sinf(ang);
+  // the view is a square of res / px_per_unit world units; its circumscribed circle about the view centre
+  const float span = (float)res / px_per_unit;
+  const float vcy = (cy - 0.5f * (float)res) / px_per_unit;        // view centre ahead of the car by this much
+  const float ccx = x + (-sa) * vcy, ccy = y + ca * vcy;
+  const float R = 0.7072f * span + half_width;
+  for (int j = threadIdx.x; j < T; j += blockDim.x) {
+    const int j1 = j + 1 == T ? 0 : j + 1;
+    const float ax = tr[2 * j], ay = tr[2 * j + 1], bx = tr[2 * j1], by = tr[2 * j1 + 1];
+    if (seg_dist2(ccx, ccy, ax, ay, bx, by) <= R * R) {
+      const int k = atomicAdd(&nseg, 1);
+      seg[4 * k] = ax; seg[4 * k + 1] = ay; seg[4 * k + 2] = bx; seg[4 * k + 3] = by;
+    }
+  }
+  __syncthreads();
+  const int n = nseg;
+  const float w2 = half_width * half_width;
+  for (int p = threadIdx.x; p < res * res; p += blockDim.x) {
+    const int i = p / res, j = p - i * res;
+    const float lx = ((float)j + 0.5f - 0.5f * (float)res) / px_per_unit, ly = (cy - ((float)i + 0.5f)) / px_per_unit;
+    float v = 0.3f;
+    if (fabsf(lx) <= car_hw && fabsf(ly) <= car_hl) v = 1.0f;
+    else {
+      const float qx = x + ca * lx - sa * ly, qy = y + sa * lx + ca * ly;
+      for (int k = 0; k < n; ++k)
+        if (seg_dist2(qx, qy, seg[4 * k], seg[4 * k + 1], seg[4 * k + 2], seg[4 * k + 3]) <= w2) { v = 0.7f; break; }
+    }
+    img[(size_t)env * res * res + p] = v;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// params: 17 scalars in the order of CarParams followed by wheel_x[4], wheel_y[4] (25 floats, host memory)
+int nb_car_step(const float* state, const float* action, int lda, const float* track, int T, float* next, float* reward,
+                float* term, int N, const float* params, void* stream) {
+  if (N <= 0 || T <= 0 || lda < 3) return NB_ERR_BAD_ARG;
+  CarParams P;
+  float* dst = &P.dt;
+  for (int i = 0; i < 17; ++i) dst[i] = params[i];
+  for (int w = 0; w < 4; ++w) { P.wheel_x[w] = params[17 + w]; P.wheel_y[w] = params[21 + w]; }
+  const int tpb = 128;
+  car_step_kernel<<<(N * 32 + tpb - 1) / tpb, tpb, 0, (cudaStream_t)stream>>>(state, action, lda, track, T, next, reward, term, N, P);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_car_render(const float* state, int S, const float* track, int T, float* img, int N, int res, float px_per_unit,
+                  float cy, float half_width, float car_hw, float car_hl, void* stream) {
+  if (N <= 0 || T <= 0 || res <= 0 || (size_t)T * 16 > 48 * 1024) return NB_ERR_BAD_ARG;
+  car_render_kernel<<<N, 256, (size_t)T * 16, (cudaStream_t)stream>>>(state, S, track, T, img, res, px_per_unit, cy, half_width,
+                                                                     car_hw, car_hl);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+}  // extern "C"

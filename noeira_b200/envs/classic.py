@@ -64,6 +64,7 @@ class _TensorEnv(BatchedEnv):
         self.done.copy_(done.float())
         self.ep_return += r
         self.next_obs.copy_(self._observe(s2))
+        self.pre_reset_state = s2
         self.ep_stats[2] += r.sum()
         self.ep_stats[3] += self.n_envs
         if auto_reset and bool(done.any()):
