@@ -245,8 +245,8 @@ class FModule:
 
 
 class Tape:
-    def __init__(self, device="cpu", seed: int = 0):
-        self.device = torch.device(device)
+    def __init__(self, device="cpu", seed: int = 0, dtype=torch.float32):
+        self.device, self.dtype = torch.device(device), dtype
         self.nodes: List[_Node] = []
         self._params: Dict[str, FTensor] = {}
         self._modules: Dict[str, FModule] = {}
@@ -277,8 +277,8 @@ class Tape:
         return self.param(rows, cols, "zeros", name, decay=False)
 
     def constant(self, data) -> FTensor:
-        v = data if isinstance(data, torch.Tensor) else torch.as_tensor(data, dtype=torch.float32)
-        return FTensor(self, _Node("const", (), v.to(self.device, torch.float32), needs_grad=False))
+        v = data if isinstance(data, torch.Tensor) else torch.as_tensor(data, dtype=self.dtype)
+        return FTensor(self, _Node("const", (), v.to(self.device, self.dtype), needs_grad=False))
 
     def input(self, data) -> FTensor:
         """A leaf that receives a gradient (read it from ``.grad`` after ``backward``)."""
