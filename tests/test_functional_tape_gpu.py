@@ -16,7 +16,6 @@ def _net(tape, x, y, ps):
 def test_cuda_tape_matches_the_cpu_tape_and_trains():
     from noeira_b200.experimental.functional import Tape, TapeAdam
     from noeira_b200.ops import check_status
-    from noeira_b200 import _native
     g = torch.Generator().manual_seed(0)
     x, y = torch.randn(256, 64, generator=g), torch.randn(256, 8, generator=g)
     tapes = {}
@@ -24,7 +23,6 @@ def test_cuda_tape_matches_the_cpu_tape_and_trains():
         t = Tape(device=dev, seed=1)
         ps = (t.param(64, 128, name="w1"), t.zeros(1, 128, name="b1"), t.param(128, 8, "xavier", name="w2"), t.zeros(1, 8, name="b2"))
         tapes[dev] = (t, ps)
-    before = _native.launch_count() if hasattr(_native, "launch_count") else None
     losses = {}
     for dev, (t, ps) in tapes.items():
         loss = _net(t, x.to(dev), y.to(dev), ps)
