@@ -210,8 +210,7 @@ class GeneralModel:
         if collide_pairs is None:
             collide_pairs = [(i, j) for i in range(len(self.geoms)) for j in range(i + 1, len(self.geoms))
                              if self.geoms[i][0] != self.geoms[j][0] and self.parent[self.geoms[i][0]] != self.geoms[j][0]
-                             and self.parent[self.geoms[j][0]] != self.geoms[i][0]
-                             and not ({self.geoms[i][1].type, self.geoms[j][1].type} == {"box", "capsule"})]
+                             and self.parent[self.geoms[j][0]] != self.geoms[i][0]]
         self.pairs = list(collide_pairs)
 
     def t(self, x):
@@ -471,7 +470,8 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
         if ta == "box" or tb == "box":
             if ta == "box" and tb == "box":
                 # vertex-face contacts both ways (8 + 8 slots): a corner of one box inside the other is pushed out through
-                # the nearest face of the box that contains it.  Edge-edge crossings without a contained corner are not found.
+                # the nearest face of the box that contains it; one more slot holds the edge-edge contact of the separating-axis
+                # test (active only when an edge-cross axis is the axis of least overlap)
                 for g_in, g_box in ((gi, gj), (gj, gi)):
                     b_in, gin, c_in, R_in = _geom_frame(m, k, g_in)
                     b_bx, gbx, c_bx, R_bx = _geom_frame(m, k, g_box)
@@ -482,20 +482,24 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
                                 p = c_in + R_in @ (h_in * m.t([sx, sy, sz]))
                                 n, d = _point_in_box(p, c_bx, R_bx, h_bx)
                                 add(p + n * (0.5 * d)[:, None], n, d, b_bx, b_in, fr)
+                p, n, d = _box_box_edge_contact(*_geom_frame(m, k, gi)[2:], m.t(m.geoms[gi][1].size),
+                                                *_geom_frame(m, k, gj)[2:], m.t(m.geoms[gj][1].size))
+                add(p, n, d, m.geoms[gi][0], m.geoms[gj][0], fr)
             else:
                 g_s, g_b = (gi, gj) if tb == "box" else (gj, gi)
-                b_s, gs, c_s, _ = _geom_frame(m, k, g_s)
+                b_s, gs, c_s, R_s = _geom_frame(m, k, g_s)
                 b_b, gb, c_b, R_b = _geom_frame(m, k, g_b)
-                loc = (R_b.transpose(1, 2) @ (c_s - c_b)[:, :, None])[..., 0]
                 h = m.t(gb.size)
-                near = c_b + (R_b @ torch.maximum(torch.minimum(loc, h), -h)[:, :, None])[..., 0]      # closest point of the box
-                diff = c_s - near
-                dist = diff.norm(dim=-1)
-                inside = dist < 1e-9
-                n_in, d_in = _point_in_box(c_s, c_b, R_b, h)                                       # centre inside the box
-                n = torch.where(inside[:, None], n_in, diff / dist.clamp(min=1e-12)[:, None])
-                d = torch.where(inside, d_in + gs.size[0], gs.size[0] - dist)
-                add(c_s - n * (gs.size[0] - 0.5 * d)[:, None], n, d, b_b, b_s, fr)
+                if gs.type == "sphere":
+                    centres = [c_s]
+                else:
+                    # capsule: the point of its axis nearest to the box (alternating projections between the segment and
+                    # the box, both convex) and the two ends, each as a sphere against the box
+                    ax = R_s[:, :, 2] * gs.size[1]
+                    centres = [_segment_point_nearest_box(c_s - ax, 2 * ax, c_b, R_b, h), c_s - ax, c_s + ax]
+                for cc in centres:
+                    p, n, d = _sphere_box(cc, gs.size[0], c_b, R_b, h)
+                    add(p, n, d, b_b, b_s, fr)
             continue
         ba, pa, da, ra = _spheres_of(m, k, gi)
         bb, pb, db, rb = _spheres_of(m, k, gj)
@@ -510,6 +514,83 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
         z = torch.zeros(B, 0, 3, dtype=k.xpos.dtype, device=k.xpos.device)
         return Contacts(z, z, z[..., 0], [], [], m.t([]))
     return Contacts(torch.stack(pts, 1), torch.stack(nrm, 1), torch.stack(dep, 1), b1, b2, m.t(mu))
+
+
+def _sphere_box(c_s, radius, c_b, R_b, h):
+    """Contact (point, normal from the box to the sphere, depth) of a sphere against a box."""
+    loc = (R_b.transpose(1, 2) @ (c_s - c_b)[:, :, None])[..., 0]
+    near = c_b + (R_b @ torch.maximum(torch.minimum(loc, h), -h)[:, :, None])[..., 0]      # closest point of the box
+    diff = c_s - near
+    dist = diff.norm(dim=-1)
+    inside = dist < 1e-9
+    n_in, d_in = _point_in_box(c_s, c_b, R_b, h)                                       # centre inside the box
+    n = torch.where(inside[:, None], n_in, diff / dist.clamp(min=1e-12)[:, None])
+    d = torch.where(inside, d_in + radius, radius - dist)
+    return c_s - n * (radius - 0.5 * d)[:, None], n, d
+
+
+def _segment_point_nearest_box(p0, dvec, c_b, R_b, h, iters: int = 12):
+    """The point of the segment p0 + t·dvec (t ∈ [0, 1]) nearest to a box, by alternating projections."""
+    l2 = (dvec * dvec).sum(-1).clamp(min=1e-18)
+    t = torch.full_like(l2, 0.5)
+    for _ in range(iters):
+        q = p0 + t[:, None] * dvec
+        loc = (R_b.transpose(1, 2) @ (q - c_b)[:, :, None])[..., 0]
+        on_box = c_b + (R_b @ torch.maximum(torch.minimum(loc, h), -h)[:, :, None])[..., 0]
+        t = (((on_box - p0) * dvec).sum(-1) / l2).clamp(0, 1)
+    return p0 + t[:, None] * dvec
+
+
+def _box_box_edge_contact(c_a, R_a, h_a, c_b, R_b, h_b):
+    """Separating-axis test of two boxes over the 6 face axes and the 9 edge-cross axes.  Returns one contact (point,
+    normal from A to B, depth) that is active (depth > 0) only where the boxes overlap AND the axis of least overlap is an
+    edge-cross axis: the closest points of the two supporting edges.  Face-axis cases are left to the vertex-face contacts."""
+    B = c_a.shape[0]
+    t = c_b - c_a
+    best_d = torch.full((B,), float("inf"), dtype=c_a.dtype, device=c_a.device)
+    face_d = best_d.clone()
+    best_n = torch.zeros(B, 3, dtype=c_a.dtype, device=c_a.device)
+    best_ij = torch.zeros(B, 2, dtype=torch.long, device=c_a.device)
+    separated = torch.zeros(B, dtype=torch.bool, device=c_a.device)
+
+    def overlap(axis):
+        ra = ((R_a.transpose(1, 2) @ axis[:, :, None])[..., 0].abs() * h_a).sum(-1)
+        rb = ((R_b.transpose(1, 2) @ axis[:, :, None])[..., 0].abs() * h_b).sum(-1)
+        return ra + rb - (t * axis).sum(-1).abs()
+    for R in (R_a, R_b):
+        for i in range(3):
+            ov = overlap(R[:, :, i])
+            separated |= ov <= 0
+            face_d = torch.minimum(face_d, ov)
+    for i in range(3):
+        for j in range(3):
+            cr = torch.linalg.cross(R_a[:, :, i], R_b[:, :, j])
+            ln = cr.norm(dim=-1)
+            ok = ln > 1e-6                                       # parallel edges: the face axes cover it
+            axis = cr / ln.clamp(min=1e-12)[:, None]
+            ov = torch.where(ok, overlap(axis), torch.full_like(ln, float("inf")))
+            separated |= ov <= 0
+            better = ov < best_d
+            best_d = torch.where(better, ov, best_d)
+            sgn = torch.where((t * axis).sum(-1) < 0, -1.0, 1.0)
+            best_n = torch.where(better[:, None], axis * sgn[:, None], best_n)
+            best_ij = torch.where(better[:, None], torch.tensor([i, j], device=c_a.device)[None].expand(B, 2), best_ij)
+    # a small bias towards face contacts keeps resting boxes on their vertex-face contacts
+    use = (~separated) & (best_d < 0.95 * face_d - 1e-9)
+    # the supporting edges: from each centre go to the extreme along ±n on the two axes that are not the edge's own
+    def edge(c, R, h, idx, direction):
+        pt = c.clone()
+        for kx in range(3):
+            sg = torch.sign((R[:, :, kx] * direction).sum(-1))
+            sg = torch.where(sg == 0, torch.ones_like(sg), sg)
+            pt = pt + torch.where(idx == kx, torch.zeros_like(sg), sg * h[kx])[:, None] * R[:, :, kx]
+        d = R.gather(2, idx[:, None, None].expand(-1, 3, 1))[..., 0] * h[idx][:, None]
+        return pt - d, 2 * d
+    pa, da = edge(c_a, R_a, h_a, best_ij[:, 0], best_n)
+    pb, db = edge(c_b, R_b, h_b, best_ij[:, 1], -best_n)
+    qa, qb = closest_segment_points(pa, da, pb, db)
+    depth = torch.where(use, best_d, -torch.ones_like(best_d))
+    return 0.5 * (qa + qb), best_n, depth
 
 
 def _point_in_box(p, c, R, h):
@@ -607,9 +688,14 @@ def constraint_rows(m: GeneralModel, k: Kin, qpos, qvel, con: Contacts) -> Rows:
     return Rows(J, aref, dimp, active, kind, par, m.t(mu), body)
 
 
-def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters=50):
+def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters=50, cone: str = "pyramidal", noslip_iters: int = 0):
     """Forces ``f [B, nr]`` of the soft-constraint problem (A + R) f + J q̈₀ − a_ref = 0 with f ≥ 0 on unilateral rows and
-    |f| ≤ μ f_normal on friction rows.  Returns (f, q̈)."""
+    |f| ≤ μ f_normal on friction rows.  Returns (f, q̈).
+
+    ``cone="elliptic"`` (PGS only) bounds the NORM of the two tangential forces of a contact by μ f_normal (a circular cone)
+    instead of each of them (the box that circumscribes it): the pair is updated as a block and scaled back onto the disc.
+    ``noslip_iters`` more PGS sweeps over the friction rows alone, with their regularisation R removed, take out the slow
+    creep that the soft friction rows allow under a sustained tangential load."""
     B, nr = rows.aref.shape
     if nr == 0:
         return rows.aref, qacc0
@@ -640,11 +726,16 @@ def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters
                 fi = f[:, i] - res / dA[:, i]
                 if kind[i] == 0:
                     fi = fi.clamp(min=0)
-                else:
+                elif cone != "elliptic":
                     lim = mu[i] * f[:, par[i]].clamp(min=0)
                     fi = torch.maximum(torch.minimum(fi, lim), -lim)
                 f = f.clone()
                 f[:, i] = fi
+                if kind[i] == 1 and cone == "elliptic" and i > 0 and kind[i - 1] == 1 and par[i - 1] == par[i]:
+                    lim = mu[i] * f[:, par[i]].clamp(min=0)
+                    nrm = (f[:, i - 1] ** 2 + f[:, i] ** 2).sqrt()
+                    sc = torch.where(nrm > lim, lim / nrm.clamp(min=1e-30), torch.ones_like(nrm))
+                    f[:, i - 1], f[:, i] = f[:, i - 1] * sc, f[:, i] * sc
     elif solver == "newton":
         eye = torch.eye(nr, dtype=A.dtype, device=A.device)[None]
         for _ in range(iters):
@@ -699,13 +790,31 @@ def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters
         f = torch.maximum(torch.minimum(f, hi), lo)
     else:
         raise ValueError(solver)
+    if noslip_iters > 0:
+        fr_rows = [i for i in range(nr) if kind[i] == 1]
+        dA0 = torch.diagonal(A, dim1=1, dim2=2) - R * act                          # friction rows without their softness
+        for _ in range(noslip_iters):
+            for i in fr_rows:
+                res = (A[:, i] * f).sum(-1) - R[:, i] * act[:, i] * f[:, i] + b[:, i]
+                fi = f[:, i] - res / dA0[:, i].clamp(min=1e-12)
+                lim = mu[i] * f[:, par[i]].clamp(min=0)
+                f = f.clone()
+                f[:, i] = torch.maximum(torch.minimum(fi, lim), -lim)
+                if cone == "elliptic" and i > 0 and kind[i - 1] == 1 and par[i - 1] == par[i]:
+                    nrm = (f[:, i - 1] ** 2 + f[:, i] ** 2).sqrt()
+                    sc = torch.where(nrm > lim, lim / nrm.clamp(min=1e-30), torch.ones_like(nrm))
+                    f[:, i - 1], f[:, i] = f[:, i - 1] * sc, f[:, i] * sc
     f = f * act
     return f, qacc0 + (Minv_Jt @ f[:, :, None])[..., 0]
 
 
 # ------------------------------------------------------------------------------------------ stepping
 class GeneralSim:
-    def __init__(self, model: GeneralModel, n: int, integrator: str = "euler", solver: str = "newton", solver_iters: int = 20):
+    def __init__(self, model: GeneralModel, n: int, integrator: str = "euler", solver: str = "newton", solver_iters: int = 20,
+                 cone: str = "pyramidal", noslip_iters: int = 0):
+        self.cone, self.noslip_iters = cone, noslip_iters
+        if cone == "elliptic" and solver != "pgs":
+            raise ValueError("the elliptic cone is a projection of the PGS solver")
         self.m, self.n, self.integrator, self.solver, self.solver_iters = model, n, integrator, solver, solver_iters
         self.qpos, self.qvel = model.init_state(n)
         self.ctrl = torch.zeros(n, len(model.motors), dtype=model.dtype, device=model.device)
@@ -733,7 +842,7 @@ class GeneralSim:
         qacc0 = torch.linalg.solve(Mh, tau[:, :, None])[..., 0]
         con = collide(m, k)
         rows = constraint_rows(m, k, qpos, qvel, con)
-        f, qacc = solve_constraints(m, Mh, qacc0, rows, self.solver, self.solver_iters)
+        f, qacc = solve_constraints(m, Mh, qacc0, rows, self.solver, self.solver_iters, self.cone, self.noslip_iters)
         self.last = dict(kin=k, M=M, qacc=qacc, rows=rows, force=f, contacts=con, qvel=qvel)
         return qacc
 

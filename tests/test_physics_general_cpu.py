@@ -318,3 +318,108 @@ def test_fixed_tendon_spring_limit_and_energy():
     # the stop absorbs most of the relative motion (a soft, critically damped constraint), momentum is shared
     assert 0.05 <= worst < 0.06 and abs(float(s2.qvel[0, 0] - s2.qvel[0, 1])) < 0.1
     assert abs(float(s2.qvel[0, 0] + s2.qvel[0, 1]) - 0.5) < 1e-9
+
+
+def test_capsule_on_box_and_crossed_boxes_edge_contact():
+    opt = Options(timestep=0.002, solref=(0.01, 1.0))
+    base = Body(-1, (0, 0, 0.1), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("box", (0.4, 0.4, 0.1), density=3000.0)])
+    # a capsule lying along x on top of the box: axis point + both ends carry it, so it neither sinks nor tips
+    cap = Body(-1, (0.05, 0.0, 0.262), joints=[Joint(G.FREE, (0, 0, 1))],
+               geoms=[Geom("capsule", (0.06, 0.2), quat=(0.70710678, 0, 0.70710678, 0))])
+    m = G.GeneralModel([base, cap], opt=opt, plane=True)
+    sim = G.GeneralSim(m, 1, solver="newton", solver_iters=30)
+    for _ in range(500):
+        sim.step()
+    assert float(sim.qvel.abs().max()) < 5e-3
+    assert abs(float(sim.qpos[0, 7 + 2]) - 0.26) < 4e-3                             # box top 0.2 + radius 0.06
+    zaxis = G.quat_to_mat(sim.qpos[:, 10:14])[0, :, 2]
+    assert float(zaxis[2]) > 0.9995                                                 # the body did not tip (its capsule stays level)
+    # geometry: the nearest point of a segment to a box, against dense sampling
+    g = torch.Generator().manual_seed(0)
+    p0 = torch.randn(64, 3, generator=g, dtype=torch.float64)
+    dv = torch.randn(64, 3, generator=g, dtype=torch.float64)
+    cb = 0.3 * torch.randn(64, 3, generator=g, dtype=torch.float64)
+    q = torch.randn(64, 4, generator=g, dtype=torch.float64)
+    Rb = G.quat_to_mat(q / q.norm(dim=1, keepdim=True))
+    h = torch.tensor([0.3, 0.2, 0.1], dtype=torch.float64)
+
+    def dist_to_box(pts):
+        loc = (Rb.transpose(1, 2)[:, None] @ (pts - cb[:, None])[..., None])[..., 0]
+        return (loc - torch.maximum(torch.minimum(loc, h), -h)).norm(dim=-1)
+    near = G._segment_point_nearest_box(p0, dv, cb, Rb, h, iters=40)
+    ts = torch.linspace(0, 1, 2001, dtype=torch.float64)
+    dense = dist_to_box(p0[:, None] + ts[None, :, None] * dv[:, None]).min(1).values
+    assert (dist_to_box(near[:, None])[:, 0] - dense).abs().max() < 2e-3
+
+    # two boxes crossed at 45° and tilted so that an EDGE of the upper one lies across an EDGE of the lower one
+    c_a, c_b = torch.zeros(1, 3, dtype=torch.float64), torch.tensor([[0.0, 0.0, 0.27]], dtype=torch.float64)
+    R_a = G.axis_angle_mat(torch.tensor([1.0, 0.0, 0.0], dtype=torch.float64), torch.tensor([math.pi / 4], dtype=torch.float64))
+    R_b = G.axis_angle_mat(torch.tensor([0.0, 1.0, 0.0], dtype=torch.float64), torch.tensor([math.pi / 4], dtype=torch.float64))
+    ha = hb = torch.tensor([0.5, 0.1, 0.1], dtype=torch.float64)
+    # lower box: long axis x, its upper edge along x at height 0.1·√2; upper box: long axis... rotate so its long axis is y
+    R_b = G.axis_angle_mat(torch.tensor([0.0, 0.0, 1.0], dtype=torch.float64), torch.tensor([math.pi / 2], dtype=torch.float64)) @ \
+        G.axis_angle_mat(torch.tensor([1.0, 0.0, 0.0], dtype=torch.float64), torch.tensor([math.pi / 4], dtype=torch.float64))
+    p, n, d = G._box_box_edge_contact(c_a, R_a, ha, c_b, R_b, hb)
+    want = 2 * 0.1 * math.sqrt(2) - 0.27                                            # the two ridge edges overlap by this much
+    assert abs(float(d) - want) < 1e-9 and torch.allclose(n, torch.tensor([[0.0, 0.0, 1.0]], dtype=torch.float64), atol=1e-9)
+    assert torch.allclose(p, torch.tensor([[0.0, 0.0, 0.135]], dtype=torch.float64), atol=1e-9)
+    # no corner of either box is inside the other: the vertex-face test alone finds nothing here
+    for (ci, Ri, hi, cj, Rj, hj) in ((c_a, R_a, ha, c_b, R_b, hb), (c_b, R_b, hb, c_a, R_a, ha)):
+        for sx in (-1, 1):
+            for sy in (-1, 1):
+                for sz in (-1, 1):
+                    corner = ci + (Ri @ (hi * torch.tensor([sx, sy, sz], dtype=torch.float64)))
+                    assert float(G._point_in_box(corner, cj, Rj, hj)[1]) < 0
+    # separated, and face-to-face stacks, give no edge contact
+    assert float(G._box_box_edge_contact(c_a, R_a, ha, c_b + 0.1, R_b, hb)[2]) < 0
+    eye = torch.eye(3, dtype=torch.float64)[None]
+    assert float(G._box_box_edge_contact(c_a, eye, ha, torch.tensor([[0.0, 0.0, 0.19]], dtype=torch.float64), eye, hb)[2]) < 0
+    # dynamics: the crossed upper box comes to rest on the ridge of the lower one (held fixed as a heavy body on the plane)
+    low = Body(-1, (0, 0, 0.1 * math.sqrt(2)), quat=(math.cos(math.pi / 8), math.sin(math.pi / 8), 0, 0), joints=[],
+               geoms=[Geom("box", (0.5, 0.1, 0.1))])
+    qz, qx = (math.cos(math.pi / 4), 0, 0, math.sin(math.pi / 4)), (math.cos(math.pi / 8), math.sin(math.pi / 8), 0, 0)
+    quat = tuple(float(v) for v in G.quat_mul(torch.tensor([qz], dtype=torch.float64), torch.tensor([qx], dtype=torch.float64))[0])
+    up = Body(-1, (0, 0, 0.1 * math.sqrt(2) + 0.28), quat=quat, joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("box", (0.5, 0.1, 0.1))])
+    m2 = G.GeneralModel([low, up], opt=opt, plane=False)
+    sim2 = G.GeneralSim(m2, 1, solver="newton", solver_iters=30)
+    for _ in range(150):
+        sim2.step()
+    z = float(sim2.qpos[0, 2])
+    assert 0.1 * math.sqrt(2) + 0.27 < z < 0.1 * math.sqrt(2) + 0.285 and abs(float(sim2.qvel[0, 2])) < 0.05    # caught by the edge contact
+
+
+def test_elliptic_cone_is_isotropic_and_noslip_removes_creep():
+    opt = Options(timestep=0.002, solref=(0.01, 1.0))
+    # slide the same box along a tangent axis and along the diagonal between the two: the circular cone decelerates both at
+    # μ g, the pyramid's diagonal gets up to √2 μ g
+    stop = {}
+    for cone in ("pyramidal", "elliptic"):
+        m = _free_box(opt, z=0.05, plane=True, friction=0.5)
+        sim = G.GeneralSim(m, 2, integrator="euler", solver="pgs", solver_iters=25, cone=cone)
+        sim.qvel[0, 0] = 2.0
+        sim.qvel[1, 0] = sim.qvel[1, 1] = 2.0 / math.sqrt(2)
+        t = [None, None]
+        for i in range(250):
+            sim.step()
+            sp = sim.qvel[:, :2].norm(dim=1)
+            for e in range(2):
+                if t[e] is None and float(sp[e]) < 1e-3:
+                    t[e] = i * opt.timestep
+        stop[cone] = t
+    ideal = 2.0 / (0.5 * 9.81)
+    assert all(abs(v - ideal) < 0.12 * ideal for v in stop["elliptic"]), stop        # the block projection is near isotropic
+    assert abs(stop["elliptic"][0] - stop["elliptic"][1]) < 0.1 * ideal
+    assert min(stop["pyramidal"]) < 0.85 * ideal                                    # the box bound brakes one of them harder
+    with pytest.raises(ValueError):
+        G.GeneralSim(m, 1, solver="newton", cone="elliptic")
+    # a box on a slope below the friction angle creeps with soft friction rows and holds with the no-slip sweeps
+    slope = math.radians(15.0)
+    drift = {}
+    for ns in (0, 10):
+        o2 = Options(timestep=0.002, solref=(0.02, 1.0), gravity=(9.81 * math.sin(slope), 0.0, -9.81 * math.cos(slope)))
+        m = _free_box(o2, z=0.05, plane=True, friction=0.8)
+        sim = G.GeneralSim(m, 1, solver="pgs", solver_iters=20, noslip_iters=ns)
+        for _ in range(150):
+            sim.step()
+        drift[ns] = abs(float(sim.qpos[0, 0]))
+    assert drift[10] < 0.2 * drift[0] and drift[10] < 1e-3, drift
