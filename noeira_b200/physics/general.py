@@ -105,8 +105,9 @@ class GeneralModel:
 
     def __init__(self, bodies: Sequence[Body], motors: Sequence[Motor] = (), opt: Options = None, dtype=torch.float64,
                  device="cpu", collide_pairs: Optional[Sequence[Tuple[int, int]]] = None, plane: bool = True,
-                 tendons: Sequence[Tendon] = ()):
+                 tendons: Sequence[Tendon] = (), hfield=None, broadphase: bool = False):
         self.opt = opt or Options()
+        self.hfield, self.broadphase = hfield, broadphase            # a narrowphase.HeightField fixed in the world; SAP pruning
         self.dtype, self.device = dtype, torch.device(device)
         t = lambda x: torch.as_tensor(x, dtype=dtype, device=self.device)
         self.nb = len(bodies)
@@ -160,6 +161,13 @@ class GeneralModel:
                     m, I = capsule_mass_inertia(g.size[0], g.size[1], g.density)
                     R = quat_to_mat(t(g.quat))
                     I = torch.diagonal(R @ torch.diag(t(I)) @ R.T).tolist()
+                elif g.type == "mesh":
+                    from .narrowphase import mesh_mass_inertia
+                    m, I, c = mesh_mass_inertia(g.vertices, g.density)            # in the geom's axes (taken as the body's)
+                    parts.append((m, list(I), [a + b for a, b in zip(g.pos, c)]))
+                    m_tot += m
+                    first = [f + m * (a + b) for f, a, b in zip(first, g.pos, c)]
+                    continue
                 else:
                     m, I = box_mass_inertia(g.size, g.density)
                 parts.append((m, list(I), list(g.pos)))
@@ -451,6 +459,12 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
     if m.plane:
         for gi in range(len(m.geoms)):
             b, g, c, R = _geom_frame(m, k, gi)
+            if g.type == "mesh":
+                for vtx in g.vertices:
+                    p = c + R @ m.t(vtx)
+                    d = g.size[0] + m.opt.plane_offset - (p * n_pl).sum(-1)
+                    add(p - n_pl * (g.size[0] - 0.5 * d)[:, None], n_pl.expand_as(p), d, -1, b, g.friction)
+                continue
             if g.type == "box":
                 h = m.t(g.size)
                 for sx in (-1, 1):
@@ -464,9 +478,26 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
             for e in ends:
                 d = g.size[0] - ((e * n_pl).sum(-1) - m.opt.plane_offset)
                 add(e - n_pl * (g.size[0] - 0.5 * d)[:, None], n_pl.expand_as(e), d, -1, b, g.friction)
-    for gi, gj in m.pairs:
+    if m.hfield is not None:
+        for gi in range(len(m.geoms)):
+            b, g, c, R = _geom_frame(m, k, gi)
+            fr = math.sqrt(g.friction * m.hfield.friction)
+            for centre, radius in _support_points(m, g, c, R):
+                p, n, d = m.hfield.contact(centre, radius)
+                add(p, n, d, -1, b, fr)
+    pairs = m.pairs
+    if m.broadphase and len(m.geoms) >= 2:
+        from .narrowphase import sap_overlaps
+        lo, hi = _geom_aabbs(m, k)
+        keep = sap_overlaps(lo, hi, pairs)
+        pairs = [pr for pr, kp in zip(pairs, keep) if kp]
+    for gi, gj in pairs:
         ta, tb = m.geoms[gi][1].type, m.geoms[gj][1].type
         fr = math.sqrt(m.geoms[gi][1].friction * m.geoms[gj][1].friction)
+        if ta == "mesh" or tb == "mesh":
+            for p, n, d in _convex_pair(m, k, gi, gj):
+                add(p, n, d, m.geoms[gi][0], m.geoms[gj][0], fr)
+            continue
         if ta == "box" or tb == "box":
             if ta == "box" and tb == "box":
                 # vertex-face contacts both ways (8 + 8 slots): a corner of one box inside the other is pushed out through
@@ -514,6 +545,59 @@ def collide(m: GeneralModel, k: Kin) -> Contacts:
         z = torch.zeros(B, 0, 3, dtype=k.xpos.dtype, device=k.xpos.device)
         return Contacts(z, z, z[..., 0], [], [], m.t([]))
     return Contacts(torch.stack(pts, 1), torch.stack(nrm, 1), torch.stack(dep, 1), b1, b2, m.t(mu))
+
+
+def _support_points(m, g, c, R):
+    """The shape as spheres for point-wise tests (terrain): (centres [B, 3], radius) per sphere, capsule end, box corner or
+    mesh vertex."""
+    if g.type == "sphere":
+        return [(c, g.size[0])]
+    if g.type == "capsule":
+        ax = R[:, :, 2] * g.size[1]
+        return [(c - ax, g.size[0]), (c + ax, g.size[0])]
+    if g.type == "box":
+        h = m.t(g.size)
+        return [(c + R @ (h * m.t([sx, sy, sz])), 0.0) for sx in (-1, 1) for sy in (-1, 1) for sz in (-1, 1)]
+    return [(c + R @ m.t(v), g.size[0]) for v in g.vertices]
+
+
+def _core(m, g, c, R):
+    """(vertices [B, n, 3] of the convex core, inflation radius) of a geom for the GJK / EPA pair test."""
+    pts = _support_points(m, g, c, R)
+    return torch.stack([p for p, _ in pts], 1), float(pts[0][1])
+
+
+def _geom_aabbs(m, k):
+    lo, hi = [], []
+    for gi in range(len(m.geoms)):
+        _, g, c, R = _geom_frame(m, k, gi)
+        v, r = _core(m, g, c, R)
+        lo.append(v.amin(1) - r - m.opt.margin), hi.append(v.amax(1) + r + m.opt.margin)
+    return torch.stack(lo, 1), torch.stack(hi, 1)
+
+
+_MANIFOLD_SLOTS = 5
+
+
+def _convex_pair(m, k, gi, gj):
+    """Contacts of a pair that involves a convex mesh: GJK / EPA on the host, lane by lane, into a fixed number of slots
+    (unused slots carry depth −1)."""
+    from .narrowphase import contact_manifold
+    _, ga, ca, Ra = _geom_frame(m, k, gi)
+    _, gb, cb, Rb = _geom_frame(m, k, gj)
+    va, ra = _core(m, ga, ca, Ra)
+    vb, rb = _core(m, gb, cb, Rb)
+    B = va.shape[0]
+    P = torch.zeros(B, _MANIFOLD_SLOTS, 3, dtype=va.dtype)
+    Nn = torch.zeros(B, _MANIFOLD_SLOTS, 3, dtype=va.dtype)
+    Nn[:, :, 2] = 1.0
+    D = -torch.ones(B, _MANIFOLD_SLOTS, dtype=va.dtype)
+    va_n, vb_n, cb_n = va.detach().cpu().numpy(), vb.detach().cpu().numpy(), cb.detach().cpu().numpy()
+    for e in range(B):
+        for s_, (p, n, d) in enumerate(contact_manifold(va_n[e], vb_n[e], ra, rb, cb_n[e], margin=m.opt.margin)[:_MANIFOLD_SLOTS]):
+            P[e, s_], Nn[e, s_], D[e, s_] = torch.as_tensor(p), torch.as_tensor(n), float(d)
+    dev = va.device
+    return [(P[:, s_].to(dev), Nn[:, s_].to(dev), D[:, s_].to(dev)) for s_ in range(_MANIFOLD_SLOTS)]
 
 
 def _sphere_box(c_s, radius, c_b, R_b, h):

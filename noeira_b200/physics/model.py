@@ -98,6 +98,7 @@ class Geom:
     density: float = 1000.0
     rgba: Sequence[float] = (0.7, 0.7, 0.7, 1.0)
     contact: bool = True
+    vertices: Optional[Sequence[Sequence[float]]] = None  # type "mesh": points whose convex hull is the shape; size = (margin,)
 
 
 @dataclass
