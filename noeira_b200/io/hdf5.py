@@ -36,6 +36,15 @@ def _pad8(n: int) -> int:
 
 
 # ------------------------------------------------------------------------------------------ datatypes
+VLEN_STR = np.dtype([("len", "<u4"), ("addr", "<u8"), ("idx", "<u4")])      # the 16-byte element of a variable-length string
+
+
+def _vlen_type_message(utf8: bool = True) -> bytes:
+    """Class 9 (variable length), type string, null-terminated, UTF-8 or ASCII; base type: one-byte string."""
+    base = struct.pack("<BBBBI", 0x10 | 3, 0x10 if utf8 else 0, 0, 0, 1)
+    return struct.pack("<BBBBI", 0x10 | 9, 0x01, 0x01 if utf8 else 0, 0, 16) + base
+
+
 def _decode_dtype(b: bytes) -> Tuple[np.dtype, int]:
     cls, ver = b[0] & 0x0F, b[0] >> 4
     bits0 = b[1]
@@ -47,6 +56,8 @@ def _decode_dtype(b: bytes) -> Tuple[np.dtype, int]:
         return np.dtype(f"{order}f{size}"), size
     if cls == 3:
         return np.dtype(f"S{size}"), size
+    if cls == 9 and (bits0 & 0x0F) == 1:                       # variable-length string: (length, global-heap address, index)
+        return VLEN_STR, 16
     raise H5Error(f"datatype class {cls} (version {ver}) is not supported")
 
 
@@ -94,6 +105,28 @@ class _Reader:
         return out
 
     # ---- groups
+    def global_heap_object(self, addr: int, idx: int) -> bytes:
+        """Object ``idx`` of the global heap collection at ``addr`` ("GCOL")."""
+        if bytes(self.d[addr: addr + 4]) != b"GCOL":
+            raise H5Error("bad global heap signature")
+        size = struct.unpack_from("<Q", self.d, addr + 8)[0]
+        p, end = addr + 16, addr + size
+        while p + 16 <= end:
+            oid, _ref, _res, osize = struct.unpack_from("<HHIQ", self.d, p)
+            if oid == idx:
+                return bytes(self.d[p + 16: p + 16 + osize])
+            if oid == 0:
+                break
+            p += 16 + _pad8(osize)
+        raise H5Error(f"global heap object {idx} not found")
+
+    def vlen_strings(self, a: np.ndarray) -> np.ndarray:
+        out = np.empty(a.shape, dtype=object)
+        for i, e in enumerate(a.reshape(-1)):
+            out.reshape(-1)[i] = self.global_heap_object(int(e["addr"]), int(e["idx"]))[: int(e["len"])].decode("utf-8", "replace") \
+                if int(e["addr"]) not in (0, UNDEF) else ""
+        return out
+
     def heap_name(self, heap_addr: int, off: int) -> str:
         if self.d[heap_addr: heap_addr + 4] != b"HEAP":
             raise H5Error("bad local heap")
@@ -145,7 +178,7 @@ class _Reader:
 class H5Dataset:
     def __init__(self, rd: _Reader, name: str, msgs):
         self._rd, self.name = rd, name
-        self.attrs = _attrs(msgs)
+        self.attrs = _attrs(msgs, rd)
         self.filters: List[Tuple[int, Tuple[int, ...]]] = []
         self.shape: Tuple[int, ...] = ()
         self.dtype = None
@@ -166,7 +199,12 @@ class H5Dataset:
         return self.shape[0]
 
     def read(self, start: int = 0, stop: Optional[int] = None) -> np.ndarray:
-        """The whole array, or rows ``[start, stop)`` of the first axis."""
+        """The whole array, or rows ``[start, stop)`` of the first axis.  Variable-length strings come back as an object
+        array of ``str``."""
+        a = self._read_raw(start, stop)
+        return self._rd.vlen_strings(np.asarray(a)) if self.dtype == VLEN_STR else a
+
+    def _read_raw(self, start: int = 0, stop: Optional[int] = None) -> np.ndarray:
         rd, b = self._rd, self._layout
         ver, cls = b[0], b[1]
         if ver != 3:
@@ -265,7 +303,7 @@ def _decode_filters(b: bytes):
     return out
 
 
-def _attrs(msgs) -> Dict[str, object]:
+def _attrs(msgs, rd: "_Reader" = None) -> Dict[str, object]:
     out = {}
     for t, b in msgs:
         if t != MSG_ATTR or b[0] != 1:
@@ -282,6 +320,11 @@ def _attrs(msgs) -> Dict[str, object]:
         p += _pad8(slen)
         n = int(np.prod(shape)) if shape else 1
         v = np.frombuffer(b, dt, n, p).reshape(shape)
+        if dt == VLEN_STR:
+            if rd is not None:
+                sv = rd.vlen_strings(v)
+                out[name] = sv.item() if not shape else sv
+            continue
         out[name] = (v.item() if not shape else v.copy()) if dt.kind != "S" else (v.item().rstrip(b"\0").decode() if not shape else v.copy())
     return out
 
@@ -290,7 +333,7 @@ class H5Group:
     def __init__(self, rd: _Reader, name: str, addr: int):
         self._rd, self.name, self._addr = rd, name, addr
         msgs = rd.messages(addr)
-        self.attrs = _attrs(msgs)
+        self.attrs = _attrs(msgs, rd)
         self._links: Dict[str, int] = {}
         for t, b in msgs:
             if t == MSG_SYMTAB:
@@ -385,24 +428,53 @@ class _Writer:
         body = b"".join(msgs)
         return self.alloc(struct.pack("<BBHII", 1, 0, len(msgs), 1, len(body)) + b"\0" * 4 + body)
 
-    @staticmethod
-    def attr_msgs(attrs) -> List[bytes]:
+    def attr_msgs(self, attrs) -> List[bytes]:
         out = []
         for k, v in (attrs or {}).items():
             a = np.asarray(v.encode() if isinstance(v, str) else v)
+            vlen = a.dtype.kind == "O"                          # an object array of text: variable-length strings
+            if vlen:
+                a = self.vlen_elements(a)
             if a.dtype.kind == "U":
                 a = a.astype("S")
             if a.dtype == np.bool_:
                 a = a.astype(np.uint8)
             name = k.encode() + b"\0"
-            dt = _encode_dtype(a.dtype)
+            dt = _vlen_type_message() if vlen else _encode_dtype(a.dtype)
             sp = _encode_space(a.shape)
             body = struct.pack("<BBHHH", 1, 0, len(name), len(dt), len(sp)) + name + b"\0" * (_pad8(len(name)) - len(name)) + \
                 dt + b"\0" * (_pad8(len(dt)) - len(dt)) + sp + b"\0" * (_pad8(len(sp)) - len(sp)) + a.tobytes()
-            out.append(_Writer.msg(MSG_ATTR, body))
+            out.append(self.msg(MSG_ATTR, body))
         return out
 
+    def global_heap(self, items: List[bytes]) -> List[Tuple[int, int, int]]:
+        """One global heap collection holding ``items`` → (length, collection address, object index) per item.  The
+        collection is at least 4096 bytes; the rest is the free-space object 0."""
+        body = bytearray()
+        for i, it in enumerate(items):
+            body += struct.pack("<HHIQ", i + 1, 1, 0, len(it)) + it + b"\0" * (_pad8(len(it)) - len(it))
+        total = max(4096, _pad8(16 + len(body) + 16))
+        free = total - 16 - len(body)
+        blob = b"GCOL" + struct.pack("<B3xQ", 1, total) + bytes(body) + struct.pack("<HHIQ", 0, 0, 0, free) + b"\0" * (free - 16)
+        addr = self.alloc(blob)
+        return [(len(it), addr, i + 1) for i, it in enumerate(items)]
+
+    def vlen_elements(self, a: np.ndarray) -> np.ndarray:
+        items = [(x if isinstance(x, bytes) else str(x).encode("utf-8")) for x in a.reshape(-1)]
+        el = np.zeros(len(items), VLEN_STR)
+        if items:
+            for i, (ln, addr, idx) in enumerate(self.global_heap(items)):
+                el[i] = (ln, addr, idx)
+        return el.reshape(a.shape)
+
     def dataset(self, a: np.ndarray, compression, chunk_rows, attrs) -> int:
+        a = np.asarray(a)
+        if a.dtype.kind in "UO":                                # text of any length: variable-length strings
+            el = self.vlen_elements(a)
+            msgs = [self.msg(MSG_DATASPACE, _encode_space(a.shape)), self.msg(MSG_DATATYPE, _vlen_type_message(), flags=1),
+                    self.msg(MSG_FILL, struct.pack("<BBBB", 2, 2, 0, 0)),
+                    self.msg(MSG_LAYOUT, struct.pack("<BBQQ", 3, 1, self.alloc(el.tobytes()) if el.size else UNDEF, el.nbytes))]
+            return self.header(msgs + self.attr_msgs(attrs))
         a = np.ascontiguousarray(a)
         if a.dtype == np.bool_:
             a = a.astype(np.uint8)

@@ -131,3 +131,27 @@ def test_aloha_episode_files_feed_the_act_dataset(tmp_path):
     ds = ACTDataset(back, chunk=8)
     q, img, act, valid = ds.sample(5)
     assert img.shape == (5, 2, 3, 12, 16) and act.shape == (5, 8, 6) and valid.shape == (5, 10)
+
+
+def test_variable_length_strings_round_trip(tmp_path):
+    import struct
+    from noeira_b200.io.hdf5 import H5File, write_hdf5
+    words = np.array(["pick up the red block", "", "naïve café ☕", "x" * 3000], dtype=object)
+    grid = np.array([["a", "bb"], ["ccc", "dddd"]], dtype=object)
+    path = str(tmp_path / "text.h5")
+    write_hdf5(path, {"task": {"instruction": words, "grid": grid, "fixed": np.array([b"ab", b"cd"])}, "n": np.arange(3)},
+               attrs={"task/instruction": {"langs": np.array(["en", "français"], dtype=object), "kind": "text"}})
+    with H5File(path) as f:
+        ds = f["task/instruction"]
+        got = ds.read()
+        assert got.dtype == object and list(got) == list(words)
+        assert list(ds.read(1, 3)) == list(words[1:3]) and ds[2] == words[2]
+        assert f["task/grid"].read().tolist() == grid.tolist()
+        assert list(ds.attrs["langs"]) == ["en", "français"] and ds.attrs["kind"] == "text"
+        assert f["task/fixed"].read().tolist() == [b"ab", b"cd"] and f["n"].read().tolist() == [0, 1, 2]
+    raw = open(path, "rb").read()
+    at = raw.index(b"GCOL")
+    ver, size = struct.unpack_from("<B3xQ", raw, at + 4)
+    assert ver == 1 and size >= 4096 and size % 8 == 0 and at % 8 == 0
+    oid, ref, _, osize = struct.unpack_from("<HHIQ", raw, at + 16)
+    assert (oid, ref, osize) == (1, 1, len(words[0])) and raw[at + 32: at + 32 + osize] == words[0].encode()
