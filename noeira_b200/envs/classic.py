@@ -33,6 +33,31 @@ class _TensorEnv(BatchedEnv):
         self.ep_stats = torch.zeros(4, **z)        # Σ finished returns, finished episodes, Σ rewards, steps
         self.state = None
 
+    # ---- the engine-style surface the on-policy trainers drive (PPO steps ``env.engine`` into its own rollout buffers)
+    @property
+    def engine(self):
+        return self
+
+    @property
+    def obs_pad(self) -> int:
+        return (self.obs_dim + 63) // 64 * 64
+
+    @property
+    def obs_bf16(self) -> torch.Tensor:
+        buf = torch.zeros(self.n_envs, self.obs_pad, device=self.device, dtype=torch.bfloat16)
+        buf[:, : self.obs_dim].copy_(self.obs)
+        return buf
+
+    def step(self, action, reward, done, terminated, obs_f32=None, obs_bf16=None, next_obs_f32=None, next_obs_bf16=None,
+             finished_return=None, do_reset=True, ep_stats=None, dbg=None):
+        self.step_batch(action, auto_reset=do_reset)
+        reward.copy_(self.reward), done.copy_(self.done), terminated.copy_(self.terminated)
+        for dst, src in ((obs_f32, self.obs), (obs_bf16, self.obs), (next_obs_f32, self.next_obs), (next_obs_bf16, self.next_obs)):
+            if dst is not None and dst is not src:
+                dst[:, : self.obs_dim].copy_(src)
+        if finished_return is not None and finished_return is not self.finished_return:
+            finished_return.copy_(self.finished_return)
+
     def _rand(self, *shape):
         return torch.rand(*shape, device=self.device, generator=self.gen)
 
@@ -67,12 +92,13 @@ class _TensorEnv(BatchedEnv):
         self.pre_reset_state = s2
         self.ep_stats[2] += r.sum()
         self.ep_stats[3] += self.n_envs
-        if auto_reset and bool(done.any()):
+        if auto_reset:                                       # masked, without a host read: the step can sit in a captured stream
+            fin = done.to(r.dtype)
             self.finished_return.copy_(torch.where(done, self.ep_return, self.finished_return))
-            self.ep_stats[0] += self.ep_return[done].sum()
-            self.ep_stats[1] += done.sum()
+            self.ep_stats[0] += (self.ep_return * fin).sum()
+            self.ep_stats[1] += fin.sum()
             fresh = self._sample_state(self.n_envs)
-            s2 = torch.where(done[:, None], fresh, s2)
+            s2 = torch.where(done.reshape(-1, *([1] * (s2.dim() - 1))), fresh, s2)
             self.steps.masked_fill_(done, 0)
             self.ep_return.masked_fill_(done, 0.0)
         self.state = s2

@@ -53,3 +53,16 @@ def test_full_environment_loop_with_resets_and_pixels():
         obs, r, d, tm = env.step_batch(torch.full((32,), 3, device="cuda"))
         total += r
     assert obs.shape == (32, 4, 64, 64) and torch.isfinite(total).all() and float(total.max()) > 0
+
+
+def test_ppo_drives_the_tensor_environment_through_its_engine_surface():
+    """PPO steps ``env.engine`` into its rollout buffers; tensor-program environments offer that surface too."""
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs.car_racing import CarRacingEnv
+    env = CarRacingEnv(256, device="cuda", seed=0, lookahead=6)
+    cfg = PPOConfig(n_envs=256, rollout_len=16, n_epochs=2, n_minibatches=4, use_cuda_graphs=False, seed=0)
+    tr = PPOTrainer(env, cfg)
+    for _ in range(3):
+        m = tr.train_iteration()
+    assert all(torch.isfinite(torch.as_tensor(float(v))) for v in m.values() if isinstance(v, (int, float)))
+    assert float(env.state[:, 13].max()) >= 1                                # cars moved over at least a tile
