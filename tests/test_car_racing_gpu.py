@@ -64,5 +64,5 @@ def test_ppo_drives_the_tensor_environment_through_its_engine_surface():
     tr = PPOTrainer(env, cfg)
     for _ in range(3):
         m = tr.train_iteration()
-    assert all(torch.isfinite(torch.as_tensor(float(v))) for v in m.values() if isinstance(v, (int, float)))
+    assert all(torch.isfinite(torch.as_tensor(float(m[k]))) for k in ("policy_loss", "value_loss", "entropy", "mean_step_reward"))
     assert float(env.state[:, 13].max()) >= 1                                # cars moved over at least a tile
