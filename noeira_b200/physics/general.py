@@ -772,12 +772,34 @@ def constraint_rows(m: GeneralModel, k: Kin, qpos, qvel, con: Contacts) -> Rows:
     return Rows(J, aref, dimp, active, kind, par, m.t(mu), body)
 
 
+def _disc_qp(Q, c, radius, newton_iters: int = 12):
+    """argmin ½ xᵀQx + cᵀx over ‖x‖ ≤ radius for batched symmetric positive 2 × 2 ``Q``: the unconstrained minimiser when it
+    lies inside, else (Q + λI)⁻¹(−c) with λ > 0 from Newton's iteration on the secular equation ‖x(λ)‖ = radius."""
+    w, V = torch.linalg.eigh(Q)                                                    # [B, 2], [B, 2, 2]
+    g = -(V.transpose(1, 2) @ c[:, :, None])[..., 0]                              # −c in the eigenbasis
+    w = w.clamp(min=1e-12)
+    y0 = g / w
+    inside = y0.norm(dim=1) <= radius
+    lam = torch.zeros_like(radius)
+    r = radius.clamp(min=1e-30)
+    for _ in range(newton_iters):
+        den = w + lam[:, None]
+        nrm = (g / den).norm(dim=1).clamp(min=1e-30)
+        # φ(λ) = 1/‖x‖ − 1/r is nearly linear in λ: Newton on it converges from λ = 0 without safeguards
+        dn = -((g * g) / den ** 3).sum(1) / nrm
+        lam = (lam - (1 / nrm - 1 / r) / (-dn / nrm ** 2)).clamp(min=0)
+    y = torch.where(inside[:, None], y0, g / (w + lam[:, None]))
+    y = torch.where((radius <= 0)[:, None], torch.zeros_like(y), y)
+    return (V @ y[:, :, None])[..., 0]
+
+
 def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters=50, cone: str = "pyramidal", noslip_iters: int = 0):
     """Forces ``f [B, nr]`` of the soft-constraint problem (A + R) f + J q̈₀ − a_ref = 0 with f ≥ 0 on unilateral rows and
     |f| ≤ μ f_normal on friction rows.  Returns (f, q̈).
 
     ``cone="elliptic"`` (PGS only) bounds the NORM of the two tangential forces of a contact by μ f_normal (a circular cone)
-    instead of each of them (the box that circumscribes it): the pair is updated as a block and scaled back onto the disc.
+    instead of each of them (the box that circumscribes it): the pair is updated as a block, the exact minimiser of the
+    two-variable quadratic over the disc (``_disc_qp``).
     ``noslip_iters`` more PGS sweeps over the friction rows alone, with their regularisation R removed, take out the slow
     creep that the soft friction rows allow under a sustained tangential load."""
     B, nr = rows.aref.shape
@@ -804,22 +826,33 @@ def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters
 
     if solver == "pgs":
         dA = torch.diagonal(A, dim1=1, dim2=2)
+        pair_first = {i for i in range(nr - 1) if kind[i] == 1 and kind[i + 1] == 1 and par[i] == par[i + 1]
+                      and (i == 0 or not (kind[i - 1] == 1 and par[i - 1] == par[i]))}
         for _ in range(iters):
+            skip = -1
             for i in range(nr):
+                if i == skip:
+                    continue
+                if cone == "elliptic" and i in pair_first:
+                    # the two tangential forces of a contact as one block: the quadratic restricted to them, minimised
+                    # over the disc of radius μ f_normal (a two-variable QCQP, solved in the block's eigenbasis)
+                    j = i + 1
+                    idx = [i, j]
+                    Att = A[:, idx][:, :, idx]                                           # [B, 2, 2]
+                    c = (A[:, idx] * f[:, None, :]).sum(-1) + b[:, idx] - (Att @ f[:, idx, None])[..., 0]
+                    f = f.clone()
+                    f[:, idx] = _disc_qp(Att, c, mu[i] * f[:, par[i]].clamp(min=0))
+                    skip = j
+                    continue
                 res = (A[:, i] * f).sum(-1) + b[:, i]
                 fi = f[:, i] - res / dA[:, i]
                 if kind[i] == 0:
                     fi = fi.clamp(min=0)
-                elif cone != "elliptic":
+                else:
                     lim = mu[i] * f[:, par[i]].clamp(min=0)
                     fi = torch.maximum(torch.minimum(fi, lim), -lim)
                 f = f.clone()
                 f[:, i] = fi
-                if kind[i] == 1 and cone == "elliptic" and i > 0 and kind[i - 1] == 1 and par[i - 1] == par[i]:
-                    lim = mu[i] * f[:, par[i]].clamp(min=0)
-                    nrm = (f[:, i - 1] ** 2 + f[:, i] ** 2).sqrt()
-                    sc = torch.where(nrm > lim, lim / nrm.clamp(min=1e-30), torch.ones_like(nrm))
-                    f[:, i - 1], f[:, i] = f[:, i - 1] * sc, f[:, i] * sc
     elif solver == "newton":
         eye = torch.eye(nr, dtype=A.dtype, device=A.device)[None]
         for _ in range(iters):
