@@ -793,18 +793,58 @@ def _disc_qp(Q, c, radius, newton_iters: int = 12):
     return (V @ y[:, :, None])[..., 0]
 
 
-def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters=50, cone: str = "pyramidal", noslip_iters: int = 0):
+def constraint_islands(M, rows: Rows, eps: float = 1e-12) -> List[List[int]]:
+    """Connected components of the constraint rows: two rows are coupled when J M⁻¹ Jᵀ links them in any lane of the batch
+    (they touch the same kinematic chain).  Friction rows stay with their normal row.  Rows that are inactive in every lane
+    come out as singletons."""
+    nr = rows.aref.shape[1]
+    if nr == 0:
+        return []
+    A = rows.J @ torch.linalg.solve(M, rows.J.transpose(1, 2))
+    act = rows.active.to(A.dtype)
+    link = ((A * act[:, :, None] * act[:, None, :]).abs() > eps).any(0).cpu()
+    root = list(range(nr))
+
+    def find(i):
+        while root[i] != i:
+            root[i] = root[root[i]]
+            i = root[i]
+        return i
+    for i in range(nr):
+        if rows.parent_row[i] >= 0:
+            root[find(i)] = find(rows.parent_row[i])
+        for j in torch.nonzero(link[i]).flatten().tolist():
+            root[find(i)] = find(j)
+    groups: Dict[int, List[int]] = {}
+    for i in range(nr):
+        groups.setdefault(find(i), []).append(i)
+    return sorted(groups.values())
+
+
+def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters=50, cone: str = "pyramidal", noslip_iters: int = 0,
+                      islands: bool = False):
     """Forces ``f [B, nr]`` of the soft-constraint problem (A + R) f + J q̈₀ − a_ref = 0 with f ≥ 0 on unilateral rows and
     |f| ≤ μ f_normal on friction rows.  Returns (f, q̈).
 
     ``cone="elliptic"`` (PGS only) bounds the NORM of the two tangential forces of a contact by μ f_normal (a circular cone)
     instead of each of them (the box that circumscribes it): the pair is updated as a block, the exact minimiser of the
     two-variable quadratic over the disc (``_disc_qp``).
+    ``islands=True`` splits the rows into their connected components first (``constraint_islands``).
     ``noslip_iters`` more PGS sweeps over the friction rows alone, with their regularisation R removed, take out the slow
     creep that the soft friction rows allow under a sustained tangential load."""
     B, nr = rows.aref.shape
     if nr == 0:
         return rows.aref, qacc0
+    if islands:
+        # every island is its own problem (the coupling matrix is block diagonal over them): smaller dense solves for the
+        # Newton method, shorter sweeps for PGS
+        f = torch.zeros_like(rows.aref)
+        for isl in constraint_islands(M, rows):
+            local = {g: l for l, g in enumerate(isl)}
+            sub = Rows(rows.J[:, isl], rows.aref[:, isl], rows.d[:, isl], rows.active[:, isl], [rows.kind[i] for i in isl],
+                       [local.get(rows.parent_row[i], -1) for i in isl], rows.mu[isl], [rows.body[i] for i in isl])
+            f[:, isl] = solve_constraints(m, M, qacc0, sub, solver, iters, cone, noslip_iters)[0]
+        return f, qacc0 + (torch.linalg.solve(M, rows.J.transpose(1, 2)) @ f[:, :, None])[..., 0]
     Minv_Jt = torch.linalg.solve(M, rows.J.transpose(1, 2))                     # [B, nv, nr]
     A = rows.J @ Minv_Jt
     act = rows.active.to(A.dtype)
@@ -928,8 +968,8 @@ def solve_constraints(m: GeneralModel, M, qacc0, rows: Rows, solver="pgs", iters
 # ------------------------------------------------------------------------------------------ stepping
 class GeneralSim:
     def __init__(self, model: GeneralModel, n: int, integrator: str = "euler", solver: str = "newton", solver_iters: int = 20,
-                 cone: str = "pyramidal", noslip_iters: int = 0):
-        self.cone, self.noslip_iters = cone, noslip_iters
+                 cone: str = "pyramidal", noslip_iters: int = 0, islands: bool = False):
+        self.cone, self.noslip_iters, self.islands = cone, noslip_iters, islands
         if cone == "elliptic" and solver != "pgs":
             raise ValueError("the elliptic cone is a projection of the PGS solver")
         self.m, self.n, self.integrator, self.solver, self.solver_iters = model, n, integrator, solver, solver_iters
@@ -959,7 +999,7 @@ class GeneralSim:
         qacc0 = torch.linalg.solve(Mh, tau[:, :, None])[..., 0]
         con = collide(m, k)
         rows = constraint_rows(m, k, qpos, qvel, con)
-        f, qacc = solve_constraints(m, Mh, qacc0, rows, self.solver, self.solver_iters, self.cone, self.noslip_iters)
+        f, qacc = solve_constraints(m, Mh, qacc0, rows, self.solver, self.solver_iters, self.cone, self.noslip_iters, self.islands)
         self.last = dict(kin=k, M=M, qacc=qacc, rows=rows, force=f, contacts=con, qvel=qvel)
         return qacc
 

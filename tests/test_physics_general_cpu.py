@@ -445,3 +445,32 @@ def test_elliptic_cone_is_isotropic_and_noslip_removes_creep():
             sim.step()
         drift[ns] = abs(float(sim.qpos[0, 0]))
     assert drift[10] < 0.2 * drift[0] and drift[10] < 1e-3, drift
+
+
+def test_constraint_islands_split_independent_bodies_and_give_the_same_forces():
+    opt = Options(timestep=0.002, solref=(0.01, 1.0))
+    bodies = [Body(-1, (0, 0, 0.049), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("box", (0.2, 0.1, 0.05))]),
+              Body(-1, (3.0, 0, 0.099), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("sphere", (0.1,))]),
+              Body(-1, (3.0, 0, 0.29), joints=[Joint(G.FREE, (0, 0, 1))], geoms=[Geom("sphere", (0.1,))])]      # stacked on the second
+    m = G.GeneralModel(bodies, opt=opt, plane=True)
+    qpos, qvel = m.init_state(2)
+    qvel[1, 0] = 0.5
+    k = G.kinematics(m, qpos, qvel)
+    con = G.collide(m, k)
+    rows = G.constraint_rows(m, k, qpos, qvel, con)
+    M = G.mass_matrix(m, k)
+    isl = G.constraint_islands(M, rows)
+    active = [i for i in range(rows.aref.shape[1]) if bool(rows.active[:, i].any())]
+    big = [g for g in isl if len(g) > 1 and any(i in active for i in g)]
+    bodies_of = [{rows.body[i] for i in g if i in active} for g in big]
+    assert any(b == {0} for b in bodies_of) and any({1, 2} <= b for b in bodies_of)      # the box alone; the two balls together
+    assert not any(0 in b and (1 in b or 2 in b) for b in bodies_of)
+    qacc0 = torch.linalg.solve(M, (-G.bias_force(m, k, qvel))[:, :, None])[..., 0]
+    for solver, iters in (("newton", 30), ("pgs", 200)):
+        f1, a1 = G.solve_constraints(m, M, qacc0, rows, solver, iters)
+        f2, a2 = G.solve_constraints(m, M, qacc0, rows, solver, iters, islands=True)
+        assert (f1 - f2).abs().max() < 1e-6 * max(1.0, float(f1.abs().max())) and (a1 - a2).abs().max() < 1e-6
+    sim = G.GeneralSim(m, 1, solver="newton", solver_iters=20, islands=True)
+    for _ in range(100):
+        sim.step()
+    assert abs(float(sim.qpos[0, 2]) - 0.05) < 2e-3 and abs(float(sim.qpos[0, 14 + 2]) - 0.3) < 6e-3
