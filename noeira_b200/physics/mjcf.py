@@ -118,6 +118,24 @@ def from_mjcf(source: str, opt: Optional[Options] = None, general: bool = False)
     if wb is None:
         raise MjcfError("no <worldbody>")
     bodies: List[Body] = []
+    has_plane = False
+    # assets with their data inline: <mesh name vertex="x y z …" scale="…"/> (the convex hull of the points is the shape) and
+    # <hfield name nrow ncol size="rx ry top base" elevation="…"/> (values in [0, 1] scaled by ``top``); file references raise
+    meshes, hfields = {}, {}
+    for asset in root.findall("asset"):
+        for e in asset:
+            if e.tag == "mesh":
+                if "vertex" not in e.attrib:
+                    raise MjcfError(f"mesh {e.get('name')!r}: only inline vertex=\"…\" data is supported, not files")
+                v = np.array(_floats(e.get("vertex"))).reshape(-1, 3) * np.array(_floats(e.get("scale", "1 1 1"), 3))
+                meshes[e.get("name")] = [tuple(float(x) for x in r) for r in v]
+            elif e.tag == "hfield":
+                if "elevation" not in e.attrib:
+                    raise MjcfError(f"hfield {e.get('name')!r}: only inline elevation=\"…\" data is supported, not files")
+                nrow, ncol = int(e.get("nrow")), int(e.get("ncol"))
+                rx, ry, top, _base = _floats(e.get("size"), 4)
+                hfields[e.get("name")] = (np.array(_floats(e.get("elevation"), nrow * ncol)).reshape(nrow, ncol) * top, rx, ry)
+    hfield = None
 
     def ang(x):
         return np.deg2rad(x) if degrees else x
@@ -144,7 +162,14 @@ def from_mjcf(source: str, opt: Optional[Options] = None, general: bool = False)
         if typ == "box" and general:
             return Geom("box", tuple(size[:3]), tuple(_floats(a.get("pos", "0 0 0"), 3)), tuple(_quat_of(a, degrees)), fr, dens, rgba,
                         contact)
-        raise MjcfError(f"geom type {typ!r} is not supported (capsule, sphere; box in the general engine; plane at world level)")
+        if typ == "mesh" and general:
+            name = a.get("mesh")
+            if name not in meshes:
+                raise MjcfError(f"geom refers to mesh {name!r}, which <asset> does not define with inline vertices")
+            return Geom("mesh", (float(a.get("margin", "0")),), tuple(_floats(a.get("pos", "0 0 0"), 3)), tuple(_quat_of(a, degrees)),
+                        fr, dens, rgba, contact, vertices=meshes[name])
+        raise MjcfError(f"geom type {typ!r} is not supported (capsule, sphere; box and mesh in the general engine; plane and "
+                        "hfield at world level)")
 
     def parse_body(elem, parent, childclass):
         cc = elem.get("childclass", childclass)
@@ -197,10 +222,18 @@ def from_mjcf(source: str, opt: Optional[Options] = None, general: bool = False)
             parse_body(ch, -1, None)
         elif ch.tag == "geom":
             a = defaults.resolve("geom", ch, None)
+            if a.get("type", "sphere") == "hfield" and general:
+                from .narrowphase import HeightField
+                if a.get("hfield") not in hfields:
+                    raise MjcfError(f"geom refers to hfield {a.get('hfield')!r}, which <asset> does not define inline")
+                data, rx, ry = hfields[a["hfield"]]
+                hfield = HeightField(data, rx, ry, tuple(_floats(a.get("pos", "0 0 0"), 3)), _floats(a.get("friction", "1"))[0])
+                continue
             if a.get("type", "sphere") != "plane":
-                raise MjcfError("world-level geoms other than the ground plane are not supported")
+                raise MjcfError("world-level geoms other than the ground plane (and a height field in the general engine) are not supported")
             p = _floats(a.get("pos", "0 0 0"), 3)
             o.plane_offset = p[2]
+            has_plane = True
         elif ch.tag not in ("light", "camera", "site"):
             raise MjcfError(f"<{ch.tag}> in <worldbody> is not supported")
     if not bodies:
@@ -214,5 +247,6 @@ def from_mjcf(source: str, opt: Optional[Options] = None, general: bool = False)
             acts.append(Actuator(a["joint"], _floats(a.get("gear", "1"))[0], tuple(_floats(a.get("ctrlrange", "-1 1"), 2))))
     if general:
         from .general import GeneralModel, Motor
-        return GeneralModel(bodies, [Motor(a.joint, a.gear, tuple(a.ctrlrange)) for a in acts], o)
+        return GeneralModel(bodies, [Motor(a.joint, a.gear, tuple(a.ctrlrange)) for a in acts], o, hfield=hfield,
+                            plane=has_plane or hfield is None)
     return RigidModel(bodies, acts, o)

@@ -69,3 +69,34 @@ def test_mjcf_model_matches_hand_built(tmp_path):
                    [Actuator("knee", 5.0)], Options())
     (ia, fa), (ib, fb) = a.pack(), b.pack()
     assert (ia == ib).all() and np.allclose(fa, fb, atol=1e-7)
+
+
+def test_inline_mesh_and_height_field_assets_in_the_general_engine():
+    import torch
+    from noeira_b200.physics import general as G
+    from noeira_b200.physics.mjcf import MjcfError, from_mjcf
+    xml = """<mujoco><option timestep="0.002"/>
+      <asset>
+        <mesh name="wedge" vertex="0 0 0  0.2 0 0  0 0.2 0  0.2 0.2 0  0 0 0.1  0 0.2 0.1" scale="1 1 2"/>
+        <hfield name="ramp" nrow="2" ncol="3" size="2 1 0.4 0.1" elevation="0 0.5 1  0 0.5 1"/>
+      </asset>
+      <worldbody>
+        <geom type="hfield" hfield="ramp" friction="0.9"/>
+        <body name="rock" pos="0 0 1"><freejoint/><geom type="mesh" mesh="wedge" density="500"/></body>
+        <body name="ball" pos="-1 0 0.5"><freejoint/><geom type="sphere" size="0.1"/></body>
+      </worldbody></mujoco>"""
+    m = from_mjcf(xml, general=True)
+    g = m.geoms[0][1]
+    assert g.type == "mesh" and len(g.vertices) == 6 and max(v[2] for v in g.vertices) == 0.2        # scaled
+    assert abs(float(m.mass[0]) - 500 * 0.5 * 0.2 * 0.2 * 0.2) < 1e-9                                  # a triangular prism
+    assert m.hfield is not None and not m.plane and m.hfield.friction == 0.9
+    h, n = m.hfield.sample(torch.tensor([-2.0, 0.0, 2.0], dtype=torch.float64), torch.zeros(3, dtype=torch.float64))
+    assert torch.allclose(h, torch.tensor([0.0, 0.2, 0.4], dtype=torch.float64))
+    sim = G.GeneralSim(m, 1, solver="newton", solver_iters=20)
+    for _ in range(200):
+        sim.step()
+    hb, _ = m.hfield.sample(sim.qpos[:, 7], sim.qpos[:, 8])
+    assert 0.09 < float(sim.qpos[0, 9] - hb) < 0.12                                                    # the ball sits on the ramp
+    assert float(sim.qpos[0, 7]) < -1.0                                                                # and rolled downhill
+    with pytest.raises(MjcfError):
+        from_mjcf(xml.replace('vertex="0 0 0  0.2 0 0  0 0.2 0  0.2 0.2 0  0 0 0.1  0 0.2 0.1"', 'file="wedge.stl"'), general=True)
