@@ -24,20 +24,19 @@ __device__ __forceinline__ float seg_dist2(float qx, float qy, float ax, float a
   return dx * dx + dy * dy;
 }
 
-// state [N, CAR_HDR + T] -> next [N, CAR_HDR + T]; action [N, lda] (steer, gas, brake); track [K, T, 2]
-__global__ void car_step_kernel(const float* __restrict__ state, const float* __restrict__ action, int lda,
-                                const float* __restrict__ track, int T, float* __restrict__ next, float* __restrict__ reward,
-                                float* __restrict__ term, int N, CarParams P) {
-  const int env = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (env >= N) return;
-  const int S = CAR_HDR + T;
-  const float* s = state + (size_t)env * S;
-  float* o = next + (size_t)env * S;
+struct CarStepOut {      // valid in lane 0
+  float hdr[CAR_HDR];
+  float reward;
+  int term;
+};
+
+// One warp advances one lane of the batch: the lanes share the tiles (surface under each wheel, visit flags written to
+// ``o_flags``), lane 0 integrates the tire model and the hull.  ``s`` is the state row, ``a`` its action (steer, gas, brake).
+__device__ __forceinline__ void car_step_warp(const float* __restrict__ s, const float* __restrict__ a, const float* __restrict__ tr,
+                                              int T, float* __restrict__ o_flags, const CarParams& P, int lane, CarStepOut& R) {
   const float x = s[0], y = s[1], ang = s[2], vx = s[3], vy = s[4], om = s[5];
   float joint[4] = {s[6], s[7], 0.f, 0.f}, womega[4] = {s[8], s[9], s[10], s[11]};
-  const int trk = (int)s[12];
   float gas_state = s[14];
-  const float* tr = track + (size_t)trk * T * 2;
   const float ca = cosf(ang), sa = sinf(ang);
   float wx[4], wy[4], rx[4], ry[4];
 #pragma unroll
@@ -63,7 +62,7 @@ __global__ void car_step_kernel(const float* __restrict__ state, const float* __
     }
     const float was = s[CAR_HDR + j];
     if (hit && was == 0.f) ++fresh;
-    o[CAR_HDR + j] = (hit || was != 0.f) ? 1.f : 0.f;
+    o_flags[j] = (hit || was != 0.f) ? 1.f : 0.f;
   }
 #pragma unroll
   for (int sft = 16; sft; sft >>= 1) {
@@ -72,7 +71,6 @@ __global__ void car_step_kernel(const float* __restrict__ state, const float* __
     for (int w = 0; w < 4; ++w) dmin[w] = fminf(dmin[w], __shfl_xor_sync(0xffffffffu, dmin[w], sft));
   }
   if (lane) return;
-  const float* a = action + (size_t)env * lda;
   const float steer = fminf(fmaxf(a[0], -1.f), 1.f), gas = fminf(fmaxf(a[1], 0.f), 1.f), brake = fminf(fmaxf(a[2], 0.f), 1.f);
   gas_state += fminf(gas - gas_state, 0.1f);
   float fx = 0.f, fy = 0.f, tq = 0.f;
@@ -108,12 +106,141 @@ __global__ void car_step_kernel(const float* __restrict__ state, const float* __
   const float visited = s[13] + (float)fresh;
   const bool out = fabsf(x2) > P.playfield || fabsf(y2) > P.playfield;
   const bool lap = visited >= P.lap_fraction * (float)T;
+  float* o = R.hdr;
   o[0] = x2; o[1] = y2; o[2] = ang + P.dt * om2; o[3] = vx2; o[4] = vy2; o[5] = om2;
   o[6] = joint[0]; o[7] = joint[1];
   o[8] = womega[0]; o[9] = womega[1]; o[10] = womega[2]; o[11] = womega[3];
   o[12] = s[12]; o[13] = visited; o[14] = gas_state; o[15] = s[15];
-  reward[env] = out ? -100.f : -0.1f + P.tile_reward * (float)fresh;
-  term[env] = (out || lap) ? 1.f : 0.f;
+  R.reward = out ? -100.f : -0.1f + P.tile_reward * (float)fresh;
+  R.term = (out || lap) ? 1 : 0;
+}
+
+// state [N, CAR_HDR + T] -> next [N, CAR_HDR + T]; action [N, lda] (steer, gas, brake); track [K, T, 2]
+__global__ void car_step_kernel(const float* __restrict__ state, const float* __restrict__ action, int lda,
+                                const float* __restrict__ track, int T, float* __restrict__ next, float* __restrict__ reward,
+                                float* __restrict__ term, int N, CarParams P) {
+  const int env = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (env >= N) return;
+  const int S = CAR_HDR + T;
+  const float* s = state + (size_t)env * S;
+  float* o = next + (size_t)env * S;
+  CarStepOut R;
+  car_step_warp(s, action + (size_t)env * lda, track + (size_t)((int)s[12]) * T * 2, T, o + CAR_HDR, P, lane, R);
+  if (lane) return;
+#pragma unroll
+  for (int i = 0; i < CAR_HDR; ++i) o[i] = R.hdr[i];
+  reward[env] = R.reward;
+  term[env] = R.term ? 1.f : 0.f;
+}
+
+struct CarEnvIO {
+  const float* state; float* state_out; float* pre_out;          // [N, CAR_HDR + T]: current, after reset, before reset
+  const float* action; int lda;
+  const float* track; int T, K;
+  const float* start_pose;                                        // [K, 3] x, y, heading at tile 0
+  int* steps; float* ep_return; int* episodes;                    // [N]
+  float* reward; float* done; float* term; float* finished_return; float* ep_stats;
+  float* obs; float* next_obs;                                    // [N, obs_dim] fp32 (may be null)
+  __nv_bfloat16* obs_bf16; __nv_bfloat16* next_obs_bf16; int ld_bf16;   // (may be null)
+  int N, obs_dim, lookahead, stride, max_steps, do_reset;
+  unsigned seed;
+};
+
+__device__ __forceinline__ void car_write_obs(const float* h, const float* tr, int T, int near, int lookahead, int stride,
+                                              float* o32, __nv_bfloat16* o16, int lane) {
+  // 13 values from the header and the speed, then look-ahead points in the car frame (x right, y forward)
+  const float sa = sinf(h[2]), ca = cosf(h[2]);
+  for (int i = lane; i < 13 + 2 * lookahead; i += 32) {
+    float v;
+    if (i < 12) v = h[i];
+    else if (i == 12) v = sqrtf(h[3] * h[3] + h[4] * h[4]);
+    else {
+      const int l = (i - 13) >> 1;
+      const int idx = (near + (1 + l) * stride) % T;
+      const float rx = tr[2 * idx] - h[0], ry = tr[2 * idx + 1] - h[1];
+      v = ((i - 13) & 1) ? (-sa * rx + ca * ry) : (ca * rx + sa * ry);
+    }
+    if (o32) o32[i] = v;
+    if (o16) o16[i] = __float2bfloat16(v);
+  }
+}
+
+// The whole environment step for one lane of the batch per warp: dynamics, reward, time limit, episode statistics,
+// the observation of the successor, the reset (a new track from a counter hash, the start pose of that track, cleared visit
+// flags) and the observation after it.  ``state_out`` may be ``state`` itself: every read of the old row precedes the
+// warp-wide exchange of lane 0's results, every write of the new row follows it.
+__global__ void car_env_step_kernel(CarEnvIO io, CarParams P) {
+  const int env = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (env >= io.N) return;
+  const int T = io.T, S = CAR_HDR + T;
+  const float* s = io.state + (size_t)env * S;
+  float* pre = io.pre_out + (size_t)env * S;
+  float* post = io.state_out + (size_t)env * S;
+  const float* tr = io.track + (size_t)((int)s[12]) * T * 2;
+  CarStepOut R;
+  car_step_warp(s, io.action + (size_t)env * io.lda, tr, T, pre + CAR_HDR, P, lane, R);
+  float h[CAR_HDR];
+#pragma unroll
+  for (int i = 0; i < CAR_HDR; ++i) h[i] = __shfl_sync(0xffffffffu, R.hdr[i], 0);
+  const int term = __shfl_sync(0xffffffffu, R.term, 0);
+  const float reward = __shfl_sync(0xffffffffu, R.reward, 0);
+  const int steps = io.steps[env] + 1;
+  const int done = term || steps >= io.max_steps;
+  // nearest tile to the hull (for the look-ahead points)
+  int near = 0;
+  if (io.lookahead > 0) {
+    float best = 3.4e38f;
+    for (int j = lane; j < T; j += 32) {
+      const float dx = tr[2 * j] - h[0], dy = tr[2 * j + 1] - h[1], d = dx * dx + dy * dy;
+      if (d < best) { best = d; near = j; }
+    }
+#pragma unroll
+    for (int sft = 16; sft; sft >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, sft);
+      const int on = __shfl_xor_sync(0xffffffffu, near, sft);
+      if (ob < best || (ob == best && on < near)) { best = ob; near = on; }
+    }
+  }
+  __syncwarp();                                   // the visit flags of ``pre`` are read back below
+  if (lane < CAR_HDR) pre[lane] = h[lane];
+  car_write_obs(h, tr, T, near, io.lookahead, io.stride, io.next_obs ? io.next_obs + (size_t)env * io.obs_dim : nullptr,
+                io.next_obs_bf16 ? io.next_obs_bf16 + (size_t)env * io.ld_bf16 : nullptr, lane);
+  const bool reset = done && io.do_reset;
+  const float ret = io.ep_return[env] + reward;
+  if (lane == 0) {
+    io.reward[env] = reward;
+    io.term[env] = term ? 1.f : 0.f;
+    io.done[env] = done ? 1.f : 0.f;
+    if (io.ep_stats) {
+      atomicAdd(io.ep_stats + 2, reward);
+      atomicAdd(io.ep_stats + 3, 1.f);
+      if (reset) { atomicAdd(io.ep_stats + 0, ret); atomicAdd(io.ep_stats + 1, 1.f); }
+    }
+    if (reset && io.finished_return) io.finished_return[env] = ret;
+    io.ep_return[env] = reset ? 0.f : ret;
+    io.steps[env] = reset ? 0 : steps;
+  }
+  if (!reset) {
+    for (int j = lane; j < S; j += 32) post[j] = j < CAR_HDR ? h[j] : pre[j];
+    car_write_obs(h, tr, T, near, io.lookahead, io.stride, io.obs ? io.obs + (size_t)env * io.obs_dim : nullptr,
+                  io.obs_bf16 ? io.obs_bf16 + (size_t)env * io.ld_bf16 : nullptr, lane);
+    return;
+  }
+  int ep = 0;
+  if (lane == 0) { ep = io.episodes[env] + 1; io.episodes[env] = ep; }
+  ep = __shfl_sync(0xffffffffu, ep, 0);
+  unsigned z = io.seed * 0x9E3779B9u + (unsigned)env * 0x85EBCA6Bu + (unsigned)ep * 0xC2B2AE35u;    // a counter hash
+  z ^= z >> 16; z *= 0x7FEB352Du; z ^= z >> 15; z *= 0x846CA68Bu; z ^= z >> 16;
+  const int tid = (int)(z % (unsigned)io.K);
+  float g[CAR_HDR];
+#pragma unroll
+  for (int i = 0; i < CAR_HDR; ++i) g[i] = 0.f;
+  g[0] = io.start_pose[3 * tid]; g[1] = io.start_pose[3 * tid + 1]; g[2] = io.start_pose[3 * tid + 2];
+  g[12] = (float)tid;
+  for (int j = lane; j < S; j += 32) post[j] = j < CAR_HDR ? g[j] : 0.f;
+  car_write_obs(g, io.track + (size_t)tid * T * 2, T, 0, io.lookahead, io.stride,
+                io.obs ? io.obs + (size_t)env * io.obs_dim : nullptr,
+                io.obs_bf16 ? io.obs_bf16 + (size_t)env * io.ld_bf16 : nullptr, lane);
 }
 
 // pose = the state rows (x, y, angle first, track id at 12); image [N, res, res], the car at (res/2, cy) heading up
@@ -173,6 +300,32 @@ int nb_car_step(const float* state, const float* action, int lda, const float* t
   for (int w = 0; w < 4; ++w) { P.wheel_x[w] = params[17 + w]; P.wheel_y[w] = params[21 + w]; }
   const int tpb = 128;
   car_step_kernel<<<(N * 32 + tpb - 1) / tpb, tpb, 0, (cudaStream_t)stream>>>(state, action, lda, track, T, next, reward, term, N, P);
+  NB_LAUNCH_CHECK();
+  return NB_OK;
+}
+
+int nb_car_env_step(const void* state, void* state_out, void* pre_out, const void* action, int lda, const void* track, int T, int K,
+                    const void* start_pose, void* steps, void* ep_return, void* episodes, void* reward, void* done, void* term,
+                    void* finished_return, void* ep_stats, void* obs, void* next_obs, void* obs_bf16, void* next_obs_bf16,
+                    int ld_bf16, int N, int obs_dim, int lookahead, int stride, int max_steps, int do_reset, unsigned seed,
+                    const float* params, void* stream) {
+  if (N <= 0 || T <= 0 || K <= 0 || lda < 3 || obs_dim != 13 + 2 * lookahead || state == pre_out || state_out == pre_out)
+    return NB_ERR_BAD_ARG;
+  CarParams P;
+  float* dst = &P.dt;
+  for (int i = 0; i < 17; ++i) dst[i] = params[i];
+  for (int w = 0; w < 4; ++w) { P.wheel_x[w] = params[17 + w]; P.wheel_y[w] = params[21 + w]; }
+  CarEnvIO io;
+  io.state = (const float*)state; io.state_out = (float*)state_out; io.pre_out = (float*)pre_out;
+  io.action = (const float*)action; io.lda = lda; io.track = (const float*)track; io.T = T; io.K = K;
+  io.start_pose = (const float*)start_pose; io.steps = (int*)steps; io.ep_return = (float*)ep_return; io.episodes = (int*)episodes;
+  io.reward = (float*)reward; io.done = (float*)done; io.term = (float*)term; io.finished_return = (float*)finished_return;
+  io.ep_stats = (float*)ep_stats; io.obs = (float*)obs; io.next_obs = (float*)next_obs;
+  io.obs_bf16 = (__nv_bfloat16*)obs_bf16; io.next_obs_bf16 = (__nv_bfloat16*)next_obs_bf16; io.ld_bf16 = ld_bf16;
+  io.N = N; io.obs_dim = obs_dim; io.lookahead = lookahead; io.stride = stride; io.max_steps = max_steps; io.do_reset = do_reset;
+  io.seed = seed;
+  const int tpb = 128;
+  car_env_step_kernel<<<(N * 32 + tpb - 1) / tpb, tpb, 0, (cudaStream_t)stream>>>(io, P);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

@@ -1,9 +1,10 @@
 """Top-down car racing as a batched environment: random closed tracks, a slip-based tire model on a rigid hull, tile-visit
 reward, a 13-value state observation and an ego-centric grey-scale camera with frame stacking.
 
-On CUDA the step is one kernel (``csrc/car_racing.cu::car_step_kernel``: one warp per lane of the batch; the lanes of
-the warp share the track tiles, lane 0 integrates) and the camera another (one CTA per lane of the batch culls the track
-to the view, one thread per pixel).  The same arithmetic written with tensor operations (``_dynamics_tensor``,
+On CUDA the whole environment step is one kernel (``csrc/car_racing.cu::car_env_step_kernel``: one warp per lane of the
+batch; the lanes of the warp share the track tiles, lane 0 integrates; reward, time limit, episode statistics, both
+observations and the reset in the same launch) and the camera another (one CTA per lane of the batch culls the track to
+the view, one thread per pixel).  The same arithmetic written with tensor operations (``_dynamics_tensor``,
 ``_render_tensor``) runs on CPU and is the oracle of the GPU tests.
 
 Physics follows Gymnasium's ``car_dynamics.py`` constants on a single rigid hull, as the reference does
@@ -88,6 +89,11 @@ class CarRacingEnv(_TensorEnv):
         self._cparams = (ctypes.c_float * 25)(*[float(v) for v in self.params.values()], *WHEEL_X, *WHEEL_Y)
         assert list(self.params) == list(PARAMS)
         self.use_kernels = self.device.type == "cuda"
+        d = self.track[:, 1] - self.track[:, 0]
+        self._start_pose = torch.cat([self.track[:, 0], torch.atan2(-d[:, 0], d[:, 1])[:, None]], 1).contiguous()     # [K, 3]
+        self._episodes = torch.zeros(n_envs, dtype=torch.int32, device=self.device)
+        self._spare = None
+        self.seed = int(seed)
 
     # ---- state ---------------------------------------------------------------------------------------------------------
     def _sample_state(self, n):
@@ -123,6 +129,43 @@ class CarRacingEnv(_TensorEnv):
         if self.use_kernels and s.is_cuda:
             return self._dynamics_kernel(s, a)
         return self._dynamics_tensor(s, a)
+
+    # ---- the whole environment step as one kernel (CUDA) -----------------------------------------------------------------
+    def _fused(self) -> bool:
+        return self.use_kernels and self.device.type == "cuda" and self.state is not None
+
+    def step(self, action, reward, done, terminated, obs_f32=None, obs_bf16=None, next_obs_f32=None, next_obs_bf16=None,
+             finished_return=None, do_reset=True, ep_stats=None, dbg=None):
+        """Engine-style step into caller-owned buffers.  On CUDA this is ONE launch: dynamics, reward, time limit, episode
+        statistics, both observations (fp32 and / or padded bf16 rows) and the reset, whose new track comes from a counter
+        hash of (seed, lane, episode)."""
+        if not self._fused():
+            return super().step(action, reward, done, terminated, obs_f32, obs_bf16, next_obs_f32, next_obs_bf16, finished_return,
+                                do_reset, ep_stats, dbg)
+        from .._native import check, cuda_lib, ptr, stream_ptr
+        c = ctypes
+        assert action.dtype == torch.float32 and action.stride(-1) == 1 and self.state.is_contiguous()
+        if self._spare is None or self._spare.shape != self.state.shape:
+            self._spare = torch.empty_like(self.state)
+        out, pre = self.state, self._spare                       # in place: a captured rollout keeps its addresses
+        ld16 = (obs_bf16 if obs_bf16 is not None else next_obs_bf16).stride(0) if (obs_bf16 is not None or next_obs_bf16 is not None) else 0
+        check(cuda_lib().nb_car_env_step(
+            ptr(self.state), ptr(out), ptr(pre), ptr(action), c.c_int(action.stride(0)), ptr(self.track), c.c_int(self.tiles),
+            c.c_int(self.track.shape[0]), ptr(self._start_pose), ptr(self.steps), ptr(self.ep_return), ptr(self._episodes), ptr(reward),
+            ptr(done), ptr(terminated), ptr(finished_return), ptr(ep_stats), ptr(obs_f32), ptr(next_obs_f32), ptr(obs_bf16),
+            ptr(next_obs_bf16), c.c_int(ld16), c.c_int(self.n_envs), c.c_int(self.obs_dim), c.c_int(self.lookahead),
+            c.c_int(self.lookahead_stride), c.c_int(self.max_steps), c.c_int(1 if do_reset else 0), c.c_uint(self.seed & 0xFFFFFFFF),
+            self._cparams, stream_ptr()), "car_env_step")
+        self.pre_reset_state = pre
+
+    def step_batch(self, action, auto_reset: bool = True):
+        if not self._fused():
+            return super().step_batch(action, auto_reset)
+        a = action.to(self.device, torch.float32)
+        a = a if (a.dim() == 2 and a.stride(-1) == 1) else a.reshape(self.n_envs, -1).contiguous()
+        self.step(a, self.reward, self.done, self.terminated, obs_f32=self.obs, next_obs_f32=self.next_obs,
+                  finished_return=self.finished_return, do_reset=auto_reset, ep_stats=self.ep_stats)
+        return self.obs, self.reward, self.done, self.terminated
 
     def _dynamics_kernel(self, s, a):
         from .._native import check, cuda_lib, ptr, stream_ptr

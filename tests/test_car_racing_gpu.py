@@ -66,3 +66,51 @@ def test_ppo_drives_the_tensor_environment_through_its_engine_surface():
         m = tr.train_iteration()
     assert all(torch.isfinite(torch.as_tensor(float(m[k]))) for k in ("policy_loss", "value_loss", "entropy", "mean_step_reward"))
     assert float(env.state[:, 13].max()) >= 1                                # cars moved over at least a tile
+
+
+def test_fused_environment_step_matches_the_tensor_program_including_resets():
+    """One launch per step: dynamics, reward, time limit, statistics, both observations and the reset, against the same step
+    assembled from the tensor program (the reset's track choice is read back from the kernel's new state)."""
+    from noeira_b200.envs.car_racing import HDR, CarRacingEnv, scripted_driver
+    from noeira_b200.ops import check_status
+    N = 96
+    k = CarRacingEnv(N, device="cuda", seed=4, lookahead=5, n_tracks=6)
+    e = CarRacingEnv(N, device="cuda", seed=4, lookahead=5, n_tracks=6)
+    e.use_kernels = False
+    k.max_steps = 37                                                   # time-limit resets within the test
+    k.reset_batch()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n_done, r_sum = 0, 0.0
+    for step in range(100):
+        a = scripted_driver(k, target_speed=45.0) + 0.3 * torch.randn(N, 3, device="cuda", generator=g)
+        s, steps, ret = k.state.clone(), k.steps.clone(), k.ep_return.clone()
+        obs, r, d, tm = k.step_batch(a)
+        s2, r_ref, t_ref = e._dynamics_tensor(s, a)
+        done_ref = t_ref | (steps + 1 >= 37)
+        assert torch.equal(d > 0.5, done_ref) and torch.equal(tm > 0.5, t_ref) and (r - r_ref).abs().max() < 1e-4, step
+        tol = 2e-3 * max(1.0, float(s2[:, :16].abs().max()))
+        assert (k.pre_reset_state[:, :16] - s2[:, :16]).abs().max() < tol and torch.equal(k.pre_reset_state[:, 16:], s2[:, 16:])
+        assert (k.next_obs - e._observe(k.pre_reset_state)).abs().max() < 1e-3
+        assert (k.obs - e._observe(k.state)).abs().max() < 1e-3
+        keep = ~done_ref
+        assert torch.equal(k.state[keep], k.pre_reset_state[keep])
+        if done_ref.any():
+            new = k.state[done_ref]
+            tid = new[:, 12].long()
+            assert (tid >= 0).all() and (tid < 6).all() and torch.equal(new[:, 0:2], k.track[tid, 0])
+            assert float(new[:, 3:12].abs().max()) == 0 and float(new[:, 13:].abs().sum()) == 0
+            assert float(k.steps[done_ref].abs().max()) == 0 and float(k.ep_return[done_ref].abs().max()) == 0
+            assert (k.finished_return[done_ref] - (ret + r)[done_ref]).abs().max() < 1e-3
+        assert torch.equal(k.steps[keep], steps[keep] + 1)
+        n_done += int(done_ref.sum())
+        r_sum += float(r.sum())
+    torch.cuda.synchronize()
+    check_status()
+    st = k.ep_stats.tolist()
+    assert n_done >= 2 * N and st[1] == n_done and st[3] == 100 * N and abs(st[2] - r_sum) < 1e-3 * max(1.0, abs(r_sum))
+    assert len(torch.unique(k.state[:, 12])) > 1                        # resets draw different tracks
+    # bf16 rows for the on-policy trainer
+    ob, nb = torch.zeros(N, 64, device="cuda", dtype=torch.bfloat16), torch.zeros(N, 64, device="cuda", dtype=torch.bfloat16)
+    k.step(a, k.reward, k.done, k.terminated, obs_bf16=ob, next_obs_bf16=nb, ep_stats=k.ep_stats)
+    assert (ob[:, :23].float() - e._observe(k.state)).abs().max() < 0.02 * max(1.0, float(e._observe(k.state).abs().max()))
+    assert float(ob[:, 23:].abs().max()) == 0
