@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--res", type=int, default=96)
     ap.add_argument("--ppo-iters", type=int, default=0)
+    ap.add_argument("--graphs", type=int, default=1, help="replay the PPO rollout and update from CUDA graphs")
     args = ap.parse_args()
     from noeira_b200.envs.car_racing import CarRacingEnv, scripted_driver
     env = CarRacingEnv(args.envs, device="cuda", seed=0, lookahead=8)
@@ -52,12 +53,13 @@ def main():
     if args.ppo_iters:
         from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
         tr = PPOTrainer(env, PPOConfig(n_envs=args.envs, rollout_len=32, n_epochs=4, n_minibatches=8, hidden=256, entropy_coef=1e-3,
-                                       use_cuda_graphs=False))
+                                       use_cuda_graphs=bool(args.graphs)))
         curve = []
         for it in range(args.ppo_iters):
             m = tr.train_iteration()
             if it % max(1, args.ppo_iters // 8) == 0 or it == args.ppo_iters - 1:
                 curve.append((it, round(float(m["mean_step_reward"]), 4)))
+        out["graphs"] = bool(args.graphs)
         out["ppo_iteration_ms"] = timed(lambda: tr.train_iteration(read_metrics=False), 5)
         out["ppo_env_steps_per_s"] = args.envs * 32 / out["ppo_iteration_ms"] * 1e3
         out["ppo_reward_per_step"] = curve

@@ -26,9 +26,8 @@ def main():
         total += r
     print(f"scripted driver: return over 1000 steps {float(total.mean()):.1f}, tiles visited {float(ref.visited_fraction().mean()):.2f}")
     env = CarRacingEnv(args.envs, device="cuda", seed=0, lookahead=8)
-    # the environment is a tensor program around its step kernel, stepped eagerly (no graph capture of the rollout)
-    tr = PPOTrainer(env, PPOConfig(n_envs=args.envs, rollout_len=64, n_epochs=4, n_minibatches=8, hidden=256, entropy_coef=1e-3,
-                                   use_cuda_graphs=False))
+    # the environment step is one kernel launch that works in place, so the whole rollout replays from a CUDA graph
+    tr = PPOTrainer(env, PPOConfig(n_envs=args.envs, rollout_len=64, n_epochs=4, n_minibatches=8, hidden=256, entropy_coef=1e-3))
     for it in range(args.iterations):
         m = tr.train_iteration()
         if it % 10 == 9:

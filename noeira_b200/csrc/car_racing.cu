@@ -1,5 +1,5 @@
 // Top-down car racing: one fused step kernel (tile test + tire model + rigid hull, one warp per lane of the batch) and the
-// ego-centric grey-scale camera (one CTA per lane: cull the track to the view, then one thread per pixel).
+// ego-centric grey-scale camera (one CTA per lane: cull the track to the view, then to blocks of 8 x 8 pixels, one warp each).
 // The tire model is the slip model of Gymnasium's car_dynamics.py on a single rigid hull, as the reference's
 // noeira/physics2d/car/ does (wheel_friction.mojo, car_dynamics.mojo); the image palette (grass 0.3, road 0.7, car 1.0)
 // follows noeira/envs/car_racing/car_racing_pixel.mojo.
@@ -272,17 +272,45 @@ __global__ void car_render_kernel(const float* __restrict__ state, int S, const 
   __syncthreads();
   const int n = nseg;
   const float w2 = half_width * half_width;
-  for (int p = threadIdx.x; p < res * res; p += blockDim.x) {
-    const int i = p / res, j = p - i * res;
-    const float lx = ((float)j + 0.5f - 0.5f * (float)res) / px_per_unit, ly = (cy - ((float)i + 0.5f)) / px_per_unit;
-    float v = 0.3f;
-    if (fabsf(lx) <= car_hw && fabsf(ly) <= car_hl) v = 1.0f;
-    else {
-      const float qx = x + ca * lx - sa * ly, qy = y + sa * lx + ca * ly;
-      for (int k = 0; k < n; ++k)
-        if (seg_dist2(qx, qy, seg[4 * k], seg[4 * k + 1], seg[4 * k + 2], seg[4 * k + 3]) <= w2) { v = 0.7f; break; }
+  // second level of culling: the image in blocks of 8 x 8 pixels, one warp per block.  The lanes test the view's segments
+  // against the block's circumscribed circle (grown by the road's half width) and compact the survivors into the warp's
+  // list; most blocks of grass keep none, blocks of road two or three, so a pixel tests a handful of segments.
+  int* mine = reinterpret_cast<int*>(seg + 4 * T) + (threadIdx.x >> 5) * T;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int nb = (res + 7) >> 3;
+  const float rb = 5.657f / px_per_unit + half_width;                  // half diagonal of 8 pixels, in world units
+  for (int b = warp; b < nb * nb; b += nwarp) {
+    const int by = b / nb, bx = b - by * nb;
+    const float clx = ((float)(bx * 8 + 4) - 0.5f * (float)res) / px_per_unit, cly = (cy - (float)(by * 8 + 4)) / px_per_unit;
+    const float bcx = x + ca * clx - sa * cly, bcy = y + sa * clx + ca * cly;
+    int m = 0;
+    for (int k0 = 0; k0 < n; k0 += 32) {
+      const int k = k0 + lane;
+      const bool hit = k < n && seg_dist2(bcx, bcy, seg[4 * k], seg[4 * k + 1], seg[4 * k + 2], seg[4 * k + 3]) <= rb * rb;
+      const unsigned bal = __ballot_sync(0xffffffffu, hit);
+      if (hit) mine[m + __popc(bal & ((1u << lane) - 1u))] = k;
+      m += __popc(bal);
     }
-    img[(size_t)env * res * res + p] = v;
+    __syncwarp();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int p = lane + 32 * half;
+      const int i = by * 8 + (p >> 3), j = bx * 8 + (p & 7);
+      if (i < res && j < res) {
+        const float lx = ((float)j + 0.5f - 0.5f * (float)res) / px_per_unit, ly = (cy - ((float)i + 0.5f)) / px_per_unit;
+        float v = 0.3f;
+        if (fabsf(lx) <= car_hw && fabsf(ly) <= car_hl) v = 1.0f;
+        else {
+          const float qx = x + ca * lx - sa * ly, qy = y + sa * lx + ca * ly;
+          for (int q = 0; q < m; ++q) {
+            const int k = mine[q];
+            if (seg_dist2(qx, qy, seg[4 * k], seg[4 * k + 1], seg[4 * k + 2], seg[4 * k + 3]) <= w2) { v = 0.7f; break; }
+          }
+        }
+        img[(size_t)env * res * res + (size_t)i * res + j] = v;
+      }
+    }
+    __syncwarp();
   }
 }
 
@@ -332,8 +360,8 @@ int nb_car_env_step(const void* state, void* state_out, void* pre_out, const voi
 
 int nb_car_render(const float* state, int S, const float* track, int T, float* img, int N, int res, float px_per_unit,
                   float cy, float half_width, float car_hw, float car_hl, void* stream) {
-  if (N <= 0 || T <= 0 || res <= 0 || (size_t)T * 16 > 48 * 1024) return NB_ERR_BAD_ARG;
-  car_render_kernel<<<N, 256, (size_t)T * 16, (cudaStream_t)stream>>>(state, S, track, T, img, res, px_per_unit, cy, half_width,
+  if (N <= 0 || T <= 0 || res <= 0 || (size_t)T * 48 > 48 * 1024) return NB_ERR_BAD_ARG;
+  car_render_kernel<<<N, 256, (size_t)T * 16 + 8 * (size_t)T * 4, (cudaStream_t)stream>>>(state, S, track, T, img, res, px_per_unit, cy, half_width,
                                                                      car_hw, car_hl);
   NB_LAUNCH_CHECK();
   return NB_OK;
