@@ -114,3 +114,16 @@ def test_fused_environment_step_matches_the_tensor_program_including_resets():
     k.step(a, k.reward, k.done, k.terminated, obs_bf16=ob, next_obs_bf16=nb, ep_stats=k.ep_stats)
     assert (ob[:, :23].float() - e._observe(k.state)).abs().max() < 0.02 * max(1.0, float(e._observe(k.state).abs().max()))
     assert float(ob[:, 23:].abs().max()) == 0
+
+
+def test_ppo_learns_to_drive_from_captured_rollouts():
+    """The in-place fused step lets rollout and update replay from CUDA graphs; 130 iterations of 32 x 4096 steps take the
+    reward per step from the idle level (about −0.1 + the first tiles) to several tiles per ten steps."""
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs.car_racing import CarRacingEnv
+    env = CarRacingEnv(4096, device="cuda", seed=0, lookahead=8)
+    tr = PPOTrainer(env, PPOConfig(n_envs=4096, rollout_len=32, n_epochs=4, n_minibatches=8, hidden=256, entropy_coef=1e-3, seed=0))
+    hist = [float(tr.train_iteration()["mean_step_reward"]) for _ in range(130)]
+    early, late = sum(hist[10:30]) / 20, sum(hist[-10:]) / 10
+    assert tr._graphs and late > 0.4 and late > early + 0.3, (early, late)
+    assert float(env.visited_fraction().max()) > 0.3
