@@ -71,6 +71,10 @@ class PPOTrainer:
         self.env = env
         self.cfg = cfg = cfg or PPOConfig(n_envs=env.n_envs)
         assert cfg.n_envs == env.n_envs
+        if cfg.use_cuda_graphs and not getattr(env, "graph_safe", True):
+            # an environment stepped by tensor operations with its own random generator cannot sit in a captured stream
+            import dataclasses
+            self.cfg = cfg = dataclasses.replace(cfg, use_cuda_graphs=False)
         self.device = env.device
         self.lib = cuda_lib()
         nn.manual_seed(cfg.seed)

@@ -131,6 +131,10 @@ class CarRacingEnv(_TensorEnv):
         return self._dynamics_tensor(s, a)
 
     # ---- the whole environment step as one kernel (CUDA) -----------------------------------------------------------------
+    @property
+    def graph_safe(self) -> bool:
+        return self.use_kernels and self.device.type == "cuda"   # one in-place launch with a counter-hash generator
+
     def _fused(self) -> bool:
         return self.use_kernels and self.device.type == "cuda" and self.state is not None
 

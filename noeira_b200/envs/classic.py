@@ -17,6 +17,7 @@ from .batched_env import BatchedEnv
 class _TensorEnv(BatchedEnv):
     obs_dim = act_dim = 0
     max_steps = 200
+    graph_safe = False           # steps are tensor operations drawing from the environment's own generator
 
     def __init__(self, n_envs: int, device="cpu", seed: int = 0):
         self.n_envs, self.device = int(n_envs), torch.device(device)

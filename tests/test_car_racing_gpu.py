@@ -127,3 +127,13 @@ def test_ppo_learns_to_drive_from_captured_rollouts():
     early, late = sum(hist[10:30]) / 20, sum(hist[-10:]) / 10
     assert tr._graphs and late > 0.4 and late > early + 0.3, (early, late)
     assert float(env.visited_fraction().max()) > 0.3
+
+
+def test_ppo_steps_a_classic_tensor_environment_without_graphs():
+    from noeira_b200.agents.ppo import PPOConfig, PPOTrainer
+    from noeira_b200.envs import PendulumEnv
+    env = PendulumEnv(512, device="cuda", seed=0)
+    tr = PPOTrainer(env, PPOConfig(n_envs=512, rollout_len=16, n_epochs=2, n_minibatches=4, seed=0))
+    assert tr.cfg.use_cuda_graphs is False                          # the environment declares itself unsafe to capture
+    m = [tr.train_iteration() for _ in range(3)][-1]
+    assert torch.isfinite(torch.as_tensor(float(m["policy_loss"]))) and -17.0 < float(m["mean_step_reward"]) < 0.0
