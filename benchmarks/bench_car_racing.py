@@ -47,6 +47,7 @@ def main():
     out["step_kernel_ms"] = timed(lambda: env._dynamics(env.state, a), args.iters)
     out["env_step_ms"] = timed(lambda: env.step_batch(a), args.iters)
     out["render_ms"] = timed(lambda: env.render(args.res), args.iters)
+    out["render_uint8_ms"] = timed(lambda: env.render(args.res, uint8=True), args.iters)
     out["env_steps_per_s"] = args.envs / out["env_step_ms"] * 1e3
     out["frames_per_s"] = args.envs / out["render_ms"] * 1e3
     out["render_write_gbs"] = args.envs * args.res * args.res * 4 / out["render_ms"] / 1e6

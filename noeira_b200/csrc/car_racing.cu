@@ -244,8 +244,9 @@ __global__ void car_env_step_kernel(CarEnvIO io, CarParams P) {
 }
 
 // pose = the state rows (x, y, angle first, track id at 12); image [N, res, res], the car at (res/2, cy) heading up
+template <typename Pix>
 __global__ void car_render_kernel(const float* __restrict__ state, int S, const float* __restrict__ track, int T,
-                                  float* __restrict__ img, int res, float px_per_unit, float cy, float half_width,
+                                  Pix* __restrict__ img, int res, float px_per_unit, float cy, float half_width,
                                   float car_hw, float car_hl) {
   extern __shared__ float seg[];   // culled segments: ax ay bx by
   __shared__ int nseg;
@@ -307,7 +308,7 @@ __global__ void car_render_kernel(const float* __restrict__ state, int S, const 
             if (seg_dist2(qx, qy, seg[4 * k], seg[4 * k + 1], seg[4 * k + 2], seg[4 * k + 3]) <= w2) { v = 0.7f; break; }
           }
         }
-        img[(size_t)env * res * res + (size_t)i * res + j] = v;
+        img[(size_t)env * res * res + (size_t)i * res + j] = sizeof(Pix) == 1 ? (Pix)(v * 255.f + 0.5f) : (Pix)v;
       }
     }
     __syncwarp();
@@ -358,11 +359,17 @@ int nb_car_env_step(const void* state, void* state_out, void* pre_out, const voi
   return NB_OK;
 }
 
-int nb_car_render(const float* state, int S, const float* track, int T, float* img, int N, int res, float px_per_unit,
-                  float cy, float half_width, float car_hw, float car_hl, void* stream) {
+// img: fp32 values 0.3 / 0.7 / 1.0, or with ``u8`` bytes 77 / 179 / 255
+int nb_car_render(const float* state, int S, const float* track, int T, void* img, int N, int res, float px_per_unit,
+                  float cy, float half_width, float car_hw, float car_hl, int u8, void* stream) {
   if (N <= 0 || T <= 0 || res <= 0 || (size_t)T * 48 > 48 * 1024) return NB_ERR_BAD_ARG;
-  car_render_kernel<<<N, 256, (size_t)T * 16 + 8 * (size_t)T * 4, (cudaStream_t)stream>>>(state, S, track, T, img, res, px_per_unit, cy, half_width,
-                                                                     car_hw, car_hl);
+  const size_t smem = (size_t)T * 16 + 8 * (size_t)T * 4;
+  if (u8)
+    car_render_kernel<unsigned char><<<N, 256, smem, (cudaStream_t)stream>>>(state, S, track, T, (unsigned char*)img, res, px_per_unit,
+                                                                            cy, half_width, car_hw, car_hl);
+  else
+    car_render_kernel<float><<<N, 256, smem, (cudaStream_t)stream>>>(state, S, track, T, (float*)img, res, px_per_unit, cy, half_width,
+                                                                    car_hw, car_hl);
   NB_LAUNCH_CHECK();
   return NB_OK;
 }

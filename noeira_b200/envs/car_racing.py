@@ -230,21 +230,23 @@ class CarRacingEnv(_TensorEnv):
         return s2, r, out | lap
 
     # ---- camera --------------------------------------------------------------------------------------------------------
-    def render(self, res: int = 96, state=None) -> torch.Tensor:
+    def render(self, res: int = 96, state=None, uint8: bool = False) -> torch.Tensor:
         """Ego-centric grey-scale image [N, res, res]: the car at (res / 2, 3 res / 4) heading up, Gymnasium's zoom
-        (2.7 · 6 pixels per unit in a 1000-pixel window, scaled to ``res``)."""
+        (2.7 · 6 pixels per unit in a 1000-pixel window, scaled to ``res``).  fp32 values 0.3 / 0.7 / 1.0, or with ``uint8``
+        the bytes 77 / 179 / 255 (a quarter of the memory traffic, what a replay buffer of frames stores)."""
         s = self.state if state is None else state
         ppu, cy = 2.7 * SCALE * res / 1000.0, 0.75 * res
         if self.use_kernels and s.is_cuda:
             from .._native import check, cuda_lib, ptr, stream_ptr
             s = s.contiguous()
-            img = torch.empty(s.shape[0], res, res, device=s.device)
+            img = torch.empty(s.shape[0], res, res, device=s.device, dtype=torch.uint8 if uint8 else torch.float32)
             c_f = ctypes.c_float
             check(cuda_lib().nb_car_render(ptr(s), ctypes.c_int(s.shape[1]), ptr(self.track), ctypes.c_int(self.tiles), ptr(img),
                                            ctypes.c_int(s.shape[0]), ctypes.c_int(res), c_f(ppu), c_f(cy), c_f(self.params["half_width"]),
-                                           c_f(CAR_HW), c_f(CAR_HL), stream_ptr()), "car_render")
+                                           c_f(CAR_HW), c_f(CAR_HL), ctypes.c_int(1 if uint8 else 0), stream_ptr()), "car_render")
             return img
-        return self._render_tensor(s, res, ppu, cy)
+        img = self._render_tensor(s, res, ppu, cy)
+        return (img * 255.0 + 0.5).to(torch.uint8) if uint8 else img
 
     def _render_tensor(self, s, res, ppu, cy):
         dev = s.device

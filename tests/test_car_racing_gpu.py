@@ -42,6 +42,8 @@ def test_camera_kernel_matches_the_tensor_program():
         # pixels whose centre lies within rounding of the road edge may differ
         assert (a != b).float().mean() < 2e-3
         assert (a == 0.7).float().mean() > 0.1 and (a == 1.0).any()
+        u = env.render(res, uint8=True)
+        assert u.dtype == torch.uint8 and torch.equal(u, (a * 255.0 + 0.5).to(torch.uint8)) and set(u.unique().tolist()) <= {77, 179, 255}
 
 
 def test_full_environment_loop_with_resets_and_pixels():
