@@ -82,3 +82,26 @@ def test_ilqr_swings_pendulum_to_target():
     _, _, J1 = lin.plan(x0, iterations=1)
     _, _, J5 = lin.plan(x0, iterations=5)
     assert abs(J1 - J5) < 1e-6 * max(1.0, J5)
+
+
+def test_tensor_environments_offer_the_engine_style_step():
+    """What the on-policy trainer drives: ``env.engine.step`` into caller-owned reward / done rows and padded bf16
+    observation rows, with the reset applied by masks (no host read inside the step)."""
+    import torch
+    from noeira_b200.envs import CarRacingEnv, PendulumEnv
+    for env in (PendulumEnv(16, seed=0), CarRacingEnv(16, seed=0, lookahead=2)):
+        env.max_steps = 5
+        env.reset_batch()
+        assert env.engine is env and env.obs_pad == 64 and env.graph_safe is False
+        first = env.obs_bf16
+        assert first.shape == (16, 64) and first.dtype == torch.bfloat16 and float(first[:, env.obs_dim:].abs().max()) == 0
+        r, d, t = torch.zeros(16), torch.zeros(16), torch.zeros(16)
+        ob, nb = torch.zeros(16, 64, dtype=torch.bfloat16), torch.zeros(16, 64, dtype=torch.bfloat16)
+        a = torch.zeros(16, 8)                                         # padded action rows
+        for k in range(5):
+            env.engine.step(a, r, d, t, obs_bf16=ob, next_obs_bf16=nb, ep_stats=env.ep_stats)
+            assert torch.equal(ob[:, : env.obs_dim].float(), env.obs.to(torch.bfloat16).float())
+            assert torch.equal(nb[:, : env.obs_dim].float(), env.next_obs.to(torch.bfloat16).float())
+        assert float(d.min()) == 1.0 and float(t.max()) == 0.0           # the time limit ended every lane, none terminated
+        assert int(env.steps.max()) == 0 and float(env.ep_stats[1]) == 16 and float(env.ep_stats[3]) == 80
+        assert not torch.equal(ob, nb)                                 # the row after the reset differs from the successor's
