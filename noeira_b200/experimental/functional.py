@@ -240,7 +240,9 @@ class FModule:
         self.tape, self.module, self.name = tape, module, name
 
     def __call__(self, *xs: FTensor) -> FTensor:
-        y = self.module.forward(*[x.value for x in xs])
+        # on CUDA the activations of ``nn`` modules are bf16 rows (their kernels read nothing else); the tape's are fp32
+        cuda = self.tape.device.type == "cuda"
+        y = self.module.forward(*[(x.value.to(torch.bfloat16) if cuda and x.value.is_floating_point() else x.value) for x in xs])
         return self.tape._record("module", tuple(xs), y.float() if y.dtype != torch.float32 else y, saved=self.module)
 
 
@@ -479,7 +481,7 @@ def _bw_gather(n):
 
 def _bw_module(n):
     mod = n.saved
-    dx = mod.vjp(n.grad)
+    dx = mod.vjp(n.grad.to(torch.bfloat16).contiguous() if n.grad.is_cuda else n.grad)
     dxs = dx if isinstance(dx, (tuple, list)) else (dx,)
     for i, d in zip(n.inputs, dxs):
         if d is not None:

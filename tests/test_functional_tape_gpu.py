@@ -45,3 +45,26 @@ def test_cuda_tape_matches_the_cpu_tape_and_trains():
         opt.step()
         first = first if first is not None else loss.item()
     assert loss.item() < 0.7 * first
+
+
+def test_module_node_on_cuda_runs_in_the_modules_activation_dtype():
+    """An ``nn`` module inside a CUDA tape gets bf16 rows (what its kernels read) and hands fp32 back to the tape."""
+    from noeira_b200 import nn
+    from noeira_b200.experimental.functional import F, Tape
+    g = torch.Generator().manual_seed(0)
+    x, y = torch.randn(256, 64, generator=g), torch.randn(256, 8, generator=g)
+    res = {}
+    for dev in ("cpu", "cuda"):
+        nn.manual_seed(3)
+        t = Tape(device=dev, seed=2)
+        net = t.module(nn.Sequential(nn.Linear(64, 64, act="tanh"), nn.LayerNorm(64)), "net")
+        w = t.param(64, 8, "xavier", name="w")
+        loss = F.mse(F.linear(net(t.constant(x.to(dev))), w), y.to(dev))
+        loss.backward()
+        res[dev] = (loss.item(), {n: p.grad.detach().float().cpu().clone() for n, p in t.named_params()})
+    torch.cuda.synchronize()
+    assert abs(res["cpu"][0] - res["cuda"][0]) < 0.03 * abs(res["cpu"][0])
+    for n, gc in res["cpu"][1].items():
+        gg = res["cuda"][1][n][tuple(slice(0, k) for k in gc.shape)]
+        cos = float((gc * gg).sum() / (gc.norm() * gg.norm()).clamp_min(1e-30))
+        assert cos > 0.99, (n, cos)
