@@ -243,7 +243,7 @@ class FModule:
         # on CUDA the activations of ``nn`` modules are bf16 rows (their kernels read nothing else); the tape's are fp32
         cuda = self.tape.device.type == "cuda"
         y = self.module.forward(*[(x.value.to(torch.bfloat16) if cuda and x.value.is_floating_point() else x.value) for x in xs])
-        return self.tape._record("module", tuple(xs), y.float() if y.dtype != torch.float32 else y, saved=self.module)
+        return self.tape._record("module", tuple(xs), y.float() if y.dtype != torch.float32 else y, saved=self.module, force=True)
 
 
 class Tape:
@@ -323,8 +323,9 @@ class Tape:
         """Drop the nodes of the step; parameters and modules stay."""
         self.nodes.clear()
 
-    def _record(self, op, inputs, value, saved=None) -> FTensor:
-        needs = self._grad_on and any(i.node.needs_grad for i in inputs)
+    def _record(self, op, inputs, value, saved=None, force: bool = False) -> FTensor:
+        """``force``: the node holds parameters of its own (a module), so it is recorded even on constant inputs."""
+        needs = self._grad_on and (force or any(i.node.needs_grad for i in inputs))
         node = _Node(op, tuple(i.node for i in inputs), value, saved if needs else None, needs_grad=needs)
         if needs:
             self.nodes.append(node)

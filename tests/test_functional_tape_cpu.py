@@ -94,6 +94,12 @@ def test_module_bridge_matches_the_modules_own_backward():
     for (n1, p1), (n2, p2) in zip(ref.named_params(), tape.named_params()):
         assert n2 == "net." + n1 and torch.allclose(p1.grad, p2.grad, atol=1e-6), n1
     assert xin.grad.shape == x.shape and abs(loss.item() - float((y ** 2).mean())) < 1e-6
+    # a module on a CONSTANT input is still recorded: its own parameters need the reverse pass
+    tape.reset()
+    tape.zero_grad()
+    (net(tape.constant(x)) ** 2.0).mean().backward()
+    for (n1, p1), (_, p2) in zip(ref.named_params(), tape.named_params()):
+        assert torch.allclose(p1.grad, p2.grad, atol=1e-6), n1
 
 
 def test_training_with_the_arena_optimizer_reset_and_no_grad():
